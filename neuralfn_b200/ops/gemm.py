@@ -1,0 +1,95 @@
+"""BF16 GEMM family on tcgen05/TMEM with fused epilogues (Python front-end).
+
+``gemm(a, b)`` computes ``opA @ opB^T`` where each operand is stored either
+K-major (``[rows, K]``) or MN-major (``[K, rows]``); this gives the three linear
+layer products without transposes:
+
+* forward          ``y = x @ w.T``      -> ``gemm(x, w)``
+* input gradient   ``dx = dy @ w``      -> ``gemm(dy, w, b_mn=True)``
+* weight gradient  ``dw = dy.T @ x``    -> ``gemm(dy, x, a_mn=True, b_mn=True)``
+
+Reference counterpart: the linear kernels and cuBLASLt call sites of
+neuralfn/csrc/tile_cuda/kernels.cu:16746-17574.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+EPI_BIAS = 1 << 0
+EPI_SAVE_PRE = 1 << 1
+EPI_RESID = 1 << 2
+EPI_DACT = 1 << 3
+EPI_ACCUM = 1 << 4
+EPI_OUT_F32 = 1 << 5
+EPI_ACT_SHIFT = 8
+ACT_IDS = {"none": 0, None: 0, "gelu_tanh": 1, "gelu": 1, "gelu_erf": 2, "silu": 3, "relu2": 4,
+           "tanh_cap": 5}
+
+
+def _check2d(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be 2-D with a contiguous last dimension, got "
+                         f"shape={tuple(t.shape)} stride={t.stride()}")
+    if t.dtype != torch.bfloat16:
+        raise ValueError(f"{name} must be bfloat16")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         bias: torch.Tensor | None = None, act: str | None = None, act_param: float = 0.0,
+         save_pre: torch.Tensor | None = None, resid: torch.Tensor | None = None,
+         dact_pre: torch.Tensor | None = None, accum: bool = False,
+         out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
+         alpha: float = 1.0) -> torch.Tensor:
+    _check2d(a, "a")
+    _check2d(b, "b")
+    if a_mn:
+        k, m = a.shape
+    else:
+        m, k = a.shape
+    if b_mn:
+        kb, n = b.shape
+    else:
+        n, kb = b.shape
+    if kb != k:
+        raise ValueError(f"contraction mismatch: {k} vs {kb}")
+    if out is None:
+        out = torch.empty((m, n), device=a.device, dtype=out_dtype)
+    if out.shape != (m, n) or out.stride(1) != 1:
+        raise ValueError("bad out tensor")
+    flags = ACT_IDS[act] << EPI_ACT_SHIFT
+    args = _lib.GemmArgs()
+    args.a, args.b, args.c = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.m, args.n, args.k = m, n, k
+    args.lda, args.ldb, args.ldc = a.stride(0), b.stride(0), out.stride(0)
+    args.a_mn, args.b_mn = int(a_mn), int(b_mn)
+    args.alpha, args.act_param = alpha, act_param
+    if bias is not None:
+        if bias.dtype != torch.bfloat16 or bias.numel() != n:
+            raise ValueError("bias must be bf16 [N]")
+        flags |= EPI_BIAS
+        args.bias = bias.data_ptr()
+    if save_pre is not None:
+        flags |= EPI_SAVE_PRE
+        args.aux_out, args.ld_aux_out = save_pre.data_ptr(), save_pre.stride(0)
+    if resid is not None:
+        _check2d(resid, "resid")
+        flags |= EPI_RESID
+        args.aux_in, args.ld_aux_in = resid.data_ptr(), resid.stride(0)
+    if dact_pre is not None:
+        _check2d(dact_pre, "dact_pre")
+        flags |= EPI_DACT
+        args.aux_in, args.ld_aux_in = dact_pre.data_ptr(), dact_pre.stride(0)
+    if accum:
+        flags |= EPI_ACCUM
+    if out.dtype == torch.float32:
+        flags |= EPI_OUT_F32
+    elif out.dtype != torch.bfloat16:
+        raise ValueError("out must be bf16 or fp32")
+    args.flags = flags
+    rc = _lib.load().nfn_gemm_bf16(ctypes.byref(args), ctypes.c_void_p(_lib.stream_ptr()))
+    _lib.check(rc, "nfn_gemm_bf16")
+    return out
