@@ -1,0 +1,257 @@
+"""Python front-ends of the non-GEMM kernels in ``libnfn_b200_kernels.so``.
+
+All functions take CUDA tensors, launch on the current stream and return/modify
+tensors; none of them synchronises. Argument checking lives here (shape, dtype,
+contiguity) so the C side only sees validated raw pointers.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_void_p, c_int, c_float, c_longlong, c_double
+
+import torch
+
+from . import _lib
+
+_bf16 = torch.bfloat16
+
+
+def _p(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _st() -> c_void_p:
+    return c_void_p(_lib.stream_ptr())
+
+
+def _need(t: torch.Tensor, dtype, name: str) -> None:
+    if t.dtype != dtype or not t.is_contiguous():
+        raise ValueError(f"{name}: expected contiguous {dtype}, got {t.dtype} stride={t.stride()}")
+
+
+# --------------------------------------------------------------------- norms --
+NORM_LAYER, NORM_RMS = 0, 1
+
+
+def norm_forward(x, weight, bias, *, eps: float, mode: int, centered: bool = False,
+                 out=None, mean=None, rstd=None):
+    """x: bf16 [rows, C]. Returns (y, mean, rstd); stats are fp32 [rows]."""
+    _need(x, _bf16, "x")
+    rows, C = x.shape
+    y = torch.empty_like(x) if out is None else out
+    if mean is None and mode == NORM_LAYER:
+        mean = torch.empty(rows, device=x.device, dtype=torch.float32)
+    if rstd is None:
+        rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+    rc = _lib.load().nfn_norm_forward(_p(x), _p(weight), _p(bias), _p(y), _p(mean), _p(rstd),
+                                      c_int(rows), c_int(C), c_float(eps), c_int(mode),
+                                      c_int(int(centered)), _st())
+    _lib.check(rc, "nfn_norm_forward")
+    return y, mean, rstd
+
+
+def norm_backward_dx(dy, x, weight, mean, rstd, *, mode: int, centered: bool = False,
+                     dresid=None, out=None):
+    _need(dy, _bf16, "dy")
+    _need(x, _bf16, "x")
+    rows, C = x.shape
+    dx = torch.empty_like(x) if out is None else out
+    rc = _lib.load().nfn_norm_backward_dx(_p(dy), _p(x), _p(weight), _p(mean), _p(rstd), _p(dresid),
+                                          _p(dx), c_int(rows), c_int(C), c_int(mode),
+                                          c_int(int(centered)), _st())
+    _lib.check(rc, "nfn_norm_backward_dx")
+    return dx
+
+
+def norm_backward_wb(dy, x, mean, rstd, dweight, dbias, scratch, *, mode: int, accumulate: bool = False):
+    """dweight/dbias: bf16 [C] (either may be None). scratch: fp32 >= 64*2*C."""
+    rows, C = x.shape
+    if scratch.numel() < 64 * 2 * C:
+        raise ValueError("norm_backward_wb: scratch too small")
+    rc = _lib.load().nfn_norm_backward_wb(_p(dy), _p(x), _p(mean), _p(rstd), _p(dweight), _p(dbias),
+                                          _p(scratch), c_int(rows), c_int(C), c_int(mode),
+                                          c_int(int(accumulate)), _st())
+    _lib.check(rc, "nfn_norm_backward_wb")
+
+
+def colsum(dy, out, scratch, *, accumulate: bool = False):
+    """out[c] = sum_r dy[r, c]; dy bf16 [rows, C] (row stride allowed), out bf16 [C]."""
+    rows, C = dy.shape
+    if dy.stride(1) != 1 or scratch.numel() < 64 * C:
+        raise ValueError("colsum: bad operands")
+    rc = _lib.load().nfn_colsum(_p(dy), c_int(dy.stride(0)), _p(out), _p(scratch), c_int(rows),
+                                c_int(C), c_int(int(accumulate)), _st())
+    _lib.check(rc, "nfn_colsum")
+    return out
+
+
+def qk_norm_forward(qkv, n_q_heads: int, n_kv_heads: int, head_dim: int, *, eps: float = 1e-6,
+                    q_scale: float = 1.0, rstd=None):
+    """In place on the q and k head groups of packed ``qkv`` rows (q | k | v)."""
+    tokens, ld = qkv.shape
+    if rstd is None:
+        rstd = torch.empty(tokens, n_q_heads + n_kv_heads, device=qkv.device, dtype=torch.float32)
+    rc = _lib.load().nfn_qk_norm_forward(_p(qkv), _p(rstd), c_int(tokens), c_int(n_q_heads),
+                                         c_int(n_kv_heads), c_int(head_dim), c_int(qkv.stride(0)),
+                                         c_float(eps), c_float(q_scale), _st())
+    _lib.check(rc, "nfn_qk_norm_forward")
+    return rstd
+
+
+def qk_norm_backward(dqkv, qkv_normed, rstd, n_q_heads: int, n_kv_heads: int, head_dim: int, *,
+                     q_scale: float = 1.0):
+    tokens = dqkv.shape[0]
+    rc = _lib.load().nfn_qk_norm_backward(_p(dqkv), _p(qkv_normed), _p(rstd), c_int(tokens),
+                                          c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim),
+                                          c_int(dqkv.stride(0)), c_float(q_scale), _st())
+    _lib.check(rc, "nfn_qk_norm_backward")
+
+
+# ----------------------------------------------------------------- attention --
+def attention_forward(q, k, v, *, B: int, T: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                      causal: bool = True, window: int = 0, scale: float | None = None,
+                      out=None, lse=None, need_lse: bool = True):
+    """q: bf16 [B*T, >= Hq*D] view (row stride free), k/v: [B*T, >= Hkv*D] views.
+    Returns (o [B*T, Hq*D], lse [B, Hq, T])."""
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if t.dtype != _bf16 or t.stride(1) != 1 or t.shape[0] != B * T:
+            raise ValueError(f"attention: bad {name}")
+    if scale is None:
+        scale = head_dim ** -0.5
+    o = torch.empty(B * T, n_q_heads * head_dim, device=q.device, dtype=_bf16) if out is None else out
+    if lse is None and need_lse:
+        lse = torch.empty(B, n_q_heads, T, device=q.device, dtype=torch.float32)
+    rc = _lib.load().nfn_attention_forward(
+        _p(q), _p(k), _p(v), _p(o), _p(lse), c_int(B), c_int(T), c_int(n_q_heads), c_int(n_kv_heads),
+        c_int(head_dim), c_int(q.stride(0)), c_int(k.stride(0)), c_int(v.stride(0)), c_int(o.stride(0)),
+        c_int(int(causal)), c_int(window), c_float(scale), _st())
+    _lib.check(rc, "nfn_attention_forward")
+    return o, lse
+
+
+def attention_backward(do, q, k, v, o, lse, *, B: int, T: int, n_q_heads: int, n_kv_heads: int,
+                       head_dim: int, causal: bool = True, window: int = 0, scale: float | None = None,
+                       dq, dk, dv, delta=None, dq_accum=None):
+    """Gradients of attention. dq/dk/dv are bf16 [B*T, *] views (row stride free).
+    ``dq_accum``: fp32 [B*T, Hq*D] scratch (zeroed here); ``delta``: fp32 [B, Hq, T] scratch."""
+    if scale is None:
+        scale = head_dim ** -0.5
+    if delta is None:
+        delta = torch.empty(B, n_q_heads, T, device=q.device, dtype=torch.float32)
+    if dq_accum is None:
+        dq_accum = torch.empty(B * T, n_q_heads * head_dim, device=q.device, dtype=torch.float32)
+    rc = _lib.load().nfn_attention_backward(
+        _p(do), _p(q), _p(k), _p(v), _p(o), _p(lse), _p(delta), _p(dq_accum), _p(dq), _p(dk), _p(dv),
+        c_int(B), c_int(T), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim),
+        c_int(do.stride(0)), c_int(q.stride(0)), c_int(k.stride(0)), c_int(v.stride(0)),
+        c_int(o.stride(0)), c_int(dq.stride(0)), c_int(dk.stride(0)), c_int(dv.stride(0)),
+        c_int(int(causal)), c_int(window), c_float(scale), _st())
+    _lib.check(rc, "nfn_attention_backward")
+    return dq, dk, dv
+
+
+# ---------------------------------------------------------------------- loss --
+def cross_entropy(logits, targets, *, vocab: int, cap: float = 0.0, z_coef: float = 0.0,
+                  grad_scale: float = 1.0, loss_scale: float = 1.0, row_scale=None,
+                  write_grad: bool = True, row_loss=None, row_lse=None, mean_loss=None):
+    """logits: bf16 [rows, ld] (soft-capped already when cap > 0); overwritten with
+    d(loss)/d(logits) * grad_scale when ``write_grad``. targets: int32 [rows]."""
+    _need(logits, _bf16, "logits")
+    _need(targets, torch.int32, "targets")
+    rows, ld = logits.shape
+    dev = logits.device
+    if row_loss is None:
+        row_loss = torch.empty(rows, device=dev, dtype=torch.float32)
+    if mean_loss is None:
+        mean_loss = torch.empty(1, device=dev, dtype=torch.float32)
+    rc = _lib.load().nfn_cross_entropy(_p(logits), _p(targets), _p(row_scale), _p(row_loss), _p(row_lse),
+                                       _p(mean_loss), c_int(rows), c_int(vocab), c_int(ld), c_float(cap),
+                                       c_float(z_coef), c_float(grad_scale), c_float(loss_scale),
+                                       c_int(int(write_grad)), _st())
+    _lib.check(rc, "nfn_cross_entropy")
+    return mean_loss, row_loss
+
+
+# ----------------------------------------------------------------- embedding --
+def embedding_forward(tokens, wte, wpe, *, T: int, out=None):
+    _need(tokens, torch.int32, "tokens")
+    n = tokens.numel()
+    vocab, C = wte.shape
+    out = torch.empty(n, C, device=wte.device, dtype=_bf16) if out is None else out
+    rc = _lib.load().nfn_embedding_forward(_p(tokens), _p(wte), _p(wpe), _p(out), c_int(n), c_int(T),
+                                           c_int(C), c_int(vocab), _st())
+    _lib.check(rc, "nfn_embedding_forward")
+    return out
+
+
+def embedding_backward(dout, tokens, dwte, dwpe, *, B: int, T: int, accumulate_wpe: bool = False):
+    C = dout.shape[1]
+    vocab = dwte.shape[0] if dwte is not None else 0
+    rc = _lib.load().nfn_embedding_backward(_p(dout), _p(tokens), _p(dwte), _p(dwpe), c_int(B), c_int(T),
+                                            c_int(C), c_int(vocab), c_int(int(accumulate_wpe)), _st())
+    _lib.check(rc, "nfn_embedding_backward")
+
+
+# ----------------------------------------------------------------- optimizer --
+HP_LR, HP_BETA1, HP_BETA2, HP_EPS, HP_WD, HP_BC1, HP_BC2, HP_GRAD_SCALE, HP_MAX_NORM = range(9)
+HYPER_SIZE = 16
+
+
+def optim_max_partials() -> int:
+    return int(_lib.load().nfn_optim_max_partials())
+
+
+def grad_clip_scale(grad, partial, hyper, clip):
+    rc = _lib.load().nfn_grad_clip_scale(_p(grad), c_longlong(grad.numel()), _p(partial), _p(hyper),
+                                         _p(clip), _st())
+    _lib.check(rc, "nfn_grad_clip_scale")
+
+
+def adamw_flat(master, m, v, grad, param, n_decay: int, hyper, clip):
+    rc = _lib.load().nfn_adamw_flat(_p(master), _p(m), _p(v), _p(grad), _p(param),
+                                    c_longlong(master.numel()), c_longlong(n_decay), _p(hyper),
+                                    _p(clip), _st())
+    _lib.check(rc, "nfn_adamw_flat")
+
+
+def _ptr_array(ptrs):
+    arr = (c_void_p * len(ptrs))(*[c_void_p(int(p)) for p in ptrs])
+    return arr
+
+
+def peer_arrive(peer_flag_ptrs, rank: int, world: int, slot: int, epoch: int):
+    rc = _lib.load().nfn_peer_arrive(_ptr_array(peer_flag_ptrs), c_int(rank), c_int(world), c_int(slot),
+                                     c_int(epoch), _st())
+    _lib.check(rc, "nfn_peer_arrive")
+
+
+def peer_wait(my_flags_ptr: int, world: int, slot: int, epoch: int, timeout_s: float = 2.0):
+    rc = _lib.load().nfn_peer_wait(c_void_p(my_flags_ptr), c_int(world), c_int(slot), c_int(epoch),
+                                   c_double(timeout_s), _st())
+    _lib.check(rc, "nfn_peer_wait")
+
+
+def dp_reduce(peer_grad_ptrs, rank: int, world: int, lo: int, n: int, gshard, partial):
+    rc = _lib.load().nfn_dp_reduce(_ptr_array(peer_grad_ptrs), c_int(rank), c_int(world), c_longlong(lo),
+                                   c_longlong(n), _p(gshard), _p(partial), _st())
+    _lib.check(rc, "nfn_dp_reduce")
+
+
+def dp_norm_publish(partial, shard_n: int, peer_slot_ptrs, rank: int, world: int, epoch: int):
+    rc = _lib.load().nfn_dp_norm_publish(_p(partial), c_longlong(shard_n), _ptr_array(peer_slot_ptrs),
+                                         c_int(rank), c_int(world), c_int(epoch), _st())
+    _lib.check(rc, "nfn_dp_norm_publish")
+
+
+def dp_norm_collect(my_slots_ptr: int, world: int, epoch: int, hyper, clip, timeout_s: float = 2.0):
+    rc = _lib.load().nfn_dp_norm_collect(c_void_p(my_slots_ptr), c_int(world), c_int(epoch), _p(hyper),
+                                         _p(clip), c_double(timeout_s), _st())
+    _lib.check(rc, "nfn_dp_norm_collect")
+
+
+def dp_adamw(master, m, v, gshard, peer_param_ptrs, rank: int, world: int, lo: int, n: int,
+             n_decay_global: int, hyper, clip):
+    rc = _lib.load().nfn_dp_adamw(_p(master), _p(m), _p(v), _p(gshard), _ptr_array(peer_param_ptrs),
+                                  c_int(rank), c_int(world), c_longlong(lo), c_longlong(n),
+                                  c_longlong(n_decay_global), _p(hyper), _p(clip), _st())
+    _lib.check(rc, "nfn_dp_adamw")
