@@ -1,0 +1,209 @@
+#!/usr/bin/env python
+"""Headline benchmark: GPT-2 124M (QK-norm + logit soft-cap 30 + z-loss 1e-4) training
+throughput in tokens/s, bf16, data parallel with sharded AdamW, micro-batch 16 x 1024
+per GPU, synthetic uniform-random token ids, gpt2-normal random init.
+
+    python bench.py --gpus N --steps K --warmup W            # this framework
+    python bench.py --impl reference --gpus N --steps K ...  # unmodified reference (Torch path)
+
+For N > 1 launch under ``python -m torch.distributed.run --nproc-per-node N``. Rank 0
+prints one JSON line. ``value`` is device-timed (CUDA events, max over ranks) over K
+steps on a batch already resident on the device; ``e2e`` repeats the measurement
+through the public ``DenseGPTTrainer.train_step`` call including the pinned-host ->
+device batch copy and the device -> host loss read of every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+BASELINE_TOKENS_PER_S = 212725.0  # reference README.md:2333-2335 (1x RTX 5090, B=64, T=1024)
+METRIC = "train_compute_tokens_per_second"
+MODEL = "gpt2_124M_qknorm_softcap30_zloss1e-4"
+
+
+def _dist_setup(n_gpus: int):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if world != n_gpus:
+        raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    return rank, world, local
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu = gpu_index
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
+                                     timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([f.strip() for f in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        sm = [int(s[0]) for s in self.samples if s and s[0].isdigit()]
+        mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names)
+                   if any(len(s) > 2 + i and s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+    from neuralfn_b200.models.gpt2 import GPT2Config
+    from neuralfn_b200.parallel.dp import AdamWConfig
+    from neuralfn_b200.trainers.dense_gpt import DenseGPTTrainer
+
+    rank, world, local = _dist_setup(args.gpus)
+    cfg = GPT2Config.variant("gpt2_qknorm_softcap_zloss")
+    B, T = args.micro_batch, args.seq_len
+    trainer = DenseGPTTrainer(cfg, B, T, AdamWConfig(), seed=1337, use_cuda_graph=not args.no_graph)
+    gen = torch.Generator().manual_seed(1234 + rank)
+    n_host = 4
+    host = [(torch.randint(0, cfg.vocab_size, (B * T,), generator=gen, dtype=torch.int32).pin_memory(),
+             torch.randint(0, cfg.vocab_size, (B * T,), generator=gen, dtype=torch.int32).pin_memory())
+            for _ in range(n_host)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up (also builds the CUDA graph) ----
+    trainer.upload(*host[0])
+    for i in range(max(args.warmup, 3)):
+        trainer.step_on_device_batch()
+    trainer.check_status()
+
+    # ---- device-timed region: K optimizer steps on a device-resident batch ----
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local) as clocks:
+        start.record()
+        for _ in range(args.steps):
+            trainer.step_on_device_batch()
+        stop.record()
+        barrier()
+    ms = start.elapsed_time(stop)
+    # ---- end to end through the public API: H2D batch copy + D2H loss every step ----
+    last_loss = trainer.train_step(*host[0])
+    barrier()
+    t0 = time.perf_counter()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for i in range(args.steps):
+        last_loss = trainer.train_step(*host[i % n_host])
+    e_stop.record()
+    barrier()
+    e2e_ms = max(e_start.elapsed_time(e_stop), 0.0)
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3
+    trainer.check_status()
+
+    t = torch.tensor([ms, max(e2e_ms, e2e_wall_ms)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+    tokens = args.steps * B * T * world
+    value = tokens / (ms / 1e3)
+    e2e = tokens / (e2e_ms / 1e3)
+    out = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": value / BASELINE_TOKENS_PER_S, "dtype": "bf16",
+        "data": "synthetic uniform-random token ids, random-init weights (gpt2-normal, std 0.02)",
+        "config": {"model": MODEL, "global_batch": B * world, "micro_batch_per_gpu": B, "seq_len": T,
+                   "parallelism": f"dp{world}" if world > 1 else "single",
+                   "optimizer": "sharded AdamW (fp32 master/m/v), grad clip 1.0",
+                   "cuda_graph": not args.no_graph,
+                   "l2_note": "per-step working set (~6 GB of activations and logits) far exceeds the 126 MB L2"},
+        "clocks": clocks.summary(),
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 4,
+                "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": trainer.launches_per_step * args.steps,
+        "launches_per_step": trainer.launches_per_step,
+        "final_loss": last_loss,
+        "impl": "neuralfn_b200",
+    }
+    if world > 1:
+        dist.destroy_process_group()
+    return out if rank == 0 else {}
+
+
+def run_reference(args) -> dict:
+    """The unmodified reference (installed under baseline/_ref) through its own public API:
+    ``build_gpt2_qknorm_spec`` -> ``build_gpt_root_graph`` -> ``TorchTrainer.train`` on one GPU.
+    The reference has no data-parallel mode, so N > 1 is reported as unavailable."""
+    root = os.path.dirname(os.path.abspath(__file__))
+    ref = os.path.join(root, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "neuralfn")):
+        return {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of the reference)"}
+    if args.gpus > 1:
+        return {"impl": "reference",
+                "unavailable": "the reference has no data-parallel training mode (single process, single device)"}
+    sys.path.insert(0, ref)
+    try:
+        from baseline.reference_arm import run as run_ref
+    except Exception as exc:  # pragma: no cover
+        return {"impl": "reference", "unavailable": f"reference arm import failed: {exc!r}"[:300]}
+    try:
+        return run_ref(args, METRIC, MODEL, BASELINE_TOKENS_PER_S, ClockSampler)
+    except Exception as exc:
+        return {"impl": "reference", "unavailable": f"reference run failed: {exc!r}"[:300]}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--micro-batch", type=int, default=16)
+    ap.add_argument("--seq-len", type=int, default=1024)
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if out:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

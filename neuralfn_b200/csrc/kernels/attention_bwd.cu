@@ -46,7 +46,6 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                "f"(d)
                : "memory");
 }
-__device__ __forceinline__ void bar_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 template <int D, int STAGES>
 __global__ void __launch_bounds__(AB_THREADS)
@@ -66,9 +65,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sQdO = sV + TILE;                 // STAGES x (Q tile, dO tile)
   uint8_t* sP = sQdO + STAGES * 2 * TILE;
   uint8_t* sdS = sP + PT;
-  float* s_lse = reinterpret_cast<float*>(sdS + PT);  // [2][128]
-  float* s_delta = s_lse + 2 * AB_BLK;                // [2][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 2 * AB_BLK);
+  float* s_lse = reinterpret_cast<float*>(sdS + PT);  // [4 warps][128]
+  float* s_delta = s_lse + 4 * AB_BLK;                // [4 warps][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 4 * AB_BLK);
   uint64_t* bar_kv = bars;            // 1
   uint64_t* bar_qdo = bars + 1;       // STAGES (<= 2)
   uint64_t* bar_sdp = bars + 3;       // S^T and dP^T complete
@@ -225,16 +224,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int hq = hk * G + s / nqb;
       const int i = i_lo + s % nqb;
       const int q0 = i * AB_BLK;
-      // stage lse / delta of this query tile
-      {
-        const int q = q0 + r;
+      // stage lse / delta of this query tile: every warp keeps a private copy of the 128
+      // values, so only warp-level synchronisation is needed (no CTA barrier that a
+      // timed-out warp could leave the others stuck on)
+      float* lse2 = s_lse + warp * AB_BLK;
+      float* dlt = s_delta + warp * AB_BLK;
+      __syncwarp();
+#pragma unroll
+      for (int e = 0; e < AB_BLK / 32; ++e) {
+        const int q = q0 + e * 32 + lane;
         const size_t idx = ((size_t)b * p.Hq + hq) * p.T + q;
-        s_lse[(s & 1) * AB_BLK + r] = q < p.T ? p.lse[idx] * LOG2E : INFINITY;
-        s_delta[(s & 1) * AB_BLK + r] = q < p.T ? p.delta[idx] : 0.f;
+        lse2[e * 32 + lane] = q < p.T ? p.lse[idx] * LOG2E : INFINITY;
+        dlt[e * 32 + lane] = q < p.T ? p.delta[idx] : 0.f;
       }
-      bar_sync_128();
-      const float* lse2 = s_lse + (s & 1) * AB_BLK;
-      const float* dlt = s_delta + (s & 1) * AB_BLK;
+      __syncwarp();
       ok = mbar_wait_bounded(smem_u32(bar_sdp), s & 1, cta_abort, p.status, NFN_ERR_WAIT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -316,8 +319,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     // dK / dV leave TMEM once
     if (ok && nsteps > 0) {
-      // the last bar_out wait above already covers every product issued before it
-      if (kidx < p.T) {
+      // the last bar_out wait above already covers every product issued before it.
+      // tcgen05.ld is warp-collective: every lane issues the loads, only rows inside
+      // the sequence store.
+      const bool row_ok = kidx < p.T;
+      {
         __nv_bfloat16* dkrow = p.dk + (size_t)(row0 + kidx) * p.ld_dk + hk * D;
         __nv_bfloat16* dvrow = p.dv + (size_t)(row0 + kidx) * p.ld_dv + hk * D;
 #pragma unroll
@@ -332,7 +338,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             u.y = pack_bf16x2(__uint_as_float(v[8 * e + 2]), __uint_as_float(v[8 * e + 3]));
             u.z = pack_bf16x2(__uint_as_float(v[8 * e + 4]), __uint_as_float(v[8 * e + 5]));
             u.w = pack_bf16x2(__uint_as_float(v[8 * e + 6]), __uint_as_float(v[8 * e + 7]));
-            reinterpret_cast<uint4*>(dvrow + c * 32)[e] = u;
+            if (row_ok) reinterpret_cast<uint4*>(dvrow + c * 32)[e] = u;
           }
           tmem_ld_32x32(t_row + COL_DK + c * 32, v);
           tmem_ld_wait();
@@ -343,7 +349,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             u.y = pack_bf16x2(__uint_as_float(v[8 * e + 2]) * p.scale, __uint_as_float(v[8 * e + 3]) * p.scale);
             u.z = pack_bf16x2(__uint_as_float(v[8 * e + 4]) * p.scale, __uint_as_float(v[8 * e + 5]) * p.scale);
             u.w = pack_bf16x2(__uint_as_float(v[8 * e + 6]) * p.scale, __uint_as_float(v[8 * e + 7]) * p.scale);
-            reinterpret_cast<uint4*>(dkrow + c * 32)[e] = u;
+            if (row_ok) reinterpret_cast<uint4*>(dkrow + c * 32)[e] = u;
           }
         }
       }
@@ -421,7 +427,7 @@ static int launch_attn_bwd(const void* dout, const void* q, const void* k, const
                            int ld_k, int ld_v, int ld_o, int ld_dq, int ld_dk, int ld_dv, int causal,
                            int window, float scale, cudaStream_t st) {
   constexpr size_t TILE = AB_BLK * D * 2, PT = AB_BLK * AB_BLK * 2;
-  constexpr size_t SMEM = 2 * TILE + STAGES * 2 * TILE + 2 * PT + 4 * AB_BLK * 4 + 128 + 1024;
+  constexpr size_t SMEM = 2 * TILE + STAGES * 2 * TILE + 2 * PT + 8 * AB_BLK * 4 + 128 + 1024;
   auto kern = attn_bwd_kernel<D, STAGES>;
   static bool attr[64] = {};
   int dev = 0;
@@ -456,7 +462,7 @@ static int launch_attn_bwd(const void* dout, const void* q, const void* k, const
     attn_dq_convert_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
         dq_accum, (__nv_bfloat16*)dq, rows, Hq * D, ld_dq, scale);
   }
-  return launch_check("attn_bwd");
+  return launch_check("attn_bwd", 3);
 }
 
 }  // namespace nfn

@@ -3,6 +3,7 @@
 // library links without libcuda).
 #include "common.h"
 
+#include <atomic>
 #include <mutex>
 #include <string>
 #include <unordered_map>
@@ -14,6 +15,9 @@ namespace nfn {
 static __device__ int g_status_word[8];
 
 static thread_local std::string g_last_error;
+static std::atomic<long long> g_launches{0};
+void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launches() { return g_launches.load(std::memory_order_relaxed); }
 
 void set_last_error(const char* msg) { g_last_error = msg; }
 
@@ -184,5 +188,7 @@ int nfn_status_peek(void) {
 }
 
 const char* nfn_last_error(void) { return nfn::g_last_error.c_str(); }
+
+long long nfn_launch_count(void) { return nfn::launches(); }
 
 }  // extern "C"

@@ -24,13 +24,19 @@ bool make_tmap_3d(CUtensorMap* out, const void* ptr, int elem_size, uint64_t d0,
                   uint64_t d2, uint64_t stride1_elems, uint64_t stride2_elems, uint32_t b0,
                   uint32_t b1, uint32_t b2, int swizzle_bytes);
 
-inline int launch_check(const char* what) {
+// Number of kernels this library has launched in this process (host-side count).
+void count_launches(int n);
+long long launches();
+
+// Checks the launch(es) just issued; `n_kernels` of them are added to the launch count.
+inline int launch_check(const char* what, int n_kernels = 1) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     (void)what;
     return -100 - static_cast<int>(e);
   }
+  count_launches(n_kernels);
   return 0;
 }
 

@@ -100,5 +100,5 @@ extern "C" int nfn_embedding_backward(const void* dout, const int* tokens, void*
     wte_bwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
         (const __nv_bfloat16*)dout, tokens, (__nv_bfloat16*)dwte, n, C, vocab);
   }
-  return launch_check("embedding_bwd");
+  return launch_check("embedding_bwd", (dwpe ? 1 : 0) + (dwte ? 1 : 0));
 }

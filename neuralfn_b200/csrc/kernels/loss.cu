@@ -180,7 +180,7 @@ extern "C" int nfn_cross_entropy(void* logits, const int* targets, const float* 
         grad_scale, write_grad);
   }
   if (mean_loss) sum_rows_kernel<<<1, 1024, 0, st>>>(row_loss, mean_loss, rows, loss_scale, 0);
-  return launch_check("cross_entropy");
+  return launch_check("cross_entropy", mean_loss ? 2 : 1);
 }
 
 extern "C" int nfn_sum_f32(const float* v, float* out, int n, float scale, int accumulate,

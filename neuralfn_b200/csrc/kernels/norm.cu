@@ -396,7 +396,7 @@ extern "C" int nfn_norm_backward_wb(const void* dy, const void* x, const float* 
                                                    rows, C, mode);
   norm_bwd_wb_final_kernel<<<ceil_div(C, 256), 256, 0, st>>>(scratch, (__nv_bfloat16*)dw,
                                                              (__nv_bfloat16*)db, RY, C, accumulate);
-  return launch_check("norm_bwd_wb");
+  return launch_check("norm_bwd_wb", 2);
 }
 
 // scratch: fp32 [64 * C]
@@ -410,7 +410,7 @@ extern "C" int nfn_colsum(const void* dy, int ld, void* out, float* scratch, int
   colsum_partial_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)dy, ld, scratch, rows, C);
   colsum_final_kernel<<<ceil_div(C, 256), 256, 0, st>>>(scratch, (__nv_bfloat16*)out, RY, C,
                                                         accumulate);
-  return launch_check("colsum");
+  return launch_check("colsum", 2);
 }
 
 extern "C" int nfn_qk_norm_forward(void* qkv, float* rstd, int tokens, int n_q_heads,

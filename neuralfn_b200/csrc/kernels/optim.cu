@@ -150,11 +150,7 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
+__device__ __forceinline__ unsigned long long globaltimer_ns() { return global_timer_ns(); }
 // Wait until *p >= want. Returns false on timeout.
 __device__ __forceinline__ bool wait_flag_ge(const int* p, int want, unsigned long long timeout_ns) {
   const unsigned long long t0 = globaltimer_ns();
@@ -167,14 +163,17 @@ __device__ __forceinline__ bool wait_flag_ge(const int* p, int want, unsigned lo
 
 // flags layout on every rank: int[slots][world]. Rank r signals slot s by writing
 // `epoch` into every peer's flags[s][r].
-__global__ void peer_arrive_kernel(PeerTable flags, int rank, int world, int slot, int epoch) {
+__global__ void peer_arrive_kernel(PeerTable flags, int rank, int world, int slot, int epoch,
+                                   const int* epoch_dev) {
+  if (epoch_dev) epoch += *epoch_dev;
   __threadfence_system();
   const int t = threadIdx.x;
   if (t < world) st_release_sys(static_cast<int*>(flags.p[t]) + slot * world + rank, epoch);
 }
-__global__ void peer_wait_kernel(const int* my_flags, int world, int slot, int epoch,
+__global__ void peer_wait_kernel(const int* my_flags, int world, int slot, int epoch, const int* epoch_dev,
                                  unsigned long long timeout_ns, int* status) {
   const int t = threadIdx.x;
+  if (epoch_dev) epoch += *epoch_dev;
   if (t < world) {
     if (!wait_flag_ge(my_flags + slot * world + t, epoch, timeout_ns)) atomicCAS(status, 0, NFN_ERR_WAIT_PEER);
   }
@@ -220,9 +219,10 @@ dp_reduce_kernel(PeerTable grads, int rank, int world, long long lo8, long long 
 // norm slots: slots[rank] = {sumsq, epoch} written as one 8-byte release store.
 __global__ void __launch_bounds__(256)
 dp_norm_publish_kernel(const float* __restrict__ partial, int npartial, PeerTable norm_slots,
-                       int rank, int world, int epoch) {
+                       int rank, int world, int epoch, const int* epoch_dev) {
   __shared__ float red[8];
   __shared__ float total;
+  if (epoch_dev) epoch += *epoch_dev;
   float s = 0.f;
   for (int i = threadIdx.x; i < npartial; i += 256) s += partial[i];
   s = block_sum_256(s, red);
@@ -238,10 +238,12 @@ dp_norm_publish_kernel(const float* __restrict__ partial, int npartial, PeerTabl
 }
 // Wait for all ranks' squared norms of this epoch, then compute the clip factor.
 __global__ void dp_norm_collect_kernel(const unsigned long long* my_slots, int world, int epoch,
+                                       const int* epoch_dev,
                                        const float* __restrict__ hyper, float* __restrict__ clip,
                                        unsigned long long timeout_ns, int* status) {
   __shared__ float vals[MAX_PEERS];
   __shared__ int bad;
+  if (epoch_dev) epoch += *epoch_dev;
   if (threadIdx.x == 0) bad = 0;
   __syncthreads();
   const int t = threadIdx.x;
@@ -313,6 +315,16 @@ static bool fill_table(PeerTable& t, void* const* ptrs, int world) {
 
 using namespace nfn;
 
+namespace nfn {
+__global__ void counter_add_kernel(int* p, int v) { if (threadIdx.x == 0) *p += v; }
+}
+// *p += v on the stream: the device-resident signal epoch advanced once per step, so a
+// captured step graph produces fresh epochs on every replay.
+extern "C" int nfn_counter_add(int* p, int v, nfn_stream_t stream) {
+  counter_add_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p, v);
+  return launch_check("counter_add");
+}
+
 extern "C" int nfn_optim_max_partials(void) { return sm_count() * 8; }
 
 // partial: fp32 [nfn_optim_max_partials()]; clip: fp32 [2]
@@ -323,7 +335,7 @@ extern "C" int nfn_grad_clip_scale(const void* grad, long long n, float* partial
   const int grid = grid_for(n / 8);
   sumsq_bf16_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)grad, n / 8, partial);
   clip_scale_kernel<<<1, 256, 0, st>>>(partial, grid, hyper, clip);
-  return launch_check("grad_clip_scale");
+  return launch_check("grad_clip_scale", 2);
 }
 
 extern "C" int nfn_adamw_flat(float* master, float* m, float* v, const void* grad, void* param,
@@ -336,18 +348,20 @@ extern "C" int nfn_adamw_flat(float* master, float* m, float* v, const void* gra
 }
 
 extern "C" int nfn_peer_arrive(void* const* peer_flags, int rank, int world, int slot, int epoch,
+                               const int* epoch_dev,
                                nfn_stream_t stream) {
   PeerTable t;
   if (!fill_table(t, peer_flags, world)) return fail(-1, "peer_arrive: bad world size");
-  peer_arrive_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(t, rank, world, slot, epoch);
+  peer_arrive_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(t, rank, world, slot, epoch, epoch_dev);
   return launch_check("peer_arrive");
 }
 
-extern "C" int nfn_peer_wait(const int* my_flags, int world, int slot, int epoch, double timeout_s,
+extern "C" int nfn_peer_wait(const int* my_flags, int world, int slot, int epoch, const int* epoch_dev,
+                             double timeout_s,
                              nfn_stream_t stream) {
   if (world < 1 || world > MAX_PEERS) return fail(-1, "peer_wait: bad world size");
   peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      my_flags, world, slot, epoch, (unsigned long long)(timeout_s * 1e9), status_ptr());
+      my_flags, world, slot, epoch, epoch_dev, (unsigned long long)(timeout_s * 1e9), status_ptr());
   return launch_check("peer_wait");
 }
 
@@ -363,19 +377,21 @@ extern "C" int nfn_dp_reduce(void* const* peer_grads, int rank, int world, long 
 }
 
 extern "C" int nfn_dp_norm_publish(const float* partial, long long shard_n, void* const* peer_slots,
-                                   int rank, int world, int epoch, nfn_stream_t stream) {
+                                   int rank, int world, int epoch, const int* epoch_dev,
+                                   nfn_stream_t stream) {
   PeerTable t;
   if (!fill_table(t, peer_slots, world)) return fail(-1, "dp_norm_publish: bad world size");
   dp_norm_publish_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      partial, grid_for(shard_n / 8), t, rank, world, epoch);
+      partial, grid_for(shard_n / 8), t, rank, world, epoch, epoch_dev);
   return launch_check("dp_norm_publish");
 }
 
-extern "C" int nfn_dp_norm_collect(const void* my_slots, int world, int epoch, const float* hyper,
+extern "C" int nfn_dp_norm_collect(const void* my_slots, int world, int epoch, const int* epoch_dev,
+                                   const float* hyper,
                                    float* clip, double timeout_s, nfn_stream_t stream) {
   if (world < 1 || world > MAX_PEERS) return fail(-1, "dp_norm_collect: bad world size");
   dp_norm_collect_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      (const unsigned long long*)my_slots, world, epoch, hyper, clip,
+      (const unsigned long long*)my_slots, world, epoch, epoch_dev, hyper, clip,
       (unsigned long long)(timeout_s * 1e9), status_ptr());
   return launch_check("dp_norm_collect");
 }

@@ -75,16 +75,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait. Returns false (after raising the abort flag and recording `code`)
 // when the barrier does not flip within the iteration budget or when another
 // role already aborted.
-constexpr uint32_t kWaitSpinLimit = 1u << 22;
+constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s of wall clock
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int* cta_abort, int* status,
                                                   int code) {
-  for (uint32_t it = 0; it < kWaitSpinLimit; ++it) {
+  // fast path: a short burst of polls before the clock is consulted
+#pragma unroll 1
+  for (int it = 0; it < 32; ++it)
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 255u) == 255u) {
+  const unsigned long long t0 = global_timer_ns();
+#pragma unroll 1
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 15u) == 15u) {
       if (*cta_abort) return false;
-      __nanosleep(64);
+      if (global_timer_ns() - t0 > kWaitLimitNs) break;
+      __nanosleep(32);
     }
   }
   *cta_abort = 1;

@@ -1,0 +1,361 @@
+"""Dense GPT-2 family (gpt2, gpt2_zloss, gpt2_softcap, gpt2_qknorm, gpt2_stable) as an
+explicit forward/backward engine over the sm_100a kernel library.
+
+The engine owns flat bf16 parameter and gradient buffers (so the data-parallel
+reduce-scatter/AdamW kernels can address them by offset), per-layer activation
+stashes, and issues every kernel of a training step itself - there is no autograd
+tape in the hot path, which makes the whole step capturable in one CUDA graph.
+
+Layer math and variant semantics follow the reference's native dense trainer
+(``neuralfn/csrc/native_gpt2/nfn_gpt2_native_train.cpp:25816-25965`` forward block,
+``:771-789`` variants, init ``:23194-23240``): pre-LN blocks, tanh-GELU, tied LM head
+over a vocabulary padded to a multiple of 64... (50257 -> 50304), weightless per-head
+RMS on Q and K after the bias when ``qk_norm``, ``cap*tanh(logit/cap)`` when
+``logit_softcap``, and ``z * lse^2`` added to the token loss when ``z_loss``.
+A plain PyTorch fp32 implementation of the same math (``reference_forward``) is the
+oracle for the tests and the CPU path.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Iterator
+
+import torch
+import torch.nn.functional as F
+
+__all__ = ["GPT2Config", "ParamSpec", "gpt2_param_specs", "FlatLayout", "GPT2Engine",
+           "reference_forward", "init_gpt2_params_"]
+
+
+@dataclass
+class GPT2Config:
+    n_layer: int = 12
+    n_head: int = 12
+    d_model: int = 768
+    vocab_size: int = 50257
+    max_seq_len: int = 1024
+    mlp_mult: int = 4
+    qk_norm: bool = False
+    qk_norm_eps: float = 1e-6
+    logit_softcap: float = 0.0
+    z_loss: float = 0.0
+    ln_eps: float = 1e-5
+    vocab_pad_to: int = 128
+
+    @property
+    def padded_vocab(self) -> int:
+        p = self.vocab_pad_to
+        return (self.vocab_size + p - 1) // p * p
+
+    @property
+    def head_dim(self) -> int:
+        return self.d_model // self.n_head
+
+    @classmethod
+    def variant(cls, name: str, **kw) -> "GPT2Config":
+        """Named dense variants: defaults z=1e-4, cap=30, qk-norm as in the reference presets
+        (``neuralfn/config.py:900-949``)."""
+        table = {
+            "gpt2": {},
+            "gpt2_zloss": {"z_loss": 1e-4},
+            "gpt2_softcap": {"logit_softcap": 30.0},
+            "gpt2_qknorm": {"qk_norm": True},
+            "gpt2_stable": {"qk_norm": True, "z_loss": 1e-4},
+            "gpt2_qknorm_softcap_zloss": {"qk_norm": True, "logit_softcap": 30.0, "z_loss": 1e-4},
+        }
+        if name not in table:
+            raise KeyError(f"unknown dense GPT variant {name!r}")
+        return cls(**{**table[name], **kw})
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    name: str
+    shape: tuple[int, ...]
+    decay: bool
+    init: str  # "normal" | "resid" | "zeros" | "ones"
+
+    @property
+    def numel(self) -> int:
+        return math.prod(self.shape)
+
+
+def gpt2_param_specs(cfg: GPT2Config) -> list[ParamSpec]:
+    """Tensors in dense-checkpoint order (wte, wpe, per layer ..., ln_f)."""
+    C, L, Vp, T = cfg.d_model, cfg.n_layer, cfg.padded_vocab, cfg.max_seq_len
+    H = cfg.mlp_mult * C
+    specs = [ParamSpec("wte", (Vp, C), True, "normal"), ParamSpec("wpe", (T, C), True, "normal")]
+    for l in range(L):
+        p = f"h.{l}."
+        specs += [
+            ParamSpec(p + "ln_1.weight", (C,), False, "ones"), ParamSpec(p + "ln_1.bias", (C,), False, "zeros"),
+            ParamSpec(p + "attn.c_attn.weight", (3 * C, C), True, "normal"),
+            ParamSpec(p + "attn.c_attn.bias", (3 * C,), False, "zeros"),
+            ParamSpec(p + "attn.c_proj.weight", (C, C), True, "resid"),
+            ParamSpec(p + "attn.c_proj.bias", (C,), False, "zeros"),
+            ParamSpec(p + "ln_2.weight", (C,), False, "ones"), ParamSpec(p + "ln_2.bias", (C,), False, "zeros"),
+            ParamSpec(p + "mlp.c_fc.weight", (H, C), True, "normal"),
+            ParamSpec(p + "mlp.c_fc.bias", (H,), False, "zeros"),
+            ParamSpec(p + "mlp.c_proj.weight", (C, H), True, "resid"),
+            ParamSpec(p + "mlp.c_proj.bias", (C,), False, "zeros"),
+        ]
+    specs += [ParamSpec("ln_f.weight", (C,), False, "ones"), ParamSpec("ln_f.bias", (C,), False, "zeros")]
+    return specs
+
+
+class FlatLayout:
+    """Offsets of named tensors inside one flat buffer: all weight-decayed tensors
+    first, then the rest, each start aligned to 8 elements (16 bytes for bf16) and the
+    total padded so it splits evenly into ``world`` shards of a multiple of 8."""
+
+    def __init__(self, specs: list[ParamSpec], world: int = 1, align: int = 8) -> None:
+        self.specs = {s.name: s for s in specs}
+        self.order = [s for s in specs if s.decay] + [s for s in specs if not s.decay]
+        self.offsets: dict[str, int] = {}
+        cur = 0
+        for s in self.order:
+            if not s.decay and "n_decay" not in self.__dict__:
+                self.n_decay = cur
+            self.offsets[s.name] = cur
+            cur += (s.numel + align - 1) // align * align
+        if "n_decay" not in self.__dict__:
+            self.n_decay = cur
+        self.n_used = cur
+        quantum = align * world
+        self.n_total = (cur + quantum - 1) // quantum * quantum
+        self.world = world
+        self.shard = self.n_total // world
+
+    def view(self, flat: torch.Tensor, name: str) -> torch.Tensor:
+        s = self.specs[name]
+        o = self.offsets[name]
+        return flat[o:o + s.numel].view(*s.shape)
+
+    def views(self, flat: torch.Tensor) -> dict[str, torch.Tensor]:
+        return {s.name: self.view(flat, s.name) for s in self.order}
+
+
+def init_gpt2_params_(cfg: GPT2Config, layout: FlatLayout, master: torch.Tensor, seed: int = 1337) -> None:
+    """gpt2-normal initialisation into an fp32 flat buffer: N(0, 0.02) for embeddings and
+    input projections, N(0, 0.02/sqrt(2L)) for the two residual projections, zero biases,
+    unit LayerNorm weights, zero rows for the vocabulary padding."""
+    gen = torch.Generator(device=master.device)
+    gen.manual_seed(seed)
+    master.zero_()
+    for s in layout.order:
+        v = layout.view(master, s.name)
+        if s.init == "normal":
+            v.normal_(0.0, 0.02, generator=gen)
+        elif s.init == "resid":
+            v.normal_(0.0, 0.02 / math.sqrt(2 * cfg.n_layer), generator=gen)
+        elif s.init == "ones":
+            v.fill_(1.0)
+    layout.view(master, "wte")[cfg.vocab_size:].zero_()
+
+
+# ------------------------------------------------------------------------ oracle --
+def reference_forward(cfg: GPT2Config, params: dict[str, torch.Tensor], tokens: torch.Tensor,
+                      targets: torch.Tensor | None = None):
+    """Plain PyTorch restatement (any dtype/device). Returns (loss, logits[B,T,V])."""
+    B, T = tokens.shape
+    C, nh, hd = cfg.d_model, cfg.n_head, cfg.head_dim
+    x = params["wte"][tokens] + params["wpe"][:T]
+    for l in range(cfg.n_layer):
+        p = f"h.{l}."
+        h = F.layer_norm(x, (C,), params[p + "ln_1.weight"], params[p + "ln_1.bias"], cfg.ln_eps)
+        qkv = F.linear(h, params[p + "attn.c_attn.weight"], params[p + "attn.c_attn.bias"])
+        q, k, v = (t.view(B, T, nh, hd).transpose(1, 2) for t in qkv.split(C, dim=-1))
+        if cfg.qk_norm:
+            q = q * torch.rsqrt(q.float().pow(2).mean(-1, keepdim=True) + cfg.qk_norm_eps).to(q.dtype)
+            k = k * torch.rsqrt(k.float().pow(2).mean(-1, keepdim=True) + cfg.qk_norm_eps).to(k.dtype)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        a = a.transpose(1, 2).reshape(B, T, C)
+        x = x + F.linear(a, params[p + "attn.c_proj.weight"], params[p + "attn.c_proj.bias"])
+        h = F.layer_norm(x, (C,), params[p + "ln_2.weight"], params[p + "ln_2.bias"], cfg.ln_eps)
+        h = F.gelu(F.linear(h, params[p + "mlp.c_fc.weight"], params[p + "mlp.c_fc.bias"]), approximate="tanh")
+        x = x + F.linear(h, params[p + "mlp.c_proj.weight"], params[p + "mlp.c_proj.bias"])
+    x = F.layer_norm(x, (C,), params["ln_f.weight"], params["ln_f.bias"], cfg.ln_eps)
+    logits = F.linear(x, params["wte"])[..., :cfg.vocab_size]
+    if cfg.logit_softcap > 0:
+        logits = cfg.logit_softcap * torch.tanh(logits / cfg.logit_softcap)
+    loss = None
+    if targets is not None:
+        lf = logits.float().view(-1, cfg.vocab_size)
+        lse = torch.logsumexp(lf, dim=-1)
+        tv = lf.gather(1, targets.view(-1, 1).long()).squeeze(1)
+        loss = (lse - tv + cfg.z_loss * lse * lse).mean()
+    return loss, logits
+
+
+# ------------------------------------------------------------------------ engine --
+@dataclass
+class _LayerActs:
+    ln1: torch.Tensor
+    ln1_mean: torch.Tensor
+    ln1_rstd: torch.Tensor
+    qkv: torch.Tensor
+    qk_rstd: torch.Tensor | None
+    att: torch.Tensor
+    lse: torch.Tensor
+    x1: torch.Tensor
+    ln2: torch.Tensor
+    ln2_mean: torch.Tensor
+    ln2_rstd: torch.Tensor
+    fc_pre: torch.Tensor
+    fc_act: torch.Tensor
+    x2: torch.Tensor
+
+
+class GPT2Engine:
+    """Forward/backward of the dense GPT over preallocated buffers (CUDA only).
+
+    ``params``/``grads`` are flat bf16 buffers supplied by the caller (plain CUDA
+    tensors, or symmetric-memory tensors when data parallel); the optimizer lives in
+    ``neuralfn_b200.parallel.dp``.
+    """
+
+    def __init__(self, cfg: GPT2Config, layout: FlatLayout, params: torch.Tensor, grads: torch.Tensor,
+                 batch: int, seq: int) -> None:
+        from ..ops import kernels as K
+        from ..ops.gemm import gemm
+        self.K, self.gemm = K, gemm
+        self.cfg, self.layout = cfg, layout
+        self.B, self.T = batch, seq
+        if seq > cfg.max_seq_len:
+            raise ValueError("sequence longer than max_seq_len")
+        self.params, self.grads = params, grads
+        self.p = layout.views(params)
+        self.g = layout.views(grads)
+        dev = params.device
+        N, C, Hd = batch * seq, cfg.d_model, cfg.mlp_mult * cfg.d_model
+        bf, f32 = torch.bfloat16, torch.float32
+        e = lambda *s, dtype=bf: torch.empty(*s, device=dev, dtype=dtype)  # noqa: E731
+        self.x0 = e(N, C)
+        self.acts = [
+            _LayerActs(ln1=e(N, C), ln1_mean=e(N, dtype=f32), ln1_rstd=e(N, dtype=f32), qkv=e(N, 3 * C),
+                       qk_rstd=e(N, 2 * cfg.n_head, dtype=f32) if cfg.qk_norm else None, att=e(N, C),
+                       lse=e(batch, cfg.n_head, seq, dtype=f32), x1=e(N, C), ln2=e(N, C),
+                       ln2_mean=e(N, dtype=f32), ln2_rstd=e(N, dtype=f32), fc_pre=e(N, Hd),
+                       fc_act=e(N, Hd), x2=e(N, C))
+            for _ in range(cfg.n_layer)]
+        self.lnf = e(N, C)
+        self.lnf_mean, self.lnf_rstd = e(N, dtype=f32), e(N, dtype=f32)
+        self.logits = e(N, cfg.padded_vocab)
+        self.row_loss = e(N, dtype=f32)
+        self.loss = torch.zeros(1, device=dev, dtype=f32)
+        # backward temporaries (shared by all layers)
+        self.d_res_a, self.d_res_b = e(N, C), e(N, C)
+        self.d_ln = e(N, C)
+        self.d_fc = e(N, Hd)
+        self.d_qkv = e(N, 3 * C)
+        self.d_att = e(N, C)
+        self.delta = e(batch, cfg.n_head, seq, dtype=f32)
+        self.dq_accum = e(N, C, dtype=f32)
+        self.scratch = e(64 * 2 * max(Hd, 3 * C), dtype=f32)
+        self.tokens = torch.zeros(N, device=dev, dtype=torch.int32)
+        self.targets = torch.zeros(N, device=dev, dtype=torch.int32)
+
+    # ------------------------------------------------------------------ forward --
+    def forward(self, *, compute_grad_logits: bool = True, grad_scale: float | None = None) -> torch.Tensor:
+        """Runs on ``self.tokens``/``self.targets``. Leaves d(loss)/d(logits) in ``self.logits``
+        when ``compute_grad_logits``; returns the mean-loss tensor (device, fp32[1])."""
+        K, gemm, cfg, p = self.K, self.gemm, self.cfg, self.p
+        B, T, N = self.B, self.T, self.B * self.T
+        C, nh, hd = cfg.d_model, cfg.n_head, cfg.head_dim
+        K.embedding_forward(self.tokens, p["wte"], p["wpe"], T=T, out=self.x0)
+        x = self.x0
+        for l, a in enumerate(self.acts):
+            pre = f"h.{l}."
+            K.norm_forward(x, p[pre + "ln_1.weight"], p[pre + "ln_1.bias"], eps=cfg.ln_eps,
+                           mode=K.NORM_LAYER, out=a.ln1, mean=a.ln1_mean, rstd=a.ln1_rstd)
+            gemm(a.ln1, p[pre + "attn.c_attn.weight"], bias=p[pre + "attn.c_attn.bias"], out=a.qkv)
+            if cfg.qk_norm:
+                K.qk_norm_forward(a.qkv, nh, nh, hd, eps=cfg.qk_norm_eps, rstd=a.qk_rstd)
+            K.attention_forward(a.qkv[:, :C], a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], B=B, T=T,
+                                n_q_heads=nh, n_kv_heads=nh, head_dim=hd, causal=True,
+                                out=a.att, lse=a.lse)
+            gemm(a.att, p[pre + "attn.c_proj.weight"], bias=p[pre + "attn.c_proj.bias"], resid=x, out=a.x1)
+            K.norm_forward(a.x1, p[pre + "ln_2.weight"], p[pre + "ln_2.bias"], eps=cfg.ln_eps,
+                           mode=K.NORM_LAYER, out=a.ln2, mean=a.ln2_mean, rstd=a.ln2_rstd)
+            gemm(a.ln2, p[pre + "mlp.c_fc.weight"], bias=p[pre + "mlp.c_fc.bias"], act="gelu_tanh",
+                 save_pre=a.fc_pre, out=a.fc_act)
+            gemm(a.fc_act, p[pre + "mlp.c_proj.weight"], bias=p[pre + "mlp.c_proj.bias"], resid=a.x1,
+                 out=a.x2)
+            x = a.x2
+        K.norm_forward(x, p["ln_f.weight"], p["ln_f.bias"], eps=cfg.ln_eps, mode=K.NORM_LAYER,
+                       out=self.lnf, mean=self.lnf_mean, rstd=self.lnf_rstd)
+        if cfg.logit_softcap > 0:
+            gemm(self.lnf, p["wte"], act="tanh_cap", act_param=cfg.logit_softcap, out=self.logits)
+        else:
+            gemm(self.lnf, p["wte"], out=self.logits)
+        K.cross_entropy(self.logits, self.targets, vocab=cfg.vocab_size, cap=cfg.logit_softcap,
+                        z_coef=cfg.z_loss, grad_scale=(1.0 / N if grad_scale is None else grad_scale),
+                        loss_scale=1.0 / N, write_grad=compute_grad_logits, row_loss=self.row_loss,
+                        mean_loss=self.loss)
+        return self.loss
+
+    # ----------------------------------------------------------------- backward --
+    def backward(self) -> None:
+        """Consumes d(logits) left by ``forward`` and writes every gradient (no accumulation:
+        each call overwrites ``self.grads``)."""
+        K, gemm, cfg, p, g = self.K, self.gemm, self.cfg, self.p, self.g
+        B, T = self.B, self.T
+        C, nh, hd = cfg.d_model, cfg.n_head, cfg.head_dim
+        sc = self.scratch
+        dlogits = self.logits
+        # tied head: d(lnf) and d(wte)
+        gemm(dlogits, p["wte"], b_mn=True, out=self.d_ln)
+        gemm(dlogits, self.lnf, a_mn=True, b_mn=True, out=g["wte"])
+        x_last = self.acts[-1].x2 if self.acts else self.x0
+        dx, spare = self.d_res_a, self.d_res_b
+        K.norm_backward_dx(self.d_ln, x_last, p["ln_f.weight"], self.lnf_mean, self.lnf_rstd,
+                           mode=K.NORM_LAYER, out=dx)
+        K.norm_backward_wb(self.d_ln, x_last, self.lnf_mean, self.lnf_rstd, g["ln_f.weight"],
+                           g["ln_f.bias"], sc, mode=K.NORM_LAYER)
+        for l in range(cfg.n_layer - 1, -1, -1):
+            a = self.acts[l]
+            pre = f"h.{l}."
+            x_in = self.acts[l - 1].x2 if l > 0 else self.x0
+            # ---- MLP branch: x2 = c_proj(gelu(c_fc(ln2))) + x1 ----
+            gemm(dx, p[pre + "mlp.c_proj.weight"], b_mn=True, act="gelu_tanh", dact_pre=a.fc_pre,
+                 out=self.d_fc)
+            gemm(dx, a.fc_act, a_mn=True, b_mn=True, out=g[pre + "mlp.c_proj.weight"])
+            K.colsum(dx, g[pre + "mlp.c_proj.bias"], sc)
+            gemm(self.d_fc, p[pre + "mlp.c_fc.weight"], b_mn=True, out=self.d_ln)
+            gemm(self.d_fc, a.ln2, a_mn=True, b_mn=True, out=g[pre + "mlp.c_fc.weight"])
+            K.colsum(self.d_fc, g[pre + "mlp.c_fc.bias"], sc)
+            K.norm_backward_dx(self.d_ln, a.x1, p[pre + "ln_2.weight"], a.ln2_mean, a.ln2_rstd,
+                               mode=K.NORM_LAYER, dresid=dx, out=spare)
+            K.norm_backward_wb(self.d_ln, a.x1, a.ln2_mean, a.ln2_rstd, g[pre + "ln_2.weight"],
+                               g[pre + "ln_2.bias"], sc, mode=K.NORM_LAYER)
+            dx, spare = spare, dx  # dx now holds d(x1)
+            # ---- attention branch: x1 = c_proj(att) + x ----
+            gemm(dx, p[pre + "attn.c_proj.weight"], b_mn=True, out=self.d_att)
+            gemm(dx, a.att, a_mn=True, b_mn=True, out=g[pre + "attn.c_proj.weight"])
+            K.colsum(dx, g[pre + "attn.c_proj.bias"], sc)
+            K.attention_backward(self.d_att, a.qkv[:, :C], a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], a.att,
+                                 a.lse, B=B, T=T, n_q_heads=nh, n_kv_heads=nh, head_dim=hd, causal=True,
+                                 dq=self.d_qkv[:, :C], dk=self.d_qkv[:, C:2 * C], dv=self.d_qkv[:, 2 * C:],
+                                 delta=self.delta, dq_accum=self.dq_accum)
+            if cfg.qk_norm:
+                K.qk_norm_backward(self.d_qkv, a.qkv, a.qk_rstd, nh, nh, hd)
+            gemm(self.d_qkv, p[pre + "attn.c_attn.weight"], b_mn=True, out=self.d_ln)
+            gemm(self.d_qkv, a.ln1, a_mn=True, b_mn=True, out=g[pre + "attn.c_attn.weight"])
+            K.colsum(self.d_qkv, g[pre + "attn.c_attn.bias"], sc)
+            K.norm_backward_dx(self.d_ln, x_in, p[pre + "ln_1.weight"], a.ln1_mean, a.ln1_rstd,
+                               mode=K.NORM_LAYER, dresid=dx, out=spare)
+            K.norm_backward_wb(self.d_ln, x_in, a.ln1_mean, a.ln1_rstd, g[pre + "ln_1.weight"],
+                               g[pre + "ln_1.bias"], sc, mode=K.NORM_LAYER)
+            dx, spare = spare, dx
+        K.embedding_backward(dx, self.tokens, g["wte"], g["wpe"][:T], B=B, T=T)
+        if T < cfg.max_seq_len:
+            g["wpe"][T:].zero_()
+
+    def set_batch(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
+        """Copy a batch (any integer dtype, host or device) into the engine's int32 inputs."""
+        self.tokens.copy_(tokens.reshape(-1), non_blocking=True)
+        self.targets.copy_(targets.reshape(-1), non_blocking=True)
+
+    def logits_view(self) -> torch.Tensor:
+        return self.logits.view(self.B, self.T, -1)[..., :self.cfg.vocab_size]

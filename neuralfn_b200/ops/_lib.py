@@ -68,6 +68,14 @@ def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far (host-side counter;
+    launches replayed from a CUDA graph are not seen by it)."""
+    lib = load()
+    lib.nfn_launch_count.restype = ctypes.c_longlong
+    return int(lib.nfn_launch_count())
+
+
 def status_read_reset() -> int:
     """Synchronise and return the first error code any kernel recorded (0 = ok)."""
     return int(load().nfn_status_read_reset())

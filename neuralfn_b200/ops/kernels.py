@@ -219,15 +219,21 @@ def _ptr_array(ptrs):
     return arr
 
 
-def peer_arrive(peer_flag_ptrs, rank: int, world: int, slot: int, epoch: int):
+def counter_add(counter, value: int = 1):
+    """counter (int32 device tensor)[0] += value, on the stream."""
+    rc = _lib.load().nfn_counter_add(_p(counter), c_int(value), _st())
+    _lib.check(rc, "nfn_counter_add")
+
+
+def peer_arrive(peer_flag_ptrs, rank: int, world: int, slot: int, epoch: int, epoch_dev=None):
     rc = _lib.load().nfn_peer_arrive(_ptr_array(peer_flag_ptrs), c_int(rank), c_int(world), c_int(slot),
-                                     c_int(epoch), _st())
+                                     c_int(epoch), _p(epoch_dev), _st())
     _lib.check(rc, "nfn_peer_arrive")
 
 
-def peer_wait(my_flags_ptr: int, world: int, slot: int, epoch: int, timeout_s: float = 2.0):
+def peer_wait(my_flags_ptr: int, world: int, slot: int, epoch: int, timeout_s: float = 2.0, epoch_dev=None):
     rc = _lib.load().nfn_peer_wait(c_void_p(my_flags_ptr), c_int(world), c_int(slot), c_int(epoch),
-                                   c_double(timeout_s), _st())
+                                   _p(epoch_dev), c_double(timeout_s), _st())
     _lib.check(rc, "nfn_peer_wait")
 
 
@@ -237,15 +243,16 @@ def dp_reduce(peer_grad_ptrs, rank: int, world: int, lo: int, n: int, gshard, pa
     _lib.check(rc, "nfn_dp_reduce")
 
 
-def dp_norm_publish(partial, shard_n: int, peer_slot_ptrs, rank: int, world: int, epoch: int):
+def dp_norm_publish(partial, shard_n: int, peer_slot_ptrs, rank: int, world: int, epoch: int, epoch_dev=None):
     rc = _lib.load().nfn_dp_norm_publish(_p(partial), c_longlong(shard_n), _ptr_array(peer_slot_ptrs),
-                                         c_int(rank), c_int(world), c_int(epoch), _st())
+                                         c_int(rank), c_int(world), c_int(epoch), _p(epoch_dev), _st())
     _lib.check(rc, "nfn_dp_norm_publish")
 
 
-def dp_norm_collect(my_slots_ptr: int, world: int, epoch: int, hyper, clip, timeout_s: float = 2.0):
-    rc = _lib.load().nfn_dp_norm_collect(c_void_p(my_slots_ptr), c_int(world), c_int(epoch), _p(hyper),
-                                         _p(clip), c_double(timeout_s), _st())
+def dp_norm_collect(my_slots_ptr: int, world: int, epoch: int, hyper, clip, timeout_s: float = 2.0,
+                    epoch_dev=None):
+    rc = _lib.load().nfn_dp_norm_collect(c_void_p(my_slots_ptr), c_int(world), c_int(epoch), _p(epoch_dev),
+                                         _p(hyper), _p(clip), c_double(timeout_s), _st())
     _lib.check(rc, "nfn_dp_norm_collect")
 
 

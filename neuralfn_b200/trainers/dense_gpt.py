@@ -1,0 +1,174 @@
+"""Dense GPT trainer: engine + sharded optimizer + CUDA-graph step.
+
+Public call a user makes::
+
+    trainer = DenseGPTTrainer(GPT2Config.variant("gpt2_qknorm_softcap_zloss"), batch=16, seq=1024)
+    loss = trainer.train_step(tokens, targets)      # host (pinned) or device int tensors
+
+One optimizer step = forward + backward + (data-parallel reduce) + AdamW, captured
+once into a CUDA graph and replayed; per step the host only uploads the batch and
+the 16-float hyper-parameter block. Under ``torch.distributed`` (one process per
+GPU) every rank trains on its own micro-batch and the gradient reduction, sharded
+update and parameter all-gather run inside the peer-memory kernels of
+``neuralfn_b200.parallel.dp`` - the step makes no NCCL call.
+
+Mirrors the contract of the reference's native dense trainer loop
+(``nfn_gpt2_native_train.cpp:28362-28470``: zero/accumulate grads, clip on device,
+scheduled lr, one AdamW launch) for the no-accumulation case.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from ..models.gpt2 import FlatLayout, GPT2Config, GPT2Engine, gpt2_param_specs, init_gpt2_params_
+from ..parallel.dp import AdamWConfig, ShardedAdamW, SymmetricBuffers
+
+__all__ = ["DenseGPTTrainer", "TrainReport"]
+
+
+@dataclass
+class TrainReport:
+    steps: int
+    tokens_processed: int
+    train_loop_wall_ms: float
+    train_compute_tokens_per_second: float
+    train_losses: list[float]
+
+
+class DenseGPTTrainer:
+    def __init__(self, cfg: GPT2Config, batch: int, seq: int, optim: AdamWConfig | None = None, *,
+                 device: torch.device | str | None = None, seed: int = 1337, use_cuda_graph: bool = True,
+                 group=None) -> None:
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("DenseGPTTrainer runs on CUDA (sm_100a); use models.gpt2.reference_forward on CPU")
+        self.cfg, self.batch, self.seq = cfg, batch, seq
+        self.optim_cfg = optim or AdamWConfig()
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.layout = FlatLayout(gpt2_param_specs(cfg), world=self.world)
+        self.bufs = SymmetricBuffers(self.layout.n_total, self.device, group)
+        # identical initial weights on every rank (same seed), fp32 master -> bf16 params
+        master = torch.empty(self.layout.n_total, dtype=torch.float32, device=self.device)
+        init_gpt2_params_(cfg, self.layout, master, seed)
+        self.opt = ShardedAdamW(self.layout, self.bufs, self.optim_cfg, master_init=master)
+        self.bufs.params.copy_(master.to(torch.bfloat16))
+        del master
+        self.bufs.grads.zero_()
+        self.engine = GPT2Engine(cfg, self.layout, self.bufs.params, self.bufs.grads, batch, seq)
+        self.use_cuda_graph = use_cuda_graph
+        self._graph: torch.cuda.CUDAGraph | None = None
+        self._warmed = False
+        self.launches_per_step = 0
+        self._h_tokens = torch.zeros(batch * seq, dtype=torch.int32).pin_memory()
+        self._h_targets = torch.zeros(batch * seq, dtype=torch.int32).pin_memory()
+        self._h_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
+        if self.world > 1:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group)
+
+    # ------------------------------------------------------------------ step --
+    def _launch_step(self) -> None:
+        self.engine.forward()
+        self.engine.backward()
+        self.opt.launch_step()
+
+    def _run_step(self) -> None:
+        """forward + backward + optimizer on the batch already in the engine buffers."""
+        from ..ops import _lib
+        self.opt.stage_hyper()
+        if not self.use_cuda_graph:
+            before = _lib.launch_count()
+            self._launch_step()
+            self.launches_per_step = _lib.launch_count() - before
+        elif not self._warmed:
+            # the first step runs eagerly: it sets kernel attributes and fills the
+            # tensor-map cache, neither of which may happen during stream capture
+            before = _lib.launch_count()
+            self._launch_step()
+            self.launches_per_step = _lib.launch_count() - before
+            self._warmed = True
+        elif self._graph is None:
+            torch.cuda.synchronize(self.device)
+            self._graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph):
+                self._launch_step()
+            self._graph.replay()
+        else:
+            self._graph.replay()
+        self.opt.step_count += 1
+
+    def upload(self, tokens: torch.Tensor, targets: torch.Tensor) -> int:
+        """Copy a batch into the device input buffers; returns the bytes moved host->device."""
+        moved = 0
+        for src, stage, dst in ((tokens, self._h_tokens, self.engine.tokens),
+                                (targets, self._h_targets, self.engine.targets)):
+            src = src.reshape(-1)
+            if src.device.type == "cpu":
+                if src.dtype == torch.int32 and src.is_pinned():
+                    dst.copy_(src, non_blocking=True)
+                else:
+                    stage.copy_(src)
+                    dst.copy_(stage, non_blocking=True)
+                moved += dst.numel() * dst.element_size()
+            else:
+                dst.copy_(src)
+        return moved
+
+    def train_step(self, tokens: torch.Tensor, targets: torch.Tensor, *, return_loss: bool = True):
+        """One optimizer step. Returns the mean token loss of this rank's micro-batch (python
+        float, read back from the device) when ``return_loss``."""
+        self.upload(tokens, targets)
+        self._run_step()
+        if return_loss:
+            self._h_loss.copy_(self.engine.loss, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return float(self._h_loss[0])
+        return None
+
+    def step_on_device_batch(self) -> None:
+        """Step on whatever batch is already resident (used by kernel-only timing)."""
+        self._run_step()
+
+    @property
+    def tokens_per_step(self) -> int:
+        return self.batch * self.seq * self.world
+
+    # --------------------------------------------------------------- training --
+    def train(self, batches, max_steps: int, log_every: int = 0) -> TrainReport:
+        losses = []
+        torch.cuda.synchronize(self.device)
+        t0 = time.perf_counter()
+        n = 0
+        for tokens, targets in batches:
+            loss = self.train_step(tokens, targets)
+            losses.append(loss)
+            n += 1
+            if log_every and n % log_every == 0 and self.rank == 0:
+                print(f"step {n:6d} loss {loss:.4f} lr {self.opt.hyper_host[0].item():.3e} "
+                      f"gnorm {self.opt.grad_norm:.3f}", flush=True)
+            if n >= max_steps:
+                break
+        torch.cuda.synchronize(self.device)
+        wall = (time.perf_counter() - t0) * 1e3
+        toks = n * self.tokens_per_step
+        return TrainReport(n, toks, wall, toks / (wall / 1e3) if wall > 0 else 0.0, losses)
+
+    def check_status(self) -> None:
+        from ..ops import _lib
+        _lib.assert_status_ok("dense gpt step")
+
+    # ------------------------------------------------------------ checkpoints --
+    def full_master(self) -> torch.Tensor:
+        """fp32 master weights of the whole model on this rank (gathers shards)."""
+        if self.world == 1:
+            return self.opt.master.clone()
+        parts = [torch.empty_like(self.opt.master) for _ in range(self.world)]
+        dist.all_gather(parts, self.opt.master)
+        return torch.cat(parts)
