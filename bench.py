@@ -176,9 +176,6 @@ def run_reference(args) -> dict:
     ref = os.path.join(root, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "neuralfn")):
         return {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of the reference)"}
-    if args.gpus > 1:
-        return {"impl": "reference",
-                "unavailable": "the reference has no data-parallel training mode (single process, single device)"}
     sys.path.insert(0, ref)
     try:
         from baseline.reference_arm import run as run_ref

@@ -1,0 +1,99 @@
+// Epilogue building blocks of the tcgen05 GEMM: activation math on 8-wide register
+// groups (branches hoisted out of the element loops so only the selected activation
+// is ever evaluated), TMA bulk stores out of a swizzled shared-memory staging tile,
+// and the direct (bounds-checked) store path used for fp32 / accumulating outputs.
+#pragma once
+#include "common.h"
+#include "sm100_ptx.cuh"
+
+namespace nfn {
+
+struct GemmParams {
+  void* c;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* aux_in;
+  __nv_bfloat16* aux_out;
+  int m, n, k;
+  int ldc, ld_aux_in, ld_aux_out;
+  int flags;
+  float alpha, act_param;
+  int tiles_m, tiles_n;
+  int split_k;        // >= 1; tile index space is tiles_m * tiles_n * split_k
+  int kb_per_split;   // k-blocks handled by one split
+  long long split_stride;  // elements between consecutive split slices of the fp32 workspace
+  int* status;
+};
+
+__device__ __forceinline__ void act8(float (&v)[8], int act, float prm) {
+  if (act == NFN_ACT_GELU_TANH) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = gelu_tanh_f(v[j]);
+  } else if (act == NFN_ACT_GELU_ERF) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = gelu_erf_f(v[j]);
+  } else if (act == NFN_ACT_SILU) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = silu_f(v[j]);
+  } else if (act == NFN_ACT_RELU2) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const float r = fmaxf(v[j], 0.f); v[j] = r * r; }
+  } else if (act == NFN_ACT_TANH_CAP) {
+    const float inv = 1.f / prm;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = prm * fast_tanh(v[j] * inv);
+  }
+}
+
+// v[j] *= act'(pre[j])
+__device__ __forceinline__ void dact8(float (&v)[8], const float (&pre)[8], int act, float prm) {
+  if (act == NFN_ACT_GELU_TANH) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= dgelu_tanh_f(pre[j]);
+  } else if (act == NFN_ACT_GELU_ERF) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= dgelu_erf_f(pre[j]);
+  } else if (act == NFN_ACT_SILU) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= dsilu_f(pre[j]);
+  } else if (act == NFN_ACT_RELU2) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= pre[j] > 0.f ? 2.f * pre[j] : 0.f;
+  } else if (act == NFN_ACT_TANH_CAP) {
+    const float inv = 1.f / prm;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const float t = fast_tanh(pre[j] * inv); v[j] *= 1.f - t * t; }
+  }
+}
+
+__device__ __forceinline__ void unpack8_bf16(const uint4& u, float (&f)[8]) {
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8_bf16(const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+  return u;
+}
+
+// ---- TMA bulk store (shared -> global), bulk async-group completion ---------------
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t smem_src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(tmap), "r"(smem_src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Row r of a [128 x 64] bf16 staging tile with the 128-byte swizzle TMA expects:
+// 16-byte chunk c of row r lives at chunk (c ^ (r & 7)).
+__device__ __forceinline__ void stage_store8(uint8_t* tile, int r, int chunk, const uint4& v) {
+  *reinterpret_cast<uint4*>(tile + r * 128 + ((chunk ^ (r & 7)) << 4)) = v;
+}
+
+}  // namespace nfn

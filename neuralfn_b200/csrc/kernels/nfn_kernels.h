@@ -57,6 +57,9 @@ typedef struct {
   const void* bias;
   const void* aux_in; int ld_aux_in;
   void* aux_out; int ld_aux_out;
+  // split-K (plain products only): 0 = choose automatically, 1 = never, n > 1 = force n.
+  // Needs an fp32 workspace of split * M * N elements; without one no split happens.
+  void* workspace; long long workspace_bytes; int split_k;
 } nfn_gemm_args;
 
 int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream);

@@ -248,89 +248,6 @@ __global__ void colsum_final_kernel(const float* __restrict__ partial, __nv_bflo
   out[col] = __float2bfloat16(a + (accumulate ? __bfloat162float(out[col]) : 0.f));
 }
 
-// --------------------------------------------------------------- QK norm -----
-// Packed qkv rows: [tokens, 3*H*D] laid out (q | k | v), each H heads of D.
-// In place: q and k heads are replaced by x * rsqrt(mean(x^2) + eps) (* q_scale for q).
-// rstd[tokens, 2, H] saved for the backward. One warp per (token, q-or-k head).
-template <int D>
-__global__ void __launch_bounds__(256)
-qk_norm_fwd_kernel(__nv_bfloat16* __restrict__ qkv, float* __restrict__ rstd, int tokens, int Hq,
-                   int Hkv, int ld, float eps, float q_scale) {
-  constexpr int PER = D / 32;  // elements per lane (2 or 4)
-  const int warp_global = blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  const int heads = Hq + Hkv;
-  if (warp_global >= tokens * heads) return;
-  const int tok = warp_global / heads, h = warp_global % heads;
-  __nv_bfloat16* p = qkv + (size_t)tok * ld + h * D + lane * PER;  // q heads then k heads are contiguous
-  float v[PER];
-  float sq = 0.f;
-  if (PER == 2) {
-    float2 f = unpack_bf16x2(*reinterpret_cast<uint32_t*>(p));
-    v[0] = f.x; v[1] = f.y;
-  } else {
-    uint2 u = *reinterpret_cast<uint2*>(p);
-    float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y);
-    v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y;
-  }
-#pragma unroll
-  for (int j = 0; j < PER; ++j) sq += v[j] * v[j];
-  const float rs = rsqrtf(warp_sum(sq) / D + eps);
-  const float sc = rs * (h < Hq ? q_scale : 1.f);
-  if (lane == 0) rstd[(size_t)tok * heads + h] = rs;
-  if (PER == 2) {
-    *reinterpret_cast<uint32_t*>(p) = pack_bf16x2(v[0] * sc, v[1] * sc);
-  } else {
-    uint2 u;
-    u.x = pack_bf16x2(v[0] * sc, v[1] * sc); u.y = pack_bf16x2(v[2] * sc, v[3] * sc);
-    *reinterpret_cast<uint2*>(p) = u;
-  }
-}
-// Backward in place on dqkv: given normalised y (= x*rstd*scale) and dy:
-//   dx = scale*rstd * (dy - n * mean(dy*n)),  n = y/scale
-template <int D>
-__global__ void __launch_bounds__(256)
-qk_norm_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __restrict__ qkv_normed,
-                   const float* __restrict__ rstd, int tokens, int Hq, int Hkv, int ld,
-                   float q_scale) {
-  constexpr int PER = D / 32;
-  const int warp_global = blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  const int heads = Hq + Hkv;
-  if (warp_global >= tokens * heads) return;
-  const int tok = warp_global / heads, h = warp_global % heads;
-  const size_t off = (size_t)tok * ld + h * D + lane * PER;
-  const float sc = (h < Hq ? q_scale : 1.f);
-  float dy[PER], n[PER];
-  if (PER == 2) {
-    float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(dqkv + off));
-    float2 b = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(qkv_normed + off));
-    dy[0] = a.x; dy[1] = a.y; n[0] = b.x / sc; n[1] = b.y / sc;
-  } else {
-    uint2 ua = *reinterpret_cast<const uint2*>(dqkv + off);
-    uint2 ub = *reinterpret_cast<const uint2*>(qkv_normed + off);
-    float2 a0 = unpack_bf16x2(ua.x), a1 = unpack_bf16x2(ua.y);
-    float2 b0 = unpack_bf16x2(ub.x), b1 = unpack_bf16x2(ub.y);
-    dy[0] = a0.x; dy[1] = a0.y; dy[2] = a1.x; dy[3] = a1.y;
-    n[0] = b0.x / sc; n[1] = b0.y / sc; n[2] = b1.x / sc; n[3] = b1.y / sc;
-  }
-  float dot = 0.f;
-#pragma unroll
-  for (int j = 0; j < PER; ++j) dot += dy[j] * n[j];
-  dot = warp_sum(dot) / D;
-  const float rs = rstd[(size_t)tok * heads + h] * sc;
-  float o[PER];
-#pragma unroll
-  for (int j = 0; j < PER; ++j) o[j] = rs * (dy[j] - n[j] * dot);
-  if (PER == 2) {
-    *reinterpret_cast<uint32_t*>(dqkv + off) = pack_bf16x2(o[0], o[1]);
-  } else {
-    uint2 u;
-    u.x = pack_bf16x2(o[0], o[1]); u.y = pack_bf16x2(o[2], o[3]);
-    *reinterpret_cast<uint2*>(dqkv + off) = u;
-  }
-}
-
 template <typename F>
 static int dispatch_vec(int C, F&& f) {
   if (C % 8) return fail(-1, "norm: width must be a multiple of 8");
@@ -413,40 +330,3 @@ extern "C" int nfn_colsum(const void* dy, int ld, void* out, float* scratch, int
   return launch_check("colsum", 2);
 }
 
-extern "C" int nfn_qk_norm_forward(void* qkv, float* rstd, int tokens, int n_q_heads,
-                                   int n_kv_heads, int head_dim, int ld, float eps, float q_scale,
-                                   nfn_stream_t stream) {
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int warps = tokens * (n_q_heads + n_kv_heads);
-  if (warps <= 0) return 0;
-  const int grid = ceil_div(warps, 8);
-  if (head_dim == 64)
-    qk_norm_fwd_kernel<64><<<grid, 256, 0, st>>>((__nv_bfloat16*)qkv, rstd, tokens, n_q_heads,
-                                                 n_kv_heads, ld, eps, q_scale);
-  else if (head_dim == 128)
-    qk_norm_fwd_kernel<128><<<grid, 256, 0, st>>>((__nv_bfloat16*)qkv, rstd, tokens, n_q_heads,
-                                                  n_kv_heads, ld, eps, q_scale);
-  else
-    return fail(-1, "qk_norm: head_dim must be 64 or 128");
-  return launch_check("qk_norm_fwd");
-}
-
-extern "C" int nfn_qk_norm_backward(void* dqkv, const void* qkv_normed, const float* rstd,
-                                    int tokens, int n_q_heads, int n_kv_heads, int head_dim, int ld,
-                                    float q_scale, nfn_stream_t stream) {
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int warps = tokens * (n_q_heads + n_kv_heads);
-  if (warps <= 0) return 0;
-  const int grid = ceil_div(warps, 8);
-  if (head_dim == 64)
-    qk_norm_bwd_kernel<64><<<grid, 256, 0, st>>>((__nv_bfloat16*)dqkv,
-                                                 (const __nv_bfloat16*)qkv_normed, rstd, tokens,
-                                                 n_q_heads, n_kv_heads, ld, q_scale);
-  else if (head_dim == 128)
-    qk_norm_bwd_kernel<128><<<grid, 256, 0, st>>>((__nv_bfloat16*)dqkv,
-                                                  (const __nv_bfloat16*)qkv_normed, rstd, tokens,
-                                                  n_q_heads, n_kv_heads, ld, q_scale);
-  else
-    return fail(-1, "qk_norm: head_dim must be 64 or 128");
-  return launch_check("qk_norm_bwd");
-}

@@ -253,6 +253,7 @@ class GPT2Engine:
         self.delta = e(batch, cfg.n_head, seq, dtype=f32)
         self.dq_accum = e(N, C, dtype=f32)
         self.scratch = e(64 * 2 * max(Hd, 3 * C), dtype=f32)
+        self.ws = e(32 * 1024 * 1024, dtype=f32)  # split-K partial slices of the weight-gradient GEMMs
         self.tokens = torch.zeros(N, device=dev, dtype=torch.int32)
         self.targets = torch.zeros(N, device=dev, dtype=torch.int32)
 
@@ -320,10 +321,10 @@ class GPT2Engine:
             # ---- MLP branch: x2 = c_proj(gelu(c_fc(ln2))) + x1 ----
             gemm(dx, p[pre + "mlp.c_proj.weight"], b_mn=True, act="gelu_tanh", dact_pre=a.fc_pre,
                  out=self.d_fc)
-            gemm(dx, a.fc_act, a_mn=True, b_mn=True, out=g[pre + "mlp.c_proj.weight"])
+            gemm(dx, a.fc_act, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "mlp.c_proj.weight"])
             K.colsum(dx, g[pre + "mlp.c_proj.bias"], sc)
             gemm(self.d_fc, p[pre + "mlp.c_fc.weight"], b_mn=True, out=self.d_ln)
-            gemm(self.d_fc, a.ln2, a_mn=True, b_mn=True, out=g[pre + "mlp.c_fc.weight"])
+            gemm(self.d_fc, a.ln2, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "mlp.c_fc.weight"])
             K.colsum(self.d_fc, g[pre + "mlp.c_fc.bias"], sc)
             K.norm_backward_dx(self.d_ln, a.x1, p[pre + "ln_2.weight"], a.ln2_mean, a.ln2_rstd,
                                mode=K.NORM_LAYER, dresid=dx, out=spare)
@@ -332,7 +333,7 @@ class GPT2Engine:
             dx, spare = spare, dx  # dx now holds d(x1)
             # ---- attention branch: x1 = c_proj(att) + x ----
             gemm(dx, p[pre + "attn.c_proj.weight"], b_mn=True, out=self.d_att)
-            gemm(dx, a.att, a_mn=True, b_mn=True, out=g[pre + "attn.c_proj.weight"])
+            gemm(dx, a.att, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "attn.c_proj.weight"])
             K.colsum(dx, g[pre + "attn.c_proj.bias"], sc)
             K.attention_backward(self.d_att, a.qkv[:, :C], a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], a.att,
                                  a.lse, B=B, T=T, n_q_heads=nh, n_kv_heads=nh, head_dim=hd, causal=True,
@@ -341,7 +342,7 @@ class GPT2Engine:
             if cfg.qk_norm:
                 K.qk_norm_backward(self.d_qkv, a.qkv, a.qk_rstd, nh, nh, hd)
             gemm(self.d_qkv, p[pre + "attn.c_attn.weight"], b_mn=True, out=self.d_ln)
-            gemm(self.d_qkv, a.ln1, a_mn=True, b_mn=True, out=g[pre + "attn.c_attn.weight"])
+            gemm(self.d_qkv, a.ln1, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "attn.c_attn.weight"])
             K.colsum(self.d_qkv, g[pre + "attn.c_attn.bias"], sc)
             K.norm_backward_dx(self.d_ln, x_in, p[pre + "ln_1.weight"], a.ln1_mean, a.ln1_rstd,
                                mode=K.NORM_LAYER, dresid=dx, out=spare)

@@ -59,7 +59,7 @@ def build_kernels(force: bool = False, verbose: bool = False, ptxas_info: bool =
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     out = LIB_DIR / "libnfn_b200_kernels.so"
     sources = sorted(KERNEL_SRC.glob("*.cu"))
-    headers = sorted(list(KERNEL_SRC.glob("*.h")) + list(KERNEL_SRC.glob("*.cuh")))
+    headers = sorted(list(KERNEL_SRC.glob("*.h")) + list(KERNEL_SRC.glob("*.cuh")) + list(KERNEL_SRC.glob("*.inc")))
     hdr_digest = _digest(headers)
     extra = ["-Xptxas", "-v"] if ptxas_info else []
     jobs = []

@@ -29,6 +29,7 @@ class GemmArgs(ctypes.Structure):
         ("bias", ctypes.c_void_p),
         ("aux_in", ctypes.c_void_p), ("ld_aux_in", ctypes.c_int),
         ("aux_out", ctypes.c_void_p), ("ld_aux_out", ctypes.c_int),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_longlong), ("split_k", ctypes.c_int),
     ]
 
 

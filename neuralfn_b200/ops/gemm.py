@@ -43,7 +43,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          save_pre: torch.Tensor | None = None, resid: torch.Tensor | None = None,
          dact_pre: torch.Tensor | None = None, accum: bool = False,
          out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
-         alpha: float = 1.0) -> torch.Tensor:
+         alpha: float = 1.0, workspace: torch.Tensor | None = None, split_k: int = 0) -> torch.Tensor:
     _check2d(a, "a")
     _check2d(b, "b")
     if a_mn:
@@ -90,6 +90,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     elif out.dtype != torch.bfloat16:
         raise ValueError("out must be bf16 or fp32")
     args.flags = flags
+    if workspace is not None:
+        args.workspace = workspace.data_ptr()
+        args.workspace_bytes = workspace.numel() * workspace.element_size()
+        args.split_k = split_k
+    else:
+        args.split_k = 1
     rc = _lib.load().nfn_gemm_bf16(ctypes.byref(args), ctypes.c_void_p(_lib.stream_ptr()))
     _lib.check(rc, "nfn_gemm_bf16")
     return out
