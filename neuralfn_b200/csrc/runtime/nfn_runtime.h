@@ -95,6 +95,17 @@ int nfn_write_records(const char* path, int kind, uint64_t records, uint32_t seq
                       uint32_t pad_token_id, const char* tokenizer_sha256, const char* chat_template_sha256,
                       const char* tokenizer_revision, const char* split, const void* payload, uint64_t payload_bytes);
 
+// ---- checkpoint containers --------------------------------------------------------------
+// header + N caller-described segments. Writing is exclusive (never overwrites, follows no
+// symlink, staged + fsync + link); reading demands the exact size. out_sha65 (optional)
+// receives the SHA-256 of the whole file as lower-case hex + NUL.
+int nfn_ckpt_write(const char* path, const void* header, uint64_t header_bytes, const void* const* segments,
+                   const uint64_t* segment_bytes, int n_segments, char* out_sha65);
+int nfn_ckpt_read(const char* path, void* header, uint64_t header_bytes, void* const* segments,
+                  const uint64_t* segment_bytes, int n_segments, char* out_sha65);
+int nfn_ckpt_peek(const char* path, void* header, uint64_t header_bytes, uint64_t* file_bytes);
+int nfn_ckpt_publish_dir(const char* staging_dir, const char* final_dir);
+
 #ifdef __cplusplus
 }
 #endif

@@ -51,6 +51,10 @@ def lib() -> C.CDLL:
         "nfn_records_reset": (None, [vp]),
         "nfn_records_next": (i32, [vp, vp, vp, vp, vp, i64]),
         "nfn_write_records": (i32, [cp, i32, u64, u32, u32, u32, cp, cp, cp, cp, vp, u64]),
+        "nfn_ckpt_write": (i32, [cp, vp, u64, C.POINTER(vp), C.POINTER(u64), i32, C.c_char_p]),
+        "nfn_ckpt_read": (i32, [cp, vp, u64, C.POINTER(vp), C.POINTER(u64), i32, C.c_char_p]),
+        "nfn_ckpt_peek": (i32, [cp, vp, u64, C.POINTER(u64)]),
+        "nfn_ckpt_publish_dir": (i32, [cp, cp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)

@@ -1,0 +1,110 @@
+"""Dense GPT checkpoint files: byte layout against the documented reference format,
+exclusive writes, exact-size reads, single-file and rank-sharded optimizer round trips."""
+import json
+import struct
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+from neuralfn_b200.checkpoint import (consolidate_sharded_optimizer, inspect_dense_model, load_dense_checkpoint,
+                                      read_dense_model, save_dense_checkpoint, write_container)
+from neuralfn_b200.data._rt import NativeRuntimeError
+from neuralfn_b200.models.gpt2 import FlatLayout, GPT2Config, gpt2_param_specs, init_gpt2_params_
+from neuralfn_b200.parallel.dp import AdamWConfig, ShardedAdamW, SymmetricBuffers
+
+
+def _cpu_trainer(seed=3):
+    cfg = GPT2Config.variant("gpt2_qknorm_softcap_zloss", n_layer=2, n_head=2, d_model=32, vocab_size=100, max_seq_len=16)
+    layout = FlatLayout(gpt2_param_specs(cfg), world=1)
+    bufs = SymmetricBuffers(layout.n_total, torch.device("cpu"))
+    master = torch.empty(layout.n_total)
+    init_gpt2_params_(cfg, layout, master, seed)
+    opt = ShardedAdamW(layout, bufs, AdamWConfig(), master_init=master)
+    opt.m.normal_(generator=torch.Generator().manual_seed(seed))
+    opt.v.uniform_(generator=torch.Generator().manual_seed(seed + 1))
+    opt.step_count = 7
+    return SimpleNamespace(cfg=cfg, layout=layout, bufs=bufs, opt=opt, device=torch.device("cpu"))
+
+
+def test_model_file_layout_and_roundtrip(tmp_path):
+    tr = _cpu_trainer()
+    digests = save_dense_checkpoint(tr, tmp_path, sharded_optimizer=False)
+    raw = (tmp_path / "model_00000007.bin").read_bytes()
+    head = struct.unpack("<256i", raw[:1024])
+    assert head[:8] == (20240326, 5, 16, 100, 2, 2, 32, 128) and not any(head[8:])
+    specs = gpt2_param_specs(tr.cfg)
+    assert len(raw) == 1024 + 2 * sum(s.numel for s in specs)
+    # first tensor is wte[Vp, C] in bf16, directly after the header
+    wte = torch.frombuffer(bytearray(raw[1024:1024 + 2 * 128 * 32]), dtype=torch.bfloat16).view(128, 32)
+    assert torch.equal(wte, tr.layout.view(tr.bufs.params, "wte"))
+    info = inspect_dense_model(tmp_path / "model_00000007.bin")
+    assert info["parameter_count"] == sum(s.numel for s in specs)
+    cfg, tensors, sha = read_dense_model(tmp_path / "model_00000007.bin")
+    assert cfg.qk_norm and cfg.logit_softcap == 30.0 and sha == digests["model_00000007.bin"]
+    assert torch.equal(tensors["h.1.mlp.c_proj.weight"], tr.layout.view(tr.bufs.params, "h.1.mlp.c_proj.weight"))
+    phead = struct.unpack("<32q", (tmp_path / "parameters_00000007.bin").read_bytes()[:256])
+    assert phead[:3] == (20260711, 1, 7) and phead[9] == len(specs)
+    ohead = struct.unpack("<32q", (tmp_path / "optimizer_00000007.bin").read_bytes()[:256])
+    assert ohead[0] == 20260710 and ohead[10] == 2 * phead[10]
+    assert json.loads((tmp_path / "DONE_00000007").read_text()) == digests
+
+
+def test_resume_restores_master_and_moments(tmp_path):
+    a = _cpu_trainer(seed=3)
+    save_dense_checkpoint(a, tmp_path, sharded_optimizer=False)
+    b = _cpu_trainer(seed=9)
+    got = load_dense_checkpoint(b, tmp_path)
+    assert got == {"step": 7, "model": True, "master": True, "moments": True} and b.opt.step_count == 7
+    used = a.layout.n_used
+    for name in ("master", "m", "v"):
+        x, y = getattr(a.opt, name), getattr(b.opt, name)
+        for s in gpt2_param_specs(a.cfg):
+            assert torch.equal(a.layout.view(x, s.name), b.layout.view(y, s.name)), (name, s.name)
+    assert torch.equal(a.bufs.params[:used], b.bufs.params[:used])
+
+
+def test_sharded_optimizer_manifest_and_consolidation(tmp_path):
+    a = _cpu_trainer()
+    digests = save_dense_checkpoint(a, tmp_path, sharded_optimizer=True)
+    man = json.loads((tmp_path / "optimizer_00000007.manifest.json").read_text())
+    assert man["world_size"] == 1 and man["shards"][0]["sha256"] == digests["optimizer_00000007.rank00000.bin"]
+    master, m, v = consolidate_sharded_optimizer(tmp_path, 7, a.cfg)
+    assert torch.equal(m, a.opt.m) and torch.equal(v, a.opt.v) and torch.equal(master, a.opt.master)
+    b = _cpu_trainer(seed=11)
+    assert load_dense_checkpoint(b, tmp_path)["moments"]
+    assert torch.equal(b.opt.v, a.opt.v)
+    blob = bytearray((tmp_path / "optimizer_00000007.rank00000.bin").read_bytes())
+    blob[-1] ^= 1
+    (tmp_path / "optimizer_00000007.rank00000.bin").write_bytes(bytes(blob))
+    with pytest.raises(ValueError, match="checksum"):
+        load_dense_checkpoint(_cpu_trainer(), tmp_path)
+
+
+def test_model_only_is_a_warm_start(tmp_path):
+    a = _cpu_trainer()
+    save_dense_checkpoint(a, tmp_path, sharded_optimizer=False)
+    for f in ("parameters_00000007.bin", "optimizer_00000007.bin"):
+        (tmp_path / f).unlink()
+    b = _cpu_trainer(seed=5)
+    got = load_dense_checkpoint(b, tmp_path)
+    assert got["model"] and not got["moments"] and b.opt.step_count == 0
+    assert float(b.opt.m.abs().sum()) == 0.0
+    assert torch.equal(b.opt.master[:a.layout.n_used], a.bufs.params[:a.layout.n_used].float())
+
+
+def test_container_refuses_overwrite_symlink_and_wrong_size(tmp_path):
+    p = tmp_path / "x.bin"
+    write_container(p, b"head", [np.arange(4, dtype=np.int32)])
+    with pytest.raises(NativeRuntimeError, match="overwrite"):
+        write_container(p, b"head", [np.arange(4, dtype=np.int32)])
+    link = tmp_path / "link.bin"
+    link.symlink_to(tmp_path / "target.bin")
+    with pytest.raises(NativeRuntimeError):
+        write_container(link, b"head", [])
+    from neuralfn_b200.checkpoint import read_container
+    with pytest.raises(NativeRuntimeError, match="size"):
+        read_container(p, 4, [torch.empty(5, dtype=torch.int32)])
+    hdr, _ = read_container(p, 4, [torch.empty(4, dtype=torch.int32)])
+    assert hdr == b"head"
