@@ -1,0 +1,372 @@
+// Single-token (decode) attention over a bf16 KV cache, split along the context so that a
+// batch of a few dozen sequences still fills 148 SMs. The step is bound by reading K and V
+// once; everything else is fused around that read:
+//
+//   * prologue: per-head RMS norm of the new q and k (optional weights), rotary embedding
+//     at position len-1, query scaling - straight from the packed QKV row of the new token;
+//   * cache append: the new k/v row is written to its slot by exactly one CTA, while every
+//     CTA treats that row as a register-resident extra position, so no CTA waits on another;
+//   * hybrid cache: `cap` is either the full context (global layers) or the window size of
+//     a ring buffer (local layers): slot = position % cap, and once the ring is full every
+//     slot is live (softmax does not care about order);
+//   * grouped-query attention: one CTA serves up to four query heads of one KV head, so K
+//     and V rows are read once per group;
+//   * combine: partial (max, sum, output) per split go to a workspace; the last CTA to
+//     finish a (sequence, head group) - found with a self-resetting ticket - merges them
+//     and writes the bf16 output. One launch, no second kernel.
+//
+// Thread mapping: 128 threads = 16 sub-groups of 8 lanes; a sub-group owns one cache
+// position at a time, each lane two contiguous chunks of head_dim/16 elements (one in each
+// rotary half, so a rotation pair lives in one lane). Dot products reduce over 8 lanes.
+//
+// Behavioural counterpart in the reference: kernels.cu:2475-2880 (decode attention with
+// local ring / global caches and fused QK-norm + RoPE + append).
+#include <algorithm>
+#include <cfloat>
+
+#include "common.h"
+#include "nfn_kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace nfn {
+
+struct DecodeParams {
+  const __nv_bfloat16* qkv;
+  int ld;
+  __nv_bfloat16* kc;
+  __nv_bfloat16* vc;
+  long long batch_stride;  // elements between sequences in the cache
+  const int* lengths;
+  __nv_bfloat16* out;
+  int B, Hq, Hkv, cap, splits, gtiles;
+  const __nv_bfloat16* qw;
+  const __nv_bfloat16* kw;
+  int qk_norm;
+  float eps;
+  const float* cosT;
+  const float* sinT;
+  int max_pos;
+  float sign, scale;
+  int* tickets;
+  float* part_ml;
+  float* part_o;
+};
+
+template <int CH>
+__device__ __forceinline__ void load_chunk(const __nv_bfloat16* p, float* dst) {
+  if constexpr (CH == 8) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = unpack_bf16x2(w[i]);
+      dst[2 * i] = f.x;
+      dst[2 * i + 1] = f.y;
+    }
+  } else {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+    dst[0] = a.x; dst[1] = a.y; dst[2] = b.x; dst[3] = b.y;
+  }
+}
+template <int CH>
+__device__ __forceinline__ void store_chunk(__nv_bfloat16* p, const float* src) {
+  if constexpr (CH == 8) {
+    uint4 u;
+    u.x = pack_bf16x2(src[0], src[1]); u.y = pack_bf16x2(src[2], src[3]);
+    u.z = pack_bf16x2(src[4], src[5]); u.w = pack_bf16x2(src[6], src[7]);
+    *reinterpret_cast<uint4*>(p) = u;
+  } else {
+    uint2 u;
+    u.x = pack_bf16x2(src[0], src[1]); u.y = pack_bf16x2(src[2], src[3]);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+}
+__device__ __forceinline__ float sum8(float x) {
+  x += __shfl_xor_sync(0xffffffffu, x, 4);
+  x += __shfl_xor_sync(0xffffffffu, x, 2);
+  x += __shfl_xor_sync(0xffffffffu, x, 1);
+  return x;
+}
+
+// loads one head vector in the lane layout, applies norm (+weights), rotation and scale
+template <int HD>
+__device__ __forceinline__ void load_head(const __nv_bfloat16* src, const __nv_bfloat16* w, bool norm, float eps, const float* cosr,
+                                          const float* sinr, float sign, float scale, int sub, float* v /* HD/8 */) {
+  constexpr int CH = HD / 16, HALF = HD / 2;
+  load_chunk<CH>(src + sub * CH, v);
+  load_chunk<CH>(src + HALF + sub * CH, v + CH);
+  if (norm) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2 * CH; ++i) ss += v[i] * v[i];
+    ss = sum8(ss);
+    const float r = rsqrtf(ss / (float)HD + eps);
+    float wv[2 * CH];
+    if (w) {
+      load_chunk<CH>(w + sub * CH, wv);
+      load_chunk<CH>(w + HALF + sub * CH, wv + CH);
+    }
+#pragma unroll
+    for (int i = 0; i < 2 * CH; ++i) v[i] *= w ? r * wv[i] : r;
+  }
+  if (sign != 0.f) {
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const float c = cosr[sub * CH + i], s = sinr[sub * CH + i], lo = v[i], hi = v[CH + i];
+      v[i] = lo * c - sign * hi * s;
+      v[CH + i] = hi * c + sign * lo * s;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2 * CH; ++i) v[i] *= scale;
+}
+
+template <int HD, int G>
+__global__ void __launch_bounds__(128)
+decode_attention_kernel(const DecodeParams p) {
+  constexpr int CH = HD / 16, EPL = HD / 8, HALF = HD / 2, NGRP = 16;
+  extern __shared__ float smem[];  // [NGRP][G][HD] acc, then [NGRP][G][2] (m, l)
+  float* sm_acc = smem;
+  float* sm_ml = smem + NGRP * G * HD;
+  __shared__ int sh_last;
+
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int kvh = blockIdx.y / p.gtiles, gt = blockIdx.y % p.gtiles;
+  const int group = p.Hq / p.Hkv;          // query heads per kv head
+  const int g0 = gt * G;                   // first query head (within the group) of this CTA
+  const int gcount = min(G, group - g0);
+  const int grp = threadIdx.x >> 3, sub = threadIdx.x & 7;
+
+  const int len = p.lengths[b];
+  if (len <= 0) return;  // uniform per CTA: empty sequence slot, nothing to do and no ticket needed
+  const int pos = len - 1;
+  const int slot_new = pos % p.cap;
+  const int n_slots = min(len, p.cap);
+  const int tpos = min(pos, p.max_pos - 1);
+  const float* cosr = p.cosT ? p.cosT + (long long)tpos * HALF : nullptr;
+  const float* sinr = p.sinT ? p.sinT + (long long)tpos * HALF : nullptr;
+  const float sign = cosr ? p.sign : 0.f;
+
+  const __nv_bfloat16* row = p.qkv + (long long)b * p.ld;
+  float q[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    if (g < gcount)
+      load_head<HD>(row + (long long)(kvh * group + g0 + g) * HD, p.qw, p.qk_norm, p.eps, cosr, sinr, sign, p.scale, sub, q[g]);
+    else
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) q[g][i] = 0.f;
+  }
+
+  float m[G], l[G], acc[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -FLT_MAX;
+    l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) acc[g][i] = 0.f;
+  }
+
+  // Every lane of the warp calls this together (the reductions use full-warp shuffles);
+  // `valid` says whether this sub-group's position counts.
+  auto absorb = [&](const float* kv, const float* vv, bool valid) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float d = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) d += q[g][i] * kv[i];
+      d = sum8(d);
+      if (!valid) continue;
+      const float mn = fmaxf(m[g], d);
+      const float corr = __expf(m[g] - mn), w = __expf(d - mn);
+      l[g] = l[g] * corr + w;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) acc[g][i] = acc[g][i] * corr + w * vv[i];
+      m[g] = mn;
+    }
+  };
+
+  __nv_bfloat16* kbase = p.kc + (long long)b * p.batch_stride + (long long)kvh * p.cap * HD;
+  __nv_bfloat16* vbase = p.vc + (long long)b * p.batch_stride + (long long)kvh * p.cap * HD;
+
+  // the new token: from registers, by sub-group 0 of split 0; that sub-group of query tile 0
+  // also appends it to the cache
+  if (split == 0 && threadIdx.x < 32) {  // whole warp 0: its four sub-groups compute the same row
+    float kn[EPL], vn[EPL];
+    load_head<HD>(row + (long long)(p.Hq + kvh) * HD, p.kw, p.qk_norm, p.eps, cosr, sinr, sign, 1.f, sub, kn);
+    const __nv_bfloat16* vsrc = row + (long long)(p.Hq + p.Hkv + kvh) * HD;
+    load_chunk<CH>(vsrc + sub * CH, vn);
+    load_chunk<CH>(vsrc + HALF + sub * CH, vn + CH);
+    if (gt == 0 && grp == 0) {
+      store_chunk<CH>(kbase + (long long)slot_new * HD + sub * CH, kn);
+      store_chunk<CH>(kbase + (long long)slot_new * HD + HALF + sub * CH, kn + CH);
+      store_chunk<CH>(vbase + (long long)slot_new * HD + sub * CH, vn);
+      store_chunk<CH>(vbase + (long long)slot_new * HD + HALF + sub * CH, vn + CH);
+    }
+    // attend to the values the cache will hold (bf16-rounded), as later steps will see them
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      kn[i] = __bfloat162float(__float2bfloat16(kn[i]));
+      vn[i] = __bfloat162float(__float2bfloat16(vn[i]));
+    }
+    absorb(kn, vn, grp == 0);
+  }
+
+  const int per = (n_slots + p.splits - 1) / p.splits;
+  const int s_lo = split * per, s_hi = min(n_slots, s_lo + per);
+  for (int s0 = s_lo; s0 < s_hi; s0 += NGRP) {  // trip count is the same for every thread
+    const int s = s0 + grp;
+    const bool valid = s < s_hi && s != slot_new;
+    float kv[EPL], vv[EPL];
+    if (valid) {
+      const __nv_bfloat16* kr = kbase + (long long)s * HD;
+      const __nv_bfloat16* vr = vbase + (long long)s * HD;
+      load_chunk<CH>(kr + sub * CH, kv);
+      load_chunk<CH>(kr + HALF + sub * CH, kv + CH);
+      load_chunk<CH>(vr + sub * CH, vv);
+      load_chunk<CH>(vr + HALF + sub * CH, vv + CH);
+    } else {
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) kv[i] = vv[i] = 0.f;
+    }
+    absorb(kv, vv, valid);
+  }
+
+  // ---- merge the 16 sub-groups of this CTA -------------------------------------------------
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      sm_acc[(grp * G + g) * HD + sub * CH + i] = acc[g][i];
+      sm_acc[(grp * G + g) * HD + HALF + sub * CH + i] = acc[g][CH + i];
+    }
+    if (sub == 0) {
+      sm_ml[(grp * G + g) * 2] = m[g];
+      sm_ml[(grp * G + g) * 2 + 1] = l[g];
+    }
+  }
+  __syncthreads();
+  const long long unit = ((long long)b * p.Hkv + kvh) * p.gtiles + gt;
+  float* po = p.part_o + (unit * p.splits + split) * (long long)(G * HD);
+  float* pml = p.part_ml + (unit * p.splits + split) * (long long)(G * 2);
+  for (int e = threadIdx.x; e < G * HD; e += blockDim.x) {
+    const int g = e / HD, d = e % HD;
+    float mx = -FLT_MAX;
+#pragma unroll
+    for (int r = 0; r < NGRP; ++r) mx = fmaxf(mx, sm_ml[(r * G + g) * 2]);
+    float o = 0.f, ls = 0.f;
+#pragma unroll
+    for (int r = 0; r < NGRP; ++r) {
+      const float w = __expf(sm_ml[(r * G + g) * 2] - mx);
+      o += w * sm_acc[(r * G + g) * HD + d];
+      ls += w * sm_ml[(r * G + g) * 2 + 1];
+    }
+    po[e] = o;
+    if (d == 0) {
+      pml[g * 2] = mx;
+      pml[g * 2 + 1] = ls;
+    }
+  }
+
+  // ---- ticket: the last split to finish merges all splits -----------------------------------
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(&p.tickets[unit], 1);
+    sh_last = (t == p.splits - 1);
+    if (sh_last) p.tickets[unit] = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!sh_last) return;
+  __threadfence();
+  const float* ao = p.part_o + unit * p.splits * (long long)(G * HD);
+  const float* aml = p.part_ml + unit * p.splits * (long long)(G * 2);
+  for (int e = threadIdx.x; e < gcount * HD; e += blockDim.x) {
+    const int g = e / HD, d = e % HD;
+    float mx = -FLT_MAX;
+    for (int s = 0; s < p.splits; ++s) mx = fmaxf(mx, __ldcg(aml + (s * G + g) * 2));
+    float o = 0.f, ls = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+      const float w = __expf(__ldcg(aml + (s * G + g) * 2) - mx);
+      o += w * __ldcg(ao + (long long)(s * G + g) * HD + d);
+      ls += w * __ldcg(aml + (s * G + g) * 2 + 1);
+    }
+    p.out[(long long)b * p.Hq * HD + (long long)(kvh * group + g0 + g) * HD + d] = __float2bfloat16(ls > 0.f ? o / ls : 0.f);
+  }
+}
+
+template <int HD, int G>
+static int launch_decode(const DecodeParams& p, cudaStream_t st) {
+  const size_t smem = (size_t)16 * G * (HD + 2) * sizeof(float);
+  auto kern = decode_attention_kernel<HD, G>;
+  if (smem > 48 * 1024) {
+    static bool done = false;  // attribute is per function, set once per process and device-independent in effect
+    if (!done) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return fail(-2, "decode_attention: cannot raise the dynamic shared memory limit");
+      done = true;
+    }
+  }
+  dim3 grid(p.splits, p.Hkv * p.gtiles, p.B);
+  kern<<<grid, 128, smem, st>>>(p);
+  return launch_check("decode_attention", 1);
+}
+
+}  // namespace nfn
+
+using namespace nfn;
+
+extern "C" long long nfn_decode_attention_workspace_bytes(int B, int n_q_heads, int n_kv_heads, int head_dim, int max_splits) {
+  if (B <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || max_splits <= 0) return -1;
+  const int group = n_q_heads / n_kv_heads, G = group >= 4 ? 4 : (group >= 2 ? 2 : 1), gtiles = (group + G - 1) / G;
+  const long long units = (long long)B * n_kv_heads * gtiles;
+  return 256 + ((units * 4 + 255) / 256) * 256 + units * max_splits * (long long)G * (head_dim + 2) * 4;
+}
+
+extern "C" int nfn_decode_attention(const void* qkv, int ld, void* k_cache, void* v_cache, long long cache_batch_stride,
+                                    const int* lengths, void* out, int B, int n_q_heads, int n_kv_heads, int head_dim, int cap,
+                                    const void* q_norm_weight, const void* k_norm_weight, int qk_norm, float eps,
+                                    const float* cos_table, const float* sin_table, int max_pos, float rope_sign, float scale,
+                                    void* workspace, long long workspace_bytes, int splits, nfn_stream_t stream) {
+  if (B <= 0) return 0;
+  if (!qkv || !k_cache || !v_cache || !lengths || !out || !workspace) return fail(-1, "decode_attention: null operand");
+  if (head_dim != 64 && head_dim != 128) return fail(-1, "decode_attention: head_dim must be 64 or 128");
+  if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads) return fail(-1, "decode_attention: n_q_heads must be a multiple of n_kv_heads");
+  if (cap <= 0 || cache_batch_stride < (long long)n_kv_heads * cap * head_dim) return fail(-1, "decode_attention: cache stride smaller than heads * cap * head_dim");
+  if (ld < (n_q_heads + 2 * n_kv_heads) * head_dim || ld % 8) return fail(-1, "decode_attention: qkv row stride too small or not a multiple of 8");
+  if ((cos_table == nullptr) != (sin_table == nullptr) || (cos_table && max_pos <= 0)) return fail(-1, "decode_attention: cos/sin tables must come together");
+  if (cos_table && rope_sign != 1.f && rope_sign != -1.f) return fail(-1, "decode_attention: rope_sign must be +1 or -1");
+  const int group = n_q_heads / n_kv_heads, G = group >= 4 ? 4 : (group >= 2 ? 2 : 1), gtiles = (group + G - 1) / G;
+  const long long units = (long long)B * n_kv_heads * gtiles;
+  if (splits <= 0) {
+    // enough CTAs for ~2 waves, at least 256 cache positions per split
+    const long long want = (2LL * sm_count() + units - 1) / units;
+    splits = (int)std::max<long long>(1, std::min<long long>(want, (cap + 255) / 256));
+  }
+  splits = min(splits, 64);
+  const long long ticket_bytes = ((units * 4 + 255) / 256) * 256;
+  const long long need = ticket_bytes + units * splits * (long long)G * (head_dim + 2) * 4;
+  if (workspace_bytes < need) return fail(-1, "decode_attention: workspace too small (see nfn_decode_attention_workspace_bytes)");
+  if (reinterpret_cast<uintptr_t>(workspace) % 16) return fail(-1, "decode_attention: workspace must be 16-byte aligned");
+  DecodeParams p;
+  p.qkv = static_cast<const __nv_bfloat16*>(qkv);
+  p.ld = ld;
+  p.kc = static_cast<__nv_bfloat16*>(k_cache);
+  p.vc = static_cast<__nv_bfloat16*>(v_cache);
+  p.batch_stride = cache_batch_stride;
+  p.lengths = lengths;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.B = B; p.Hq = n_q_heads; p.Hkv = n_kv_heads; p.cap = cap; p.splits = splits; p.gtiles = gtiles;
+  p.qw = static_cast<const __nv_bfloat16*>(q_norm_weight);
+  p.kw = static_cast<const __nv_bfloat16*>(k_norm_weight);
+  p.qk_norm = qk_norm; p.eps = eps;
+  p.cosT = cos_table; p.sinT = sin_table; p.max_pos = max_pos; p.sign = rope_sign; p.scale = scale;
+  char* ws = static_cast<char*>(workspace);
+  p.tickets = reinterpret_cast<int*>(ws);
+  p.part_ml = reinterpret_cast<float*>(ws + ticket_bytes);
+  p.part_o = p.part_ml + units * splits * (long long)G * 2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (head_dim == 128) return G == 4 ? launch_decode<128, 4>(p, st) : (G == 2 ? launch_decode<128, 2>(p, st) : launch_decode<128, 1>(p, st));
+  return G == 4 ? launch_decode<64, 4>(p, st) : (G == 2 ? launch_decode<64, 2>(p, st) : launch_decode<64, 1>(p, st));
+}

@@ -64,6 +64,89 @@ typedef struct {
 
 int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream);
 
+// ---- GEMMs fused with their collective (gemm_tp.cu) ----------------------------------------
+// K-major bf16 operands: A [M, K], B [N, K] (out x in), C = A . B^T. Buffers named "peer"
+// are the same allocation on every rank (symmetric memory), indexed by rank.
+//   NFN_TP_AG_A: `a` is the local gathered buffer [M, K] (lda == K); this rank's rows
+//                [rank * rows_per_rank, +rows_per_rank) are already in it, the other rows are
+//                pulled from peer_bufs[r] inside the kernel. C [M, N] = bias/activation epilogue.
+//   NFN_TP_AG_B: the same with the gathered operand on the B side (`b` [N, K], ldb == K).
+//   NFN_TP_RS:   C is not written; partial tiles go to peer_bufs[owner] (bf16 slots
+//                [world, rows_per_rank, N]); the kernel then reduces this rank's slots into
+//                `out` [rows_per_rank, N] (+ bias + resid).
+// ctrl_*: per-rank control block of ctrl_ints int32 (zero-initialised once): [0, 8) flags
+// written by peers, [16] ticket, [32, 32 + blocks) block flags. epoch must grow by one per
+// call on every rank alike; the value used is epoch + *epoch_dev (epoch_dev may be NULL).
+enum { NFN_TP_AG_A = 0, NFN_TP_AG_B = 1, NFN_TP_RS = 2 };
+typedef struct {
+  int mode;
+  const void* a; const void* b; void* c;
+  int m, n, k;
+  int lda, ldb, ldc;
+  int flags; float act_param; const void* bias;   // NFN_EPI_BIAS and activation bits
+  int rank, world, rows_per_rank;
+  int epoch; const int* epoch_dev;
+  const void* peer_bufs[8];
+  int* ctrl_local; int* ctrl_peer[8]; int ctrl_ints;
+  void* out; int ld_out; const void* resid; int ld_resid;   // NFN_TP_RS only
+  int n_copy;                                               // gather CTAs (0 = default 16)
+} nfn_gemm_tp_args;
+int nfn_gemm_tp(const nfn_gemm_tp_args* args, nfn_stream_t stream);
+
+// ---- rotary embedding (rope.cu) -----------------------------------------------------------------
+// In place on the q and k heads of packed rows (q | k | v). sign = +1: "hf" convention,
+// -1: "legacy"; the backward pass is the same call with the opposite sign. Tables are fp32
+// [max_pos, rot_dim/2]; positions (optional int32 per row) default to row % T.
+int nfn_rope_inplace(void* qkv, int ld, long long tokens, int T, int n_q_heads, int n_kv_heads, int head_dim,
+                     int rot_dim, const float* cos_table, const float* sin_table, const int* positions,
+                     int max_pos, float sign, float q_scale, nfn_stream_t stream);
+// Per-head RMS norm (optional bf16 weights [head_dim]) + rotation + query scale in one pass.
+int nfn_qk_norm_rope_forward(void* qkv, int ld, long long tokens, int T, int n_q_heads, int n_kv_heads, int head_dim,
+                             const void* q_weight, const void* k_weight, const float* cos_table,
+                             const float* sin_table, const int* positions, int max_pos, float sign, float eps,
+                             float q_scale, float* rstd_out, nfn_stream_t stream);
+
+// ---- token selection (sampling.cu) --------------------------------------------------------------
+// logits: bf16 (is_fp32 = 0) or fp32 rows of V entries, row stride ld. Ties go to the lowest
+// index. index_offset is added to every result (vocabulary shard offset under tensor
+// parallelism). argmax workspace: rows * 8 bytes at least, rows * 512 for full parallelism.
+int nfn_argmax_rows(const void* logits, int is_fp32, long long ld, int rows, int V, int* out_idx, float* out_val,
+                    void* workspace, long long workspace_bytes, int index_offset, nfn_stream_t stream);
+// Merges per-rank winners laid out [world, rows] (values and already-offset indices).
+int nfn_argmax_merge(const float* vals, const int* idx, int world, int rows, int* out_idx, float* out_val,
+                     nfn_stream_t stream);
+// temperature <= 0 or top_k == 1: greedy. top_k = 0 and top_p in {0, 1}: no truncation.
+// row_params (optional, fp32 [rows, 3] = temperature, top_k, top_p) overrides the scalars per
+// row. Randomness: Philox4x32-10 keyed by seed, counter (element/4, row, offset + *offset_dev).
+int nfn_sample_rows(const void* logits, int is_fp32, long long ld, int rows, int V, int* out_idx, float* out_logprob,
+                    float temperature, int top_k, float top_p, const float* row_params, unsigned long long seed,
+                    unsigned long long offset, const unsigned long long* offset_dev, int index_offset,
+                    nfn_stream_t stream);
+
+// ---- decode attention (decode_attention.cu) -----------------------------------------------------
+// One new token per sequence. qkv: bf16 [B, ld] packed (q | k | v) rows of the new token;
+// caches: bf16 [B, n_kv_heads, cap, head_dim] with cache_batch_stride elements between
+// sequences; lengths[b] counts the new token; out: bf16 [B, n_q_heads * head_dim]. The call
+// appends the (normed, rotated) k and v of the new token at slot (len - 1) % cap. The
+// workspace must be zero-filled once before its first use and is left ready for the next call.
+long long nfn_decode_attention_workspace_bytes(int B, int n_q_heads, int n_kv_heads, int head_dim, int max_splits);
+int nfn_decode_attention(const void* qkv, int ld, void* k_cache, void* v_cache, long long cache_batch_stride,
+                         const int* lengths, void* out, int B, int n_q_heads, int n_kv_heads, int head_dim, int cap,
+                         const void* q_norm_weight, const void* k_norm_weight, int qk_norm, float eps,
+                         const float* cos_table, const float* sin_table, int max_pos, float rope_sign, float scale,
+                         void* workspace, long long workspace_bytes, int splits, nfn_stream_t stream);
+
+// ---- quantised weights (quant.cu) ---------------------------------------------------------------
+enum { NFN_QTYPE_Q4_K = 12, NFN_QTYPE_Q5_K = 13, NFN_QTYPE_Q6_K = 14 };  // GGUF type ids
+int nfn_quant_block_bytes(int qtype);
+int nfn_dequant_kquant(int qtype, const void* blocks, long long n_blocks, void* out_bf16, nfn_stream_t stream);
+int nfn_dequant_nf4(const void* codes, const float* absmax, long long n_weights, int group, void* out_bf16,
+                    nfn_stream_t stream);
+// y[b, n] = W1[n, :] . x[b, :]  (silu(W1 x) * (W2 x) when w2 != NULL) + bias[n] + resid[b, n];
+// W rows are K/256 consecutive super-blocks; B <= 8.
+int nfn_kquant_gemv(int qtype, const void* w1, const void* w2, const void* x, int ldx, void* y, int ldy,
+                    const void* bias, const void* resid, int ld_resid, int B, int N, int K, nfn_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

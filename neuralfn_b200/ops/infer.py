@@ -1,0 +1,166 @@
+"""Python front-ends of the inference-side kernels: rotary embedding, fused QK-norm + RoPE,
+argmax / sampling, split-KV decode attention, K-quant / NF4 dequantisation and the
+quantised skinny product. Same conventions as ``ops.kernels``: CUDA tensors in, current
+stream, no synchronisation.
+"""
+from __future__ import annotations
+
+import math
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+
+import torch
+
+from . import _lib
+
+_bf16 = torch.bfloat16
+
+__all__ = ["rope_tables", "rope_inplace", "qk_norm_rope_forward", "argmax_rows", "argmax_merge", "sample_rows",
+           "DecodeAttentionWorkspace", "decode_attention", "dequant_kquant", "dequant_nf4", "kquant_gemv", "quant_block_bytes"]
+
+
+def _p(t) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _st() -> c_void_p:
+    return c_void_p(_lib.stream_ptr())
+
+
+def rope_tables(max_pos: int, rot_dim: int, base: float = 10000.0, *, inv_freq: torch.Tensor | None = None,
+                device=None) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 cos/sin tables [max_pos, rot_dim/2]; pass ``inv_freq`` for scaled variants."""
+    if inv_freq is None:
+        inv_freq = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.float64) / rot_dim))
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float64), inv_freq.double().cpu())
+    return ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous()
+
+
+def _sign(convention) -> float:
+    if convention in ("hf", 1, 1.0):
+        return 1.0
+    if convention in ("legacy", -1, -1.0):
+        return -1.0
+    raise ValueError("rotary convention must be 'legacy' or 'hf'")
+
+
+def rope_inplace(qkv, *, T: int, n_q_heads: int, n_kv_heads: int, head_dim: int, cos, sin, convention="legacy",
+                 rot_dim: int | None = None, positions=None, q_scale: float = 1.0, backward: bool = False) -> None:
+    """Rotates the q and k heads of packed bf16 rows in place. ``backward=True`` applies the
+    inverse rotation (the gradient of the forward call; q_scale is applied again)."""
+    assert qkv.dtype == _bf16 and qkv.dim() == 2 and qkv.stride(1) == 1
+    rot_dim = head_dim if rot_dim is None else rot_dim
+    sign = _sign(convention) * (-1.0 if backward else 1.0)
+    rc = _lib.load().nfn_rope_inplace(_p(qkv), c_int(qkv.stride(0)), c_longlong(qkv.shape[0]), c_int(T), c_int(n_q_heads),
+                                      c_int(n_kv_heads), c_int(head_dim), c_int(rot_dim), _p(cos), _p(sin), _p(positions),
+                                      c_int(cos.shape[0]), c_float(sign), c_float(q_scale), _st())
+    _lib.check(rc, "nfn_rope_inplace")
+
+
+def qk_norm_rope_forward(qkv, *, T: int, n_q_heads: int, n_kv_heads: int, head_dim: int, cos, sin, convention="legacy",
+                         q_weight=None, k_weight=None, positions=None, eps: float = 1e-6, q_scale: float = 1.0, rstd=None):
+    rc = _lib.load().nfn_qk_norm_rope_forward(_p(qkv), c_int(qkv.stride(0)), c_longlong(qkv.shape[0]), c_int(T), c_int(n_q_heads),
+                                              c_int(n_kv_heads), c_int(head_dim), _p(q_weight), _p(k_weight), _p(cos), _p(sin),
+                                              _p(positions), c_int(cos.shape[0]), c_float(_sign(convention)), c_float(eps),
+                                              c_float(q_scale), _p(rstd), _st())
+    _lib.check(rc, "nfn_qk_norm_rope_forward")
+    return rstd
+
+
+def argmax_rows(logits, *, index_offset: int = 0, workspace=None, return_values: bool = False):
+    assert logits.dim() == 2 and logits.stride(1) == 1 and logits.dtype in (_bf16, torch.float32)
+    rows, V = logits.shape
+    idx = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    val = torch.empty(rows, dtype=torch.float32, device=logits.device) if return_values else None
+    if workspace is None:
+        workspace = torch.empty(rows * 64 * 8, dtype=torch.uint8, device=logits.device)
+    rc = _lib.load().nfn_argmax_rows(_p(logits), c_int(logits.dtype == torch.float32), c_longlong(logits.stride(0)), c_int(rows),
+                                     c_int(V), _p(idx), _p(val), _p(workspace), c_longlong(workspace.numel()), c_int(index_offset), _st())
+    _lib.check(rc, "nfn_argmax_rows")
+    return (idx, val) if return_values else idx
+
+
+def argmax_merge(vals, idx):
+    world, rows = vals.shape
+    out = torch.empty(rows, dtype=torch.int32, device=vals.device)
+    rc = _lib.load().nfn_argmax_merge(_p(vals), _p(idx), c_int(world), c_int(rows), _p(out), _p(None), _st())
+    _lib.check(rc, "nfn_argmax_merge")
+    return out
+
+
+def sample_rows(logits, *, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0, offset: int = 0,
+                offset_dev=None, row_params=None, index_offset: int = 0, return_logprob: bool = False):
+    assert logits.dim() == 2 and logits.stride(1) == 1 and logits.dtype in (_bf16, torch.float32)
+    rows, V = logits.shape
+    idx = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    lp = torch.empty(rows, dtype=torch.float32, device=logits.device) if return_logprob else None
+    rc = _lib.load().nfn_sample_rows(_p(logits), c_int(logits.dtype == torch.float32), c_longlong(logits.stride(0)), c_int(rows),
+                                     c_int(V), _p(idx), _p(lp), c_float(temperature), c_int(top_k), c_float(top_p), _p(row_params),
+                                     c_ulonglong(seed), c_ulonglong(offset), _p(offset_dev), c_int(index_offset), _st())
+    _lib.check(rc, "nfn_sample_rows")
+    return (idx, lp) if return_logprob else idx
+
+
+class DecodeAttentionWorkspace:
+    """Zero-initialised scratch for ``decode_attention`` (tickets + per-split partials)."""
+
+    def __init__(self, B: int, n_q_heads: int, n_kv_heads: int, head_dim: int, device, max_splits: int = 64) -> None:
+        n = _lib.load().nfn_decode_attention_workspace_bytes
+        n.restype = c_longlong
+        nbytes = n(c_int(B), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(max_splits))
+        if nbytes <= 0:
+            raise ValueError("bad decode attention geometry")
+        self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+
+
+def decode_attention(qkv, k_cache, v_cache, lengths, *, n_q_heads: int, n_kv_heads: int, head_dim: int, workspace: DecodeAttentionWorkspace,
+                     cos=None, sin=None, convention="hf", qk_norm: bool = False, q_norm_weight=None, k_norm_weight=None,
+                     eps: float = 1e-6, scale: float | None = None, splits: int = 0, out=None):
+    """qkv bf16 [B, >= (Hq+2Hkv)*D]; caches bf16 [B, Hkv, cap, D]; lengths int32 [B] (counting
+    the new token). Appends the new k/v and returns bf16 [B, Hq*D]."""
+    B = qkv.shape[0]
+    assert k_cache.dtype == _bf16 and k_cache.dim() == 4 and k_cache.shape == v_cache.shape and k_cache[0].is_contiguous()
+    assert k_cache.stride(0) == v_cache.stride(0) and lengths.dtype == torch.int32
+    cap = k_cache.shape[2]
+    out = torch.empty(B, n_q_heads * head_dim, dtype=_bf16, device=qkv.device) if out is None else out
+    scale = head_dim ** -0.5 if scale is None else scale
+    rc = _lib.load().nfn_decode_attention(
+        _p(qkv), c_int(qkv.stride(0)), _p(k_cache), _p(v_cache), c_longlong(k_cache.stride(0)), _p(lengths), _p(out), c_int(B),
+        c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(cap), _p(q_norm_weight), _p(k_norm_weight), c_int(int(qk_norm)),
+        c_float(eps), _p(cos), _p(sin), c_int(0 if cos is None else cos.shape[0]), c_float(_sign(convention) if cos is not None else 0.0),
+        c_float(scale), _p(workspace.buf), c_longlong(workspace.buf.numel()), c_int(splits), _st())
+    _lib.check(rc, "nfn_decode_attention")
+    return out
+
+
+def quant_block_bytes(qtype: int) -> int:
+    return int(_lib.load().nfn_quant_block_bytes(c_int(qtype)))
+
+
+def dequant_kquant(qtype: int, blocks: torch.Tensor, out=None) -> torch.Tensor:
+    """blocks: uint8 tensor holding whole super-blocks -> bf16 [n_blocks * 256]."""
+    assert blocks.dtype == torch.uint8 and blocks.is_contiguous()
+    nb = blocks.numel() // quant_block_bytes(qtype)
+    out = torch.empty(nb * 256, dtype=_bf16, device=blocks.device) if out is None else out
+    _lib.check(_lib.load().nfn_dequant_kquant(c_int(qtype), _p(blocks), c_longlong(nb), _p(out), _st()), "nfn_dequant_kquant")
+    return out
+
+
+def dequant_nf4(codes: torch.Tensor, absmax: torch.Tensor, group: int = 64, out=None) -> torch.Tensor:
+    n = codes.numel() * 2
+    out = torch.empty(n, dtype=_bf16, device=codes.device) if out is None else out
+    _lib.check(_lib.load().nfn_dequant_nf4(_p(codes), _p(absmax), c_longlong(n), c_int(group), _p(out), _st()), "nfn_dequant_nf4")
+    return out
+
+
+def kquant_gemv(qtype: int, w: torch.Tensor, x: torch.Tensor, N: int, *, w_gate_pair: torch.Tensor | None = None, bias=None,
+                resid=None, out=None) -> torch.Tensor:
+    """y[b, n] = W[n] . x[b] for quantised W (uint8 [N * K/256 * block_bytes]); with
+    ``w_gate_pair`` the result is silu(W x) * (W_pair x). x: bf16 [B <= 8, K]."""
+    assert x.dtype == _bf16 and x.dim() == 2 and x.stride(1) == 1
+    B, K = x.shape
+    assert w.numel() == N * (K // 256) * quant_block_bytes(qtype), "weight size does not match N x K"
+    out = torch.empty(B, N, dtype=_bf16, device=x.device) if out is None else out
+    rc = _lib.load().nfn_kquant_gemv(c_int(qtype), _p(w), _p(w_gate_pair), _p(x), c_int(x.stride(0)), _p(out), c_int(out.stride(0)),
+                                     _p(bias), _p(resid), c_int(0 if resid is None else resid.stride(0)), c_int(B), c_int(N), c_int(K), _st())
+    _lib.check(rc, "nfn_kquant_gemv")
+    return out

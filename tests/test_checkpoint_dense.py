@@ -22,6 +22,7 @@ def _cpu_trainer(seed=3):
     master = torch.empty(layout.n_total)
     init_gpt2_params_(cfg, layout, master, seed)
     opt = ShardedAdamW(layout, bufs, AdamWConfig(), master_init=master)
+    bufs.params.copy_(master.bfloat16())
     opt.m.normal_(generator=torch.Generator().manual_seed(seed))
     opt.v.uniform_(generator=torch.Generator().manual_seed(seed + 1))
     opt.step_count = 7

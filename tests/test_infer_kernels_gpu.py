@@ -1,0 +1,212 @@
+"""Inference-side kernels against fp32 PyTorch / numpy references."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _rope_ref(x, cos, sin, sign):
+    half = x.shape[-1] // 2
+    x1, x2 = x[..., :half], x[..., half:]
+    return torch.cat((x1 * cos - sign * x2 * sin, x2 * cos + sign * x1 * sin), dim=-1)
+
+
+@pytest.mark.parametrize("hd,convention", [(64, "legacy"), (128, "hf")])
+def test_rope_inplace_forward_and_inverse(hd, convention):
+    from neuralfn_b200.ops import infer
+    torch.manual_seed(0)
+    B, T, Hq, Hkv = 2, 37, 4, 2
+    qkv = torch.randn(B * T, (Hq + 2 * Hkv) * hd, device=_dev()).bfloat16()
+    orig = qkv.clone()
+    cos, sin = infer.rope_tables(64, hd, 10000.0, device=_dev())
+    infer.rope_inplace(qkv, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=cos, sin=sin, convention=convention, q_scale=0.5)
+    sign = 1.0 if convention == "hf" else -1.0
+    x = orig.float().view(B, T, Hq + 2 * Hkv, hd)
+    c, s = cos[:T, None, :], sin[:T, None, :]
+    ref = x.clone()
+    ref[:, :, :Hq + Hkv] = _rope_ref(x[:, :, :Hq + Hkv], c, s, sign)
+    ref[:, :, :Hq] *= 0.5
+    torch.testing.assert_close(qkv.float().view(B, T, -1, hd), ref, atol=2e-2, rtol=2e-2)
+    assert torch.equal(qkv.view(B, T, -1, hd)[:, :, Hq + Hkv:], orig.view(B, T, -1, hd)[:, :, Hq + Hkv:])  # v untouched
+    infer.rope_inplace(qkv, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=cos, sin=sin, convention=convention,
+                       q_scale=2.0, backward=True)
+    torch.testing.assert_close(qkv.float(), orig.float(), atol=3e-2, rtol=3e-2)
+
+
+def test_qk_norm_rope_fused_matches_composition():
+    from neuralfn_b200.ops import infer
+    torch.manual_seed(1)
+    T, Hq, Hkv, hd = 19, 4, 1, 128
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * hd, device=_dev()).bfloat16()
+    qw = (1 + 0.1 * torch.randn(hd, device=_dev())).bfloat16()
+    kw = (1 + 0.1 * torch.randn(hd, device=_dev())).bfloat16()
+    pos = torch.randint(0, 500, (T,), device=_dev(), dtype=torch.int32)
+    cos, sin = infer.rope_tables(512, hd, 500000.0, device=_dev())
+    x = qkv.float().view(T, -1, hd)
+    got = qkv.clone()
+    rstd = torch.empty(T * (Hq + Hkv), device=_dev())
+    infer.qk_norm_rope_forward(got, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=cos, sin=sin, convention="hf",
+                               q_weight=qw, k_weight=kw, positions=pos, eps=1e-6, q_scale=hd ** -0.5, rstd=rstd)
+    r = torch.rsqrt(x[:, :Hq + Hkv].pow(2).mean(-1, keepdim=True) + 1e-6)
+    w = torch.cat([qw.float().expand(Hq, hd), kw.float().expand(Hkv, hd)])[None]
+    ref = _rope_ref(x[:, :Hq + Hkv] * r * w, cos[pos.long()][:, None], sin[pos.long()][:, None], 1.0)
+    ref[:, :Hq] *= hd ** -0.5
+    torch.testing.assert_close(got.float().view(T, -1, hd)[:, :Hq + Hkv], ref, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(rstd.view(T, -1), r.squeeze(-1), atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_argmax_rows_ties_and_offsets(dtype):
+    from neuralfn_b200.ops import infer
+    torch.manual_seed(2)
+    logits = torch.randn(32, 50304, device=_dev()).to(dtype)
+    logits[3, 100] = logits[3, 40000] = 50.0  # tie -> lowest index
+    logits[5, 7] = float("nan")
+    idx, val = infer.argmax_rows(logits, index_offset=1000, return_values=True)
+    ref = torch.where(torch.isnan(logits), torch.full_like(logits, -1e30), logits).float().argmax(-1)
+    ref[3] = 100
+    assert torch.equal(idx.long() - 1000, ref)
+    assert float(val[3]) == 50.0
+    one = infer.argmax_rows(logits[:1, :1000].contiguous())
+    assert int(one[0]) == int(logits[0, :1000].float().argmax())
+
+
+def test_sampling_truncation_and_distribution():
+    from neuralfn_b200.ops import infer
+    torch.manual_seed(3)
+    V, rows = 1000, 2048
+    base = torch.randn(V, device=_dev()) * 2.0
+    logits = base.expand(rows, V).contiguous()
+    # greedy
+    assert torch.equal(infer.sample_rows(logits, temperature=0.0).long(), base.argmax().expand(rows))
+    # top-k: only the k best may appear, frequencies follow the renormalised softmax
+    k = 5
+    top = base.topk(k)
+    got = infer.sample_rows(logits, temperature=1.0, top_k=k, seed=11)
+    assert set(got.tolist()) <= set(top.indices.tolist())
+    p = torch.softmax(top.values, 0)
+    freq = torch.stack([(got == i).float().mean() for i in top.indices])
+    assert float((freq - p).abs().max()) < 0.05
+    # top-p: the smallest prefix of the sorted distribution reaching p
+    rounded = base.bfloat16().float()
+    probs = torch.softmax(rounded / 0.8, 0)
+    srt = probs.sort(descending=True)
+    n_keep = int((srt.values.cumsum(0) < 0.6).sum()) + 1
+    got = infer.sample_rows(rounded.expand(rows, V).contiguous(), temperature=0.8, top_p=0.6, seed=5)
+    # everything tied with the last kept value (and the next distinct value, for a
+    # cumulative sum that lands on the boundary) may appear
+    floor = srt.values[min(n_keep, V - 1)]
+    allowed = set(torch.nonzero(probs >= floor).flatten().tolist())
+    assert set(got.tolist()) <= allowed and len(set(got.tolist())) >= max(1, n_keep - 1)
+    # different offsets give different draws, same offset repeats
+    a = infer.sample_rows(logits, temperature=1.0, seed=1, offset=0)
+    b = infer.sample_rows(logits, temperature=1.0, seed=1, offset=0)
+    c = infer.sample_rows(logits, temperature=1.0, seed=1, offset=1)
+    assert torch.equal(a, b) and not torch.equal(a, c)
+    # untruncated sampling: chi-square-ish check on the 10 most likely tokens
+    full = infer.sample_rows(logits, temperature=1.0, seed=99, return_logprob=True)
+    pf = torch.softmax(base, 0)
+    for i in pf.topk(10).indices.tolist():
+        assert abs(float((full[0] == i).float().mean()) - float(pf[i])) < 0.03
+    lp_ref = torch.log_softmax(base, 0)[full[0].long()]
+    torch.testing.assert_close(full[1], lp_ref, atol=2e-3, rtol=2e-3)
+
+
+def _decode_ref(q, kc, vc, lengths, cap, scale):
+    B, Hq, hd = q.shape
+    Hkv = kc.shape[1]
+    out = torch.zeros(B, Hq, hd, device=q.device)
+    for b in range(B):
+        n = min(int(lengths[b]), cap)
+        for h in range(Hq):
+            kv = h // (Hq // Hkv)
+            s = (kc[b, kv, :n].float() @ q[b, h]) * scale
+            out[b, h] = torch.softmax(s, 0) @ vc[b, kv, :n].float()
+    return out
+
+
+@pytest.mark.parametrize("hd,Hq,Hkv,cap,ring", [(128, 4, 1, 700, False), (64, 6, 2, 128, True), (128, 8, 8, 300, False)])
+def test_decode_attention_append_and_attend(hd, Hq, Hkv, cap, ring):
+    from neuralfn_b200.ops import infer
+    torch.manual_seed(4)
+    B = 5
+    dev = _dev()
+    if ring:
+        lengths = torch.tensor([1, 90, 128, 129, 700], dtype=torch.int32, device=dev)
+    else:
+        lengths = torch.tensor([1, 2, 257, cap, 100], dtype=torch.int32, device=dev)
+    kc = torch.randn(B, Hkv, cap, hd, device=dev).bfloat16()
+    vc = torch.randn(B, Hkv, cap, hd, device=dev).bfloat16()
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * hd, device=dev).bfloat16()
+    qw = (1 + 0.1 * torch.randn(hd, device=dev)).bfloat16()
+    kw = (1 + 0.1 * torch.randn(hd, device=dev)).bfloat16()
+    cos, sin = infer.rope_tables(1024, hd, 10000.0, device=dev)
+    ws = infer.DecodeAttentionWorkspace(B, Hq, Hkv, hd, dev)
+    # reference: normalise + rotate the new q/k, write k/v into the slot, full softmax
+    x = qkv.float().view(B, Hq + 2 * Hkv, hd)
+    pos = (lengths - 1).long()
+    r = torch.rsqrt(x[:, :Hq + Hkv].pow(2).mean(-1, keepdim=True) + 1e-6)
+    w = torch.cat([qw.float().expand(Hq, hd), kw.float().expand(Hkv, hd)])[None]
+    qk = _rope_ref(x[:, :Hq + Hkv] * r * w, cos[pos][:, None], sin[pos][:, None], 1.0)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    for b in range(B):
+        slot = int(pos[b]) % cap
+        kc_ref[b, :, slot] = qk[b, Hq:].bfloat16()
+        vc_ref[b, :, slot] = x[b, Hq + Hkv:].bfloat16()
+    ref = _decode_ref(qk[:, :Hq], kc_ref, vc_ref, lengths, cap, hd ** -0.5)
+    for splits in (0, 3):
+        k2, v2 = kc.clone(), vc.clone()
+        out = infer.decode_attention(qkv, k2, v2, lengths, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, workspace=ws, cos=cos, sin=sin,
+                                     convention="hf", qk_norm=True, q_norm_weight=qw, k_norm_weight=kw, splits=splits)
+        torch.testing.assert_close(out.float().view(B, Hq, hd), ref, atol=2e-2, rtol=2e-2)
+        torch.testing.assert_close(k2.float(), kc_ref.float(), atol=2e-2, rtol=2e-2)
+        assert torch.equal(v2, vc_ref)
+    assert int(ws.buf[:256].sum()) == 0  # tickets are back to zero
+
+
+@pytest.mark.parametrize("name", ["Q4_K", "Q5_K", "Q6_K"])
+def test_kquant_dequant_matches_numpy_oracle(name):
+    from neuralfn_b200.ops import infer
+    from neuralfn_b200.quant import kquant
+    t = kquant.GGML_TYPE[name]
+    raw = kquant.random_blocks(t, 300, seed=7)
+    ref = torch.from_numpy(kquant.dequantize(t, raw.tobytes()))
+    got = infer.dequant_kquant(t, torch.from_numpy(raw).to(_dev()).reshape(-1))
+    torch.testing.assert_close(got.float().cpu(), ref, atol=2e-2, rtol=1e-2)
+
+
+def test_nf4_dequant():
+    from neuralfn_b200.ops import infer
+    from neuralfn_b200.quant import kquant
+    w = np.random.default_rng(0).normal(size=64 * 50).astype(np.float32)
+    codes, absmax = kquant.nf4_encode(w)
+    got = infer.dequant_nf4(torch.from_numpy(codes).to(_dev()), torch.from_numpy(absmax).to(_dev()))
+    torch.testing.assert_close(got.float().cpu(), torch.from_numpy(kquant.nf4_decode(codes, absmax)), atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("name,B,N,K,gated", [("Q4_K", 1, 96, 512, False), ("Q4_K", 8, 70, 4096 + 256, True),
+                                                ("Q6_K", 3, 33, 768, False), ("Q5_K", 2, 64, 256, True)])
+def test_kquant_gemv(name, B, N, K, gated):
+    from neuralfn_b200.ops import infer
+    from neuralfn_b200.quant import kquant
+    t = kquant.GGML_TYPE[name]
+    dev = _dev()
+    nb = N * K // 256
+    raw1, raw2 = kquant.random_blocks(t, nb, seed=1), kquant.random_blocks(t, nb, seed=2)
+    w1 = torch.from_numpy(kquant.dequantize(t, raw1.tobytes())).view(N, K).to(dev)
+    w2 = torch.from_numpy(kquant.dequantize(t, raw2.tobytes())).view(N, K).to(dev)
+    x = (torch.randn(B, K, device=dev) * 0.5).bfloat16()
+    bias = torch.randn(N, device=dev).bfloat16()
+    resid = torch.randn(B, N, device=dev).bfloat16()
+    a = x.float() @ w1.T
+    ref = (torch.nn.functional.silu(a) * (x.float() @ w2.T) if gated else a) + bias.float() + resid.float()
+    got = infer.kquant_gemv(t, torch.from_numpy(raw1).to(dev).reshape(-1), x, N,
+                            w_gate_pair=torch.from_numpy(raw2).to(dev).reshape(-1) if gated else None, bias=bias, resid=resid)
+    torch.testing.assert_close(got.float(), ref, atol=0.05 * float(ref.abs().max()), rtol=2e-2)
