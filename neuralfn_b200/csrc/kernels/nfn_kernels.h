@@ -93,6 +93,18 @@ typedef struct {
 } nfn_gemm_tp_args;
 int nfn_gemm_tp(const nfn_gemm_tp_args* args, nfn_stream_t stream);
 
+// ---- one-shot all-reduce + residual + RMS norm (allreduce_fused.cu) ---------------------------
+// peer_bufs[r]: rank r's copy of the symmetric bf16 [rows, ld] partial-result buffer;
+// multicast_buf: multicast address of that buffer (NVSwitch reduction) or NULL for peer loads.
+// resid (optional) is updated in place with sum + bias + resid; out receives the RMS-normed
+// row (norm_weight != NULL) or the reduced row itself. ctrl blocks: >= 32 int32, zeroed once.
+int nfn_allreduce_resid_norm(const void* const* peer_bufs, const void* multicast_buf, int* ctrl_local, int* const* ctrl_peer,
+                             int rank, int world, int epoch, const int* epoch_dev, int rows, int n, int ld,
+                             const void* bias, void* resid, int ld_resid, const void* norm_weight, float eps,
+                             int centered, void* out, int ld_out, nfn_stream_t stream);
+// Stream-ordered wait until every peer finished reading this rank's buffer in call `epoch`.
+int nfn_allreduce_wait_readers(const int* ctrl_local, int world, int epoch, const int* epoch_dev, nfn_stream_t stream);
+
 // ---- rotary embedding (rope.cu) -----------------------------------------------------------------
 // In place on the q and k heads of packed rows (q | k | v). sign = +1: "hf" convention,
 // -1: "legacy"; the backward pass is the same call with the opposite sign. Tables are fp32

@@ -223,6 +223,47 @@ class TensorParallelContext:
         self._launch(RS, x, weight, None, M, N, K, rows, sym.ptrs, bias=bias, out=out, resid=resid)
         return out
 
+    # ------------------------------------------- decode: all-reduce + residual + RMS norm --
+    def partial_buffer(self, rows: int, n: int) -> tuple[torch.Tensor, "_Symmetric"]:
+        """Symmetric [rows, n] bf16 buffer for a rank's partial projection output (two
+        alternate). Write the partial into it, then call ``allreduce_resid_norm``."""
+        sym = self._buffer("ar", rows * n)
+        return sym.t.view(rows, n), sym
+
+    def allreduce_resid_norm(self, partial: torch.Tensor, sym: "_Symmetric | None", *, bias=None, resid=None, norm_weight=None,
+                             eps: float = 1e-6, centered: bool = False, use_multicast: bool = True):
+        """sum over ranks of ``partial`` (+ bias + resid, resid updated in place), then RMS
+        norm with ``norm_weight`` when given. Returns the bf16 [rows, n] result."""
+        rows, n = partial.shape
+        if self.impl != "fused":
+            y = partial.float().clone()
+            if self.world > 1:
+                dist.all_reduce(y, group=self.group)
+            y = y + bias.float() if bias is not None else y
+            if resid is not None:
+                y = y + resid.float()
+                resid.copy_(y.to(resid.dtype))
+                y = resid.float()
+            if norm_weight is not None:
+                w = norm_weight.float()
+                y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * (1 + w if centered else w)
+            return y.to(partial.dtype)
+        assert sym is not None and partial.data_ptr() == sym.t.data_ptr(), "partial must be the symmetric partial_buffer"
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=self.device)
+        ptr_arr = (c_void_p * 8)(*sym.ptrs)
+        ctrl_arr = (c_void_p * 8)(*[p + 4 * 1024 for p in self.ctrl.ptrs])  # second half of the control block
+        mc = 0
+        if use_multicast and sym.handle is not None:
+            mc = int(getattr(sym.handle, "multicast_ptr", 0) or 0)
+        rc = _lib.load().nfn_allreduce_resid_norm(
+            ptr_arr, c_void_p(mc), c_void_p(self.ctrl.t.data_ptr() + 4 * 1024), ctrl_arr, c_int(self.rank), c_int(self.world),
+            c_int(self._next_epoch()), c_void_p(self.epoch_dev.data_ptr()), c_int(rows), c_int(n), c_int(partial.stride(0)),
+            c_void_p(0 if bias is None else bias.data_ptr()), c_void_p(0 if resid is None else resid.data_ptr()),
+            c_int(0 if resid is None else resid.stride(0)), c_void_p(0 if norm_weight is None else norm_weight.data_ptr()),
+            c_float(eps), c_int(int(centered)), c_void_p(out.data_ptr()), c_int(out.stride(0)), c_void_p(_lib.stream_ptr()))
+        _lib.check(rc, "nfn_allreduce_resid_norm")
+        return out
+
     def advance_epoch_on_device(self, by: int = 1) -> None:
         """For CUDA-graph replays: bump the device-side epoch base by the number of fused
         calls the captured graph contains."""

@@ -58,6 +58,23 @@ def _worker(rank, world, port, backend, impl, out_q):
             y = ctx.row_linear(xk, wk, bias=b.to(dev, dt), resid=resid.to(dev, dt))
         ref = (x @ w.T + b)[rank * rows:(rank + 1) * rows] + resid
         errs["row"] = float((y.float().cpu() - ref).abs().max())
+        # decode-sized all-reduce + residual + RMS norm (plain peer loads, then multicast if offered)
+        B, Nd = 32, 1664
+        parts = [torch.randn(B, Nd, generator=torch.Generator().manual_seed(20 + r)) for r in range(world)]
+        res0 = torch.randn(B, Nd, generator=torch.Generator().manual_seed(40))
+        nw = 1 + 0.1 * torch.randn(Nd, generator=torch.Generator().manual_seed(41))
+        total = sum(p.to(dt).float() for p in parts) + res0.to(dt).float()
+        total = total.to(dt).float()
+        ref = total * torch.rsqrt(total.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.to(dt).float()
+        for it, mc in enumerate((False, True, False)):
+            if impl == "fused":
+                buf, sym = ctx.partial_buffer(B, Nd)
+                buf.copy_(parts[rank].to(dev, dt))
+            else:
+                buf, sym = parts[rank].to(dev, dt), None
+            resid = res0.to(dev, dt).clone()
+            y = ctx.allreduce_resid_norm(buf, sym, resid=resid, norm_weight=nw.to(dev, dt), use_multicast=mc)
+            errs[f"allreduce{it}"] = max(float((y.float().cpu() - ref).abs().max()), float((resid.float().cpu() - total).abs().max()))
         if backend == "nccl":
             torch.cuda.synchronize()
             from neuralfn_b200.ops import _lib
@@ -85,6 +102,7 @@ def test_torch_impl_on_two_gloo_ranks():
     res = _run(2, "gloo", "torch")
     for rank, errs in res.items():
         assert errs["column"] < 1e-4 and errs["gathered_weight"] < 1e-4 and errs["row"] < 1e-4, (rank, errs)
+        assert max(errs[f"allreduce{i}"] for i in range(3)) < 1e-4, (rank, errs)
 
 
 @pytest.mark.gpu
@@ -105,6 +123,17 @@ def test_single_rank_paths_on_one_gpu(impl):
     for _ in range(2):
         y = ctx.row_linear(xd, wd, bias=bd, resid=resid)
     torch.testing.assert_close(y.float(), ref + resid.float(), atol=5e-2, rtol=3e-2)
+    if impl == "fused":
+        buf, sym = ctx.partial_buffer(32, 6656)
+        buf.copy_(torch.randn(32, 6656, device=dev))
+        r0 = torch.randn(32, 6656, device=dev).bfloat16()
+        resid = r0.clone()
+        nw = (0.1 * torch.randn(6656, device=dev)).bfloat16()
+        y = ctx.allreduce_resid_norm(buf, sym, bias=None, resid=resid, norm_weight=nw, centered=True)
+        tot = (buf.float() + r0.float()).bfloat16().float()
+        torch.testing.assert_close(resid.float(), tot, atol=0, rtol=0)
+        ref = tot * torch.rsqrt(tot.pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + nw.float())
+        torch.testing.assert_close(y.float(), ref, atol=3e-2, rtol=2e-2)
     torch.cuda.synchronize()
     assert _lib.status_read_reset() == 0
 
@@ -117,3 +146,4 @@ def test_fused_matches_oracle_on_two_gpus():
     for rank, errs in res.items():
         assert errs["status"] == 0, (rank, errs)
         assert errs["column"] < 0.06 and errs["gathered_weight"] < 0.06 and errs["row"] < 0.08, (rank, errs)
+        assert max(errs[f"allreduce{i}"] for i in range(3)) < 0.08, (rank, errs)
