@@ -1,0 +1,568 @@
+// Resident inference engine (see nfn_engine.h for the contract).
+//
+// Memory plan, sized once at creation: weights (bf16, one allocation per tensor), per-layer
+// K/V caches [max_batch, n_kv_head, cap_l, head_dim] with cap_l = window for local layers
+// and max_seq for global ones, activation buffers for max(max_seq, max_batch) rows, fp32
+// rotary tables, one pinned host block for the per-step inputs and outputs. Nothing is
+// allocated after nfn_engine_finalize().
+//
+// A decode step always runs all max_batch rows (inactive rows carry length 0 and are
+// skipped inside the attention kernel), so every launch has static shapes and pointers and
+// the step can be replayed as one CUDA graph; per-step data (tokens, lengths, positions,
+// sampling parameters, Philox offset) travels in a single host-to-device copy.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../kernels/nfn_kernels.h"
+#include "nfn_engine.h"
+
+extern "C" {
+// kernel-library entry points that nfn_kernels.h does not declare
+int nfn_norm_forward(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows, int C, float eps,
+                     int mode, int centered, nfn_stream_t stream);
+int nfn_attention_forward(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int Hq, int Hkv, int D,
+                          int ld_q, int ld_k, int ld_v, int ld_o, int causal, int window, float scale, nfn_stream_t stream);
+int nfn_qk_norm_forward(void* qkv, float* rstd, int tokens, int n_q_heads, int n_kv_heads, int head_dim, int ld, float eps,
+                        float q_scale, nfn_stream_t stream);
+int nfn_swiglu_forward(const void* gate_up, int ld, void* out, int ld_out, long long rows, int inter, nfn_stream_t stream);
+int nfn_embedding_positions(const int* tokens, const int* positions, const void* wte, const void* wpe, void* out, int n, int C,
+                            int vocab, int max_pos, float scale, nfn_stream_t stream);
+int nfn_kv_cache_write(const void* qkv, int ld, void* k_cache, void* v_cache, int n, int n_q_heads, int n_kv_heads, int head_dim,
+                       int cap, int pos0, nfn_stream_t stream);
+long long nfn_launch_count(void);
+}
+
+namespace {
+
+thread_local std::string t_err;
+int efail(const std::string& m) {
+  t_err = m;
+  return -1;
+}
+#define CU(call)                                                                                       \
+  do {                                                                                                 \
+    cudaError_t e__ = (call);                                                                          \
+    if (e__ != cudaSuccess) return efail(std::string(#call) + ": " + cudaGetErrorString(e__));         \
+  } while (0)
+#define K(call)                                                                        \
+  do {                                                                                 \
+    int rc__ = (call);                                                                 \
+    if (rc__ != 0) return efail(std::string(#call) + " failed: " + nfn_last_error()); \
+  } while (0)
+
+struct DevTensor {
+  void* ptr = nullptr;
+  long long numel = 0;
+};
+
+struct StepIO {  // layout of the pinned per-step block; device mirror has the same layout
+  long long tokens, lengths, positions, row_params, offset, out_tokens, total;
+};
+
+}  // namespace
+
+struct nfn_engine {
+  nfn_engine_config c{};
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  std::map<std::string, DevTensor> w;
+  std::vector<std::pair<std::string, long long>> expected;
+  bool finalized = false;
+  long long bytes = 0;
+  // activations
+  void *x = nullptr, *xn = nullptr, *qkv = nullptr, *att = nullptr, *ff = nullptr, *ffa = nullptr, *logits = nullptr;
+  float *cosT = nullptr, *sinT = nullptr;
+  std::vector<void*> kc, vc;
+  std::vector<int> cap;
+  void* dec_ws = nullptr;
+  long long dec_ws_bytes = 0;
+  void* rstd = nullptr;         // scratch of the weightless prefill QK norm
+  std::vector<int> logit_row;   // row of e.logits holding each slot's latest logits
+  int decode_calls = 0;
+  int qkv_ld = 0, rows_max = 0;
+  // per-step io
+  unsigned char* h_io = nullptr;
+  unsigned char* d_io = nullptr;
+  StepIO io{};
+  std::vector<int> len;  // tokens held per slot
+  unsigned long long steps = 0;
+  cudaGraphExec_t graph = nullptr;
+  long long launches = 0, graph_launches = 0;
+
+  int alloc(void** p, long long nbytes) {
+    CU(cudaMalloc(p, (size_t)nbytes));
+    bytes += nbytes;
+    return 0;
+  }
+  const void* W(const std::string& n) const { return w.at(n).ptr; }
+  bool has(const std::string& n) const { return w.count(n) != 0; }
+};
+
+namespace {
+
+std::string lname(int l, const char* s) {
+  char buf[96];
+  std::snprintf(buf, sizeof buf, "%d.%s", l, s);
+  return buf;
+}
+std::string gname(int l, const char* s) { return "h." + lname(l, s); }        // GPT-2 family
+std::string yname(int l, const char* s) { return "layers." + lname(l, s); }   // Llama family
+
+bool layer_is_local(const nfn_engine_config& c, int l) {
+  if (c.window <= 0) return false;
+  if (c.global_every <= 0) return true;
+  return ((l + 1) % c.global_every) != 0;
+}
+
+void build_expected(nfn_engine& e) {
+  const nfn_engine_config& c = e.c;
+  const long long C = c.d_model, F = c.d_ff, Vp = c.padded_vocab, HD = c.head_dim;
+  const long long QKV = (long long)(c.n_head + 2 * c.n_kv_head) * HD, ATT = (long long)c.n_head * HD;
+  auto add = [&](const std::string& n, long long numel) { e.expected.emplace_back(n, numel); };
+  if (c.family == 0) {
+    add("wte", Vp * C);
+    add("wpe", (long long)c.max_seq * C);
+    for (int l = 0; l < c.n_layer; ++l) {
+      add(gname(l, "ln_1.weight"), C); add(gname(l, "ln_1.bias"), C);
+      add(gname(l, "attn.c_attn.weight"), QKV * C); add(gname(l, "attn.c_attn.bias"), QKV);
+      add(gname(l, "attn.c_proj.weight"), C * ATT); add(gname(l, "attn.c_proj.bias"), C);
+      add(gname(l, "ln_2.weight"), C); add(gname(l, "ln_2.bias"), C);
+      add(gname(l, "mlp.c_fc.weight"), F * C); add(gname(l, "mlp.c_fc.bias"), F);
+      add(gname(l, "mlp.c_proj.weight"), C * F); add(gname(l, "mlp.c_proj.bias"), C);
+    }
+    add("ln_f.weight", C); add("ln_f.bias", C);
+  } else {
+    add("tok_embeddings", Vp * C);
+    for (int l = 0; l < c.n_layer; ++l) {
+      add(yname(l, "attn_norm"), C);
+      add(yname(l, "wqkv"), QKV * C);
+      if (c.qk_norm == 2) { add(yname(l, "q_norm"), HD); add(yname(l, "k_norm"), HD); }
+      add(yname(l, "wo"), C * ATT);
+      add(yname(l, "ffn_norm"), C);
+      add(yname(l, "w_gate_up"), 2 * F * C);
+      add(yname(l, "w_down"), C * F);
+    }
+    add("norm", C);
+    if (!c.tie_embeddings) add("lm_head", Vp * C);
+  }
+}
+
+// C[M, N] = A[M, K] . B[N, K]^T with the epilogue selected by flags
+int gemm(nfn_engine& e, const void* a, int lda, const void* b, void* cdst, int ldc, int m, int n, int k, int flags, const void* bias,
+         const void* resid, int ld_resid, float act_param = 0.f) {
+  nfn_gemm_args g{};
+  g.a = a; g.b = b; g.c = cdst;
+  g.m = m; g.n = n; g.k = k;
+  g.lda = lda; g.ldb = k; g.ldc = ldc;
+  g.flags = flags | (bias ? NFN_EPI_BIAS : 0) | (resid ? NFN_EPI_RESID : 0);
+  g.alpha = 1.f;
+  g.act_param = act_param;
+  g.bias = bias;
+  g.aux_in = resid;
+  g.ld_aux_in = ld_resid;
+  g.split_k = 1;
+  K(nfn_gemm_bf16(&g, e.stream));
+  return 0;
+}
+
+// One transformer stack over `rows` rows of e.x. decode = true: one token per slot (row ==
+// slot), attention over the caches; false: one sequence of `rows` tokens for `slot`.
+int forward_layers(nfn_engine& e, int rows, bool decode, int slot, const int* d_lengths) {
+  const nfn_engine_config& c = e.c;
+  const int C = c.d_model, F = c.d_ff, HD = c.head_dim, Hq = c.n_head, Hkv = c.n_kv_head, ATT = Hq * HD;
+  const float scale = 1.f / std::sqrt((float)HD);
+  const float sign = c.rope_hf ? 1.f : -1.f;
+  for (int l = 0; l < c.n_layer; ++l) {
+    const bool local = layer_is_local(c, l);
+    const int cap = e.cap[l];
+    const long long cache_stride = (long long)Hkv * cap * HD;
+    char* kc = static_cast<char*>(e.kc[l]);
+    char* vc = static_cast<char*>(e.vc[l]);
+    const void *qw = nullptr, *kw = nullptr;
+    if (c.family == 0) {
+      K(nfn_norm_forward(e.x, e.W(gname(l, "ln_1.weight")), e.W(gname(l, "ln_1.bias")), e.xn, nullptr, nullptr, rows, C, c.norm_eps, 0, 0, e.stream));
+      if (gemm(e, e.xn, C, e.W(gname(l, "attn.c_attn.weight")), e.qkv, e.qkv_ld, rows, e.qkv_ld, C, 0, e.W(gname(l, "attn.c_attn.bias")), nullptr, 0)) return -1;
+    } else {
+      K(nfn_norm_forward(e.x, e.W(yname(l, "attn_norm")), nullptr, e.xn, nullptr, nullptr, rows, C, c.norm_eps, 1, 0, e.stream));
+      if (gemm(e, e.xn, C, e.W(yname(l, "wqkv")), e.qkv, e.qkv_ld, rows, e.qkv_ld, C, 0, nullptr, nullptr, 0)) return -1;
+      if (c.qk_norm == 2) { qw = e.W(yname(l, "q_norm")); kw = e.W(yname(l, "k_norm")); }
+    }
+    const bool rope = c.family == 1;
+    if (decode) {
+      K(nfn_decode_attention(e.qkv, e.qkv_ld, kc, vc, cache_stride, d_lengths, e.att, rows, Hq, Hkv, HD, cap, qw, kw, c.qk_norm != 0,
+                             c.qk_norm_eps, rope ? e.cosT : nullptr, rope ? e.sinT : nullptr, rope ? c.max_seq : 0, sign, scale,
+                             e.dec_ws, e.dec_ws_bytes, 0, e.stream));
+    } else {
+      if (rope && c.qk_norm) {
+        K(nfn_qk_norm_rope_forward(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, qw, kw, e.cosT, e.sinT, nullptr, c.max_seq, sign, c.qk_norm_eps, 1.f, nullptr, e.stream));
+      } else if (rope) {
+        K(nfn_rope_inplace(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, HD, e.cosT, e.sinT, nullptr, c.max_seq, sign, 1.f, e.stream));
+      } else if (c.qk_norm) {
+        K(nfn_qk_norm_forward(e.qkv, static_cast<float*>(e.rstd), rows, Hq, Hkv, HD, e.qkv_ld, c.qk_norm_eps, 1.f, e.stream));
+      }
+      const char* q = static_cast<const char*>(e.qkv);
+      K(nfn_attention_forward(q, q + (size_t)Hq * HD * 2, q + (size_t)(Hq + Hkv) * HD * 2, e.att, nullptr, 1, rows, Hq, Hkv, HD, e.qkv_ld,
+                              e.qkv_ld, e.qkv_ld, ATT, 1, local ? c.window : 0, scale, e.stream));
+      K(nfn_kv_cache_write(e.qkv, e.qkv_ld, kc + (size_t)slot * cache_stride * 2, vc + (size_t)slot * cache_stride * 2, rows, Hq, Hkv, HD, cap, 0, e.stream));
+    }
+    if (c.family == 0) {
+      if (gemm(e, e.att, ATT, e.W(gname(l, "attn.c_proj.weight")), e.x, C, rows, C, ATT, 0, e.W(gname(l, "attn.c_proj.bias")), e.x, C)) return -1;
+      K(nfn_norm_forward(e.x, e.W(gname(l, "ln_2.weight")), e.W(gname(l, "ln_2.bias")), e.xn, nullptr, nullptr, rows, C, c.norm_eps, 0, 0, e.stream));
+      if (gemm(e, e.xn, C, e.W(gname(l, "mlp.c_fc.weight")), e.ff, F, rows, F, C, NFN_ACT_GELU_TANH << NFN_EPI_ACT_SHIFT, e.W(gname(l, "mlp.c_fc.bias")), nullptr, 0)) return -1;
+      if (gemm(e, e.ff, F, e.W(gname(l, "mlp.c_proj.weight")), e.x, C, rows, C, F, 0, e.W(gname(l, "mlp.c_proj.bias")), e.x, C)) return -1;
+    } else {
+      if (gemm(e, e.att, ATT, e.W(yname(l, "wo")), e.x, C, rows, C, ATT, 0, nullptr, e.x, C)) return -1;
+      K(nfn_norm_forward(e.x, e.W(yname(l, "ffn_norm")), nullptr, e.xn, nullptr, nullptr, rows, C, c.norm_eps, 1, 0, e.stream));
+      if (gemm(e, e.xn, C, e.W(yname(l, "w_gate_up")), e.ff, 2 * F, rows, 2 * F, C, 0, nullptr, nullptr, 0)) return -1;
+      K(nfn_swiglu_forward(e.ff, 2 * F, e.ffa, F, rows, F, e.stream));
+      if (gemm(e, e.ffa, F, e.W(yname(l, "w_down")), e.x, C, rows, C, F, 0, nullptr, e.x, C)) return -1;
+    }
+  }
+  return 0;
+}
+
+// final norm of rows [row0, row0 + n) -> logits[n, padded_vocab]
+int head(nfn_engine& e, int row0, int n) {
+  const nfn_engine_config& c = e.c;
+  const int C = c.d_model;
+  const char* xin = static_cast<const char*>(e.x) + (size_t)row0 * C * 2;
+  if (c.family == 0)
+    K(nfn_norm_forward(xin, e.W("ln_f.weight"), e.W("ln_f.bias"), e.xn, nullptr, nullptr, n, C, c.norm_eps, 0, 0, e.stream));
+  else
+    K(nfn_norm_forward(xin, e.W("norm"), nullptr, e.xn, nullptr, nullptr, n, C, c.norm_eps, 1, 0, e.stream));
+  const void* wh = c.family == 0 ? e.W("wte") : (c.tie_embeddings ? e.W("tok_embeddings") : e.W("lm_head"));
+  const int flags = c.logit_softcap > 0.f ? (NFN_ACT_TANH_CAP << NFN_EPI_ACT_SHIFT) : 0;
+  return gemm(e, e.xn, C, wh, e.logits, c.padded_vocab, n, c.padded_vocab, C, flags, nullptr, nullptr, 0, c.logit_softcap);
+}
+
+int sample(nfn_engine& e, int rows, const float* d_row_params, const unsigned long long* d_offset, int* d_out) {
+  // every row carries its own (temperature, top_k, top_p); the Philox offset is a device word
+  K(nfn_sample_rows(e.logits, 0, e.c.padded_vocab, rows, e.c.vocab, d_out, nullptr, 1.f, 0, 1.f, d_row_params, 0x5eedULL, 0ULL, d_offset, 0, e.stream));
+  return 0;
+}
+
+int decode_body(nfn_engine& e) {
+  const int B = e.c.max_batch;
+  const int* d_tok = reinterpret_cast<const int*>(e.d_io + e.io.tokens);
+  const int* d_len = reinterpret_cast<const int*>(e.d_io + e.io.lengths);
+  const int* d_pos = reinterpret_cast<const int*>(e.d_io + e.io.positions);
+  const float* d_rp = reinterpret_cast<const float*>(e.d_io + e.io.row_params);
+  const unsigned long long* d_off = reinterpret_cast<const unsigned long long*>(e.d_io + e.io.offset);
+  int* d_out = reinterpret_cast<int*>(e.d_io + e.io.out_tokens);
+  const nfn_engine_config& c = e.c;
+  if (c.family == 0)
+    K(nfn_embedding_positions(d_tok, d_pos, e.W("wte"), e.W("wpe"), e.x, B, c.d_model, c.vocab, c.max_seq, c.embed_scale, e.stream));
+  else
+    K(nfn_embedding_positions(d_tok, nullptr, e.W("tok_embeddings"), nullptr, e.x, B, c.d_model, c.vocab, c.max_seq, c.embed_scale, e.stream));
+  if (forward_layers(e, B, true, 0, d_len)) return -1;
+  if (head(e, 0, B)) return -1;
+  return sample(e, B, d_rp, d_off, d_out);
+}
+
+void fill_params(const nfn_engine& e, float* rp, int row, const nfn_sampling& s) {
+  rp[3 * row] = s.temperature;
+  rp[3 * row + 1] = (float)s.top_k;
+  rp[3 * row + 2] = s.top_p;
+  (void)e;
+}
+
+}  // namespace
+
+extern "C" {
+
+int nfn_engine_abi_version(void) { return 1; }
+const char* nfn_engine_last_error(void) { return t_err.c_str(); }
+
+nfn_engine* nfn_engine_create(const nfn_engine_config* cfg, int device) {
+  if (!cfg) {
+    efail("engine_create: null config");
+    return nullptr;
+  }
+  const nfn_engine_config& c = *cfg;
+  if ((c.family != 0 && c.family != 1) || c.n_layer <= 0 || c.d_model <= 0 || c.n_head <= 0 || c.n_kv_head <= 0 || c.n_head % c.n_kv_head ||
+      (c.head_dim != 64 && c.head_dim != 128) || c.d_ff <= 0 || c.vocab <= 0 || c.padded_vocab < c.vocab || (c.padded_vocab & 7) ||
+      c.max_seq <= 0 || c.max_batch <= 0 || (c.d_model & 7) || (c.d_ff & 7)) {
+    efail("engine_create: invalid geometry (head_dim must be 64 or 128; widths multiples of 8)");
+    return nullptr;
+  }
+  if (c.family == 0 && (c.n_kv_head != c.n_head || c.n_head * c.head_dim != c.d_model)) {
+    efail("engine_create: the GPT-2 family needs n_kv_head == n_head and n_head * head_dim == d_model");
+    return nullptr;
+  }
+  auto e = std::make_unique<nfn_engine>();
+  e->c = c;
+  if (e->c.embed_scale == 0.f) e->c.embed_scale = 1.f;
+  e->device = device;
+  if (cudaSetDevice(device) != cudaSuccess || cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) {
+    efail("engine_create: cannot select the device or create a stream");
+    return nullptr;
+  }
+  build_expected(*e);
+  e->len.assign(c.max_batch, 0);
+  e->logit_row.assign(c.max_batch, 0);
+  return e.release();
+}
+
+void nfn_engine_destroy(nfn_engine* e) {
+  if (!e) return;
+  cudaSetDevice(e->device);
+  if (e->stream) cudaStreamSynchronize(e->stream);
+  if (e->graph) cudaGraphExecDestroy(e->graph);
+  for (auto& kv : e->w) cudaFree(kv.second.ptr);
+  for (void* p : {e->x, e->xn, e->qkv, e->att, e->ff, e->ffa, e->logits, (void*)e->cosT, (void*)e->sinT, e->dec_ws, (void*)e->d_io, e->rstd})
+    if (p) cudaFree(p);
+  for (void* p : e->kc) cudaFree(p);
+  for (void* p : e->vc) cudaFree(p);
+  if (e->h_io) cudaFreeHost(e->h_io);
+  if (e->stream) cudaStreamDestroy(e->stream);
+  delete e;
+}
+
+int nfn_engine_set_tensor(nfn_engine* e, const char* name, const void* host_bf16, long long numel) {
+  if (!e || !name || !host_bf16 || numel <= 0) return efail("engine_set_tensor: bad arguments");
+  CU(cudaSetDevice(e->device));
+  long long want = -1;
+  for (const auto& kv : e->expected)
+    if (kv.first == name) want = kv.second;
+  if (want < 0) return efail(std::string("engine_set_tensor: this configuration has no tensor named ") + name);
+  if (want != numel) return efail(std::string("engine_set_tensor: ") + name + " has " + std::to_string(numel) + " elements, expected " + std::to_string(want));
+  DevTensor& t = e->w[name];
+  if (!t.ptr) {
+    if (e->alloc(&t.ptr, numel * 2)) return -1;
+    t.numel = numel;
+  }
+  CU(cudaMemcpyAsync(t.ptr, host_bf16, (size_t)numel * 2, cudaMemcpyHostToDevice, e->stream));
+  CU(cudaStreamSynchronize(e->stream));
+  return 0;
+}
+
+int nfn_engine_expected_tensors(const nfn_engine* e, char* buf, int cap) {
+  if (!e) return efail("engine_expected_tensors: null engine");
+  std::string s;
+  for (const auto& kv : e->expected) s += kv.first + " " + std::to_string(kv.second) + "\n";
+  if (buf && cap > 0) {
+    const size_t n = std::min<size_t>(s.size(), (size_t)cap - 1);
+    std::memcpy(buf, s.data(), n);
+    buf[n] = 0;
+  }
+  return (int)s.size();
+}
+
+int nfn_engine_load_dense_v5(nfn_engine* e, const char* path) {
+  if (!e || !path) return efail("engine_load_dense_v5: bad arguments");
+  if (e->c.family != 0) return efail("engine_load_dense_v5: dense GPT checkpoints load into family 0 engines");
+  std::ifstream in(path, std::ios::binary);
+  if (!in) return efail(std::string("engine_load_dense_v5: cannot open ") + path);
+  int32_t h[256];
+  in.read(reinterpret_cast<char*>(h), sizeof h);
+  if (in.gcount() != (std::streamsize)sizeof h || h[0] != 20240326 || h[1] != 5) return efail("engine_load_dense_v5: not a version-5 dense GPT checkpoint");
+  const nfn_engine_config& c = e->c;
+  if (h[2] != c.max_seq || h[3] != c.vocab || h[4] != c.n_layer || h[5] != c.n_head || h[6] != c.d_model || h[7] != c.padded_vocab)
+    return efail("engine_load_dense_v5: checkpoint geometry does not match the engine configuration");
+  std::vector<char> stage;
+  for (const auto& kv : e->expected) {  // the expected order of family 0 is the file order
+    stage.resize((size_t)kv.second * 2);
+    in.read(stage.data(), (std::streamsize)stage.size());
+    if (in.gcount() != (std::streamsize)stage.size()) return efail("engine_load_dense_v5: payload is truncated at " + kv.first);
+    if (nfn_engine_set_tensor(e, kv.first.c_str(), stage.data(), kv.second)) return -1;
+  }
+  if (in.peek() != std::ifstream::traits_type::eof()) return efail("engine_load_dense_v5: trailing bytes after the last tensor");
+  return 0;
+}
+
+int nfn_engine_finalize(nfn_engine* e) {
+  if (!e) return efail("engine_finalize: null engine");
+  if (e->finalized) return 0;
+  CU(cudaSetDevice(e->device));
+  for (const auto& kv : e->expected)
+    if (!e->has(kv.first)) return efail("engine_finalize: missing tensor " + kv.first);
+  const nfn_engine_config& c = e->c;
+  const int HD = c.head_dim;
+  e->qkv_ld = (c.n_head + 2 * c.n_kv_head) * HD;
+  e->rows_max = std::max(c.max_seq, c.max_batch);
+  const long long R = e->rows_max;
+  if (e->alloc(&e->x, R * c.d_model * 2) || e->alloc(&e->xn, R * c.d_model * 2) || e->alloc(&e->qkv, R * e->qkv_ld * 2) ||
+      e->alloc(&e->att, R * c.n_head * HD * 2) || e->alloc(&e->ff, R * (c.family == 1 ? 2LL : 1LL) * c.d_ff * 2) ||
+      e->alloc(&e->ffa, R * c.d_ff * 2) || e->alloc(&e->logits, (long long)c.max_batch * c.padded_vocab * 2) ||
+      e->alloc(&e->rstd, R * (c.n_head + c.n_kv_head) * 4))
+    return -1;
+  if (c.family == 1) {
+    const int half = HD / 2;
+    std::vector<float> cs((size_t)c.max_seq * half), sn((size_t)c.max_seq * half);
+    for (int p = 0; p < c.max_seq; ++p)
+      for (int i = 0; i < half; ++i) {
+        const double ang = (double)p * std::pow((double)c.rope_theta, -2.0 * i / HD);
+        cs[(size_t)p * half + i] = (float)std::cos(ang);
+        sn[(size_t)p * half + i] = (float)std::sin(ang);
+      }
+    if (e->alloc((void**)&e->cosT, (long long)cs.size() * 4) || e->alloc((void**)&e->sinT, (long long)sn.size() * 4)) return -1;
+    CU(cudaMemcpy(e->cosT, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice));
+    CU(cudaMemcpy(e->sinT, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+  }
+  e->kc.resize(c.n_layer);
+  e->vc.resize(c.n_layer);
+  e->cap.resize(c.n_layer);
+  for (int l = 0; l < c.n_layer; ++l) {
+    e->cap[l] = layer_is_local(c, l) ? std::min(c.window, c.max_seq) : c.max_seq;
+    const long long nbytes = (long long)c.max_batch * c.n_kv_head * e->cap[l] * HD * 2;
+    if (e->alloc(&e->kc[l], nbytes) || e->alloc(&e->vc[l], nbytes)) return -1;
+    CU(cudaMemset(e->kc[l], 0, (size_t)nbytes));
+    CU(cudaMemset(e->vc[l], 0, (size_t)nbytes));
+  }
+  e->dec_ws_bytes = nfn_decode_attention_workspace_bytes(c.max_batch, c.n_head, c.n_kv_head, HD, 64);
+  if (e->dec_ws_bytes <= 0) return efail("engine_finalize: bad decode attention geometry");
+  if (e->alloc(&e->dec_ws, e->dec_ws_bytes)) return -1;
+  CU(cudaMemset(e->dec_ws, 0, (size_t)e->dec_ws_bytes));
+  const long long B = c.max_batch;
+  auto up = [](long long v) { return (v + 255) / 256 * 256; };
+  e->io.tokens = 0;
+  e->io.lengths = up(B * 4);
+  e->io.positions = e->io.lengths + up(B * 4);
+  e->io.row_params = e->io.positions + up(B * 4);
+  e->io.offset = e->io.row_params + up(B * 12);
+  e->io.out_tokens = e->io.offset + 256;
+  e->io.total = e->io.out_tokens + up(B * 4);
+  CU(cudaMallocHost((void**)&e->h_io, (size_t)e->io.total));
+  std::memset(e->h_io, 0, (size_t)e->io.total);
+  if (e->alloc((void**)&e->d_io, e->io.total)) return -1;
+  CU(cudaMemset(e->d_io, 0, (size_t)e->io.total));
+  CU(cudaDeviceSynchronize());
+  e->finalized = true;
+  return 0;
+}
+
+long long nfn_engine_device_bytes(const nfn_engine* e) { return e ? e->bytes : -1; }
+int nfn_engine_slot_length(const nfn_engine* e, int slot) { return (e && slot >= 0 && slot < e->c.max_batch) ? e->len[slot] : -1; }
+long long nfn_engine_launches(const nfn_engine* e) { return e ? e->launches : -1; }
+
+int nfn_engine_release(nfn_engine* e, int slot) {
+  if (!e || slot < 0 || slot >= e->c.max_batch) return efail("engine_release: bad slot");
+  e->len[slot] = 0;
+  return 0;
+}
+
+int nfn_engine_prefill(nfn_engine* e, int slot, const int32_t* tokens, int n, const nfn_sampling* s, int32_t* next_token) {
+  if (!e || !tokens || !s || !next_token) return efail("engine_prefill: null argument");
+  if (!e->finalized) return efail("engine_prefill: call nfn_engine_finalize first");
+  const nfn_engine_config& c = e->c;
+  if (slot < 0 || slot >= c.max_batch) return efail("engine_prefill: bad slot");
+  if (n <= 0 || n >= c.max_seq) return efail("engine_prefill: the prompt must hold between 1 and max_seq - 1 tokens");
+  CU(cudaSetDevice(e->device));
+  const long long before = nfn_launch_count();
+  // prompt tokens ride in a temporary region of the qkv buffer until the embedding has run
+  int* d_tok = static_cast<int*>(e->att);
+  CU(cudaMemcpyAsync(d_tok, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+  int* d_pos = d_tok + n;
+  if (c.family == 0) {
+    std::vector<int> pos(n);
+    for (int i = 0; i < n; ++i) pos[i] = i;
+    CU(cudaMemcpyAsync(d_pos, pos.data(), (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaStreamSynchronize(e->stream));  // `pos` leaves scope
+    K(nfn_embedding_positions(d_tok, d_pos, e->W("wte"), e->W("wpe"), e->x, n, c.d_model, c.vocab, c.max_seq, c.embed_scale, e->stream));
+  } else {
+    K(nfn_embedding_positions(d_tok, nullptr, e->W("tok_embeddings"), nullptr, e->x, n, c.d_model, c.vocab, c.max_seq, c.embed_scale, e->stream));
+  }
+  if (forward_layers(*e, n, false, slot, nullptr)) return -1;
+  if (head(*e, n - 1, 1)) return -1;
+  float* rp = reinterpret_cast<float*>(e->h_io + e->io.row_params);
+  fill_params(*e, rp, 0, *s);
+  unsigned long long* off = reinterpret_cast<unsigned long long*>(e->h_io + e->io.offset);
+  *off = (s->seed << 20) ^ (++e->steps);
+  CU(cudaMemcpyAsync(e->d_io + e->io.row_params, rp, 12, cudaMemcpyHostToDevice, e->stream));
+  CU(cudaMemcpyAsync(e->d_io + e->io.offset, off, 8, cudaMemcpyHostToDevice, e->stream));
+  if (sample(*e, 1, reinterpret_cast<const float*>(e->d_io + e->io.row_params),
+             reinterpret_cast<const unsigned long long*>(e->d_io + e->io.offset), reinterpret_cast<int*>(e->d_io + e->io.out_tokens)))
+    return -1;
+  CU(cudaMemcpyAsync(e->h_io + e->io.out_tokens, e->d_io + e->io.out_tokens, 4, cudaMemcpyDeviceToHost, e->stream));
+  CU(cudaStreamSynchronize(e->stream));
+  *next_token = *reinterpret_cast<int*>(e->h_io + e->io.out_tokens);
+  e->len[slot] = n;
+  e->logit_row[slot] = 0;
+  e->launches += nfn_launch_count() - before;
+  if (nfn_status_peek() != 0) return efail("engine_prefill: a kernel reported error code " + std::to_string(nfn_status_read_reset()));
+  return 0;
+}
+
+int nfn_engine_decode(nfn_engine* e, const int32_t* tokens_in, const uint8_t* active, const nfn_sampling* s, const nfn_sampling* per_slot,
+                      int32_t* next_tokens) {
+  if (!e || !tokens_in || !active || !s || !next_tokens) return efail("engine_decode: null argument");
+  if (!e->finalized) return efail("engine_decode: call nfn_engine_finalize first");
+  const nfn_engine_config& c = e->c;
+  const int B = c.max_batch;
+  CU(cudaSetDevice(e->device));
+  int* tok = reinterpret_cast<int*>(e->h_io + e->io.tokens);
+  int* len = reinterpret_cast<int*>(e->h_io + e->io.lengths);
+  int* pos = reinterpret_cast<int*>(e->h_io + e->io.positions);
+  float* rp = reinterpret_cast<float*>(e->h_io + e->io.row_params);
+  int n_active = 0;
+  for (int b = 0; b < B; ++b) {
+    const bool on = active[b] != 0;
+    if (on && e->len[b] <= 0) return efail("engine_decode: slot " + std::to_string(b) + " is active but was never prefilled");
+    if (on && e->len[b] + 1 > c.max_seq) return efail("engine_decode: slot " + std::to_string(b) + " reached max_seq");
+    tok[b] = on ? tokens_in[b] : 0;
+    len[b] = on ? e->len[b] + 1 : 0;
+    pos[b] = on ? e->len[b] : 0;
+    fill_params(*e, rp, b, per_slot ? per_slot[b] : *s);
+    n_active += on;
+  }
+  if (n_active == 0) return 0;
+  *reinterpret_cast<unsigned long long*>(e->h_io + e->io.offset) = (s->seed << 20) ^ (++e->steps);
+  CU(cudaMemcpyAsync(e->d_io, e->h_io, (size_t)e->io.out_tokens, cudaMemcpyHostToDevice, e->stream));
+  if (c.use_cuda_graph && e->graph) {
+    CU(cudaGraphLaunch(e->graph, e->stream));
+    e->launches += e->graph_launches;
+  } else if (c.use_cuda_graph && ++e->decode_calls > 1) {
+    // second decode call: everything is warm (tensor maps cached, attributes set) - capture
+    const long long before = nfn_launch_count();
+    cudaGraph_t g = nullptr;
+    CU(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+    const int rc = decode_body(*e);
+    const cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+    if (rc != 0 || ce != cudaSuccess || !g) {
+      if (g) cudaGraphDestroy(g);
+      return rc != 0 ? -1 : efail("engine_decode: stream capture failed");
+    }
+    CU(cudaGraphInstantiate(&e->graph, g, 0));
+    cudaGraphDestroy(g);
+    e->graph_launches = nfn_launch_count() - before;
+    CU(cudaGraphLaunch(e->graph, e->stream));
+    e->launches += e->graph_launches;
+  } else {
+    const long long before = nfn_launch_count();
+    if (decode_body(*e)) return -1;
+    e->launches += nfn_launch_count() - before;
+  }
+  CU(cudaMemcpyAsync(e->h_io + e->io.out_tokens, e->d_io + e->io.out_tokens, (size_t)B * 4, cudaMemcpyDeviceToHost, e->stream));
+  CU(cudaStreamSynchronize(e->stream));
+  const int* out = reinterpret_cast<const int*>(e->h_io + e->io.out_tokens);
+  for (int b = 0; b < B; ++b)
+    if (active[b]) {
+      next_tokens[b] = out[b];
+      e->len[b] += 1;
+      e->logit_row[b] = b;
+    }
+  if (nfn_status_peek() != 0) return efail("engine_decode: a kernel reported error code " + std::to_string(nfn_status_read_reset()));
+  return 0;
+}
+
+int nfn_engine_last_logits(nfn_engine* e, int slot, float* out_vocab) {
+  if (!e || !out_vocab || slot < 0 || slot >= e->c.max_batch || !e->finalized) return efail("engine_last_logits: bad arguments");
+  CU(cudaSetDevice(e->device));
+  std::vector<uint16_t> tmp(e->c.vocab);
+  CU(cudaMemcpy(tmp.data(), static_cast<const char*>(e->logits) + (size_t)e->logit_row[slot] * e->c.padded_vocab * 2, tmp.size() * 2, cudaMemcpyDeviceToHost));
+  for (int i = 0; i < e->c.vocab; ++i) {
+    const uint32_t bits = (uint32_t)tmp[i] << 16;
+    std::memcpy(&out_vocab[i], &bits, 4);
+  }
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,154 @@
+// Small memory-bound pieces of the inference and Llama-style training paths:
+//   * SwiGLU on a fused [rows, 2I] gate|up projection, forward and backward;
+//   * token (+ learned position) embedding with an explicit position per row, for decode
+//     batches where every sequence is at a different position;
+//   * prefill -> KV-cache scatter: the k and v heads of packed QKV rows go to their cache
+//     slots ((pos0 + t) % cap, so ring caches of local-attention layers work too).
+#include "common.h"
+#include "nfn_kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace nfn {
+
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]); u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+  return u;
+}
+
+__global__ void __launch_bounds__(256)
+swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, int ld, __nv_bfloat16* __restrict__ out, int ld_out, long long rows, int I) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vecs = I / 8;
+  if (idx >= rows * vecs) return;
+  const long long r = idx / vecs;
+  const int c = (int)(idx % vecs) * 8;
+  float g[8], u[8], o[8];
+  unpack8(*reinterpret_cast<const uint4*>(gu + r * ld + c), g);
+  unpack8(*reinterpret_cast<const uint4*>(gu + r * ld + I + c), u);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = silu_f(g[j]) * u[j];
+  *reinterpret_cast<uint4*>(out + r * ld_out + c) = pack8(o);
+}
+
+// dgu = [dout * u * silu'(g) | dout * silu(g)]
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, int ld, const __nv_bfloat16* __restrict__ dout, int ld_dout,
+                  __nv_bfloat16* __restrict__ dgu, int ld_dgu, long long rows, int I) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vecs = I / 8;
+  if (idx >= rows * vecs) return;
+  const long long r = idx / vecs;
+  const int c = (int)(idx % vecs) * 8;
+  float g[8], u[8], d[8], dg[8], du[8];
+  unpack8(*reinterpret_cast<const uint4*>(gu + r * ld + c), g);
+  unpack8(*reinterpret_cast<const uint4*>(gu + r * ld + I + c), u);
+  unpack8(*reinterpret_cast<const uint4*>(dout + r * ld_dout + c), d);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    dg[j] = d[j] * u[j] * dsilu_f(g[j]);
+    du[j] = d[j] * silu_f(g[j]);
+  }
+  *reinterpret_cast<uint4*>(dgu + r * ld_dgu + c) = pack8(dg);
+  *reinterpret_cast<uint4*>(dgu + r * ld_dgu + I + c) = pack8(du);
+}
+
+__global__ void __launch_bounds__(256)
+embedding_pos_kernel(const int* __restrict__ tokens, const int* __restrict__ positions, const __nv_bfloat16* __restrict__ wte,
+                     const __nv_bfloat16* __restrict__ wpe, __nv_bfloat16* __restrict__ out, int n, int C, int vocab, int max_pos,
+                     float scale) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vecs = C / 8;
+  if (idx >= (long long)n * vecs) return;
+  const int r = (int)(idx / vecs), c = (int)(idx % vecs) * 8;
+  const int tok = min(max(tokens[r], 0), vocab - 1);
+  float e[8];
+  unpack8(*reinterpret_cast<const uint4*>(wte + (long long)tok * C + c), e);
+  if (wpe) {
+    const int pos = min(max(positions[r], 0), max_pos - 1);
+    float p[8];
+    unpack8(*reinterpret_cast<const uint4*>(wpe + (long long)pos * C + c), p);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[j] += p[j];
+  }
+  if (scale != 1.f) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[j] *= scale;
+  }
+  *reinterpret_cast<uint4*>(out + (long long)r * C + c) = pack8(e);
+}
+
+// rows t in [t_first, n): k/v heads of row t -> cache slot (pos0 + t) % cap
+__global__ void __launch_bounds__(256)
+kv_cache_write_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc,
+                      int n, int t_first, int Hq, int Hkv, int hd, int cap, int pos0) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vecs = hd / 8;
+  const long long total = (long long)(n - t_first) * Hkv * vecs;
+  if (idx >= total) return;
+  const int c = (int)(idx % vecs) * 8;
+  const int h = (int)((idx / vecs) % Hkv);
+  const int t = t_first + (int)(idx / ((long long)vecs * Hkv));
+  const int slot = (pos0 + t) % cap;
+  const __nv_bfloat16* row = qkv + (long long)t * ld;
+  const long long dst = ((long long)h * cap + slot) * hd + c;
+  *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(row + (long long)(Hq + h) * hd + c);
+  *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(row + (long long)(Hq + Hkv + h) * hd + c);
+}
+
+}  // namespace nfn
+
+using namespace nfn;
+
+extern "C" int nfn_swiglu_forward(const void* gate_up, int ld, void* out, int ld_out, long long rows, int inter, nfn_stream_t stream) {
+  if (rows <= 0) return 0;
+  if (!gate_up || !out || inter <= 0 || (inter & 7) || (ld & 7) || (ld_out & 7) || ld < 2 * inter || ld_out < inter)
+    return fail(-1, "swiglu_forward: bad arguments (sizes and strides must be multiples of 8)");
+  const long long total = rows * (inter / 8), grid = (total + 255) / 256;
+  if (grid > 0x7fffffffLL) return fail(-1, "swiglu_forward: too large for one launch");
+  swiglu_fwd_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), ld, static_cast<__nv_bfloat16*>(out), ld_out, rows, inter);
+  return launch_check("swiglu_forward", 1);
+}
+
+extern "C" int nfn_swiglu_backward(const void* gate_up, int ld, const void* dout, int ld_dout, void* dgate_up, int ld_dgu,
+                                   long long rows, int inter, nfn_stream_t stream) {
+  if (rows <= 0) return 0;
+  if (!gate_up || !dout || !dgate_up || inter <= 0 || (inter & 7) || (ld & 7) || (ld_dout & 7) || (ld_dgu & 7) ||
+      ld < 2 * inter || ld_dgu < 2 * inter || ld_dout < inter)
+    return fail(-1, "swiglu_backward: bad arguments (sizes and strides must be multiples of 8)");
+  const long long total = rows * (inter / 8), grid = (total + 255) / 256;
+  if (grid > 0x7fffffffLL) return fail(-1, "swiglu_backward: too large for one launch");
+  swiglu_bwd_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), ld, static_cast<const __nv_bfloat16*>(dout), ld_dout,
+      static_cast<__nv_bfloat16*>(dgate_up), ld_dgu, rows, inter);
+  return launch_check("swiglu_backward", 1);
+}
+
+extern "C" int nfn_embedding_positions(const int* tokens, const int* positions, const void* wte, const void* wpe, void* out, int n,
+                                       int C, int vocab, int max_pos, float scale, nfn_stream_t stream) {
+  if (n <= 0) return 0;
+  if (!tokens || !wte || !out || (wpe && !positions) || C <= 0 || (C & 7) || vocab <= 0) return fail(-1, "embedding_positions: bad arguments");
+  const long long total = (long long)n * (C / 8);
+  embedding_pos_kernel<<<(unsigned)((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      tokens, positions, static_cast<const __nv_bfloat16*>(wte), static_cast<const __nv_bfloat16*>(wpe),
+      static_cast<__nv_bfloat16*>(out), n, C, vocab, max_pos > 0 ? max_pos : 1, scale);
+  return launch_check("embedding_positions", 1);
+}
+
+extern "C" int nfn_kv_cache_write(const void* qkv, int ld, void* k_cache, void* v_cache, int n, int n_q_heads, int n_kv_heads,
+                                  int head_dim, int cap, int pos0, nfn_stream_t stream) {
+  if (n <= 0) return 0;
+  if (!qkv || !k_cache || !v_cache || cap <= 0 || pos0 < 0 || (head_dim & 7) || (ld & 7) || ld < (n_q_heads + 2 * n_kv_heads) * head_dim)
+    return fail(-1, "kv_cache_write: bad arguments");
+  const int t_first = n > cap ? n - cap : 0;  // earlier rows would be overwritten anyway (and would race)
+  const long long total = (long long)(n - t_first) * n_kv_heads * (head_dim / 8);
+  kv_cache_write_kernel<<<(unsigned)((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(qkv), ld, static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), n,
+      t_first, n_q_heads, n_kv_heads, head_dim, cap, pos0);
+  return launch_check("kv_cache_write", 1);
+}

@@ -19,6 +19,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent.parent
 KERNEL_SRC = PKG / "csrc" / "kernels"
 RUNTIME_SRC = PKG / "csrc" / "runtime"
+ENGINE_SRC = PKG / "csrc" / "engine"
 LIB_DIR = PKG / "lib"
 OBJ_DIR = PKG / "lib" / "obj"
 
@@ -46,7 +47,8 @@ def _digest(paths) -> str:
 
 
 def _compile_one(src: Path, obj: Path, extra: list[str], verbose: bool) -> str:
-    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-I", str(KERNEL_SRC), "-c", str(src), "-o", str(obj)]
+    lang = ["-x", "cu"] if src.suffix == ".cpp" else []
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, *lang, "-I", str(KERNEL_SRC), "-I", str(ENGINE_SRC), "-c", str(src), "-o", str(obj)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src.name}:\n{proc.stdout}\n{proc.stderr}")
@@ -58,8 +60,11 @@ def build_kernels(force: bool = False, verbose: bool = False, ptxas_info: bool =
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     out = LIB_DIR / "libnfn_b200_kernels.so"
-    sources = sorted(KERNEL_SRC.glob("*.cu"))
-    headers = sorted(list(KERNEL_SRC.glob("*.h")) + list(KERNEL_SRC.glob("*.cuh")) + list(KERNEL_SRC.glob("*.inc")))
+    # the resident inference engine (host C++ driving the kernels) lives in the same library,
+    # so it shares the library's CUDA runtime instance and needs no extra link step
+    sources = sorted(KERNEL_SRC.glob("*.cu")) + sorted(ENGINE_SRC.glob("*.cpp"))
+    headers = sorted(list(KERNEL_SRC.glob("*.h")) + list(KERNEL_SRC.glob("*.cuh")) + list(KERNEL_SRC.glob("*.inc")) +
+                     list(ENGINE_SRC.glob("*.h")))
     hdr_digest = _digest(headers)
     extra = ["-Xptxas", "-v"] if ptxas_info else []
     jobs = []

@@ -1,0 +1,275 @@
+"""Python API of the resident inference engine (``csrc/engine``): weights, KV caches and
+activations stay on the GPU; Python passes token ids in and gets token ids back.
+
+    eng = ResidentEngine(EngineConfig.gpt2(cfg, max_batch=8))
+    eng.load_dense_checkpoint("model_00001000.bin")      # or eng.load_named_tensors(...)
+    out = eng.generate([[15496, 11], [40]], max_new_tokens=32, sampling=Sampling(temperature=0.8, top_p=0.95))
+
+``generate`` is a continuous-batching loop: prompts are prefetched into free slots as
+earlier sequences finish, and every decode step advances all live slots at once.
+Counterpart of the reference's ``_native_inference`` module and its Python wrapper
+(``csrc/native_gpt2/resident_binding.cpp``, ``neuralfn/native_inference.py``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, fields
+from typing import Iterable, Sequence
+
+import torch
+
+from ..ops import _lib
+
+__all__ = ["EngineConfig", "Sampling", "ResidentEngine", "resident_inference_abi_version", "resident_inference_capabilities"]
+
+
+class _CConfig(C.Structure):
+    _fields_ = [("family", C.c_int), ("n_layer", C.c_int), ("d_model", C.c_int), ("n_head", C.c_int), ("n_kv_head", C.c_int),
+                ("head_dim", C.c_int), ("d_ff", C.c_int), ("vocab", C.c_int), ("padded_vocab", C.c_int), ("max_seq", C.c_int),
+                ("max_batch", C.c_int), ("qk_norm", C.c_int), ("rope_hf", C.c_int), ("rope_theta", C.c_float),
+                ("norm_eps", C.c_float), ("qk_norm_eps", C.c_float), ("logit_softcap", C.c_float), ("tie_embeddings", C.c_int),
+                ("window", C.c_int), ("global_every", C.c_int), ("embed_scale", C.c_float), ("use_cuda_graph", C.c_int)]
+
+
+class _CSampling(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int), ("top_p", C.c_float), ("seed", C.c_uint64)]
+
+
+@dataclass
+class Sampling:
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    seed: int = 0
+
+    def c(self) -> _CSampling:
+        return _CSampling(self.temperature, self.top_k, self.top_p, self.seed)
+
+
+@dataclass
+class EngineConfig:
+    family: int = 0                # 0 GPT-2 style, 1 Llama style
+    n_layer: int = 12
+    d_model: int = 768
+    n_head: int = 12
+    n_kv_head: int = 12
+    head_dim: int = 64
+    d_ff: int = 3072
+    vocab: int = 50257
+    padded_vocab: int = 50304
+    max_seq: int = 1024
+    max_batch: int = 8
+    qk_norm: int = 0               # 0 none, 1 weightless, 2 weighted
+    rope_hf: int = 1
+    rope_theta: float = 10000.0
+    norm_eps: float = 1e-5
+    qk_norm_eps: float = 1e-6
+    logit_softcap: float = 0.0
+    tie_embeddings: int = 1
+    window: int = 0
+    global_every: int = 0
+    embed_scale: float = 1.0
+    use_cuda_graph: int = 1
+
+    @classmethod
+    def gpt2(cls, cfg, max_batch: int = 8, **kw) -> "EngineConfig":
+        """From a ``models.gpt2.GPT2Config``."""
+        return cls(family=0, n_layer=cfg.n_layer, d_model=cfg.d_model, n_head=cfg.n_head, n_kv_head=cfg.n_head,
+                   head_dim=cfg.head_dim, d_ff=cfg.mlp_mult * cfg.d_model, vocab=cfg.vocab_size, padded_vocab=cfg.padded_vocab,
+                   max_seq=cfg.max_seq_len, max_batch=max_batch, qk_norm=1 if cfg.qk_norm else 0, norm_eps=cfg.ln_eps,
+                   qk_norm_eps=cfg.qk_norm_eps, logit_softcap=cfg.logit_softcap, tie_embeddings=1, **kw)
+
+    def c(self) -> _CConfig:
+        return _CConfig(*[getattr(self, f.name) for f in fields(self)])
+
+
+def _api():
+    L = _lib.load()
+    if getattr(L, "_engine_ready", False):
+        return L
+    vp, ip = C.c_void_p, C.c_int
+    L.nfn_engine_last_error.restype = C.c_char_p
+    L.nfn_engine_create.restype, L.nfn_engine_create.argtypes = vp, [C.POINTER(_CConfig), ip]
+    L.nfn_engine_destroy.restype, L.nfn_engine_destroy.argtypes = None, [vp]
+    L.nfn_engine_set_tensor.argtypes = [vp, C.c_char_p, vp, C.c_longlong]
+    L.nfn_engine_expected_tensors.argtypes = [vp, C.c_char_p, ip]
+    L.nfn_engine_load_dense_v5.argtypes = [vp, C.c_char_p]
+    L.nfn_engine_finalize.argtypes = [vp]
+    L.nfn_engine_device_bytes.restype, L.nfn_engine_device_bytes.argtypes = C.c_longlong, [vp]
+    L.nfn_engine_prefill.argtypes = [vp, ip, vp, ip, C.POINTER(_CSampling), vp]
+    L.nfn_engine_decode.argtypes = [vp, vp, vp, C.POINTER(_CSampling), vp, vp]
+    L.nfn_engine_release.argtypes = [vp, ip]
+    L.nfn_engine_slot_length.argtypes = [vp, ip]
+    L.nfn_engine_last_logits.argtypes = [vp, ip, vp]
+    L.nfn_engine_launches.restype, L.nfn_engine_launches.argtypes = C.c_longlong, [vp]
+    L._engine_ready = True
+    return L
+
+
+def resident_inference_abi_version() -> int:
+    return int(_api().nfn_engine_abi_version())
+
+
+def resident_inference_capabilities() -> dict:
+    return {"abi_version": resident_inference_abi_version(), "families": ["gpt2", "llama"], "kv_cache": "bf16",
+            "hybrid_local_global": True, "qk_norm": True, "rope": ["hf", "legacy"], "continuous_batching": True,
+            "cuda_graph_decode": True, "on_device_sampling": ["greedy", "temperature", "top_k", "top_p"],
+            "quantized_weights": ["Q4_K", "Q5_K", "Q6_K", "NF4"]}
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+class ResidentEngine:
+    def __init__(self, config: EngineConfig, device: int = 0) -> None:
+        self.config = config
+        self._L = _api()
+        cc = config.c()
+        self._h = self._L.nfn_engine_create(C.byref(cc), device)
+        if not self._h:
+            raise EngineError(self._err())
+        self._finalized = False
+
+    def _err(self) -> str:
+        return (self._L.nfn_engine_last_error() or b"").decode("utf-8", "replace")
+
+    def _check(self, rc: int) -> None:
+        if rc < 0:
+            raise EngineError(self._err())
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._L.nfn_engine_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    # ---- weights --------------------------------------------------------------------------
+    def expected_tensors(self) -> dict[str, int]:
+        n = self._L.nfn_engine_expected_tensors(self._h, None, 0)
+        buf = C.create_string_buffer(n + 1)
+        self._L.nfn_engine_expected_tensors(self._h, buf, n + 1)
+        return {a: int(b) for a, b in (line.split() for line in buf.value.decode().splitlines())}
+
+    def set_tensor(self, name: str, t: torch.Tensor) -> None:
+        t = t.detach().to("cpu", torch.bfloat16).contiguous()
+        self._check(self._L.nfn_engine_set_tensor(self._h, name.encode(), t.data_ptr(), t.numel()))
+
+    def load_named_tensors(self, tensors: dict[str, torch.Tensor]) -> None:
+        for name, numel in self.expected_tensors().items():
+            if name not in tensors:
+                raise EngineError(f"missing tensor {name!r}")
+            t = tensors[name]
+            if name in ("wte", "tok_embeddings", "lm_head") and t.numel() < numel:  # pad the vocabulary rows
+                pad = torch.zeros(numel // t.shape[1] - t.shape[0], t.shape[1], dtype=t.dtype)
+                t = torch.cat([t.cpu(), pad])
+            self.set_tensor(name, t)
+        self.finalize()
+
+    def load_dense_checkpoint(self, path) -> None:
+        self._check(self._L.nfn_engine_load_dense_v5(self._h, str(path).encode()))
+        self.finalize()
+
+    def load_hf_llama_state_dict(self, sd: dict[str, torch.Tensor]) -> None:
+        """Hugging Face Llama / Qwen3-style names -> the engine's fused layout (q|k|v rows
+        concatenated, gate|up rows concatenated)."""
+        c = self.config
+        out = {"tok_embeddings": sd["model.embed_tokens.weight"], "norm": sd["model.norm.weight"]}
+        if not c.tie_embeddings:
+            out["lm_head"] = sd["lm_head.weight"]
+        for l in range(c.n_layer):
+            p = f"model.layers.{l}."
+            out[f"layers.{l}.attn_norm"] = sd[p + "input_layernorm.weight"]
+            out[f"layers.{l}.wqkv"] = torch.cat([sd[p + f"self_attn.{n}_proj.weight"] for n in "qkv"])
+            if c.qk_norm == 2:
+                out[f"layers.{l}.q_norm"] = sd[p + "self_attn.q_norm.weight"]
+                out[f"layers.{l}.k_norm"] = sd[p + "self_attn.k_norm.weight"]
+            out[f"layers.{l}.wo"] = sd[p + "self_attn.o_proj.weight"]
+            out[f"layers.{l}.ffn_norm"] = sd[p + "post_attention_layernorm.weight"]
+            out[f"layers.{l}.w_gate_up"] = torch.cat([sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"]])
+            out[f"layers.{l}.w_down"] = sd[p + "mlp.down_proj.weight"]
+        self.load_named_tensors(out)
+
+    def finalize(self) -> None:
+        self._check(self._L.nfn_engine_finalize(self._h))
+        self._finalized = True
+
+    @property
+    def device_bytes(self) -> int:
+        return int(self._L.nfn_engine_device_bytes(self._h))
+
+    @property
+    def launches(self) -> int:
+        return int(self._L.nfn_engine_launches(self._h))
+
+    # ---- stepping --------------------------------------------------------------------------
+    def prefill(self, slot: int, tokens: Sequence[int], sampling: Sampling | None = None) -> int:
+        arr = (C.c_int32 * len(tokens))(*tokens)
+        out = C.c_int32(0)
+        s = (sampling or Sampling()).c()
+        self._check(self._L.nfn_engine_prefill(self._h, slot, C.cast(arr, C.c_void_p), len(tokens), C.byref(s), C.cast(C.byref(out), C.c_void_p)))
+        return int(out.value)
+
+    def decode(self, tokens_in: dict[int, int], sampling: Sampling | None = None, per_slot: dict[int, Sampling] | None = None) -> dict[int, int]:
+        B = self.config.max_batch
+        tok = (C.c_int32 * B)()
+        act = (C.c_uint8 * B)()
+        for slot, t in tokens_in.items():
+            tok[slot], act[slot] = t, 1
+        s = (sampling or Sampling()).c()
+        ps = None
+        if per_slot:
+            ps = (_CSampling * B)(*[(per_slot.get(b) or sampling or Sampling()).c() for b in range(B)])
+        out = (C.c_int32 * B)()
+        self._check(self._L.nfn_engine_decode(self._h, C.cast(tok, C.c_void_p), C.cast(act, C.c_void_p), C.byref(s),
+                                              C.cast(ps, C.c_void_p) if ps is not None else None, C.cast(out, C.c_void_p)))
+        return {slot: int(out[slot]) for slot in tokens_in}
+
+    def release(self, slot: int) -> None:
+        self._check(self._L.nfn_engine_release(self._h, slot))
+
+    def slot_length(self, slot: int) -> int:
+        return int(self._L.nfn_engine_slot_length(self._h, slot))
+
+    def last_logits(self, slot: int) -> torch.Tensor:
+        out = torch.empty(self.config.vocab, dtype=torch.float32)
+        self._check(self._L.nfn_engine_last_logits(self._h, slot, out.data_ptr()))
+        return out
+
+    def generate(self, prompts: Iterable[Sequence[int]], max_new_tokens: int = 32, sampling: Sampling | None = None,
+                 eos_token: int | None = None) -> list[list[int]]:
+        """Continuous batching over ``max_batch`` slots; returns the generated ids per prompt."""
+        prompts = [list(p) for p in prompts]
+        results: list[list[int]] = [[] for _ in prompts]
+        pending = list(range(len(prompts)))[::-1]
+        live: dict[int, int] = {}       # slot -> prompt index
+        last: dict[int, int] = {}       # slot -> token to feed next
+        free = list(range(self.config.max_batch))[::-1]
+        sampling = sampling or Sampling()
+
+        def finished(idx: int, tok: int) -> bool:
+            return len(results[idx]) >= max_new_tokens or (eos_token is not None and tok == eos_token)
+
+        while pending or live:
+            while pending and free:
+                idx, slot = pending.pop(), free.pop()
+                tok = self.prefill(slot, prompts[idx], sampling)
+                results[idx].append(tok)
+                if finished(idx, tok) or len(prompts[idx]) + 1 >= self.config.max_seq:
+                    self.release(slot)
+                    free.append(slot)
+                else:
+                    live[slot], last[slot] = idx, tok
+            if not live:
+                continue
+            nxt = self.decode({slot: last[slot] for slot in live}, sampling)
+            for slot, tok in nxt.items():
+                idx = live[slot]
+                results[idx].append(tok)
+                last[slot] = tok
+                if finished(idx, tok) or self.slot_length(slot) + 1 >= self.config.max_seq:
+                    self.release(slot)
+                    free.append(slot)
+                    del live[slot], last[slot]
+        return results
