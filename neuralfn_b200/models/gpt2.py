@@ -52,6 +52,16 @@ class GPT2Config:
     def head_dim(self) -> int:
         return self.d_model // self.n_head
 
+    # hooks used by trainers.dense_gpt.DenseGPTTrainer (every model family provides them)
+    def param_specs(self) -> "list[ParamSpec]":
+        return gpt2_param_specs(self)
+
+    def init_params_(self, layout: "FlatLayout", master: torch.Tensor, seed: int) -> None:
+        init_gpt2_params_(self, layout, master, seed)
+
+    def make_engine(self, layout, params, grads, batch: int, seq: int) -> "GPT2Engine":
+        return GPT2Engine(self, layout, params, grads, batch, seq)
+
     @classmethod
     def variant(cls, name: str, **kw) -> "GPT2Config":
         """Named dense variants: defaults z=1e-4, cap=30, qk-norm as in the reference presets

@@ -132,6 +132,25 @@ def decode_attention(qkv, k_cache, v_cache, lengths, *, n_q_heads: int, n_kv_hea
     return out
 
 
+def swiglu_forward(gate_up: torch.Tensor, inter: int, out=None) -> torch.Tensor:
+    """gate_up bf16 [rows, 2 * inter] (gate | up) -> silu(gate) * up, bf16 [rows, inter]."""
+    rows = gate_up.shape[0]
+    out = torch.empty(rows, inter, dtype=_bf16, device=gate_up.device) if out is None else out
+    rc = _lib.load().nfn_swiglu_forward(_p(gate_up), c_int(gate_up.stride(0)), _p(out), c_int(out.stride(0)), c_longlong(rows),
+                                        c_int(inter), _st())
+    _lib.check(rc, "nfn_swiglu_forward")
+    return out
+
+
+def swiglu_backward(gate_up: torch.Tensor, dout: torch.Tensor, inter: int, out=None) -> torch.Tensor:
+    rows = gate_up.shape[0]
+    out = torch.empty_like(gate_up) if out is None else out
+    rc = _lib.load().nfn_swiglu_backward(_p(gate_up), c_int(gate_up.stride(0)), _p(dout), c_int(dout.stride(0)), _p(out),
+                                         c_int(out.stride(0)), c_longlong(rows), c_int(inter), _st())
+    _lib.check(rc, "nfn_swiglu_backward")
+    return out
+
+
 def quant_block_bytes(qtype: int) -> int:
     return int(_lib.load().nfn_quant_block_bytes(c_int(qtype)))
 

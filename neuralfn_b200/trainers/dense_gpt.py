@@ -24,7 +24,7 @@ from dataclasses import dataclass
 import torch
 import torch.distributed as dist
 
-from ..models.gpt2 import FlatLayout, GPT2Config, GPT2Engine, gpt2_param_specs, init_gpt2_params_
+from ..models.gpt2 import FlatLayout, GPT2Config
 from ..parallel.dp import AdamWConfig, ShardedAdamW, SymmetricBuffers
 
 __all__ = ["DenseGPTTrainer", "TrainReport"]
@@ -40,7 +40,7 @@ class TrainReport:
 
 
 class DenseGPTTrainer:
-    def __init__(self, cfg: GPT2Config, batch: int, seq: int, optim: AdamWConfig | None = None, *,
+    def __init__(self, cfg, batch: int, seq: int, optim: AdamWConfig | None = None, *,
                  device: torch.device | str | None = None, seed: int = 1337, use_cuda_graph: bool = True,
                  group=None) -> None:
         if device is None:
@@ -52,16 +52,16 @@ class DenseGPTTrainer:
         self.optim_cfg = optim or AdamWConfig()
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.layout = FlatLayout(gpt2_param_specs(cfg), world=self.world)
+        self.layout = FlatLayout(cfg.param_specs(), world=self.world)
         self.bufs = SymmetricBuffers(self.layout.n_total, self.device, group)
         # identical initial weights on every rank (same seed), fp32 master -> bf16 params
         master = torch.empty(self.layout.n_total, dtype=torch.float32, device=self.device)
-        init_gpt2_params_(cfg, self.layout, master, seed)
+        cfg.init_params_(self.layout, master, seed)
         self.opt = ShardedAdamW(self.layout, self.bufs, self.optim_cfg, master_init=master)
         self.bufs.params.copy_(master.to(torch.bfloat16))
         del master
         self.bufs.grads.zero_()
-        self.engine = GPT2Engine(cfg, self.layout, self.bufs.params, self.bufs.grads, batch, seq)
+        self.engine = cfg.make_engine(self.layout, self.bufs.params, self.bufs.grads, batch, seq)
         self.use_cuda_graph = use_cuda_graph
         self._graph: torch.cuda.CUDAGraph | None = None
         self._warmed = False
