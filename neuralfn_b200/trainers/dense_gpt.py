@@ -18,6 +18,7 @@ scheduled lr, one AdamW launch) for the no-accumulation case.
 """
 from __future__ import annotations
 
+import ctypes
 import time
 from dataclasses import dataclass
 
@@ -42,7 +43,7 @@ class TrainReport:
 class DenseGPTTrainer:
     def __init__(self, cfg, batch: int, seq: int, optim: AdamWConfig | None = None, *,
                  device: torch.device | str | None = None, seed: int = 1337, use_cuda_graph: bool = True,
-                 group=None) -> None:
+                 group=None, grad_accum_steps: int = 1) -> None:
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device())
         self.device = torch.device(device)
@@ -63,8 +64,14 @@ class DenseGPTTrainer:
         self.bufs.grads.zero_()
         self.engine = cfg.make_engine(self.layout, self.bufs.params, self.bufs.grads, batch, seq)
         self.use_cuda_graph = use_cuda_graph
-        self._graph: torch.cuda.CUDAGraph | None = None
-        self._warmed = False
+        # gradient accumulation: `grad_accum_steps` micro-batches per optimizer step, summed in
+        # an fp32 side buffer; each phase of the cycle is its own captured graph
+        self.grad_accum = max(1, int(grad_accum_steps))
+        self._micro = 0
+        self._acc = (torch.zeros(self.layout.n_total, dtype=torch.float32, device=self.device)
+                     if self.grad_accum > 1 else None)
+        self._graphs: dict[str, torch.cuda.CUDAGraph] = {}
+        self._warm: set[str] = set()
         self.launches_per_step = 0
         self._h_tokens = torch.zeros(batch * seq, dtype=torch.int32).pin_memory()
         self._h_targets = torch.zeros(batch * seq, dtype=torch.int32).pin_memory()
@@ -74,35 +81,50 @@ class DenseGPTTrainer:
             dist.barrier(group)
 
     # ------------------------------------------------------------------ step --
-    def _launch_step(self) -> None:
+    def _launch_phase(self, phase: str) -> None:
+        from ..ops import _lib
         self.engine.forward()
         self.engine.backward()
-        self.opt.launch_step()
+        if phase != "single":
+            mode = {"first": 0, "mid": 1, "last": 2}[phase]
+            rc = _lib.load().nfn_grad_accumulate(ctypes.c_void_p(self._acc.data_ptr()), ctypes.c_void_p(self.bufs.grads.data_ptr()),
+                                                 ctypes.c_longlong(self.layout.n_total), ctypes.c_int(mode),
+                                                 ctypes.c_float(1.0 / self.grad_accum), ctypes.c_void_p(_lib.stream_ptr()))
+            _lib.check(rc, "nfn_grad_accumulate")
+        if phase in ("single", "last"):
+            self.opt.launch_step()
 
     def _run_step(self) -> None:
-        """forward + backward + optimizer on the batch already in the engine buffers."""
+        """forward + backward (+ accumulate) (+ optimizer) on the batch already in the engine
+        buffers. The optimizer runs on the last micro-batch of each accumulation cycle."""
         from ..ops import _lib
-        self.opt.stage_hyper()
-        if not self.use_cuda_graph:
-            before = _lib.launch_count()
-            self._launch_step()
-            self.launches_per_step = _lib.launch_count() - before
-        elif not self._warmed:
-            # the first step runs eagerly: it sets kernel attributes and fills the
+        k, i = self.grad_accum, self._micro
+        phase = "single" if k == 1 else ("first" if i == 0 else ("last" if i == k - 1 else "mid"))
+        final = phase in ("single", "last")
+        if final:
+            self.opt.stage_hyper()
+        if not self.use_cuda_graph or phase not in self._warm:
+            # the first run of a phase is eager: it sets kernel attributes and fills the
             # tensor-map cache, neither of which may happen during stream capture
             before = _lib.launch_count()
-            self._launch_step()
-            self.launches_per_step = _lib.launch_count() - before
-            self._warmed = True
-        elif self._graph is None:
+            self._launch_phase(phase)
+            if final:
+                self.launches_per_step = _lib.launch_count() - before
+            self._warm.add(phase)
+        elif phase not in self._graphs:
             torch.cuda.synchronize(self.device)
-            self._graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self._graph):
-                self._launch_step()
-            self._graph.replay()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._launch_phase(phase)
+            self._graphs[phase] = g
+            g.replay()
         else:
-            self._graph.replay()
-        self.opt.step_count += 1
+            self._graphs[phase].replay()
+        if final:
+            self.opt.step_count += 1
+            self._micro = 0
+        else:
+            self._micro += 1
 
     def upload(self, tokens: torch.Tensor, targets: torch.Tensor) -> int:
         """Copy a batch into the device input buffers; returns the bytes moved host->device."""
@@ -122,8 +144,10 @@ class DenseGPTTrainer:
         return moved
 
     def train_step(self, tokens: torch.Tensor, targets: torch.Tensor, *, return_loss: bool = True):
-        """One optimizer step. Returns the mean token loss of this rank's micro-batch (python
-        float, read back from the device) when ``return_loss``."""
+        """One micro-batch: forward, backward and - on the last micro-batch of an accumulation
+        cycle (every call when ``grad_accum_steps == 1``) - the optimizer step. Returns the mean
+        token loss of this rank's micro-batch (python float, read back from the device) when
+        ``return_loss``."""
         self.upload(tokens, targets)
         self._run_step()
         if return_loss:
@@ -138,6 +162,7 @@ class DenseGPTTrainer:
 
     @property
     def tokens_per_step(self) -> int:
+        """Tokens consumed by one ``train_step`` call (one micro-batch on every rank)."""
         return self.batch * self.seq * self.world
 
     # --------------------------------------------------------------- training --

@@ -69,3 +69,25 @@ def test_trainer_loss_decreases_and_graph_matches_eager(kernel_lib):
         results.append(losses)
     # graph replay and eager launches run the same kernels on the same data
     assert max(abs(a - b) for a, b in zip(*results)) < 5e-2
+
+
+def test_gradient_accumulation_matches_one_large_batch(kernel_lib):
+    from neuralfn_b200.models.gpt2 import GPT2Config
+    from neuralfn_b200.parallel.dp import AdamWConfig
+    from neuralfn_b200.trainers.dense_gpt import DenseGPTTrainer
+    cfg = GPT2Config.variant("gpt2", n_layer=2, n_head=2, d_model=128, vocab_size=512, max_seq_len=64)
+    opt = AdamWConfig(lr=1e-3, warmup_steps=1, total_steps=20, weight_decay=0.0)
+    torch.manual_seed(1)
+    tok = torch.randint(0, 512, (4, 64))
+    tgt = torch.roll(tok, -1, dims=1)
+    big = DenseGPTTrainer(cfg, 4, 64, opt, seed=11)
+    acc = DenseGPTTrainer(cfg, 2, 64, opt, seed=11, grad_accum_steps=2)
+    for _ in range(4):  # eager, then captured phases
+        big.train_step(tok, tgt)
+        acc.train_step(tok[:2], tgt[:2])
+        acc.train_step(tok[2:], tgt[2:])
+    assert big.opt.step_count == acc.opt.step_count == 4
+    a, b = big.opt.master[:big.layout.n_used], acc.opt.master[:acc.layout.n_used]
+    rel = float((a - b).norm() / a.norm())
+    assert rel < 2e-3, rel
+    big.check_status()
