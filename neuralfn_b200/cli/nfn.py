@@ -1,0 +1,215 @@
+"""``nfn`` command line: train / infer / inspect, one JSON document per invocation on stdout.
+
+    nfn train --base-model gpt --template-name gpt2_qknorm --dataset fineweb10B --output-dir runs/a
+    nfn train --base-model llama --n-layer 16 --d-model 1024 --n-head 16 --n-kv-head 4 --print-plan
+    nfn train ... --gpus 8                  # re-launches itself under torchrun, one rank per GPU
+    nfn infer --checkpoint runs/a/model_00020000.bin --prompt-tokens 15496,11,995 --max-new-tokens 64
+    nfn inspect-checkpoint runs/a/model_00020000.bin
+    nfn list-templates | nfn list-presets | nfn native-info | nfn dataset-info PATH
+
+Help and the template listing import neither torch nor the kernel library, so they answer
+instantly (the reference's dispatcher makes the same promise, ``cli/nfn.py:322-575``).
+Flag names follow the reference's native trainer (``nfn_gpt2_native_train.cpp:1093-1198``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+
+def _add_train_flags(p: argparse.ArgumentParser) -> None:
+    p.add_argument("--base-model", default="gpt", help="gpt | gpt2 | gpt3 | nanogpt | llama")
+    p.add_argument("--template-name", default="gpt2")
+    p.add_argument("--dataset", default="", help="dataset alias, directory or shard file (empty: synthetic uniform tokens)")
+    p.add_argument("--output-dir", default="")
+    p.add_argument("--batch-size", type=int, default=64)
+    p.add_argument("--seq-len", type=int, default=1024)
+    p.add_argument("--train-batch-tokens", type=int, default=524288)
+    p.add_argument("--n-layer", type=int, default=12)
+    p.add_argument("--n-head", type=int, default=12)
+    p.add_argument("--n-kv-head", type=int, default=0)
+    p.add_argument("--d-model", type=int, default=768)
+    p.add_argument("--d-ff", type=int, default=0)
+    p.add_argument("--vocab-size", type=int, default=50257)
+    p.add_argument("--learning-rate", type=float, default=6e-4)
+    p.add_argument("--lr-schedule", default="cosine", choices=["cosine", "constant"])
+    p.add_argument("--final-lr-fraction", type=float, default=0.0)
+    p.add_argument("--warmup-steps", type=int, default=60)
+    p.add_argument("--lr-schedule-total-steps", type=int, default=0)
+    p.add_argument("--weight-decay", type=float, default=0.1)
+    p.add_argument("--beta1", type=float, default=0.9)
+    p.add_argument("--beta2", type=float, default=0.95)
+    p.add_argument("--eps", type=float, default=1e-8)
+    p.add_argument("--max-grad-norm", type=float, default=1.0)
+    p.add_argument("--max-steps", type=int, default=20000)
+    p.add_argument("--eval-every", type=int, default=5000)
+    p.add_argument("--eval-batches", type=int, default=20)
+    p.add_argument("--train-loss-every", type=int, default=250)
+    p.add_argument("--progress-every", type=int, default=10)
+    p.add_argument("--checkpoint-every", type=int, default=5000)
+    p.add_argument("--seed", type=int, default=1337)
+    p.add_argument("--resume", action="store_true")
+    p.add_argument("--no-cuda-graph", action="store_true")
+    p.add_argument("--gpus", type=int, default=0, help="launch this many ranks on this node (0: stay in this process)")
+    p.add_argument("--print-plan", "--dry-run", dest="print_plan", action="store_true")
+
+
+def _train_config(a):
+    from ..native_train import NativeTrainConfig
+    return NativeTrainConfig(
+        base_model=a.base_model, template_name=a.template_name, dataset=a.dataset, output_dir=a.output_dir, batch_size=a.batch_size,
+        seq_len=a.seq_len, train_batch_tokens=a.train_batch_tokens, n_layer=a.n_layer, n_head=a.n_head, n_kv_head=a.n_kv_head,
+        d_model=a.d_model, d_ff=a.d_ff, vocab_size=a.vocab_size, learning_rate=a.learning_rate, lr_schedule=a.lr_schedule,
+        final_lr_fraction=a.final_lr_fraction, warmup_steps=a.warmup_steps, lr_schedule_total_steps=a.lr_schedule_total_steps,
+        weight_decay=a.weight_decay, beta1=a.beta1, beta2=a.beta2, eps=a.eps, max_grad_norm=a.max_grad_norm, max_steps=a.max_steps,
+        eval_every=a.eval_every, eval_batches=a.eval_batches, train_loss_every=a.train_loss_every, progress_every=a.progress_every,
+        checkpoint_every=a.checkpoint_every, seed=a.seed, resume=a.resume, use_cuda_graph=not a.no_cuda_graph)
+
+
+def cmd_train(a) -> int:
+    if a.print_plan:
+        from ..native_train import training_plan
+        print(json.dumps({"status": "plan", **training_plan(_train_config(a), max(1, a.gpus))}, indent=2))
+        return 0
+    if a.gpus > 1 and "RANK" not in os.environ:
+        # one process per GPU: hand the same command line to the torch launcher
+        import subprocess
+        argv, skip = [], False
+        for x in sys.argv[1:]:
+            if skip:
+                skip = False
+            elif x == "--gpus":
+                skip = True
+            elif not x.startswith("--gpus="):
+                argv.append(x)
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.gpus}", "--master-addr", "127.0.0.1",
+               "--master-port", str(29500 + os.getpid() % 2000), "-m", "neuralfn_b200.cli.nfn", *argv]
+        return subprocess.call(cmd)
+    cfg = _train_config(a)
+    from ..native_train import run_native_training
+    report = run_native_training(cfg)
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(report, default=str))
+    return 0
+
+
+def cmd_infer(a) -> int:
+    from ..checkpoint import read_dense_model
+    from ..serving import EngineConfig, ResidentEngine, Sampling
+    cfg, tensors, sha = read_dense_model(a.checkpoint)
+    eng = ResidentEngine(EngineConfig.gpt2(cfg, max_batch=a.max_batch))
+    eng.load_named_tensors(tensors)
+    prompts = [[int(t) for t in p.split(",") if t] for p in a.prompt_tokens.split(";")]
+    out = eng.generate(prompts, max_new_tokens=a.max_new_tokens,
+                       sampling=Sampling(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p, seed=a.seed),
+                       eos_token=a.eos_token if a.eos_token >= 0 else None)
+    print(json.dumps({"status": "ok", "checkpoint_sha256": sha, "prompts": prompts, "generated": out,
+                      "device_bytes": eng.device_bytes, "kernel_launches": eng.launches}))
+    return 0
+
+
+def cmd_inspect(a) -> int:
+    from ..checkpoint import inspect_dense_model
+    info = inspect_dense_model(a.path)
+    info.pop("config", None)
+    from ..data._rt import sha256_file
+    info["sha256"] = sha256_file(a.path)
+    print(json.dumps({"status": "ok", **info}, indent=2))
+    return 0
+
+
+def cmd_checkpoint_layout(a) -> int:
+    from ..native_train import build_model_config
+    cfg = build_model_config(_train_config(a))
+    off, rows = 1024, []
+    for s in cfg.param_specs():
+        rows.append({"name": s.name, "shape": list(s.shape), "offset": off, "nbytes": 2 * s.numel, "weight_decay": s.decay})
+        off += 2 * s.numel
+    print(json.dumps({"status": "ok", "header_bytes": 1024, "file_bytes": off, "tensors": rows}, indent=2))
+    return 0
+
+
+def cmd_list_templates(_a) -> int:
+    from ..native_templates import GPT_VARIANTS, LLAMA_TEMPLATES
+    print(json.dumps({"gpt": list(GPT_VARIANTS), "llama": list(LLAMA_TEMPLATES)}, indent=2))
+    return 0
+
+
+def cmd_list_presets(_a) -> int:
+    from ..presets import PRESET_BUILDERS
+    print(json.dumps(sorted(PRESET_BUILDERS), indent=2))
+    return 0
+
+
+def cmd_native_info(_a) -> int:
+    from ..ops import _lib
+    info = {"kernel_library": str(_lib.lib_path()), "kernel_library_present": _lib.available(), "target": "sm_100a",
+            "native_families": ["gpt", "gpt2", "gpt3", "nanogpt", "llama"],
+            "fused_collectives": ["dp_reduce_adamw", "ag_gemm", "gemm_rs", "allreduce_resid_norm"]}
+    try:
+        import torch
+        info["cuda_available"] = bool(torch.cuda.is_available())
+        if torch.cuda.is_available():
+            info["device"] = torch.cuda.get_device_name(0)
+            info["device_count"] = torch.cuda.device_count()
+    except Exception as exc:  # pragma: no cover - torch is a hard dependency elsewhere
+        info["torch_error"] = str(exc)
+    print(json.dumps(info, indent=2))
+    return 0
+
+
+def cmd_dataset_info(a) -> int:
+    from ..data import TokenDataset
+    ds = TokenDataset(a.path, allow_train_as_val=True)
+    print(json.dumps(ds.describe(a.seq_len, a.batch_size, a.train_batch_tokens), indent=2))
+    return 0
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="nfn", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="command", required=True)
+    t = sub.add_parser("train", help="native training run (JSON report on stdout)")
+    _add_train_flags(t)
+    t.set_defaults(fn=cmd_train)
+    i = sub.add_parser("infer", help="generate from a dense checkpoint with the resident engine")
+    i.add_argument("--checkpoint", required=True)
+    i.add_argument("--prompt-tokens", required=True, help="comma-separated ids; ';' separates prompts")
+    i.add_argument("--max-new-tokens", type=int, default=144)
+    i.add_argument("--temperature", type=float, default=0.0)
+    i.add_argument("--top-k", type=int, default=0)
+    i.add_argument("--top-p", type=float, default=1.0)
+    i.add_argument("--seed", type=int, default=1337)
+    i.add_argument("--eos-token", type=int, default=-1)
+    i.add_argument("--max-batch", type=int, default=8)
+    i.set_defaults(fn=cmd_infer)
+    c = sub.add_parser("inspect-checkpoint", help="validate and checksum a dense checkpoint")
+    c.add_argument("path")
+    c.set_defaults(fn=cmd_inspect)
+    lay = sub.add_parser("checkpoint-layout", help="tensor table of the checkpoint a configuration would write")
+    _add_train_flags(lay)
+    lay.set_defaults(fn=cmd_checkpoint_layout)
+    sub.add_parser("list-templates").set_defaults(fn=cmd_list_templates)
+    sub.add_parser("list-presets").set_defaults(fn=cmd_list_presets)
+    sub.add_parser("native-info").set_defaults(fn=cmd_native_info)
+    d = sub.add_parser("dataset-info")
+    d.add_argument("path")
+    d.add_argument("--seq-len", type=int, default=1024)
+    d.add_argument("--batch-size", type=int, default=64)
+    d.add_argument("--train-batch-tokens", type=int, default=524288)
+    d.set_defaults(fn=cmd_dataset_info)
+    return ap
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    try:
+        return int(args.fn(args) or 0)
+    except Exception as exc:
+        print(json.dumps({"status": "error", "error": f"{type(exc).__name__}: {exc}"}))
+        return 1
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -37,8 +37,17 @@ struct AttnFwdParams {
   int* status;
 };
 
+// Shared memory one CTA needs (tiles + barriers). With head_dim 64 this is 112 KB + 128 B, so
+// two CTAs share an SM (and its 512 TMEM columns, 256 each): while one CTA's softmax warps
+// work on their S tile the other CTA's MMAs run, which hides most of the QK -> softmax -> PV
+// dependency chain that a single resident CTA exposes.
 template <int D>
-__global__ void __launch_bounds__(ATT_THREADS)
+__host__ __device__ constexpr uint32_t attn_fwd_smem_bytes() {
+  return ATT_BM * D * 2 + 2 * (2 * ATT_BN * D * 2) + ATT_BM * ATT_BN * 2 + 128;
+}
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, (D == 64 ? 2 : 1))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnFwdParams p) {
   constexpr uint32_t Q_BYTES = ATT_BM * D * 2;
@@ -52,6 +61,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
+  {
+    // The launch asks for exactly attn_fwd_smem_bytes<D>(): the dynamic window starts
+    // 1024-aligned on this architecture. Should it ever not, give up cleanly (status word)
+    // rather than run past the allocation.
+    uint32_t dyn;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+    if (static_cast<uint32_t>(smem - smem_raw) + attn_fwd_smem_bytes<D>() > dyn) {
+      if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, NFN_ERR_WAIT_MISC);
+      return;
+    }
+  }
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + Q_BYTES;
   uint8_t* sP = sKV + 2 * KV_STAGE;
@@ -321,7 +341,7 @@ template <int D>
 static int launch_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B,
                            int T, int Hq, int Hkv, int ld_q, int ld_k, int ld_v, int ld_o,
                            int causal, int window, float scale, cudaStream_t st) {
-  constexpr size_t SMEM = ATT_BM * D * 2 + 2 * (2 * ATT_BN * D * 2) + ATT_BM * ATT_BN * 2 + 1024 + 128;
+  constexpr size_t SMEM = attn_fwd_smem_bytes<D>();
   auto kern = attn_fwd_kernel<D>;
   static bool attr[64] = {};
   int dev = 0;

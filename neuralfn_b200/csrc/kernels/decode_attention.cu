@@ -50,7 +50,23 @@ struct DecodeParams {
   int* tickets;
   float* part_ml;
   float* part_o;
+  int* status;
 };
+
+constexpr int DEC_TILE = 32;    // cache positions per shared-memory stage
+constexpr int DEC_STAGES = 4;   // stages in flight per CTA
+
+__device__ __forceinline__ void dec_bulk_g2s(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+template <int HD, int G>
+constexpr size_t decode_smem_bytes() {
+  const size_t ring = (size_t)DEC_STAGES * 2 * DEC_TILE * HD * 2, merge = (size_t)16 * G * (HD + 2) * sizeof(float);
+  return ring > merge ? ring : merge;
+}
 
 template <int CH>
 __device__ __forceinline__ void load_chunk(const __nv_bfloat16* p, float* dst) {
@@ -126,10 +142,13 @@ template <int HD, int G>
 __global__ void __launch_bounds__(128)
 decode_attention_kernel(const DecodeParams p) {
   constexpr int CH = HD / 16, EPL = HD / 8, HALF = HD / 2, NGRP = 16;
-  extern __shared__ float smem[];  // [NGRP][G][HD] acc, then [NGRP][G][2] (m, l)
+  extern __shared__ __align__(128) float smem[];  // stage ring, later [NGRP][G][HD] acc + [NGRP][G][2] (m, l)
   float* sm_acc = smem;
   float* sm_ml = smem + NGRP * G * HD;
   __shared__ int sh_last;
+  __shared__ int sh_abort_store;
+  __shared__ __align__(8) uint64_t sh_full[DEC_STAGES];
+  volatile int* sh_abort_ptr = &sh_abort_store;
 
   const int split = blockIdx.x, b = blockIdx.z;
   const int kvh = blockIdx.y / p.gtiles, gt = blockIdx.y % p.gtiles;
@@ -140,6 +159,12 @@ decode_attention_kernel(const DecodeParams p) {
 
   const int len = p.lengths[b];
   if (len <= 0) return;  // uniform per CTA: empty sequence slot, nothing to do and no ticket needed
+  if (threadIdx.x == 0) {
+    sh_abort_store = 0;
+    for (int s = 0; s < DEC_STAGES; ++s) mbar_init(smem_u32(&sh_full[s]), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
   const int pos = len - 1;
   const int slot_new = pos % p.cap;
   const int n_slots = min(len, p.cap);
@@ -213,25 +238,57 @@ decode_attention_kernel(const DecodeParams p) {
     absorb(kn, vn, grp == 0);
   }
 
+  // The cache rows of this split stream through a ring of shared-memory stages filled by
+  // bulk async copies (a tile of DEC_TILE positions of one head is one contiguous run of
+  // the cache), several tiles ahead of the arithmetic: enough bytes in flight per SM to
+  // cover HBM latency, which per-thread loads at this register budget cannot provide.
   const int per = (n_slots + p.splits - 1) / p.splits;
   const int s_lo = split * per, s_hi = min(n_slots, s_lo + per);
-  for (int s0 = s_lo; s0 < s_hi; s0 += NGRP) {  // trip count is the same for every thread
-    const int s = s0 + grp;
-    const bool valid = s < s_hi && s != slot_new;
-    float kv[EPL], vv[EPL];
-    if (valid) {
-      const __nv_bfloat16* kr = kbase + (long long)s * HD;
-      const __nv_bfloat16* vr = vbase + (long long)s * HD;
-      load_chunk<CH>(kr + sub * CH, kv);
+  const int ntiles = s_hi > s_lo ? (s_hi - s_lo + DEC_TILE - 1) / DEC_TILE : 0;
+  constexpr uint32_t ROW = HD * 2, STAGE = 2 * DEC_TILE * ROW;  // K tile then V tile
+  uint8_t* stage_base = reinterpret_cast<uint8_t*>(smem);
+  auto issue = [&](int t) {  // thread 0 only
+    const int st = t % DEC_STAGES;
+    const int s0 = s_lo + t * DEC_TILE, n = min(DEC_TILE, s_hi - s0);
+    const uint32_t bytes = (uint32_t)n * ROW, bar = smem_u32(&sh_full[st]);
+    mbar_expect_tx(bar, 2 * bytes);
+    dec_bulk_g2s(smem_u32(stage_base + st * STAGE), kbase + (long long)s0 * HD, bytes, bar);
+    dec_bulk_g2s(smem_u32(stage_base + st * STAGE + DEC_TILE * ROW), vbase + (long long)s0 * HD, bytes, bar);
+  };
+  if (threadIdx.x == 0)
+    for (int t = 0; t < min(DEC_STAGES, ntiles); ++t) issue(t);
+  bool alive = true;
+  for (int t = 0; t < ntiles; ++t) {
+    const int st = t % DEC_STAGES;
+    alive = mbar_wait_bounded(smem_u32(&sh_full[st]), (t / DEC_STAGES) & 1, sh_abort_ptr, p.status, NFN_ERR_WAIT_FULL);
+    alive = __syncthreads_and(alive);
+    if (!alive) break;
+    const int s0 = s_lo + t * DEC_TILE;
+    const uint8_t* kt = stage_base + st * STAGE;
+    const uint8_t* vt = kt + DEC_TILE * ROW;
+#pragma unroll
+    for (int r = 0; r < DEC_TILE / NGRP; ++r) {  // trip count is the same for every thread
+      const int row = r * NGRP + grp, s = s0 + row;
+      const bool valid = s < s_hi && s != slot_new;
+      float kv[EPL], vv[EPL];
+      const __nv_bfloat16* kr = reinterpret_cast<const __nv_bfloat16*>(kt + row * ROW);
+      const __nv_bfloat16* vr = reinterpret_cast<const __nv_bfloat16*>(vt + row * ROW);
+      load_chunk<CH>(kr + sub * CH, kv);  // rows past the tile's end hold stale data: masked by `valid`
       load_chunk<CH>(kr + HALF + sub * CH, kv + CH);
       load_chunk<CH>(vr + sub * CH, vv);
       load_chunk<CH>(vr + HALF + sub * CH, vv + CH);
-    } else {
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) kv[i] = vv[i] = 0.f;
+      absorb(kv, vv, valid);
     }
-    absorb(kv, vv, valid);
+    __syncthreads();  // everyone is done with this stage
+    if (threadIdx.x == 0 && t + DEC_STAGES < ntiles) issue(t + DEC_STAGES);
   }
+  if (!alive) {
+    // a copy never arrived: leave without touching the workspace; give copies still in
+    // flight time to land before this CTA's shared memory is handed to another CTA
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    return;
+  }
+  __syncthreads();  // the stage ring is reused below as the merge buffer
 
   // ---- merge the 16 sub-groups of this CTA -------------------------------------------------
 #pragma unroll
@@ -298,14 +355,16 @@ decode_attention_kernel(const DecodeParams p) {
 
 template <int HD, int G>
 static int launch_decode(const DecodeParams& p, cudaStream_t st) {
-  const size_t smem = (size_t)16 * G * (HD + 2) * sizeof(float);
+  constexpr size_t smem = decode_smem_bytes<HD, G>();
   auto kern = decode_attention_kernel<HD, G>;
   if (smem > 48 * 1024) {
-    static bool done = false;  // attribute is per function, set once per process and device-independent in effect
-    if (!done) {
+    static bool done[64] = {};  // per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!done[dev & 63]) {
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return fail(-2, "decode_attention: cannot raise the dynamic shared memory limit");
-      done = true;
+      done[dev & 63] = true;
     }
   }
   dim3 grid(p.splits, p.Hkv * p.gtiles, p.B);
@@ -340,9 +399,10 @@ extern "C" int nfn_decode_attention(const void* qkv, int ld, void* k_cache, void
   const int group = n_q_heads / n_kv_heads, G = group >= 4 ? 4 : (group >= 2 ? 2 : 1), gtiles = (group + G - 1) / G;
   const long long units = (long long)B * n_kv_heads * gtiles;
   if (splits <= 0) {
-    // enough CTAs for ~2 waves, at least 256 cache positions per split
-    const long long want = (2LL * sm_count() + units - 1) / units;
-    splits = (int)std::max<long long>(1, std::min<long long>(want, (cap + 255) / 256));
+    // one full wave at two resident CTAs per SM (rounding down, so no straggler wave), and at
+    // least 128 cache positions per split
+    const long long want = (2LL * sm_count()) / units;
+    splits = (int)std::max<long long>(1, std::min<long long>(want, (cap + 127) / 128));
   }
   splits = min(splits, 64);
   const long long ticket_bytes = ((units * 4 + 255) / 256) * 256;
@@ -366,6 +426,7 @@ extern "C" int nfn_decode_attention(const void* qkv, int ld, void* k_cache, void
   p.tickets = reinterpret_cast<int*>(ws);
   p.part_ml = reinterpret_cast<float*>(ws + ticket_bytes);
   p.part_o = p.part_ml + units * splits * (long long)G * 2;
+  p.status = status_ptr();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (head_dim == 128) return G == 4 ? launch_decode<128, 4>(p, st) : (G == 2 ? launch_decode<128, 2>(p, st) : launch_decode<128, 1>(p, st));
   return G == 4 ? launch_decode<64, 4>(p, st) : (G == 2 ? launch_decode<64, 2>(p, st) : launch_decode<64, 1>(p, st));

@@ -178,6 +178,7 @@ kquant_gemv_kernel(const uint8_t* __restrict__ W1, const uint8_t* __restrict__ W
       *reinterpret_cast<uint4*>(xs + b * xstride + kk) = v;
     }
     __syncthreads();
+#pragma unroll 2  // two super-blocks' worth of weight loads in flight per warp
     for (int kb = 0; kb < kc / 256; ++kb) {
       const long long gblk = (long long)(k0 / 256 + kb);
       int runs[L::kRuns];

@@ -1,0 +1,56 @@
+"""CLI paths that need no GPU (plan, layout, listings, checkpoint inspection) and a GPU
+end-to-end run: shards -> nfn train -> checkpoint -> resume -> nfn infer."""
+import json
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+
+def _nfn(*args, check=True):
+    p = subprocess.run([sys.executable, "-m", "neuralfn_b200.cli.nfn", *args], capture_output=True, text=True, timeout=600)
+    if check:
+        assert p.returncode == 0, p.stdout + p.stderr
+    return p
+
+
+def test_plan_layout_and_listings():
+    plan = json.loads(_nfn("train", "--print-plan", "--batch-size", "16", "--gpus", "8").stdout)
+    assert plan["grad_accum_steps"] == 4 and plan["effective_train_batch_tokens"] == 524288 and plan["parameters"] > 124e6
+    lay = json.loads(_nfn("checkpoint-layout", "--n-layer", "2").stdout)
+    assert lay["tensors"][0]["name"] == "wte" and lay["tensors"][0]["offset"] == 1024
+    assert lay["file_bytes"] == 1024 + sum(t["nbytes"] for t in lay["tensors"])
+    assert "gpt2_qknorm" in json.loads(_nfn("list-templates").stdout)["gpt"]
+    assert len(json.loads(_nfn("list-presets").stdout)) >= 67
+    assert json.loads(_nfn("native-info").stdout)["target"] == "sm_100a"
+    bad = _nfn("train", "--base-model", "rwkv", "--print-plan", check=False)
+    assert bad.returncode == 1 and json.loads(bad.stdout)["status"] == "error"
+
+
+@pytest.mark.gpu
+def test_train_resume_and_infer_end_to_end(tmp_path):
+    from neuralfn_b200.data import write_legacy_shard
+    rng = np.random.default_rng(0)
+    data = tmp_path / "data"
+    data.mkdir()
+    period = rng.integers(0, 300, 97)
+    write_legacy_shard(data / "fineweb_train_000000.bin", np.tile(period, 700), with_header=True)
+    write_legacy_shard(data / "fineweb_val_000000.bin", np.tile(period, 60))
+    out = tmp_path / "run"
+    common = ["train", "--base-model", "gpt", "--template-name", "gpt2_qknorm", "--dataset", str(data), "--output-dir", str(out),
+              "--batch-size", "4", "--seq-len", "64", "--train-batch-tokens", "512", "--n-layer", "2", "--n-head", "2", "--d-model", "128",
+              "--vocab-size", "300", "--learning-rate", "3e-3", "--warmup-steps", "2", "--eval-every", "10", "--eval-batches", "2",
+              "--train-loss-every", "5", "--checkpoint-every", "10", "--progress-every", "0"]
+    r1 = json.loads(_nfn(*common, "--max-steps", "10").stdout.strip().splitlines()[-1])
+    assert r1["status"] == "ok" and r1["plan"]["grad_accum_steps"] == 2 and r1["steps"] == 10
+    assert r1["train_losses"][-1]["loss"] < r1["train_losses"][0]["loss"]
+    assert r1["train_compute_tokens_per_second"] > 0 and (out / "DONE_00000010").exists()
+    r2 = json.loads(_nfn(*common, "--max-steps", "20", "--resume").stdout.strip().splitlines()[-1])
+    assert r2["resumed_from_step"] == 10 and r2["steps"] == 10 and (out / "model_00000020.bin").exists()
+    assert r2["validation"]["losses"][-1]["loss"] < r1["validation"]["losses"][-1]["loss"] + 0.05
+    info = json.loads(_nfn("inspect-checkpoint", str(out / "model_00000020.bin")).stdout)
+    assert info["num_layers"] == 2 and len(info["sha256"]) == 64
+    gen = json.loads(_nfn("infer", "--checkpoint", str(out / "model_00000020.bin"), "--prompt-tokens",
+                          ",".join(map(str, period[:12])), "--max-new-tokens", "8").stdout.strip().splitlines()[-1])
+    assert gen["status"] == "ok" and len(gen["generated"][0]) == 8
