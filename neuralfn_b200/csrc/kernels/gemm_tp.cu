@@ -63,6 +63,10 @@ struct TpParams {
   int ld_out;
   const __nv_bfloat16* resid;
   int ld_resid;
+  // GROUPED: m tile -> group (expert) table and the number of live m tiles, both written by
+  // an earlier kernel on the stream; B is a [groups, N, K] stack read through a 3-D map
+  const int* tile_group;
+  const int* num_m_tiles_dev;
   int* status;
 };
 
@@ -119,6 +123,12 @@ struct TileCoord {
 };
 __device__ __forceinline__ TileCoord tile_coord(const TpParams& p, int t, int BN) {
   TileCoord c;
+  if (p.mode == NFN_TP_GROUPED) {
+    c.mt = t / p.tiles_n;
+    c.nt = t % p.tiles_n;
+    c.owner = p.rank;
+    return c;
+  }
   if (p.mode == NFN_TP_AG_B) {
     const int per = p.rows_per_rank / BN;  // n tiles per rank
     const int ln = t / p.tiles_m;
@@ -243,7 +253,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 
   // ========================================================================= GEMM CTAs ==
   const uint32_t tmem_base = *tmem_slot;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int live_m_tiles = (p.mode == NFN_TP_GROUPED) ? min(p.tiles_m, max(0, *p.num_m_tiles_dev)) : p.tiles_m;
+  const int num_tiles = live_m_tiles * p.tiles_n;
   const int total_kb = (p.k + TP_BK - 1) / TP_BK;
   const int first = (int)blockIdx.x - p.n_copy, stride = (int)gridDim.x - p.n_copy;
 
@@ -253,6 +264,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       bool ok = true;
       for (int t = first; t < num_tiles && ok; t += stride) {
         const TileCoord tc = tile_coord(p, t, BN);
+        const int group = (p.mode == NFN_TP_GROUPED) ? p.tile_group[tc.mt] : 0;
         if (p.mode != NFN_TP_RS && tc.owner != p.rank) {
           // wait for the gathered block(s) this tile reads
           const int blocks = (p.mode == NFN_TP_AG_B) ? BN / TP_BM : 1;
@@ -271,7 +283,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
           mbar_expect_tx(fb, STAGE_BYTES);
           tma_load_2d(sa, &tma_a, fb, kb * TP_BK, tc.mt * TP_BM);
-          tma_load_2d(sa + A_BYTES, &tma_b, fb, kb * TP_BK, tc.nt * BN);
+          if (p.mode == NFN_TP_GROUPED) tma_load_3d(sa + A_BYTES, &tma_b, fb, kb * TP_BK, tc.nt * BN, group);
+          else tma_load_2d(sa + A_BYTES, &tma_b, fb, kb * TP_BK, tc.nt * BN);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -475,7 +488,13 @@ static int launch_tp(const nfn_gemm_tp_args& a, cudaStream_t stream) {
   CUtensorMap ta, tb;
   TpMaps maps;
   if (!make_tmap_2d(&ta, a.a, 2, (uint64_t)a.k, (uint64_t)a.m, (uint64_t)a.lda, TP_BK, TP_BM, 128)) return -3;
-  if (!make_tmap_2d(&tb, a.b, 2, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.ldb, TP_BK, BN, 128)) return -3;
+  if (a.mode == NFN_TP_GROUPED) {
+    if (!make_tmap_3d(&tb, a.b, 2, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.groups, (uint64_t)a.ldb, (uint64_t)a.ldb * a.n, TP_BK, BN, 1, 128)) return -3;
+    p.tile_group = a.tile_group;
+    p.num_m_tiles_dev = a.num_m_tiles_dev;
+  } else if (!make_tmap_2d(&tb, a.b, 2, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.ldb, TP_BK, BN, 128)) {
+    return -3;
+  }
   if (a.mode == NFN_TP_RS) {
     const long long slot_elems = (long long)a.rows_per_rank * a.n;
     for (int r = 0; r < a.world; ++r) {
@@ -497,7 +516,7 @@ static int launch_tp(const nfn_gemm_tp_args& a, cudaStream_t stream) {
     p.local_buf = local;
     for (int r = 0; r < a.world; ++r)
       p.peer_src[r] = static_cast<const unsigned char*>(a.peer_bufs[r]) + (long long)r * a.rows_per_rank * gathered_ld * 2;
-    if (a.world > 1) p.n_copy = a.n_copy > 0 ? a.n_copy : 16;
+    if (a.world > 1 && a.mode != NFN_TP_GROUPED) p.n_copy = a.n_copy > 0 ? a.n_copy : 16;
   }
   int grid = std::min(sms, tiles + p.n_copy);
   if (grid <= p.n_copy) grid = p.n_copy + 1;
@@ -513,7 +532,15 @@ extern "C" int nfn_gemm_tp(const nfn_gemm_tp_args* args, nfn_stream_t stream_) {
   if (!args) return fail(-1, "gemm_tp: null args");
   const nfn_gemm_tp_args& a = *args;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (a.mode != NFN_TP_AG_A && a.mode != NFN_TP_AG_B && a.mode != NFN_TP_RS) return fail(-1, "gemm_tp: unknown mode");
+  if (a.mode != NFN_TP_AG_A && a.mode != NFN_TP_AG_B && a.mode != NFN_TP_RS && a.mode != NFN_TP_GROUPED) return fail(-1, "gemm_tp: unknown mode");
+  if (a.mode == NFN_TP_GROUPED) {
+    // grouped GEMM: rows of A are sorted by group and padded to whole 128-row tiles; tile t
+    // multiplies with B[tile_group[t]]. Single rank, no flags.
+    if (a.m <= 0 || a.n <= 0 || a.k <= 0 || (a.k & 7) || (a.n & 7) || (a.lda & 7) || (a.ldb & 7) || (a.ldc & 7)) return fail(-1, "gemm_tp: grouped sizes and leading dimensions must be multiples of 8");
+    if (!a.a || !a.b || !a.c || !a.tile_group || !a.num_m_tiles_dev || a.groups <= 0) return fail(-1, "gemm_tp: grouped mode needs a, b, c, tile_group, num_m_tiles_dev and groups");
+    if (a.m % TP_BM) return fail(-1, "gemm_tp: grouped row capacity must be a multiple of 128");
+    return (a.n >= 2048) ? launch_tp<256, 4>(a, stream) : launch_tp<128, 6>(a, stream);
+  }
   if (a.m <= 0 || a.n <= 0 || a.k <= 0) return fail(-1, "gemm_tp: empty problem");
   if (a.world < 1 || a.world > TP_MAX_WORLD || a.rank < 0 || a.rank >= a.world) return fail(-1, "gemm_tp: bad rank / world (at most 8 ranks)");
   if ((a.k & 7) || (a.n & 7) || (a.lda & 7) || (a.ldb & 7)) return fail(-1, "gemm_tp: K, N and leading dimensions must be multiples of 8");

@@ -77,7 +77,10 @@ int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream);
 // ctrl_*: per-rank control block of ctrl_ints int32 (zero-initialised once): [0, 8) flags
 // written by peers, [16] ticket, [32, 32 + blocks) block flags. epoch must grow by one per
 // call on every rank alike; the value used is epoch + *epoch_dev (epoch_dev may be NULL).
-enum { NFN_TP_AG_A = 0, NFN_TP_AG_B = 1, NFN_TP_RS = 2 };
+//   NFN_TP_GROUPED: single-rank grouped GEMM (mixture-of-experts): A rows sorted by group and
+//                padded to 128-row tiles, B = [groups, N, K]; tile t uses B[tile_group[t]];
+//                only the first *num_m_tiles_dev tiles are computed (device-side count).
+enum { NFN_TP_AG_A = 0, NFN_TP_AG_B = 1, NFN_TP_RS = 2, NFN_TP_GROUPED = 3 };
 typedef struct {
   int mode;
   const void* a; const void* b; void* c;
@@ -90,6 +93,7 @@ typedef struct {
   int* ctrl_local; int* ctrl_peer[8]; int ctrl_ints;
   void* out; int ld_out; const void* resid; int ld_resid;   // NFN_TP_RS only
   int n_copy;                                               // gather CTAs (0 = default 16)
+  const int* tile_group; const int* num_m_tiles_dev; int groups;   // NFN_TP_GROUPED only
 } nfn_gemm_tp_args;
 int nfn_gemm_tp(const nfn_gemm_tp_args* args, nfn_stream_t stream);
 

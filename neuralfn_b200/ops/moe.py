@@ -1,0 +1,116 @@
+"""Mixture-of-experts feed-forward on the sm_100a kernels: router GEMM (fp32 logits) ->
+top-k routing -> expert-sorted permutation -> grouped tcgen05 GEMM (gate|up) -> SwiGLU ->
+grouped GEMM (down) -> weighted combine. No host synchronisation anywhere: the number of
+live tiles is read by the grouped GEMM from device memory.
+
+Weights: ``w_router`` [E, d], ``w_gate_up`` [E, 2F, d] (gate rows then up rows per expert),
+``w_down`` [E, d, F], all bf16. Matches the math of the tensor-runtime stages
+``router_topk`` + ``grouped_swiglu_experts`` (reference ``torch_backend.py`` MoE stages and
+``kernels.cu:12612-12862``).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from . import _lib
+from .gemm import gemm
+from .infer import swiglu_forward
+
+__all__ = ["MoEWorkspace", "moe_forward", "moe_reference"]
+
+GROUPED = 3
+
+
+def _p(t):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _st():
+    return c_void_p(_lib.stream_ptr())
+
+
+class MoEWorkspace:
+    """Buffers for up to ``max_tokens`` tokens (worst-case padded row capacity)."""
+
+    def __init__(self, max_tokens: int, n_experts: int, top_k: int, d_model: int, d_ff: int, device) -> None:
+        cap = (max_tokens * top_k + n_experts * 127 + 127) // 128 * 128
+        self.capacity_rows, self.max_tiles = cap, cap // 128
+        i32 = dict(dtype=torch.int32, device=device)
+        self.logits = torch.empty(max_tokens, n_experts, dtype=torch.float32, device=device)
+        self.topk_idx = torch.empty(max_tokens, top_k, **i32)
+        self.topk_w = torch.empty(max_tokens, top_k, dtype=torch.float32, device=device)
+        self.counts = torch.zeros(n_experts, **i32)
+        self.offsets = torch.zeros(n_experts + 1, **i32)
+        self.cursor = torch.zeros(n_experts, **i32)
+        self.tile_expert = torch.zeros(self.max_tiles, **i32)
+        self.plan = torch.zeros(2, **i32)
+        self.row_of = torch.empty(max_tokens * top_k, **i32)
+        bf = dict(dtype=torch.bfloat16, device=device)
+        self.xs = torch.zeros(cap, d_model, **bf)
+        self.h = torch.empty(cap, 2 * d_ff, **bf)
+        self.a = torch.empty(cap, d_ff, **bf)
+        self.ys = torch.empty(cap, d_model, **bf)
+
+
+def _grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ws: MoEWorkspace) -> None:
+    from ..parallel.tp import GemmTpArgs
+    E, N, K = w.shape
+    args = GemmTpArgs()
+    args.mode = GROUPED
+    args.a, args.b, args.c = a.data_ptr(), w.data_ptr(), out.data_ptr()
+    args.m, args.n, args.k = a.shape[0], N, K
+    args.lda, args.ldb, args.ldc = a.stride(0), K, out.stride(0)
+    args.tile_group, args.num_m_tiles_dev, args.groups = ws.tile_expert.data_ptr(), ws.plan.data_ptr(), E
+    _lib.check(_lib.load().nfn_gemm_tp(ctypes.byref(args), _st()), "nfn_gemm_tp(grouped)")
+
+
+def moe_forward(x: torch.Tensor, w_router: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, top_k: int, ws: MoEWorkspace, *,
+                score_fn: str = "softmax", norm_topk: bool = True, route_scale: float = 1.0, resid: torch.Tensor | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """x bf16 [T, d] -> bf16 [T, d] (+ resid)."""
+    T, d = x.shape
+    E, F2, _ = w_gate_up.shape
+    F = F2 // 2
+    L = _lib.load()
+    gemm(x, w_router, out=ws.logits[:T], out_dtype=torch.float32)
+    ws.counts.zero_()
+    _lib.check(L.nfn_moe_route(_p(ws.logits), c_int(ws.logits.stride(0)), c_int(T), c_int(E), c_int(top_k), c_int(1 if score_fn == "sigmoid" else 0),
+                               c_int(int(norm_topk)), c_float(route_scale), _p(ws.topk_idx), _p(ws.topk_w), _p(ws.counts), _st()), "nfn_moe_route")
+    _lib.check(L.nfn_moe_plan(_p(ws.counts), c_int(E), c_int(ws.max_tiles), _p(ws.offsets), _p(ws.cursor), _p(ws.tile_expert), _p(ws.plan), _st()),
+               "nfn_moe_plan")
+    _lib.check(L.nfn_moe_permute(_p(x), c_int(x.stride(0)), c_int(T), c_int(top_k), c_int(d), _p(ws.topk_idx), _p(ws.offsets), _p(ws.cursor),
+                                 c_int(ws.capacity_rows), _p(ws.xs), _p(ws.row_of), _st()), "nfn_moe_permute")
+    _grouped_gemm(ws.xs, w_gate_up, ws.h, ws)
+    swiglu_forward(ws.h, F, out=ws.a)
+    _grouped_gemm(ws.a, w_down, ws.ys, ws)
+    out = torch.empty(T, d, dtype=torch.bfloat16, device=x.device) if out is None else out
+    _lib.check(L.nfn_moe_combine(_p(ws.ys), c_int(d), c_int(T), c_int(top_k), _p(ws.row_of), _p(ws.topk_w), _p(resid),
+                                 c_int(0 if resid is None else resid.stride(0)), _p(out), c_int(out.stride(0)), _st()), "nfn_moe_combine")
+    return out
+
+
+def moe_reference(x, w_router, w_gate_up, w_down, top_k: int, *, score_fn: str = "softmax", norm_topk: bool = True,
+                  route_scale: float = 1.0, resid=None) -> torch.Tensor:
+    """fp32 PyTorch oracle of ``moe_forward`` (dense loop over experts)."""
+    xf = x.float()
+    logits = xf @ w_router.float().T
+    scores = torch.sigmoid(logits) if score_fn == "sigmoid" else torch.softmax(logits, -1)
+    w, idx = scores.topk(top_k, dim=-1)
+    if norm_topk:
+        w = w / w.sum(-1, keepdim=True)
+    w = w * route_scale
+    F = w_gate_up.shape[1] // 2
+    out = torch.zeros_like(xf)
+    for e in range(w_gate_up.shape[0]):
+        sel = (idx == e)
+        rows = sel.any(-1).nonzero().flatten()
+        if rows.numel() == 0:
+            continue
+        h = xf[rows] @ w_gate_up[e].float().T
+        a = torch.nn.functional.silu(h[:, :F]) * h[:, F:]
+        y = a @ w_down[e].float().T
+        out[rows] += y * (w[rows] * sel[rows]).sum(-1, keepdim=True)
+    return out + (resid.float() if resid is not None else 0)

@@ -41,7 +41,8 @@ class GemmTpArgs(ctypes.Structure):
                 ("rank", c_int), ("world", c_int), ("rows_per_rank", c_int),
                 ("epoch", c_int), ("epoch_dev", c_void_p),
                 ("peer_bufs", c_void_p * 8), ("ctrl_local", c_void_p), ("ctrl_peer", c_void_p * 8), ("ctrl_ints", c_int),
-                ("out", c_void_p), ("ld_out", c_int), ("resid", c_void_p), ("ld_resid", c_int), ("n_copy", c_int)]
+                ("out", c_void_p), ("ld_out", c_int), ("resid", c_void_p), ("ld_resid", c_int), ("n_copy", c_int),
+                ("tile_group", c_void_p), ("num_m_tiles_dev", c_void_p), ("groups", c_int)]
 
 
 class _Symmetric:
