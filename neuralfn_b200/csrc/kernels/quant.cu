@@ -11,15 +11,16 @@
 // even column, as in the reference's torch_backend.py:1060-1072), one fp32 absmax per group
 // of 64 weights.
 //
-// Skinny product: a CTA of 8 warps owns 32 output rows; the activations of up to 8 batch
-// rows are staged once per CTA in shared memory as bf16, K-chunk by K-chunk, and every warp
-// keeps 4 weight rows in flight so one shared-memory read of x feeds 4 rows. Each lane
-// decodes 8 weights of a super-block with one or two small loads. Optional second weight
-// matrix gives the gated form silu(W1 x) * (W2 x) in the same pass.
+// Skinny product: a CTA of 8 warps owns 32 output rows whose quantised weights stream through
+// a ring of bulk-copied shared-memory stages; the activations of up to 8 batch rows stay in
+// shared memory; one warp multiplies one row, every lane decoding 8 weights per super-block.
+// An optional second weight matrix gives the gated form silu(W1 x) * (W2 x) in the same pass.
 //
 // The reference's counterparts: glimmer_k_mmq.cu (fused K-quant products),
 // kernels.cu:1324-2015 (dequantisation), torch_backend.py:990-1097 (NF4 LoRA linear).
 #include <cuda_fp16.h>
+
+#include <algorithm>
 
 #include "common.h"
 #include "nfn_kernels.h"
@@ -145,119 +146,167 @@ dequant_nf4_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ 
 }
 
 // ---- skinny product ---------------------------------------------------------------------------
-constexpr int GEMV_WARPS = 8, GEMV_ROWS_PER_WARP = 4, GEMV_ROWS = GEMV_WARPS * GEMV_ROWS_PER_WARP;
-constexpr int GEMV_KCHUNK = 4096;  // activations staged per pass: BT * 4096 * 2 bytes (64 KB at BT = 8)
+// A CTA owns GEMV_ROWS_CTA consecutive output rows. Their quantised weights are one
+// contiguous byte range (rows are stored back to back), which streams through a ring of
+// shared-memory stages - GEMV_STAGE_ROWS rows per stage, one bulk async copy each - so tens of
+// kilobytes are in flight per SM regardless of how few registers the math needs. The
+// activations of all batch rows sit in shared memory for the whole kernel; warp w of a stage
+// multiplies row w: every lane decodes 8 weights of each super-block from shared memory.
+constexpr int GEMV_WARPS = 8, GEMV_STAGE_ROWS = GEMV_WARPS, GEMV_ROWS_CTA = 32;
+
+__device__ __forceinline__ void gemv_bulk_g2s(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
+               : "memory");
+}
 
 template <class L, int BT, bool GATED>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 kquant_gemv_kernel(const uint8_t* __restrict__ W1, const uint8_t* __restrict__ W2, const __nv_bfloat16* __restrict__ x, int ldx,
                    __nv_bfloat16* __restrict__ y, int ldy, const __nv_bfloat16* __restrict__ bias,
-                   const __nv_bfloat16* __restrict__ resid, int ld_resid, int B, int N, int K) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [BT][xstride]
-  const int xstride = min(GEMV_KCHUNK, K);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row0 = blockIdx.x * GEMV_ROWS + warp * GEMV_ROWS_PER_WARP;
+                   const __nv_bfloat16* __restrict__ resid, int ld_resid, int B, int N, int K, int n_stages, int* status) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full[4];
+  __shared__ int sh_abort;
   const int kblocks = K / 256;
+  const uint32_t row_bytes = (uint32_t)kblocks * L::kBytes;
+  const uint32_t stage_bytes = ((GEMV_STAGE_ROWS * row_bytes + 127u) / 128u) * 128u;
   constexpr int NM = GATED ? 2 : 1;
-  float acc[NM][GEMV_ROWS_PER_WARP][BT];
-#pragma unroll
-  for (int m = 0; m < NM; ++m)
-#pragma unroll
-    for (int r = 0; r < GEMV_ROWS_PER_WARP; ++r)
-#pragma unroll
-      for (int b = 0; b < BT; ++b) acc[m][r][b] = 0.f;
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [BT][K]
+  unsigned char* ring = smem_raw + (((size_t)BT * K * 2 + 127) / 128) * 128;  // [n_stages][NM][stage_bytes]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * GEMV_ROWS_CTA;
+  const int rows_cta = min(GEMV_ROWS_CTA, N - row0);
+  const int n_iters = (rows_cta + GEMV_STAGE_ROWS - 1) / GEMV_STAGE_ROWS;
 
-  for (int k0 = 0; k0 < K; k0 += GEMV_KCHUNK) {
-    const int kc = min(GEMV_KCHUNK, K - k0);
-    __syncthreads();
-    for (int i = threadIdx.x * 8; i < BT * kc; i += blockDim.x * 8) {
-      const int b = i / kc, kk = i % kc;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (b < B) v = *reinterpret_cast<const uint4*>(x + (long long)b * ldx + k0 + kk);
-      *reinterpret_cast<uint4*>(xs + b * xstride + kk) = v;
+  if (threadIdx.x == 0) {
+    sh_abort = 0;
+    for (int s = 0; s < n_stages; ++s) mbar_init(smem_u32(&full[s]), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  auto issue = [&](int it) {  // thread 0: one bulk copy per weight matrix (16-byte granules; a sub-16-byte tail is copied by hand)
+    const int st = it % n_stages;
+    const int r = row0 + it * GEMV_STAGE_ROWS, rows = min(GEMV_STAGE_ROWS, row0 + rows_cta - r);
+    const uint32_t bytes = (uint32_t)rows * row_bytes, bulk = bytes & ~15u;
+    const uint32_t bar = smem_u32(&full[st]);
+    mbar_expect_tx(bar, NM * bulk);
+    gemv_bulk_g2s(smem_u32(ring + ((size_t)st * NM) * stage_bytes), W1 + (size_t)r * row_bytes, bulk, bar);
+    if (GATED) gemv_bulk_g2s(smem_u32(ring + ((size_t)st * NM + 1) * stage_bytes), W2 + (size_t)r * row_bytes, bulk, bar);
+  };
+  if (threadIdx.x == 0)
+    for (int it = 0; it < min(n_stages, n_iters); ++it) issue(it);
+  // activations: all batch rows, zero-filled beyond B
+  for (int i = threadIdx.x * 8; i < BT * K; i += blockDim.x * 8) {
+    const int b = i / K, kk = i % K;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (b < B) v = *reinterpret_cast<const uint4*>(x + (long long)b * ldx + kk);
+    *reinterpret_cast<uint4*>(xs + (size_t)b * K + kk) = v;
+  }
+  __syncthreads();
+
+  for (int it = 0; it < n_iters; ++it) {
+    const int st = it % n_stages;
+    const int r = row0 + it * GEMV_STAGE_ROWS, rows = min(GEMV_STAGE_ROWS, row0 + rows_cta - r);
+    bool ok = mbar_wait_bounded(smem_u32(&full[st]), (it / n_stages) & 1, &sh_abort, status, NFN_ERR_WAIT_FULL);
+    ok = __syncthreads_and(ok);
+    if (!ok) {
+      for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let copies in flight land before the CTA goes away
+      return;
     }
-    __syncthreads();
-#pragma unroll 2  // two super-blocks' worth of weight loads in flight per warp
-    for (int kb = 0; kb < kc / 256; ++kb) {
-      const long long gblk = (long long)(k0 / 256 + kb);
-      int runs[L::kRuns];
-      float w[NM][GEMV_ROWS_PER_WARP][8];
-#pragma unroll
-      for (int r = 0; r < GEMV_ROWS_PER_WARP; ++r) {
-        const int row = min(row0 + r, N - 1);
-        L::decode(W1 + ((long long)row * kblocks + gblk) * L::kBytes, lane, w[0][r], runs);
-        if (GATED) L::decode(W2 + ((long long)row * kblocks + gblk) * L::kBytes, lane, w[NM - 1][r], runs);
+    unsigned char* w1s = ring + ((size_t)st * NM) * stage_bytes;
+    unsigned char* w2s = w1s + stage_bytes;
+    {  // tail bytes the 16-byte bulk granularity left out (at most 15 per matrix)
+      const uint32_t bytes = (uint32_t)rows * row_bytes, bulk = bytes & ~15u;
+      if (threadIdx.x < bytes - bulk) {
+        w1s[bulk + threadIdx.x] = W1[(size_t)r * row_bytes + bulk + threadIdx.x];
+        if (GATED) w2s[bulk + threadIdx.x] = W2[(size_t)r * row_bytes + bulk + threadIdx.x];
       }
+      if (bytes != bulk) __syncthreads();
+    }
+    if (warp < rows) {
+      float acc[NM][BT];
 #pragma unroll
-      for (int b = 0; b < BT; ++b) {
-        float xv[8];
-        const __nv_bfloat16* xr = xs + b * xstride + kb * 256;
+      for (int m = 0; m < NM; ++m)
 #pragma unroll
-        for (int r = 0; r < L::kRuns; ++r) {
-          if (L::kRunLen == 4) {
-            const uint2 u = *reinterpret_cast<const uint2*>(xr + runs[r]);
-            const float2 p0 = unpack_bf16x2(u.x), p1 = unpack_bf16x2(u.y);
-            xv[r * 4] = p0.x; xv[r * 4 + 1] = p0.y; xv[r * 4 + 2] = p1.x; xv[r * 4 + 3] = p1.y;
-          } else {
-            const float2 p0 = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(xr + runs[r]));
-            xv[r * 2] = p0.x; xv[r * 2 + 1] = p0.y;
+        for (int b = 0; b < BT; ++b) acc[m][b] = 0.f;
+      const unsigned char* wr1 = w1s + (size_t)warp * row_bytes;
+      const unsigned char* wr2 = w2s + (size_t)warp * row_bytes;
+#pragma unroll 2
+      for (int kb = 0; kb < kblocks; ++kb) {
+        int runs[L::kRuns];
+        float w[NM][8];
+        L::decode(wr1 + (size_t)kb * L::kBytes, lane, w[0], runs);
+        if (GATED) L::decode(wr2 + (size_t)kb * L::kBytes, lane, w[NM - 1], runs);
+#pragma unroll
+        for (int b = 0; b < BT; ++b) {
+          float xv[8];
+          const __nv_bfloat16* xr = xs + (size_t)b * K + kb * 256;
+#pragma unroll
+          for (int q = 0; q < L::kRuns; ++q) {
+            if (L::kRunLen == 4) {
+              const uint2 u = *reinterpret_cast<const uint2*>(xr + runs[q]);
+              const float2 p0 = unpack_bf16x2(u.x), p1 = unpack_bf16x2(u.y);
+              xv[q * 4] = p0.x; xv[q * 4 + 1] = p0.y; xv[q * 4 + 2] = p1.x; xv[q * 4 + 3] = p1.y;
+            } else {
+              const float2 p0 = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(xr + runs[q]));
+              xv[q * 2] = p0.x; xv[q * 2 + 1] = p0.y;
+            }
+          }
+#pragma unroll
+          for (int m = 0; m < NM; ++m) {
+            float s = acc[m][b];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s = fmaf(w[m][i], xv[i], s);
+            acc[m][b] = s;
           }
         }
+      }
 #pragma unroll
-        for (int m = 0; m < NM; ++m)
+      for (int m = 0; m < NM; ++m)
 #pragma unroll
-          for (int r = 0; r < GEMV_ROWS_PER_WARP; ++r) {
-            float s = acc[m][r][b];
+        for (int b = 0; b < BT; ++b) {
+          float s = acc[m][b];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) s = fmaf(w[m][r][i], xv[i], s);
-            acc[m][r][b] = s;
-          }
+          for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          acc[m][b] = s;
+        }
+      if (lane == 0) {
+        const int row = r + warp;
+#pragma unroll
+        for (int b = 0; b < BT; ++b) {
+          if (b >= B) continue;
+          float v = acc[0][b];
+          if (GATED) v = silu_f(v) * acc[NM - 1][b];
+          if (bias) v += __bfloat162float(bias[row]);
+          if (resid) v += __bfloat162float(resid[(long long)b * ld_resid + row]);
+          y[(long long)b * ldy + row] = __float2bfloat16(v);
+        }
       }
     }
-  }
-#pragma unroll
-  for (int m = 0; m < NM; ++m)
-#pragma unroll
-    for (int r = 0; r < GEMV_ROWS_PER_WARP; ++r)
-#pragma unroll
-      for (int b = 0; b < BT; ++b) {
-        float s = acc[m][r][b];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        acc[m][r][b] = s;
-      }
-  if (lane == 0) {
-#pragma unroll
-    for (int r = 0; r < GEMV_ROWS_PER_WARP; ++r) {
-      const int row = row0 + r;
-      if (row >= N) continue;
-#pragma unroll
-      for (int b = 0; b < BT; ++b) {
-        if (b >= B) continue;
-        float v = acc[0][r][b];
-        if (GATED) v = silu_f(v) * acc[NM - 1][r][b];
-        if (bias) v += __bfloat162float(bias[row]);
-        if (resid) v += __bfloat162float(resid[(long long)b * ld_resid + row]);
-        y[(long long)b * ldy + row] = __float2bfloat16(v);
-      }
-    }
+    __syncthreads();  // everyone is done with this stage
+    if (threadIdx.x == 0 && it + n_stages < n_iters) issue(it + n_stages);
   }
 }
 
 template <class L, int BT>
 static int launch_gemv(const void* w1, const void* w2, const void* x, int ldx, void* y, int ldy, const void* bias, const void* resid,
                        int ld_resid, int B, int N, int K, cudaStream_t st) {
-  const size_t smem = (size_t)BT * std::min(GEMV_KCHUNK, K) * 2;
-  const dim3 grid((N + GEMV_ROWS - 1) / GEMV_ROWS);
+  const int nm = w2 ? 2 : 1;
+  const size_t x_bytes = (((size_t)BT * K * 2 + 127) / 128) * 128;
+  const size_t stage = ((((size_t)GEMV_STAGE_ROWS * (K / 256) * L::kBytes) + 127) / 128) * 128 * nm;
+  const size_t budget = 200 * 1024;
+  if (x_bytes + 2 * stage > budget) return fail(-1, "kquant_gemv: K too large for the shared-memory plan (split the batch or use the dequantised GEMM path)");
+  const int n_stages = (int)std::min<size_t>(4, (budget - x_bytes) / stage);
+  const size_t smem = x_bytes + (size_t)n_stages * stage;
+  const dim3 grid((N + GEMV_ROWS_CTA - 1) / GEMV_ROWS_CTA);
   auto run = [&](auto kern) -> int {
-    if (smem > 48 * 1024 &&
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)BT * GEMV_KCHUNK * 2)) != cudaSuccess)
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget) != cudaSuccess)
       return fail(-2, "kquant_gemv: cannot raise the dynamic shared memory limit");
     kern<<<grid, GEMV_WARPS * 32, smem, st>>>(static_cast<const uint8_t*>(w1), static_cast<const uint8_t*>(w2),
                                              static_cast<const __nv_bfloat16*>(x), ldx, static_cast<__nv_bfloat16*>(y), ldy,
                                              static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(resid),
-                                             ld_resid, B, N, K);
+                                             ld_resid, B, N, K, n_stages, status_ptr());
     return launch_check("kquant_gemv", 1);
   };
   return w2 ? run(kquant_gemv_kernel<L, BT, true>) : run(kquant_gemv_kernel<L, BT, false>);
@@ -330,15 +379,15 @@ extern "C" int nfn_kquant_gemv(int qtype, const void* w1, const void* w2, const 
   if (ldy < N || (resid && ld_resid < N)) return fail(-1, "kquant_gemv: output / residual stride smaller than N");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (qtype == NFN_QTYPE_Q4_K) {
-    if (reinterpret_cast<uintptr_t>(w1) % 4 || reinterpret_cast<uintptr_t>(w2) % 4) return fail(-1, "kquant_gemv: Q4_K blocks must be 4-byte aligned");
+    if (reinterpret_cast<uintptr_t>(w1) % 16 || reinterpret_cast<uintptr_t>(w2) % 16) return fail(-1, "kquant_gemv: weight matrices must be 16-byte aligned");
     return dispatch_gemv<Q4KLane>(w1, w2, x, ldx, y, ldy, bias, resid, ld_resid, B, N, K, st);
   }
   if (qtype == NFN_QTYPE_Q5_K) {
-    if (reinterpret_cast<uintptr_t>(w1) % 4 || reinterpret_cast<uintptr_t>(w2) % 4) return fail(-1, "kquant_gemv: Q5_K blocks must be 4-byte aligned");
+    if (reinterpret_cast<uintptr_t>(w1) % 16 || reinterpret_cast<uintptr_t>(w2) % 16) return fail(-1, "kquant_gemv: weight matrices must be 16-byte aligned");
     return dispatch_gemv<Q5KLane>(w1, w2, x, ldx, y, ldy, bias, resid, ld_resid, B, N, K, st);
   }
   if (qtype == NFN_QTYPE_Q6_K) {
-    if (reinterpret_cast<uintptr_t>(w1) % 2 || reinterpret_cast<uintptr_t>(w2) % 2) return fail(-1, "kquant_gemv: Q6_K blocks must be 2-byte aligned");
+    if (reinterpret_cast<uintptr_t>(w1) % 16 || reinterpret_cast<uintptr_t>(w2) % 16) return fail(-1, "kquant_gemv: weight matrices must be 16-byte aligned");
     return dispatch_gemv<Q6KLane>(w1, w2, x, ldx, y, ldy, bias, resid, ld_resid, B, N, K, st);
   }
   return fail(-1, "kquant_gemv: unknown quantisation type");

@@ -75,9 +75,23 @@ def moe_forward(x: torch.Tensor, w_router: torch.Tensor, w_gate_up: torch.Tensor
     E, F2, _ = w_gate_up.shape
     F = F2 // 2
     L = _lib.load()
-    gemm(x, w_router, out=ws.logits[:T], out_dtype=torch.float32)
+    if E % 8:
+        # the GEMM wants N in multiples of 8: pad the router with zero rows once (their logits are
+        # never looked at - the routing kernel reads the first E columns only)
+        key = (w_router.data_ptr(), w_router._version)
+        if getattr(ws, "_router_key", None) != key:
+            Ep = (E + 7) // 8 * 8
+            ws._router_pad = torch.zeros(Ep, d, dtype=w_router.dtype, device=w_router.device)
+            ws._router_pad[:E].copy_(w_router)
+            ws._logits_pad = torch.empty(ws.logits.shape[0], Ep, dtype=torch.float32, device=w_router.device)
+            ws._router_key = key
+        gemm(x, ws._router_pad, out=ws._logits_pad[:T], out_dtype=torch.float32)
+        logits = ws._logits_pad
+    else:
+        gemm(x, w_router, out=ws.logits[:T], out_dtype=torch.float32)
+        logits = ws.logits
     ws.counts.zero_()
-    _lib.check(L.nfn_moe_route(_p(ws.logits), c_int(ws.logits.stride(0)), c_int(T), c_int(E), c_int(top_k), c_int(1 if score_fn == "sigmoid" else 0),
+    _lib.check(L.nfn_moe_route(_p(logits), c_int(logits.stride(0)), c_int(T), c_int(E), c_int(top_k), c_int(1 if score_fn == "sigmoid" else 0),
                                c_int(int(norm_topk)), c_float(route_scale), _p(ws.topk_idx), _p(ws.topk_w), _p(ws.counts), _st()), "nfn_moe_route")
     _lib.check(L.nfn_moe_plan(_p(ws.counts), c_int(E), c_int(ws.max_tiles), _p(ws.offsets), _p(ws.cursor), _p(ws.tile_expert), _p(ws.plan), _st()),
                "nfn_moe_plan")
