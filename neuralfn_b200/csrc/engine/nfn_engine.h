@@ -35,6 +35,15 @@ typedef struct {
   int global_every;     // with window > 0: layers l with (l + 1) % global_every == 0 are global
   float embed_scale;    // multiplies the token embedding (1 = off)
   int use_cuda_graph;
+  // Glimmer-style blocks (family 1 only); all zero = plain Llama
+  int gated_attention;  // wqkv carries n_head * head_dim extra gate rows; attention output *= sigmoid(gate)
+  int sandwich_norms;   // h += RMS(branch; post_*_norm) instead of h += branch (needs post_attn_norm / post_ffn_norm tensors)
+  int centered_norms;   // block norms apply (1 + w); the final norm never does
+  int embed_norm;       // weightless RMS norm of the token embedding
+  int rope_local_only;  // rotary embedding on sliding-window layers only (global layers have no position signal)
+  float q_scale;        // multiplies the normalised, rotated query (0 = 1)
+  float output_multiplier;  // multiplies the logits before the soft cap (0 = 1)
+  float post_norm_eps;  // epsilon of the sandwich norms (0 = norm_eps)
 } nfn_engine_config;
 
 typedef struct {

@@ -37,6 +37,9 @@ int nfn_embedding_positions(const int* tokens, const int* positions, const void*
                             int vocab, int max_pos, float scale, nfn_stream_t stream);
 int nfn_kv_cache_write(const void* qkv, int ld, void* k_cache, void* v_cache, int n, int n_q_heads, int n_kv_heads, int head_dim,
                        int cap, int pos0, nfn_stream_t stream);
+int nfn_sigmoid_gate_inplace(void* att, int ld_att, const void* gate, int ld_gate, long long rows, int width, nfn_stream_t stream);
+int nfn_rmsnorm_residual(const void* x, const void* weight, const void* resid, void* out, long long rows, int C, float eps, int centered,
+                         nfn_stream_t stream);
 long long nfn_launch_count(void);
 }
 
@@ -85,6 +88,9 @@ struct nfn_engine {
   void* dec_ws = nullptr;
   long long dec_ws_bytes = 0;
   void* rstd = nullptr;         // scratch of the weightless prefill QK norm
+  void* branch = nullptr;       // output of a block branch before its sandwich norm
+  void* ones = nullptr;         // unit norm weights (weightless embedding norm)
+  void* zero_pos = nullptr;     // int32 zeros: "position 0" for layers without rotary embedding
   std::vector<int> logit_row;   // row of e.logits holding each slot's latest logits
   int decode_calls = 0;
   int qkv_ld = 0, rows_max = 0;
@@ -125,7 +131,8 @@ bool layer_is_local(const nfn_engine_config& c, int l) {
 void build_expected(nfn_engine& e) {
   const nfn_engine_config& c = e.c;
   const long long C = c.d_model, F = c.d_ff, Vp = c.padded_vocab, HD = c.head_dim;
-  const long long QKV = (long long)(c.n_head + 2 * c.n_kv_head) * HD, ATT = (long long)c.n_head * HD;
+  const long long ATT = (long long)c.n_head * HD;
+  const long long QKV = (long long)(c.n_head + 2 * c.n_kv_head) * HD + ((c.family == 1 && c.gated_attention) ? ATT : 0);
   auto add = [&](const std::string& n, long long numel) { e.expected.emplace_back(n, numel); };
   if (c.family == 0) {
     add("wte", Vp * C);
@@ -146,9 +153,11 @@ void build_expected(nfn_engine& e) {
       add(yname(l, "wqkv"), QKV * C);
       if (c.qk_norm == 2) { add(yname(l, "q_norm"), HD); add(yname(l, "k_norm"), HD); }
       add(yname(l, "wo"), C * ATT);
+      if (c.sandwich_norms) add(yname(l, "post_attn_norm"), C);
       add(yname(l, "ffn_norm"), C);
       add(yname(l, "w_gate_up"), 2 * F * C);
       add(yname(l, "w_down"), C * F);
+      if (c.sandwich_norms) add(yname(l, "post_ffn_norm"), C);
     }
     add("norm", C);
     if (!c.tie_embeddings) add("lm_head", Vp * C);
@@ -157,13 +166,13 @@ void build_expected(nfn_engine& e) {
 
 // C[M, N] = A[M, K] . B[N, K]^T with the epilogue selected by flags
 int gemm(nfn_engine& e, const void* a, int lda, const void* b, void* cdst, int ldc, int m, int n, int k, int flags, const void* bias,
-         const void* resid, int ld_resid, float act_param = 0.f) {
+         const void* resid, int ld_resid, float act_param = 0.f, float alpha = 1.f) {
   nfn_gemm_args g{};
   g.a = a; g.b = b; g.c = cdst;
   g.m = m; g.n = n; g.k = k;
   g.lda = lda; g.ldb = k; g.ldc = ldc;
   g.flags = flags | (bias ? NFN_EPI_BIAS : 0) | (resid ? NFN_EPI_RESID : 0);
-  g.alpha = 1.f;
+  g.alpha = alpha;
   g.act_param = act_param;
   g.bias = bias;
   g.aux_in = resid;
@@ -191,22 +200,30 @@ int forward_layers(nfn_engine& e, int rows, bool decode, int slot, const int* d_
       K(nfn_norm_forward(e.x, e.W(gname(l, "ln_1.weight")), e.W(gname(l, "ln_1.bias")), e.xn, nullptr, nullptr, rows, C, c.norm_eps, 0, 0, e.stream));
       if (gemm(e, e.xn, C, e.W(gname(l, "attn.c_attn.weight")), e.qkv, e.qkv_ld, rows, e.qkv_ld, C, 0, e.W(gname(l, "attn.c_attn.bias")), nullptr, 0)) return -1;
     } else {
-      K(nfn_norm_forward(e.x, e.W(yname(l, "attn_norm")), nullptr, e.xn, nullptr, nullptr, rows, C, c.norm_eps, 1, 0, e.stream));
+      K(nfn_norm_forward(e.x, e.W(yname(l, "attn_norm")), nullptr, e.xn, nullptr, nullptr, rows, C, c.norm_eps, 1, c.centered_norms, e.stream));
       if (gemm(e, e.xn, C, e.W(yname(l, "wqkv")), e.qkv, e.qkv_ld, rows, e.qkv_ld, C, 0, nullptr, nullptr, 0)) return -1;
       if (c.qk_norm == 2) { qw = e.W(yname(l, "q_norm")); kw = e.W(yname(l, "k_norm")); }
     }
-    const bool rope = c.family == 1;
+    const bool rope = c.family == 1 && (!c.rope_local_only || local);
+    const float q_scale = (c.family == 1 && c.q_scale > 0.f) ? c.q_scale : 1.f;
     if (decode) {
       K(nfn_decode_attention(e.qkv, e.qkv_ld, kc, vc, cache_stride, d_lengths, e.att, rows, Hq, Hkv, HD, cap, qw, kw, c.qk_norm != 0,
-                             c.qk_norm_eps, rope ? e.cosT : nullptr, rope ? e.sinT : nullptr, rope ? c.max_seq : 0, sign, scale,
+                             c.qk_norm_eps, rope ? e.cosT : nullptr, rope ? e.sinT : nullptr, rope ? c.max_seq : 0, sign, scale * q_scale,
                              e.dec_ws, e.dec_ws_bytes, 0, e.stream));
     } else {
       if (rope && c.qk_norm) {
-        K(nfn_qk_norm_rope_forward(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, qw, kw, e.cosT, e.sinT, nullptr, c.max_seq, sign, c.qk_norm_eps, 1.f, nullptr, e.stream));
+        K(nfn_qk_norm_rope_forward(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, qw, kw, e.cosT, e.sinT, nullptr, c.max_seq, sign, c.qk_norm_eps, q_scale, nullptr, e.stream));
       } else if (rope) {
-        K(nfn_rope_inplace(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, HD, e.cosT, e.sinT, nullptr, c.max_seq, sign, 1.f, e.stream));
-      } else if (c.qk_norm) {
-        K(nfn_qk_norm_forward(e.qkv, static_cast<float*>(e.rstd), rows, Hq, Hkv, HD, e.qkv_ld, c.qk_norm_eps, 1.f, e.stream));
+        K(nfn_rope_inplace(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, HD, e.cosT, e.sinT, nullptr, c.max_seq, sign, q_scale, e.stream));
+      } else if (c.qk_norm == 1) {
+        K(nfn_qk_norm_forward(e.qkv, static_cast<float*>(e.rstd), rows, Hq, Hkv, HD, e.qkv_ld, c.qk_norm_eps, q_scale, e.stream));
+      } else if (q_scale != 1.f && c.qk_norm != 2) {
+        return efail("engine: a query scale without QK norm or rotary embedding is not supported in prefill");
+      } else if (c.qk_norm == 2) {
+        // no rotation on this layer: run the fused kernel at position 0 for every row (cos 1, sin 0)
+        if (!e.cosT) return efail("engine: weighted QK norm / query scale need the rotary tables (family 1)");
+        K(nfn_qk_norm_rope_forward(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, qw, kw, e.cosT, e.sinT, static_cast<const int*>(e.zero_pos), c.max_seq, sign,
+                                   c.qk_norm_eps, q_scale, nullptr, e.stream));
       }
       const char* q = static_cast<const char*>(e.qkv);
       K(nfn_attention_forward(q, q + (size_t)Hq * HD * 2, q + (size_t)(Hq + Hkv) * HD * 2, e.att, nullptr, 1, rows, Hq, Hkv, HD, e.qkv_ld,
@@ -219,11 +236,26 @@ int forward_layers(nfn_engine& e, int rows, bool decode, int slot, const int* d_
       if (gemm(e, e.xn, C, e.W(gname(l, "mlp.c_fc.weight")), e.ff, F, rows, F, C, NFN_ACT_GELU_TANH << NFN_EPI_ACT_SHIFT, e.W(gname(l, "mlp.c_fc.bias")), nullptr, 0)) return -1;
       if (gemm(e, e.ff, F, e.W(gname(l, "mlp.c_proj.weight")), e.x, C, rows, C, F, 0, e.W(gname(l, "mlp.c_proj.bias")), e.x, C)) return -1;
     } else {
-      if (gemm(e, e.att, ATT, e.W(yname(l, "wo")), e.x, C, rows, C, ATT, 0, nullptr, e.x, C)) return -1;
-      K(nfn_norm_forward(e.x, e.W(yname(l, "ffn_norm")), nullptr, e.xn, nullptr, nullptr, rows, C, c.norm_eps, 1, 0, e.stream));
+      const float post_eps = c.post_norm_eps > 0.f ? c.post_norm_eps : c.norm_eps;
+      if (c.gated_attention) {
+        const char* gate = static_cast<const char*>(e.qkv) + (size_t)(Hq + 2 * Hkv) * HD * 2;
+        K(nfn_sigmoid_gate_inplace(e.att, ATT, gate, e.qkv_ld, rows, ATT, e.stream));
+      }
+      if (c.sandwich_norms) {
+        if (gemm(e, e.att, ATT, e.W(yname(l, "wo")), e.branch, C, rows, C, ATT, 0, nullptr, nullptr, 0)) return -1;
+        K(nfn_rmsnorm_residual(e.branch, e.W(yname(l, "post_attn_norm")), e.x, e.x, rows, C, post_eps, c.centered_norms, e.stream));
+      } else if (gemm(e, e.att, ATT, e.W(yname(l, "wo")), e.x, C, rows, C, ATT, 0, nullptr, e.x, C)) {
+        return -1;
+      }
+      K(nfn_norm_forward(e.x, e.W(yname(l, "ffn_norm")), nullptr, e.xn, nullptr, nullptr, rows, C, c.norm_eps, 1, c.centered_norms, e.stream));
       if (gemm(e, e.xn, C, e.W(yname(l, "w_gate_up")), e.ff, 2 * F, rows, 2 * F, C, 0, nullptr, nullptr, 0)) return -1;
       K(nfn_swiglu_forward(e.ff, 2 * F, e.ffa, F, rows, F, e.stream));
-      if (gemm(e, e.ffa, F, e.W(yname(l, "w_down")), e.x, C, rows, C, F, 0, nullptr, e.x, C)) return -1;
+      if (c.sandwich_norms) {
+        if (gemm(e, e.ffa, F, e.W(yname(l, "w_down")), e.branch, C, rows, C, F, 0, nullptr, nullptr, 0)) return -1;
+        K(nfn_rmsnorm_residual(e.branch, e.W(yname(l, "post_ffn_norm")), e.x, e.x, rows, C, post_eps, c.centered_norms, e.stream));
+      } else if (gemm(e, e.ffa, F, e.W(yname(l, "w_down")), e.x, C, rows, C, F, 0, nullptr, e.x, C)) {
+        return -1;
+      }
     }
   }
   return 0;
@@ -240,7 +272,8 @@ int head(nfn_engine& e, int row0, int n) {
     K(nfn_norm_forward(xin, e.W("norm"), nullptr, e.xn, nullptr, nullptr, n, C, c.norm_eps, 1, 0, e.stream));
   const void* wh = c.family == 0 ? e.W("wte") : (c.tie_embeddings ? e.W("tok_embeddings") : e.W("lm_head"));
   const int flags = c.logit_softcap > 0.f ? (NFN_ACT_TANH_CAP << NFN_EPI_ACT_SHIFT) : 0;
-  return gemm(e, e.xn, C, wh, e.logits, c.padded_vocab, n, c.padded_vocab, C, flags, nullptr, nullptr, 0, c.logit_softcap);
+  const float mult = (c.family == 1 && c.output_multiplier > 0.f) ? c.output_multiplier : 1.f;
+  return gemm(e, e.xn, C, wh, e.logits, c.padded_vocab, n, c.padded_vocab, C, flags, nullptr, nullptr, 0, c.logit_softcap, mult);
 }
 
 int sample(nfn_engine& e, int rows, const float* d_row_params, const unsigned long long* d_offset, int* d_out) {
@@ -262,6 +295,7 @@ int decode_body(nfn_engine& e) {
     K(nfn_embedding_positions(d_tok, d_pos, e.W("wte"), e.W("wpe"), e.x, B, c.d_model, c.vocab, c.max_seq, c.embed_scale, e.stream));
   else
     K(nfn_embedding_positions(d_tok, nullptr, e.W("tok_embeddings"), nullptr, e.x, B, c.d_model, c.vocab, c.max_seq, c.embed_scale, e.stream));
+  if (c.family == 1 && c.embed_norm) K(nfn_norm_forward(e.x, e.ones, nullptr, e.x, nullptr, nullptr, B, c.d_model, c.norm_eps, 1, 0, e.stream));
   if (forward_layers(e, B, true, 0, d_len)) return -1;
   if (head(e, 0, B)) return -1;
   return sample(e, B, d_rp, d_off, d_out);
@@ -317,7 +351,7 @@ void nfn_engine_destroy(nfn_engine* e) {
   if (e->stream) cudaStreamSynchronize(e->stream);
   if (e->graph) cudaGraphExecDestroy(e->graph);
   for (auto& kv : e->w) cudaFree(kv.second.ptr);
-  for (void* p : {e->x, e->xn, e->qkv, e->att, e->ff, e->ffa, e->logits, (void*)e->cosT, (void*)e->sinT, e->dec_ws, (void*)e->d_io, e->rstd})
+  for (void* p : {e->x, e->xn, e->qkv, e->att, e->ff, e->ffa, e->logits, (void*)e->cosT, (void*)e->sinT, e->dec_ws, (void*)e->d_io, e->rstd, e->branch, e->ones, e->zero_pos})
     if (p) cudaFree(p);
   for (void* p : e->kc) cudaFree(p);
   for (void* p : e->vc) cudaFree(p);
@@ -386,14 +420,20 @@ int nfn_engine_finalize(nfn_engine* e) {
     if (!e->has(kv.first)) return efail("engine_finalize: missing tensor " + kv.first);
   const nfn_engine_config& c = e->c;
   const int HD = c.head_dim;
-  e->qkv_ld = (c.n_head + 2 * c.n_kv_head) * HD;
+  e->qkv_ld = (c.n_head + 2 * c.n_kv_head) * HD + ((c.family == 1 && c.gated_attention) ? c.n_head * HD : 0);
   e->rows_max = std::max(c.max_seq, c.max_batch);
   const long long R = e->rows_max;
   if (e->alloc(&e->x, R * c.d_model * 2) || e->alloc(&e->xn, R * c.d_model * 2) || e->alloc(&e->qkv, R * e->qkv_ld * 2) ||
       e->alloc(&e->att, R * c.n_head * HD * 2) || e->alloc(&e->ff, R * (c.family == 1 ? 2LL : 1LL) * c.d_ff * 2) ||
       e->alloc(&e->ffa, R * c.d_ff * 2) || e->alloc(&e->logits, (long long)c.max_batch * c.padded_vocab * 2) ||
-      e->alloc(&e->rstd, R * (c.n_head + c.n_kv_head) * 4))
+      e->alloc(&e->rstd, R * (c.n_head + c.n_kv_head) * 4) || e->alloc(&e->branch, R * c.d_model * 2) ||
+      e->alloc(&e->ones, (long long)c.d_model * 2) || e->alloc(&e->zero_pos, R * 4))
     return -1;
+  {
+    std::vector<uint16_t> one(c.d_model, 0x3F80);  // bf16 1.0
+    CU(cudaMemcpy(e->ones, one.data(), one.size() * 2, cudaMemcpyHostToDevice));
+    CU(cudaMemset(e->zero_pos, 0, (size_t)R * 4));
+  }
   if (c.family == 1) {
     const int half = HD / 2;
     std::vector<float> cs((size_t)c.max_seq * half), sn((size_t)c.max_seq * half);
@@ -470,6 +510,7 @@ int nfn_engine_prefill(nfn_engine* e, int slot, const int32_t* tokens, int n, co
   } else {
     K(nfn_embedding_positions(d_tok, nullptr, e->W("tok_embeddings"), nullptr, e->x, n, c.d_model, c.vocab, c.max_seq, c.embed_scale, e->stream));
   }
+  if (c.family == 1 && c.embed_norm) K(nfn_norm_forward(e->x, e->ones, nullptr, e->x, nullptr, nullptr, n, c.d_model, c.norm_eps, 1, 0, e->stream));
   if (forward_layers(*e, n, false, slot, nullptr)) return -1;
   if (head(*e, n - 1, 1)) return -1;
   float* rp = reinterpret_cast<float*>(e->h_io + e->io.row_params);

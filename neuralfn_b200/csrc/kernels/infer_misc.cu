@@ -152,3 +152,85 @@ extern "C" int nfn_kv_cache_write(const void* qkv, int ld, void* k_cache, void* 
       t_first, n_q_heads, n_kv_heads, head_dim, cap, pos0);
   return launch_check("kv_cache_write", 1);
 }
+
+// ---- gated attention output and sandwich norms (Glimmer-style blocks) ---------------------------
+namespace nfn {
+
+// att[r, c] *= sigmoid(gate[r, c])
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(__nv_bfloat16* __restrict__ att, int ld_att, const __nv_bfloat16* __restrict__ gate, int ld_gate, long long rows, int width) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vecs = width / 8;
+  if (idx >= rows * vecs) return;
+  const long long r = idx / vecs;
+  const int c = (int)(idx % vecs) * 8;
+  float a[8], g[8];
+  unpack8(*reinterpret_cast<const uint4*>(att + r * ld_att + c), a);
+  unpack8(*reinterpret_cast<const uint4*>(gate + r * ld_gate + c), g);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a[j] *= 1.f / (1.f + __expf(-g[j]));
+  *reinterpret_cast<uint4*>(att + r * ld_att + c) = pack8(a);
+}
+
+// out[r, :] = resid[r, :] + RMS(x[r, :]) * (centered ? 1 + w : w); one 256-thread block per row
+__global__ void __launch_bounds__(256)
+rmsnorm_residual_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ resid,
+                        __nv_bfloat16* __restrict__ out, int C, float eps, int centered) {
+  __shared__ float red[8];
+  const long long r = blockIdx.x;
+  const int vecs = C / 8;
+  float ss = 0.f;
+  for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + r * C + v * 8), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float rstd = rsqrtf(tot / (float)C + eps);
+  for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+    float f[8], wv[8], rv[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + r * C + v * 8), f);
+    unpack8(*reinterpret_cast<const uint4*>(w + v * 8), wv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = f[j] * rstd * (centered ? 1.f + wv[j] : wv[j]);
+    if (resid) {
+      unpack8(*reinterpret_cast<const uint4*>(resid + r * C + v * 8), rv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += rv[j];
+    }
+    *reinterpret_cast<uint4*>(out + r * C + v * 8) = pack8(f);
+  }
+}
+
+}  // namespace nfn
+
+extern "C" int nfn_sigmoid_gate_inplace(void* att, int ld_att, const void* gate, int ld_gate, long long rows, int width, nfn_stream_t stream) {
+  using namespace nfn;
+  if (rows <= 0) return 0;
+  if (!att || !gate || width <= 0 || (width & 7) || (ld_att & 7) || (ld_gate & 7)) return fail(-1, "sigmoid_gate: bad arguments");
+  const long long total = rows * (width / 8), grid = (total + 255) / 256;
+  if (grid > 0x7fffffffLL) return fail(-1, "sigmoid_gate: too large for one launch");
+  sigmoid_gate_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(att), ld_att,
+                                                                                    static_cast<const __nv_bfloat16*>(gate), ld_gate, rows, width);
+  return launch_check("sigmoid_gate", 1);
+}
+
+// Contiguous rows of C elements. resid may be NULL; out may alias resid (each element is read
+// before it is written by the same thread).
+extern "C" int nfn_rmsnorm_residual(const void* x, const void* weight, const void* resid, void* out, long long rows, int C, float eps,
+                                    int centered, nfn_stream_t stream) {
+  using namespace nfn;
+  if (rows <= 0) return 0;
+  if (!x || !weight || !out || C <= 0 || (C & 7) || rows > 0x7fffffffLL) return fail(-1, "rmsnorm_residual: bad arguments");
+  rmsnorm_residual_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight), static_cast<const __nv_bfloat16*>(resid),
+      static_cast<__nv_bfloat16*>(out), C, eps, centered);
+  return launch_check("rmsnorm_residual", 1);
+}

@@ -28,7 +28,9 @@ class _CConfig(C.Structure):
                 ("head_dim", C.c_int), ("d_ff", C.c_int), ("vocab", C.c_int), ("padded_vocab", C.c_int), ("max_seq", C.c_int),
                 ("max_batch", C.c_int), ("qk_norm", C.c_int), ("rope_hf", C.c_int), ("rope_theta", C.c_float),
                 ("norm_eps", C.c_float), ("qk_norm_eps", C.c_float), ("logit_softcap", C.c_float), ("tie_embeddings", C.c_int),
-                ("window", C.c_int), ("global_every", C.c_int), ("embed_scale", C.c_float), ("use_cuda_graph", C.c_int)]
+                ("window", C.c_int), ("global_every", C.c_int), ("embed_scale", C.c_float), ("use_cuda_graph", C.c_int),
+                ("gated_attention", C.c_int), ("sandwich_norms", C.c_int), ("centered_norms", C.c_int), ("embed_norm", C.c_int),
+                ("rope_local_only", C.c_int), ("q_scale", C.c_float), ("output_multiplier", C.c_float), ("post_norm_eps", C.c_float)]
 
 
 class _CSampling(C.Structure):
@@ -70,6 +72,17 @@ class EngineConfig:
     global_every: int = 0
     embed_scale: float = 1.0
     use_cuda_graph: int = 1
+    # Glimmer-style blocks (family 1): gated attention output, sandwich norms with (1 + w) scales,
+    # weightless embedding norm, rotary embedding on sliding-window layers only, query scale,
+    # logit multiplier
+    gated_attention: int = 0
+    sandwich_norms: int = 0
+    centered_norms: int = 0
+    embed_norm: int = 0
+    rope_local_only: int = 0
+    q_scale: float = 0.0
+    output_multiplier: float = 0.0
+    post_norm_eps: float = 0.0
 
     @classmethod
     def gpt2(cls, cfg, max_batch: int = 8, **kw) -> "EngineConfig":
@@ -78,6 +91,20 @@ class EngineConfig:
                    head_dim=cfg.head_dim, d_ff=cfg.mlp_mult * cfg.d_model, vocab=cfg.vocab_size, padded_vocab=cfg.padded_vocab,
                    max_seq=cfg.max_seq_len, max_batch=max_batch, qk_norm=1 if cfg.qk_norm else 0, norm_eps=cfg.ln_eps,
                    qk_norm_eps=cfg.qk_norm_eps, logit_softcap=cfg.logit_softcap, tie_embeddings=1, **kw)
+
+    @classmethod
+    def glimmer(cls, *, n_layer: int, d_model: int, n_head: int, n_kv_head: int, head_dim: int, d_ff: int, vocab: int, max_seq: int,
+                window: int, max_batch: int = 8, logit_softcap: float = 20.0, **kw) -> "EngineConfig":
+        """Muse-Glimmer block layout: every 4th layer global without position signal, the others
+        sliding-window with rotary embedding (theta 5e5), weightless per-head QK norm with query scale
+        3.87, gated attention, centered sandwich norms, output multiplier 0.19611613513818404."""
+        base = dict(family=1, n_layer=n_layer, d_model=d_model, n_head=n_head, n_kv_head=n_kv_head, head_dim=head_dim, d_ff=d_ff,
+                    vocab=vocab, padded_vocab=(vocab + 127) // 128 * 128, max_seq=max_seq, max_batch=max_batch, qk_norm=1, rope_hf=1,
+                    rope_theta=5.0e5, norm_eps=1e-5, qk_norm_eps=1e-6, logit_softcap=logit_softcap, tie_embeddings=0, window=window,
+                    global_every=4, gated_attention=1, sandwich_norms=1, centered_norms=1, embed_norm=1, rope_local_only=1,
+                    q_scale=3.87, output_multiplier=0.19611613513818404, post_norm_eps=1e-8)
+        base.update(kw)
+        return cls(**base)
 
     def c(self) -> _CConfig:
         return _CConfig(*[getattr(self, f.name) for f in fields(self)])

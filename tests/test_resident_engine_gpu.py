@@ -141,3 +141,76 @@ def test_generate_continuous_batching_is_order_independent():
     assert a == b and all(len(x) == 6 for x in a)
     c = eng.generate(prompts[:2], max_new_tokens=5, sampling=Sampling(temperature=1.0, top_k=20, seed=3))
     assert all(0 <= t < cfg.vocab_size for seq in c for t in seq)
+
+
+def _glimmer_ref(cfg, w, tokens):
+    """fp32 reference of the Glimmer block layout (see EngineConfig.glimmer)."""
+    T = len(tokens)
+    hd, Hq, Hkv, C, F_ = cfg.head_dim, cfg.n_head, cfg.n_kv_head, cfg.d_model, cfg.d_ff
+
+    def rms(v, wt, eps, centered):
+        y = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+        return y if wt is None else y * ((1 + wt) if centered else wt)
+
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2).double() / hd))
+    ang = torch.outer(torch.arange(T).double(), inv)
+    cos, sin = ang.cos().float()[:, None], ang.sin().float()[:, None]
+
+    def rope(v):
+        a, b = v[..., :hd // 2], v[..., hd // 2:]
+        return torch.cat((a * cos - b * sin, b * cos + a * sin), -1)
+
+    x = rms(w["tok_embeddings"][torch.tensor(tokens)], None, cfg.norm_eps, False)
+    for l in range(cfg.n_layer):
+        local = (l + 1) % cfg.global_every != 0
+        n = rms(x, w[f"layers.{l}.attn_norm"], cfg.norm_eps, True)
+        p = n @ w[f"layers.{l}.wqkv"].T
+        q = p[:, :Hq * hd].view(T, Hq, hd)
+        k = p[:, Hq * hd:(Hq + Hkv) * hd].view(T, Hkv, hd)
+        v = p[:, (Hq + Hkv) * hd:(Hq + 2 * Hkv) * hd].view(T, Hkv, hd)
+        g = p[:, (Hq + 2 * Hkv) * hd:]
+        q, k = rms(q, None, cfg.qk_norm_eps, False), rms(k, None, cfg.qk_norm_eps, False)
+        if local:
+            q, k = rope(q), rope(k)
+        q = q * cfg.q_scale
+        k, v = k.repeat_interleave(Hq // Hkv, 1), v.repeat_interleave(Hq // Hkv, 1)
+        s = torch.einsum("thd,shd->hts", q, k) / math.sqrt(hd)
+        i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+        mask = (j <= i) & ((i - j < cfg.window) if local else True)
+        a = torch.einsum("hts,shd->thd", s.masked_fill(~mask, float("-inf")).softmax(-1), v).reshape(T, Hq * hd)
+        a = a * torch.sigmoid(g)
+        x = x + rms(a @ w[f"layers.{l}.wo"].T, w[f"layers.{l}.post_attn_norm"], cfg.post_norm_eps, True)
+        m = rms(x, w[f"layers.{l}.ffn_norm"], cfg.norm_eps, True)
+        gu = m @ w[f"layers.{l}.w_gate_up"].T
+        f = (F.silu(gu[:, :F_]) * gu[:, F_:]) @ w[f"layers.{l}.w_down"].T
+        x = x + rms(f, w[f"layers.{l}.post_ffn_norm"], cfg.post_norm_eps, True)
+    logits = cfg.output_multiplier * (rms(x, w["norm"], cfg.norm_eps, False) @ w["lm_head"].T)
+    return (cfg.logit_softcap * torch.tanh(logits / cfg.logit_softcap))[:, :cfg.vocab]
+
+
+def test_glimmer_layout_matches_reference():
+    from neuralfn_b200.serving import EngineConfig, ResidentEngine
+    cfg = EngineConfig.glimmer(n_layer=4, d_model=256, n_head=4, n_kv_head=2, head_dim=128, d_ff=512, vocab=500, max_seq=64, window=12,
+                               max_batch=2)
+    eng = ResidentEngine(cfg)
+    g = torch.Generator().manual_seed(2)
+    w, shapes = {}, {"tok_embeddings": (512, 256), "lm_head": (512, 256)}
+    for l in range(4):
+        shapes.update({f"layers.{l}.wqkv": ((4 + 4 + 4) * 128, 256), f"layers.{l}.wo": (256, 512), f"layers.{l}.w_gate_up": (1024, 256),
+                       f"layers.{l}.w_down": (256, 512)})
+    for name, numel in eng.expected_tensors().items():
+        if "norm" in name:
+            w[name] = (0.1 * torch.randn(numel, generator=g)).bfloat16() if name != "norm" else (1 + 0.1 * torch.randn(numel, generator=g)).bfloat16()
+        else:
+            w[name] = (torch.randn(numel, generator=g) * 0.05).bfloat16()
+    eng.load_named_tensors(w)
+    wf = {k: (v.float().view(*shapes[k]) if k in shapes else v.float()) for k, v in w.items()}
+    seq = [3, 99, 401, 7, 7, 320, 64, 2, 11, 450, 13, 14, 15, 16, 17, 18]
+    nxt = eng.prefill(0, seq)
+    ref = _glimmer_ref(cfg, wf, seq)[-1]
+    assert (eng.last_logits(0) - ref).abs().max() < 0.1, float((eng.last_logits(0) - ref).abs().max())
+    for step in range(10):
+        seq.append(nxt)
+        nxt = eng.decode({0: seq[-1]})[0]
+        err = float((eng.last_logits(0) - _glimmer_ref(cfg, wf, seq)[-1]).abs().max())
+        assert err < 0.12, (step, err)
