@@ -1,0 +1,85 @@
+"""Platform state store, MCP tool server (JSON-RPC) and REST app routes, all in-process."""
+import json
+
+import pytest
+
+from neuralfn_b200.server import LiveStateStore
+from neuralfn_b200.server.mcp_server import McpToolServer
+
+XOR_X = [[0, 0], [0, 1], [1, 0], [1, 1]]
+XOR_Y = [[0], [1], [1], [0]]
+
+
+def _xor_session(call):
+    sid = call("create_session", {"name": "xor"})["session_id"]
+    ins = [call("add_node", {"session_id": sid, "builtin": "input", "role": "input"})["node_id"] for _ in range(2)]
+    hid = [call("add_node", {"session_id": sid, "builtin": "sigmoid"})["node_id"] for _ in range(4)]
+    out = call("add_node", {"session_id": sid, "builtin": "sigmoid", "role": "output"})["node_id"]
+    k = 0
+    for i in ins:
+        for h in hid:
+            k += 1
+            call("add_edge", {"session_id": sid, "src_node": i, "dst_node": h, "weight": 0.5 * ((-1) ** k) * (1 + k % 3), "bias": 0.1 * (k % 4)})
+    for j, h in enumerate(hid):
+        call("add_edge", {"session_id": sid, "src_node": h, "dst_node": out, "weight": 0.7 * ((-1) ** j), "bias": 0.0})
+    return sid
+
+
+def test_mcp_tools_build_execute_and_train(tmp_path):
+    server = McpToolServer(LiveStateStore(tmp_path / "snap"))
+    names = {t["name"] for t in server.list_tools()}
+    assert {"get_graph", "replace_graph", "execute", "train_start", "train_status", "list_presets", "semantic_match", "native_info"} <= names
+    call = server.call
+    sid = _xor_session(call)
+    before = call("execute", {"session_id": sid, "inputs": [0, 1]})["outputs"]
+    assert len(before) == 1 and 0 < before[0] < 1
+    rid = call("train_start", {"session_id": sid, "inputs": XOR_X, "targets": XOR_Y, "method": "sgd", "steps": 1500, "learning_rate": 0.5})["run_id"]
+    status = server.store.wait(rid, timeout=120)
+    assert status["status"] == "finished" and status["steps"] == 1500 and status["last_loss"] < 0.1, status
+    # snapshots survive a restart
+    again = LiveStateStore(tmp_path / "snap")
+    assert again.execute(sid, [0, 1]) == call("execute", {"session_id": sid, "inputs": [0, 1]})["outputs"]
+    assert "gpt2" in call("list_presets") and call("trace_torch", {"name": "gpt2"})["parameters"] > 0
+    assert call("semantic_match", {"text": "repair the software"})["action"] == "repair"
+    assert call("training_plan", {"config": {"batch_size": 16}})["grad_accum_steps"] == 32
+
+
+def test_json_rpc_protocol():
+    server = McpToolServer()
+    init = server.handle({"jsonrpc": "2.0", "id": 1, "method": "initialize", "params": {}})
+    assert init["result"]["serverInfo"]["name"] == "neuralfn_b200"
+    tools = server.handle({"jsonrpc": "2.0", "id": 2, "method": "tools/list"})["result"]["tools"]
+    assert all("inputSchema" in t for t in tools)
+    ok = server.handle({"jsonrpc": "2.0", "id": 3, "method": "tools/call", "params": {"name": "create_session", "arguments": {"name": "a"}}})
+    assert not ok["result"]["isError"] and "session_id" in json.loads(ok["result"]["content"][0]["text"])
+    bad = server.handle({"jsonrpc": "2.0", "id": 4, "method": "tools/call", "params": {"name": "get_graph", "arguments": {"session_id": "nope"}}})
+    assert bad["result"]["isError"]
+    assert server.handle({"jsonrpc": "2.0", "id": 5, "method": "bogus"})["error"]["code"] == -32601
+    assert server.handle({"jsonrpc": "2.0", "method": "notifications/initialized"}) is None
+
+
+def test_rest_routes_share_the_store(monkeypatch):
+    pytest.importorskip("fastapi")
+    from neuralfn_b200.server.app import InferenceConcurrencyGate, create_app
+    monkeypatch.setenv("NEURALFN_API_TOKEN", "s3cret")
+    store = LiveStateStore()
+    app = create_app(store)
+    routes = {r.path: r for r in app.routes if hasattr(r, "endpoint")}
+    assert {"/api/bootstrap", "/api/sessions", "/api/sessions/{sid}/execute", "/api/runs/{rid}", "/v1/generate"} <= set(routes)
+    sid = routes["/api/sessions"].endpoint.__globals__ and store.create_session("rest")
+    n1 = store.add_builtin_node(sid, "input", role="input")
+    n2 = store.add_builtin_node(sid, "identity", role="output")
+    store.add_edge(sid, n1, n2, weight=2.0, bias=1.0)
+    execute = next(r.endpoint for r in app.routes if getattr(r, "path", "") == "/api/sessions/{sid}/execute")
+    assert execute(sid, {"inputs": [3.0]}) == {"outputs": [7.0]}
+    from fastapi import HTTPException
+    with pytest.raises(HTTPException) as e:
+        execute("missing", {"inputs": [1.0]})
+    assert e.value.status_code == 404
+    gen = next(r.endpoint for r in app.routes if getattr(r, "path", "") == "/v1/generate")
+    with pytest.raises(HTTPException) as e:
+        gen({"prompts": [[1]]})
+    assert e.value.status_code == 503
+    with InferenceConcurrencyGate(max_waiting=1) as g:
+        with pytest.raises(RuntimeError):
+            g.__class__.__enter__(g)
