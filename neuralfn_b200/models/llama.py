@@ -45,6 +45,16 @@ class LlamaConfig:
     z_loss: float = 0.0
     vocab_pad_to: int = 128
     head_dim_override: int = 0
+    # pipeline-parallel stage view: this engine owns layers [pp_layer_begin, pp_layer_end); the first
+    # stage also owns the embedding, the last one the final norm and the head (0 / 0 = whole model)
+    pp_layer_begin: int = 0
+    pp_layer_end: int = 0
+    pp_first: bool = True
+    pp_last: bool = True
+
+    @property
+    def layer_range(self) -> range:
+        return range(self.pp_layer_begin, self.pp_layer_end or self.n_layer)
 
     @property
     def head_dim(self) -> int:
@@ -72,8 +82,10 @@ class LlamaConfig:
 
 def llama_param_specs(cfg: LlamaConfig) -> list[ParamSpec]:
     C, F_, Vp, hd = cfg.d_model, cfg.d_ff, cfg.padded_vocab, cfg.head_dim
-    specs = [ParamSpec("tok_embeddings", (Vp, C), True, "normal")]
-    for l in range(cfg.n_layer):
+    if cfg.tie_embeddings and not (cfg.pp_first and cfg.pp_last):
+        raise ValueError("tied embeddings need the first and the last pipeline stage on one rank")
+    specs = [ParamSpec("tok_embeddings", (Vp, C), True, "normal")] if cfg.pp_first else []
+    for l in cfg.layer_range:
         p = f"layers.{l}."
         specs += [ParamSpec(p + "attn_norm", (C,), False, "ones"),
                   ParamSpec(p + "wqkv", (cfg.qkv_dim, C), True, "normal"),
@@ -81,9 +93,10 @@ def llama_param_specs(cfg: LlamaConfig) -> list[ParamSpec]:
                   ParamSpec(p + "ffn_norm", (C,), False, "ones"),
                   ParamSpec(p + "w_gate_up", (2 * F_, C), True, "normal"),
                   ParamSpec(p + "w_down", (C, F_), True, "resid")]
-    specs.append(ParamSpec("norm", (C,), False, "ones"))
-    if not cfg.tie_embeddings:
-        specs.append(ParamSpec("lm_head", (Vp, C), True, "normal"))
+    if cfg.pp_last:
+        specs.append(ParamSpec("norm", (C,), False, "ones"))
+        if not cfg.tie_embeddings:
+            specs.append(ParamSpec("lm_head", (Vp, C), True, "normal"))
     return specs
 
 
@@ -99,8 +112,9 @@ def init_llama_params_(cfg: LlamaConfig, layout: FlatLayout, master: torch.Tenso
             v.normal_(0.0, 0.02 / math.sqrt(2 * cfg.n_layer), generator=gen)
         elif s.init == "ones":
             v.fill_(1.0)
-    layout.view(master, "tok_embeddings")[cfg.vocab_size:].zero_()
-    if not cfg.tie_embeddings:
+    if cfg.pp_first:
+        layout.view(master, "tok_embeddings")[cfg.vocab_size:].zero_()
+    if cfg.pp_last and not cfg.tie_embeddings:
         layout.view(master, "lm_head")[cfg.vocab_size:].zero_()
 
 
@@ -183,7 +197,8 @@ class LlamaEngine:
         self.acts = [dict(n1=e(N, C), r1=e(N, dtype=f32), qkv=e(N, Q),
                           qk_rstd=e(N, cfg.n_head + cfg.n_kv_head, dtype=f32) if cfg.qk_norm else None,
                           att=e(N, A), lse=e(batch, cfg.n_head, seq, dtype=f32), x1=e(N, C), n2=e(N, C), r2=e(N, dtype=f32),
-                          gu=e(N, 2 * Fd), h=e(N, Fd), x2=e(N, C)) for _ in range(cfg.n_layer)]
+                          gu=e(N, 2 * Fd), h=e(N, Fd), x2=e(N, C)) for _ in cfg.layer_range]
+        self.layers = list(cfg.layer_range)
         self.nf, self.rf = e(N, C), e(N, dtype=f32)
         self.mean_scratch = e(N, dtype=f32)  # RMS norms have no mean; the kernel wrapper wants a buffer
         self.logits = e(N, cfg.padded_vocab)
@@ -208,9 +223,10 @@ class LlamaEngine:
         K, I, gemm, cfg, p = self.K, self.I, self.gemm, self.cfg, self.p
         B, T, N = self.B, self.T, self.B * self.T
         Hq, Hkv, hd = cfg.n_head, cfg.n_kv_head, cfg.head_dim
-        K.embedding_forward(self.tokens, p["tok_embeddings"], None, T=T, out=self.x0)
-        x = self.x0
-        for l, a in enumerate(self.acts):
+        if cfg.pp_first:
+            K.embedding_forward(self.tokens, p["tok_embeddings"], None, T=T, out=self.x0)
+        x = self.x0  # later stages: filled by the pipeline runtime with the previous stage's output
+        for l, a in zip(self.layers, self.acts):
             pre = f"layers.{l}."
             K.norm_forward(x, p[pre + "attn_norm"], None, eps=cfg.norm_eps, mode=K.NORM_RMS, mean=self.mean_scratch,out=a["n1"], rstd=a["r1"])
             gemm(a["n1"], p[pre + "wqkv"], out=a["qkv"])
@@ -227,6 +243,8 @@ class LlamaEngine:
             I.swiglu_forward(a["gu"], cfg.d_ff, out=a["h"])
             gemm(a["h"], p[pre + "w_down"], resid=a["x1"], out=a["x2"])
             x = a["x2"]
+        if not cfg.pp_last:
+            return x  # hand to the next stage
         K.norm_forward(x, p["norm"], None, eps=cfg.norm_eps, mode=K.NORM_RMS, mean=self.mean_scratch,out=self.nf, rstd=self.rf)
         head = p["tok_embeddings"] if cfg.tie_embeddings else p["lm_head"]
         if cfg.logit_softcap > 0:
@@ -243,19 +261,20 @@ class LlamaEngine:
         B, T = self.B, self.T
         Hq, Hkv, hd = cfg.n_head, cfg.n_kv_head, cfg.head_dim
         sc, ws = self.scratch, self.ws
-        head_name = "tok_embeddings" if cfg.tie_embeddings else "lm_head"
-        gemm(self.logits, p[head_name], b_mn=True, out=self.d_n)
-        gemm(self.logits, self.nf, a_mn=True, b_mn=True, out=g[head_name])
-        if not cfg.tie_embeddings:
+        dx, spare = self.d_a, self.d_b  # later stages: d_a was filled with the next stage's input gradient
+        if cfg.pp_last:
+            head_name = "tok_embeddings" if cfg.tie_embeddings else "lm_head"
+            gemm(self.logits, p[head_name], b_mn=True, out=self.d_n)
+            gemm(self.logits, self.nf, a_mn=True, b_mn=True, out=g[head_name])
+            x_last = self.acts[-1]["x2"] if self.acts else self.x0
+            K.norm_backward_dx(self.d_n, x_last, p["norm"], None, self.rf, mode=K.NORM_RMS, out=dx)
+            K.norm_backward_wb(self.d_n, x_last, None, self.rf, g["norm"], None, sc, mode=K.NORM_RMS)
+        if cfg.pp_first and not cfg.tie_embeddings:
             g["tok_embeddings"].zero_()
-        x_last = self.acts[-1]["x2"] if self.acts else self.x0
-        dx, spare = self.d_a, self.d_b
-        K.norm_backward_dx(self.d_n, x_last, p["norm"], None, self.rf, mode=K.NORM_RMS, out=dx)
-        K.norm_backward_wb(self.d_n, x_last, None, self.rf, g["norm"], None, sc, mode=K.NORM_RMS)
-        for l in range(cfg.n_layer - 1, -1, -1):
-            a = self.acts[l]
+        for i in range(len(self.layers) - 1, -1, -1):
+            a, l = self.acts[i], self.layers[i]
             pre = f"layers.{l}."
-            x_in = self.acts[l - 1]["x2"] if l > 0 else self.x0
+            x_in = self.acts[i - 1]["x2"] if i > 0 else self.x0
             # MLP: x2 = w_down(swiglu(w_gate_up(n2))) + x1
             gemm(dx, p[pre + "w_down"], b_mn=True, out=self.d_h)
             gemm(dx, a["h"], a_mn=True, b_mn=True, workspace=ws, out=g[pre + "w_down"])
@@ -284,7 +303,9 @@ class LlamaEngine:
             K.norm_backward_dx(self.d_n, x_in, p[pre + "attn_norm"], None, a["r1"], mode=K.NORM_RMS, dresid=dx, out=spare)
             K.norm_backward_wb(self.d_n, x_in, None, a["r1"], g[pre + "attn_norm"], None, sc, mode=K.NORM_RMS)
             dx, spare = spare, dx
-        K.embedding_backward(dx, self.tokens, g["tok_embeddings"], None, B=B, T=T)
+        self.d_input = dx  # gradient w.r.t. this stage's input (sent to the previous stage)
+        if cfg.pp_first:
+            K.embedding_backward(dx, self.tokens, g["tok_embeddings"], None, B=B, T=T)
 
     def set_batch(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
         self.tokens.copy_(tokens.reshape(-1), non_blocking=True)
