@@ -205,3 +205,225 @@ extern "C" int nfn_moe_combine(const void* ys, int d, int T, int k, const int* r
       static_cast<__nv_bfloat16*>(out), ld_out);
   return launch_check("moe_combine", 1);
 }
+
+// ---- expert parallelism over peer memory --------------------------------------------------------
+// Experts are split across `world` ranks (El = E / world each). Every rank routes its own
+// tokens, sorts them by (global) expert into a symmetric send buffer and publishes its
+// per-expert counts to all peers. From the full count table every rank derives, without
+// any further communication, (a) where each (expert, source rank) segment sits in the
+// owner's receive buffer and (b) where the rows it sent will be found again. Dispatch is a
+// PULL: the owner copies the segments out of the peers' send buffers (plain 16-byte loads
+// over NVLink). After the expert FFN (grouped GEMMs) the combine is a pull as well: each
+// source reads its rows out of the owners' output buffers and applies the routing weights.
+// Nothing is sent back explicitly and no rank writes another rank's memory except flags and
+// the count table.
+namespace nfn {
+
+constexpr int EP_MAX_WORLD = 8;
+
+struct EpPeers {
+  const void* p[EP_MAX_WORLD];
+};
+struct EpPeersMut {
+  int* p[EP_MAX_WORLD];
+};
+
+__device__ __forceinline__ void ep_st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ep_ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// counts[E] of this rank -> row `rank` of every rank's table [world][E]; then flag; then wait
+// for every rank's row to arrive here. One block.
+__global__ void moe_ep_exchange_counts_kernel(const int* __restrict__ counts, int E, EpPeersMut tables, EpPeersMut flags, int* my_flags,
+                                              int rank, int world, int epoch, const int* epoch_dev, int* status) {
+  const int ep = epoch + (epoch_dev ? *epoch_dev : 0);
+  for (int r = 0; r < world; ++r)
+    for (int e = threadIdx.x; e < E; e += blockDim.x) tables.p[r][rank * E + e] = counts[e];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < world) ep_st_release_sys(flags.p[threadIdx.x] + rank, ep);
+  if (threadIdx.x < world) {
+    const unsigned long long t0 = global_timer_ns();
+    while (ep_ld_acquire_sys(my_flags + threadIdx.x) - ep < 0) {
+      if (global_timer_ns() - t0 > 10ull * kWaitLimitNs) {
+        if (status) atomicCAS(status, 0, NFN_ERR_WAIT_PEER);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+// From the count table [world][E]:
+//   src_off[e]            first row of expert e in THIS rank's send buffer (tight packing)
+//   recv_off[le]          first row of local expert le in this rank's receive buffer (128-row padded)
+//   seg_src_row[le*W+s]   first row of segment (le, s) inside rank s's send buffer
+//   seg_dst_row[le*W+s]   first row of that segment in this rank's receive buffer
+//   seg_rows[le*W+s]      rows of the segment
+//   home_row[e]           where THIS rank's rows for expert e start in the owner's receive buffer
+//   tile_expert / plan    as in moe_plan_kernel, for the local experts
+__global__ void moe_ep_plan_kernel(const int* __restrict__ table, int E, int world, int rank, int max_tiles, int* __restrict__ src_off,
+                                   int* __restrict__ cursor, int* __restrict__ recv_off, int* __restrict__ seg_src_row,
+                                   int* __restrict__ seg_dst_row, int* __restrict__ seg_rows, int* __restrict__ home_row,
+                                   int* __restrict__ tile_expert, int* __restrict__ plan) {
+  if (threadIdx.x != 0) return;
+  const int El = E / world;
+  int run = 0;
+  for (int e = 0; e < E; ++e) {
+    src_off[e] = run;
+    cursor[e] = 0;
+    run += table[rank * E + e];
+  }
+  src_off[E] = run;
+  for (int owner = 0; owner < world; ++owner) {
+    int roff = 0;
+    for (int le = 0; le < El; ++le) {
+      const int e = owner * El + le;
+      int tot = 0;
+      for (int s = 0; s < world; ++s) {
+        if (owner == rank) {
+          int pre = 0;
+          for (int e2 = 0; e2 < e; ++e2) pre += table[s * E + e2];
+          seg_src_row[le * world + s] = pre;
+          seg_dst_row[le * world + s] = roff + tot;
+          seg_rows[le * world + s] = table[s * E + e];
+        }
+        if (s == rank) home_row[e] = roff + tot;
+        tot += table[s * E + e];
+      }
+      if (owner == rank) {
+        recv_off[le] = roff;
+        for (int t = roff / MOE_TILE; t < (roff + (tot + MOE_TILE - 1) / MOE_TILE * MOE_TILE) / MOE_TILE && t < max_tiles; ++t) tile_expert[t] = le;
+      }
+      roff += (tot + MOE_TILE - 1) / MOE_TILE * MOE_TILE;
+    }
+    if (owner == rank) {
+      recv_off[El] = roff;
+      plan[0] = min(roff / MOE_TILE, max_tiles);
+      plan[1] = roff;
+    }
+  }
+}
+
+// grid (segments, row chunks): copies segment rows from the source rank's send buffer
+__global__ void __launch_bounds__(256)
+moe_ep_pull_kernel(EpPeers send_bufs, const int* __restrict__ seg_src_row, const int* __restrict__ seg_dst_row, const int* __restrict__ seg_rows,
+                   int world, int d, int capacity_rows, __nv_bfloat16* __restrict__ xs) {
+  const int seg = blockIdx.x, s = seg % world;
+  const int rows = seg_rows[seg];
+  const long long src0 = seg_src_row[seg], dst0 = seg_dst_row[seg];
+  const int vecs = d / 8;
+  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(send_bufs.p[s]) + src0 * d);
+  uint4* dst = reinterpret_cast<uint4*>(xs + dst0 * d);
+  const long long total = (long long)rows * vecs;
+  for (long long i = (long long)blockIdx.y * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.y * blockDim.x) {
+    if (dst0 + i / vecs >= capacity_rows) break;
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + i) : "memory");
+    dst[i] = v;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+moe_ep_combine_kernel(EpPeers ys_bufs, int d, int T, int k, int E, int world, const int* __restrict__ topk_idx, const int* __restrict__ row_of,
+                      const int* __restrict__ src_off, const int* __restrict__ home_row, const float* __restrict__ topk_w,
+                      const __nv_bfloat16* __restrict__ resid, int ld_resid, __nv_bfloat16* __restrict__ out, int ld_out) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vecs = d / 8, El = E / world;
+  if (idx >= (long long)T * vecs) return;
+  const int tok = (int)(idx / vecs), c = (int)(idx % vecs) * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int j = 0; j < k; ++j) {
+    const long long item = (long long)tok * k + j;
+    const int e = topk_idx[item], local_row = row_of[item];
+    if (local_row < 0) continue;
+    const long long row = (long long)home_row[e] + (local_row - src_off[e]);
+    const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(ys_bufs.p[e / El]);
+    uint4 u;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(base + row * d + c) : "memory");
+    const float w = topk_w[item];
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), dd = unpack_bf16x2(u.w);
+    acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * b.x; acc[3] += w * b.y;
+    acc[4] += w * cc.x; acc[5] += w * cc.y; acc[6] += w * dd.x; acc[7] += w * dd.y;
+  }
+  if (resid) {
+    const uint4 u = *reinterpret_cast<const uint4*>(resid + (long long)tok * ld_resid + c);
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), dd = unpack_bf16x2(u.w);
+    acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += cc.x; acc[5] += cc.y; acc[6] += dd.x; acc[7] += dd.y;
+  }
+  uint4 o;
+  o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]); o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+  *reinterpret_cast<uint4*>(out + (long long)tok * ld_out + c) = o;
+}
+
+}  // namespace nfn
+
+// tables[r] / flags[r]: rank r's count table [world][E] and flag array [world] (symmetric memory).
+extern "C" int nfn_moe_ep_exchange_counts(const int* counts, int E, int* const* tables, int* const* flags, int rank, int world, int epoch,
+                                          const int* epoch_dev, nfn_stream_t stream) {
+  using namespace nfn;
+  if (!counts || !tables || !flags || E <= 0 || E > MOE_MAX_E || world < 1 || world > EP_MAX_WORLD || rank < 0 || rank >= world || E % world)
+    return fail(-1, "moe_ep_exchange_counts: bad arguments (E must be a multiple of world <= 8)");
+  EpPeersMut t{}, f{};
+  for (int r = 0; r < world; ++r) {
+    if (!tables[r] || !flags[r]) return fail(-1, "moe_ep_exchange_counts: missing peer pointer");
+    t.p[r] = tables[r];
+    f.p[r] = flags[r];
+  }
+  moe_ep_exchange_counts_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts, E, t, f, flags[rank], rank, world, epoch, epoch_dev, status_ptr());
+  return launch_check("moe_ep_exchange_counts", 1);
+}
+
+// Sizes: src_off E+1, cursor E, recv_off E/world+1, seg_* (E/world)*world, home_row E, tile_expert max_tiles, plan 2.
+extern "C" int nfn_moe_ep_plan(const int* table, int E, int world, int rank, int max_tiles, int* src_off, int* cursor, int* recv_off,
+                               int* seg_src_row, int* seg_dst_row, int* seg_rows, int* home_row, int* tile_expert, int* plan,
+                               nfn_stream_t stream) {
+  using namespace nfn;
+  if (!table || !src_off || !cursor || !recv_off || !seg_src_row || !seg_dst_row || !seg_rows || !home_row || !tile_expert || !plan ||
+      E <= 0 || E > MOE_MAX_E || world < 1 || world > EP_MAX_WORLD || E % world || max_tiles <= 0)
+    return fail(-1, "moe_ep_plan: bad arguments");
+  moe_ep_plan_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(table, E, world, rank, max_tiles, src_off, cursor, recv_off, seg_src_row,
+                                                                      seg_dst_row, seg_rows, home_row, tile_expert, plan);
+  return launch_check("moe_ep_plan", 1);
+}
+
+extern "C" int nfn_moe_ep_pull(const void* const* send_bufs, const int* seg_src_row, const int* seg_dst_row, const int* seg_rows,
+                               int n_local_experts, int world, int d, int capacity_rows, void* xs, nfn_stream_t stream) {
+  using namespace nfn;
+  if (!send_bufs || !seg_src_row || !seg_dst_row || !seg_rows || !xs || (d & 7) || world < 1 || world > EP_MAX_WORLD || n_local_experts <= 0)
+    return fail(-1, "moe_ep_pull: bad arguments");
+  EpPeers s{};
+  for (int r = 0; r < world; ++r) {
+    if (!send_bufs[r]) return fail(-1, "moe_ep_pull: missing peer pointer");
+    s.p[r] = send_bufs[r];
+  }
+  const dim3 grid(n_local_experts * world, 16);
+  moe_ep_pull_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(s, seg_src_row, seg_dst_row, seg_rows, world, d, capacity_rows,
+                                                                         static_cast<__nv_bfloat16*>(xs));
+  return launch_check("moe_ep_pull", 1);
+}
+
+extern "C" int nfn_moe_ep_combine(const void* const* ys_bufs, int d, int T, int k, int E, int world, const int* topk_idx, const int* row_of,
+                                  const int* src_off, const int* home_row, const float* topk_w, const void* resid, int ld_resid, void* out,
+                                  int ld_out, nfn_stream_t stream) {
+  using namespace nfn;
+  if (T <= 0) return 0;
+  if (!ys_bufs || !topk_idx || !row_of || !src_off || !home_row || !topk_w || !out || (d & 7) || (ld_out & 7) || world < 1 || world > EP_MAX_WORLD || E % world)
+    return fail(-1, "moe_ep_combine: bad arguments");
+  EpPeers y{};
+  for (int r = 0; r < world; ++r) {
+    if (!ys_bufs[r]) return fail(-1, "moe_ep_combine: missing peer pointer");
+    y.p[r] = ys_bufs[r];
+  }
+  const long long total = (long long)T * (d / 8), grid = (total + 255) / 256;
+  if (grid > 0x7fffffffLL) return fail(-1, "moe_ep_combine: too large for one launch");
+  moe_ep_combine_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      y, d, T, k, E, world, topk_idx, row_of, src_off, home_row, topk_w, static_cast<const __nv_bfloat16*>(resid), ld_resid,
+      static_cast<__nv_bfloat16*>(out), ld_out);
+  return launch_check("moe_ep_combine", 1);
+}
