@@ -165,7 +165,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
     }
   } else {
+#define EPI_TILE_FIRST ((int)blockIdx.x)
+#define EPI_TILE_STEP ((int)gridDim.x)
+#define EPI_TILE_M0(t2) (((t2) % p.tiles_m) * BM)
+#define EPI_RELEASE_ACC(acc) mbar_arrive(smem_u32(&tempty_bar[acc]))
 #include "gemm_epilogue_body.inc"
+#undef EPI_TILE_FIRST
+#undef EPI_TILE_STEP
+#undef EPI_TILE_M0
+#undef EPI_RELEASE_ACC
   }
 
   // ---------------------------------------------------------------- teardown --

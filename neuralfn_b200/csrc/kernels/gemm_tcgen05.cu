@@ -128,7 +128,25 @@ static int launch_gemm(const nfn_gemm_args& a, int split_k, cudaStream_t stream)
   return launch_check("gemm", launched);
 }
 
+int try_launch_gemm_pair(const nfn_gemm_args& a, cudaStream_t stream);  // gemm_2cta.cu
+
+// CTA-pair (cta_group::2) kernel for eligible K-major products: -1 = read NFN_GEMM_PAIR once.
+static int g_pair_mode = -1;
+static bool pair_enabled() {
+  if (g_pair_mode < 0) {
+    const char* e = getenv("NFN_GEMM_PAIR");
+    g_pair_mode = (e && e[0] == '1') ? 1 : 0;
+  }
+  return g_pair_mode == 1;
+}
+
 }  // namespace nfn
+
+extern "C" int nfn_gemm_set_pair_mode(int on) {
+  const int old = nfn::pair_enabled() ? 1 : 0;
+  nfn::g_pair_mode = on ? 1 : 0;
+  return old;
+}
 
 extern "C" int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream_) {
   using namespace nfn;
@@ -169,6 +187,10 @@ extern "C" int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream_) {
     if (want > 1 && !(a.flags & plain_mask) && a.workspace &&
         (long long)want * a.m * a.n * 4 <= a.workspace_bytes)
       split = want;
+  }
+  if (wide && split == 1 && !a.a_mn && !a.b_mn && pair_enabled()) {
+    const int rc = try_launch_gemm_pair(a, stream);
+    if (rc != 0) return rc < 0 ? rc : 0;
   }
 #define NFN_DISPATCH(AMN, BMN)                                              \
   return wide ? launch_gemm<256, 4, AMN, BMN>(a, split, stream)             \

@@ -91,3 +91,33 @@ def test_gemm_strided_views(kernel_lib):
     _lib.assert_status_ok("gemm views")
     _close(out, x.float() @ w.float().t(), 128)
     assert outbuf[:, :64].abs().max().item() == 0 and outbuf[:, 128:].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(16384, 768, 768), (16384, 2304, 768), (8192, 3072, 768), (16384, 768, 3072),
+                                   (8192 + 128, 2304 + 64, 768 + 32)])
+def test_gemm_cta_pair(kernel_lib, m, n, k):
+    """CTA-pair (cta_group::2) kernel: plain product and the fused epilogues against fp32."""
+    from neuralfn_b200.ops import _lib
+    from neuralfn_b200.ops.gemm import gemm
+    L = _lib.load()
+    torch.manual_seed(3)
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(m, n, device="cuda", dtype=torch.bfloat16)
+    base = x.float() @ w.float().t()
+    old = L.nfn_gemm_set_pair_mode(1)
+    try:
+        y = gemm(x, w)
+        _lib.assert_status_ok("gemm pair")
+        _close(y, base, k)
+        pre = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        y = gemm(x, w, bias=bias, act="gelu_tanh", save_pre=pre)
+        _lib.assert_status_ok("gemm pair gelu")
+        _close(pre, base + bias.float(), k)
+        _close(y, torch.nn.functional.gelu(base + bias.float(), approximate="tanh"), k)
+        y = gemm(x, w, bias=bias, resid=res)
+        _lib.assert_status_ok("gemm pair resid")
+        _close(y, base + bias.float() + res.float(), k)
+    finally:
+        L.nfn_gemm_set_pair_mode(old)
