@@ -77,6 +77,27 @@ int nfn_engine_release(nfn_engine* e, int slot);
 int nfn_engine_slot_length(const nfn_engine* e, int slot);
 // Copies the bf16 logits of the last step for `slot` to the host as fp32 (vocab entries).
 int nfn_engine_last_logits(nfn_engine* e, int slot, float* out_vocab);
+
+// ---- block verification (speculative decoding, appends at a position > 0) ---------------------
+// Allocates the staging buffers once (max_rows <= 128 rows per slot and call;
+// max_batch * max_rows must not exceed max(max_seq, max_batch)).
+int nfn_engine_enable_verify(nfn_engine* e, int max_rows);
+// Runs `rows` tokens per slot (tokens[slot * rows + r]; n_rows[slot] of them live, 0 = slot not
+// in this call) through the model at positions length[slot] ..., WITHOUT touching the KV caches:
+// attention reads the cache prefix plus the block, the block's K/V go to per-layer staging
+// buffers. argmax_out[slot * rows + r] = most likely successor after row r.
+int nfn_engine_verify(nfn_engine* e, const int32_t* tokens, const int32_t* n_rows, int rows, int32_t* argmax_out);
+// fp32 logits of row `row` of `slot` in the last verification.
+int nfn_engine_verify_logits(nfn_engine* e, int slot, int row, float* out_vocab);
+// Appends the first accepted[slot] rows of the last verification to the caches (one launch for
+// all layers) and advances the slot lengths; rows that were not accepted leave no trace.
+int nfn_engine_commit(nfn_engine* e, const int32_t* accepted);
+// Shortens a slot to its first n tokens. Fails when a sliding-window cache of the slot has
+// already wrapped (its older rows are gone).
+int nfn_engine_truncate(nfn_engine* e, int slot, int n);
+// Copies the first n cached tokens of src_slot into dst_slot (device-to-device; the two slots
+// are independent afterwards).
+int nfn_engine_fork(nfn_engine* e, int src_slot, int dst_slot, int n);
 // Kernel launches issued so far by this engine (graph replays count their captured launches).
 long long nfn_engine_launches(const nfn_engine* e);
 

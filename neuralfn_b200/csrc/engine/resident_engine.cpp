@@ -102,6 +102,18 @@ struct nfn_engine {
   unsigned long long steps = 0;
   cudaGraphExec_t graph = nullptr;
   long long launches = 0, graph_launches = 0;
+  // block verification (speculative decoding, appends at a position > 0); set up by nfn_engine_enable_verify
+  int v_rows_max = 0, v_rows = 0;         // rows per slot: capacity / of the last verification
+  std::vector<void*> stage_k, stage_v;    // per layer [max_batch * v_rows_max, n_kv_head * head_dim]
+  void** d_tables = nullptr;              // device copies of stage_k | stage_v | kc | vc pointer arrays
+  int* d_caps = nullptr;
+  void* logits_v = nullptr;               // [max_batch * v_rows_max, padded_vocab] bf16
+  void* blk_ws = nullptr;
+  long long blk_ws_bytes = 0;
+  int *d_vtok = nullptr, *d_vpos = nullptr, *d_vlen = nullptr, *d_vrows = nullptr, *d_vout = nullptr;
+  void* argmax_ws = nullptr;
+  std::vector<int> h_vrows;               // live rows per slot of the last verification
+  std::vector<int> logit_src;             // 0: e.logits, 1: logits_v
 
   int alloc(void** p, long long nbytes) {
     CU(cudaMalloc(p, (size_t)nbytes));
@@ -183,8 +195,12 @@ int gemm(nfn_engine& e, const void* a, int lda, const void* b, void* cdst, int l
 }
 
 // One transformer stack over `rows` rows of e.x. decode = true: one token per slot (row ==
-// slot), attention over the caches; false: one sequence of `rows` tokens for `slot`.
-int forward_layers(nfn_engine& e, int rows, bool decode, int slot, const int* d_lengths) {
+// slot), attention over the caches; false: one sequence of `rows` tokens for `slot`. With
+// block_rows > 0 (and decode = false) the rows are max_batch blocks of block_rows rows that
+// continue each slot at d_lengths[slot]: attention reads the caches plus the block, the
+// block's K/V go to the staging buffers, the caches stay untouched.
+int forward_layers(nfn_engine& e, int rows, bool decode, int slot, const int* d_lengths, int block_rows = 0, const int* d_block_pos = nullptr,
+                   const int* d_block_live = nullptr) {
   const nfn_engine_config& c = e.c;
   const int C = c.d_model, F = c.d_ff, HD = c.head_dim, Hq = c.n_head, Hkv = c.n_kv_head, ATT = Hq * HD;
   const float scale = 1.f / std::sqrt((float)HD);
@@ -212,9 +228,9 @@ int forward_layers(nfn_engine& e, int rows, bool decode, int slot, const int* d_
                              e.dec_ws, e.dec_ws_bytes, 0, e.stream));
     } else {
       if (rope && c.qk_norm) {
-        K(nfn_qk_norm_rope_forward(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, qw, kw, e.cosT, e.sinT, nullptr, c.max_seq, sign, c.qk_norm_eps, q_scale, nullptr, e.stream));
+        K(nfn_qk_norm_rope_forward(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, qw, kw, e.cosT, e.sinT, d_block_pos, c.max_seq, sign, c.qk_norm_eps, q_scale, nullptr, e.stream));
       } else if (rope) {
-        K(nfn_rope_inplace(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, HD, e.cosT, e.sinT, nullptr, c.max_seq, sign, q_scale, e.stream));
+        K(nfn_rope_inplace(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, HD, e.cosT, e.sinT, d_block_pos, c.max_seq, sign, q_scale, e.stream));
       } else if (c.qk_norm == 1) {
         K(nfn_qk_norm_forward(e.qkv, static_cast<float*>(e.rstd), rows, Hq, Hkv, HD, e.qkv_ld, c.qk_norm_eps, q_scale, e.stream));
       } else if (q_scale != 1.f && c.qk_norm != 2) {
@@ -225,10 +241,15 @@ int forward_layers(nfn_engine& e, int rows, bool decode, int slot, const int* d_
         K(nfn_qk_norm_rope_forward(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, qw, kw, e.cosT, e.sinT, static_cast<const int*>(e.zero_pos), c.max_seq, sign,
                                    c.qk_norm_eps, q_scale, nullptr, e.stream));
       }
-      const char* q = static_cast<const char*>(e.qkv);
-      K(nfn_attention_forward(q, q + (size_t)Hq * HD * 2, q + (size_t)(Hq + Hkv) * HD * 2, e.att, nullptr, 1, rows, Hq, Hkv, HD, e.qkv_ld,
-                              e.qkv_ld, e.qkv_ld, ATT, 1, local ? c.window : 0, scale, e.stream));
-      K(nfn_kv_cache_write(e.qkv, e.qkv_ld, kc + (size_t)slot * cache_stride * 2, vc + (size_t)slot * cache_stride * 2, rows, Hq, Hkv, HD, cap, 0, e.stream));
+      if (block_rows > 0) {
+        K(nfn_block_attention(e.qkv, e.qkv_ld, kc, vc, d_lengths, d_block_live, e.att, ATT, e.stage_k[l], e.stage_v[l], c.max_batch, block_rows, Hq,
+                              Hkv, HD, cap, local ? cap : 0, 1, scale, e.blk_ws, e.blk_ws_bytes, 0, e.stream));
+      } else {
+        const char* q = static_cast<const char*>(e.qkv);
+        K(nfn_attention_forward(q, q + (size_t)Hq * HD * 2, q + (size_t)(Hq + Hkv) * HD * 2, e.att, nullptr, 1, rows, Hq, Hkv, HD, e.qkv_ld,
+                                e.qkv_ld, e.qkv_ld, ATT, 1, local ? c.window : 0, scale, e.stream));
+        K(nfn_kv_cache_write(e.qkv, e.qkv_ld, kc + (size_t)slot * cache_stride * 2, vc + (size_t)slot * cache_stride * 2, rows, Hq, Hkv, HD, cap, 0, e.stream));
+      }
     }
     if (c.family == 0) {
       if (gemm(e, e.att, ATT, e.W(gname(l, "attn.c_proj.weight")), e.x, C, rows, C, ATT, 0, e.W(gname(l, "attn.c_proj.bias")), e.x, C)) return -1;
@@ -262,7 +283,7 @@ int forward_layers(nfn_engine& e, int rows, bool decode, int slot, const int* d_
 }
 
 // final norm of rows [row0, row0 + n) -> logits[n, padded_vocab]
-int head(nfn_engine& e, int row0, int n) {
+int head(nfn_engine& e, int row0, int n, void* logits_dst = nullptr) {
   const nfn_engine_config& c = e.c;
   const int C = c.d_model;
   const char* xin = static_cast<const char*>(e.x) + (size_t)row0 * C * 2;
@@ -273,7 +294,7 @@ int head(nfn_engine& e, int row0, int n) {
   const void* wh = c.family == 0 ? e.W("wte") : (c.tie_embeddings ? e.W("tok_embeddings") : e.W("lm_head"));
   const int flags = c.logit_softcap > 0.f ? (NFN_ACT_TANH_CAP << NFN_EPI_ACT_SHIFT) : 0;
   const float mult = (c.family == 1 && c.output_multiplier > 0.f) ? c.output_multiplier : 1.f;
-  return gemm(e, e.xn, C, wh, e.logits, c.padded_vocab, n, c.padded_vocab, C, flags, nullptr, nullptr, 0, c.logit_softcap, mult);
+  return gemm(e, e.xn, C, wh, logits_dst ? logits_dst : e.logits, c.padded_vocab, n, c.padded_vocab, C, flags, nullptr, nullptr, 0, c.logit_softcap, mult);
 }
 
 int sample(nfn_engine& e, int rows, const float* d_row_params, const unsigned long long* d_offset, int* d_out) {
@@ -342,6 +363,8 @@ nfn_engine* nfn_engine_create(const nfn_engine_config* cfg, int device) {
   build_expected(*e);
   e->len.assign(c.max_batch, 0);
   e->logit_row.assign(c.max_batch, 0);
+  e->logit_src.assign(c.max_batch, 0);
+  e->h_vrows.assign(c.max_batch, 0);
   return e.release();
 }
 
@@ -527,6 +550,7 @@ int nfn_engine_prefill(nfn_engine* e, int slot, const int32_t* tokens, int n, co
   *next_token = *reinterpret_cast<int*>(e->h_io + e->io.out_tokens);
   e->len[slot] = n;
   e->logit_row[slot] = 0;
+  e->logit_src[slot] = 0;
   e->launches += nfn_launch_count() - before;
   if (nfn_status_peek() != 0) return efail("engine_prefill: a kernel reported error code " + std::to_string(nfn_status_read_reset()));
   return 0;
@@ -589,6 +613,7 @@ int nfn_engine_decode(nfn_engine* e, const int32_t* tokens_in, const uint8_t* ac
       next_tokens[b] = out[b];
       e->len[b] += 1;
       e->logit_row[b] = b;
+      e->logit_src[b] = 0;
     }
   if (nfn_status_peek() != 0) return efail("engine_decode: a kernel reported error code " + std::to_string(nfn_status_read_reset()));
   return 0;
@@ -598,11 +623,177 @@ int nfn_engine_last_logits(nfn_engine* e, int slot, float* out_vocab) {
   if (!e || !out_vocab || slot < 0 || slot >= e->c.max_batch || !e->finalized) return efail("engine_last_logits: bad arguments");
   CU(cudaSetDevice(e->device));
   std::vector<uint16_t> tmp(e->c.vocab);
-  CU(cudaMemcpy(tmp.data(), static_cast<const char*>(e->logits) + (size_t)e->logit_row[slot] * e->c.padded_vocab * 2, tmp.size() * 2, cudaMemcpyDeviceToHost));
+  const char* src = static_cast<const char*>(e->logit_src[slot] ? e->logits_v : e->logits);
+  CU(cudaMemcpy(tmp.data(), src + (size_t)e->logit_row[slot] * e->c.padded_vocab * 2, tmp.size() * 2, cudaMemcpyDeviceToHost));
   for (int i = 0; i < e->c.vocab; ++i) {
     const uint32_t bits = (uint32_t)tmp[i] << 16;
     std::memcpy(&out_vocab[i], &bits, 4);
   }
+  return 0;
+}
+
+// ---- block verification, commit, truncate, fork -------------------------------------------------
+
+int nfn_engine_enable_verify(nfn_engine* e, int max_rows) {
+  if (!e || !e->finalized) return efail("engine_enable_verify: finalize the engine first");
+  if (e->v_rows_max > 0) return max_rows <= e->v_rows_max ? 0 : efail("engine_enable_verify: already enabled with fewer rows");
+  const nfn_engine_config& c = e->c;
+  if (max_rows < 1 || max_rows > 128) return efail("engine_enable_verify: 1 <= max_rows <= 128");
+  if ((long long)c.max_batch * max_rows > e->rows_max)
+    return efail("engine_enable_verify: max_batch * max_rows exceeds the activation rows (max(max_seq, max_batch))");
+  CU(cudaSetDevice(e->device));
+  const long long B = c.max_batch, rows = B * max_rows, kvw = (long long)c.n_kv_head * c.head_dim;
+  e->stage_k.assign(c.n_layer, nullptr);
+  e->stage_v.assign(c.n_layer, nullptr);
+  for (int l = 0; l < c.n_layer; ++l)
+    if (e->alloc(&e->stage_k[l], rows * kvw * 2) || e->alloc(&e->stage_v[l], rows * kvw * 2)) return -1;
+  std::vector<void*> tab;
+  tab.insert(tab.end(), e->stage_k.begin(), e->stage_k.end());
+  tab.insert(tab.end(), e->stage_v.begin(), e->stage_v.end());
+  tab.insert(tab.end(), e->kc.begin(), e->kc.end());
+  tab.insert(tab.end(), e->vc.begin(), e->vc.end());
+  if (e->alloc((void**)&e->d_tables, (long long)tab.size() * sizeof(void*)) || e->alloc((void**)&e->d_caps, (long long)c.n_layer * 4)) return -1;
+  CU(cudaMemcpy(e->d_tables, tab.data(), tab.size() * sizeof(void*), cudaMemcpyHostToDevice));
+  CU(cudaMemcpy(e->d_caps, e->cap.data(), (size_t)c.n_layer * 4, cudaMemcpyHostToDevice));
+  if (e->alloc(&e->logits_v, rows * c.padded_vocab * 2)) return -1;
+  e->blk_ws_bytes = nfn_block_attention_workspace_bytes(c.max_batch, std::min(max_rows, 32), c.n_head, c.n_kv_head, c.head_dim, 8);
+  if (e->blk_ws_bytes <= 0) return efail("engine_enable_verify: bad attention geometry");
+  if (e->alloc(&e->blk_ws, e->blk_ws_bytes)) return -1;
+  CU(cudaMemset(e->blk_ws, 0, (size_t)e->blk_ws_bytes));
+  if (e->alloc((void**)&e->d_vtok, rows * 4) || e->alloc((void**)&e->d_vpos, rows * 4) || e->alloc((void**)&e->d_vout, rows * 4) ||
+      e->alloc((void**)&e->d_vlen, B * 4) || e->alloc((void**)&e->d_vrows, B * 4) || e->alloc(&e->argmax_ws, rows * 512))
+    return -1;
+  e->v_rows_max = max_rows;
+  return 0;
+}
+
+int nfn_engine_verify(nfn_engine* e, const int32_t* tokens, const int32_t* n_rows, int rows, int32_t* argmax_out) {
+  if (!e || !tokens || !n_rows || !argmax_out) return efail("engine_verify: null argument");
+  if (e->v_rows_max <= 0) return efail("engine_verify: call nfn_engine_enable_verify first");
+  if (rows < 1 || rows > e->v_rows_max) return efail("engine_verify: rows outside [1, max_rows]");
+  const nfn_engine_config& c = e->c;
+  const int B = c.max_batch, total = B * rows;
+  CU(cudaSetDevice(e->device));
+  std::vector<int> tok(total, 0), pos(total, 0), len(B, 0), live(B, 0);
+  int any = 0;
+  for (int b = 0; b < B; ++b) {
+    const int n = n_rows[b];
+    if (n < 0 || n > rows) return efail("engine_verify: n_rows[slot] outside [0, rows]");
+    if (n > 0 && e->len[b] + n > c.max_seq) return efail("engine_verify: slot " + std::to_string(b) + " would pass max_seq");
+    live[b] = n;
+    len[b] = e->len[b];
+    any += n;
+    for (int r = 0; r < rows; ++r) {
+      tok[b * rows + r] = r < n ? tokens[b * rows + r] : 0;
+      pos[b * rows + r] = std::min(e->len[b] + r, c.max_seq - 1);
+    }
+  }
+  if (!any) return 0;
+  const long long before = nfn_launch_count();
+  CU(cudaMemcpyAsync(e->d_vtok, tok.data(), (size_t)total * 4, cudaMemcpyHostToDevice, e->stream));
+  CU(cudaMemcpyAsync(e->d_vpos, pos.data(), (size_t)total * 4, cudaMemcpyHostToDevice, e->stream));
+  CU(cudaMemcpyAsync(e->d_vlen, len.data(), (size_t)B * 4, cudaMemcpyHostToDevice, e->stream));
+  CU(cudaMemcpyAsync(e->d_vrows, live.data(), (size_t)B * 4, cudaMemcpyHostToDevice, e->stream));
+  CU(cudaStreamSynchronize(e->stream));  // the host vectors leave scope at return; also orders after earlier steps
+  if (c.family == 0)
+    K(nfn_embedding_positions(e->d_vtok, e->d_vpos, e->W("wte"), e->W("wpe"), e->x, total, c.d_model, c.vocab, c.max_seq, c.embed_scale, e->stream));
+  else
+    K(nfn_embedding_positions(e->d_vtok, nullptr, e->W("tok_embeddings"), nullptr, e->x, total, c.d_model, c.vocab, c.max_seq, c.embed_scale, e->stream));
+  if (c.family == 1 && c.embed_norm) K(nfn_norm_forward(e->x, e->ones, nullptr, e->x, nullptr, nullptr, total, c.d_model, c.norm_eps, 1, 0, e->stream));
+  if (forward_layers(*e, total, false, 0, e->d_vlen, rows, e->d_vpos, e->d_vrows)) return -1;
+  if (head(*e, 0, total, e->logits_v)) return -1;
+  K(nfn_argmax_rows(e->logits_v, 0, c.padded_vocab, total, c.vocab, e->d_vout, nullptr, e->argmax_ws, (long long)B * e->v_rows_max * 512, 0, e->stream));
+  CU(cudaMemcpyAsync(argmax_out, e->d_vout, (size_t)total * 4, cudaMemcpyDeviceToHost, e->stream));
+  CU(cudaStreamSynchronize(e->stream));
+  e->v_rows = rows;
+  e->h_vrows = live;
+  e->launches += nfn_launch_count() - before;
+  if (nfn_status_peek() != 0) return efail("engine_verify: a kernel reported error code " + std::to_string(nfn_status_read_reset()));
+  return 0;
+}
+
+int nfn_engine_verify_logits(nfn_engine* e, int slot, int row, float* out_vocab) {
+  if (!e || !out_vocab || e->v_rows <= 0 || slot < 0 || slot >= e->c.max_batch || row < 0 || row >= e->h_vrows[slot])
+    return efail("engine_verify_logits: no such verification row");
+  CU(cudaSetDevice(e->device));
+  std::vector<uint16_t> tmp(e->c.vocab);
+  CU(cudaMemcpy(tmp.data(), static_cast<const char*>(e->logits_v) + ((size_t)slot * e->v_rows + row) * e->c.padded_vocab * 2, tmp.size() * 2,
+                cudaMemcpyDeviceToHost));
+  for (int i = 0; i < e->c.vocab; ++i) {
+    const uint32_t bits = (uint32_t)tmp[i] << 16;
+    std::memcpy(&out_vocab[i], &bits, 4);
+  }
+  return 0;
+}
+
+int nfn_engine_commit(nfn_engine* e, const int32_t* accepted) {
+  if (!e || !accepted) return efail("engine_commit: null argument");
+  if (e->v_rows <= 0) return efail("engine_commit: no verification to commit");
+  const nfn_engine_config& c = e->c;
+  const int B = c.max_batch, L = c.n_layer;
+  CU(cudaSetDevice(e->device));
+  std::vector<int> acc(B, 0);
+  int any = 0;
+  for (int b = 0; b < B; ++b) {
+    if (accepted[b] < 0 || accepted[b] > e->h_vrows[b]) return efail("engine_commit: accepted[slot] outside [0, verified rows]");
+    acc[b] = accepted[b];
+    any += acc[b];
+  }
+  if (any) {
+    // d_vlen still holds the lengths the verification ran at; d_vrows is reused for the accepted counts
+    CU(cudaMemcpyAsync(e->d_vrows, acc.data(), (size_t)B * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    const long long before = nfn_launch_count();
+    K(nfn_kv_commit_layers(e->d_tables, e->d_tables + L, e->d_tables + 2 * L, e->d_tables + 3 * L, e->d_caps, e->d_vlen, e->d_vrows, L, B, e->v_rows,
+                           c.n_kv_head, c.head_dim, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    e->launches += nfn_launch_count() - before;
+  }
+  for (int b = 0; b < B; ++b)
+    if (acc[b] > 0) {
+      e->logit_row[b] = b * e->v_rows + acc[b] - 1;
+      e->logit_src[b] = 1;
+      e->len[b] += acc[b];
+    }
+  std::fill(e->h_vrows.begin(), e->h_vrows.end(), 0);  // a verification commits once
+  return 0;
+}
+
+// A ring cache keeps only the newest `cap` positions: once it has wrapped, the rows an earlier
+// length would need have been overwritten, so such a slot can only be truncated to its own length.
+static bool ring_prefix_intact(const nfn_engine& e, int slot, int n) {
+  if (n == e.len[slot]) return true;
+  for (int l = 0; l < e.c.n_layer; ++l)
+    if (layer_is_local(e.c, l) && e.len[slot] > e.cap[l]) return false;
+  return true;
+}
+
+int nfn_engine_truncate(nfn_engine* e, int slot, int n) {
+  if (!e || slot < 0 || slot >= e->c.max_batch) return efail("engine_truncate: bad slot");
+  if (n < 0 || n > e->len[slot]) return efail("engine_truncate: length outside [0, current length]");
+  if (n > 0 && !ring_prefix_intact(*e, slot, n)) return efail("engine_truncate: a sliding-window cache of this slot has wrapped; only a reset is possible");
+  e->len[slot] = n;
+  return 0;
+}
+
+int nfn_engine_fork(nfn_engine* e, int src_slot, int dst_slot, int n) {
+  if (!e || !e->finalized) return efail("engine_fork: engine not ready");
+  const nfn_engine_config& c = e->c;
+  if (src_slot < 0 || src_slot >= c.max_batch || dst_slot < 0 || dst_slot >= c.max_batch || src_slot == dst_slot) return efail("engine_fork: bad slots");
+  if (n < 0 || n > e->len[src_slot]) return efail("engine_fork: prefix longer than the source");
+  if (n > 0 && !ring_prefix_intact(*e, src_slot, n)) return efail("engine_fork: a sliding-window cache of the source has wrapped past this prefix");
+  CU(cudaSetDevice(e->device));
+  for (int l = 0; l < c.n_layer && n > 0; ++l) {
+    // rows [0, min(n, cap)) of every kv head; whole-slot copy when most of it is live
+    const size_t head_bytes = (size_t)e->cap[l] * c.head_dim * 2, slot_bytes = head_bytes * c.n_kv_head;
+    const size_t live = (size_t)std::min(n, e->cap[l]) * c.head_dim * 2;
+    char* kc = static_cast<char*>(e->kc[l]);
+    char* vc = static_cast<char*>(e->vc[l]);
+    CU(cudaMemcpy2DAsync(kc + dst_slot * slot_bytes, head_bytes, kc + src_slot * slot_bytes, head_bytes, live, c.n_kv_head, cudaMemcpyDeviceToDevice, e->stream));
+    CU(cudaMemcpy2DAsync(vc + dst_slot * slot_bytes, head_bytes, vc + src_slot * slot_bytes, head_bytes, live, c.n_kv_head, cudaMemcpyDeviceToDevice, e->stream));
+  }
+  CU(cudaStreamSynchronize(e->stream));
+  e->len[dst_slot] = n;
   return 0;
 }
 

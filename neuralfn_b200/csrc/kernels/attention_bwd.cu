@@ -71,9 +71,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* bar_kv = bars;            // 1
   uint64_t* bar_qdo = bars + 1;       // STAGES (<= 2)
   uint64_t* bar_sdp = bars + 3;       // S^T and dP^T complete
-  uint64_t* bar_pds = bars + 4;       // 128 arrivals: P^T and dS^T in shared memory
+  uint64_t* bar_pds = bars + 4;       // 4 arrivals (one per warp): P^T and dS^T in shared memory
   uint64_t* bar_out = bars + 5;       // dV/dK/dQ products retired
-  uint64_t* bar_dqfree = bars + 6;    // 128 arrivals: dQ tile read out of TMEM
+  uint64_t* bar_dqfree = bars + 6;    // 4 arrivals (one per warp): dQ tile read out of TMEM
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -101,9 +101,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(smem_u32(&bar_qdo[0]), 1);
     mbar_init(smem_u32(&bar_qdo[1]), 1);
     mbar_init(smem_u32(bar_sdp), 1);
-    mbar_init(smem_u32(bar_pds), 128);
+    mbar_init(smem_u32(bar_pds), 4);  // one arrival per softmax warp
     mbar_init(smem_u32(bar_out), 1);
-    mbar_init(smem_u32(bar_dqfree), 128);
+    mbar_init(smem_u32(bar_dqfree), 4);  // one arrival per softmax warp
     fence_mbar_init();
   }
   if (warp == 4) {
@@ -292,7 +292,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(smem_u32(bar_pds));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(bar_pds));
       // dQ tile: lane r == query row q0 + r
       ok = mbar_wait_bounded(smem_u32(bar_out), s & 1, cta_abort, p.status, NFN_ERR_WAIT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
@@ -315,7 +316,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(bar_dqfree));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(bar_dqfree));
     }
     // dK / dV leave TMEM once
     if (ok && nsteps > 0) {

@@ -79,7 +79,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* bar_q = bars;          // 1
   uint64_t* bar_kv = bars + 1;     // 2
   uint64_t* bar_s = bars + 3;      // 1
-  uint64_t* bar_p = bars + 4;      // 1 (128 arrivals)
+  uint64_t* bar_p = bars + 4;      // 4 arrivals (one per softmax warp)
   uint64_t* bar_o = bars + 5;      // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -109,7 +109,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(smem_u32(&bar_kv[0]), 1);
     mbar_init(smem_u32(&bar_kv[1]), 1);
     mbar_init(smem_u32(bar_s), 1);
-    mbar_init(smem_u32(bar_p), 128);
+    mbar_init(smem_u32(bar_p), 4);  // one arrival per softmax warp
     mbar_init(smem_u32(bar_o), 1);
     fence_mbar_init();
   }
@@ -288,7 +288,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(smem_u32(bar_p));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(bar_p));
       // rescale the running state while the PV product runs
       l_run = l_run * alpha + l_blk;
       m_run = m_new;

@@ -9,7 +9,7 @@
 //   warp 0 (each CTA)   TMA producer: A rows [m0 + 128 r, +128), B rows [n0 + 128 r, +128) with
 //                       cta_group::2 loads whose transaction bytes count on the LEADER's barrier
 //   warp 1 (leader)     MMA issuer; commits are multicast to both CTAs' barriers
-//   warps 2..5 (each)   epilogue of the CTA's own 128 rows (same fused epilogue / TMA-store
+//   warps 2..9 (each)   epilogue of the CTA's own 128 rows (same fused epilogue / TMA-store
 //                       path as the 1-CTA kernel); the peer releases the accumulator with a
 //                       remote mbarrier arrive on the leader's barrier
 //
@@ -25,7 +25,7 @@ namespace nfn {
 constexpr int P2_BM = 128;          // rows per CTA (256 per pair)
 constexpr int P2_BN = 256;          // columns per pair tile; each CTA stages 128 of the B rows
 constexpr int P2_BK = 64;
-constexpr int P2_THREADS = 192;
+constexpr int P2_THREADS = 320;
 constexpr int P2_STAGES = 6;
 constexpr uint32_t P2_EPI_TILE = 128 * 64 * 2;
 
@@ -111,9 +111,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&tfull_bar[b]), 1);   // multicast commit, in each CTA
-      mbar_init(smem_u32(&tempty_bar[b]), 8);  // leader's copy: 4 epilogue warps of each CTA
+      mbar_init(smem_u32(&tempty_bar[b]), 16);  // leader's copy: 8 epilogue warps of each CTA
     }
-    mbar_init(smem_u32(epi_bar), 128);
+    mbar_init(smem_u32(epi_bar), 8);
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
@@ -138,8 +138,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
-        const int m0 = (tile % p.tiles_m) * (2 * BM) + (int)rank * BM;
-        const int nb0 = (tile / p.tiles_m) * BN + (int)rank * (BN / 2);
+        int tm, tn;
+        tile_mn(p, tile, tm, tn);
+        const int m0 = tm * (2 * BM) + (int)rank * BM;
+        const int nb0 = tn * BN + (int)rank * (BN / 2);
         for (int kb = 0; kb < total_kb; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1, cta_abort, p.status, NFN_ERR_WAIT_EMPTY)) {
             ok = false;
@@ -189,7 +191,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     const uint32_t tempty_leader1 = mapa_shared(smem_u32(&tempty_bar[1]), 0);
 #define EPI_TILE_FIRST pair
 #define EPI_TILE_STEP n_pairs
-#define EPI_TILE_M0(t2) (((t2) % p.tiles_m) * (2 * BM) + (int)rank * BM)
+#define EPI_TILE_M0(tm) ((tm) * (2 * BM) + (int)rank * BM)
 #define EPI_RELEASE_ACC(acc) mbar_arrive_cluster((acc) ? tempty_leader1 : tempty_leader0)
 #include "gemm_epilogue_body.inc"
 #undef EPI_TILE_FIRST
@@ -269,6 +271,7 @@ int try_launch_gemm_pair(const nfn_gemm_args& a, cudaStream_t stream) {
   p.kb_per_split = ceil_div(a.k, P2_BK);
   p.split_stride = 0;
   p.status = status_ptr();
+  p.raster_gw = pick_raster_gw(a.m, a.k, p.tiles_n);
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = std::min(max_pairs[dev & 63], tiles);
   gemm_bf16_pair_kernel<<<2 * pairs, P2_THREADS, SMEM, stream>>>(ta, tb, tc, tx, p);

@@ -22,7 +22,33 @@ struct GemmParams {
   int kb_per_split;   // k-blocks handled by one split
   long long split_stride;  // elements between consecutive split slices of the fp32 workspace
   int* status;
+  int raster_gw;      // tile order: bands of this many n-tiles, n fastest inside a band (1 = m fastest)
 };
+
+// Tile index -> (m-tile, n-tile). CTAs that run at the same time hold consecutive indices, so a
+// band of `raster_gw` n-tiles shares each A row panel while it is still in L2; with a band of 1
+// the order is m-fastest and consecutive CTAs share the B tile instead.
+__device__ __forceinline__ void tile_mn(const GemmParams& p, int t2, int& tm, int& tn) {
+  if (p.raster_gw <= 1) {
+    tm = t2 % p.tiles_m;
+    tn = t2 / p.tiles_m;
+    return;
+  }
+  const int band_tiles = p.raster_gw * p.tiles_m;
+  const int band = t2 / band_tiles, r = t2 - band * band_tiles;
+  const int n_first = band * p.raster_gw;
+  const int w = min(p.raster_gw, p.tiles_n - n_first);
+  tm = r / w;
+  tn = n_first + r % w;
+}
+
+// Band width for a product with an [M, K] A operand and `tiles_n` column tiles: when A does not
+// fit in L2 beside everything else, walk n first so that every A panel is fetched from HBM once.
+inline int pick_raster_gw(long long m, long long k, int tiles_n) {
+  const long long a_bytes = m * k * 2;
+  if (tiles_n <= 1 || a_bytes <= (40ll << 20)) return 1;
+  return tiles_n < 8 ? tiles_n : 8;
+}
 
 __device__ __forceinline__ void act8(float (&v)[8], int act, float prm) {
   if (act == NFN_ACT_GELU_TANH) {

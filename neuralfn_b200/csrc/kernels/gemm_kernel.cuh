@@ -2,7 +2,7 @@
 //
 //   warp 0      : TMA producer   (one lane issues cp.async.bulk.tensor tile loads)
 //   warp 1      : MMA issuer     (one lane issues tcgen05.mma; owns the TMEM allocation)
-//   warps 2..5  : epilogue       (tcgen05.ld accumulator -> fused epilogue -> global)
+//   warps 2..9  : epilogue       (tcgen05.ld accumulator -> fused epilogue -> global)
 //
 // Tiles are 128 x BN x 64 with a STAGES-deep shared-memory ring (128-byte swizzle,
 // filled by TMA, consumed by tcgen05.mma through shared-memory matrix descriptors).
@@ -19,7 +19,7 @@ namespace nfn {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;
 constexpr int EPI_CHUNK = 64;                       // columns per staged chunk
 constexpr uint32_t EPI_TILE_BYTES = BM * EPI_CHUNK * 2;  // 16 KB
 
@@ -43,7 +43,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   uint64_t* empty_bar = bars + STAGES;
   uint64_t* tfull_bar = bars + 2 * STAGES;
   uint64_t* tempty_bar = bars + 2 * STAGES + 2;
-  uint64_t* epi_bar = bars + 2 * STAGES + 4;  // 128 arrivals: epilogue-wide sync with a bounded wait
+  uint64_t* epi_bar = bars + 2 * STAGES + 4;  // 8 arrivals (one per epilogue warp): epilogue-wide sync with a bounded wait
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -58,9 +58,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&tfull_bar[b]), 1);
-      mbar_init(smem_u32(&tempty_bar[b]), 4);
+      mbar_init(smem_u32(&tempty_bar[b]), 8);
     }
-    mbar_init(smem_u32(epi_bar), 128);
+    mbar_init(smem_u32(epi_bar), 8);
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
@@ -85,8 +85,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int sp = tile / tiles_mn, t2 = tile % tiles_mn;
-        const int m0 = (t2 % p.tiles_m) * BM;
-        const int n0 = (t2 / p.tiles_m) * BN;
+        int tm, tn;
+        tile_mn(p, t2, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
         const int kb_lo = sp * p.kb_per_split;
         const int kb_hi = min(total_kb, kb_lo + p.kb_per_split);
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
@@ -167,7 +168,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   } else {
 #define EPI_TILE_FIRST ((int)blockIdx.x)
 #define EPI_TILE_STEP ((int)gridDim.x)
-#define EPI_TILE_M0(t2) (((t2) % p.tiles_m) * BM)
+#define EPI_TILE_M0(tm) ((tm) * BM)
 #define EPI_RELEASE_ACC(acc) mbar_arrive(smem_u32(&tempty_bar[acc]))
 #include "gemm_epilogue_body.inc"
 #undef EPI_TILE_FIRST

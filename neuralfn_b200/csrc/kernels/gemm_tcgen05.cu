@@ -87,6 +87,7 @@ static int launch_gemm(const nfn_gemm_args& a, int split_k, cudaStream_t stream)
   p.kb_per_split = ceil_div(a.k, BK);
   p.split_stride = 0;
   p.status = status_ptr();
+  p.raster_gw = A_MN ? 1 : pick_raster_gw(a.m, a.k, p.tiles_n);
 
   const bool out_f32 = a.flags & NFN_EPI_OUT_F32;
   const bool accum = a.flags & NFN_EPI_ACCUM;

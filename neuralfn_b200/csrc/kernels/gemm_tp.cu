@@ -180,7 +180,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       mbar_init(smem_u32(&tfull_bar[b]), 1);
       mbar_init(smem_u32(&tempty_bar[b]), 4);
     }
-    mbar_init(smem_u32(epi_bar), 128);
+    mbar_init(smem_u32(epi_bar), 4);  // one arrival per epilogue warp
     fence_mbar_init();
   }
   if (!is_copy_cta && warp == 1) {
@@ -329,7 +329,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     bool epi_ok = true;
     auto epi_sync = [&]() {
       __syncwarp();
-      mbar_arrive(smem_u32(epi_bar));
+      if (lane == 0) mbar_arrive(smem_u32(epi_bar));
       bool w = mbar_wait_bounded(smem_u32(epi_bar), epi_phase, cta_abort, p.status, NFN_ERR_WAIT_MISC);
       epi_phase ^= 1;
       w = __all_sync(0xffffffffu, w);

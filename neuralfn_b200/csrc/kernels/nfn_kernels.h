@@ -156,6 +156,26 @@ int nfn_decode_attention(const void* qkv, int ld, void* k_cache, void* v_cache, 
                          const float* cos_table, const float* sin_table, int max_pos, float rope_sign, float scale,
                          void* workspace, long long workspace_bytes, int splits, nfn_stream_t stream);
 
+// ---- block attention over a KV cache (block_attention.cu) ------------------------------------------
+// `rows` (<= 128) new rows per sequence attend to the sequence's cached keys plus the block's own
+// keys; the caches are only read. qkv: [B*rows, ld] packed q | k | v (norm / rotary already
+// applied); caches [B][n_kv_heads][cap][head_dim]; lengths[b] = tokens already cached (the block
+// starts at that position); n_rows (optional) = live rows per sequence, 0 skips the sequence.
+// window = 0: every cached key is visible; otherwise keys inside (q - window, q] (window <= cap).
+// causal = 0 lets every block row see the whole block (draft blocks). stage_k / stage_v
+// (optional, [B*rows, n_kv_heads*head_dim]) receive the block's own K / V rows for a later
+// nfn_kv_commit_layers. splits = 0 picks the KV split count.
+long long nfn_block_attention_workspace_bytes(int B, int rows, int n_q_heads, int n_kv_heads, int head_dim, int max_splits);
+int nfn_block_attention(const void* qkv, int ld, const void* k_cache, const void* v_cache, const int* lengths, const int* n_rows,
+                        void* out, int ld_o, void* stage_k, void* stage_v, int B, int rows, int n_q_heads, int n_kv_heads,
+                        int head_dim, int cap, int window, int causal, float scale, void* workspace, long long workspace_bytes,
+                        int splits, nfn_stream_t stream);
+// Appends the first accepted[b] staged rows of every layer to that layer's cache at positions
+// lengths[b] ... (ring rows position % caps[layer]). All pointer arrays live in device memory.
+int nfn_kv_commit_layers(const void* const* stage_k, const void* const* stage_v, void* const* k_caches, void* const* v_caches,
+                         const int* caps, const int* lengths, const int* accepted, int n_layers, int B, int rows, int n_kv_heads,
+                         int head_dim, nfn_stream_t stream);
+
 // ---- quantised weights (quant.cu) ---------------------------------------------------------------
 enum { NFN_QTYPE_Q4_K = 12, NFN_QTYPE_Q5_K = 13, NFN_QTYPE_Q6_K = 14 };  // GGUF type ids
 int nfn_quant_block_bytes(int qtype);

@@ -15,7 +15,8 @@ from . import _lib
 _bf16 = torch.bfloat16
 
 __all__ = ["rope_tables", "rope_inplace", "qk_norm_rope_forward", "argmax_rows", "argmax_merge", "sample_rows",
-           "DecodeAttentionWorkspace", "decode_attention", "dequant_kquant", "dequant_nf4", "kquant_gemv", "quant_block_bytes"]
+           "DecodeAttentionWorkspace", "decode_attention", "BlockAttentionWorkspace", "block_attention", "kv_commit_layers",
+           "dequant_kquant", "dequant_nf4", "kquant_gemv", "quant_block_bytes"]
 
 
 def _p(t) -> c_void_p:
@@ -130,6 +131,52 @@ def decode_attention(qkv, k_cache, v_cache, lengths, *, n_q_heads: int, n_kv_hea
         c_float(scale), _p(workspace.buf), c_longlong(workspace.buf.numel()), c_int(splits), _st())
     _lib.check(rc, "nfn_decode_attention")
     return out
+
+
+class BlockAttentionWorkspace:
+    """Zero-initialised scratch for ``block_attention`` (tickets + per-split partials)."""
+
+    def __init__(self, B: int, rows: int, n_q_heads: int, n_kv_heads: int, head_dim: int, device, max_splits: int = 16) -> None:
+        n = _lib.load().nfn_block_attention_workspace_bytes
+        n.restype = c_longlong
+        nbytes = n(c_int(B), c_int(rows), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(max_splits))
+        if nbytes <= 0:
+            raise ValueError("bad block attention geometry")
+        self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+
+
+def block_attention(qkv, k_cache, v_cache, lengths, *, rows: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                    workspace: BlockAttentionWorkspace, window: int = 0, causal: bool = True, n_rows=None, stage_k=None, stage_v=None,
+                    scale: float | None = None, splits: int = 0, out=None):
+    """``rows`` new rows per sequence against the cached keys plus the block itself; the caches are
+    not written. qkv bf16 [B*rows, >= (Hq+2Hkv)*D] (norm / rotary applied); caches bf16
+    [B, Hkv, cap, D]; lengths int32 [B] = tokens already cached. Returns bf16 [B*rows, Hq*D]."""
+    B = k_cache.shape[0]
+    assert qkv.shape[0] == B * rows and k_cache.dtype == _bf16 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert lengths.dtype == torch.int32 and (n_rows is None or n_rows.dtype == torch.int32)
+    cap = k_cache.shape[2]
+    out = torch.empty(B * rows, n_q_heads * head_dim, dtype=_bf16, device=qkv.device) if out is None else out
+    scale = head_dim ** -0.5 if scale is None else scale
+    rc = _lib.load().nfn_block_attention(
+        _p(qkv), c_int(qkv.stride(0)), _p(k_cache), _p(v_cache), _p(lengths), _p(n_rows), _p(out), c_int(out.stride(0)), _p(stage_k),
+        _p(stage_v), c_int(B), c_int(rows), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(cap), c_int(window),
+        c_int(int(causal)), c_float(scale), _p(workspace.buf), c_longlong(workspace.buf.numel()), c_int(splits), _st())
+    _lib.check(rc, "nfn_block_attention")
+    return out
+
+
+def kv_commit_layers(stage_k: list, stage_v: list, k_caches: list, v_caches: list, lengths, accepted, *, rows: int) -> None:
+    """Appends the first ``accepted[b]`` staged rows of every layer to that layer's cache
+    (ring rows ``position % cap``). One launch for all layers."""
+    dev = lengths.device
+    B, Hkv, _, D = k_caches[0].shape
+    ptrs = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)  # noqa: E731
+    caps = torch.tensor([t.shape[2] for t in k_caches], dtype=torch.int32, device=dev)
+    sk, sv, kc, vc = ptrs(stage_k), ptrs(stage_v), ptrs(k_caches), ptrs(v_caches)
+    rc = _lib.load().nfn_kv_commit_layers(_p(sk), _p(sv), _p(kc), _p(vc), _p(caps), _p(lengths), _p(accepted), c_int(len(k_caches)),
+                                          c_int(B), c_int(rows), c_int(Hkv), c_int(D), _st())
+    _lib.check(rc, "nfn_kv_commit_layers")
+    torch.cuda.current_stream().synchronize()  # the pointer tables above must outlive the launch
 
 
 def swiglu_forward(gate_up: torch.Tensor, inter: int, out=None) -> torch.Tensor:

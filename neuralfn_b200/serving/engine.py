@@ -129,6 +129,12 @@ def _api():
     L.nfn_engine_slot_length.argtypes = [vp, ip]
     L.nfn_engine_last_logits.argtypes = [vp, ip, vp]
     L.nfn_engine_launches.restype, L.nfn_engine_launches.argtypes = C.c_longlong, [vp]
+    L.nfn_engine_enable_verify.argtypes = [vp, ip]
+    L.nfn_engine_verify.argtypes = [vp, vp, vp, ip, vp]
+    L.nfn_engine_verify_logits.argtypes = [vp, ip, ip, vp]
+    L.nfn_engine_commit.argtypes = [vp, vp]
+    L.nfn_engine_truncate.argtypes = [vp, ip, ip]
+    L.nfn_engine_fork.argtypes = [vp, ip, ip, ip]
     L._engine_ready = True
     return L
 
@@ -263,6 +269,61 @@ class ResidentEngine:
         out = torch.empty(self.config.vocab, dtype=torch.float32)
         self._check(self._L.nfn_engine_last_logits(self._h, slot, out.data_ptr()))
         return out
+
+    # ---- block verification / session operations ----------------------------------------------
+    def enable_verify(self, max_rows: int = 17) -> None:
+        """Allocates the staging buffers for ``verify`` / ``commit`` (once)."""
+        self._check(self._L.nfn_engine_enable_verify(self._h, max_rows))
+        self._verify_rows = max(max_rows, getattr(self, "_verify_rows", 0))
+
+    def verify(self, blocks: dict[int, Sequence[int]]) -> dict[int, list[int]]:
+        """Runs each slot's token block at the slot's current position without touching its KV
+        cache. Returns, per slot, the most likely successor after every block row."""
+        if not getattr(self, "_verify_rows", 0):
+            self.enable_verify()
+        B = self.config.max_batch
+        rows = max(len(v) for v in blocks.values())
+        tok = (C.c_int32 * (B * rows))()
+        live = (C.c_int32 * B)()
+        for slot, ids in blocks.items():
+            live[slot] = len(ids)
+            for r, t in enumerate(ids):
+                tok[slot * rows + r] = t
+        out = (C.c_int32 * (B * rows))()
+        self._check(self._L.nfn_engine_verify(self._h, C.cast(tok, C.c_void_p), C.cast(live, C.c_void_p), rows, C.cast(out, C.c_void_p)))
+        self._last_verify_rows = rows
+        return {slot: [int(out[slot * rows + r]) for r in range(len(ids))] for slot, ids in blocks.items()}
+
+    def verify_logits(self, slot: int, row: int) -> torch.Tensor:
+        out = torch.empty(self.config.vocab, dtype=torch.float32)
+        self._check(self._L.nfn_engine_verify_logits(self._h, slot, row, out.data_ptr()))
+        return out
+
+    def commit(self, accepted: dict[int, int]) -> None:
+        """Appends the first ``accepted[slot]`` rows of the last ``verify`` to the caches."""
+        acc = (C.c_int32 * self.config.max_batch)()
+        for slot, n in accepted.items():
+            acc[slot] = n
+        self._check(self._L.nfn_engine_commit(self._h, C.cast(acc, C.c_void_p)))
+
+    def append(self, slot: int, tokens: Sequence[int], chunk: int | None = None) -> int:
+        """Extends a slot that already holds tokens (``prefill`` only starts at position 0).
+        Returns the most likely next token."""
+        if not getattr(self, "_verify_rows", 0):
+            self.enable_verify()
+        chunk = min(chunk or self._verify_rows, self._verify_rows)
+        nxt = -1
+        for i in range(0, len(tokens), chunk):
+            part = list(tokens[i:i + chunk])
+            nxt = self.verify({slot: part})[slot][-1]
+            self.commit({slot: len(part)})
+        return nxt
+
+    def truncate(self, slot: int, n: int) -> None:
+        self._check(self._L.nfn_engine_truncate(self._h, slot, n))
+
+    def fork(self, src_slot: int, dst_slot: int, n: int | None = None) -> None:
+        self._check(self._L.nfn_engine_fork(self._h, src_slot, dst_slot, self.slot_length(src_slot) if n is None else n))
 
     def generate(self, prompts: Iterable[Sequence[int]], max_new_tokens: int = 32, sampling: Sampling | None = None,
                  eos_token: int | None = None) -> list[list[int]]:

@@ -210,3 +210,79 @@ def test_kquant_gemv(name, B, N, K, gated):
     got = infer.kquant_gemv(t, torch.from_numpy(raw1).to(dev).reshape(-1), x, N,
                             w_gate_pair=torch.from_numpy(raw2).to(dev).reshape(-1) if gated else None, bias=bias, resid=resid)
     torch.testing.assert_close(got.float(), ref, atol=0.05 * float(ref.abs().max()), rtol=2e-2)
+
+
+def _block_attention_ref(qkv, kc, vc, lengths, rows, Hq, Hkv, D, window, causal, n_rows):
+    """fp32 oracle: logical key list per sequence = cached positions still in the cache + block rows."""
+    B, _, cap, _ = kc.shape
+    G = Hq // Hkv
+    out = torch.zeros(B * rows, Hq * D, dtype=torch.float32, device=qkv.device)
+    q = qkv[:, :Hq * D].float().view(B, rows, Hq, D)
+    kb = qkv[:, Hq * D:(Hq + Hkv) * D].float().view(B, rows, Hkv, D)
+    vb = qkv[:, (Hq + Hkv) * D:(Hq + 2 * Hkv) * D].float().view(B, rows, Hkv, D)
+    for b in range(B):
+        pos0, nr = int(lengths[b]), rows if n_rows is None else int(n_rows[b])
+        if nr <= 0:
+            continue
+        first = max(0, pos0 - cap)
+        pos = torch.arange(first, pos0, device=qkv.device)
+        kk = torch.cat([kc[b, :, pos % cap].float(), kb[b, :nr].transpose(0, 1)], dim=1)  # [Hkv, n, D]
+        vv = torch.cat([vc[b, :, pos % cap].float(), vb[b, :nr].transpose(0, 1)], dim=1)
+        kpos = torch.cat([pos, pos0 + torch.arange(nr, device=qkv.device)])
+        for r in range(nr):
+            qp = pos0 + r
+            vis = torch.ones_like(kpos, dtype=torch.bool)
+            if causal:
+                vis &= kpos <= qp
+            if window > 0:
+                vis &= (kpos > qp - window) | (kpos >= pos0)
+            for h in range(Hq):
+                s = (kk[h // G] @ q[b, r, h]) * D ** -0.5
+                s = s.masked_fill(~vis, float("-inf"))
+                out[b * rows + r, h * D:(h + 1) * D] = torch.softmax(s, 0) @ vv[h // G]
+    return out
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,rows,cap,window,causal,splits", [
+    (64, 8, 2, 16, 300, 0, True, 1), (64, 8, 2, 16, 300, 0, True, 3), (128, 8, 1, 16, 700, 0, True, 0),
+    (128, 4, 2, 5, 256, 256, True, 0), (64, 4, 4, 17, 200, 200, True, 2), (128, 16, 2, 16, 520, 0, False, 0),
+    (64, 2, 2, 100, 384, 0, True, 0), (128, 32, 4, 1, 640, 0, True, 0)])
+def test_block_attention_matches_fp32(kernel_lib, D, Hq, Hkv, rows, cap, window, causal, splits):
+    from neuralfn_b200.ops import _lib
+    from neuralfn_b200.ops.infer import BlockAttentionWorkspace, block_attention, kv_commit_layers
+    torch.manual_seed(11)
+    dev, B = "cuda", 3
+    ld = (Hq + 2 * Hkv) * D + 64
+    qkv = torch.randn(B * rows, ld, device=dev, dtype=torch.bfloat16)
+    kc = torch.randn(B, Hkv, cap, D, device=dev, dtype=torch.bfloat16)
+    vc = torch.randn(B, Hkv, cap, D, device=dev, dtype=torch.bfloat16)
+    # sequence 0: short (ring not wrapped), 1: wrapped ring / long, 2: empty cache
+    lengths = torch.tensor([min(cap, 131), (cap * 2 + 37) if window else cap - rows, 0], dtype=torch.int32, device=dev)
+    n_rows = torch.tensor([rows, max(1, rows - 2), rows], dtype=torch.int32, device=dev)
+    ws = BlockAttentionWorkspace(B, rows, Hq, Hkv, D, dev)
+    sk = torch.zeros(B * rows, Hkv * D, device=dev, dtype=torch.bfloat16)
+    sv = torch.zeros_like(sk)
+    for _ in range(2):  # second call exercises the self-resetting tickets
+        out = block_attention(qkv, kc, vc, lengths, rows=rows, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, workspace=ws, window=window,
+                              causal=causal, n_rows=n_rows, stage_k=sk, stage_v=sv, splits=splits)
+    _lib.assert_status_ok("block_attention")
+    ref = _block_attention_ref(qkv, kc, vc, lengths.cpu(), rows, Hq, Hkv, D, window, causal, n_rows.cpu())
+    for b in range(B):
+        nr = int(n_rows[b])
+        got = out[b * rows:b * rows + nr].float()
+        assert (got - ref[b * rows:b * rows + nr]).abs().max().item() < 3e-2
+        assert torch.equal(sk[b * rows:b * rows + nr].view(nr, Hkv, D), qkv[b * rows:b * rows + nr, Hq * D:(Hq + Hkv) * D].view(nr, Hkv, D))
+    # commit a prefix and check the ring rows
+    accepted = torch.tensor([min(3, rows), 1, min(2, rows)], dtype=torch.int32, device=dev)
+    k2, v2 = kc.clone(), vc.clone()
+    kv_commit_layers([sk], [sv], [k2], [v2], lengths, accepted, rows=rows)
+    for b in range(B):
+        for i in range(int(accepted[b])):
+            slot = (int(lengths[b]) + i) % cap
+            assert torch.equal(k2[b, :, slot], sk[b * rows + i].view(Hkv, D))
+            assert torch.equal(v2[b, :, slot], sv[b * rows + i].view(Hkv, D))
+    untouched = torch.ones(B, cap, dtype=torch.bool, device=dev)
+    for b in range(B):
+        for i in range(int(accepted[b])):
+            untouched[b, (int(lengths[b]) + i) % cap] = False
+    assert torch.equal(k2.transpose(1, 2)[untouched], kc.transpose(1, 2)[untouched])

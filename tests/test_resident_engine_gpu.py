@@ -214,3 +214,69 @@ def test_glimmer_layout_matches_reference():
         nxt = eng.decode({0: seq[-1]})[0]
         err = float((eng.last_logits(0) - _glimmer_ref(cfg, wf, seq)[-1]).abs().max())
         assert err < 0.12, (step, err)
+
+
+def _small_llama_engine(window=0, max_batch=3, hd=64, max_seq=96):
+    from neuralfn_b200.serving import EngineConfig, ResidentEngine
+    cfg = EngineConfig(family=1, n_layer=3, d_model=256, n_head=4, n_kv_head=2, head_dim=hd, d_ff=512, vocab=777, padded_vocab=784,
+                       max_seq=max_seq, max_batch=max_batch, qk_norm=2, rope_hf=1, rope_theta=10000.0, norm_eps=1e-5, tie_embeddings=0,
+                       window=window, global_every=3 if window else 0)
+    eng = ResidentEngine(cfg)
+    g = torch.Generator().manual_seed(5)
+    w = {}
+    for name, numel in eng.expected_tensors().items():
+        w[name] = ((1 + 0.1 * torch.randn(numel, generator=g)) if name.endswith("norm") else torch.randn(numel, generator=g) * 0.04).bfloat16()
+    eng.load_named_tensors(w)
+    return eng
+
+
+@pytest.mark.parametrize("window,hd", [(0, 64), (16, 128)])
+def test_verify_matches_sequential_decode_and_commit_is_prefix_exact(window, hd):
+    eng = _small_llama_engine(window, hd=hd)
+    eng.enable_verify(8)
+    prompt = [3, 99, 501, 7, 7, 320, 64, 2, 11, 600, 13, 14, 15, 16, 17, 18, 19, 20, 21, 22]
+    # slot 1: plain greedy decoding is the oracle
+    t = eng.prefill(1, prompt)
+    oracle, logits = [t], []
+    for _ in range(7):
+        t = eng.decode({1: t})[1]
+        oracle.append(t)
+        logits.append(eng.last_logits(1))
+    # slot 0: verify the oracle's first 6 tokens as one block: every row must predict the next oracle token
+    first = eng.prefill(0, prompt)
+    assert first == oracle[0]
+    got = eng.verify({0: oracle[:6]})[0]
+    for r in range(6):
+        err = float((eng.verify_logits(0, r) - logits[r]).abs().max())
+        assert err < 0.12, (r, err)
+    assert got == oracle[1:7]
+    assert eng.slot_length(0) == len(prompt)  # nothing was appended yet
+    # accept 4 rows, then continue with single-token decoding: the stream must stay on the oracle
+    eng.commit({0: 4})
+    assert eng.slot_length(0) == len(prompt) + 4
+    assert float((eng.last_logits(0) - logits[3]).abs().max()) < 0.12
+    t = oracle[4]
+    for i in range(5, 8):
+        t = eng.decode({0: t})[0]
+        assert t == oracle[i]
+
+
+def test_append_truncate_and_fork():
+    eng = _small_llama_engine(0)
+    prompt = list(range(5, 45))
+    full_next = eng.prefill(0, prompt)
+    ref = eng.last_logits(0)
+    # the same tokens through prefill(…20) + append(20 more, in chunks of 8)
+    eng.prefill(1, prompt[:20])
+    nxt = eng.append(1, prompt[20:], chunk=8)
+    assert eng.slot_length(1) == 40 and nxt == full_next
+    assert float((eng.last_logits(1) - ref).abs().max()) < 0.12
+    # fork the first 30 tokens into slot 2 and finish there
+    eng.fork(0, 2, 30)
+    assert eng.slot_length(2) == 30
+    assert eng.append(2, prompt[30:]) == full_next
+    # truncate slot 0 to 30 tokens and replay the tail
+    eng.truncate(0, 30)
+    assert eng.append(0, prompt[30:]) == full_next
+    with pytest.raises(Exception):
+        eng.truncate(0, 1000)
