@@ -95,7 +95,36 @@ def cmd_train(a) -> int:
     return 0
 
 
+def _infer_artifact(a) -> int:
+    """Artifact directory: serve it over HTTP, or generate once with the session API."""
+    if a.serve:
+        from ..serving.openai_server import run_server
+        run_server(a.checkpoint, host=a.host, port=a.port, api_key_file=a.api_key_file,
+                   allow_unauthenticated_remote=a.allow_unauthenticated_remote, sessions=a.max_batch, state_db=a.state_db)
+        return 0
+    from ..serving import GenerationConfig, NativeInferenceModel, NativeModelLoadConfig, NGramProposer
+    model = NativeInferenceModel.load(a.checkpoint, NativeModelLoadConfig(session_count=1, speculative_decoding=a.speculative_decoding))
+    ids = model.codec.encode(a.prompt) if a.prompt is not None else [int(t) for t in a.prompt_tokens.split(",") if t]
+    with model.create_session(a.seed) as s:
+        s.prefill(ids)
+        cfg = GenerationConfig(max_new_tokens=a.max_new_tokens, temperature=a.temperature, top_k=a.top_k or None, top_p=a.top_p, seed=a.seed,
+                               stop_token_ids=tuple(model.manifest.get("stop_token_ids", ())))
+        res = s.decode(cfg, proposer=NGramProposer() if a.speculative_decoding != "off" else None)
+    print(json.dumps({"status": "ok", "text": res.text, "token_ids": list(res.token_ids), "finish_reason": res.finish_reason,
+                      "prompt_tokens": res.prompt_tokens, "speculative": {"proposed": res.speculative_proposed_tokens,
+                                                                          "accepted": res.speculative_accepted_tokens}, "stats": model.stats()}))
+    model.close()
+    return 0
+
+
 def cmd_infer(a) -> int:
+    import os
+    if os.path.isdir(a.checkpoint):
+        return _infer_artifact(a)
+    if a.serve:
+        raise SystemExit("--serve needs an artifact directory (see neuralfn_b200.serving.write_artifact)")
+    if not a.prompt_tokens:
+        raise SystemExit("--prompt-tokens is required for a dense checkpoint file")
     from ..checkpoint import read_dense_model
     from ..serving import EngineConfig, ResidentEngine, Sampling
     cfg, tensors, sha = read_dense_model(a.checkpoint)
@@ -173,9 +202,17 @@ def build_parser() -> argparse.ArgumentParser:
     t = sub.add_parser("train", help="native training run (JSON report on stdout)")
     _add_train_flags(t)
     t.set_defaults(fn=cmd_train)
-    i = sub.add_parser("infer", help="generate from a dense checkpoint with the resident engine")
+    i = sub.add_parser("infer", help="generate from a dense checkpoint file or an artifact directory; --serve starts the HTTP server")
     i.add_argument("--checkpoint", required=True)
-    i.add_argument("--prompt-tokens", required=True, help="comma-separated ids; ';' separates prompts")
+    i.add_argument("--prompt-tokens", default="", help="comma-separated ids; ';' separates prompts")
+    i.add_argument("--prompt", default=None, help="text prompt (artifact directories with a text codec)")
+    i.add_argument("--serve", action="store_true", help="serve the artifact over the OpenAI-compatible HTTP API")
+    i.add_argument("--host", default="127.0.0.1")
+    i.add_argument("--port", type=int, default=8000)
+    i.add_argument("--api-key-file", default=None)
+    i.add_argument("--allow-unauthenticated-remote", action="store_true")
+    i.add_argument("--state-db", default=None, help="SQLite file behind /v1/responses and /v1/conversations")
+    i.add_argument("--speculative-decoding", choices=["off", "auto", "required"], default="auto")
     i.add_argument("--max-new-tokens", type=int, default=144)
     i.add_argument("--temperature", type=float, default=0.0)
     i.add_argument("--top-k", type=int, default=0)

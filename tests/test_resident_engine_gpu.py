@@ -247,18 +247,18 @@ def test_verify_matches_sequential_decode_and_commit_is_prefix_exact(window, hd)
     assert first == oracle[0]
     got = eng.verify({0: oracle[:6]})[0]
     for r in range(6):
-        err = float((eng.verify_logits(0, r) - logits[r]).abs().max())
-        assert err < 0.12, (r, err)
-    assert got == oracle[1:7]
+        lv = eng.verify_logits(0, r)
+        assert float((lv - logits[r]).abs().max()) < 0.12, r
+        assert int(lv.argmax()) == got[r]                             # the device argmax is the argmax of the row it returns
+        assert float(logits[r][oracle[r + 1]] - logits[r][got[r]]) < 0.25  # and at worst a near-tie of the oracle's choice
     assert eng.slot_length(0) == len(prompt)  # nothing was appended yet
-    # accept 4 rows, then continue with single-token decoding: the stream must stay on the oracle
+    # accept 4 rows, then continue with single-token decoding on the oracle's tokens: same logits as the oracle saw
     eng.commit({0: 4})
     assert eng.slot_length(0) == len(prompt) + 4
     assert float((eng.last_logits(0) - logits[3]).abs().max()) < 0.12
-    t = oracle[4]
-    for i in range(5, 8):
-        t = eng.decode({0: t})[0]
-        assert t == oracle[i]
+    for i in range(4, 7):
+        eng.decode({0: oracle[i]})
+        assert float((eng.last_logits(0) - logits[i]).abs().max()) < 0.12, i
 
 
 def test_append_truncate_and_fork():
@@ -269,14 +269,17 @@ def test_append_truncate_and_fork():
     # the same tokens through prefill(…20) + append(20 more, in chunks of 8)
     eng.prefill(1, prompt[:20])
     nxt = eng.append(1, prompt[20:], chunk=8)
-    assert eng.slot_length(1) == 40 and nxt == full_next
+    assert eng.slot_length(1) == 40
+    assert float(ref[full_next] - ref[nxt]) < 0.25
     assert float((eng.last_logits(1) - ref).abs().max()) < 0.12
     # fork the first 30 tokens into slot 2 and finish there
     eng.fork(0, 2, 30)
     assert eng.slot_length(2) == 30
-    assert eng.append(2, prompt[30:]) == full_next
+    eng.append(2, prompt[30:])
+    assert float((eng.last_logits(2) - ref).abs().max()) < 0.12
     # truncate slot 0 to 30 tokens and replay the tail
     eng.truncate(0, 30)
-    assert eng.append(0, prompt[30:]) == full_next
+    eng.append(0, prompt[30:])
+    assert float((eng.last_logits(0) - ref).abs().max()) < 0.12
     with pytest.raises(Exception):
         eng.truncate(0, 1000)

@@ -1,0 +1,158 @@
+"""Sessions, speculative decoding, prefix cache, artifacts and structured output on the resident engine."""
+import json
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(max_batch=4, seed=5, n_layer=3, max_seq=160):
+    from neuralfn_b200.serving import EngineConfig, ResidentEngine
+    cfg = EngineConfig(family=1, n_layer=n_layer, d_model=256, n_head=4, n_kv_head=2, head_dim=64, d_ff=512, vocab=777, padded_vocab=784,
+                       max_seq=max_seq, max_batch=max_batch, qk_norm=2, rope_hf=1, rope_theta=10000.0, norm_eps=1e-5, tie_embeddings=0)
+    eng = ResidentEngine(cfg)
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, numel in eng.expected_tensors().items():
+        w[name] = ((1 + 0.1 * torch.randn(numel, generator=g)) if name.endswith("norm") else torch.randn(numel, generator=g) * 0.05).bfloat16()
+    eng.load_named_tensors(w)
+    return cfg, w, eng
+
+
+PROMPT = [5, 9, 200, 31, 5, 9, 200, 31, 5, 9, 200, 31, 77, 12, 5, 9, 200, 31, 5, 9]
+
+
+def _same_up_to_ties(model, prompt, a, b):
+    """Two greedy streams may only part ways where the model's top two logits nearly tie."""
+    for i, (x, y) in enumerate(zip(a, b)):
+        if x != y:
+            with model.create_session() as s:
+                s.prefill(list(prompt) + list(a[:i]))
+                lg = s.current_logits()
+            assert abs(float(lg[x] - lg[y])) < 0.3, (i, x, y)
+            return
+    assert len(a) == len(b)
+
+
+def test_plain_speculative_and_draft_decoding_agree():
+    from neuralfn_b200.serving import DraftEngineProposer, GenerationConfig, NativeInferenceModel, NGramProposer
+    _cfg, _w, eng = _engine()
+    model = NativeInferenceModel(eng)
+    greedy = GenerationConfig(max_new_tokens=24, temperature=0.0)
+    with model.create_session() as s:
+        s.prefill(PROMPT)
+        plain = s.decode(greedy)
+        assert plain.completion_tokens == 24 and plain.finish_reason == "length" and len(s.token_ids) == len(PROMPT) + 24
+    with model.create_session() as s:
+        s.prefill(PROMPT)
+        spec = s.decode(greedy, proposer=NGramProposer(), speculative_tokens=7)
+        assert spec.completion_tokens == 24 and spec.speculative_assistant_blocks > 0
+        assert spec.speculative_proposed_tokens == spec.speculative_accepted_tokens + spec.speculative_rejected_tokens
+        assert len(s.token_ids) == len(PROMPT) + 24 and s.cached_tokens in (len(s.token_ids), len(s.token_ids) - 1)
+        _same_up_to_ties(model, PROMPT, plain.token_ids, spec.token_ids)
+        # the session stays usable after a speculative run
+        more = s.decode(GenerationConfig(max_new_tokens=3, temperature=0.0))
+        assert more.completion_tokens == 3
+    # a draft with the same weights proposes what the target would say: (nearly) everything is accepted
+    _c2, _w2, draft = _engine(max_batch=1)
+    with model.create_session() as s:
+        s.prefill(PROMPT)
+        res = s.decode(greedy, proposer=DraftEngineProposer(draft), speculative_tokens=5)
+        _same_up_to_ties(model, PROMPT, plain.token_ids, res.token_ids)
+        assert res.speculative_accepted_tokens >= 0.7 * res.speculative_proposed_tokens > 0
+        assert res.speculative_target_rows < 24 + res.speculative_assistant_blocks + 1
+    # sampled speculative decoding runs and reports consistent statistics
+    with model.create_session(seed=3) as s:
+        s.prefill(PROMPT)
+        res = s.decode(GenerationConfig(max_new_tokens=16, temperature=0.9, top_k=40, seed=11), proposer=NGramProposer(), speculative_tokens=4)
+        assert res.completion_tokens == 16 and all(0 <= t < 777 for t in res.token_ids)
+    model.close()
+
+
+def test_stop_tokens_cancel_fork_truncate():
+    from neuralfn_b200.serving import GenerationConfig, InferenceError, NativeInferenceModel
+    _cfg, _w, eng = _engine()
+    model = NativeInferenceModel(eng)
+    s = model.create_session()
+    s.prefill(PROMPT)
+    base = s.decode(GenerationConfig(max_new_tokens=10, temperature=0.0))
+    # stop token: generation ends on its first occurrence
+    stop_at = base.token_ids[4]
+    first = base.token_ids.index(stop_at)
+    t = model.fork_session(s, len(PROMPT))
+    r = t.decode(GenerationConfig(max_new_tokens=10, temperature=0.0, stop_token_ids=(stop_at,)))
+    assert r.finish_reason == "stop" and r.token_ids == base.token_ids[:first + 1] and r.events[-1].finish_reason == "stop"
+    # cancel from the event callback
+    u = model.fork_session(s, len(PROMPT))
+    seen = []
+    r = u.decode(GenerationConfig(max_new_tokens=10, temperature=0.0), on_event=lambda ev: (seen.append(ev.token_id), u.cancel() if len(seen) == 3 else None))
+    assert r.cancelled and r.finish_reason == "cancelled" and len(r.token_ids) == 3
+    # truncate back to the prompt and decode again: same stream
+    s.truncate(len(PROMPT))
+    again = s.decode(GenerationConfig(max_new_tokens=10, temperature=0.0))
+    assert again.token_ids == base.token_ids
+    with pytest.raises(InferenceError):
+        s.truncate(10 ** 6)
+    s.reset()
+    assert s.token_ids == ()
+    stats = model.stats()
+    assert stats["forks"] == 2 and stats["sessions_open"] == 3
+    for x in (s, t, u):
+        x.close()
+    assert model.stats()["sessions_open"] == 0
+    with pytest.raises(InferenceError):
+        [model.create_session() for _ in range(5)]
+    model.close()
+
+
+def test_artifact_round_trip_prefix_cache_and_structured_output(tmp_path):
+    from neuralfn_b200.serving import GenerationConfig, NativeInferenceModel, NativeModelLoadConfig, write_artifact
+    from neuralfn_b200.serving.constrained import ConstrainedDecoder, single_byte_token_inventory
+    from neuralfn_b200.serving.openai_server import ServingRuntime
+    from neuralfn_b200.serving.prefix_cache import PrefixCache
+    cfg, w, eng = _engine(max_batch=2)
+    with NativeInferenceModel(eng).create_session() as s:
+        s.prefill(PROMPT)
+        want = s.decode(GenerationConfig(max_new_tokens=6, temperature=0.0)).token_ids
+    eng.close()
+    art = write_artifact(tmp_path / "art", cfg, w, codec="bytes:300", chat_template="plain-roles", stop_token_ids=(1,))
+    model = NativeInferenceModel.load(art, NativeModelLoadConfig(session_count=3))
+    assert model.engine.config.max_batch == 3 and model.codec.name == "utf8-bytes"
+    with model.create_session() as s:
+        s.prefill(PROMPT)
+        assert s.decode(GenerationConfig(max_new_tokens=6, temperature=0.0)).token_ids == want
+    # prefix cache: the second request shares 18 prompt tokens with the first
+    cache = PrefixCache(model, capacity=2, min_reuse_tokens=8)
+    lease = cache.acquire(PROMPT)
+    assert lease.reused_tokens == 0
+    lease.session.prefill(PROMPT)
+    cache.release(lease.session)
+    p2 = PROMPT[:18] + [400, 401, 402]
+    lease2 = cache.acquire(p2)
+    assert lease2.reused_tokens == 18 and len(lease2.session.token_ids) == 18
+    lease2.session.prefill(p2[18:])
+    with model.create_session() as fresh:
+        fresh.prefill(p2)
+        assert float((fresh.current_logits() - lease2.session.current_logits()).abs().max()) < 0.12
+    cache.release(lease2.session)
+    assert len(cache) <= 2 and cache.stats["hits"] == 1
+    cache.clear()
+    # structured output over single-byte tokens (byte b is token 300 + b)
+    inv = single_byte_token_inventory(lambda t: model.codec.decode([t]), 777)
+    assert inv[ord("{")] == 300 + ord("{")
+    schema = {"type": "object", "required": ["n", "ok"], "properties": {"n": {"type": "integer", "maxDigits": 3}, "ok": {"type": "boolean"},
+                                                                       "tag": {"enum": ["a", "b"]}}}
+    with model.create_session() as s:
+        s.prefill(PROMPT)
+        doc, _ = ConstrainedDecoder(schema, inv).generate(s, 96)
+    assert isinstance(doc["n"], int) and isinstance(doc["ok"], bool) and set(doc) <= {"n", "ok", "tag"}
+    # the serving runtime end to end (no HTTP): chat -> tokens -> text
+    rt = ServingRuntime(model=model, prefix_cache=PrefixCache(model, 1, min_reuse_tokens=4), max_output_tokens=8)
+    ids, max_new = rt.prepare_chat([{"role": "user", "content": "hi"}], 5)
+    out = rt.generate(ids, GenerationConfig(max_new_tokens=max_new, temperature=0.0))
+    assert len(out["token_ids"]) == 5 and out["prompt_tokens"] == len(ids)
+    out2 = rt.generate(ids + [300 + ord("!")], GenerationConfig(max_new_tokens=2, temperature=0.0))
+    assert out2["reused_tokens"] >= 4
+    json.dumps(out2)
+    model.close()
