@@ -176,6 +176,24 @@ int nfn_kv_commit_layers(const void* const* stage_k, const void* const* stage_v,
                          const int* caps, const int* lengths, const int* accepted, int n_layers, int B, int rows, int n_kv_heads,
                          int head_dim, nfn_stream_t stream);
 
+// ---- TurboQuant KV cache (turboquant.cu) ------------------------------------------------------------
+// Device tables of one codec: rotation / projection [D, D] fp32 (rotated = R x), centroids [5][16]
+// fp32 (row = bit width), fields [D][2] int32 (bit offset inside the index area, width).
+// Record: [norm f32 | residual norm f32 + D/8 sign bytes (qjl keys) | packed indices | pad to 16].
+typedef struct {
+  const float* rotation; const float* projection; const float* centroids;
+  const int* key_fields; const int* value_fields;
+  int D, qjl, key_rec_bytes, value_rec_bytes;
+} nfn_tq_tables;
+// Encodes head vectors x[row, h * D ...] (bf16, row stride ld) into records[seq[row]][h][slot[row]].
+int nfn_turboquant_encode(const nfn_tq_tables* tables, const void* x, long long ld, const int* seq, const int* slot, int rows,
+                          int n_heads, int cap, int is_key, void* records, nfn_stream_t stream);
+// One query row per sequence against records [B][n_kv_heads][cap]; the first min(lengths[b], cap)
+// rows of every head are live. q: bf16 [B, ld_q]; out: bf16 [B, ld_o].
+int nfn_turboquant_attention(const nfn_tq_tables* tables, const void* q, int ld_q, const void* k_records, const void* v_records,
+                             const int* lengths, void* out, int ld_o, int B, int n_q_heads, int n_kv_heads, int cap, float scale,
+                             nfn_stream_t stream);
+
 // ---- quantised weights (quant.cu) ---------------------------------------------------------------
 enum { NFN_QTYPE_Q4_K = 12, NFN_QTYPE_Q5_K = 13, NFN_QTYPE_Q6_K = 14 };  // GGUF type ids
 int nfn_quant_block_bytes(int qtype);

@@ -393,12 +393,16 @@ class ConstrainedDecoder:
         self.grammar.reset()
         self._seen = history_len
 
-    def allowed_tokens(self, history: Sequence[int]) -> list[int]:
+    def _sync(self, history: Sequence[int]) -> None:
+        """Feeds the grammar the bytes of the tokens generated since the last call."""
         for t in history[self._seen:]:
             if t in self.token_to_byte:
                 self.grammar.advance(self.token_to_byte[t])
         self._seen = len(history)
-        out = [self.byte_to_token[b] for b in self.grammar.allowed_bytes() if b in self.byte_to_token]
+
+    def allowed_tokens(self, history: Sequence[int]) -> list[int]:
+        self._sync(history)
+        out =[self.byte_to_token[b] for b in self.grammar.allowed_bytes() if b in self.byte_to_token]
         if self.grammar.complete and self.stop_token is not None:
             out.append(self.stop_token)
         return out
@@ -407,18 +411,16 @@ class ConstrainedDecoder:
         """Greedy byte-exact generation; returns (parsed JSON value, GenerationResult)."""
         from .inference import GenerationConfig
         self.start(len(session.token_ids))
-        produced = bytearray()
         total = None
         for _ in range(max_new_tokens):
+            self._sync(session.token_ids)
             if self.grammar.must_stop:
                 break
             res = session.decode(GenerationConfig(max_new_tokens=1, temperature=0.0), allowed_tokens=self.allowed_tokens)
-            tok = res.token_ids[0]
             total = res
-            if tok == self.stop_token:
+            if res.token_ids[0] == self.stop_token:
                 break
-            produced.append(self.token_to_byte[tok])
-        self.allowed_tokens(session.token_ids)  # feed the last byte
+        self._sync(session.token_ids)
         if not self.grammar.complete:
             raise SchemaError("generation ended before the document was complete")
         return json.loads(bytes(self.grammar.emitted).decode("ascii")), total

@@ -297,7 +297,7 @@ class NativeInferenceModel:
                 raise InferenceError(f"artifact needs ~{need >> 20} MiB on the device, {free >> 20} MiB free (reserve {lc.vram_reserve_bytes or 0})")
         engine = ResidentEngine(cfg, device=lc.cuda_device)
         from ..checkpoint.named import read_named_tensors
-        engine.load_named_tensors(read_named_tensors(root / manifest["weights"]))
+        engine.load_named_tensors(read_named_tensors(root / manifest["weights"])[0])
         codec = load_text_codec(manifest.get("text_codec"), root)
         return cls(engine, codec=codec, manifest=manifest, artifact_root=root, load_config=lc, **kw)
 
