@@ -176,6 +176,12 @@ int nfn_kv_commit_layers(const void* const* stage_k, const void* const* stage_v,
                          const int* caps, const int* lengths, const int* accepted, int n_layers, int B, int rows, int n_kv_heads,
                          int head_dim, nfn_stream_t stream);
 
+// ---- GEMM over K-quant weights, dequantisation fused into the operand pipeline (gemm_kquant.cu) ----
+// C[M, N] = A[M, K] . dequant(W)^T with args->b pointing at N rows of K / 256 super-blocks
+// (qtype: NFN_QTYPE_Q4_K / Q5_K / Q6_K, declared below). K-major A, bf16 output, the bias /
+// activation / residual epilogues of nfn_gemm_bf16; ldb, a_mn, b_mn and split_k are ignored or refused.
+int nfn_gemm_kquant(int qtype, const nfn_gemm_args* args, nfn_stream_t stream);
+
 // ---- TurboQuant KV cache (turboquant.cu) ------------------------------------------------------------
 // Device tables of one codec: rotation / projection [D, D] fp32 (rotated = R x), centroids [5][16]
 // fp32 (row = bit width), fields [D][2] int32 (bit offset inside the index area, width).

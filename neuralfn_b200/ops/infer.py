@@ -16,7 +16,7 @@ _bf16 = torch.bfloat16
 
 __all__ = ["rope_tables", "rope_inplace", "qk_norm_rope_forward", "argmax_rows", "argmax_merge", "sample_rows",
            "DecodeAttentionWorkspace", "decode_attention", "BlockAttentionWorkspace", "block_attention", "kv_commit_layers",
-           "dequant_kquant", "dequant_nf4", "kquant_gemv", "quant_block_bytes"]
+           "dequant_kquant", "dequant_nf4", "kquant_gemv", "gemm_kquant", "quant_block_bytes"]
 
 
 def _p(t) -> c_void_p:
@@ -229,4 +229,29 @@ def kquant_gemv(qtype: int, w: torch.Tensor, x: torch.Tensor, N: int, *, w_gate_
     rc = _lib.load().nfn_kquant_gemv(c_int(qtype), _p(w), _p(w_gate_pair), _p(x), c_int(x.stride(0)), _p(out), c_int(out.stride(0)),
                                      _p(bias), _p(resid), c_int(0 if resid is None else resid.stride(0)), c_int(B), c_int(N), c_int(K), _st())
     _lib.check(rc, "nfn_kquant_gemv")
+    return out
+
+
+def gemm_kquant(qtype: int, x: torch.Tensor, w: torch.Tensor, N: int, *, bias=None, act: str | None = None, resid=None, out=None,
+                alpha: float = 1.0) -> torch.Tensor:
+    """Prefill product ``x @ dequant(W)^T`` with the dequantisation fused into the GEMM's operand
+    pipeline. x: bf16 [M, K] (K a multiple of 256); w: uint8, N rows of K / 256 super-blocks."""
+    from .gemm import ACT_IDS, EPI_ACT_SHIFT, EPI_BIAS, EPI_RESID
+    assert x.dtype == _bf16 and x.dim() == 2 and x.stride(1) == 1
+    M, K = x.shape
+    assert w.numel() == N * (K // 256) * quant_block_bytes(qtype), "weight size does not match N x K"
+    out = torch.empty(M, N, dtype=_bf16, device=x.device) if out is None else out
+    a = _lib.GemmArgs()
+    a.a, a.b, a.c = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    a.m, a.n, a.k = M, N, K
+    a.lda, a.ldb, a.ldc = x.stride(0), K, out.stride(0)
+    a.flags = ACT_IDS[act] << EPI_ACT_SHIFT
+    a.alpha, a.split_k = alpha, 1
+    if bias is not None:
+        a.bias, a.flags = bias.data_ptr(), a.flags | EPI_BIAS
+    if resid is not None:
+        a.aux_in, a.ld_aux_in, a.flags = resid.data_ptr(), resid.stride(0), a.flags | EPI_RESID
+    import ctypes
+    rc = _lib.load().nfn_gemm_kquant(c_int(qtype), ctypes.byref(a), _st())
+    _lib.check(rc, "nfn_gemm_kquant")
     return out

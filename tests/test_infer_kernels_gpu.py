@@ -286,3 +286,26 @@ def test_block_attention_matches_fp32(kernel_lib, D, Hq, Hkv, rows, cap, window,
         for i in range(int(accepted[b])):
             untouched[b, (int(lengths[b]) + i) % cap] = False
     assert torch.equal(k2.transpose(1, 2)[untouched], kc.transpose(1, 2)[untouched])
+
+
+@pytest.mark.parametrize("name,M,N,K", [("Q4_K", 256, 128, 512), ("Q4_K", 1000, 264, 2048), ("Q5_K", 384, 256, 768), ("Q6_K", 300, 136, 1024),
+                                         ("Q6_K", 2048, 512, 6656)])
+def test_gemm_with_fused_kquant_dequant(kernel_lib, name, M, N, K):
+    from neuralfn_b200.ops import _lib, infer
+    from neuralfn_b200.quant import kquant
+    t = kquant.GGML_TYPE[name]
+    dev = _dev()
+    raw = kquant.random_blocks(t, N * K // 256, seed=3)
+    w = torch.from_numpy(kquant.dequantize(t, raw.tobytes())).view(N, K).to(dev)
+    x = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
+    bias = torch.randn(N, device=dev).bfloat16()
+    resid = torch.randn(M, N, device=dev).bfloat16()
+    wq = torch.from_numpy(raw).to(dev).reshape(-1)
+    got = infer.gemm_kquant(t, x, wq, N)
+    _lib.assert_status_ok("gemm_kquant")
+    ref = x.float() @ w.bfloat16().float().T  # the kernel rounds the decoded weights to bf16, like the two-step path
+    torch.testing.assert_close(got.float(), ref, atol=0.02 * float(ref.abs().max()), rtol=2e-2)
+    got = infer.gemm_kquant(t, x, wq, N, bias=bias, act="silu", resid=resid)
+    _lib.assert_status_ok("gemm_kquant epilogue")
+    ref2 = torch.nn.functional.silu(ref + bias.float()) + resid.float()
+    torch.testing.assert_close(got.float(), ref2, atol=0.02 * float(ref2.abs().max()), rtol=2e-2)

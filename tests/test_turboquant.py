@@ -87,4 +87,5 @@ def test_device_encode_and_attention_match_the_oracle(kernel_lib, profile, D, Hq
                 h = hk * G + g
                 ref = codec.attention_oracle(qn[b, h * D:(h + 1) * D], keys, vals, D ** -0.5)
                 assert np.abs(out[b, h * D:(h + 1) * D] - ref).max() < 0.03, (b, h)
-    assert cache.bytes_per_token <= (0.25 if D == 128 else 0.375) * (2 * Hkv * D * 2)  # 64 of 256 bytes per vector at D = 128
+    # per vector at D = 128: 64 of 256 bytes (80 for a QJL key with its sign bits and residual norm)
+    assert cache.bytes_per_token <= (0.29 if D == 128 else 0.4) * (2 * Hkv * D * 2)
