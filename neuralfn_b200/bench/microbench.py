@@ -164,9 +164,65 @@ def case_kquant_gemv(args):
     return _report("q4_k_gemv", ms, bytes_=float(raw.numel()), flops=2.0 * B * N * Kd, args=args, extra={"B": B, "N": N, "K": Kd})
 
 
+
+def case_gemm_kquant(args):
+    """Prefill product over Q4_K weights, dequantisation fused into the GEMM pipeline, against the
+    two-step path (dequantise to bf16, then the bf16 GEMM)."""
+    from neuralfn_b200.ops import infer as I
+    from neuralfn_b200.ops.gemm import gemm
+    from neuralfn_b200.quant import kquant
+    dev = torch.device("cuda")
+    M, N, Kd = args.m, args.n, args.k
+    raw = torch.from_numpy(kquant.random_blocks(12, N * Kd // 256, seed=0)).to(dev).reshape(-1)
+    x = torch.randn(M, Kd, device=dev).bfloat16()
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    wbuf = torch.empty(N * Kd, device=dev, dtype=torch.bfloat16)
+    ms = time_kernel(lambda: I.gemm_kquant(12, x, raw, N, out=out), args.iters, args.warmup, args.flush)
+    two = time_kernel(lambda: gemm(x, I.dequant_kquant(12, raw, out=wbuf).view(N, Kd), out=out), args.iters, args.warmup, args.flush)
+    return _report("q4_k_gemm_fused_dequant", ms, bytes_=float(raw.numel()) + 2.0 * M * (Kd + N), flops=2.0 * M * N * Kd, args=args,
+                   extra={"m": M, "n": N, "k": Kd, "two_step_ms": round(two, 5)})
+
+
+def case_block_attention(args):
+    """Speculative verification block (16 rows per sequence) against a bf16 KV cache."""
+    from neuralfn_b200.ops import infer as I
+    dev = torch.device("cuda")
+    B, Hq, Hkv, D, ctx, R = args.batch, args.heads, args.kv_heads or 1, args.head_dim, args.seq, 16
+    kc = torch.randn(B, Hkv, ctx + 128, D, device=dev).bfloat16()
+    vc = torch.randn(B, Hkv, ctx + 128, D, device=dev).bfloat16()
+    qkv = torch.randn(B * R, (Hq + 2 * Hkv) * D, device=dev).bfloat16()
+    lengths = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+    ws = I.BlockAttentionWorkspace(B, R, Hq, Hkv, D, dev)
+    out = torch.empty(B * R, Hq * D, device=dev, dtype=torch.bfloat16)
+    ms = time_kernel(lambda: I.block_attention(qkv, kc, vc, lengths, rows=R, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, workspace=ws, out=out),
+                     args.iters, args.warmup, args.flush)
+    return _report("block_attention_16_rows", ms, bytes_=2.0 * B * Hkv * ctx * D * 2, flops=4.0 * B * Hq * R * ctx * D, args=args,
+                   extra={"B": B, "Hq": Hq, "Hkv": Hkv, "ctx": ctx, "D": D, "rows": R})
+
+
+def case_turboquant_attention(args):
+    """Decode attention over TurboQuant records (3.5 bits per coordinate)."""
+    from neuralfn_b200.quant.turboquant import TurboQuantCodec, TurboQuantKVCache, default_outlier_indices
+    dev = torch.device("cuda")
+    B, Hq, Hkv, D, ctx = args.batch, args.heads, args.kv_heads or 1, args.head_dim, args.seq
+    codec = TurboQuantCodec(D, profile="mse-3.5", seed=0, outlier_indices=default_outlier_indices(D))
+    cache = TurboQuantKVCache(codec, B, Hkv, ctx, dev)
+    cache.k.copy_(torch.randint(0, 255, cache.k.shape, dtype=torch.uint8, device=dev))
+    cache.v.copy_(torch.randint(0, 255, cache.v.shape, dtype=torch.uint8, device=dev))
+    cache.k.view(torch.float32)[..., 0] = 1.0  # finite norms
+    cache.v.view(torch.float32)[..., 0] = 1.0
+    cache._len_host = [ctx] * B
+    cache.lengths.fill_(ctx)
+    q = torch.randn(B, Hq * D, device=dev).bfloat16()
+    ms = time_kernel(lambda: cache.attention(q, Hq), args.iters, args.warmup, args.flush)
+    return _report("turboquant_decode_attention", ms, bytes_=float(B * ctx * cache.bytes_per_token), args=args,
+                   extra={"B": B, "Hq": Hq, "Hkv": Hkv, "ctx": ctx, "D": D, "bytes_per_token": cache.bytes_per_token})
+
+
 CASES = {"gemm": case_gemm, "attention_fwd": case_attention, "attention_bwd": lambda a: case_attention(a, True),
          "cross_entropy": case_cross_entropy, "norm": case_norm, "adamw": case_adamw, "decode_attention": case_decode_attention,
-         "kquant_gemv": case_kquant_gemv}
+         "kquant_gemv": case_kquant_gemv, "gemm_kquant": case_gemm_kquant, "block_attention": case_block_attention,
+         "turboquant_attention": case_turboquant_attention}
 
 
 def run_all(args):

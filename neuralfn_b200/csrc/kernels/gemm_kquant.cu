@@ -15,6 +15,12 @@
 // Per stage the full barrier collects five arrivals: the TMA thread's expect_tx and one elected
 // lane of every decoder warp (after its writes were fenced into the async proxy).
 //
+// The same pipeline serves NF4 base weights (4-bit codes, one fp32 absmax per 64 weights) and a
+// fused LoRA branch: the rank-r update s * (x A^T) B^T rides along as ONE extra k-block whose A
+// tile is the pre-computed T = s * x A^T (bf16 [M, 64], zero-padded beyond r) and whose B tile
+// is the adapter's B matrix (bf16 [N, 64]), both fetched by TMA, so base product and adapter
+// accumulate in the same TMEM tile and leave through one epilogue.
+//
 // Reference counterpart: the grouped MMQ prefill path (neuralfn/csrc/tile_cuda/glimmer_k_mmq.cu,
 // kernels.cu:1324-2015), which runs llama.cpp's int8 mma.sync tiles; this kernel keeps the
 // weights in their GGUF bytes and feeds the 5th-generation tensor cores in bf16 instead.
@@ -42,6 +48,33 @@ __device__ __forceinline__ void kq_scale_min(int j, const uint8_t* q, float* sc,
 }
 __device__ __forceinline__ void kq_store8(uint8_t* tile, int row, int chunk, const float (&v)[8]) {
   *reinterpret_cast<uint4*>(tile + row * 128 + ((chunk ^ (row & 7)) << 4)) = pack8_bf16(v);
+}
+
+constexpr int NFN_QTYPE_NF4_ = NFN_QTYPE_NF4;
+__constant__ float kq_nf4[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+                                 -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+                                 0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+                                 0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+
+// 64 NF4 weights (32 code bytes, low nibble = even element) times their group's absmax
+__device__ __forceinline__ void kq_decode_nf4(const uint8_t* codes, float absmax, uint8_t* tile, int row) {
+  const uint4* q = reinterpret_cast<const uint4*>(codes);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint4 u = __ldg(q + h);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {  // 4 bytes -> 8 weights
+      float v[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t byte = (w[c] >> (8 * e)) & 0xFF;
+        v[2 * e] = kq_nf4[byte & 0xF] * absmax;
+        v[2 * e + 1] = kq_nf4[byte >> 4] * absmax;
+      }
+      kq_store8(tile, row, 4 * h + c, v);
+    }
+  }
 }
 
 // 64 weights [64 j, 64 j + 64) of one super-block -> row `row` of the shared tile.
@@ -138,8 +171,11 @@ __device__ __forceinline__ void kq_decode_quarter<NFN_QTYPE_Q6_K>(const uint8_t*
 template <int QT>
 __global__ void __launch_bounds__(KQ_THREADS, 1)
 gemm_kquant_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_c,
-                   const __grid_constant__ CUtensorMap tma_aux, const uint8_t* __restrict__ wq, const GemmParams p) {
+                   const __grid_constant__ CUtensorMap tma_aux, const __grid_constant__ CUtensorMap tma_lt,
+                   const __grid_constant__ CUtensorMap tma_lb, const uint8_t* __restrict__ wq, const float* __restrict__ absmax,
+                   const int lora, const GemmParams p) {
   constexpr int BN = KQ_BN, STAGES = KQ_STAGES;
+  constexpr bool NF4 = QT == NFN_QTYPE_NF4_;
   constexpr int BLOCK_BYTES = QT == NFN_QTYPE_Q4_K ? 144 : (QT == NFN_QTYPE_Q5_K ? 176 : 210);
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t TMEM_COLS = 2 * BN;
@@ -182,7 +218,8 @@ gemm_kquant_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
 
   const int tiles_mn = p.tiles_m * p.tiles_n;
   const int num_tiles = tiles_mn;
-  const int total_kb = p.k / BK;
+  const int main_kb = p.k / BK;
+  const int total_kb = main_kb + (lora ? 1 : 0);  // the adapter rides along as one more k-block
   const int blocks_per_row = p.k / 256;
 
   if (warp == 0) {
@@ -198,8 +235,15 @@ gemm_kquant_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
             break;
           }
           const uint32_t fb = smem_u32(&full_bar[stage]);
-          mbar_expect_tx(fb, A_BYTES);
-          tma_load_2d(smem_u32(smem + stage * STAGE_BYTES), &tma_a, fb, kb * BK, tm * BM);
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          if (kb < main_kb) {
+            mbar_expect_tx(fb, A_BYTES);
+            tma_load_2d(sa, &tma_a, fb, kb * BK, tm * BM);
+          } else {
+            mbar_expect_tx(fb, A_BYTES + B_BYTES);
+            tma_load_2d(sa, &tma_lt, fb, 0, tm * BM);
+            tma_load_2d(sa + A_BYTES, &tma_lb, fb, 0, tn * BN);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -243,14 +287,19 @@ gemm_kquant_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       int tm, tn;
       tile_mn(p, tile, tm, tn);
       const int n = tn * BN + r;
-      const uint8_t* rowp = wq + (size_t)min(n, p.n - 1) * blocks_per_row * BLOCK_BYTES;
+      const int nc = min(n, p.n - 1);
+      const uint8_t* rowp = NF4 ? wq + (size_t)nc * (p.k / 2) : wq + (size_t)nc * blocks_per_row * BLOCK_BYTES;
+      const float* absrow = NF4 ? absmax + (size_t)nc * main_kb : nullptr;
       for (int kb = 0; kb < total_kb; ++kb) {
         ok = mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1, cta_abort, p.status, NFN_ERR_WAIT_EMPTY);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         uint8_t* tile_b = smem + stage * STAGE_BYTES + A_BYTES;
-        if (n < p.n) {
-          kq_decode_quarter<QT>(rowp + (size_t)(kb >> 2) * BLOCK_BYTES, kb & 3, tile_b, r);
+        if (kb >= main_kb) {
+          // adapter block: both tiles come by TMA; only the arrival is owed
+        } else if (n < p.n) {
+          if constexpr (NF4) kq_decode_nf4(rowp + (size_t)kb * 32, __ldg(absrow + kb), tile_b, r);
+          else kq_decode_quarter<(NF4 ? NFN_QTYPE_Q4_K : QT)>(rowp + (size_t)(kb >> 2) * BLOCK_BYTES, kb & 3, tile_b, r);
         } else {
           const float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
@@ -286,7 +335,8 @@ gemm_kquant_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
 }
 
 template <int QT>
-static int launch_gemm_kquant(const nfn_gemm_args& a, cudaStream_t stream) {
+static int launch_gemm_kquant(const nfn_gemm_args& a, const float* absmax, const void* lora_t, int ld_t, const void* lora_b, int ld_b,
+                              cudaStream_t stream) {
   constexpr size_t SMEM = 1024 + (size_t)KQ_STAGES * (BM * BK * 2 + KQ_BN * BK * 2) + 2 * EPI_TILE_BYTES + 256;
   auto kern = gemm_kquant_kernel<QT>;
   static bool attr[64] = {};
@@ -301,6 +351,12 @@ static int launch_gemm_kquant(const nfn_gemm_args& a, cudaStream_t stream) {
   if (!make_tmap_2d(&tc, a.c, 2, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldc, EPI_CHUNK, BM, 128)) return -3;
   tx = tc;
   if ((a.flags & NFN_EPI_SAVE_PRE) && !make_tmap_2d(&tx, a.aux_out, 2, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ld_aux_out, EPI_CHUNK, BM, 128)) return -3;
+  CUtensorMap tlt = ta, tlb = ta;
+  const int lora = lora_t != nullptr;
+  if (lora) {
+    if (!make_tmap_2d(&tlt, lora_t, 2, 64, (uint64_t)a.m, (uint64_t)ld_t, BK, BM, 128)) return -3;
+    if (!make_tmap_2d(&tlb, lora_b, 2, 64, (uint64_t)a.n, (uint64_t)ld_b, BK, KQ_BN, 128)) return -3;
+  }
   GemmParams p;
   p.c = a.c;
   p.bias = static_cast<const __nv_bfloat16*>(a.bias);
@@ -319,7 +375,7 @@ static int launch_gemm_kquant(const nfn_gemm_args& a, cudaStream_t stream) {
   // the packed bytes behind it stay in L2
   p.raster_gw = 1;
   const int tiles = p.tiles_m * p.tiles_n;
-  kern<<<std::min(tiles, sm_count()), KQ_THREADS, SMEM, stream>>>(ta, tc, tx, static_cast<const uint8_t*>(a.b), p);
+  kern<<<std::min(tiles, sm_count()), KQ_THREADS, SMEM, stream>>>(ta, tc, tx, tlt, tlb, static_cast<const uint8_t*>(a.b), absmax, lora, p);
   return launch_check("gemm_kquant");
 }
 
@@ -327,23 +383,35 @@ static int launch_gemm_kquant(const nfn_gemm_args& a, cudaStream_t stream) {
 
 using namespace nfn;
 
-extern "C" int nfn_gemm_kquant(int qtype, const nfn_gemm_args* args, nfn_stream_t stream_) {
+extern "C" int nfn_gemm_quant_lora(int qtype, const nfn_gemm_args* args, const float* absmax, const void* lora_t, int ld_t,
+                                   const void* lora_b, int ld_b, nfn_stream_t stream_) {
   if (!args) return fail(-1, "gemm_kquant: null args");
   const nfn_gemm_args& a = *args;
   if (a.m <= 0 || a.n <= 0 || a.k <= 0) return fail(-1, "gemm_kquant: empty problem");
-  if (a.k % 256) return fail(-1, "gemm_kquant: K must be a multiple of the 256-weight super-block");
+  const bool nf4 = qtype == NFN_QTYPE_NF4;
+  if (nf4 ? (a.k % 64 != 0 || !absmax) : (a.k % 256 != 0))
+    return fail(-1, "gemm_kquant: K must be a multiple of the quantisation group (256; 64 with absmax for NF4)");
+  if ((lora_t == nullptr) != (lora_b == nullptr)) return fail(-1, "gemm_kquant: give both adapter operands or none");
+  if (lora_t && ((ld_t & 7) || (ld_b & 7) || ld_t < 64 || ld_b < 64 || ((reinterpret_cast<uintptr_t>(lora_t) | reinterpret_cast<uintptr_t>(lora_b)) & 15)))
+    return fail(-1, "gemm_kquant: adapter operands are bf16 [M, 64] and [N, 64], 16-byte aligned");
   if ((a.n & 7) || (a.ldc & 7) || (a.lda & 7)) return fail(-1, "gemm_kquant: N, lda and ldc must be multiples of 8");
   if (a.a_mn || a.b_mn || a.split_k > 1 || (a.flags & (NFN_EPI_OUT_F32 | NFN_EPI_ACCUM))) return fail(-1, "gemm_kquant: K-major operands, bf16 output, no split-K");
   if ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.c)) & 15) return fail(-1, "gemm_kquant: operands must be 16-byte aligned");
   if (reinterpret_cast<uintptr_t>(a.b) & (qtype == NFN_QTYPE_Q6_K ? 1 : 15)) return fail(-1, "gemm_kquant: weight blocks are misaligned");
+  if (nf4 && (a.k / 2) % 16) return fail(-1, "gemm_kquant: NF4 rows must be 16-byte multiples (K % 32 == 0)");
   if ((a.flags & NFN_EPI_BIAS) && !a.bias) return fail(-1, "gemm_kquant: bias flag without bias");
   if ((a.flags & (NFN_EPI_RESID | NFN_EPI_DACT)) && (!a.aux_in || (a.ld_aux_in & 7))) return fail(-1, "gemm_kquant: aux_in missing or misaligned");
   if ((a.flags & NFN_EPI_SAVE_PRE) && (!a.aux_out || (a.ld_aux_out & 7))) return fail(-1, "gemm_kquant: aux_out missing or misaligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
   switch (qtype) {
-    case NFN_QTYPE_Q4_K: return launch_gemm_kquant<NFN_QTYPE_Q4_K>(a, st);
-    case NFN_QTYPE_Q5_K: return launch_gemm_kquant<NFN_QTYPE_Q5_K>(a, st);
-    case NFN_QTYPE_Q6_K: return launch_gemm_kquant<NFN_QTYPE_Q6_K>(a, st);
+    case NFN_QTYPE_Q4_K: return launch_gemm_kquant<NFN_QTYPE_Q4_K>(a, absmax, lora_t, ld_t, lora_b, ld_b, st);
+    case NFN_QTYPE_Q5_K: return launch_gemm_kquant<NFN_QTYPE_Q5_K>(a, absmax, lora_t, ld_t, lora_b, ld_b, st);
+    case NFN_QTYPE_Q6_K: return launch_gemm_kquant<NFN_QTYPE_Q6_K>(a, absmax, lora_t, ld_t, lora_b, ld_b, st);
+    case NFN_QTYPE_NF4: return launch_gemm_kquant<NFN_QTYPE_NF4>(a, absmax, lora_t, ld_t, lora_b, ld_b, st);
   }
-  return fail(-1, "gemm_kquant: qtype must be Q4_K, Q5_K or Q6_K");
+  return fail(-1, "gemm_kquant: qtype must be Q4_K, Q5_K, Q6_K or NF4");
+}
+
+extern "C" int nfn_gemm_kquant(int qtype, const nfn_gemm_args* args, nfn_stream_t stream) {
+  return nfn_gemm_quant_lora(qtype, args, nullptr, nullptr, 0, nullptr, 0, stream);
 }

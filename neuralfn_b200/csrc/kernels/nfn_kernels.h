@@ -181,6 +181,12 @@ int nfn_kv_commit_layers(const void* const* stage_k, const void* const* stage_v,
 // (qtype: NFN_QTYPE_Q4_K / Q5_K / Q6_K, declared below). K-major A, bf16 output, the bias /
 // activation / residual epilogues of nfn_gemm_bf16; ldb, a_mn, b_mn and split_k are ignored or refused.
 int nfn_gemm_kquant(int qtype, const nfn_gemm_args* args, nfn_stream_t stream);
+// The same with NF4 base weights (qtype NFN_QTYPE_NF4: args->b = N rows of K / 2 code bytes, low
+// nibble = even element; absmax fp32 [N, K / 64]) and / or a fused LoRA branch: lora_t = bf16
+// [M, >= 64] holding scale * (x A^T) in its first r columns and zeros up to column 64, lora_b =
+// bf16 [N, >= 64] holding the adapter's B matrix likewise. Pass NULL adapters for none.
+int nfn_gemm_quant_lora(int qtype, const nfn_gemm_args* args, const float* absmax, const void* lora_t, int ld_t,
+                        const void* lora_b, int ld_b, nfn_stream_t stream);
 
 // ---- TurboQuant KV cache (turboquant.cu) ------------------------------------------------------------
 // Device tables of one codec: rotation / projection [D, D] fp32 (rotated = R x), centroids [5][16]
@@ -201,7 +207,7 @@ int nfn_turboquant_attention(const nfn_tq_tables* tables, const void* q, int ld_
                              nfn_stream_t stream);
 
 // ---- quantised weights (quant.cu) ---------------------------------------------------------------
-enum { NFN_QTYPE_Q4_K = 12, NFN_QTYPE_Q5_K = 13, NFN_QTYPE_Q6_K = 14 };  // GGUF type ids
+enum { NFN_QTYPE_Q4_K = 12, NFN_QTYPE_Q5_K = 13, NFN_QTYPE_Q6_K = 14, NFN_QTYPE_NF4 = 100 };  // GGUF type ids; NF4 is this library's own
 int nfn_quant_block_bytes(int qtype);
 int nfn_dequant_kquant(int qtype, const void* blocks, long long n_blocks, void* out_bf16, nfn_stream_t stream);
 int nfn_dequant_nf4(const void* codes, const float* absmax, long long n_weights, int group, void* out_bf16,

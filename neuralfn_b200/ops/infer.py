@@ -16,7 +16,7 @@ _bf16 = torch.bfloat16
 
 __all__ = ["rope_tables", "rope_inplace", "qk_norm_rope_forward", "argmax_rows", "argmax_merge", "sample_rows",
            "DecodeAttentionWorkspace", "decode_attention", "BlockAttentionWorkspace", "block_attention", "kv_commit_layers",
-           "dequant_kquant", "dequant_nf4", "kquant_gemv", "gemm_kquant", "quant_block_bytes"]
+           "dequant_kquant", "dequant_nf4", "kquant_gemv", "gemm_kquant", "NF4LoRALinear", "QTYPE_NF4", "quant_block_bytes"]
 
 
 def _p(t) -> c_void_p:
@@ -255,3 +255,65 @@ def gemm_kquant(qtype: int, x: torch.Tensor, w: torch.Tensor, N: int, *, bias=No
     rc = _lib.load().nfn_gemm_kquant(c_int(qtype), ctypes.byref(a), _st())
     _lib.check(rc, "nfn_gemm_kquant")
     return out
+
+
+QTYPE_NF4 = 100
+
+
+class NF4LoRALinear:
+    """A frozen NF4 base weight [N, K] (codes + per-64 absmax) with a trainable rank-r adapter:
+    ``y = x W^T + (alpha / r) * (x A^T) B^T``. Forward is one tiny GEMM (x A^T, 64 padded columns)
+    plus ONE fused launch that decodes the NF4 tiles inside the GEMM pipeline and accumulates the
+    adapter as an extra k-block. Backward returns dX, dA, dB; the base weight is decoded to a
+    transient bf16 matrix for dX = dY W (the decode-in-pipeline kernel covers K-major products only).
+
+    Reference counterparts: ``tile_ops.h:19-27``, ``muse_glimmer_native_train.cpp:3324-3419``,
+    ``torch_backend.py:990-1097``."""
+
+    def __init__(self, codes: torch.Tensor, absmax: torch.Tensor, N: int, K: int, lora_a: torch.Tensor, lora_b: torch.Tensor, alpha: float = 16.0):
+        r = lora_a.shape[0]
+        assert codes.dtype == torch.uint8 and codes.numel() == N * K // 2 and absmax.numel() == N * K // 64 and absmax.dtype == torch.float32
+        assert lora_a.shape == (r, K) and lora_b.shape == (N, r) and r <= 64 and K % 64 == 0 and N % 8 == 0
+        self.codes, self.absmax, self.N, self.K, self.r, self.scale = codes, absmax, N, K, r, alpha / r
+        self.a, self.b = lora_a, lora_b
+        dev = codes.device
+        self._a_pad = torch.zeros(64, K, dtype=_bf16, device=dev)
+        self._b_pad = torch.zeros(N, 64, dtype=_bf16, device=dev)
+        self.refresh_adapter()
+
+    def refresh_adapter(self) -> None:
+        """Call after an optimizer step on ``a`` / ``b``."""
+        self._a_pad[:self.r].copy_(self.a)
+        self._b_pad[:, :self.r].copy_(self.b)
+
+    def forward(self, x: torch.Tensor, bias=None, out=None) -> torch.Tensor:
+        import ctypes
+
+        from .gemm import EPI_BIAS, gemm
+        assert x.dtype == _bf16 and x.dim() == 2 and x.shape[1] == self.K and x.stride(1) == 1
+        M = x.shape[0]
+        t = gemm(x, self._a_pad, alpha=self.scale)  # [M, 64]: scale * x A^T, zero beyond column r
+        out = torch.empty(M, self.N, dtype=_bf16, device=x.device) if out is None else out
+        a = _lib.GemmArgs()
+        a.a, a.b, a.c = x.data_ptr(), self.codes.data_ptr(), out.data_ptr()
+        a.m, a.n, a.k = M, self.N, self.K
+        a.lda, a.ldb, a.ldc = x.stride(0), self.K, out.stride(0)
+        a.alpha, a.split_k, a.flags = 1.0, 1, 0
+        if bias is not None:
+            a.bias, a.flags = bias.data_ptr(), EPI_BIAS
+        rc = _lib.load().nfn_gemm_quant_lora(c_int(QTYPE_NF4), ctypes.byref(a), _p(self.absmax), _p(t), c_int(t.stride(0)), _p(self._b_pad),
+                                             c_int(self._b_pad.stride(0)), _st())
+        _lib.check(rc, "nfn_gemm_quant_lora")
+        self._saved_t = t
+        return out
+
+    def backward(self, x: torch.Tensor, dy: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """(dX bf16 [M, K], dA fp32 [r, K], dB fp32 [N, r]) for the last forward's input ``x``."""
+        from .gemm import gemm
+        w = dequant_nf4(self.codes, self.absmax).view(self.N, self.K)
+        u = gemm(dy, self._b_pad, b_mn=True, alpha=self.scale)       # [M, 64] = scale * dY B
+        dx = gemm(dy, w, b_mn=True)                                   # dY W
+        dx = gemm(u, self._a_pad, b_mn=True, resid=dx)                # + u A
+        da = gemm(u, x, a_mn=True, b_mn=True, out_dtype=torch.float32)[:self.r]        # u^T x
+        db = gemm(dy, self._saved_t, a_mn=True, b_mn=True, out_dtype=torch.float32)[:, :self.r]  # dY^T (scale x A^T)
+        return dx, da, db

@@ -309,3 +309,35 @@ def test_gemm_with_fused_kquant_dequant(kernel_lib, name, M, N, K):
     _lib.assert_status_ok("gemm_kquant epilogue")
     ref2 = torch.nn.functional.silu(ref + bias.float()) + resid.float()
     torch.testing.assert_close(got.float(), ref2, atol=0.02 * float(ref2.abs().max()), rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K,r", [(256, 128, 512, 8), (1000, 264, 1024, 16)])
+def test_nf4_lora_linear_fused_forward_and_backward(kernel_lib, M, N, K, r):
+    from neuralfn_b200.ops import _lib, infer
+    from neuralfn_b200.quant import kquant
+    dev = _dev()
+    rng = np.random.default_rng(4)
+    w0 = (rng.normal(size=N * K) * 0.05).astype(np.float32)
+    codes, absmax = kquant.nf4_encode(w0)
+    w = torch.from_numpy(kquant.nf4_decode(codes, absmax)).view(N, K).to(dev)
+    A = (torch.randn(r, K, device=dev) * 0.05).bfloat16()
+    B = (torch.randn(N, r, device=dev) * 0.05).bfloat16()
+    x = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
+    dy = (torch.randn(M, N, device=dev) * 0.1).bfloat16()
+    lin = infer.NF4LoRALinear(torch.from_numpy(codes).to(dev), torch.from_numpy(absmax).to(dev), N, K, A, B, alpha=16.0)
+    y = lin.forward(x)
+    _lib.assert_status_ok("nf4 lora forward")
+    s = 16.0 / r
+    xf, Af, Bf, wf = x.float(), A.float(), B.float(), w.bfloat16().float()
+    ref = xf @ wf.T + s * (xf @ Af.T) @ Bf.T
+    torch.testing.assert_close(y.float(), ref, atol=0.02 * float(ref.abs().max()), rtol=2e-2)
+    base_only = infer.NF4LoRALinear(lin.codes, lin.absmax, N, K, torch.zeros_like(A), B).forward(x)
+    torch.testing.assert_close(base_only.float(), xf @ wf.T, atol=0.02 * float(ref.abs().max()), rtol=2e-2)
+    dx, da, db = lin.backward(x, dy)
+    _lib.assert_status_ok("nf4 lora backward")
+    dyf = dy.float()
+    dx_ref = dyf @ wf + s * (dyf @ Bf) @ Af
+    da_ref = s * (dyf @ Bf).T @ xf
+    db_ref = s * dyf.T @ (xf @ Af.T)
+    for got, want in ((dx.float(), dx_ref), (da, da_ref), (db, db_ref)):
+        torch.testing.assert_close(got, want, atol=0.03 * float(want.abs().max()), rtol=3e-2)
