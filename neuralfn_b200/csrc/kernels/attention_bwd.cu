@@ -9,8 +9,8 @@
 //     dV  += P^T dO_i           (keys x D, accumulated over all steps in TMEM)
 //     dK  += dS^T Q_i           (keys x D, accumulated over all steps in TMEM)
 //     dQ_i = dS K_j             (queries x D)         -> TMEM [0,D) (re-uses the S columns)
-// 128 softmax threads (one key row each) turn S^T/dP^T into P^T and dS^T = P^T o (dP^T - delta)
-// and write both as bf16 into 128-byte-swizzled shared tiles; the same dS^T tile serves
+// 256 softmax threads (two per key row, each taking half of the query columns; the backward has
+// no row reductions) turn S^T/dP^T into P^T and dS^T = P^T o (dP^T - delta) and write both as bf16 into 128-byte-swizzled shared tiles; the same dS^T tile serves
 // as K-major A operand for dK and as MN-major A operand for dQ, and the Q/dO/K tiles
 // serve as K-major or MN-major B operands, so nothing is ever transposed in memory.
 // dQ partial tiles are added into an fp32 accumulator with vector reductions; dK/dV
@@ -26,7 +26,9 @@
 namespace nfn {
 
 constexpr int AB_BLK = 128;
-constexpr int AB_THREADS = 160;
+constexpr int AB_SOFTMAX_WARPS = 8;  // two per TMEM lane quarter: each takes half of the columns
+constexpr int AB_CTRL_WARP = AB_SOFTMAX_WARPS;
+constexpr int AB_THREADS = (AB_SOFTMAX_WARPS + 1) * 32;
 
 struct AttnBwdParams {
   const float* lse;    // [B, Hq, T]
@@ -65,15 +67,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sQdO = sV + TILE;                 // STAGES x (Q tile, dO tile)
   uint8_t* sP = sQdO + STAGES * 2 * TILE;
   uint8_t* sdS = sP + PT;
-  float* s_lse = reinterpret_cast<float*>(sdS + PT);  // [4 warps][128]
-  float* s_delta = s_lse + 4 * AB_BLK;                // [4 warps][128]
+  float* s_lse = reinterpret_cast<float*>(sdS + PT);  // [8 warps][64]
+  float* s_delta = s_lse + 4 * AB_BLK;                // [8 warps][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 4 * AB_BLK);
   uint64_t* bar_kv = bars;            // 1
   uint64_t* bar_qdo = bars + 1;       // STAGES (<= 2)
   uint64_t* bar_sdp = bars + 3;       // S^T and dP^T complete
-  uint64_t* bar_pds = bars + 4;       // 4 arrivals (one per warp): P^T and dS^T in shared memory
+  uint64_t* bar_pds = bars + 4;       // 8 arrivals (one per warp): P^T and dS^T in shared memory
   uint64_t* bar_out = bars + 5;       // dV/dK/dQ products retired
-  uint64_t* bar_dqfree = bars + 6;    // 4 arrivals (one per warp): dQ tile read out of TMEM
+  uint64_t* bar_dqfree = bars + 6;    // 8 arrivals (one per warp): dQ tile read out of TMEM
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -101,12 +103,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(smem_u32(&bar_qdo[0]), 1);
     mbar_init(smem_u32(&bar_qdo[1]), 1);
     mbar_init(smem_u32(bar_sdp), 1);
-    mbar_init(smem_u32(bar_pds), 4);  // one arrival per softmax warp
+    mbar_init(smem_u32(bar_pds), AB_SOFTMAX_WARPS);  // one arrival per softmax warp
     mbar_init(smem_u32(bar_out), 1);
-    mbar_init(smem_u32(bar_dqfree), 4);  // one arrival per softmax warp
+    mbar_init(smem_u32(bar_dqfree), AB_SOFTMAX_WARPS);  // one arrival per softmax warp
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == AB_CTRL_WARP) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tmem_relinquish();
   }
@@ -116,7 +118,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   const int row0 = b * p.T;
 
-  if (warp == 4) {
+  if (warp == AB_CTRL_WARP) {
     if (lane == 0 && nsteps > 0) {
       // ------------------------------------------------------ control thread --
       auto load_qdo = [&](int s) {
@@ -215,9 +217,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------ softmax threads --
-    const int r = threadIdx.x;   // key row within the block == TMEM lane; also query row for dQ
+    // warp w owns TMEM lanes 32 (w & 3) ... and, of every 128-column tile, the half (w >> 2): the
+    // backward pass has no row reductions (P and dS are element-wise given lse and delta), so two
+    // warps can share a row without talking to each other
+    const int quarter = warp & 3, half = warp >> 2;
+    const int r = quarter * 32 + lane;  // key row within the block == TMEM lane; also query row for dQ
     const int kidx = k0 + r;
-    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const float LOG2E = 1.4426950408889634f;
     bool ok = true;
     for (int s = 0; s < nsteps; ++s) {
@@ -227,12 +233,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // stage lse / delta of this query tile: every warp keeps a private copy of the 128
       // values, so only warp-level synchronisation is needed (no CTA barrier that a
       // timed-out warp could leave the others stuck on)
-      float* lse2 = s_lse + warp * AB_BLK;
-      float* dlt = s_delta + warp * AB_BLK;
+      float* lse2 = s_lse + warp * (AB_BLK / 2);   // this warp's 64 query columns
+      float* dlt = s_delta + warp * (AB_BLK / 2);
       __syncwarp();
 #pragma unroll
-      for (int e = 0; e < AB_BLK / 32; ++e) {
-        const int q = q0 + e * 32 + lane;
+      for (int e = 0; e < AB_BLK / 64; ++e) {
+        const int q = q0 + half * (AB_BLK / 2) + e * 32 + lane;
         const size_t idx = ((size_t)b * p.Hq + hq) * p.T + q;
         lse2[e * 32 + lane] = q < p.T ? p.lse[idx] * LOG2E : INFINITY;
         dlt[e * 32 + lane] = q < p.T ? p.delta[idx] : 0.f;
@@ -259,7 +265,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         return true;
       };
 #pragma unroll 1
-      for (int c = 0; c < AB_BLK / 32; ++c) {
+      for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t sv_[32], dp_[32];
         tmem_ld_32x32(t_row + COL_S + c * 32, sv_);
         tmem_ld_32x32(t_row + COL_DP + c * 32, dp_);
@@ -267,15 +273,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint32_t pk[16], dk_[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const int qa = c * 32 + 2 * e;
-          float p0 = fast_exp2(__uint_as_float(sv_[2 * e]) * p.scale_log2 - lse2[qa]);
-          float p1 = fast_exp2(__uint_as_float(sv_[2 * e + 1]) * p.scale_log2 - lse2[qa + 1]);
+          const int qa = c * 32 + 2 * e, ql = qa - half * (AB_BLK / 2);
+          float p0 = fast_exp2(__uint_as_float(sv_[2 * e]) * p.scale_log2 - lse2[ql]);
+          float p1 = fast_exp2(__uint_as_float(sv_[2 * e + 1]) * p.scale_log2 - lse2[ql + 1]);
           if (need_mask) {
             if (!visible(q0 + qa)) p0 = 0.f;
             if (!visible(q0 + qa + 1)) p1 = 0.f;
           }
-          const float d0 = p0 * (__uint_as_float(dp_[2 * e]) - dlt[qa]);
-          const float d1 = p1 * (__uint_as_float(dp_[2 * e + 1]) - dlt[qa + 1]);
+          const float d0 = p0 * (__uint_as_float(dp_[2 * e]) - dlt[ql]);
+          const float d1 = p1 * (__uint_as_float(dp_[2 * e + 1]) - dlt[ql + 1]);
           pk[e] = pack_bf16x2(p0, p1);
           dk_[e] = pack_bf16x2(d0, d1);
         }
@@ -303,7 +309,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int q = q0 + r;
         float* dst = p.dq_accum + (size_t)(row0 + q) * (p.Hq * D) + hq * D;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
           uint32_t v[32];
           tmem_ld_32x32(t_row + COL_DQ + c * 32, v);
           tmem_ld_wait();
@@ -329,7 +335,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         __nv_bfloat16* dkrow = p.dk + (size_t)(row0 + kidx) * p.ld_dk + hk * D;
         __nv_bfloat16* dvrow = p.dv + (size_t)(row0 + kidx) * p.ld_dv + hk * D;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
           uint32_t v[32];
           tmem_ld_32x32(t_row + COL_DV + c * 32, v);
           tmem_ld_wait();
@@ -355,7 +361,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
       }
-    } else if (nsteps == 0 && kidx < p.T) {
+    } else if (nsteps == 0 && kidx < p.T && half == 0) {
       // no query sees these keys: zero gradients
       __nv_bfloat16* dkrow = p.dk + (size_t)(row0 + kidx) * p.ld_dk + hk * D;
       __nv_bfloat16* dvrow = p.dv + (size_t)(row0 + kidx) * p.ld_dv + hk * D;
@@ -371,7 +377,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (*cta_abort) {
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
-  if (warp == 4) {
+  if (warp == AB_CTRL_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }

@@ -168,6 +168,33 @@ __device__ __forceinline__ void kq_decode_quarter<NFN_QTYPE_Q6_K>(const uint8_t*
   }
 }
 
+// Pulls the bytes a later k-block will decode into L1 so that the decode itself does not sit out a
+// full L2 / HBM round trip per stage (a decoder thread handles its stages one after another).
+__device__ __forceinline__ void kq_prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
+
+template <int QT>
+__device__ __forceinline__ void kq_prefetch(const uint8_t* rowp, int kb, int main_kb) {
+  if (kb >= main_kb) return;
+  if constexpr (QT == NFN_QTYPE_NF4_) {
+    kq_prefetch_l1(rowp + (size_t)kb * 32);
+  } else {
+    constexpr int BB = QT == NFN_QTYPE_Q4_K ? 144 : (QT == NFN_QTYPE_Q5_K ? 176 : 210);
+    const uint8_t* blk = rowp + (size_t)(kb >> 2) * BB;
+    const int j = kb & 3;
+    if constexpr (QT == NFN_QTYPE_Q4_K) {
+      kq_prefetch_l1(blk);
+      kq_prefetch_l1(blk + 16 + 32 * j);
+    } else if constexpr (QT == NFN_QTYPE_Q5_K) {
+      kq_prefetch_l1(blk);
+      kq_prefetch_l1(blk + 48 + 32 * j);
+    } else {
+      kq_prefetch_l1(blk + 64 * (j >> 1));
+      kq_prefetch_l1(blk + 128 + 32 * (j >> 1));
+      kq_prefetch_l1(blk + 192);
+    }
+  }
+}
+
 template <int QT>
 __global__ void __launch_bounds__(KQ_THREADS, 1)
 gemm_kquant_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_c,
@@ -290,7 +317,10 @@ gemm_kquant_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       const int nc = min(n, p.n - 1);
       const uint8_t* rowp = NF4 ? wq + (size_t)nc * (p.k / 2) : wq + (size_t)nc * blocks_per_row * BLOCK_BYTES;
       const float* absrow = NF4 ? absmax + (size_t)nc * main_kb : nullptr;
+      kq_prefetch<QT>(rowp, 0, main_kb);
+      kq_prefetch<QT>(rowp, 1, main_kb);
       for (int kb = 0; kb < total_kb; ++kb) {
+        kq_prefetch<QT>(rowp, kb + 2, main_kb);
         ok = mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1, cta_abort, p.status, NFN_ERR_WAIT_EMPTY);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;

@@ -86,18 +86,25 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int* cta_abort, int* status,
                                                   int code) {
-  // fast path: a short burst of polls before the clock is consulted
-#pragma unroll 1
-  for (int it = 0; it < 32; ++it)
-    if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_timer_ns();
+  // mbarrier.try_wait already parks the thread in hardware for a short, bounded time and wakes
+  // it when the phase completes, so the loop below polls without sleeping: a software sleep on
+  // top (even a "32 ns" one costs the better part of a microsecond) would land on every hand-off
+  // of a dependent pipeline such as attention's QK -> softmax -> PV chain. The wall clock is
+  // read only every 256 polls, and the thread starts yielding once it has waited 50 us.
+  unsigned long long t0 = 0;
 #pragma unroll 1
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 15u) == 15u) {
+    if ((it & 255u) == 255u) {
       if (*cta_abort) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) break;
-      __nanosleep(32);
+      const unsigned long long now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitNs) {
+        break;
+      } else if (now - t0 > 50000ull) {
+        __nanosleep(256);
+      }
     }
   }
   *cta_abort = 1;

@@ -167,3 +167,30 @@ def test_sha256(tmp_path):
     blob = bytes(range(256)) * 1000 + b"tail"
     (tmp_path / "blob").write_bytes(blob)
     assert sha256_file(tmp_path / "blob") == hashlib.sha256(blob).hexdigest()
+
+
+def test_dataset_manager_prepares_verifies_and_loads(tmp_path):
+    from neuralfn_b200.data import TokenDataset, TokenSampler
+    from neuralfn_b200.data.manager import DatasetError, DatasetManager
+    src = tmp_path / "corpus.txt"
+    src.write_text("\n\n".join(f"document number {i} says hello to the world" for i in range(40)), encoding="utf-8")
+    mgr = DatasetManager(tmp_path / "cache")
+    man = mgr.prepare_text("tiny", [src], tokenizer="bytes", val_fraction=0.1, shard_tokens=600, document_separator=[0])
+    assert man["vocab_size"] == 256 and man["val_tokens"] > 0 and len([s for s in man["shards"] if s["split"] == "train"]) >= 2
+    assert mgr.list() == [{"name": "tiny", "variants": ["bytes"]}] and mgr.info("tiny")["train_tokens"] == man["train_tokens"]
+    mgr.verify("tiny")
+    with pytest.raises(DatasetError):
+        mgr.prepare_text("tiny", [src], tokenizer="bytes")
+    ds = TokenDataset(str(mgr.path("tiny")))
+    assert ds.tokens("train") == man["train_tokens"] and ds.tokens("val") == man["val_tokens"]
+    x, y = TokenSampler(ds, "train", 16, 2).next()
+    assert x.shape == (2, 16) and (x[:, 1:] == y[:, :-1]).all() and int(x.max()) < 256
+    # a flipped byte in a shard is caught
+    shard = mgr.path("tiny") / man["shards"][0]["file"]
+    raw = bytearray(shard.read_bytes())
+    raw[-1] ^= 1
+    shard.write_bytes(bytes(raw))
+    with pytest.raises(DatasetError):
+        mgr.verify("tiny")
+    mgr.delete("tiny")
+    assert mgr.list() == []
