@@ -9,8 +9,8 @@
 //     dV  += P^T dO_i           (keys x D, accumulated over all steps in TMEM)
 //     dK  += dS^T Q_i           (keys x D, accumulated over all steps in TMEM)
 //     dQ_i = dS K_j             (queries x D)         -> TMEM [0,D) (re-uses the S columns)
-// 256 softmax threads (two per key row, each taking half of the query columns; the backward has
-// no row reductions) turn S^T/dP^T into P^T and dS^T = P^T o (dP^T - delta) and write both as bf16 into 128-byte-swizzled shared tiles; the same dS^T tile serves
+// 512 softmax threads (four per key row, each taking a quarter of the query columns; the backward
+// has no row reductions, and one warp per scheduler leaves most issue slots empty) turn S^T/dP^T into P^T and dS^T = P^T o (dP^T - delta) and write both as bf16 into 128-byte-swizzled shared tiles; the same dS^T tile serves
 // as K-major A operand for dK and as MN-major A operand for dQ, and the Q/dO/K tiles
 // serve as K-major or MN-major B operands, so nothing is ever transposed in memory.
 // dQ partial tiles are added into an fp32 accumulator with vector reductions; dK/dV
@@ -26,7 +26,9 @@
 namespace nfn {
 
 constexpr int AB_BLK = 128;
-constexpr int AB_SOFTMAX_WARPS = 8;  // two per TMEM lane quarter: each takes half of the columns
+constexpr int AB_SPLIT = 4;                        // warps per TMEM lane quarter; each takes 128 / AB_SPLIT columns
+constexpr int AB_COLS = 128 / AB_SPLIT;
+constexpr int AB_SOFTMAX_WARPS = 4 * AB_SPLIT;
 constexpr int AB_CTRL_WARP = AB_SOFTMAX_WARPS;
 constexpr int AB_THREADS = (AB_SOFTMAX_WARPS + 1) * 32;
 
@@ -67,15 +69,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sQdO = sV + TILE;                 // STAGES x (Q tile, dO tile)
   uint8_t* sP = sQdO + STAGES * 2 * TILE;
   uint8_t* sdS = sP + PT;
-  float* s_lse = reinterpret_cast<float*>(sdS + PT);  // [8 warps][64]
-  float* s_delta = s_lse + 4 * AB_BLK;                // [8 warps][64]
+  float* s_lse = reinterpret_cast<float*>(sdS + PT);  // [softmax warps][columns per warp]
+  float* s_delta = s_lse + 4 * AB_BLK;                // likewise
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 4 * AB_BLK);
   uint64_t* bar_kv = bars;            // 1
   uint64_t* bar_qdo = bars + 1;       // STAGES (<= 2)
   uint64_t* bar_sdp = bars + 3;       // S^T and dP^T complete
-  uint64_t* bar_pds = bars + 4;       // 8 arrivals (one per warp): P^T and dS^T in shared memory
+  uint64_t* bar_pds = bars + 4;       // one arrival per softmax warp: P^T and dS^T in shared memory
   uint64_t* bar_out = bars + 5;       // dV/dK/dQ products retired
-  uint64_t* bar_dqfree = bars + 6;    // 8 arrivals (one per warp): dQ tile read out of TMEM
+  uint64_t* bar_dqfree = bars + 6;    // one arrival per softmax warp: dQ tile read out of TMEM
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -220,7 +222,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // warp w owns TMEM lanes 32 (w & 3) ... and, of every 128-column tile, the half (w >> 2): the
     // backward pass has no row reductions (P and dS are element-wise given lse and delta), so two
     // warps can share a row without talking to each other
-    const int quarter = warp & 3, half = warp >> 2;
+    const int quarter = warp & 3, half = warp >> 2;  // `half`: which column slice (0 .. AB_SPLIT - 1)
     const int r = quarter * 32 + lane;  // key row within the block == TMEM lane; also query row for dQ
     const int kidx = k0 + r;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -233,12 +235,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // stage lse / delta of this query tile: every warp keeps a private copy of the 128
       // values, so only warp-level synchronisation is needed (no CTA barrier that a
       // timed-out warp could leave the others stuck on)
-      float* lse2 = s_lse + warp * (AB_BLK / 2);   // this warp's 64 query columns
-      float* dlt = s_delta + warp * (AB_BLK / 2);
+      float* lse2 = s_lse + warp * AB_COLS;   // this warp's query columns
+      float* dlt = s_delta + warp * AB_COLS;
       __syncwarp();
 #pragma unroll
-      for (int e = 0; e < AB_BLK / 64; ++e) {
-        const int q = q0 + half * (AB_BLK / 2) + e * 32 + lane;
+      for (int e = 0; e < AB_COLS / 32; ++e) {
+        const int q = q0 + half * AB_COLS + e * 32 + lane;
         const size_t idx = ((size_t)b * p.Hq + hq) * p.T + q;
         lse2[e * 32 + lane] = q < p.T ? p.lse[idx] * LOG2E : INFINITY;
         dlt[e * 32 + lane] = q < p.T ? p.delta[idx] : 0.f;
@@ -265,7 +267,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         return true;
       };
 #pragma unroll 1
-      for (int c = 2 * half; c < 2 * half + 2; ++c) {
+      for (int c = half * (AB_COLS / 32); c < (half + 1) * (AB_COLS / 32); ++c) {
         uint32_t sv_[32], dp_[32];
         tmem_ld_32x32(t_row + COL_S + c * 32, sv_);
         tmem_ld_32x32(t_row + COL_DP + c * 32, dp_);
@@ -273,7 +275,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint32_t pk[16], dk_[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const int qa = c * 32 + 2 * e, ql = qa - half * (AB_BLK / 2);
+          const int qa = c * 32 + 2 * e, ql = qa - half * AB_COLS;
           float p0 = fast_exp2(__uint_as_float(sv_[2 * e]) * p.scale_log2 - lse2[ql]);
           float p1 = fast_exp2(__uint_as_float(sv_[2 * e + 1]) * p.scale_log2 - lse2[ql + 1]);
           if (need_mask) {
@@ -309,7 +311,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int q = q0 + r;
         float* dst = p.dq_accum + (size_t)(row0 + q) * (p.Hq * D) + hq * D;
 #pragma unroll
-        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+        for (int c = half; c < D / 32; c += AB_SPLIT) {
           uint32_t v[32];
           tmem_ld_32x32(t_row + COL_DQ + c * 32, v);
           tmem_ld_wait();
@@ -335,7 +337,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         __nv_bfloat16* dkrow = p.dk + (size_t)(row0 + kidx) * p.ld_dk + hk * D;
         __nv_bfloat16* dvrow = p.dv + (size_t)(row0 + kidx) * p.ld_dv + hk * D;
 #pragma unroll
-        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+        for (int c = half; c < D / 32; c += AB_SPLIT) {
           uint32_t v[32];
           tmem_ld_32x32(t_row + COL_DV + c * 32, v);
           tmem_ld_wait();

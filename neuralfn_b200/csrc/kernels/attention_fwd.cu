@@ -1,7 +1,10 @@
 // Flash-attention forward on tcgen05 (sm_100a).
 //
-// One CTA handles a 128-query tile of one (batch, head). Warps 0-3 (128 threads, one
-// query row each) run the online softmax; warp 4 is the control warp whose lane 0
+// One CTA handles a 128-query tile of one (batch, head). Warps 0-7 run the online softmax: two
+// threads per query row (warps w and w + 4 share TMEM lane quarter w & 3), each taking half of the
+// key columns of S and half of the output columns, so that every scheduler has two warps to
+// interleave; the pair exchanges its half-row maxima (and, at the end, its half-row sums) through
+// four spare TMEM columns behind a two-arrival mbarrier. Warp 8 is the control warp whose lane 0
 // issues the TMA loads (Q once, K/V through a two-stage ring) and the two tensor-core
 // products per key block:
 //     S = Q K^T   (128 x 128 x D, accumulator in TMEM columns [0,128))
@@ -23,7 +26,9 @@ namespace nfn {
 
 constexpr int ATT_BM = 128;  // queries per CTA
 constexpr int ATT_BN = 128;  // keys per iteration
-constexpr int ATT_THREADS = 160;
+constexpr int ATT_SOFTMAX_WARPS = 8;
+constexpr int ATT_CTRL_WARP = ATT_SOFTMAX_WARPS;
+constexpr int ATT_THREADS = (ATT_SOFTMAX_WARPS + 1) * 32;
 
 struct AttnFwdParams {
   __nv_bfloat16* o;
@@ -55,8 +60,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr uint32_t V_BYTES = ATT_BN * D * 2;
   constexpr uint32_t P_BYTES = ATT_BM * ATT_BN * 2;
   constexpr uint32_t KV_STAGE = K_BYTES + V_BYTES;
-  constexpr uint32_t TMEM_COLS = 256;
+  constexpr uint32_t TMEM_COLS = (D == 64) ? 256 : 512;  // S | O | four mailbox columns
   constexpr uint32_t O_COL = 128;
+  constexpr uint32_t XCHG_COL = O_COL + D;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -81,7 +87,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* bar_s = bars + 3;      // 1
   uint64_t* bar_p = bars + 4;      // 4 arrivals (one per softmax warp)
   uint64_t* bar_o = bars + 5;      // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint64_t* bar_pair = bars + 6;   // 4 (one per lane quarter), 2 arrivals each
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -109,11 +116,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(smem_u32(&bar_kv[0]), 1);
     mbar_init(smem_u32(&bar_kv[1]), 1);
     mbar_init(smem_u32(bar_s), 1);
-    mbar_init(smem_u32(bar_p), 4);  // one arrival per softmax warp
+    mbar_init(smem_u32(bar_p), ATT_SOFTMAX_WARPS);  // one arrival per softmax warp
+    for (int qd = 0; qd < 4; ++qd) mbar_init(smem_u32(&bar_pair[qd]), 2);
     mbar_init(smem_u32(bar_o), 1);
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == ATT_CTRL_WARP) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tmem_relinquish();
   }
@@ -122,7 +130,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == ATT_CTRL_WARP) {
     if (lane == 0) {
       // ------------------------------------------------------ control thread --
       const int row0 = b * p.T;  // first token row of this batch in the [B*T, width] views
@@ -204,14 +212,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------ softmax threads --
-    const int r = threadIdx.x;  // row within the tile == TMEM lane
+    const int quarter = warp & 3, half = warp >> 2;
+    const int r = quarter * 32 + lane;  // row within the tile == TMEM lane
     const int q = q0 + r;
-    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    float m_run = -INFINITY, l_run = 0.f;
-    float acc[D];
+    constexpr int DH = D / 2;           // output columns this thread accumulates
+    constexpr int CH = ATT_BN / 64;     // 32-column slices of S per thread (its half of the keys)
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    float m_run = -INFINITY, l_run = 0.f;  // l_run covers this thread's key columns only
+    float acc[DH];
 #pragma unroll
-    for (int i = 0; i < D; ++i) acc[i] = 0.f;
+    for (int i = 0; i < DH; ++i) acc[i] = 0.f;
     bool ok = true;
+    uint32_t pair_phase = 0;
+    // hand `mine` to the other thread of this row and return its value
+    auto exchange = [&](float mine, int slot) -> float {
+      tmem_st_col(t_row + XCHG_COL + slot * 2 + half, __float_as_uint(mine));
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_pair[quarter]));
+      bool w = mbar_wait_bounded(smem_u32(&bar_pair[quarter]), pair_phase, cta_abort, p.status, NFN_ERR_WAIT_MISC);
+      pair_phase ^= 1;
+      w = __all_sync(0xffffffffu, w);
+      if (!w) ok = false;
+      tc_fence_after();
+      const uint32_t other = tmem_ld_col(t_row + XCHG_COL + slot * 2 + (half ^ 1));
+      tmem_ld_wait();
+      return __uint_as_float(other);
+    };
     for (int j = 0; j < nblk; ++j) {
       ok = mbar_wait_bounded(smem_u32(bar_s), j & 1, cta_abort, p.status, NFN_ERR_WAIT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
@@ -235,10 +263,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         return true;
       };
-      // pass 1: row max
+      // pass 1: maximum over this thread's half of the keys, then over the pair
       float m_blk = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < ATT_BN / 32; ++c) {
+      for (int c = half * CH; c < (half + 1) * CH; ++c) {
         uint32_t s[32];
         tmem_ld_32x32(t_row + c * 32, s);
         tmem_ld_wait();
@@ -251,6 +279,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           for (int i = 0; i < 32; ++i) m_blk = fmaxf(m_blk, __uint_as_float(s[i]));
         }
       }
+      m_blk = fmaxf(m_blk, exchange(m_blk, j & 1));
+      if (!ok) break;
       const float m_new = fmaxf(m_run, m_blk);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = fast_exp2((m_run - m_use) * p.scale_log2);  // m_run = -inf -> 0
@@ -258,7 +288,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // pass 2: p = exp2(s*scale - m*scale), row sum, bf16 P into swizzled smem
       float l_blk = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < ATT_BN / 32; ++c) {
+      for (int c = half * CH; c < (half + 1) * CH; ++c) {
         uint32_t s[32];
         tmem_ld_32x32(t_row + c * 32, s);
         tmem_ld_wait();
@@ -294,26 +324,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       l_run = l_run * alpha + l_blk;
       m_run = m_new;
 #pragma unroll
-      for (int i = 0; i < D; ++i) acc[i] *= alpha;
+      for (int i = 0; i < DH; ++i) acc[i] *= alpha;
       ok = mbar_wait_bounded(smem_u32(bar_o), j & 1, cta_abort, p.status, NFN_ERR_WAIT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < DH / 32; ++c) {
         uint32_t o[32];
-        tmem_ld_32x32(t_row + O_COL + c * 32, o);
+        tmem_ld_32x32(t_row + O_COL + half * DH + c * 32, o);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(o[i]);
       }
       tc_fence_before();
     }
+    if (ok) l_run += exchange(l_run, nblk & 1);  // both halves of the row sum
     if (ok && q < p.T) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* orow = p.o + (size_t)(b * p.T + q) * p.ld_o + h * D;
+      __nv_bfloat16* orow = p.o + (size_t)(b * p.T + q) * p.ld_o + h * D + half * DH;
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) {
+      for (int i = 0; i < DH / 8; ++i) {
         uint4 u;
         u.x = pack_bf16x2(acc[8 * i] * inv, acc[8 * i + 1] * inv);
         u.y = pack_bf16x2(acc[8 * i + 2] * inv, acc[8 * i + 3] * inv);
@@ -321,7 +352,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         u.w = pack_bf16x2(acc[8 * i + 6] * inv, acc[8 * i + 7] * inv);
         reinterpret_cast<uint4*>(orow)[i] = u;
       }
-      if (p.lse)
+      if (p.lse && half == 0)
         p.lse[((size_t)b * p.Hq + h) * p.T + q] =
             l_run > 0.f ? m_run * p.scale + logf(l_run) : -INFINITY;
     }
@@ -332,7 +363,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (*cta_abort) {
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
-  if (warp == 4) {
+  if (warp == ATT_CTRL_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }

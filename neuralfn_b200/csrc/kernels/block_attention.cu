@@ -7,8 +7,9 @@
 // One CTA handles one (sequence, kv head, chunk of the head group, KV split). The 128 MMA rows
 // are (query head of the group) x (block row): with R <= 16 eight query heads share one pass over
 // the keys, which is what makes the pass HBM-bound rather than FLOP-bound. Structure as in the
-// training forward kernel: warps 0-3 own one row each (online softmax out of TMEM, P written as
-// bf16 into a swizzled tile), warp 4 issues TMA loads of 128-key cache tiles (two-stage ring)
+// training forward kernel: warps 0-7 run the online softmax out of TMEM, two threads per row (each
+// half of the key columns and of the output columns; they swap half-row maxima and sums through
+// spare TMEM columns), P goes as bf16 into a swizzled tile; warp 8 issues TMA loads of 128-key cache tiles (two-stage ring)
 // and the two products S = Q K^T and O_j = P V.
 //
 // Cache layout [sequence][kv head][cap][D] bf16; a ring (local layer) stores position p in row
@@ -32,7 +33,9 @@ namespace nfn {
 
 constexpr int BA_M = 128;
 constexpr int BA_N = 128;
-constexpr int BA_THREADS = 160;
+constexpr int BA_SOFTMAX_WARPS = 8;  // two per TMEM lane quarter: each takes half of the key columns and half of the output columns
+constexpr int BA_CTRL_WARP = BA_SOFTMAX_WARPS;
+constexpr int BA_THREADS = (BA_SOFTMAX_WARPS + 1) * 32;
 
 struct BlockAttnParams {
   const __nv_bfloat16* qkv;
@@ -65,7 +68,7 @@ __global__ void __launch_bounds__(BA_THREADS, (D == 64 ? 2 : 1))
 block_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const BlockAttnParams p) {
   constexpr uint32_t Q_BYTES = BA_M * D * 2, K_BYTES = BA_N * D * 2, P_BYTES = BA_M * BA_N * 2;
   constexpr uint32_t KV_STAGE = 2 * K_BYTES;
-  constexpr uint32_t TMEM_COLS = 256, O_COL = 128;
+  constexpr uint32_t TMEM_COLS = (D == 64) ? 256 : 512, O_COL = 128, XCHG_COL = O_COL + D;  // S | O | four mailbox columns
   constexpr int CH = D / 8;  // 16-byte chunks per row
 
   const int s = blockIdx.x, y = blockIdx.y, b = blockIdx.z;
@@ -93,7 +96,8 @@ block_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   uint64_t* bar_s = bars + 3;
   uint64_t* bar_p = bars + 4;   // 4 arrivals
   uint64_t* bar_o = bars + 5;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint64_t* bar_pair = bars + 6;  // 4 (one per lane quarter), 2 arrivals each
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* sh_last = reinterpret_cast<int*>(tmem_slot + 2);
 
@@ -110,15 +114,16 @@ block_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   if (threadIdx.x == 0) {
     *cta_abort = 0;
     *sh_last = 0;
-    mbar_init(smem_u32(bar_q), 4);  // one arrival per softmax warp
+    mbar_init(smem_u32(bar_q), BA_SOFTMAX_WARPS);  // one arrival per softmax warp
+    for (int qd = 0; qd < 4; ++qd) mbar_init(smem_u32(&bar_pair[qd]), 2);
     mbar_init(smem_u32(&bar_kv[0]), 1);
     mbar_init(smem_u32(&bar_kv[1]), 1);
     mbar_init(smem_u32(bar_s), 1);
-    mbar_init(smem_u32(bar_p), 4);  // one arrival per softmax warp
+    mbar_init(smem_u32(bar_p), BA_SOFTMAX_WARPS);  // one arrival per softmax warp
     mbar_init(smem_u32(bar_o), 1);
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == BA_CTRL_WARP) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tmem_relinquish();
   }
@@ -127,7 +132,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == BA_CTRL_WARP) {
     if (lane == 0 && nblk > 0) {
       // ------------------------------------------------------ control thread --
       const int crow0 = (b * p.Hkv + hk) * p.cap;  // first cache row of this (sequence, kv head)
@@ -202,24 +207,42 @@ block_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     }
   } else {
     // ------------------------------------------------------ softmax threads --
-    const int m = threadIdx.x;               // MMA row == TMEM lane
+    const int quarter = warp & 3, half = warp >> 2;
+    const int m = quarter * 32 + lane;       // MMA row == TMEM lane
+    constexpr int DH = D / 2;                // output columns this thread accumulates
     const int gl = m / p.RP, r = m % p.RP;   // head inside the chunk, row inside the block
     const int g = g0 + gl;
     const bool row_valid = gl < p.GC && g < p.G && r < nrows;
     const int head = hk * p.G + g;
-    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    float m_run = -INFINITY, l_run = 0.f;
-    float acc[D];
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    float m_run = -INFINITY, l_run = 0.f;  // l_run: this thread's key columns only until the final exchange
+    float acc[DH];
 #pragma unroll
-    for (int i = 0; i < D; ++i) acc[i] = 0.f;
+    for (int i = 0; i < DH; ++i) acc[i] = 0.f;
     bool ok = true;
+    uint32_t pair_phase = 0;
+    auto exchange = [&](float mine, int slot) -> float {  // swap a value with the other thread of this row
+      tmem_st_col(t_row + XCHG_COL + slot * 2 + half, __float_as_uint(mine));
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_pair[quarter]));
+      bool w = mbar_wait_bounded(smem_u32(&bar_pair[quarter]), pair_phase, cta_abort, p.status, NFN_ERR_WAIT_MISC);
+      pair_phase ^= 1;
+      w = __all_sync(0xffffffffu, w);
+      if (!w) ok = false;
+      tc_fence_after();
+      const uint32_t other = tmem_ld_col(t_row + XCHG_COL + slot * 2 + (half ^ 1));
+      tmem_ld_wait();
+      return __uint_as_float(other);
+    };
 
     if (nblk > 0) {
       // Q row (zeros for padding rows) and, in split 0, key/value row m of the block itself
       const uint4 zero = make_uint4(0, 0, 0, 0);
       const uint4* qsrc = reinterpret_cast<const uint4*>(p.qkv + (size_t)(b * p.R + r) * p.ld + (size_t)head * D);
 #pragma unroll
-      for (int c = 0; c < CH; ++c) *reinterpret_cast<uint4*>(sw128_chunk(sQ, m, c)) = row_valid ? qsrc[c] : zero;
+      for (int c = half * (CH / 2); c < (half + 1) * (CH / 2); ++c) *reinterpret_cast<uint4*>(sw128_chunk(sQ, m, c)) = row_valid ? qsrc[c] : zero;
       if (staged) {
         const bool kv_valid = m < nrows;
         const __nv_bfloat16* rowp = p.qkv + (size_t)(b * p.R + (kv_valid ? m : 0)) * p.ld;
@@ -229,7 +252,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         uint4* ko = copy_out ? reinterpret_cast<uint4*>(p.stage_k + ((size_t)(b * p.R + m) * p.Hkv + hk) * D) : nullptr;
         uint4* vo = copy_out ? reinterpret_cast<uint4*>(p.stage_v + ((size_t)(b * p.R + m) * p.Hkv + hk) * D) : nullptr;
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
+        for (int c = half * (CH / 2); c < (half + 1) * (CH / 2); ++c) {
           const uint4 kq = kv_valid ? ksrc[c] : zero, vq = kv_valid ? vsrc[c] : zero;
           *reinterpret_cast<uint4*>(sw128_chunk(sKV, m, c)) = kq;
           *reinterpret_cast<uint4*>(sw128_chunk(sKV + K_BYTES, m, c)) = vq;
@@ -262,7 +285,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       };
       float m_blk = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < BA_N / 32; ++c) {
+      for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t sv[32];
         tmem_ld_32x32(t_row + c * 32, sv);
         tmem_ld_wait();
@@ -270,13 +293,15 @@ block_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         for (int i = 0; i < 32; ++i)
           if (visible(c * 32 + i)) m_blk = fmaxf(m_blk, __uint_as_float(sv[i]));
       }
+      m_blk = fmaxf(m_blk, exchange(m_blk, j & 1));
+      if (!ok) break;
       const float m_new = fmaxf(m_run, m_blk);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = fast_exp2((m_run - m_use) * p.scale_log2);
       const float moff = m_use * p.scale_log2;
       float l_blk = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < BA_N / 32; ++c) {
+      for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t sv[32];
         tmem_ld_32x32(t_row + c * 32, sv);
         tmem_ld_wait();
@@ -303,15 +328,15 @@ block_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       l_run = l_run * alpha + l_blk;
       m_run = m_new;
 #pragma unroll
-      for (int i = 0; i < D; ++i) acc[i] *= alpha;
+      for (int i = 0; i < DH; ++i) acc[i] *= alpha;
       ok = mbar_wait_bounded(smem_u32(bar_o), j & 1, cta_abort, p.status, NFN_ERR_WAIT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < DH / 32; ++c) {
         uint32_t o[32];
-        tmem_ld_32x32(t_row + O_COL + c * 32, o);
+        tmem_ld_32x32(t_row + O_COL + half * DH + c * 32, o);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(o[i]);
@@ -320,24 +345,28 @@ block_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     }
 
     // ---- combine -------------------------------------------------------------------------
+    if (ok && nblk > 0) l_run += exchange(l_run, nblk & 1);  // the whole row's sum in both threads
     const bool failed = !__all_sync(0xffffffffu, ok);
     if (p.splits > 1) {
       float* mine = p.part + ((((size_t)b * gridDim.y + y) * p.splits + s) * BA_M + m) * (D + 4);
       if (row_valid) {
-        mine[0] = failed ? -INFINITY : m_run;
-        mine[1] = failed ? 0.f : l_run;
+        if (half == 0) {
+          mine[0] = failed ? -INFINITY : m_run;
+          mine[1] = failed ? 0.f : l_run;
+        }
 #pragma unroll
-        for (int i = 0; i < D / 4; ++i) reinterpret_cast<float4*>(mine + 4)[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+        for (int i = 0; i < DH / 4; ++i)
+          reinterpret_cast<float4*>(mine + 4 + half * DH)[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
       }
       __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (m == 0) {
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (threadIdx.x == 0) {
         const int t = atomicAdd(&p.tickets[b * gridDim.y + y], 1);
         const int last = (t == p.splits - 1);
         if (last) p.tickets[b * gridDim.y + y] = 0;  // ready for the next launch
         *sh_last = last;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       if (*sh_last && row_valid) {
         __threadfence();
         const float* base = p.part + (((size_t)b * gridDim.y + y) * p.splits * BA_M + m) * (D + 4);
@@ -347,14 +376,14 @@ block_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         const float Mu = (M == -INFINITY) ? 0.f : M;
         float L = 0.f;
 #pragma unroll
-        for (int i = 0; i < D; ++i) acc[i] = 0.f;
+        for (int i = 0; i < DH; ++i) acc[i] = 0.f;
         for (int i = 0; i < p.splits; ++i) {
           const float* ps = base + i * sstride;
           const float w = fast_exp2((__ldcg(ps) - Mu) * p.scale_log2);
           L += w * __ldcg(ps + 1);
 #pragma unroll
-          for (int d4 = 0; d4 < D / 4; ++d4) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(ps + 4) + d4);
+          for (int d4 = 0; d4 < DH / 4; ++d4) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(ps + 4 + half * DH) + d4);
             acc[4 * d4] += w * v.x; acc[4 * d4 + 1] += w * v.y; acc[4 * d4 + 2] += w * v.z; acc[4 * d4 + 3] += w * v.w;
           }
         }
@@ -363,9 +392,9 @@ block_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     }
     if ((p.splits == 1 || *sh_last) && row_valid && !failed) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      uint4* orow = reinterpret_cast<uint4*>(p.out + (size_t)(b * p.R + r) * p.ld_o + (size_t)head * D);
+      uint4* orow = reinterpret_cast<uint4*>(p.out + (size_t)(b * p.R + r) * p.ld_o + (size_t)head * D + half * DH);
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) {
+      for (int i = 0; i < DH / 8; ++i) {
         uint4 u;
         u.x = pack_bf16x2(acc[8 * i] * inv, acc[8 * i + 1] * inv);
         u.y = pack_bf16x2(acc[8 * i + 2] * inv, acc[8 * i + 3] * inv);
@@ -381,7 +410,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   if (*cta_abort) {
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
-  if (warp == 4) {
+  if (warp == BA_CTRL_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }

@@ -254,6 +254,17 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, int a_mn_ma
          | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// One 32-bit value per lane to / from a single TMEM column (a few spare columns make a cheap mailbox
+// between the warps that share a lane quarter).
+__device__ __forceinline__ void tmem_st_col(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t tmem_ld_col(uint32_t taddr) {
+  uint32_t v;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v) : "r"(taddr) : "memory");
+  return v;
+}
+
 // ---------------------------------------------------------------- numerics --
 __device__ __forceinline__ float fast_tanh(float x) {
   float y;
