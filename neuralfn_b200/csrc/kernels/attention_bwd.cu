@@ -228,6 +228,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const float LOG2E = 1.4426950408889634f;
     bool ok = true;
+    float nx_lse[AB_COLS / 32], nx_dlt[AB_COLS / 32];
+    auto fetch_stats = [&](int s2) {  // lse (in log2 units) and delta of this warp's query columns at step s2
+      const int hq2 = hk * G + s2 / nqb;
+      const int q02 = (i_lo + s2 % nqb) * AB_BLK;
+#pragma unroll
+      for (int e = 0; e < AB_COLS / 32; ++e) {
+        const int q = q02 + half * AB_COLS + e * 32 + lane;
+        const size_t idx = ((size_t)b * p.Hq + hq2) * p.T + q;
+        nx_lse[e] = q < p.T ? __ldg(p.lse + idx) * LOG2E : INFINITY;
+        nx_dlt[e] = q < p.T ? __ldg(p.delta + idx) : 0.f;
+      }
+    };
     for (int s = 0; s < nsteps; ++s) {
       const int hq = hk * G + s / nqb;
       const int i = i_lo + s % nqb;
@@ -235,15 +247,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // stage lse / delta of this query tile: every warp keeps a private copy of the 128
       // values, so only warp-level synchronisation is needed (no CTA barrier that a
       // timed-out warp could leave the others stuck on)
+      // (the values were fetched into registers during the previous step's dQ phase, so their
+      // latency is off the critical path)
       float* lse2 = s_lse + warp * AB_COLS;   // this warp's query columns
       float* dlt = s_delta + warp * AB_COLS;
+      if (s == 0) fetch_stats(0);
       __syncwarp();
 #pragma unroll
       for (int e = 0; e < AB_COLS / 32; ++e) {
-        const int q = q0 + half * AB_COLS + e * 32 + lane;
-        const size_t idx = ((size_t)b * p.Hq + hq) * p.T + q;
-        lse2[e * 32 + lane] = q < p.T ? p.lse[idx] * LOG2E : INFINITY;
-        dlt[e * 32 + lane] = q < p.T ? p.delta[idx] : 0.f;
+        lse2[e * 32 + lane] = nx_lse[e];
+        dlt[e * 32 + lane] = nx_dlt[e];
       }
       __syncwarp();
       ok = mbar_wait_bounded(smem_u32(bar_sdp), s & 1, cta_abort, p.status, NFN_ERR_WAIT_TMEM_FULL);
@@ -302,6 +315,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bar_pds));
+      if (s + 1 < nsteps) fetch_stats(s + 1);
       // dQ tile: lane r == query row q0 + r
       ok = mbar_wait_bounded(smem_u32(bar_out), s & 1, cta_abort, p.status, NFN_ERR_WAIT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
