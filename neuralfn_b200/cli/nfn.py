@@ -160,6 +160,22 @@ def cmd_checkpoint_layout(a) -> int:
     return 0
 
 
+def cmd_kernels(_a) -> int:
+    from ..ops.registry import coverage_report, coverage_summary
+    print(json.dumps({"summary": coverage_summary(), "kernels": coverage_report()}, indent=2))
+    return 0
+
+
+def cmd_families(_a) -> int:
+    from ..native_registry import capability_proof_for, native_families_report
+    rows = native_families_report()
+    for r in rows:
+        p = capability_proof_for(r["family"])
+        r["native_training"], r["native_inference"], r["reasons"] = p.native_training, p.native_inference, list(p.reasons)
+    print(json.dumps(rows, indent=2))
+    return 0
+
+
 def cmd_list_templates(_a) -> int:
     from ..native_templates import GPT_VARIANTS, LLAMA_TEMPLATES
     print(json.dumps({"gpt": list(GPT_VARIANTS), "llama": list(LLAMA_TEMPLATES)}, indent=2))
@@ -230,6 +246,8 @@ def build_parser() -> argparse.ArgumentParser:
     sub.add_parser("list-templates").set_defaults(fn=cmd_list_templates)
     sub.add_parser("list-presets").set_defaults(fn=cmd_list_presets)
     sub.add_parser("native-info").set_defaults(fn=cmd_native_info)
+    sub.add_parser("kernels", help="kernel catalogue and coverage of the built library").set_defaults(fn=cmd_kernels)
+    sub.add_parser("families", help="model families, their execution routes and capability proofs").set_defaults(fn=cmd_families)
     d = sub.add_parser("dataset-info")
     d.add_argument("path")
     d.add_argument("--seq-len", type=int, default=1024)

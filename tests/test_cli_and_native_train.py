@@ -54,3 +54,21 @@ def test_train_resume_and_infer_end_to_end(tmp_path):
     gen = json.loads(_nfn("infer", "--checkpoint", str(out / "model_00000020.bin"), "--prompt-tokens",
                           ",".join(map(str, period[:12])), "--max-new-tokens", "8").stdout.strip().splitlines()[-1])
     assert gen["status"] == "ok" and len(gen["generated"][0]) == 8
+
+
+def test_kernel_registry_matches_the_built_library_and_examples_run():
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from neuralfn_b200.ops import _lib
+    from neuralfn_b200.ops.registry import KERNELS, coverage_report, coverage_summary
+    rows = coverage_report()
+    assert len(rows) == len(KERNELS)
+    if _lib.available():
+        assert not [r["op"] for r in rows if r["status"] == "missing"]
+        s = coverage_summary()
+        assert s["native"] >= 35 and s["tensor_core_kernels"] >= 6
+    root = Path(__file__).resolve().parents[1]
+    out = subprocess.run([sys.executable, str(root / "examples" / "xor_graph.py"), "/tmp/nfn_xor_example.json"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "final MSE" in out.stdout
