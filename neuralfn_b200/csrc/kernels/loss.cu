@@ -60,11 +60,20 @@ ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int* __restrict__ ta
   const int nvec = ld / 8;       // 16-byte vectors per row (ld % 8 == 0)
   const uint4* gv = reinterpret_cast<const uint4*>(g);
 
+  if (STAGE) {
+    // Bring the whole row into shared memory with asynchronous 16-byte copies: every thread has
+    // all of its vectors in flight at once instead of one dependent load per loop iteration
+    // (which caps a 1024-thread SM at about 16 KB in flight, a third of what HBM can deliver).
+    for (int i = threadIdx.x; i < nvec; i += CE_THREADS)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(ce_smem + i)), "l"(gv + i) : "memory");
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+    // each thread only reads back the vectors it copied itself: no barrier needed here
+  }
+
   // pass 1: online max / sum of exp over the valid vocabulary
   float m = -INFINITY, s = 0.f;
   for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
-    const uint4 u = gv[i];
-    if (STAGE) ce_smem[i] = u;
+    const uint4 u = STAGE ? ce_smem[i] : gv[i];
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
     float f[8];
 #pragma unroll

@@ -8,6 +8,8 @@
 //
 // Reference counterparts: neuralfn/csrc/tile_cuda/kernels.cu:13960-14934 (rms/layer norm
 // family) and :19111-19155 (qk_rms_norm_packed_bf16 forward/backward).
+#include <algorithm>
+
 #include "common.h"
 #include "sm100_ptx.cuh"
 
@@ -298,6 +300,89 @@ extern "C" int nfn_norm_backward_dx(const void* dy, const void* x, const void* w
   });
 }
 
+// dx, dweight and dbias in ONE pass over dy and x. Each block strides over the rows (one warp
+// per row at a time), keeps its column partials of dweight / dbias in registers, folds its eight
+// warps through shared memory at the end and writes one partial row; the small final kernel sums
+// the partial rows. Compared with separate dx and dweight/dbias kernels this reads dy and x once
+// instead of twice and keeps every load a 16-byte vector.
+template <int VEC>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                      const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
+                      const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dresid,
+                      __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int C, int mode, int centered) {
+  constexpr int RPB = NORM_THREADS / 32;
+  __shared__ float sacc[RPB][VEC * 256];
+  const int lane = threadIdx.x & 31, wrow = threadIdx.x >> 5;
+  float aw[VEC][8], ab[VEC][8], wv[VEC][8];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int c = (i * 32 + lane) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { aw[i][j] = 0.f; ab[i][j] = 0.f; wv[i][j] = 1.f; }
+    if (w && c < C) {
+      load8(w + c, wv[i]);
+      if (centered) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) wv[i][j] += 1.f;
+      }
+    }
+  }
+  for (int row = blockIdx.x * RPB + wrow; row < rows; row += gridDim.x * RPB) {
+    const float mean = (mode == 0) ? mean_in[row] : 0.f;
+    const float rstd = rstd_in[row];
+    const size_t off = (size_t)row * C;
+    float g[VEC][8], n[VEC][8];
+    float sg = 0.f, sgn = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < C) {
+        float xv[8];
+        load8(dy + off + c, g[i]);
+        load8(x + off + c, xv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          n[i][j] = (xv[j] - mean) * rstd;
+          aw[i][j] += g[i][j] * n[i][j];
+          ab[i][j] += g[i][j];
+          g[i][j] *= wv[i][j];
+          sg += g[i][j];
+          sgn += g[i][j] * n[i][j];
+        }
+      }
+    }
+    sg = (mode == 0) ? warp_sum(sg) / C : 0.f;
+    sgn = warp_sum(sgn) / C;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < C) {
+        float o[8], r[8];
+        if (dresid) load8(dresid + off + c, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - sg - n[i][j] * sgn) + (dresid ? r[j] : 0.f);
+        store8(dx + off + c, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < VEC; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sacc[wrow][(i * 32 + lane) * 8 + j] = pass == 0 ? aw[i][j] : ab[i][j];
+    __syncthreads();
+    for (int c = threadIdx.x; c < C; c += NORM_THREADS) {
+      float t = 0.f;
+#pragma unroll
+      for (int r = 0; r < RPB; ++r) t += sacc[r][c];
+      partial[((size_t)blockIdx.x * 2 + pass) * C + c] = t;
+    }
+  }
+}
+
 // scratch: fp32 [ry * 2 * C]; ry = nfn_norm_wb_rows()
 extern "C" int nfn_norm_wb_rows(void) { return 64; }
 
@@ -314,6 +399,33 @@ extern "C" int nfn_norm_backward_wb(const void* dy, const void* x, const float* 
   norm_bwd_wb_final_kernel<<<ceil_div(C, 256), 256, 0, st>>>(scratch, (__nv_bfloat16*)dw,
                                                              (__nv_bfloat16*)db, RY, C, accumulate);
   return launch_check("norm_bwd_wb", 2);
+}
+
+// Partial rows the fused backward may write: scratch must hold nfn_norm_fused_rows() * 2 * C floats.
+extern "C" int nfn_norm_fused_rows(void) { return 2 * 160; }
+
+extern "C" int nfn_norm_backward(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, const void* dresid,
+                                 void* dx, void* dw, void* db, float* scratch, int rows, int C, int mode, int centered, int accumulate,
+                                 nfn_stream_t stream) {
+  if (rows <= 0) return 0;
+  if (C % 8) return fail(-1, "norm_backward: C must be a multiple of 8");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (C > 1024) {  // wide rows: the two-kernel path
+    int rc = nfn_norm_backward_dx(dy, x, w, mean, rstd, dresid, dx, rows, C, mode, centered, stream);
+    if (rc) return rc;
+    return nfn_norm_backward_wb(dy, x, mean, rstd, dw, db, scratch, rows, C, mode, accumulate, stream);
+  }
+  const int grid = std::min(ceil_div(rows, NORM_THREADS / 32), std::min(2 * sm_count(), nfn_norm_fused_rows()));
+#define NFN_FUSED(V)                                                                                                   \
+  norm_bwd_fused_kernel<V><<<grid, NORM_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,           \
+      (const __nv_bfloat16*)w, mean, rstd, (const __nv_bfloat16*)dresid, (__nv_bfloat16*)dx, scratch, rows, C, mode, centered)
+  if (C <= 256) NFN_FUSED(1);
+  else if (C <= 512) NFN_FUSED(2);
+  else if (C <= 768) NFN_FUSED(3);
+  else NFN_FUSED(4);
+#undef NFN_FUSED
+  norm_bwd_wb_final_kernel<<<ceil_div(C, 256), 256, 0, st>>>(scratch, (__nv_bfloat16*)dw, (__nv_bfloat16*)db, grid, C, accumulate);
+  return launch_check("norm_backward", 2);
 }
 
 // scratch: fp32 [64 * C]

@@ -262,7 +262,7 @@ class GPT2Engine:
         self.d_att = e(N, C)
         self.delta = e(batch, cfg.n_head, seq, dtype=f32)
         self.dq_accum = e(N, C, dtype=f32)
-        self.scratch = e(64 * 2 * max(Hd, 3 * C), dtype=f32)
+        self.scratch = e(max(64 * 2 * max(Hd, 3 * C), K.norm_fused_rows() * 2 * C), dtype=f32)
         self.ws = e(32 * 1024 * 1024, dtype=f32)  # split-K partial slices of the weight-gradient GEMMs
         self.tokens = torch.zeros(N, device=dev, dtype=torch.int32)
         self.targets = torch.zeros(N, device=dev, dtype=torch.int32)
@@ -320,10 +320,8 @@ class GPT2Engine:
         gemm(dlogits, self.lnf, a_mn=True, b_mn=True, out=g["wte"])
         x_last = self.acts[-1].x2 if self.acts else self.x0
         dx, spare = self.d_res_a, self.d_res_b
-        K.norm_backward_dx(self.d_ln, x_last, p["ln_f.weight"], self.lnf_mean, self.lnf_rstd,
-                           mode=K.NORM_LAYER, out=dx)
-        K.norm_backward_wb(self.d_ln, x_last, self.lnf_mean, self.lnf_rstd, g["ln_f.weight"],
-                           g["ln_f.bias"], sc, mode=K.NORM_LAYER)
+        K.norm_backward(self.d_ln, x_last, p["ln_f.weight"], self.lnf_mean, self.lnf_rstd, g["ln_f.weight"], g["ln_f.bias"], sc,
+                        mode=K.NORM_LAYER, out=dx)
         for l in range(cfg.n_layer - 1, -1, -1):
             a = self.acts[l]
             pre = f"h.{l}."
@@ -336,10 +334,8 @@ class GPT2Engine:
             gemm(self.d_fc, p[pre + "mlp.c_fc.weight"], b_mn=True, out=self.d_ln)
             gemm(self.d_fc, a.ln2, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "mlp.c_fc.weight"])
             K.colsum(self.d_fc, g[pre + "mlp.c_fc.bias"], sc)
-            K.norm_backward_dx(self.d_ln, a.x1, p[pre + "ln_2.weight"], a.ln2_mean, a.ln2_rstd,
-                               mode=K.NORM_LAYER, dresid=dx, out=spare)
-            K.norm_backward_wb(self.d_ln, a.x1, a.ln2_mean, a.ln2_rstd, g[pre + "ln_2.weight"],
-                               g[pre + "ln_2.bias"], sc, mode=K.NORM_LAYER)
+            K.norm_backward(self.d_ln, a.x1, p[pre + "ln_2.weight"], a.ln2_mean, a.ln2_rstd, g[pre + "ln_2.weight"], g[pre + "ln_2.bias"], sc,
+                            mode=K.NORM_LAYER, dresid=dx, out=spare)
             dx, spare = spare, dx  # dx now holds d(x1)
             # ---- attention branch: x1 = c_proj(att) + x ----
             gemm(dx, p[pre + "attn.c_proj.weight"], b_mn=True, out=self.d_att)
@@ -354,10 +350,8 @@ class GPT2Engine:
             gemm(self.d_qkv, p[pre + "attn.c_attn.weight"], b_mn=True, out=self.d_ln)
             gemm(self.d_qkv, a.ln1, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "attn.c_attn.weight"])
             K.colsum(self.d_qkv, g[pre + "attn.c_attn.bias"], sc)
-            K.norm_backward_dx(self.d_ln, x_in, p[pre + "ln_1.weight"], a.ln1_mean, a.ln1_rstd,
-                               mode=K.NORM_LAYER, dresid=dx, out=spare)
-            K.norm_backward_wb(self.d_ln, x_in, a.ln1_mean, a.ln1_rstd, g[pre + "ln_1.weight"],
-                               g[pre + "ln_1.bias"], sc, mode=K.NORM_LAYER)
+            K.norm_backward(self.d_ln, x_in, p[pre + "ln_1.weight"], a.ln1_mean, a.ln1_rstd, g[pre + "ln_1.weight"], g[pre + "ln_1.bias"], sc,
+                            mode=K.NORM_LAYER, dresid=dx, out=spare)
             dx, spare = spare, dx
         K.embedding_backward(dx, self.tokens, g["wte"], g["wpe"][:T], B=B, T=T)
         if T < cfg.max_seq_len:

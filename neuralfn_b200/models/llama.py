@@ -209,7 +209,7 @@ class LlamaEngine:
         self.d_qkv, self.d_att = e(N, Q), e(N, A)
         self.delta = e(batch, cfg.n_head, seq, dtype=f32)
         self.dq_accum = e(N, A, dtype=f32)
-        self.scratch = e(64 * 2 * max(2 * Fd, Q, C), dtype=f32)
+        self.scratch = e(max(64 * 2 * max(2 * Fd, Q, C), K.norm_fused_rows() * 2 * C), dtype=f32)
         self.ws = e(32 * 1024 * 1024, dtype=f32)
         self.tokens = torch.zeros(N, device=dev, dtype=torch.int32)
         self.targets = torch.zeros(N, device=dev, dtype=torch.int32)
@@ -267,8 +267,7 @@ class LlamaEngine:
             gemm(self.logits, p[head_name], b_mn=True, out=self.d_n)
             gemm(self.logits, self.nf, a_mn=True, b_mn=True, out=g[head_name])
             x_last = self.acts[-1]["x2"] if self.acts else self.x0
-            K.norm_backward_dx(self.d_n, x_last, p["norm"], None, self.rf, mode=K.NORM_RMS, out=dx)
-            K.norm_backward_wb(self.d_n, x_last, None, self.rf, g["norm"], None, sc, mode=K.NORM_RMS)
+            K.norm_backward(self.d_n, x_last, p["norm"], None, self.rf, g["norm"], None, sc, mode=K.NORM_RMS, out=dx)
         if cfg.pp_first and not cfg.tie_embeddings:
             g["tok_embeddings"].zero_()
         for i in range(len(self.layers) - 1, -1, -1):
@@ -281,8 +280,7 @@ class LlamaEngine:
             I.swiglu_backward(a["gu"], self.d_h, cfg.d_ff, out=self.d_gu)
             gemm(self.d_gu, p[pre + "w_gate_up"], b_mn=True, out=self.d_n)
             gemm(self.d_gu, a["n2"], a_mn=True, b_mn=True, workspace=ws, out=g[pre + "w_gate_up"])
-            K.norm_backward_dx(self.d_n, a["x1"], p[pre + "ffn_norm"], None, a["r2"], mode=K.NORM_RMS, dresid=dx, out=spare)
-            K.norm_backward_wb(self.d_n, a["x1"], None, a["r2"], g[pre + "ffn_norm"], None, sc, mode=K.NORM_RMS)
+            K.norm_backward(self.d_n, a["x1"], p[pre + "ffn_norm"], None, a["r2"], g[pre + "ffn_norm"], None, sc, mode=K.NORM_RMS, dresid=dx, out=spare)
             dx, spare = spare, dx
             # attention: x1 = wo(att) + x
             gemm(dx, p[pre + "wo"], b_mn=True, out=self.d_att)
@@ -300,8 +298,7 @@ class LlamaEngine:
                 K.qk_norm_backward(self.d_qkv, a["qkv"], a["qk_rstd"], Hq, Hkv, hd)
             gemm(self.d_qkv, p[pre + "wqkv"], b_mn=True, out=self.d_n)
             gemm(self.d_qkv, a["n1"], a_mn=True, b_mn=True, workspace=ws, out=g[pre + "wqkv"])
-            K.norm_backward_dx(self.d_n, x_in, p[pre + "attn_norm"], None, a["r1"], mode=K.NORM_RMS, dresid=dx, out=spare)
-            K.norm_backward_wb(self.d_n, x_in, None, a["r1"], g[pre + "attn_norm"], None, sc, mode=K.NORM_RMS)
+            K.norm_backward(self.d_n, x_in, p[pre + "attn_norm"], None, a["r1"], g[pre + "attn_norm"], None, sc, mode=K.NORM_RMS, dresid=dx, out=spare)
             dx, spare = spare, dx
         self.d_input = dx  # gradient w.r.t. this stage's input (sent to the previous stage)
         if cfg.pp_first:

@@ -74,6 +74,26 @@ def norm_backward_wb(dy, x, mean, rstd, dweight, dbias, scratch, *, mode: int, a
     _lib.check(rc, "nfn_norm_backward_wb")
 
 
+def norm_fused_rows() -> int:
+    return int(_lib.load().nfn_norm_fused_rows())
+
+
+def norm_backward(dy, x, weight, mean, rstd, dweight, dbias, scratch, *, mode: int, centered: bool = False, dresid=None, out=None,
+                  accumulate: bool = False):
+    """dx (returned), dweight and dbias (bf16 [C], either may be None) in one pass over dy and x.
+    scratch: fp32 with at least ``norm_fused_rows() * 2 * C`` entries."""
+    _need(dy, _bf16, "dy")
+    _need(x, _bf16, "x")
+    rows, C = x.shape
+    if scratch.numel() < norm_fused_rows() * 2 * C:
+        raise ValueError("norm_backward: scratch too small")
+    dx = torch.empty_like(x) if out is None else out
+    rc = _lib.load().nfn_norm_backward(_p(dy), _p(x), _p(weight), _p(mean), _p(rstd), _p(dresid), _p(dx), _p(dweight), _p(dbias),
+                                       _p(scratch), c_int(rows), c_int(C), c_int(mode), c_int(int(centered)), c_int(int(accumulate)), _st())
+    _lib.check(rc, "nfn_norm_backward")
+    return dx
+
+
 def colsum(dy, out, scratch, *, accumulate: bool = False):
     """out[c] = sum_r dy[r, c]; dy bf16 [rows, C] (row stride allowed), out bf16 [C]."""
     rows, C = dy.shape

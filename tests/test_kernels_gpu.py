@@ -47,6 +47,14 @@ def test_norm_fwd_bwd(kernel_lib, C, mode):
     assert _rel(dw, wf.grad) < 1e-2
     if db is not None:
         assert _rel(db, bf.grad) < 1e-2
+    # the fused single-pass variant gives the same three results
+    scratch2 = torch.empty(K.norm_fused_rows() * 2 * C, device="cuda", dtype=torch.float32)
+    dw2 = torch.empty(C, device="cuda", dtype=BF)
+    db2 = torch.empty(C, device="cuda", dtype=BF) if b is not None else None
+    dx2 = K.norm_backward(dy, x, w, mean, rstd, dw2, db2, scratch2, mode=kmode, centered=centered, dresid=dres)
+    assert _rel(dx2, xf.grad + dres.float()) < 1e-2 and _rel(dw2, wf.grad) < 1e-2
+    if db2 is not None:
+        assert _rel(db2, bf.grad) < 1e-2
     _lib.assert_status_ok()
 
 
