@@ -104,6 +104,13 @@ def _infer_artifact(a) -> int:
         return 0
     from ..serving import GenerationConfig, NativeInferenceModel, NativeModelLoadConfig, NGramProposer
     model = NativeInferenceModel.load(a.checkpoint, NativeModelLoadConfig(session_count=1, speculative_decoding=a.speculative_decoding))
+    if a.chat:
+        from ..serving.chat import resolve_chat_renderer
+        from .tui import InferTUI
+        rc = InferTUI(model, resolve_chat_renderer(model.manifest.get("chat_template")), max_new_tokens=a.max_new_tokens,
+                      proposer_factory=(NGramProposer if a.speculative_decoding != "off" else None)).run()
+        model.close()
+        return rc
     ids = model.codec.encode(a.prompt) if a.prompt is not None else [int(t) for t in a.prompt_tokens.split(",") if t]
     with model.create_session(a.seed) as s:
         s.prefill(ids)
@@ -223,6 +230,7 @@ def build_parser() -> argparse.ArgumentParser:
     i.add_argument("--prompt-tokens", default="", help="comma-separated ids; ';' separates prompts")
     i.add_argument("--prompt", default=None, help="text prompt (artifact directories with a text codec)")
     i.add_argument("--serve", action="store_true", help="serve the artifact over the OpenAI-compatible HTTP API")
+    i.add_argument("--chat", action="store_true", help="interactive chat loop (/show /reset /mode /tokens /quit)")
     i.add_argument("--host", default="127.0.0.1")
     i.add_argument("--port", type=int, default=8000)
     i.add_argument("--api-key-file", default=None)

@@ -135,3 +135,54 @@ def test_state_store_persists(tmp_path):
     assert s2.schema_version() == SCHEMA_VERSION and s2.get_response(r["id"])["output_text"] == "x"
     assert s2.list_items(conv["id"])[0]["content"] == "hi"
     assert s2.delete_conversation(conv["id"]) and s2.list_items(conv["id"]) == []
+
+
+def test_train_dashboard_and_infer_tui(tmp_path):
+    import io
+    import json as _json
+
+    from neuralfn_b200.cli.tui import InferTUI, TrainDashboard, sparkline
+    assert sparkline([1, 2, 3, 4]) == "▁▃▆█" and sparkline([]) == ""
+    log = io.StringIO()
+    d = TrainDashboard(total_steps=10, tee=log)
+    for i in range(1, 6):
+        d.feed(_json.dumps({"event": "train_step", "step": i, "loss": 5.0 - 0.5 * i, "tokens_per_second": 1000.0 * i}))
+    d.feed("plain text line")
+    d.feed(_json.dumps({"event": "validation", "loss": 3.3}))
+    d.feed(_json.dumps({"event": "checkpoint", "path": "/tmp/x/model_00000005.bin"}))
+    d.feed(_json.dumps({"status": "ok", "steps": 10, "train_compute_tokens_per_second": 1234.0}))
+    assert d.step == 5 and d.status == "complete" and d.val_losses == [3.3] and d.tokens_per_second == 1234.0
+    assert log.getvalue().count("\n") == 9
+    from rich.console import Console
+    buf = io.StringIO()
+    Console(file=buf, width=100).print(d.render())
+    assert "model_00000005.bin" in buf.getvalue() and "complete" in buf.getvalue()
+
+    class Sess(FakeSession):
+        cached_tokens = 0
+        token_ids = ()
+
+        def prefill(self, ids):
+            super().prefill(ids)
+            self.token_ids = tuple(self.ids)
+
+        def truncate(self, n):
+            self.ids = self.ids[:n]
+            self.token_ids = tuple(self.ids)
+
+        def reset(self):
+            self.ids, self.token_ids = [], ()
+
+    class Model(FakeModel):
+        manifest = {}
+
+        def create_session(self, seed=None):
+            return Sess(self)
+
+    out = io.StringIO()
+    tui = InferTUI(Model(), PlainRolesRenderer(), stdin=["hello there\n", "/mode sample\n", "/tokens 5\n", "again\n", "/show\n", "/reset\n", "/bogus\n", "/quit\n", "never\n"],
+                   stdout=out, max_new_tokens=32)
+    assert tui.run() == 0
+    text = out.getvalue()
+    assert "ok:hello there" in text and "(mode: sample)" in text and "ok:ag" in text and "turns 2" in text and "(conversation cleared)" in text
+    assert "never" not in text and "commands:" in text
