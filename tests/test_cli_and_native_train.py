@@ -72,3 +72,13 @@ def test_kernel_registry_matches_the_built_library_and_examples_run():
     root = Path(__file__).resolve().parents[1]
     out = subprocess.run([sys.executable, str(root / "examples" / "xor_graph.py"), "/tmp/nfn_xor_example.json"], capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and "final MSE" in out.stdout
+
+
+def test_gpu_picker_prefers_idle_devices(monkeypatch):
+    from neuralfn_b200.utils.cuda_device import GpuInfo, parse_nvidia_smi_csv, pick_dedicated_gpu
+    g = parse_nvidia_smi_csv("0, NVIDIA B200, 183359, 120000\n1, NVIDIA B200, 183359, 4\n2, NVIDIA B200, 183359, 4\nnot a row\n")
+    assert [x.index for x in g] == [0, 1, 2] and pick_dedicated_gpu(g) == 1
+    assert pick_dedicated_gpu([GpuInfo(0, "x", 100, 10, 1), GpuInfo(1, "x", 100, 50, 0)]) == 1
+    assert pick_dedicated_gpu(g, min_free_mib=10 ** 9) is None
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "0,2")
+    assert pick_dedicated_gpu(g) == 2
