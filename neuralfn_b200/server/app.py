@@ -3,10 +3,12 @@ datasets, semantic helpers, and token-level generation through the resident engi
 
     uvicorn neuralfn_b200.server.app:create_app --factory --host 127.0.0.1 --port 8000
 
-Authentication is a single bearer token taken from ``NEURALFN_API_TOKEN`` (unset = open, for
-local use); state lives in a ``LiveStateStore`` (``NEURALFN_SNAPSHOT_DIR`` enables JSON
-snapshots). The reference's platform (``server/app.py``, ``server/routers``) adds user
-accounts, projects and a SQL store on top of the same operations.
+Authentication: a bearer token from ``NEURALFN_API_TOKEN`` (unset = open, for local use), and,
+when ``NEURALFN_DATABASE_PATH`` names a SQLite file, accounts with cookie sessions, projects,
+revisioned graph snapshots and run records (``accounts.py`` / ``platform_db.py``;
+``NEURALFN_BOOTSTRAP_ADMIN_EMAIL`` / ``_PASSWORD`` create the first administrator). Live state is a
+``LiveStateStore`` (``NEURALFN_SNAPSHOT_DIR`` enables JSON snapshots). Reference counterpart:
+``server/app.py``, ``server/routers``, ``server/settings.py:38-63``.
 """
 from __future__ import annotations
 
@@ -43,17 +45,35 @@ class InferenceConcurrencyGate:
             self._waiting -= 1
 
 
-def create_app(store: LiveStateStore | None = None, engine=None):
-    from fastapi import Body, Depends, FastAPI, Header, HTTPException
+def create_app(store: LiveStateStore | None = None, engine=None, db=None):
+    from fastapi import Body, Cookie, Depends, FastAPI, Header, HTTPException
 
     store = store or LiveStateStore(os.environ.get("NEURALFN_SNAPSHOT_DIR") or None)
     token = os.environ.get("NEURALFN_API_TOKEN", "")
+    if db is None and os.environ.get("NEURALFN_DATABASE_PATH"):
+        from .platform_db import PlatformDB
+        db = PlatformDB(os.environ["NEURALFN_DATABASE_PATH"])
     gate = InferenceConcurrencyGate()
     app = FastAPI(title="neuralfn_b200", version="0.1")
-    app.state.store, app.state.engine = store, engine
+    app.state.store, app.state.engine, app.state.db = store, engine, db
+    if db is not None:
+        from .accounts import mount_account_routes
+        db.ensure_bootstrap_admin()
+        mount_account_routes(app, db, store, secure_cookies=os.environ.get("NEURALFN_SECURE_COOKIES", "") == "1")
 
-    def auth(authorization: str | None = Header(default=None)) -> None:
-        if token and authorization != f"Bearer {token}":
+    def auth(authorization: str | None = Header(default=None), nfn_session: str | None = Cookie(default=None)) -> None:
+        """With accounts configured a signed-in cookie is required (or the bearer token, for
+        automation); without them the bearer token alone guards the routes."""
+        if token and authorization == f"Bearer {token}":
+            return
+        if db is not None:
+            from .platform_db import AuthError
+            try:
+                db.authenticate(nfn_session)
+                return
+            except AuthError as exc:
+                raise HTTPException(status_code=401, detail=str(exc)) from None
+        if token:
             raise HTTPException(status_code=401, detail="missing or wrong bearer token")
 
     def guard(fn, *a, **k):
@@ -67,7 +87,7 @@ def create_app(store: LiveStateStore | None = None, engine=None):
     @app.get("/api/bootstrap")
     def bootstrap() -> dict:
         from ..ops import _lib
-        return {"status": "ok", "auth_required": bool(token), "kernel_library": _lib.available(), "sessions": len(store.sessions)}
+        return {"status": "ok", "auth_required": bool(token) or db is not None, "accounts": db is not None, "kernel_library": _lib.available(), "sessions": len(store.sessions)}
 
     @app.get("/api/sessions", dependencies=[Depends(auth)])
     def sessions() -> list[dict]:
