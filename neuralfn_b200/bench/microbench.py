@@ -61,7 +61,7 @@ def case_gemm(args, m=None, n=None, k=None, a_mn=False, b_mn=False, tag="gemm"):
     a = torch.randn((k, m) if a_mn else (m, k), device=dev).bfloat16()
     b = torch.randn((k, n) if b_mn else (n, k), device=dev).bfloat16()
     out = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
-    ws = torch.empty(32 * 1024 * 1024, device=dev, dtype=torch.float32) if a_mn else None
+    ws = torch.empty(32 * 1024 * 1024, device=dev, dtype=torch.float32) if (a_mn or m <= 256) else None  # split-K: weight gradients, skinny decode products
     ms = time_kernel(lambda: gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, workspace=ws), args.iters, args.warmup, args.flush)
     return _report(tag, ms, flops=2.0 * m * n * k, bytes_=2.0 * (m * k + n * k + m * n), args=args,
                    extra={"m": m, "n": n, "k": k, "a_mn": a_mn, "b_mn": b_mn})
@@ -219,10 +219,42 @@ def case_turboquant_attention(args):
                    extra={"B": B, "Hq": Hq, "Hkv": Hkv, "ctx": ctx, "D": D, "bytes_per_token": cache.bytes_per_token})
 
 
+
+def case_engine_decode(args):
+    """Resident-engine decode throughput on Llama-3-8B layer shapes (8 of the 32 layers, so that the
+    weights stay a few GB): tokens/s for the whole batch and the weight bytes streamed per second."""
+    import time
+
+    from neuralfn_b200.serving import EngineConfig, ResidentEngine
+    L, d, Hq, Hkv, hd, F, V = 8, 4096, 32, 8, 128, 14336, 32000
+    B, ctx = max(1, args.batch), args.seq
+    cfg = EngineConfig(family=1, n_layer=L, d_model=d, n_head=Hq, n_kv_head=Hkv, head_dim=hd, d_ff=F, vocab=V, padded_vocab=V,
+                       max_seq=ctx + 80, max_batch=B, qk_norm=0, rope_hf=1, rope_theta=500000.0, norm_eps=1e-5, tie_embeddings=0)
+    eng = ResidentEngine(cfg)
+    g = torch.Generator().manual_seed(0)
+    w = {n: (torch.ones(k) if n.endswith("norm") else torch.randn(k, generator=g) * 0.02).bfloat16() for n, k in eng.expected_tensors().items()}
+    eng.load_named_tensors(w)
+    weight_bytes = 2 * sum(k for n, k in eng.expected_tensors().items() if n != "tok_embeddings")
+    prompt = torch.randint(0, V, (ctx,), generator=g).tolist()
+    last = {b: eng.prefill(b, prompt) for b in range(B)}
+    for _ in range(8):
+        last = eng.decode(last)
+    torch.cuda.synchronize()
+    steps = 48
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        last = eng.decode(last)
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / steps
+    return _report("engine_decode_llama8b_shape_8_layers", dt * 1e3, bytes_=float(weight_bytes), args=args,
+                   extra={"batch": B, "context": ctx, "tokens_per_second": round(B / dt, 1), "ms_per_step": round(dt * 1e3, 3),
+                          "kernel_launches_per_step": eng.launches // (steps + 8 + B) if hasattr(eng, "launches") else None})
+
+
 CASES = {"gemm": case_gemm, "attention_fwd": case_attention, "attention_bwd": lambda a: case_attention(a, True),
          "cross_entropy": case_cross_entropy, "norm": case_norm, "adamw": case_adamw, "decode_attention": case_decode_attention,
          "kquant_gemv": case_kquant_gemv, "gemm_kquant": case_gemm_kquant, "block_attention": case_block_attention,
-         "turboquant_attention": case_turboquant_attention}
+         "turboquant_attention": case_turboquant_attention, "engine_decode": case_engine_decode}
 
 
 def run_all(args):

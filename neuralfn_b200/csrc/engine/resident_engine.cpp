@@ -87,6 +87,8 @@ struct nfn_engine {
   std::vector<int> cap;
   void* dec_ws = nullptr;
   long long dec_ws_bytes = 0;
+  void* gemm_ws = nullptr;      // fp32 partial slices of split-K products
+  long long gemm_ws_bytes = 0;
   void* rstd = nullptr;         // scratch of the weightless prefill QK norm
   void* branch = nullptr;       // output of a block branch before its sandwich norm
   void* ones = nullptr;         // unit norm weights (weightless embedding norm)
@@ -183,13 +185,19 @@ int gemm(nfn_engine& e, const void* a, int lda, const void* b, void* cdst, int l
   g.a = a; g.b = b; g.c = cdst;
   g.m = m; g.n = n; g.k = k;
   g.lda = lda; g.ldb = k; g.ldc = ldc;
-  g.flags = flags | (bias ? NFN_EPI_BIAS : 0) | (resid ? NFN_EPI_RESID : 0);
+  // "+= into the residual stream" is an accumulating product; unlike a residual epilogue it may be
+  // split along K, which is what lets a decode-sized product (a handful of rows) keep every SM
+  // streaming weights instead of one CTA per 128 output columns
+  const bool accumulate = m <= 128 && resid && resid == cdst && ld_resid == ldc && !bias && flags == 0;
+  g.flags = flags | (bias ? NFN_EPI_BIAS : 0) | (accumulate ? NFN_EPI_ACCUM : (resid ? NFN_EPI_RESID : 0));
   g.alpha = alpha;
   g.act_param = act_param;
   g.bias = bias;
-  g.aux_in = resid;
-  g.ld_aux_in = ld_resid;
-  g.split_k = 1;
+  g.aux_in = accumulate ? nullptr : resid;
+  g.ld_aux_in = accumulate ? 0 : ld_resid;
+  g.workspace = e.gemm_ws;
+  g.workspace_bytes = e.gemm_ws_bytes;
+  g.split_k = 0;  // automatic: only skinny, long-K products with a plain epilogue are split
   K(nfn_gemm_bf16(&g, e.stream));
   return 0;
 }
@@ -483,6 +491,8 @@ int nfn_engine_finalize(nfn_engine* e) {
   e->dec_ws_bytes = nfn_decode_attention_workspace_bytes(c.max_batch, c.n_head, c.n_kv_head, HD, 64);
   if (e->dec_ws_bytes <= 0) return efail("engine_finalize: bad decode attention geometry");
   if (e->alloc(&e->dec_ws, e->dec_ws_bytes)) return -1;
+  e->gemm_ws_bytes = 64LL << 20;
+  if (e->alloc(&e->gemm_ws, e->gemm_ws_bytes)) return -1;
   CU(cudaMemset(e->dec_ws, 0, (size_t)e->dec_ws_bytes));
   const long long B = c.max_batch;
   auto up = [](long long v) { return (v + 255) / 256 * 256; };

@@ -182,6 +182,9 @@ extern "C" int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream_) {
     int want = a.split_k > 1 ? a.split_k : 1;
     if (a.split_k == 0 && tiles * 2 <= sms && kb >= 32) {
       want = sms / tiles;
+      // a product with at most one row tile (decode: M = batch) only streams the weights: it is
+      // bound by HBM, so use about two CTAs per SM rather than one wave
+      if (a.m <= BM) want = ceil_div(2 * sms, tiles);
       if (want > 16) want = 16;
       if (want > kb / 8) want = kb / 8;
     }

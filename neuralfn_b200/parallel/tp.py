@@ -133,9 +133,12 @@ class TensorParallelContext:
         _lib.check(_lib.load().nfn_gemm_tp(ctypes.byref(args), c_void_p(_lib.stream_ptr())), "nfn_gemm_tp")
 
     # ------------------------------------------------------------------ all-gather -> GEMM --
-    def column_linear(self, x_local: torch.Tensor, weight: torch.Tensor, bias=None, act=None, *, buffer=None, n_copy: int = 0):
+    def column_linear(self, x_local: torch.Tensor, weight: torch.Tensor, bias=None, act=None, *, buffer=None, n_copy: int = 0,
+                      return_gathered: bool = False):
         """x_local [rows, K] (this rank's sequence shard), weight [N_local, K] -> [world * rows, N_local].
-        Pass ``buffer`` (from ``gather_buffer``) when x_local already lives in its slot."""
+        Pass ``buffer`` (from ``gather_buffer``) when x_local already lives in its slot. With
+        ``return_gathered`` the result is (y, gathered x [world * rows, K]); on the fused path that
+        is a view of the symmetric buffer, valid until the second next call with the same shape."""
         rows, K = x_local.shape
         N = weight.shape[0]
         M = rows * self.world
@@ -145,9 +148,11 @@ class TensorParallelContext:
                 dist.all_gather(xs, x_local.contiguous(), group=self.group)
             else:
                 xs = [x_local]
-            y = torch.cat(xs).float() @ weight.float().T
+            xg = torch.cat(xs)
+            y = xg.float() @ weight.float().T
             y = y + bias.float() if bias is not None else y
-            return _act_torch(y, act).to(x_local.dtype)
+            y = _act_torch(y, act).to(x_local.dtype)
+            return (y, xg) if return_gathered else y
         from ..ops.gemm import gemm
         if self.impl == "nccl":
             xg = torch.empty(M, K, dtype=x_local.dtype, device=x_local.device)
@@ -155,14 +160,15 @@ class TensorParallelContext:
                 dist.all_gather_into_tensor(xg, x_local.contiguous(), group=self.group)
             else:
                 xg.copy_(x_local)
-            return gemm(xg, weight, bias=bias, act=act)
+            y = gemm(xg, weight, bias=bias, act=act)
+            return (y, xg) if return_gathered else y
         if buffer is None:
             view, buffer = self.gather_buffer(rows, K)
             view.copy_(x_local)
         xg = buffer.t.view(M, K)
         out = torch.empty(M, N, dtype=torch.bfloat16, device=self.device)
         self._launch(AG_A, xg, weight, out, M, N, K, rows, buffer.ptrs, bias=bias, act=act, n_copy=n_copy)
-        return out
+        return (out, xg) if return_gathered else out
 
     # ------------------------------------------------ weight all-gather -> GEMM (sharded params) --
     def gathered_weight_linear(self, x: torch.Tensor, weight_local: torch.Tensor, bias=None, act=None, n_copy: int = 0):
