@@ -180,11 +180,23 @@ extern "C" int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream_) {
     const int tiles = wide ? tiles256 : ceil_div(a.m, BM) * ceil_div(a.n, 128);
     const int kb = ceil_div(a.k, BK);
     int want = a.split_k > 1 ? a.split_k : 1;
-    if (a.split_k == 0 && tiles * 2 <= sms && kb >= 32) {
+    if (a.split_k == 0 && a.m <= BM && kb >= 16) {
+      // one row tile (decode / verification: M = batch): the product only streams the weights and
+      // is bound by HBM, so what matters is that every SM streams the same share. Pick the
+      // k-blocks per slice that minimise waves x (slice length + per-tile overhead), with the
+      // fp32 partial slices kept below about a tenth of the weight bytes.
+      const int overhead_kb = 2;
+      const long long max_split = std::max(1LL, (long long)a.k / (20LL * a.m));
+      long long best_cost = -1;
+      for (int per = kb; per >= 2; --per) {
+        const int s = ceil_div(kb, per);
+        if (s > max_split || s > 64) break;
+        const long long waves = ((long long)tiles * s + sms - 1) / sms;
+        const long long cost = waves * (per + overhead_kb);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; want = s; }
+      }
+    } else if (a.split_k == 0 && tiles * 2 <= sms && kb >= 32) {
       want = sms / tiles;
-      // a product with at most one row tile (decode: M = batch) only streams the weights: it is
-      // bound by HBM, so use about two CTAs per SM rather than one wave
-      if (a.m <= BM) want = ceil_div(2 * sms, tiles);
       if (want > 16) want = 16;
       if (want > kb / 8) want = kb / 8;
     }

@@ -122,22 +122,11 @@ __global__ void __launch_bounds__(NORM_THREADS)
 norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
                    const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dresid,
-                   __nv_bfloat16* __restrict__ dx, int rows, int C, int mode, int centered,
-                   float* __restrict__ wb_accum = nullptr) {
-  // wb_accum (TPR == 32 only): fp32 [2][C], zeroed by the caller; receives sum_rows dy * n and
-  // sum_rows dy. The block's eight rows are folded in shared memory first, so global memory sees
-  // one reduction per column and block instead of one per row.
+                   __nv_bfloat16* __restrict__ dx, int rows, int C, int mode, int centered) {
   __shared__ float red[8];
-  __shared__ float s_wb[TPR == 32 ? 2 * VEC * 256 : 1];
   const int lane = threadIdx.x % TPR;
   const int row = blockIdx.x * (NORM_THREADS / TPR) + threadIdx.x / TPR;
-  if (TPR == 32 && wb_accum) {
-    for (int c = threadIdx.x; c < 2 * VEC * 256; c += NORM_THREADS) s_wb[c] = 0.f;
-    __syncthreads();
-  }
-  const bool live = !(TPR == 32 && row >= rows);
-  if (TPR == 32 && !live && !wb_accum) return;
-  if (live) {
+  if (TPR == 32 && row >= rows) return;
   const float mean = (mode == 0) ? mean_in[row] : 0.f;
   const float rstd = rstd_in[row];
   const size_t off = (size_t)row * C;
@@ -154,10 +143,6 @@ norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         n[i][j] = (xv[j] - mean) * rstd;
-        if (TPR == 32 && wb_accum) {
-          atomicAdd(&s_wb[c + j], g[i][j] * n[i][j]);
-          atomicAdd(&s_wb[VEC * 256 + c + j], g[i][j]);
-        }
         const float gw = w ? (centered ? 1.f + wv[j] : wv[j]) : 1.f;
         g[i][j] *= gw;
         sg += g[i][j];
@@ -178,14 +163,6 @@ norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         o[j] = rstd * (g[i][j] - sg - n[i][j] * sgn) + (dresid ? r[j] : 0.f);
       }
       store8(dx + off + c, o);
-    }
-  }
-  }  // live
-  if (TPR == 32 && wb_accum) {
-    __syncthreads();
-    for (int c = threadIdx.x; c < C; c += NORM_THREADS) {
-      atomicAdd(wb_accum + c, s_wb[c]);
-      atomicAdd(wb_accum + C + c, s_wb[VEC * 256 + c]);
     }
   }
 }
@@ -239,69 +216,38 @@ __global__ void norm_bwd_wb_final_kernel(const float* __restrict__ partial,
   if (db) db[col] = __float2bfloat16(b + (accumulate ? __bfloat162float(db[col]) : 0.f));
 }
 
-// Column sum of a bf16 matrix [rows, C] -> bf16 [C] (bias gradients), one launch. A block owns 64
-// columns (8 threads x 8 columns, 16-byte loads) and every RY-th group of 32 rows; it writes one
-// partial row, takes a ticket, and the last block of its column group to finish adds the partial
-// rows up and writes the result. The tickets live in a static device array and reset themselves,
-// so calls on one device must not overlap (they are issued on one stream).
-constexpr int CS_COLS = 64, CS_MAX_GROUPS = 4096;
-constexpr int CS_CG = CS_COLS / 8;   // threads across the columns (8 columns each)
-constexpr int CS_RL = 256 / CS_CG;   // row lanes per block
-__device__ unsigned int g_colsum_tickets[CS_MAX_GROUPS];
-
+// Column sum of a bf16 matrix [rows, C] -> bf16 [C] (bias gradients). Same two stages.
 __global__ void __launch_bounds__(256)
-colsum_kernel(const __nv_bfloat16* __restrict__ dy, int ld, float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
-              int rows, int C, int accumulate) {
-  __shared__ float sacc[CS_RL][CS_COLS];
-  __shared__ int s_last;
-  const int cg = threadIdx.x % CS_CG, rlane = threadIdx.x / CS_CG;
-  const int col = blockIdx.x * CS_COLS + cg * 8;
+colsum_partial_kernel(const __nv_bfloat16* __restrict__ dy, int ld, float* __restrict__ partial,
+                      int rows, int C) {
+  // each thread owns 2 adjacent columns; 4 row-lanes x 64 column-pairs = 128 columns per block
+  const int cp = threadIdx.x & 63, rlane = threadIdx.x >> 6;
+  const int col = (blockIdx.x * 64 + cp) * 2;
   const int RY = gridDim.y;
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float a = 0.f, b = 0.f;
   if (col < C) {
-    const int step = RY * CS_RL;
-    int r = blockIdx.y * CS_RL + rlane;
-    for (; r + 3 * step < rows; r += 4 * step) {  // four independent loads in flight
-      float f0[8], f1[8], f2[8], f3[8];
-      load8(dy + (size_t)r * ld + col, f0);
-      load8(dy + (size_t)(r + step) * ld + col, f1);
-      load8(dy + (size_t)(r + 2 * step) * ld + col, f2);
-      load8(dy + (size_t)(r + 3 * step) * ld + col, f3);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] += (f0[k] + f1[k]) + (f2[k] + f3[k]);
-    }
-    for (; r < rows; r += step) {
-      float f0[8];
-      load8(dy + (size_t)r * ld + col, f0);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] += f0[k];
+    for (int r = blockIdx.y * 4 + rlane; r < rows; r += RY * 4) {
+      const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(dy + (size_t)r * ld + col));
+      a += f.x; b += f.y;
     }
   }
-#pragma unroll
-  for (int k = 0; k < 8; ++k) sacc[rlane][cg * 8 + k] = acc[k];
+  __shared__ float sa[4][64], sb[4][64];
+  sa[rlane][cp] = a; sb[rlane][cp] = b;
   __syncthreads();
-  const int c = blockIdx.x * CS_COLS + threadIdx.x;
-  const bool owner = threadIdx.x < CS_COLS && c < C;
-  if (owner) {
-    float t = 0.f;
-#pragma unroll
-    for (int r = 0; r < CS_RL; ++r) t += sacc[r][threadIdx.x];
-    partial[(size_t)blockIdx.y * C + c] = t;
+  if (rlane == 0 && col < C) {
+    a = sa[0][cp] + sa[1][cp] + sa[2][cp] + sa[3][cp];
+    b = sb[0][cp] + sb[1][cp] + sb[2][cp] + sb[3][cp];
+    partial[(size_t)blockIdx.y * C + col] = a;
+    partial[(size_t)blockIdx.y * C + col + 1] = b;
   }
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned int t = atomicAdd(&g_colsum_tickets[blockIdx.x], 1u);
-    s_last = (t == (unsigned)RY - 1);
-    if (s_last) g_colsum_tickets[blockIdx.x] = 0;
-  }
-  __syncthreads();
-  if (s_last && owner) {
-    __threadfence();
-    float a = 0.f;
-    for (int r = 0; r < RY; ++r) a += __ldcg(partial + (size_t)r * C + c);
-    out[c] = __float2bfloat16(a + (accumulate ? __bfloat162float(out[c]) : 0.f));
-  }
+}
+__global__ void colsum_final_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                                    int RY, int C, int accumulate) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= C) return;
+  float a = 0.f;
+  for (int r = 0; r < RY; ++r) a += partial[(size_t)r * C + col];
+  out[col] = __float2bfloat16(a + (accumulate ? __bfloat162float(out[col]) : 0.f));
 }
 
 template <typename F>
@@ -354,6 +300,89 @@ extern "C" int nfn_norm_backward_dx(const void* dy, const void* x, const void* w
   });
 }
 
+// dx, dweight and dbias in ONE pass over dy and x. Each block strides over the rows (one warp
+// per row at a time), keeps its column partials of dweight / dbias in registers, folds its eight
+// warps through shared memory at the end and writes one partial row; the small final kernel sums
+// the partial rows. Compared with separate dx and dweight/dbias kernels this reads dy and x once
+// instead of twice and keeps every load a 16-byte vector.
+template <int VEC>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                      const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
+                      const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dresid,
+                      __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int C, int mode, int centered) {
+  constexpr int RPB = NORM_THREADS / 32;
+  __shared__ float sacc[RPB][VEC * 256];
+  const int lane = threadIdx.x & 31, wrow = threadIdx.x >> 5;
+  float aw[VEC][8], ab[VEC][8], wv[VEC][8];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int c = (i * 32 + lane) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { aw[i][j] = 0.f; ab[i][j] = 0.f; wv[i][j] = 1.f; }
+    if (w && c < C) {
+      load8(w + c, wv[i]);
+      if (centered) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) wv[i][j] += 1.f;
+      }
+    }
+  }
+  for (int row = blockIdx.x * RPB + wrow; row < rows; row += gridDim.x * RPB) {
+    const float mean = (mode == 0) ? mean_in[row] : 0.f;
+    const float rstd = rstd_in[row];
+    const size_t off = (size_t)row * C;
+    float g[VEC][8], n[VEC][8];
+    float sg = 0.f, sgn = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < C) {
+        float xv[8];
+        load8(dy + off + c, g[i]);
+        load8(x + off + c, xv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          n[i][j] = (xv[j] - mean) * rstd;
+          aw[i][j] += g[i][j] * n[i][j];
+          ab[i][j] += g[i][j];
+          g[i][j] *= wv[i][j];
+          sg += g[i][j];
+          sgn += g[i][j] * n[i][j];
+        }
+      }
+    }
+    sg = (mode == 0) ? warp_sum(sg) / C : 0.f;
+    sgn = warp_sum(sgn) / C;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < C) {
+        float o[8], r[8];
+        if (dresid) load8(dresid + off + c, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - sg - n[i][j] * sgn) + (dresid ? r[j] : 0.f);
+        store8(dx + off + c, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < VEC; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sacc[wrow][(i * 32 + lane) * 8 + j] = pass == 0 ? aw[i][j] : ab[i][j];
+    __syncthreads();
+    for (int c = threadIdx.x; c < C; c += NORM_THREADS) {
+      float t = 0.f;
+#pragma unroll
+      for (int r = 0; r < RPB; ++r) t += sacc[r][c];
+      partial[((size_t)blockIdx.x * 2 + pass) * C + c] = t;
+    }
+  }
+}
+
 // scratch: fp32 [ry * 2 * C]; ry = nfn_norm_wb_rows()
 extern "C" int nfn_norm_wb_rows(void) { return 64; }
 
@@ -372,8 +401,8 @@ extern "C" int nfn_norm_backward_wb(const void* dy, const void* x, const float* 
   return launch_check("norm_bwd_wb", 2);
 }
 
-// Rows of scratch the fused backward uses: scratch must hold nfn_norm_fused_rows() * 2 * C floats.
-extern "C" int nfn_norm_fused_rows(void) { return 1; }
+// Partial rows the fused backward may write: scratch must hold nfn_norm_fused_rows() * 2 * C floats.
+extern "C" int nfn_norm_fused_rows(void) { return 2 * 160; }
 
 extern "C" int nfn_norm_backward(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, const void* dresid,
                                  void* dx, void* dw, void* db, float* scratch, int rows, int C, int mode, int centered, int accumulate,
@@ -386,19 +415,16 @@ extern "C" int nfn_norm_backward(const void* dy, const void* x, const void* w, c
     if (rc) return rc;
     return nfn_norm_backward_wb(dy, x, mean, rstd, dw, db, scratch, rows, C, mode, accumulate, stream);
   }
-  // one row per warp at full occupancy (the dx kernel), with dweight / dbias folded per block in
-  // shared memory and reduced into scratch[2][C] (zeroed here) with one atomic per column and block
-  if (cudaMemsetAsync(scratch, 0, (size_t)2 * C * sizeof(float), st) != cudaSuccess) return launch_check("norm_backward memset", 0);
-  const int grid = ceil_div(rows, NORM_THREADS / 32);
+  const int grid = std::min(ceil_div(rows, NORM_THREADS / 32), std::min(2 * sm_count(), nfn_norm_fused_rows()));
 #define NFN_FUSED(V)                                                                                                   \
-  norm_bwd_dx_kernel<V, 32><<<grid, NORM_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,          \
-      (const __nv_bfloat16*)w, mean, rstd, (const __nv_bfloat16*)dresid, (__nv_bfloat16*)dx, rows, C, mode, centered, scratch)
+  norm_bwd_fused_kernel<V><<<grid, NORM_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,           \
+      (const __nv_bfloat16*)w, mean, rstd, (const __nv_bfloat16*)dresid, (__nv_bfloat16*)dx, scratch, rows, C, mode, centered)
   if (C <= 256) NFN_FUSED(1);
   else if (C <= 512) NFN_FUSED(2);
   else if (C <= 768) NFN_FUSED(3);
   else NFN_FUSED(4);
 #undef NFN_FUSED
-  norm_bwd_wb_final_kernel<<<ceil_div(C, 256), 256, 0, st>>>(scratch, (__nv_bfloat16*)dw, (__nv_bfloat16*)db, 1, C, accumulate);
+  norm_bwd_wb_final_kernel<<<ceil_div(C, 256), 256, 0, st>>>(scratch, (__nv_bfloat16*)dw, (__nv_bfloat16*)db, grid, C, accumulate);
   return launch_check("norm_backward", 2);
 }
 
@@ -408,11 +434,11 @@ extern "C" int nfn_colsum(const void* dy, int ld, void* out, float* scratch, int
   if (rows <= 0) return 0;
   if (C % 2 || ld % 2) return fail(-1, "colsum: C and ld must be even");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (C % 8 || ld % 8 || (reinterpret_cast<uintptr_t>(dy) & 15)) return fail(-1, "colsum: C and ld must be multiples of 8 and dy 16-byte aligned");
-  const int groups = ceil_div(C, CS_COLS);
-  if (groups > CS_MAX_GROUPS) return fail(-1, "colsum: matrix too wide");
-  const int RY = std::max(1, std::min(64, 2 * sm_count() / groups));  // scratch holds 64 partial rows
-  colsum_kernel<<<dim3(groups, RY), 256, 0, st>>>((const __nv_bfloat16*)dy, ld, scratch, (__nv_bfloat16*)out, rows, C, accumulate);
-  return launch_check("colsum", 1);
+  const int RY = 64;
+  dim3 grid(ceil_div(C, 128), RY);
+  colsum_partial_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)dy, ld, scratch, rows, C);
+  colsum_final_kernel<<<ceil_div(C, 256), 256, 0, st>>>(scratch, (__nv_bfloat16*)out, RY, C,
+                                                        accumulate);
+  return launch_check("colsum", 2);
 }
 
