@@ -54,7 +54,10 @@ class LiveStateStore:
     def _snapshot(self, sid: str) -> None:
         if self.snapshot_dir:
             self.snapshot_dir.mkdir(parents=True, exist_ok=True)
-            (self.snapshot_dir / f"session_{sid}.json").write_text(graph_to_json(self.sessions[sid]))
+            final = self.snapshot_dir / f"session_{sid}.json"
+            tmp = final.with_suffix(f".tmp{threading.get_ident()}")
+            tmp.write_text(graph_to_json(self.sessions[sid]))
+            tmp.replace(final)  # readers never see a half-written snapshot
 
     def create_session(self, name: str = "untitled", graph_json: str | dict | None = None) -> str:
         with self._lock:
@@ -167,9 +170,9 @@ class LiveStateStore:
                 else:
                     raise ValueError(f"unknown training method {method!r}")
                 run.result = {"final_loss": hist[-1] if hist else None, "steps": len(hist)}
-                run.status = "stopped" if run._stop.is_set() else "finished"
                 with self._lock:
                     self._snapshot(sid)
+                run.status = "stopped" if run._stop.is_set() else "finished"
             except Exception as exc:  # surfaced through train_status
                 run.error, run.status = f"{type(exc).__name__}: {exc}", "failed"
 
