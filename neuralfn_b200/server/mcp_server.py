@@ -52,6 +52,39 @@ class McpToolServer:
             "remove_edge": (_tool("Remove an edge.", session_id=dict(_S), edge_id=dict(_S)),
                             lambda session_id, edge_id: s.remove_edge(session_id, edge_id)),
             "list_variants": (_tool("Variant library of a session's graph.", session_id=dict(_S)), lambda session_id: s.list_variants(session_id)),
+            "get_node": (_tool("One node with its edges and roles.", session_id=dict(_S), node_id=dict(_S)), lambda session_id, node_id: s.get_node(session_id, node_id)),
+            "update_node": (_tool("Rename / move a node, replace a function neuron's source, merge a module config.", session_id=dict(_S), node_id=dict(_S),
+                                  name=_opt(dict(_S)), position=_opt(dict(_A)), source_code=_opt(dict(_S)), module_config=_opt(dict(_O))),
+                            lambda session_id, node_id, **kw: s.update_node(session_id, node_id, **kw)),
+            "update_node_positions": (_tool("Move several nodes.", session_id=dict(_S), positions=dict(_O)),
+                                      lambda session_id, positions: {"moved": s.update_node_positions(session_id, positions)}),
+            "add_custom_node": (_tool("Add a function neuron from Python source.", session_id=dict(_S), source_code=dict(_S), fn_name=dict(_S),
+                                      inputs=dict(_A), outputs=dict(_A)),
+                                lambda session_id, source_code, fn_name, inputs, outputs:
+                                {"node_id": s.add_custom_node(session_id, source_code, fn_name, inputs, outputs)}),
+            "add_subgraph_node": (_tool("Add a node that wraps a nested graph.", session_id=dict(_S), name=dict(_S), subgraph=dict(_O)),
+                                  lambda session_id, name, subgraph: {"node_id": s.add_subgraph_node(session_id, name, subgraph)}),
+            "add_variant_node": (_tool("Add a subgraph node bound to a library variant.", session_id=dict(_S), family=dict(_S), version=dict(_S)),
+                                 lambda session_id, family, version: {"node_id": s.add_variant_node(session_id, family, version)}),
+            "save_node_as_variant": (_tool("Store a subgraph node in the variant library.", session_id=dict(_S), node_id=dict(_S), family=dict(_S),
+                                           version=dict(_S), link_node=_opt(dict(_B))),
+                                     lambda session_id, node_id, family, version, link_node=True:
+                                     s.save_node_as_variant(session_id, node_id, family, version, link_node)),
+            "swap_node_variant": (_tool("Point a subgraph node at another library variant.", session_id=dict(_S), node_id=dict(_S), family=dict(_S),
+                                        version=dict(_S)),
+                                  lambda session_id, node_id, family, version: s.swap_node_variant(session_id, node_id, family, version)),
+            "update_edge": (_tool("Set an edge's weight and / or bias.", session_id=dict(_S), edge_id=dict(_S), weight=_opt(dict(_N)), bias=_opt(dict(_N))),
+                            lambda session_id, edge_id, weight=None, bias=None: s.update_edge(session_id, edge_id, weight, bias)),
+            "set_io": (_tool("Declare the graph's input and output nodes.", session_id=dict(_S), input_ids=dict(_A), output_ids=dict(_A)),
+                       lambda session_id, input_ids, output_ids: s.set_io(session_id, input_ids, output_ids)),
+            "update_graph_settings": (_tool("Name, training method, runtime and trainer configs of a graph.", session_id=dict(_S), name=_opt(dict(_S)),
+                                            training_method=_opt(dict(_S)), runtime=_opt(dict(_S)), surrogate_config=_opt(dict(_O)),
+                                            evo_config=_opt(dict(_O)), torch_config=_opt(dict(_O))),
+                                      lambda session_id, **kw: s.update_graph_settings(session_id, **kw)),
+            "load_gpt_template": (_tool("Replace the graph by a model preset's tensor graph.", session_id=dict(_S), preset=_opt(dict(_S)), config=_opt(dict(_O))),
+                                  lambda session_id, preset="nanogpt", config=None: s.load_gpt_template(session_id, preset, config)),
+            "probe_node": (_tool("Sample a scalar neuron over its input ranges.", session_id=dict(_S), node_id=dict(_S), n_samples=_opt(dict(_I))),
+                           lambda session_id, node_id, n_samples=1000: s.probe_node(session_id, node_id, n_samples)),
             "execute": (_tool("Run the scalar graph on flat inputs.", session_id=dict(_S), inputs=dict(_A)),
                         lambda session_id, inputs: {"outputs": s.execute(session_id, inputs)}),
             "trace": (_tool("Run the graph and return every node's values.", session_id=dict(_S), inputs=dict(_O)),

@@ -83,3 +83,48 @@ def test_rest_routes_share_the_store(monkeypatch):
     with InferenceConcurrencyGate(max_waiting=1) as g:
         with pytest.raises(RuntimeError):
             g.__class__.__enter__(g)
+
+
+def test_mcp_edit_tools_nodes_edges_variants_settings():
+    from neuralfn_b200.server.mcp_server import McpToolServer
+    srv = McpToolServer()
+    call = srv.call
+    assert len(srv.list_tools()) >= 37
+    sid = call("create_session", {"name": "edit"})["session_id"]
+    a = call("add_node", {"session_id": sid, "builtin": "input", "role": "input"})["node_id"]
+    src = "def double_plus(x):\n    return (2.0 * x + 1.0,)\n"
+    c = call("add_custom_node", {"session_id": sid, "source_code": src, "fn_name": "double_plus", "inputs": [{"name": "x", "range": [-2.0, 2.0]}],
+                                 "outputs": [{"name": "y"}]})["node_id"]
+    e = call("add_edge", {"session_id": sid, "src_node": a, "dst_node": c})["edge_id"]
+    call("set_io", {"session_id": sid, "input_ids": [a], "output_ids": [c]})
+    assert call("execute", {"session_id": sid, "inputs": [1.5]})["outputs"] == [4.0]
+    assert call("update_edge", {"session_id": sid, "edge_id": e, "weight": 2.0, "bias": -1.0})["weight"] == 2.0
+    assert call("execute", {"session_id": sid, "inputs": [1.5]})["outputs"] == [5.0]  # 2 * (2 * 1.5 - 1) + 1
+    node = call("update_node", {"session_id": sid, "node_id": c, "name": "triple", "position": [3, 4],
+                                "source_code": "def triple(x):\n    return (3.0 * x,)\n"})
+    assert node["position"] == [3.0, 4.0] or tuple(node["position"]) == (3.0, 4.0)
+    assert call("execute", {"session_id": sid, "inputs": [1.5]})["outputs"] == [6.0]
+    assert call("get_node", {"session_id": sid, "node_id": c})["incoming"] == [e]
+    assert call("update_node_positions", {"session_id": sid, "positions": {a: [1, 1], c: [2, 2]}})["moved"] == 2
+    probe = call("probe_node", {"session_id": sid, "node_id": c, "n_samples": 200})
+    assert probe["samples"] == 200 and -6.0 <= probe["outputs"][0]["min"] < probe["outputs"][0]["max"] <= 6.0
+    with pytest.raises(ValueError):
+        call("update_node", {"session_id": sid, "node_id": c, "source_code": "x = 1\n"})  # no callable in the source
+    st = call("update_graph_settings", {"session_id": sid, "training_method": "sgd", "evo_config": {"population": 8}})
+    assert st["training_method"] == "sgd" and st["evo_config"]["population"] == 8
+    with pytest.raises(ValueError):
+        call("update_graph_settings", {"session_id": sid, "training_method": "magic"})
+
+    # subgraph nodes and the variant library
+    inner = call("get_graph", {"session_id": sid})
+    outer = call("create_session", {"name": "outer"})["session_id"]
+    n = call("add_subgraph_node", {"session_id": outer, "name": "inner", "subgraph": inner})["node_id"]
+    lib = call("save_node_as_variant", {"session_id": outer, "node_id": n, "family": "blocks", "version": "v1"})
+    assert lib == {"blocks": ["v1"]}
+    m = call("add_variant_node", {"session_id": outer, "family": "blocks", "version": "v1"})["node_id"]
+    assert call("get_node", {"session_id": outer, "node_id": m})["neuron_def"]["variant_ref"] == {"family": "blocks", "version": "v1"}
+    assert call("swap_node_variant", {"session_id": outer, "node_id": n, "family": "blocks", "version": "v1"})["id" if False else "instance_id"] == n
+    with pytest.raises(KeyError):
+        call("swap_node_variant", {"session_id": outer, "node_id": n, "family": "blocks", "version": "v9"})
+    tpl = call("load_gpt_template", {"session_id": outer, "preset": "nanogpt", "config": {"vocab_size": 64, "num_layers": 1, "model_dim": 32, "num_heads": 2}})
+    assert tpl["runtime"] == "torch" and tpl["nodes"] > 3
