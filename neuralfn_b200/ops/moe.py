@@ -19,7 +19,7 @@ from . import _lib
 from .gemm import gemm
 from .infer import swiglu_forward
 
-__all__ = ["MoEWorkspace", "moe_forward", "moe_reference"]
+__all__ = ["MoEWorkspace", "moe_forward", "moe_reference", "moe_experts", "moe_experts_native_ok"]
 
 GROUPED = 3
 
@@ -128,3 +128,89 @@ def moe_reference(x, w_router, w_gate_up, w_down, top_k: int, *, score_fn: str =
         y = a @ w_down[e].float().T
         out[rows] += y * (w[rows] * sel[rows]).sum(-1, keepdim=True)
     return out + (resid.float() if resid is not None else 0)
+
+
+# --------------------------------------------------------------------------- training path --
+class _MoEExpertsFn(torch.autograd.Function):
+    """Dropless expert FFN with gradients. Inputs in the tensor-runtime layout: x [T, d] bf16,
+    w1 / w3 [E, d, h] (gate / up), w2 [E, h, d], routing weights [T, k] (any float dtype) and
+    indices [T, k] (int64). Forward: expert-sorted permutation -> grouped tcgen05 GEMM (gate|up)
+    -> SwiGLU -> grouped GEMM (down) -> weighted combine. Backward: the same plan drives the
+    grouped input-gradient GEMMs (the stored [E, K, N] weights are already the operand layout
+    those need); weight gradients are one TN GEMM per expert over its row segment; routing
+    weights get <expert output, upstream gradient>.
+
+    Reference counterparts: ``moe_swiglu_forward/backward`` (``kernels.cu:12612-12862``), which
+    loop per token over its k experts with dense weights and no permutation."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w2, w3, weights, indices):
+        T, d = x.shape
+        E, _, h = w1.shape
+        k = indices.shape[-1]
+        L = _lib.load()
+        ws = MoEWorkspace(T, E, k, d, h, x.device)
+        ws.topk_idx.copy_(indices)
+        ws.topk_w.copy_(weights)
+        ws.counts.copy_(torch.bincount(indices.reshape(-1), minlength=E))
+        w_gu = torch.cat([w1.transpose(1, 2), w3.transpose(1, 2)], 1).contiguous()  # [E, 2h, d]
+        w_dn = w2.transpose(1, 2).contiguous()                                     # [E, d, h]
+        _lib.check(L.nfn_moe_plan(_p(ws.counts), c_int(E), c_int(ws.max_tiles), _p(ws.offsets), _p(ws.cursor), _p(ws.tile_expert), _p(ws.plan), _st()),
+                   "nfn_moe_plan")
+        _lib.check(L.nfn_moe_permute(_p(x), c_int(x.stride(0)), c_int(T), c_int(k), c_int(d), _p(ws.topk_idx), _p(ws.offsets), _p(ws.cursor),
+                                     c_int(ws.capacity_rows), _p(ws.xs), _p(ws.row_of), _st()), "nfn_moe_permute")
+        _grouped_gemm(ws.xs, w_gu, ws.h, ws)
+        swiglu_forward(ws.h, h, out=ws.a)
+        _grouped_gemm(ws.a, w_dn, ws.ys, ws)
+        out = torch.empty(T, d, dtype=torch.bfloat16, device=x.device)
+        _lib.check(L.nfn_moe_combine(_p(ws.ys), c_int(d), c_int(T), c_int(k), _p(ws.row_of), _p(ws.topk_w), _p(None), c_int(0), _p(out),
+                                     c_int(out.stride(0)), _st()), "nfn_moe_combine")
+        ctx.ws, ctx.dims = ws, (T, d, E, h, k)
+        ctx.save_for_backward(w1, w2, w3)
+        ctx.w_dtype = weights.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from .infer import swiglu_backward
+        w1, w2, w3 = ctx.saved_tensors
+        ws, (T, d, E, h, k) = ctx.ws, ctx.dims
+        dout = dout.contiguous()
+        rows = ws.row_of.long()                                         # [T * k] sorted row of every (token, slot)
+        # routing-weight gradient and the upstream gradient of every sorted row
+        ys_tk = ws.ys[rows].view(T, k, d)
+        d_w = torch.einsum("tkd,td->tk", ys_tk.float(), dout.float())
+        dys = torch.zeros_like(ws.ys)
+        dys[rows] = (dout[:, None, :].float() * ws.topk_w[:, :, None]).to(torch.bfloat16).view(T * k, d)
+        # input gradients through the two grouped GEMMs (weights as stored are the [E, N, K] operands)
+        da = torch.empty_like(ws.a)
+        _grouped_gemm(dys, w2.contiguous(), da, ws)                     # [cap, h] = dys @ w2[e]^T
+        dh = swiglu_backward(ws.h, da, h)                               # [cap, 2h]
+        dxs = torch.empty_like(ws.xs)
+        _grouped_gemm(dh, torch.cat([w1, w3], 2).contiguous(), dxs, ws)  # [cap, d] = dh @ [w1 | w3][e]^T
+        dx = dxs[rows].view(T, k, d).float().sum(1).to(torch.bfloat16)
+        # weight gradients: one TN product per expert over its row segment
+        offs, cnts = ws.offsets.tolist(), ws.counts.tolist()
+        dw1, dw2, dw3 = torch.zeros_like(w1), torch.zeros_like(w2), torch.zeros_like(w3)
+        for e in range(E):
+            c = cnts[e]
+            if c == 0:
+                continue
+            lo = offs[e]
+            xe, he, ae, ye = ws.xs[lo:lo + c], dh[lo:lo + c], ws.a[lo:lo + c], dys[lo:lo + c]
+            gemm(xe, he[:, :h], a_mn=True, b_mn=True, out=dw1[e])       # [d, h] = xs^T dh_gate
+            gemm(xe, he[:, h:], a_mn=True, b_mn=True, out=dw3[e])
+            gemm(ae, ye, a_mn=True, b_mn=True, out=dw2[e])              # [h, d] = a^T dys
+        ctx.ws = None
+        return dx, dw1, dw2, dw3, d_w.to(ctx.w_dtype), None
+
+
+def moe_experts_native_ok(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w3: torch.Tensor, indices: torch.Tensor) -> bool:
+    E, d, h = w1.shape
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w1.dtype == w2.dtype == w3.dtype == torch.bfloat16 and _lib.available()
+            and d % 64 == 0 and h % 64 == 0 and E <= 256 and indices.shape[-1] <= 8 and x.shape[0] > 0)
+
+
+def moe_experts(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w3: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+    """Differentiable expert FFN on the native kernels (see ``_MoEExpertsFn``)."""
+    return _MoEExpertsFn.apply(x.contiguous(), w1, w2, w3, weights, indices)

@@ -21,6 +21,10 @@ from torch import Tensor
 
 from .stages_core import stage
 
+import os as _os
+
+_FORCE_TORCH_MOE = _os.environ.get("NFN_B200_FORCE_TORCH", "") == "1"
+
 
 class RoutingStatsMixin:
     """Running telemetry of a router: per-expert load, mean routing entropy, top-1 share."""
@@ -149,6 +153,13 @@ def grouped_swiglu_experts(x_flat: Tensor, w1: Tensor, w2: Tensor, w3: Tensor, w
     n, d = x_flat.shape
     top_k = indices.shape[-1]
     experts = w1.shape[0]
+    if x_flat.is_cuda and not _FORCE_TORCH_MOE:
+        # CUDA + bf16 (directly or under bf16 autocast): grouped tcgen05 GEMMs with native backward
+        from ..ops.moe import moe_experts, moe_experts_native_ok
+        cast = torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16
+        xb, a1, a2, a3 = ((t.to(torch.bfloat16) for t in (x_flat, w1, w2, w3)) if cast else (x_flat, w1, w2, w3))
+        if moe_experts_native_ok(xb, a1, a2, a3, indices):
+            return moe_experts(xb, a1, a2, a3, weights, indices).to(x_flat.dtype if not cast else torch.bfloat16)
     flat_e = indices.reshape(-1)
     order = torch.argsort(flat_e, stable=True)
     token_of = (order // top_k)

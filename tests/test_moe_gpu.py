@@ -27,3 +27,43 @@ def test_moe_forward_matches_reference(T, E, k, d, F, score):
     err = (out.float() - ref).abs().amax(-1)
     assert float((err > 0.08).float().mean()) < 0.02, float(err.max())
     assert int(ws.plan[0]) * 128 == int(ws.plan[1]) and int(ws.counts.sum()) == T * k
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("E,k,T", [(8, 2, 300), (16, 4, 1024)])
+def test_moe_experts_autograd_matches_torch(E, k, T):
+    """Native expert FFN with gradients against the per-expert PyTorch loop in fp32."""
+    import neuralfn_b200.tensor.stages_moe as SM
+    from neuralfn_b200.ops.moe import moe_experts
+    d, h = 256, 384
+    g = torch.Generator(device="cuda").manual_seed(E * 100 + k)
+    x = torch.randn(T, d, device="cuda", generator=g)
+    w1, w3 = (torch.randn(E, d, h, device="cuda", generator=g) * 0.05 for _ in range(2))
+    w2 = torch.randn(E, h, d, device="cuda", generator=g) * 0.05
+    logits = torch.randn(T, E, device="cuda", generator=g)
+    wts, idx = torch.softmax(logits, -1).topk(k, -1)
+    wts = wts / wts.sum(-1, keepdim=True)
+    dout = torch.randn(T, d, device="cuda", generator=g)
+
+    ref_in = [t.clone().requires_grad_(True) for t in (x, w1, w2, w3, wts)]
+    SM._FORCE_TORCH_MOE = True
+    try:
+        ref = SM.grouped_swiglu_experts(ref_in[0], ref_in[1], ref_in[2], ref_in[3], ref_in[4], idx)
+    finally:
+        SM._FORCE_TORCH_MOE = False
+    ref.backward(dout)
+
+    got_in = [t.to(torch.bfloat16).requires_grad_(True) for t in (x, w1, w2, w3)] + [wts.clone().requires_grad_(True)]
+    got = moe_experts(got_in[0], got_in[1], got_in[2], got_in[3], got_in[4], idx)
+    got.backward(dout.to(torch.bfloat16))
+
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-9))
+
+    assert rel(got, ref) < 0.03
+    for name, a, b in zip(("dx", "dw1", "dw2", "dw3", "dweights"), got_in, ref_in):
+        assert rel(a.grad, b.grad) < 0.04, (name, rel(a.grad, b.grad))
+
+    # the stage function takes the native path for bf16 CUDA tensors
+    y = SM.grouped_swiglu_experts(got_in[0].detach(), got_in[1].detach(), got_in[2].detach(), got_in[3].detach(), wts, idx)
+    assert y.dtype == torch.bfloat16 and rel(y, ref) < 0.03
