@@ -28,7 +28,7 @@ import torch.nn as nn
 
 from ..tensor.stages_moe import grouped_swiglu_experts
 
-__all__ = ["ExpertParallelFFN", "all_to_all_rows"]
+__all__ = ["ExpertParallelFFN", "expert_parallel_ffn", "all_to_all_rows"]
 
 
 class _AllToAllRows(torch.autograd.Function):
@@ -76,33 +76,42 @@ class ExpertParallelFFN(nn.Module):
             p.copy_(t[lo:lo + self.local])
 
     def forward(self, x: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
-        T, d = x.shape
-        k, E, W = indices.shape[-1], self.n_experts, self.world
-        flat_e = indices.reshape(-1)
-        order = torch.argsort(flat_e, stable=True)            # assignments sorted by global expert (hence by owner rank)
-        token_of = order // k
-        counts = torch.bincount(flat_e, minlength=E)          # [E] rows this rank sends to every expert
-        if W > 1:
-            theirs = torch.empty_like(counts)                 # [W * local]: rows every rank sends to MY experts, by source rank
-            dist.all_to_all_single(theirs, counts, group=self.group)
-            both = torch.stack([counts, theirs]).cpu()
-            send = both[0].view(W, self.local).sum(1).tolist()
-            recv_counts = both[1].view(W, self.local)
-            recv = recv_counts.sum(1).tolist()
-        else:
-            recv_counts = counts.cpu().view(1, E)
-            send = recv = [int(recv_counts.sum())]
-        rows = x[token_of]
-        got = all_to_all_rows(rows, send, recv, self.group) if W > 1 else rows
-        # local expert id of every received row: per source rank the rows come sorted by expert
-        local_id = torch.repeat_interleave(torch.arange(self.local).repeat(recv_counts.shape[0]), recv_counts.reshape(-1)).to(x.device)
-        n = got.shape[0]
-        if n:
-            ones = torch.ones(n, 1, dtype=torch.float32, device=x.device)
-            ys = grouped_swiglu_experts(got, self.w1, self.w2, self.w3, ones, local_id.view(n, 1))
-        else:
-            ys = got * (self.w1.sum() + self.w2.sum() + self.w3.sum()) * 0  # keeps the parameters in the graph
-        back = all_to_all_rows(ys, recv, send, self.group) if W > 1 else ys
-        wsorted = weights.reshape(-1)[order].unsqueeze(-1).to(back.dtype)
-        out = torch.zeros(T, d, dtype=back.dtype, device=x.device)
-        return out.index_add(0, token_of, back * wsorted)
+        return expert_parallel_ffn(x, weights, indices, self.w1, self.w2, self.w3, self.n_experts, self.group)
+
+
+def expert_parallel_ffn(x: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w3: torch.Tensor,
+                        n_experts: int, group=None) -> torch.Tensor:
+    """Functional form: ``w1 / w2 / w3`` are this rank's experts ``[n_experts / W, ...]``."""
+    T, d = x.shape
+    W = dist.get_world_size(group) if dist.is_initialized() else 1
+    k, E, local = indices.shape[-1], n_experts, w1.shape[0]
+    if local * W != E:
+        raise ValueError(f"{local} local experts x {W} ranks != {E} experts")
+    flat_e = indices.reshape(-1)
+    order = torch.argsort(flat_e, stable=True)            # assignments sorted by global expert (hence by owner rank)
+    token_of = order // k
+    counts = torch.bincount(flat_e, minlength=E)          # [E] rows this rank sends to every expert
+    if W > 1:
+        theirs = torch.empty_like(counts)                 # [W * local]: rows every rank sends to MY experts, by source rank
+        dist.all_to_all_single(theirs, counts, group=group)
+        both = torch.stack([counts, theirs]).cpu()
+        send = both[0].view(W, local).sum(1).tolist()
+        recv_counts = both[1].view(W, local)
+        recv = recv_counts.sum(1).tolist()
+    else:
+        recv_counts = counts.cpu().view(1, E)
+        send = recv = [int(recv_counts.sum())]
+    rows = x[token_of]
+    got = all_to_all_rows(rows, send, recv, group) if W > 1 else rows
+    # local expert id of every received row: per source rank the rows come sorted by expert
+    local_id = torch.repeat_interleave(torch.arange(local).repeat(recv_counts.shape[0]), recv_counts.reshape(-1)).to(x.device)
+    n = got.shape[0]
+    if n:
+        ones = torch.ones(n, 1, dtype=torch.float32, device=x.device)
+        ys = grouped_swiglu_experts(got, w1, w2, w3, ones, local_id.view(n, 1))
+    else:
+        ys = got * (w1.sum() + w2.sum() + w3.sum()) * 0  # keeps the parameters in the graph
+    back = all_to_all_rows(ys, recv, send, group) if W > 1 else ys
+    wsorted = weights.reshape(-1)[order].unsqueeze(-1).to(back.dtype)
+    out = torch.zeros(T, d, dtype=back.dtype, device=x.device)
+    return out.index_add(0, token_of, back * wsorted)

@@ -242,6 +242,12 @@ class TPLlama:
             if self.tp.world > 1:
                 dist.all_reduce(self.grads[self.n_sharded:], group=self.tp.group)
 
+    def reduce_loss(self, share: torch.Tensor) -> torch.Tensor:
+        """Batch-mean loss from this rank's share (``loss`` returns mean-over-local-rows / W)."""
+        if self.tp.world > 1:
+            dist.all_reduce(share, group=self.tp.group)
+        return share
+
     def grad_norm(self) -> torch.Tensor:
         """Norm of the whole (unsharded) gradient, without a host synchronisation."""
         s = torch.linalg.vector_norm(self.grads[:self.n_sharded], dtype=torch.float32) ** 2
@@ -296,7 +302,4 @@ class TPLlamaTrainer:
                 upd[:mdl.layout.n_decay] += c.weight_decay * self.master[:mdl.layout.n_decay]
                 self.master -= lr * upd
                 mdl.params.detach().copy_(self.master.to(mdl.dtype))
-        out = loss.detach().clone()
-        if mdl.tp.world > 1:
-            dist.all_reduce(out, group=mdl.tp.group)
-        return out
+        return mdl.reduce_loss(loss.detach().clone())
