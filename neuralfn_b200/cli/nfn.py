@@ -54,6 +54,12 @@ def _add_train_flags(p: argparse.ArgumentParser) -> None:
     p.add_argument("--no-cuda-graph", action="store_true")
     p.add_argument("--gpus", type=int, default=0, help="launch this many ranks on this node (0: stay in this process)")
     p.add_argument("--print-plan", "--dry-run", dest="print_plan", action="store_true")
+    p.add_argument("--parallel", choices=["dp", "tp", "ep"], default="dp",
+                   help="dp: data parallel dense engines (default); tp: tensor-parallel Llama over --gpus ranks; ep: expert-parallel MoE Llama")
+    p.add_argument("--tp-model", default="tiny", help="--parallel tp: llama3_8b | llama_1b | tiny")
+    p.add_argument("--experts", type=int, default=8)
+    p.add_argument("--top-k-experts", type=int, default=2)
+    p.add_argument("--expert-hidden", type=int, default=1024)
 
 
 def _train_config(a):
@@ -68,7 +74,29 @@ def _train_config(a):
         checkpoint_every=a.checkpoint_every, seed=a.seed, resume=a.resume, use_cuda_graph=not a.no_cuda_graph)
 
 
+def _parallel_train_argv(a) -> list[str]:
+    argv = ["--parallel", a.parallel, "--dataset", a.dataset, "--batch-size", str(a.batch_size), "--seq-len", str(a.seq_len), "--max-steps", str(a.max_steps),
+            "--learning-rate", str(a.learning_rate), "--warmup-steps", str(a.warmup_steps), "--weight-decay", str(a.weight_decay),
+            "--max-grad-norm", str(a.max_grad_norm), "--progress-every", str(a.progress_every), "--checkpoint-every", str(a.checkpoint_every),
+            "--output-dir", a.output_dir, "--seed", str(a.seed)]
+    if a.resume:
+        argv.append("--resume")
+    if a.parallel == "tp":
+        return argv + ["--model", a.tp_model]
+    return argv + ["--n-layer", str(a.n_layer), "--n-head", str(a.n_head), "--n-kv-head", str(a.n_kv_head or a.n_head), "--d-model", str(a.d_model),
+                   "--vocab-size", str(a.vocab_size), "--experts", str(a.experts), "--top-k", str(a.top_k_experts), "--expert-hidden", str(a.expert_hidden)]
+
+
 def cmd_train(a) -> int:
+    if a.parallel in ("tp", "ep"):
+        # the model-parallel families have their own driver; one process per GPU
+        argv = _parallel_train_argv(a)
+        if a.gpus > 1 and "RANK" not in os.environ:
+            import subprocess
+            return subprocess.call([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.gpus}", "--master-addr",
+                                    "127.0.0.1", "--master-port", str(29500 + os.getpid() % 2000), "-m", "neuralfn_b200.parallel.train", *argv])
+        from ..parallel.train import main as parallel_main
+        return parallel_main(argv)
     if a.print_plan:
         from ..native_train import training_plan
         print(json.dumps({"status": "plan", **training_plan(_train_config(a), max(1, a.gpus))}, indent=2))
