@@ -353,6 +353,302 @@ decode_attention_kernel(const DecodeParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-core variant. One token against thousands of cached positions is bound by reading K
+// and V once, but the SIMT kernel above spends ~75 warp instructions per position on dot
+// products, reductions and exponentials and ends up latency-bound at a fifth of the HBM rate.
+// Here the query heads that share a KV head form the (padded) 16-row A operand of
+// mma.sync.m16n8k16 - the right-sized tensor instruction for 1..16 rows; a tcgen05 tile would
+// start at 64 or 128 rows - and a warp consumes 16 cache positions per step:
+//   S = Q K^T   2 n-tiles x HD/16 MMAs, K rows loaded straight from global memory as 16-byte
+//               chunks (the contraction index is permuted identically in Q and K, so every
+//               lane's B fragment is a run of contiguous bytes of one cache row);
+//   softmax     on the accumulator fragment (row max / sum over 4 lanes), one rescale per step;
+//   O += P V    HD/8 n-tiles x 1 MMA, V rows again as 16-byte chunks, two rows interleaved
+//               into a B register with one byte-permute; the output columns are permuted
+//               the same way and un-permuted once at the end.
+// About 10 warp instructions per position instead of 75; no shared memory in the main loop.
+// The four warps of a CTA take alternate steps of the CTA's position range and merge at the
+// end; splits merge through the same workspace + ticket scheme as above.
+constexpr int MMA_WARPS = 4;
+constexpr int MMA_STEP = 16;  // positions per warp step
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t word_of(const uint4& u, int i) { return i == 0 ? u.x : (i == 1 ? u.y : (i == 2 ? u.z : u.w)); }
+
+template <int HD, bool WIDE>
+constexpr size_t decode_mma_smem_bytes() {
+  constexpr int ROWS = WIDE ? 16 : 8;
+  return (size_t)(MMA_WARPS + 1) * ROWS * (HD + 2) * sizeof(float) + (size_t)(16 + 2) * HD * 2;
+}
+
+template <int HD, bool WIDE>
+__global__ void __launch_bounds__(MMA_WARPS * 32, 3)
+decode_attention_mma_kernel(const DecodeParams p) {
+  constexpr int ROWS = WIDE ? 16 : 8;          // query-head rows kept per CTA
+  constexpr int KCH = HD / 32;                 // 16-byte chunks of a K row per lane
+  constexpr int KB = HD / 16;                  // k-blocks of the S product
+  constexpr int NT = HD / 8;                   // n-tiles of the O product
+  constexpr int VCH = HD / 64;                 // 16-byte chunks of a V row per lane
+  constexpr int CH = HD / 16, HALF = HD / 2, NPART = MMA_WARPS + 1;
+  extern __shared__ __align__(128) float smem[];
+  float* sm_o = smem;                                         // [NPART][ROWS][HD]
+  float* sm_ml = smem + NPART * ROWS * HD;                    // [NPART][ROWS][2]
+  __nv_bfloat16* sm_q = reinterpret_cast<__nv_bfloat16*>(sm_ml + NPART * ROWS * 2);  // [16][HD]
+  __nv_bfloat16* sm_kn = sm_q + 16 * HD;                      // [HD] new k (rotated), then [HD] new v
+  __nv_bfloat16* sm_vn = sm_kn + HD;
+  __shared__ int sh_last;
+
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int kvh = blockIdx.y / p.gtiles, gt = blockIdx.y % p.gtiles;
+  const int group = p.Hq / p.Hkv;
+  const int g0 = gt * ROWS;
+  const int gcount = min(ROWS, group - g0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = lane >> 2, j = lane & 3;
+
+  const int len = p.lengths[b];
+  if (len <= 0) return;  // uniform per CTA
+  const int pos = len - 1;
+  const int slot_new = pos % p.cap;
+  const int n_slots = min(len, p.cap);
+  const int tpos = min(pos, p.max_pos - 1);
+  const float* cosr = p.cosT ? p.cosT + (long long)tpos * HALF : nullptr;
+  const float* sinr = p.sinT ? p.sinT + (long long)tpos * HALF : nullptr;
+  const float sign = cosr ? p.sign : 0.f;
+  const __nv_bfloat16* row = p.qkv + (long long)b * p.ld;
+  __nv_bfloat16* kbase = p.kc + (long long)b * p.batch_stride + (long long)kvh * p.cap * HD;
+  __nv_bfloat16* vbase = p.vc + (long long)b * p.batch_stride + (long long)kvh * p.cap * HD;
+
+  // ---- prologue: the 16 sub-groups of 8 lanes prepare one query head each (norm, rotary, scale)
+  {
+    const int sg = threadIdx.x >> 3, sub = threadIdx.x & 7;
+    float v[2 * CH];
+    // every lane runs load_head (its reductions are full-warp shuffles); rows past the group are zeroed
+    load_head<HD>(row + (long long)(kvh * group + g0 + min(sg, gcount - 1)) * HD, p.qw, p.qk_norm, p.eps, cosr, sinr, sign, p.scale, sub, v);
+    if (sg >= gcount) {
+#pragma unroll
+      for (int i = 0; i < 2 * CH; ++i) v[i] = 0.f;
+    }
+    store_chunk<CH>(sm_q + sg * HD + sub * CH, v);
+    store_chunk<CH>(sm_q + sg * HD + HALF + sub * CH, v + CH);
+    if (split == 0 && warp == 0) {  // the new token's k and v (all four sub-groups compute it, the first one stores)
+      float kn[2 * CH], vn[2 * CH];
+      load_head<HD>(row + (long long)(p.Hq + kvh) * HD, p.kw, p.qk_norm, p.eps, cosr, sinr, sign, 1.f, sub, kn);
+      const __nv_bfloat16* vsrc = row + (long long)(p.Hq + p.Hkv + kvh) * HD;
+      load_chunk<CH>(vsrc + sub * CH, vn);
+      load_chunk<CH>(vsrc + HALF + sub * CH, vn + CH);
+      if (sg == 0) {
+        store_chunk<CH>(sm_kn + sub * CH, kn);
+        store_chunk<CH>(sm_kn + HALF + sub * CH, kn + CH);
+        store_chunk<CH>(sm_vn + sub * CH, vn);
+        store_chunk<CH>(sm_vn + HALF + sub * CH, vn + CH);
+      }
+      if (sg == 0 && gt == 0) {  // exactly one CTA appends the row; nobody uses that slot's old content in this launch
+        store_chunk<CH>(kbase + (long long)slot_new * HD + sub * CH, kn);
+        store_chunk<CH>(kbase + (long long)slot_new * HD + HALF + sub * CH, kn + CH);
+        store_chunk<CH>(vbase + (long long)slot_new * HD + sub * CH, vn);
+        store_chunk<CH>(vbase + (long long)slot_new * HD + HALF + sub * CH, vn + CH);
+      }
+    }
+  }
+  __syncthreads();
+
+  // A fragments of Q: lane (r, j) holds, for k-block kb, the dims of ITS OWN K chunks:
+  // pair e = 2 kb (+1) -> chunk c = e / 4, pair i = e % 4 -> dims c * 32 + j * 8 + 2 i (+1)
+  uint32_t qa[KB][4];
+#pragma unroll
+  for (int kb = 0; kb < KB; ++kb) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int e = 2 * kb + h, d = (e >> 2) * 32 + j * 8 + 2 * (e & 3);
+      qa[kb][2 * h] = *reinterpret_cast<const uint32_t*>(sm_q + r * HD + d);
+      qa[kb][2 * h + 1] = WIDE ? *reinterpret_cast<const uint32_t*>(sm_q + (r + 8) * HD + d) : 0u;
+    }
+  }
+
+  float o[NT][4];
+#pragma unroll
+  for (int t = 0; t < NT; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[t][i] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // rows r and r + 8; l is this lane's share
+
+  const int per = (n_slots + p.splits - 1) / p.splits;
+  const int s_lo = split * per, s_hi = min(n_slots, s_lo + per);
+  const int nsteps = s_hi > s_lo ? (s_hi - s_lo + MMA_STEP - 1) / MMA_STEP : 0;
+  const int last_row = max(s_hi - 1, 0);
+
+  for (int st = warp; st < nsteps; st += MMA_WARPS) {
+    const int s0 = s_lo + st * MMA_STEP;
+    // K rows s0 + r and s0 + 8 + r, V rows s0 + 2j, +1, +8, +9 (clamped: masked below)
+    uint4 kq[2][KCH], vq[4][VCH];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __nv_bfloat16* kr = kbase + (long long)min(s0 + 8 * h + r, last_row) * HD + j * 8;
+#pragma unroll
+      for (int c = 0; c < KCH; ++c) kq[h][c] = ldg_stream16(kr + c * 32);
+    }
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const int rr = s0 + (q4 >> 1) * 8 + 2 * j + (q4 & 1);
+      const __nv_bfloat16* vr = vbase + (long long)min(rr, last_row) * HD + r * 8;
+#pragma unroll
+      for (int c = 0; c < VCH; ++c) vq[q4][c] = ldg_stream16(vr + c * 64);
+    }
+    // S = Q K^T for the two groups of 8 positions
+    float s[2][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[h][i] = 0.f;
+#pragma unroll
+      for (int kb = 0; kb < KB; ++kb) {
+        const int e = 2 * kb;
+        mma_bf16_16816(s[h], qa[kb], word_of(kq[h][e >> 2], e & 3), word_of(kq[h][(e + 1) >> 2], (e + 1) & 3));
+      }
+    }
+    // mask: columns 2j, 2j+1 of each group
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int sp = s0 + 8 * h + 2 * j + i;
+        if (sp >= s_hi || sp == slot_new) { s[h][i] = -INFINITY; s[h][2 + i] = -INFINITY; }
+      }
+    // online softmax per row (rows r: elements 0,1; rows r + 8: elements 2,3)
+    uint32_t pa[4];
+#pragma unroll
+    for (int hr = 0; hr < (WIDE ? 2 : 1); ++hr) {
+      float mx = fmaxf(fmaxf(s[0][2 * hr], s[0][2 * hr + 1]), fmaxf(s[1][2 * hr], s[1][2 * hr + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float mn = fmaxf(m_run[hr], mx);
+      const float mu = mn == -INFINITY ? 0.f : mn;
+      const float corr = __expf(m_run[hr] - mu);
+      const float p00 = __expf(s[0][2 * hr] - mu), p01 = __expf(s[0][2 * hr + 1] - mu);
+      const float p10 = __expf(s[1][2 * hr] - mu), p11 = __expf(s[1][2 * hr + 1] - mu);
+      l_run[hr] = l_run[hr] * corr + (p00 + p01) + (p10 + p11);
+      m_run[hr] = mn;
+      pa[hr] = pack_bf16x2(p00, p01);        // a0 / a1: positions 2j, 2j+1 of the first group
+      pa[2 + hr] = pack_bf16x2(p10, p11);    // a2 / a3: of the second group
+#pragma unroll
+      for (int t = 0; t < NT; ++t) { o[t][2 * hr] *= corr; o[t][2 * hr + 1] *= corr; }
+    }
+    if (!WIDE) { pa[1] = 0u; pa[3] = 0u; }
+    // O += P V: n-tile t takes element t % 8 of chunk t / 8 of this lane's V rows
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const int c = t >> 3, x = t & 7;
+      const uint32_t sel = (x & 1) ? 0x7632u : 0x5410u;
+      const uint32_t b0 = __byte_perm(word_of(vq[0][c], x >> 1), word_of(vq[1][c], x >> 1), sel);
+      const uint32_t b1 = __byte_perm(word_of(vq[2][c], x >> 1), word_of(vq[3][c], x >> 1), sel);
+      mma_bf16_16816(o[t], pa, b0, b1);
+    }
+  }
+
+  // ---- partials of this CTA: one per warp + the new token (split 0) ---------------------------
+#pragma unroll
+  for (int hr = 0; hr < (WIDE ? 2 : 1); ++hr) {
+    float l = l_run[hr];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int rowi = r + 8 * hr;
+    if (j == 0) {
+      sm_ml[(warp * ROWS + rowi) * 2] = m_run[hr];
+      sm_ml[(warp * ROWS + rowi) * 2 + 1] = l;
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const int d0 = (t >> 3) * 64 + (2 * j) * 8 + (t & 7);
+      sm_o[(warp * ROWS + rowi) * HD + d0] = o[t][2 * hr];
+      sm_o[(warp * ROWS + rowi) * HD + d0 + 8] = o[t][2 * hr + 1];
+    }
+  }
+  if (warp == 0) {  // slot MMA_WARPS: the new token (weight exp(q.k), value v), present in split 0 only
+    for (int g = 0; g < ROWS; ++g) {
+      float d = 0.f;
+      if (split == 0 && g < gcount)
+        for (int e = lane; e < HD; e += 32) d += __bfloat162float(sm_q[g * HD + e]) * __bfloat162float(sm_kn[e]);
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) d += __shfl_xor_sync(0xffffffffu, d, sft);
+      const bool live = split == 0 && g < gcount;
+      if (lane == 0) {
+        sm_ml[(MMA_WARPS * ROWS + g) * 2] = live ? d : -INFINITY;
+        sm_ml[(MMA_WARPS * ROWS + g) * 2 + 1] = live ? 1.f : 0.f;
+      }
+      for (int e = lane; e < HD; e += 32) sm_o[(MMA_WARPS * ROWS + g) * HD + e] = live ? __bfloat162float(sm_vn[e]) : 0.f;
+    }
+  }
+  __syncthreads();
+  const long long unit = ((long long)b * p.Hkv + kvh) * p.gtiles + gt;
+  float* po = p.part_o + (unit * p.splits + split) * (long long)(ROWS * HD);
+  float* pml = p.part_ml + (unit * p.splits + split) * (long long)(ROWS * 2);
+  for (int e = threadIdx.x; e < ROWS * HD; e += blockDim.x) {
+    const int g = e / HD, d = e % HD;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int q = 0; q < NPART; ++q) mx = fmaxf(mx, sm_ml[(q * ROWS + g) * 2]);
+    float acc = 0.f, ls = 0.f;
+    if (mx != -INFINITY) {
+#pragma unroll
+      for (int q = 0; q < NPART; ++q) {
+        const float w = __expf(sm_ml[(q * ROWS + g) * 2] - mx);
+        acc += w * sm_o[(q * ROWS + g) * HD + d];
+        ls += w * sm_ml[(q * ROWS + g) * 2 + 1];
+      }
+    }
+    po[e] = acc;
+    if (d == 0) {
+      pml[g * 2] = mx;
+      pml[g * 2 + 1] = ls;
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(&p.tickets[unit], 1);
+    sh_last = (t == p.splits - 1);
+    if (sh_last) p.tickets[unit] = 0;
+  }
+  __syncthreads();
+  if (!sh_last) return;
+  __threadfence();
+  const float* ao = p.part_o + unit * p.splits * (long long)(ROWS * HD);
+  const float* aml = p.part_ml + unit * p.splits * (long long)(ROWS * 2);
+  for (int e = threadIdx.x; e < gcount * HD; e += blockDim.x) {
+    const int g = e / HD, d = e % HD;
+    float mx = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) mx = fmaxf(mx, __ldcg(aml + (s * ROWS + g) * 2));
+    float acc = 0.f, ls = 0.f;
+    if (mx != -INFINITY)
+      for (int s = 0; s < p.splits; ++s) {
+        const float w = __expf(__ldcg(aml + (s * ROWS + g) * 2) - mx);
+        acc += w * __ldcg(ao + (long long)(s * ROWS + g) * HD + d);
+        ls += w * __ldcg(aml + (s * ROWS + g) * 2 + 1);
+      }
+    p.out[(long long)b * p.Hq * HD + (long long)(kvh * group + g0 + g) * HD + d] = __float2bfloat16(ls > 0.f ? acc / ls : 0.f);
+  }
+}
+
+template <int HD, bool WIDE>
+static int launch_decode_mma(const DecodeParams& p, cudaStream_t st) {
+  constexpr size_t smem = decode_mma_smem_bytes<HD, WIDE>();
+  static_assert(smem <= 48 * 1024, "decode_attention_mma: static budget");
+  dim3 grid(p.splits, p.Hkv * p.gtiles, p.B);
+  decode_attention_mma_kernel<HD, WIDE><<<grid, MMA_WARPS * 32, smem, st>>>(p);
+  return launch_check("decode_attention_mma", 1);
+}
+
 template <int HD, int G>
 static int launch_decode(const DecodeParams& p, cudaStream_t st) {
   constexpr size_t smem = decode_smem_bytes<HD, G>();
@@ -376,11 +672,27 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
 
 using namespace nfn;
 
+namespace nfn {
+static int g_decode_impl = 1;  // 1: tensor-core kernel, 0: SIMT kernel
+}
+
+// Selects the kernel behind nfn_decode_attention (1 = mma.sync variant, the default; 0 = SIMT). Returns the old value.
+extern "C" int nfn_decode_attention_set_impl(int impl) {
+  const int old = nfn::g_decode_impl;
+  nfn::g_decode_impl = impl ? 1 : 0;
+  return old;
+}
+
 extern "C" long long nfn_decode_attention_workspace_bytes(int B, int n_q_heads, int n_kv_heads, int head_dim, int max_splits) {
   if (B <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || max_splits <= 0) return -1;
   const int group = n_q_heads / n_kv_heads, G = group >= 4 ? 4 : (group >= 2 ? 2 : 1), gtiles = (group + G - 1) / G;
   const long long units = (long long)B * n_kv_heads * gtiles;
-  return 256 + ((units * 4 + 255) / 256) * 256 + units * max_splits * (long long)G * (head_dim + 2) * 4;
+  const long long simt = ((units * 4 + 255) / 256) * 256 + units * max_splits * (long long)G * (head_dim + 2) * 4;
+  // the tensor-core kernel keeps 8 or 16 head rows per CTA
+  const int rows = group > 8 ? 16 : 8, mtiles = (group + rows - 1) / rows;
+  const long long munits = (long long)B * n_kv_heads * mtiles;
+  const long long mma = ((munits * 4 + 255) / 256) * 256 + munits * max_splits * (long long)rows * (head_dim + 2) * 4;
+  return 256 + std::max(simt, mma);
 }
 
 extern "C" int nfn_decode_attention(const void* qkv, int ld, void* k_cache, void* v_cache, long long cache_batch_stride,
@@ -396,12 +708,14 @@ extern "C" int nfn_decode_attention(const void* qkv, int ld, void* k_cache, void
   if (ld < (n_q_heads + 2 * n_kv_heads) * head_dim || ld % 8) return fail(-1, "decode_attention: qkv row stride too small or not a multiple of 8");
   if ((cos_table == nullptr) != (sin_table == nullptr) || (cos_table && max_pos <= 0)) return fail(-1, "decode_attention: cos/sin tables must come together");
   if (cos_table && rope_sign != 1.f && rope_sign != -1.f) return fail(-1, "decode_attention: rope_sign must be +1 or -1");
-  const int group = n_q_heads / n_kv_heads, G = group >= 4 ? 4 : (group >= 2 ? 2 : 1), gtiles = (group + G - 1) / G;
+  const bool use_mma = g_decode_impl == 1;
+  const int group = n_q_heads / n_kv_heads;
+  const int G = use_mma ? (group > 8 ? 16 : 8) : (group >= 4 ? 4 : (group >= 2 ? 2 : 1)), gtiles = (group + G - 1) / G;
   const long long units = (long long)B * n_kv_heads * gtiles;
   if (splits <= 0) {
-    // one full wave at two resident CTAs per SM (rounding down, so no straggler wave), and at
-    // least 128 cache positions per split
-    const long long want = (2LL * sm_count()) / units;
+    // one full wave at two (SIMT) or three (tensor-core kernel) resident CTAs per SM (rounding
+    // down, so no straggler wave), and at least 128 cache positions per split
+    const long long want = ((use_mma ? 3LL : 2LL) * sm_count()) / units;
     splits = (int)std::max<long long>(1, std::min<long long>(want, (cap + 127) / 128));
   }
   splits = min(splits, 64);
@@ -428,6 +742,10 @@ extern "C" int nfn_decode_attention(const void* qkv, int ld, void* k_cache, void
   p.part_o = p.part_ml + units * splits * (long long)G * 2;
   p.status = status_ptr();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_mma) {
+    if (head_dim == 128) return G == 16 ? launch_decode_mma<128, true>(p, st) : launch_decode_mma<128, false>(p, st);
+    return G == 16 ? launch_decode_mma<64, true>(p, st) : launch_decode_mma<64, false>(p, st);
+  }
   if (head_dim == 128) return G == 4 ? launch_decode<128, 4>(p, st) : (G == 2 ? launch_decode<128, 2>(p, st) : launch_decode<128, 1>(p, st));
   return G == 4 ? launch_decode<64, 4>(p, st) : (G == 2 ? launch_decode<64, 2>(p, st) : launch_decode<64, 1>(p, st));
 }

@@ -150,6 +150,8 @@ int nfn_sample_rows(const void* logits, int is_fp32, long long ld, int rows, int
 // appends the (normed, rotated) k and v of the new token at slot (len - 1) % cap. The
 // workspace must be zero-filled once before its first use and is left ready for the next call.
 long long nfn_decode_attention_workspace_bytes(int B, int n_q_heads, int n_kv_heads, int head_dim, int max_splits);
+// 1 (default): mma.sync kernel, 16 cache positions per warp step; 0: SIMT kernel. Returns the previous setting.
+int nfn_decode_attention_set_impl(int impl);
 int nfn_decode_attention(const void* qkv, int ld, void* k_cache, void* v_cache, long long cache_batch_stride,
                          const int* lengths, void* out, int B, int n_q_heads, int n_kv_heads, int head_dim, int cap,
                          const void* q_norm_weight, const void* k_norm_weight, int qk_norm, float eps,

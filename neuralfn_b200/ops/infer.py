@@ -113,6 +113,14 @@ class DecodeAttentionWorkspace:
         self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
 
 
+def decode_attention_set_impl(impl: str) -> str:
+    """Selects the decode-attention kernel: ``"mma"`` (tensor-core, default) or ``"simt"``. Returns the previous one."""
+    if impl not in ("mma", "simt"):
+        raise ValueError("impl is 'mma' or 'simt'")
+    old = _lib.load().nfn_decode_attention_set_impl(c_int(1 if impl == "mma" else 0))
+    return "mma" if old else "simt"
+
+
 def decode_attention(qkv, k_cache, v_cache, lengths, *, n_q_heads: int, n_kv_heads: int, head_dim: int, workspace: DecodeAttentionWorkspace,
                      cos=None, sin=None, convention="hf", qk_norm: bool = False, q_norm_weight=None, k_norm_weight=None,
                      eps: float = 1e-6, scale: float | None = None, splits: int = 0, out=None):

@@ -132,8 +132,17 @@ def _decode_ref(q, kc, vc, lengths, cap, scale):
     return out
 
 
-@pytest.mark.parametrize("hd,Hq,Hkv,cap,ring", [(128, 4, 1, 700, False), (64, 6, 2, 128, True), (128, 8, 8, 300, False)])
-def test_decode_attention_append_and_attend(hd, Hq, Hkv, cap, ring):
+@pytest.fixture(params=["mma", "simt"])
+def decode_impl(request):
+    from neuralfn_b200.ops import infer
+    old = infer.decode_attention_set_impl(request.param)
+    yield request.param
+    infer.decode_attention_set_impl(old)
+
+
+@pytest.mark.parametrize("hd,Hq,Hkv,cap,ring", [(128, 4, 1, 700, False), (64, 6, 2, 128, True), (128, 8, 8, 300, False), (128, 24, 2, 513, False),
+                                                (64, 16, 1, 200, True)])
+def test_decode_attention_append_and_attend(hd, Hq, Hkv, cap, ring, decode_impl):
     from neuralfn_b200.ops import infer
     torch.manual_seed(4)
     B = 5
