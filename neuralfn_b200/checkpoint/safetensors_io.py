@@ -27,7 +27,8 @@ from typing import Mapping
 import numpy as np
 import torch
 
-__all__ = ["SafetensorsError", "read_safetensors", "write_safetensors", "read_sharded_checkpoint", "load_hf_llama_directory"]
+__all__ = ["SafetensorsError", "read_safetensors", "write_safetensors", "read_sharded_checkpoint", "load_hf_llama_directory",
+           "export_hf_llama_directory"]
 
 MAX_HEADER_BYTES = 100 * 1024 * 1024
 _DTYPES = {"BF16": (torch.bfloat16, 2), "F16": (torch.float16, 2), "F32": (torch.float32, 4), "F64": (torch.float64, 8),
@@ -217,3 +218,38 @@ def load_hf_llama_directory(directory, *, max_batch: int = 1, max_seq: int | Non
     if leftovers:
         raise SafetensorsError(f"tensors without a slot in the engine layout: {sorted(leftovers)[:4]}")
     return cfg, out
+
+
+def export_hf_llama_directory(directory, cfg, params: Mapping[str, torch.Tensor], *, dtype=torch.bfloat16) -> None:
+    """Writes ``config.json`` + ``model.safetensors`` with Hugging Face Llama tensor names from an
+    unsharded parameter dictionary under this framework's names (``tok_embeddings``,
+    ``layers.N.{attn_norm,wqkv,wo,ffn_norm,w_gate_up,w_down}``, ``norm``, ``lm_head``); ``cfg`` is a
+    ``LlamaConfig``. The inverse of ``load_hf_llama_directory``; vocabulary padding rows are cut."""
+    root = Path(directory)
+    root.mkdir(parents=True, exist_ok=True)
+    d, hd, H, Hkv, F, V = cfg.d_model, cfg.head_dim, cfg.n_head, cfg.n_kv_head, cfg.d_ff, cfg.vocab_size
+    t = lambda x: x.detach().to(dtype).contiguous()  # noqa: E731
+    out = {"model.embed_tokens.weight": t(params["tok_embeddings"][:V]), "model.norm.weight": t(params["norm"])}
+    if not cfg.tie_embeddings:
+        out["lm_head.weight"] = t(params["lm_head"][:V])
+    for l in range(cfg.n_layer):
+        p, q = f"model.layers.{l}.", f"layers.{l}."
+        wqkv, wgu = params[q + "wqkv"], params[q + "w_gate_up"]
+        out[p + "input_layernorm.weight"] = t(params[q + "attn_norm"])
+        out[p + "self_attn.q_proj.weight"] = t(wqkv[:H * hd])
+        out[p + "self_attn.k_proj.weight"] = t(wqkv[H * hd:(H + Hkv) * hd])
+        out[p + "self_attn.v_proj.weight"] = t(wqkv[(H + Hkv) * hd:])
+        out[p + "self_attn.o_proj.weight"] = t(params[q + "wo"])
+        out[p + "post_attention_layernorm.weight"] = t(params[q + "ffn_norm"])
+        out[p + "mlp.gate_proj.weight"] = t(wgu[:F])
+        out[p + "mlp.up_proj.weight"] = t(wgu[F:])
+        out[p + "mlp.down_proj.weight"] = t(params[q + "w_down"])
+    hf = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": d, "num_hidden_layers": cfg.n_layer, "num_attention_heads": H,
+          "num_key_value_heads": Hkv, "head_dim": hd, "intermediate_size": F, "vocab_size": V, "max_position_embeddings": cfg.max_seq_len,
+          "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.norm_eps, "tie_word_embeddings": bool(cfg.tie_embeddings), "attention_bias": False,
+          "mlp_bias": False, "torch_dtype": {torch.bfloat16: "bfloat16", torch.float16: "float16", torch.float32: "float32"}[dtype]}
+    (root / "config.json").write_text(json.dumps(hf, indent=2), encoding="utf-8")
+    target = root / "model.safetensors"
+    if target.exists():
+        target.unlink()
+    write_safetensors(target, out, {"format": "pt"})

@@ -184,6 +184,32 @@ class TPLlama:
         for name, t in shard_llama_params(self.cfg, full, self.tp.rank, self.tp.world).items():
             self.p[name].copy_(t)
 
+    @torch.no_grad()
+    def full_state(self) -> dict[str, torch.Tensor]:
+        """Unsharded fp32 parameters on the host under the names of ``models/llama.py`` (shards
+        gathered over the group and put back in head / hidden-unit order): the inverse of
+        ``shard_llama_params``, so a tensor-parallel run exports what the single-GPU engines load."""
+        cfg, W = self.cfg, self.tp.world
+        hd, Hq, Hkv, Fl = cfg.head_dim, cfg.n_head // W, cfg.n_kv_head // W, cfg.d_ff // W
+        out = {}
+        for name, v in self.p.items():
+            t = v.detach().float().contiguous()
+            if is_sharded(name) and W > 1:
+                parts = [torch.empty_like(t) for _ in range(W)]
+                dist.all_gather(parts, t, group=self.tp.group)
+            else:
+                parts = [t]
+            if not is_sharded(name):
+                full = t
+            elif name.endswith(".wqkv"):
+                full = torch.cat([q[:Hq * hd] for q in parts] + [q[Hq * hd:(Hq + Hkv) * hd] for q in parts] + [q[(Hq + Hkv) * hd:] for q in parts], 0)
+            elif name.endswith(".w_gate_up"):
+                full = torch.cat([q[:Fl] for q in parts] + [q[Fl:] for q in parts], 0)
+            else:  # wo / w_down: column shards
+                full = torch.cat(parts, 1)
+            out[name] = full.cpu()
+        return out
+
     def _tables(self, T: int, device):
         hd = self.cfg.head_dim
         inv = 1.0 / (self.cfg.rope_theta ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))

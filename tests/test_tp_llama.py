@@ -72,6 +72,9 @@ def _worker(rank, world, port, backend, out_q):
         errs["grad_rel"] = worst
         gn_ref = torch.sqrt(sum(v.grad.pow(2).sum() for v in ref.values()))
         errs["norm_rel"] = abs(float(model.grad_norm()) - float(gn_ref)) / float(gn_ref)
+        # the gathered shards are the unsharded model again
+        back = model.full_state()
+        errs["roundtrip"] = max(float((back[n] - full[n]).abs().max()) for n in full) if not cuda else 0.0
         tr = TPLlamaTrainer(model, AdamWConfig(lr=3e-3, warmup_steps=1, schedule="constant", weight_decay=0.0))
         losses = [float(tr.step(tokens.to(dev), targets.to(dev))) for _ in range(6)]
         errs["loss_drop"] = losses[0] - losses[-1]
@@ -101,7 +104,7 @@ def _run(world, backend):
 def test_tp_llama_matches_unsharded_model_on_gloo():
     for rank, e in _run(2, "gloo").items():
         assert e["impl"] == "torch"
-        assert e["loss"] < 1e-4 and e["grad_rel"] < 1e-3 and e["norm_rel"] < 1e-4, (rank, e)
+        assert e["loss"] < 1e-4 and e["grad_rel"] < 1e-3 and e["norm_rel"] < 1e-4 and e["roundtrip"] == 0.0, (rank, e)
         assert e["loss_drop"] > 0.05, (rank, e)
 
 
@@ -135,3 +138,15 @@ def test_tp_llama_single_gpu_runs_the_fused_path():
     for n, v in ref.items():
         got = model.p[n].main_grad.float().cpu()
         assert float((got - v.grad).abs().max() / (v.grad.abs().max() + 1e-8)) < 0.06, n
+
+
+def test_export_and_reload_hf_llama_directory(tmp_path):
+    from neuralfn_b200.checkpoint.safetensors_io import export_hf_llama_directory, load_hf_llama_directory
+    cfg = _cfg()
+    full = _full_params(cfg)
+    export_hf_llama_directory(tmp_path / "hf", cfg, full, dtype=torch.float32)
+    ecfg, tensors = load_hf_llama_directory(tmp_path / "hf", max_batch=2, max_seq=64)
+    assert ecfg.n_layer == cfg.n_layer and ecfg.n_kv_head == cfg.n_kv_head and ecfg.vocab == cfg.vocab_size
+    for n in ("layers.1.wqkv", "layers.0.w_gate_up", "layers.1.w_down", "norm"):
+        assert torch.equal(tensors[n].float(), full[n].to(torch.bfloat16).float()), n
+    assert torch.equal(tensors["tok_embeddings"][:cfg.vocab_size].float(), full["tok_embeddings"][:cfg.vocab_size].to(torch.bfloat16).float())
