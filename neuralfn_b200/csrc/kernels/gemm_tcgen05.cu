@@ -133,6 +133,10 @@ int try_launch_gemm_pair(const nfn_gemm_args& a, cudaStream_t stream);  // gemm_
 
 // CTA-pair (cta_group::2) kernel for eligible K-major products: -1 = read NFN_GEMM_PAIR once.
 static int g_pair_mode = -1;
+int try_launch_gemv(const nfn_gemm_args& a, cudaStream_t stream);  // gemv_bf16.cu
+static int g_gemv_mode = 1;
+static int gemv_mode() { return g_gemv_mode; }
+
 static bool pair_enabled() {
   if (g_pair_mode < 0) {
     const char* e = getenv("NFN_GEMM_PAIR");
@@ -142,6 +146,13 @@ static bool pair_enabled() {
 }
 
 }  // namespace nfn
+
+// 1 (default): products with at most four rows go to the streaming GEMV kernel; 0: always the tensor-core path.
+extern "C" int nfn_gemm_set_gemv_mode(int on) {
+  const int old = nfn::g_gemv_mode;
+  nfn::g_gemv_mode = on ? 1 : 0;
+  return old;
+}
 
 extern "C" int nfn_gemm_set_pair_mode(int on) {
   const int old = nfn::pair_enabled() ? 1 : 0;
@@ -169,6 +180,10 @@ extern "C" int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream_) {
       (!a.aux_out || (a.ld_aux_out & 7) || (reinterpret_cast<uintptr_t>(a.aux_out) & 15)))
     return fail(-1, "gemm: aux_out missing or misaligned");
 
+  if (a.m <= 4 && gemv_mode() != 0) {  // one to four rows: pure weight streaming (gemv_bf16.cu)
+    const int rc = try_launch_gemv(a, stream);
+    if (rc != 0) return rc < 0 ? rc : 0;
+  }
   const int sms = sm_count();
   const int tiles256 = ceil_div(a.m, BM) * ceil_div(a.n, 256);
   const bool wide = tiles256 >= sms && (a.n % 256 == 0 || a.n >= 1024);

@@ -121,3 +121,36 @@ def test_gemm_cta_pair(kernel_lib, m, n, k):
         _close(y, base + bias.float() + res.float(), k)
     finally:
         L.nfn_gemm_set_pair_mode(old)
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1000, 1032), (6144, 14336)])
+def test_gemv_small_m_with_epilogues(kernel_lib, m, n, k):
+    """Products with at most four rows take the weight-streaming GEMV kernel; same epilogue semantics
+    as the tensor-core path (checked against fp32 and against the GEMM path itself)."""
+    from neuralfn_b200.ops import _lib
+    from neuralfn_b200.ops.gemm import gemm
+    torch.manual_seed(m * 7 + n)
+    a = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+    bias = (torch.randn(n, device="cuda") * 0.1).bfloat16()
+    resid = torch.randn(m, n, device="cuda").bfloat16()
+    ref = a.float() @ w.float().t()
+    _close(gemm(a, w), ref, k)
+    out = gemm(a, w, bias=bias, act="gelu_tanh", resid=resid)
+    full = torch.nn.functional.gelu(ref + bias.float(), approximate="tanh") + resid.float()
+    _close(out, full, k)
+    acc = resid.clone()
+    gemm(a, w, out=acc, accum=True, alpha=0.5)
+    _close(acc, resid.float() + 0.5 * ref, k)
+    capped = gemm(a, w, act="tanh_cap", act_param=2.0)
+    _close(capped, 2.0 * torch.tanh(ref / 2.0), k)
+    # the tensor-core path gives the same numbers
+    L = _lib.load()
+    old = L.nfn_gemm_set_gemv_mode(0)
+    try:
+        tc = gemm(a, w, bias=bias, act="gelu_tanh", resid=resid)
+    finally:
+        L.nfn_gemm_set_gemv_mode(old)
+    torch.testing.assert_close(out.float(), tc.float(), atol=3e-2, rtol=3e-2)
+    _lib.assert_status_ok("gemv")
