@@ -161,6 +161,7 @@ class GenerationResult:
     speculative_rejected_tokens: int = 0
     speculative_target_rows: int = 0
     speculative_assistant_blocks: int = 0
+    compute_policy: dict | None = None   # inference_policy.compute_policy_payload of the generation
 
 
 # ------------------------------------------------------------------------------- proposers
@@ -591,7 +592,8 @@ class NativeInferenceSession:
                 on_event(ev)
             return stop or len(out) >= cfg.max_new_tokens
 
-        with self.model._lock:
+        from ..inference_policy import compute_policy_payload, inference_execution
+        with inference_execution(cfg.temperature, native_engine=True) as policy, self.model._lock:
             done = cfg.max_new_tokens == 0
             while not done:
                 if self._cancel.is_set():
@@ -612,7 +614,8 @@ class NativeInferenceSession:
             last = events[-1]
             events[-1] = GenerationEvent(last.token_id, last.index, last.position, last.text, finish, last.committed, last.kind)
         d = {k: self._stats[k] - before[k] for k in before if k.startswith("speculative")}
-        return GenerationResult(tuple(out), self.model.codec.decode(out), finish, prompt_tokens, len(out), tuple(events), finish == "cancelled", **d)
+        return GenerationResult(tuple(out), self.model.codec.decode(out), finish, prompt_tokens, len(out), tuple(events), finish == "cancelled", **d,
+                                compute_policy=compute_policy_payload(policy, backend="resident-engine-sm100a"))
 
     def _plain_step(self, cfg: GenerationConfig, emit, allowed_tokens) -> bool:
         """One token without speculation."""
