@@ -247,6 +247,28 @@ def cmd_dataset_info(a) -> int:
     return 0
 
 
+def cmd_compat_train(a) -> int:
+    from ..native_train import NativeTrainConfig, run_native_training, training_plan
+    from .compat import translate_llmc_args
+    rest = [x for x in a.rest if x != "--"]
+    kw, notes = translate_llmc_args(rest)
+    cfg = NativeTrainConfig(**kw)
+    if a.print_plan:
+        print(json.dumps({"status": "plan", **notes, **training_plan(cfg, 1)}, indent=2))
+        return 0
+    report = run_native_training(cfg)
+    print(json.dumps({**report, **notes}, default=str))
+    return 0
+
+
+def cmd_migrate_native(a) -> int:
+    from ..native_ir import migrate_graph_to_native
+    man = migrate_graph_to_native(a.graph, a.out_dir, model_name=a.name or None, stop_token_ids=[int(x) for x in a.stop_tokens.split(",") if x])
+    print(json.dumps({"status": "ok", "out_dir": a.out_dir, "model": man["model"], "capabilities": man["capabilities"],
+                      "tensor_bytes": man["tensors"]["total_bytes"]}, indent=2))
+    return 0
+
+
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="nfn", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="command", required=True)
@@ -284,6 +306,16 @@ def build_parser() -> argparse.ArgumentParser:
     sub.add_parser("native-info").set_defaults(fn=cmd_native_info)
     sub.add_parser("kernels", help="kernel catalogue and coverage of the built library").set_defaults(fn=cmd_kernels)
     sub.add_parser("families", help="model families, their execution routes and capability proofs").set_defaults(fn=cmd_families)
+    ct = sub.add_parser("compat-train", help="run a train_gpt2cu (llm.c) command line: nfn compat-train -- -i data -o out -e d12 -b 64 -t 1024")
+    ct.add_argument("--print-plan", action="store_true")
+    ct.add_argument("rest", nargs=argparse.REMAINDER)
+    ct.set_defaults(fn=cmd_compat_train)
+    mg = sub.add_parser("migrate-native", help="lower a graph JSON file into a native execution manifest + raw tensor bundle")
+    mg.add_argument("graph")
+    mg.add_argument("out_dir")
+    mg.add_argument("--name", default="")
+    mg.add_argument("--stop-tokens", default="")
+    mg.set_defaults(fn=cmd_migrate_native)
     d = sub.add_parser("dataset-info")
     d.add_argument("path")
     d.add_argument("--seq-len", type=int, default=1024)

@@ -82,3 +82,33 @@ def test_gpu_picker_prefers_idle_devices(monkeypatch):
     assert pick_dedicated_gpu(g, min_free_mib=10 ** 9) is None
     monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "0,2")
     assert pick_dedicated_gpu(g) == 2
+
+
+def test_compat_launcher_translates_llmc_flags(capsys):
+    from neuralfn_b200.cli import nfn
+    from neuralfn_b200.cli.compat import translate_llmc_args
+    kw, notes = translate_llmc_args(["-i", "data/fineweb/train_*.bin", "-j", "data/fineweb/val_*.bin", "-o", "out", "-e", "d24", "-b", "32", "-t", "2048",
+                                     "-d", "524288", "-l", "0.0003", "-u", "700", "-q", "0.1", "-c", "0.1", "-x", "100", "-z", "1", "-r", "0", "-k", "cosine"])
+    assert (kw["n_layer"], kw["n_head"], kw["d_model"]) == (24, 16, 1024) and kw["dataset"] == "data/fineweb" and kw["batch_size"] == 32
+    assert kw["seq_len"] == 2048 and kw["warmup_steps"] == 700 and kw["final_lr_fraction"] == 0.1 and kw["max_steps"] == 100
+    assert set(notes["ignored"]) == {"-z", "-r", "val_pattern"}
+    import pytest
+    with pytest.raises(ValueError):
+        translate_llmc_args(["-e", "gpt2_124M.bin"])
+    with pytest.raises(ValueError):
+        translate_llmc_args(["--bogus", "1"])
+    assert nfn.main(["compat-train", "--print-plan", "--", "-e", "d12", "-b", "16", "-t", "1024", "-d", "524288"]) == 0
+    plan = json.loads(capsys.readouterr().out)
+    assert plan["status"] == "plan" and plan["grad_accum_steps"] == 32
+
+
+def test_migrate_native_cli(tmp_path, capsys):
+    from neuralfn_b200.cli import nfn
+    from neuralfn_b200.presets import build_preset
+    from neuralfn_b200.serialization import save_graph
+    from neuralfn_b200.torch_templates import build_gpt_root_graph
+    g = build_gpt_root_graph(build_preset("gpt2", vocab_size=64, num_layers=1, model_dim=32, num_heads=2))
+    save_graph(g, tmp_path / "g.json")
+    assert nfn.main(["migrate-native", str(tmp_path / "g.json"), str(tmp_path / "out"), "--name", "gpt2", "--stop-tokens", "1,2"]) == 0
+    out = json.loads(capsys.readouterr().out)
+    assert out["status"] == "ok" and out["model"]["family"] in ("gpt", "gpt2") and (tmp_path / "out" / "tensors.bin").is_file()
