@@ -20,7 +20,7 @@ import sys
 
 
 def _add_train_flags(p: argparse.ArgumentParser) -> None:
-    p.add_argument("--base-model", default="gpt", help="gpt | gpt2 | gpt3 | nanogpt | llama")
+    p.add_argument("--base-model", default="gpt", help="gpt | gpt2 | gpt3 | nanogpt | llama | embedding")
     p.add_argument("--template-name", default="gpt2")
     p.add_argument("--dataset", default="", help="dataset alias, directory or shard file (empty: synthetic uniform tokens)")
     p.add_argument("--output-dir", default="")
@@ -54,6 +54,13 @@ def _add_train_flags(p: argparse.ArgumentParser) -> None:
     p.add_argument("--no-cuda-graph", action="store_true")
     p.add_argument("--gpus", type=int, default=0, help="launch this many ranks on this node (0: stay in this process)")
     p.add_argument("--print-plan", "--dry-run", dest="print_plan", action="store_true")
+    p.add_argument("--embedding-dataset", action="append", default=[], help="--base-model embedding: text file, one text per line (repeatable)")
+    p.add_argument("--embedding-hidden-dim", type=int, default=128)
+    p.add_argument("--embedding-output-dim", type=int, default=128)
+    p.add_argument("--embedding-layers", type=int, default=2)
+    p.add_argument("--embedding-heads", type=int, default=4)
+    p.add_argument("--embedding-max-tokens", type=int, default=128)
+    p.add_argument("--embedding-pooling", choices=["mean", "cls"], default="mean")
     p.add_argument("--parallel", choices=["dp", "tp", "ep"], default="dp",
                    help="dp: data parallel dense engines (default); tp: tensor-parallel Llama over --gpus ranks; ep: expert-parallel MoE Llama")
     p.add_argument("--tp-model", default="tiny", help="--parallel tp: llama3_8b | llama_1b | tiny")
@@ -87,7 +94,46 @@ def _parallel_train_argv(a) -> list[str]:
                    "--vocab-size", str(a.vocab_size), "--experts", str(a.experts), "--top-k", str(a.top_k_experts), "--expert-hidden", str(a.expert_hidden)]
 
 
+def cmd_train_embedding(a) -> int:
+    import torch
+    from ..embedding import EmbeddingConfig, EmbeddingEncoder, EmbeddingTrainer, read_corpus, save_embedding_model
+    if not a.embedding_dataset:
+        raise ValueError("--base-model embedding needs at least one --embedding-dataset FILE")
+    corpus = read_corpus(a.embedding_dataset)
+    torch.manual_seed(a.seed)
+    cfg = EmbeddingConfig(hidden_dim=a.embedding_hidden_dim, output_dim=a.embedding_output_dim, num_layers=a.embedding_layers,
+                          num_heads=a.embedding_heads, max_tokens=a.embedding_max_tokens, pooling=a.embedding_pooling)
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    model = EmbeddingEncoder(cfg).to(dev)
+    lr = a.learning_rate if a.learning_rate != 6e-4 else 1e-3
+    trainer = EmbeddingTrainer(model, learning_rate=lr, weight_decay=a.weight_decay, warmup_steps=min(a.warmup_steps, max(1, a.max_steps // 10)),
+                               max_steps=a.max_steps, grad_clip=a.max_grad_norm, seed=a.seed)
+
+    def on_step(step, rec):
+        if a.progress_every and step % a.progress_every == 0:
+            print(json.dumps({"event": "train_step", "step": step, "loss": rec["total"], "mlm": rec["mlm"], "contrastive": rec["contrastive"]}), flush=True)
+
+    hist = trainer.train(corpus, batch_size=a.batch_size, on_step=on_step)
+    out = a.output_dir or "artifacts/embedding"
+    save_embedding_model(model, out, trainer)
+    print(json.dumps({"event": "complete", "status": "ok", "steps": len(hist), "first_loss": hist[0]["total"], "final_loss": hist[-1]["total"],
+                      "texts": len(corpus), "output_dir": out}))
+    return 0
+
+
+def cmd_embed(a) -> int:
+    from ..embedding import load_embedding_model, read_corpus
+    if (a.text is None) == (a.input is None):
+        raise ValueError("nfn embed needs exactly one of --text or --input")
+    texts = [a.text] if a.text is not None else read_corpus([a.input])
+    vecs = load_embedding_model(a.checkpoint).embed(texts)
+    print(json.dumps({"dim": int(vecs.shape[1]), "embeddings": [[round(float(x), 6) for x in v] for v in vecs]}))
+    return 0
+
+
 def cmd_train(a) -> int:
+    if a.base_model == "embedding":
+        return cmd_train_embedding(a)
     if a.parallel in ("tp", "ep"):
         # the model-parallel families have their own driver; one process per GPU
         argv = _parallel_train_argv(a)
@@ -306,6 +352,11 @@ def build_parser() -> argparse.ArgumentParser:
     sub.add_parser("native-info").set_defaults(fn=cmd_native_info)
     sub.add_parser("kernels", help="kernel catalogue and coverage of the built library").set_defaults(fn=cmd_kernels)
     sub.add_parser("families", help="model families, their execution routes and capability proofs").set_defaults(fn=cmd_families)
+    em = sub.add_parser("embed", help="unit-length text vectors from an embedding model directory")
+    em.add_argument("--checkpoint", required=True)
+    em.add_argument("--text", default=None)
+    em.add_argument("--input", default=None, help="file with one text per line")
+    em.set_defaults(fn=cmd_embed)
     ct = sub.add_parser("compat-train", help="run a train_gpt2cu (llm.c) command line: nfn compat-train -- -i data -o out -e d12 -b 64 -t 1024")
     ct.add_argument("--print-plan", action="store_true")
     ct.add_argument("rest", nargs=argparse.REMAINDER)

@@ -13,6 +13,10 @@ extern "C" {
 const char* nfn_rt_last_error(void);
 int nfn_rt_sha256_file(const char* path, char* out65);
 int nfn_rt_sha256(const void* data, uint64_t bytes, char* out65);
+// shipped preset catalogue compiled into the runtime (shipped_presets.h)
+int nfn_rt_preset_count(void);
+const char* nfn_rt_preset_name(int index);
+const char* nfn_rt_preset_family(const char* name);
 
 // ---- token / byte shard datasets -------------------------------------------------------
 // On-disk formats (compatible with the reference's token_shards.cpp:48-59,151-200):

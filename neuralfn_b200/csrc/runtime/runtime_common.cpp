@@ -270,3 +270,21 @@ extern "C" int nfn_rt_sha256(const void* data, std::uint64_t bytes, char* out65)
     return 0;
   });
 }
+
+// ---- shipped preset catalogue (generated header) --------------------------------------------------
+#include "shipped_presets.h"
+
+extern "C" int nfn_rt_preset_count(void) { return nfn_rt::kShippedPresetCount; }
+
+// Name of preset `index` (nullptr when out of range).
+extern "C" const char* nfn_rt_preset_name(int index) {
+  return index >= 0 && index < nfn_rt::kShippedPresetCount ? nfn_rt::kShippedPresets[index].name : nullptr;
+}
+
+// Family a shipped preset trains under, or nullptr for an unknown name.
+extern "C" const char* nfn_rt_preset_family(const char* name) {
+  if (!name) return nullptr;
+  for (const auto& p : nfn_rt::kShippedPresets)
+    if (std::strcmp(p.name, name) == 0) return p.family;
+  return nullptr;
+}

@@ -23,6 +23,9 @@ def lib() -> C.CDLL:
         "nfn_rt_last_error": (cp, []),
         "nfn_rt_sha256_file": (i32, [cp, C.c_char_p]),
         "nfn_rt_sha256": (i32, [vp, u64, C.c_char_p]),
+        "nfn_rt_preset_count": (i32, []),
+        "nfn_rt_preset_name": (cp, [i32]),
+        "nfn_rt_preset_family": (cp, [cp]),
         "nfn_dataset_open": (vp, [cp, i32, i32, i32]),
         "nfn_dataset_close": (None, [vp]),
         "nfn_dataset_json": (i32, [vp, i64, i64, i64, C.c_char_p, i32]),
@@ -84,6 +87,13 @@ def read_json(fn, *args) -> dict:
     buf = C.create_string_buffer(need + 1)
     check(fn(*args, buf, need + 1), "json")
     return json.loads(buf.value.decode())
+
+
+def shipped_presets() -> dict[str, str]:
+    """Preset name -> family, as compiled into the host runtime."""
+    L = lib()
+    names = [L.nfn_rt_preset_name(i).decode() for i in range(L.nfn_rt_preset_count())]
+    return {n: L.nfn_rt_preset_family(n.encode()).decode() for n in names}
 
 
 def sha256_file(path: str) -> str:

@@ -20,7 +20,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
-__all__ = ["NativeTrainerSpec", "NativeCapabilityProof", "NATIVE_FAMILIES", "resolve_family", "classify_native_model", "capability_proof_for",
+__all__ = ["shipped_preset_header", "NativeTrainerSpec", "NativeCapabilityProof", "NATIVE_FAMILIES", "resolve_family", "classify_native_model", "capability_proof_for",
            "native_families_report"]
 
 
@@ -128,3 +128,23 @@ def native_families_report() -> list[dict]:
     return [{"family": s.family, "aliases": list(s.aliases), "reference_binary": s.reference_binary, "route": s.route, "presets": list(s.presets),
              "resident_inference": s.resident_inference, "parallel": list(s.parallel), "checkpoint_formats": list(s.checkpoint_formats)}
             for s in NATIVE_FAMILIES.values()]
+
+
+def shipped_preset_header() -> str:
+    """C header with the shipped preset names and the family each one trains under, compiled into
+    the host runtime (``nfn_rt_preset_family``) so native tools can validate a template name
+    without Python. ``csrc/runtime/shipped_presets.h`` is this text; a test keeps the two equal.
+    Reference counterpart: ``csrc/native_train/shipped_gpt_template_presets.h`` and its generator."""
+    from .presets import SHIPPED_GPT_TEMPLATE_PRESETS
+    rows = []
+    for name in SHIPPED_GPT_TEMPLATE_PRESETS:
+        try:
+            family = classify_native_model(name)[0].family
+        except KeyError:
+            family = "tensor-runtime"
+        rows.append(f'    {{"{name}", "{family}"}},')
+    body = "\n".join(rows)
+    return ("// Generated by neuralfn_b200.native_registry.shipped_preset_header(); do not edit by hand.\n"
+            "#pragma once\n\nnamespace nfn_rt {\n\nstruct ShippedPreset {\n  const char* name;\n  const char* family;\n};\n\n"
+            f"constexpr int kShippedPresetCount = {len(rows)};\n"
+            "constexpr ShippedPreset kShippedPresets[kShippedPresetCount] = {\n" + body + "\n};\n\n}  // namespace nfn_rt\n")

@@ -70,3 +70,17 @@ def test_family_checkpoint_round_trip_and_fail_closed(tmp_path):
     (out / "checkpoint.json").write_text(json.dumps(d))
     with pytest.raises(FamilyCheckpointError):
         inspect_family_llama_checkpoint(out)
+
+
+def test_shipped_preset_header_matches_generator_and_runtime():
+    from pathlib import Path
+
+    import neuralfn_b200
+    from neuralfn_b200.data import _rt
+    from neuralfn_b200.native_registry import shipped_preset_header
+    from neuralfn_b200.presets import SHIPPED_GPT_TEMPLATE_PRESETS
+    header = Path(neuralfn_b200.__file__).parent / "csrc" / "runtime" / "shipped_presets.h"
+    assert header.read_text() == shipped_preset_header(), "regenerate csrc/runtime/shipped_presets.h"
+    compiled = _rt.shipped_presets()
+    assert list(compiled) == list(SHIPPED_GPT_TEMPLATE_PRESETS) and compiled["gpt2"] == "gpt" and compiled["llama"] == "llama"
+    assert _rt.lib().nfn_rt_preset_family(b"no_such_preset") is None
