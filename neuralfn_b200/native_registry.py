@@ -30,7 +30,7 @@ class NativeTrainerSpec:
     aliases: tuple[str, ...]
     reference_binary: str
     presets: tuple[str, ...]
-    route: str                      # native-gpt | native-llama | tensor-runtime
+    route: str                      # native-gpt | native-llama | native-moe | tensor-runtime
     resident_inference: bool = False
     parallel: tuple[str, ...] = ()
     checkpoint_formats: tuple[str, ...] = ()
@@ -65,9 +65,10 @@ NATIVE_FAMILIES: dict[str, NativeTrainerSpec] = {s.family: s for s in (
     _spec("gpt", ("gpt2", "gpt3", "nanogpt"), _GPT_PRESETS, "native-gpt", resident_inference=True, parallel=("dp", "tp"),
           checkpoint_formats=("dense-v5", "named-tensors")),
     _spec("gpt2-evo", (), ("gpt2_evo",)),
-    _spec("llama", (), _LLAMA_PRESETS, "native-llama", resident_inference=True, parallel=("dp", "pp"),
-          checkpoint_formats=("named-tensors", "family-llama-f32", "gguf")),
-    _spec("mixllama", ("moe",), ("mixllama", "mixllama_fast", "moe", "moe_modern", "deepseek_v3"), parallel=("ep",)),
+    _spec("llama", (), _LLAMA_PRESETS, "native-llama", resident_inference=True, parallel=("dp", "pp", "tp"),
+          checkpoint_formats=("named-tensors", "family-llama-f32", "gguf", "parallel-safetensors", "hf-llama-directory")),
+    _spec("mixllama", ("moe",), ("mixllama", "mixllama_fast", "moe", "moe_modern", "deepseek_v3"), "native-moe", parallel=("dp", "ep"),
+          checkpoint_formats=("parallel-safetensors",)),
     _spec("muse-glimmer", ("glimmer",), ("muse_glimmer",), resident_inference=True, checkpoint_formats=("named-tensors", "gguf")),
     _spec("deepseek-v4", (), ("deepseek_v4",)), _spec("jepa", (), ("jepa",)), _spec("semantic-dense-jepa", (), ("semantic_dense_jepa",)),
     _spec("moe-jepa-evo", (), ("moe_jepa_evo",)), _spec("semantic-router-moe", (), ("semantic_router_moe",)), _spec("jamba", (), ("jamba",)),
@@ -78,6 +79,9 @@ NATIVE_FAMILIES: dict[str, NativeTrainerSpec] = {s.family: s for s in (
 # presets whose block differs from what the explicit native engines implement: they train through the tensor runtime
 _NATIVE_GPT_OK = {"gpt2", "gpt2_qknorm", "gpt2_softcap", "gpt2_stable", "gpt2_zloss", "nanogpt"}
 _NATIVE_LLAMA_OK = {"llama", "llama_fast", "llama_fast_1b", "llama_modern"}
+# the expert-parallel MoE Llama (parallel/moe_llama.py) covers the plain routed-SwiGLU block: softmax / sigmoid /
+# sqrt-softplus top-k routing, density balance loss, router z-loss; shared experts and aux-free biasing go through the tensor runtime
+_NATIVE_MOE_OK = {"moe", "mixllama", "mixllama_fast"}
 
 
 def _norm(name: str) -> str:
@@ -115,7 +119,10 @@ def capability_proof_for(name: str) -> NativeCapabilityProof:
     if route == "native-llama" and preset is not None and preset not in _NATIVE_LLAMA_OK:
         route = "tensor-runtime"
         reasons.append(f"preset {preset} uses blocks outside the explicit Llama engine")
-    native_training = route in ("native-gpt", "native-llama")
+    if route == "native-moe" and preset is not None and preset not in _NATIVE_MOE_OK:
+        route = "tensor-runtime"
+        reasons.append(f"preset {preset} uses blocks outside the expert-parallel MoE Llama (shared experts, aux-free balancing, MLA)")
+    native_training = route in ("native-gpt", "native-llama", "native-moe")
     if not native_training and not reasons:
         reasons.append("the family trains through the graph compiler and TorchTrainer; its hot stages call the kernel library")
     if not spec.resident_inference:
