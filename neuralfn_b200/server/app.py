@@ -89,6 +89,26 @@ def create_app(store: LiveStateStore | None = None, engine=None, db=None):
         from ..ops import _lib
         return {"status": "ok", "auth_required": bool(token) or db is not None, "accounts": db is not None, "kernel_library": _lib.available(), "sessions": len(store.sessions)}
 
+    @app.get("/", include_in_schema=False)
+    @app.get("/editor", include_in_schema=False)
+    def editor():
+        """The single-page graph editor (vanilla JS over this API; the reference ships a React editor)."""
+        from pathlib import Path
+
+        from fastapi.responses import HTMLResponse
+        return HTMLResponse((Path(__file__).with_name("editor.html")).read_text(encoding="utf-8"))
+
+    @app.get("/api/builtins", dependencies=[Depends(auth)])
+    def builtins() -> list[str]:
+        from ..builtins import BUILTIN_MAP
+        from ..scalar_builtins import SPEC_BY_NAME
+        return sorted(set(BUILTIN_MAP) | set(SPEC_BY_NAME))
+
+    @app.delete("/api/sessions/{sid}/nodes/{node_id}", dependencies=[Depends(auth)])
+    def remove_node(sid: str, node_id: str) -> dict:
+        guard(store.remove_node, sid, node_id)
+        return {"deleted": node_id}
+
     @app.get("/api/sessions", dependencies=[Depends(auth)])
     def sessions() -> list[dict]:
         return store.list_sessions()

@@ -119,6 +119,8 @@ class LiveStateStore:
 
     def remove_node(self, sid: str, node_id: str) -> None:
         with self._lock:
+            if node_id not in self.graph(sid).nodes:
+                raise KeyError(f"unknown node {node_id!r}")
             self.graph(sid).remove_node(node_id)
             self._snapshot(sid)
 

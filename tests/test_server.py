@@ -128,3 +128,24 @@ def test_mcp_edit_tools_nodes_edges_variants_settings():
         call("swap_node_variant", {"session_id": outer, "node_id": n, "family": "blocks", "version": "v9"})
     tpl = call("load_gpt_template", {"session_id": outer, "preset": "nanogpt", "config": {"vocab_size": 64, "num_layers": 1, "model_dim": 32, "num_heads": 2}})
     assert tpl["runtime"] == "torch" and tpl["nodes"] > 3
+
+
+def test_editor_page_and_the_routes_it_uses():
+    pytest.importorskip("fastapi")
+    from fastapi.testclient import TestClient
+
+    from neuralfn_b200.server.app import create_app
+    c = TestClient(create_app())
+    page = c.get("/")
+    assert page.status_code == 200 and "text/html" in page.headers["content-type"] and 'id="canvas"' in page.text and "/api/sessions" in page.text
+    names = c.get("/api/builtins").json()
+    assert "sigmoid" in names and "input" in names
+    sid = c.post("/api/sessions", json={"name": "ui"}).json()["session_id"]
+    a = c.post(f"/api/sessions/{sid}/nodes", json={"builtin": "input", "role": "input"}).json()["node_id"]
+    b = c.post(f"/api/sessions/{sid}/nodes", json={"builtin": "sigmoid", "role": "output"}).json()["node_id"]
+    c.post(f"/api/sessions/{sid}/edges", json={"src_node": a, "dst_node": b})
+    g = c.get(f"/api/sessions/{sid}/graph").json()
+    assert set(g["nodes"]) == {a, b} and len(g["edges"]) == 1 and g["input_node_ids"] == [a]
+    assert c.delete(f"/api/sessions/{sid}/nodes/{b}").status_code == 200
+    assert set(c.get(f"/api/sessions/{sid}/graph").json()["nodes"]) == {a}
+    assert c.delete(f"/api/sessions/{sid}/nodes/nope").status_code == 404
