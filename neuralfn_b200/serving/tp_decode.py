@@ -82,6 +82,8 @@ class TPLlamaDecoder:
         self.x = torch.zeros(max_batch, C, dtype=self.dtype, device=dev)        # residual stream of the decode step
         self.tokens = torch.zeros(max_batch, dtype=torch.int64, device=dev)
         self.last_logits: torch.Tensor | None = None
+        self.sampling: tuple | None = None   # (temperature, top_k, top_p, seed); None = greedy
+        self._draws = 0
         self.use_graph = bool(use_graph and self.cuda)
         self._graph = None
         self._fused_calls_per_step = 2 * cfg.n_layer
@@ -164,6 +166,8 @@ class TPLlamaDecoder:
         off, W = self.tp.rank * self.Vl, self.tp.world
         if self.tp.rank == W - 1 and self.cfg.padded_vocab != self.cfg.vocab_size:
             logits[:, self.cfg.vocab_size - off:] = -30000.0
+        if self.sampling is not None:
+            return self._sample(logits)
         val, idx = logits.float().max(-1)
         idx = idx + off
         if W == 1:
@@ -174,6 +178,47 @@ class TPLlamaDecoder:
             allc.copy_(torch.stack(self._gather_list(mine)))
         best = allc[..., 0].argmax(0)  # the first (lowest-rank) maximum wins, as torch.argmax over the full row would pick
         return allc[..., 1].gather(0, best[None]).squeeze(0).long()
+
+    def set_sampling(self, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> None:
+        """``temperature == 0`` selects greedy decoding (the default). With sampling every rank gathers
+        the full logit rows and draws with the same counter-based generator, so all ranks pick the
+        same token without exchanging it. A captured decode graph is dropped and captured again."""
+        self.sampling = None if temperature <= 0 else (float(temperature), int(top_k), float(top_p), int(seed))
+        self._graph = None
+        self._draws = 0
+        if self.cuda:
+            self._draw_ctr = torch.zeros(1, dtype=torch.int64, device=self.dev)
+
+    def _sample(self, logits: torch.Tensor) -> torch.Tensor:
+        temperature, top_k, top_p, seed = self.sampling
+        W, B = self.tp.world, logits.shape[0]
+        if W > 1:
+            allg = torch.empty(W, B, self.Vl, dtype=logits.dtype, device=logits.device)
+            if self.cuda:
+                dist.all_gather_into_tensor(allg, logits.contiguous(), group=self.tp.group)
+            else:
+                allg.copy_(torch.stack(self._gather_list(logits.contiguous())))
+            full = allg.permute(1, 0, 2).reshape(B, W * self.Vl).contiguous()
+        else:
+            full = logits
+        if self.cuda:
+            from ..ops.infer import sample_rows
+            tok = sample_rows(full, temperature=temperature, top_k=top_k, top_p=top_p, seed=seed, offset_dev=self._draw_ctr).long()
+            self._draw_ctr += 1  # a device-side counter, so replays of a captured step draw fresh numbers
+            return tok
+        z = full.float() / temperature
+        if top_k > 0:
+            kth = z.topk(min(top_k, z.shape[-1]), -1).values[:, -1:]
+            z = z.masked_fill(z < kth, float("-inf"))
+        p = z.softmax(-1)
+        if top_p < 1.0:
+            sp, si = p.sort(-1, descending=True)
+            keep = sp.cumsum(-1) - sp < top_p
+            p = torch.zeros_like(p).scatter(-1, si, sp * keep)
+            p = p / p.sum(-1, keepdim=True)
+        gen = torch.Generator().manual_seed(seed * 1000003 + self._draws)
+        self._draws += 1
+        return torch.multinomial(p, 1, generator=gen).squeeze(-1)
 
     def _gather_list(self, t: torch.Tensor) -> list[torch.Tensor]:
         parts = [torch.empty_like(t) for _ in range(self.tp.world)]

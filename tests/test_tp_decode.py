@@ -59,11 +59,15 @@ def _worker(rank, world, port, backend, use_graph, out_q):
             gap = last.max(-1).values - last.gather(-1, got[:, i:i + 1]).squeeze(-1)
             bad += int((gap > (0.0 if not cuda else 0.08)).sum())
             seq = torch.cat([seq, got[:, i:i + 1]], 1)
+        # sampling: every rank draws the same tokens without exchanging them
+        dec.set_sampling(temperature=0.9, top_k=20, top_p=0.95, seed=11)
+        sampled = dec.generate(prompt.to(dev), 6).cpu()
         status = 0
         if cuda:
             from neuralfn_b200.ops import _lib
             status = _lib.status_read_reset()
-        out_q.put((rank, {"bad": bad, "tokens": got.tolist(), "status": status, "impl": dec.tp.impl, "max_token": int(got.max())}))
+        out_q.put((rank, {"bad": bad, "tokens": got.tolist(), "status": status, "impl": dec.tp.impl, "max_token": int(got.max()),
+                          "sampled": sampled.tolist()}))
     finally:
         dist.destroy_process_group()
 
@@ -84,7 +88,8 @@ def _run(world, backend, use_graph=False):
 
 def test_tp_decoder_matches_reference_on_gloo():
     res = _run(2, "gloo")
-    assert res[0]["tokens"] == res[1]["tokens"]
+    assert res[0]["tokens"] == res[1]["tokens"] and res[0]["sampled"] == res[1]["sampled"]
+    assert res[0]["sampled"] != res[0]["tokens"][:6] and max(max(r) for r in res[0]["sampled"]) < 500
     for e in res.values():
         assert e["bad"] == 0 and e["max_token"] < 500, e
 
@@ -95,7 +100,7 @@ def test_tp_decoder_on_two_gpus(use_graph):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     res = _run(2, "nccl", use_graph)
-    assert res[0]["tokens"] == res[1]["tokens"]
+    assert res[0]["tokens"] == res[1]["tokens"] and res[0]["sampled"] == res[1]["sampled"]
     for e in res.values():
         assert e["impl"] == "fused" and e["status"] == 0 and e["bad"] == 0, e
 
