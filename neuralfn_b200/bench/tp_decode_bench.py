@@ -77,6 +77,7 @@ def main(argv=None) -> int:
                           "warmup": a.warmup, "graph": not a.no_graph, "impl": a.impl, "dtype": "bf16", "data": "synthetic",
                           "hbm_gbs_per_gpu": round((per_rank_weight_bytes + kv_bytes) / (ms / 1e3) / 1e9, 1), "device_status": status,
                           "config": {"model": a.model, "layers": cfg.n_layer, "parallelism": f"tp{world}"}}), flush=True)
+    dec.close()
     if world > 1:
         dist.destroy_process_group()
     return 0

@@ -86,7 +86,7 @@ class TPLlamaDecoder:
         self._draws = 0
         self.use_graph = bool(use_graph and self.cuda)
         self._graph = None
-        self._fused_calls_per_step = 2 * cfg.n_layer
+        self._fused_calls_per_step = 2 * cfg.n_layer + (1 if W > 1 else 0)  # two per layer + the candidate exchange
         if self.cuda:
             from ..ops.infer import DecodeAttentionWorkspace
             self._ws = DecodeAttentionWorkspace(max_batch, self.Hq, self.Hkv, hd, dev)
@@ -172,11 +172,26 @@ class TPLlamaDecoder:
         idx = idx + off
         if W == 1:
             return idx
+        if self.tp.impl == "fused":
+            # Exchange the candidates through the fused all-reduce kernel (no NCCL call, so the step
+            # stays capturable and free of library collectives): every rank fills its own four
+            # columns of a zero [B, 4 W] row - the value (already a bf16 number) and the index as
+            # three base-128 digits, each exact in bf16 - and the sum over ranks is the gather.
+            cols = max(8, 4 * W)
+            cand, sym = self.tp.partial_buffer(logits.shape[0], cols)
+            cand.zero_()
+            mine = torch.stack([val, (idx % 128).float(), ((idx // 128) % 128).float(), (idx // 16384).float()], -1)
+            cand[:, 4 * self.tp.rank:4 * self.tp.rank + 4] = mine.to(cand.dtype)
+            allc = self.tp.allreduce_resid_norm(cand, sym)[:, :4 * W].float().view(-1, W, 4)
+            vals = allc[..., 0]
+            ids = allc[..., 1] + 128.0 * allc[..., 2] + 16384.0 * allc[..., 3]
+            best = vals.argmax(1, keepdim=True)  # the first (lowest-rank) maximum wins, as an arg-max over the full row would pick
+            return ids.gather(1, best).squeeze(1).long()
         mine = torch.stack([val, idx.float()], -1).contiguous()  # indices below 2^24 are exact in fp32
         allc = torch.empty(W, *mine.shape, dtype=mine.dtype, device=mine.device)
         dist.all_gather_into_tensor(allc, mine, group=self.tp.group) if self.cuda else \
             allc.copy_(torch.stack(self._gather_list(mine)))
-        best = allc[..., 0].argmax(0)  # the first (lowest-rank) maximum wins, as torch.argmax over the full row would pick
+        best = allc[..., 0].argmax(0)
         return allc[..., 1].gather(0, best[None]).squeeze(0).long()
 
     def set_sampling(self, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> None:
@@ -304,7 +319,7 @@ class TPLlamaDecoder:
     @torch.no_grad()
     def step(self) -> torch.Tensor:
         """One decode step for all rows; returns the new tokens [B]."""
-        if not self.use_graph:
+        if not self.use_graph or self.sampling is not None:  # sampling gathers logits with NCCL: kept out of graphs
             self._step_body()
             return self.tokens.clone()
         if self._graph is None:
@@ -339,6 +354,12 @@ class TPLlamaDecoder:
         for dst, src in zip(self.v_cache, saved[4]):
             dst.copy_(src)
         self._graph = g
+
+    def close(self) -> None:
+        """Drops the captured graph (call before tearing the process group down)."""
+        self._graph = None
+        if self.cuda:
+            torch.cuda.synchronize(self.dev)
 
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, max_new_tokens: int) -> torch.Tensor:

@@ -66,6 +66,7 @@ def _worker(rank, world, port, backend, use_graph, out_q):
         if cuda:
             from neuralfn_b200.ops import _lib
             status = _lib.status_read_reset()
+        dec.close()
         out_q.put((rank, {"bad": bad, "tokens": got.tolist(), "status": status, "impl": dec.tp.impl, "max_token": int(got.max()),
                           "sampled": sampled.tolist()}))
     finally:
