@@ -147,7 +147,7 @@ static bool pair_enabled() {
 
 }  // namespace nfn
 
-// 1 (default): products with at most four rows go to the streaming GEMV kernel; 0: always the tensor-core path.
+// 1 (default): products with at most two rows go to the streaming GEMV kernel; 0: always the tensor-core path.
 extern "C" int nfn_gemm_set_gemv_mode(int on) {
   const int old = nfn::g_gemv_mode;
   nfn::g_gemv_mode = on ? 1 : 0;
@@ -180,7 +180,7 @@ extern "C" int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream_) {
       (!a.aux_out || (a.ld_aux_out & 7) || (reinterpret_cast<uintptr_t>(a.aux_out) & 15)))
     return fail(-1, "gemm: aux_out missing or misaligned");
 
-  if (a.m <= 4 && gemv_mode() != 0) {  // one to four rows: pure weight streaming (gemv_bf16.cu)
+  if (a.m <= 2 && gemv_mode() != 0) {  // one or two rows: pure weight streaming (gemv_bf16.cu)
     const int rc = try_launch_gemv(a, stream);
     if (rc != 0) return rc < 0 ? rc : 0;
   }
