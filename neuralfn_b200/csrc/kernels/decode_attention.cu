@@ -407,22 +407,17 @@ decode_attention_mma_kernel(const DecodeParams p) {
   __nv_bfloat16* sm_kn = sm_q + 16 * HD;                      // [HD] new k (rotated), then [HD] new v
   __nv_bfloat16* sm_vn = sm_kn + HD;
   __shared__ int sh_last;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r = lane >> 2, j = lane & 3;
-  const int group = p.Hq / p.Hkv;
-  const int units_y = p.Hkv * p.gtiles, items = p.B * units_y * p.splits;
 
-  // A CTA walks work items (sequence, KV head, split): with about three resident CTAs per SM and a
-  // few items per CTA every SM keeps the same number of loads in flight until the end.
-  for (int item = blockIdx.x; item < items; item += gridDim.x) {
-  const int split = item % p.splits, yz = item / p.splits;
-  const int b = yz / units_y, kvh = (yz % units_y) / p.gtiles, gt = (yz % units_y) % p.gtiles;
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int kvh = blockIdx.y / p.gtiles, gt = blockIdx.y % p.gtiles;
+  const int group = p.Hq / p.Hkv;
   const int g0 = gt * ROWS;
   const int gcount = min(ROWS, group - g0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = lane >> 2, j = lane & 3;
 
   const int len = p.lengths[b];
-  if (len <= 0) continue;  // uniform per CTA: empty slot, no ticket expected either
-  __syncthreads();         // the previous item's readers are done with the shared buffers
+  if (len <= 0) return;  // uniform per CTA
   const int pos = len - 1;
   const int slot_new = pos % p.cap;
   const int n_slots = min(len, p.cap);
@@ -626,33 +621,30 @@ decode_attention_mma_kernel(const DecodeParams p) {
     if (sh_last) p.tickets[unit] = 0;
   }
   __syncthreads();
-  if (sh_last) {
-    __threadfence();
-    const float* ao = p.part_o + unit * p.splits * (long long)(ROWS * HD);
-    const float* aml = p.part_ml + unit * p.splits * (long long)(ROWS * 2);
-    for (int e = threadIdx.x; e < gcount * HD; e += blockDim.x) {
-      const int g = e / HD, d = e % HD;
-      float mx = -INFINITY;
-      for (int s = 0; s < p.splits; ++s) mx = fmaxf(mx, __ldcg(aml + (s * ROWS + g) * 2));
-      float acc = 0.f, ls = 0.f;
-      if (mx != -INFINITY)
-        for (int s = 0; s < p.splits; ++s) {
-          const float w = __expf(__ldcg(aml + (s * ROWS + g) * 2) - mx);
-          acc += w * __ldcg(ao + (long long)(s * ROWS + g) * HD + d);
-          ls += w * __ldcg(aml + (s * ROWS + g) * 2 + 1);
-        }
-      p.out[(long long)b * p.Hq * HD + (long long)(kvh * group + g0 + g) * HD + d] = __float2bfloat16(ls > 0.f ? acc / ls : 0.f);
-    }
+  if (!sh_last) return;
+  __threadfence();
+  const float* ao = p.part_o + unit * p.splits * (long long)(ROWS * HD);
+  const float* aml = p.part_ml + unit * p.splits * (long long)(ROWS * 2);
+  for (int e = threadIdx.x; e < gcount * HD; e += blockDim.x) {
+    const int g = e / HD, d = e % HD;
+    float mx = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) mx = fmaxf(mx, __ldcg(aml + (s * ROWS + g) * 2));
+    float acc = 0.f, ls = 0.f;
+    if (mx != -INFINITY)
+      for (int s = 0; s < p.splits; ++s) {
+        const float w = __expf(__ldcg(aml + (s * ROWS + g) * 2) - mx);
+        acc += w * __ldcg(ao + (long long)(s * ROWS + g) * HD + d);
+        ls += w * __ldcg(aml + (s * ROWS + g) * 2 + 1);
+      }
+    p.out[(long long)b * p.Hq * HD + (long long)(kvh * group + g0 + g) * HD + d] = __float2bfloat16(ls > 0.f ? acc / ls : 0.f);
   }
-  }  // work items
 }
 
 template <int HD, bool WIDE>
 static int launch_decode_mma(const DecodeParams& p, cudaStream_t st) {
   constexpr size_t smem = decode_mma_smem_bytes<HD, WIDE>();
   static_assert(smem <= 48 * 1024, "decode_attention_mma: static budget");
-  const long long items = (long long)p.splits * p.Hkv * p.gtiles * p.B;
-  const int grid = (int)std::min<long long>(items, 3LL * sm_count());
+  dim3 grid(p.splits, p.Hkv * p.gtiles, p.B);
   decode_attention_mma_kernel<HD, WIDE><<<grid, MMA_WARPS * 32, smem, st>>>(p);
   return launch_check("decode_attention_mma", 1);
 }
@@ -723,8 +715,7 @@ extern "C" int nfn_decode_attention(const void* qkv, int ld, void* k_cache, void
   if (splits <= 0) {
     // one full wave at two (SIMT) or three (tensor-core kernel) resident CTAs per SM (rounding
     // down, so no straggler wave), and at least 128 cache positions per split
-    // the tensor-core kernel walks work items with three resident CTAs per SM: about four items per CTA
-    const long long want = use_mma ? (12LL * sm_count() + units - 1) / units : (2LL * sm_count()) / units;
+    const long long want = ((use_mma ? 3LL : 2LL) * sm_count()) / units;
     splits = (int)std::max<long long>(1, std::min<long long>(want, (cap + 127) / 128));
   }
   splits = min(splits, 64);
