@@ -32,7 +32,6 @@ from ..tensor import kernel_bridge as KB
 from ..tensor.stages_moe import route_scores
 from .ep_train import expert_parallel_ffn
 from .tp_llama import TPLlamaTrainer as FlatAdamWTrainer
-from .tp_llama import _rope
 
 __all__ = ["MoELlamaConfig", "EPMoELlama", "FlatAdamWTrainer", "moe_llama_reference_loss"]
 
@@ -94,15 +93,16 @@ def _forward_loss(cfg: MoELlamaConfig, p: dict, tokens: torch.Tensor, targets: t
     M, hd, Hq, Hkv, E = B * T, cfg.head_dim, cfg.n_head, cfg.n_kv_head, cfg.n_experts
     inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))
     ang = torch.outer(torch.arange(T, dtype=torch.float64), inv)
-    cos, sin = ang.cos().to(tokens.device, dtype)[None, :, None], ang.sin().to(tokens.device, dtype)[None, :, None]
+    cos, sin = ang.cos().float().to(tokens.device).contiguous(), ang.sin().float().to(tokens.device).contiguous()
     x = F.embedding(tokens.reshape(-1).long(), p["tok_embeddings"])
     balance = x.new_zeros((), dtype=torch.float32)
     zloss = x.new_zeros((), dtype=torch.float32)
     for l in range(cfg.n_layer):
         q_ = f"layers.{l}."
         qkv = KB.linear(KB.rms_norm(x, p[q_ + "attn_norm"], cfg.norm_eps), p[q_ + "wqkv"])
-        q = _rope(qkv[:, :Hq * hd].view(B, T, Hq, hd), cos, sin, 1.0)
-        k = _rope(qkv[:, Hq * hd:(Hq + Hkv) * hd].view(B, T, Hkv, hd), cos, sin, 1.0)
+        qkv = KB.rope_packed_qkv(qkv.contiguous(), T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=cos, sin=sin, convention="hf")
+        q = qkv[:, :Hq * hd].view(B, T, Hq, hd)
+        k = qkv[:, Hq * hd:(Hq + Hkv) * hd].view(B, T, Hkv, hd)
         v = qkv[:, (Hq + Hkv) * hd:].view(B, T, Hkv, hd)
         a = KB.attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), causal=True)
         x = x + KB.linear(a.transpose(1, 2).reshape(M, Hq * hd), p[q_ + "wo"])

@@ -227,22 +227,28 @@ class TPLlama:
         rows = M // W
         lo = tp.rank * rows
         hd, Hq, Hkv, Fl = cfg.head_dim, cfg.n_head // W, cfg.n_kv_head // W, cfg.d_ff // W
-        cos, sin = self._tables(T, tokens.device)
-        sign = 1.0 if cfg.rope_convention == "hf" else -1.0
+        if getattr(self, "_rope_T", None) != (T, tokens.device):
+            hd_ = cfg.head_dim
+            inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd_, 2, dtype=torch.float64) / hd_))
+            ang = torch.outer(torch.arange(T, dtype=torch.float64), inv)
+            self._rope_f32 = (ang.cos().float().to(tokens.device).contiguous(), ang.sin().float().to(tokens.device).contiguous())
+            self._rope_T = (T, tokens.device)
         x = F.embedding(tokens.reshape(-1)[lo:lo + rows].long(), p["tok_embeddings"])
         for l in range(cfg.n_layer):
             q_ = f"layers.{l}."
             h = KB.rms_norm(x, p[q_ + "attn_norm"], cfg.norm_eps)
             qkv = _ColumnParallel.apply(h, p[q_ + "wqkv"], tp)
-            q = _rope(qkv[:, :Hq * hd].view(B, T, Hq, hd), cos, sin, sign)
-            k = _rope(qkv[:, Hq * hd:(Hq + Hkv) * hd].view(B, T, Hkv, hd), cos, sin, sign)
+            qkv = KB.rope_packed_qkv(qkv, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=self._rope_f32[0], sin=self._rope_f32[1],
+                                     convention=cfg.rope_convention)
+            q = qkv[:, :Hq * hd].view(B, T, Hq, hd)
+            k = qkv[:, Hq * hd:(Hq + Hkv) * hd].view(B, T, Hkv, hd)
             v = qkv[:, (Hq + Hkv) * hd:].view(B, T, Hkv, hd)
             a = KB.attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), causal=True, window=cfg.window)
             a = a.transpose(1, 2).reshape(M, Hq * hd)
             x = _RowParallel.apply(a, p[q_ + "wo"], x, tp)
             h = KB.rms_norm(x, p[q_ + "ffn_norm"], cfg.norm_eps)
             gu = _ColumnParallel.apply(h, p[q_ + "w_gate_up"], tp)
-            x = _RowParallel.apply(F.silu(gu[:, :Fl]) * gu[:, Fl:], p[q_ + "w_down"], x, tp)
+            x = _RowParallel.apply(KB.swiglu(gu, Fl), p[q_ + "w_down"], x, tp)
         x = KB.rms_norm(x, p["norm"], cfg.norm_eps)
         logits = KB.linear(x, p["lm_head"])
         tgt = targets.reshape(-1)[lo:lo + rows]

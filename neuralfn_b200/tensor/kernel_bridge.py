@@ -218,6 +218,67 @@ def token_cross_entropy(logits: Tensor, target_ids: Tensor, z_loss_coef: float =
 
 
 # ------------------------------------------------------------------------------ MLPs --
+class _SwiGLUFn(torch.autograd.Function):
+    """gate_up [rows, 2 F] (gate | up) -> silu(gate) * up [rows, F]."""
+
+    @staticmethod
+    def forward(ctx, gate_up, inter):
+        from ..ops.infer import swiglu_forward
+        ctx.save_for_backward(gate_up)
+        ctx.inter = inter
+        return swiglu_forward(gate_up, inter)
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..ops.infer import swiglu_backward
+        (gate_up,) = ctx.saved_tensors
+        return swiglu_backward(gate_up, dout.contiguous(), ctx.inter), None
+
+
+def swiglu(gate_up: Tensor, inter: int) -> Tensor:
+    """SwiGLU over packed (gate | up) rows; native kernels for contiguous bf16 CUDA rows."""
+    if _native_ok(gate_up) and gate_up.dim() == 2 and gate_up.is_contiguous() and inter % 8 == 0:
+        return _SwiGLUFn.apply(gate_up, int(inter))
+    return F.silu(gate_up[..., :inter]) * gate_up[..., inter:]
+
+
+class _RopeFn(torch.autograd.Function):
+    """Rotates the q and k heads of packed [B * T, (Hq + 2 Hkv) * D] rows in place (v untouched);
+    the gradient is the inverse rotation."""
+
+    @staticmethod
+    def forward(ctx, qkv, T, n_q, n_kv, head_dim, cos, sin, convention):
+        from ..ops.infer import rope_inplace
+        rope_inplace(qkv, T=T, n_q_heads=n_q, n_kv_heads=n_kv, head_dim=head_dim, cos=cos, sin=sin, convention=convention)
+        ctx.mark_dirty(qkv)
+        ctx.meta = (T, n_q, n_kv, head_dim, convention)
+        ctx.save_for_backward(cos, sin)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, dqkv):
+        from ..ops.infer import rope_inplace
+        cos, sin = ctx.saved_tensors
+        T, n_q, n_kv, head_dim, convention = ctx.meta
+        d = dqkv.contiguous().clone()
+        rope_inplace(d, T=T, n_q_heads=n_q, n_kv_heads=n_kv, head_dim=head_dim, cos=cos, sin=sin, convention=convention, backward=True)
+        return d, None, None, None, None, None, None, None
+
+
+def rope_packed_qkv(qkv: Tensor, *, T: int, n_q_heads: int, n_kv_heads: int, head_dim: int, cos: Tensor, sin: Tensor, convention: str = "hf") -> Tensor:
+    """Rotary embedding on packed QKV rows (row r is position r % T). ``cos`` / ``sin``: fp32
+    [>= T, head_dim / 2]. Native in-place kernel on bf16 CUDA rows, PyTorch otherwise."""
+    if _native_ok(qkv) and qkv.dim() == 2 and qkv.is_contiguous() and cos.dtype == torch.float32:
+        return _RopeFn.apply(qkv, T, n_q_heads, n_kv_heads, head_dim, cos, sin, convention)
+    rows, hd, half = qkv.shape[0], head_dim, head_dim // 2
+    sign = 1.0 if convention == "hf" else -1.0
+    qk = qkv[:, :(n_q_heads + n_kv_heads) * hd].reshape(rows // T, T, n_q_heads + n_kv_heads, hd)
+    c, s_ = cos[:T].to(qkv.dtype)[None, :, None], sin[:T].to(qkv.dtype)[None, :, None]
+    a, b = qk[..., :half], qk[..., half:]
+    rot = torch.cat((a * c - sign * b * s_, b * c + sign * a * s_), -1).reshape(rows, -1)
+    return torch.cat((rot, qkv[:, (n_q_heads + n_kv_heads) * hd:]), -1)
+
+
 def swiglu_mlp(x: Tensor, w_gate: Tensor, w_up: Tensor, w_down: Tensor) -> Tensor:
     g = linear(x, w_gate)
     u = linear(x, w_up)
