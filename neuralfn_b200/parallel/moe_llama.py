@@ -101,11 +101,8 @@ def _forward_loss(cfg: MoELlamaConfig, p: dict, tokens: torch.Tensor, targets: t
         q_ = f"layers.{l}."
         qkv = KB.linear(KB.rms_norm(x, p[q_ + "attn_norm"], cfg.norm_eps), p[q_ + "wqkv"])
         qkv = KB.rope_packed_qkv(qkv.contiguous(), T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=cos, sin=sin, convention="hf")
-        q = qkv[:, :Hq * hd].view(B, T, Hq, hd)
-        k = qkv[:, Hq * hd:(Hq + Hkv) * hd].view(B, T, Hkv, hd)
-        v = qkv[:, (Hq + Hkv) * hd:].view(B, T, Hkv, hd)
-        a = KB.attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), causal=True)
-        x = x + KB.linear(a.transpose(1, 2).reshape(M, Hq * hd), p[q_ + "wo"])
+        a = KB.attention_packed_qkv(qkv, B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, causal=True)
+        x = x + KB.linear(a, p[q_ + "wo"])
         h = KB.rms_norm(x, p[q_ + "ffn_norm"], cfg.norm_eps)
         logits = KB.linear(h, p[q_ + "router"]).float()
         scores = route_scores(logits, cfg.score_fn)

@@ -240,11 +240,7 @@ class TPLlama:
             qkv = _ColumnParallel.apply(h, p[q_ + "wqkv"], tp)
             qkv = KB.rope_packed_qkv(qkv, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=self._rope_f32[0], sin=self._rope_f32[1],
                                      convention=cfg.rope_convention)
-            q = qkv[:, :Hq * hd].view(B, T, Hq, hd)
-            k = qkv[:, Hq * hd:(Hq + Hkv) * hd].view(B, T, Hkv, hd)
-            v = qkv[:, (Hq + Hkv) * hd:].view(B, T, Hkv, hd)
-            a = KB.attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), causal=True, window=cfg.window)
-            a = a.transpose(1, 2).reshape(M, Hq * hd)
+            a = KB.attention_packed_qkv(qkv, B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, causal=True, window=cfg.window)
             x = _RowParallel.apply(a, p[q_ + "wo"], x, tp)
             h = KB.rms_norm(x, p[q_ + "ffn_norm"], cfg.norm_eps)
             gu = _ColumnParallel.apply(h, p[q_ + "w_gate_up"], tp)

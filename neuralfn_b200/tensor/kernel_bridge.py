@@ -185,6 +185,44 @@ def attention(q: Tensor, k: Tensor, v: Tensor, *, causal: bool = True, window: i
                                           enable_gqa=q.size(1) != k.size(1))
 
 
+class _PackedAttentionFn(torch.autograd.Function):
+    """Causal attention straight on packed rows [B * T, (Hq + 2 Hkv) * D] -> [B * T, Hq * D]:
+    the kernels take q, k and v as strided views, and the backward pass writes dq, dk and dv
+    into the three column ranges of one gradient buffer - no re-packing copies either way."""
+
+    @staticmethod
+    def forward(ctx, qkv, B, T, Hq, Hkv, D, causal, window, scale):
+        K = _K()
+        q, k, v = qkv[:, :Hq * D], qkv[:, Hq * D:(Hq + Hkv) * D], qkv[:, (Hq + Hkv) * D:(Hq + 2 * Hkv) * D]
+        o, lse = K.attention_forward(q, k, v, B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, causal=causal, window=window, scale=scale)
+        ctx.save_for_backward(qkv, o, lse)
+        ctx.meta = (B, T, Hq, Hkv, D, causal, window, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        K = _K()
+        qkv, o, lse = ctx.saved_tensors
+        B, T, Hq, Hkv, D, causal, window, scale = ctx.meta
+        q, k, v = qkv[:, :Hq * D], qkv[:, Hq * D:(Hq + Hkv) * D], qkv[:, (Hq + Hkv) * D:(Hq + 2 * Hkv) * D]
+        dqkv = torch.empty_like(qkv) if qkv.shape[1] == (Hq + 2 * Hkv) * D else torch.zeros_like(qkv)
+        K.attention_backward(do.contiguous(), q, k, v, o, lse, B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, causal=causal, window=window,
+                             scale=scale, dq=dqkv[:, :Hq * D], dk=dqkv[:, Hq * D:(Hq + Hkv) * D], dv=dqkv[:, (Hq + Hkv) * D:(Hq + 2 * Hkv) * D])
+        return dqkv, None, None, None, None, None, None, None, None
+
+
+def attention_packed_qkv(qkv: Tensor, *, B: int, T: int, n_q_heads: int, n_kv_heads: int, head_dim: int, causal: bool = True,
+                         window: int = 0, scale: float | None = None) -> Tensor:
+    """Self-attention over packed QKV rows (row = b * T + t); returns token-major [B * T, Hq * D]."""
+    Hq, Hkv, D = n_q_heads, n_kv_heads, head_dim
+    if _native_ok(qkv) and qkv.dim() == 2 and qkv.stride(1) == 1 and D in (64, 128) and Hq % Hkv == 0:
+        return _PackedAttentionFn.apply(qkv, B, T, Hq, Hkv, D, bool(causal), int(window), float(scale or D ** -0.5))
+    q = qkv[:, :Hq * D].view(B, T, Hq, D).transpose(1, 2)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].view(B, T, Hkv, D).transpose(1, 2)
+    v = qkv[:, (Hq + Hkv) * D:(Hq + 2 * Hkv) * D].view(B, T, Hkv, D).transpose(1, 2)
+    return attention(q, k, v, causal=causal, window=window, scale=scale).transpose(1, 2).reshape(B * T, Hq * D)
+
+
 # ------------------------------------------------------------------------------ loss --
 class _CrossEntropyFn(torch.autograd.Function):
     @staticmethod
