@@ -92,6 +92,24 @@ class TPLlamaDecoder:
             self._ws = DecodeAttentionWorkspace(max_batch, self.Hq, self.Hkv, hd, dev)
             self._gemm_ws = torch.empty(32 << 20, dtype=torch.uint8, device=dev)  # split-K partials of the skinny products
 
+    @classmethod
+    def from_hf_directory(cls, directory, tp: TensorParallelContext, *, max_batch: int, max_seq: int, use_graph: bool = False) -> "TPLlamaDecoder":
+        """Loads a Hugging Face Llama checkpoint directory (``config.json`` + safetensors, sharded
+        or not) and keeps this rank's shards. Every rank reads the files; only its slices go to
+        the device."""
+        from ..checkpoint.safetensors_io import load_hf_llama_directory
+        ec, tensors = load_hf_llama_directory(directory, max_batch=max_batch, max_seq=max_seq)
+        if ec.tie_embeddings:
+            tensors["lm_head"] = tensors["tok_embeddings"]
+        cfg = LlamaConfig(n_layer=ec.n_layer, n_head=ec.n_head, n_kv_head=ec.n_kv_head, d_model=ec.d_model, d_ff=ec.d_ff, vocab_size=ec.vocab,
+                          max_seq_len=max_seq, rope_theta=ec.rope_theta, rope_convention="hf", norm_eps=ec.norm_eps, head_dim_override=ec.head_dim,
+                          vocab_pad_to=8 * tp.world)
+        pad = cfg.padded_vocab - tensors["tok_embeddings"].shape[0]
+        if pad > 0:  # the decoder wants the vocabulary divisible by 8 x world
+            for k in ("tok_embeddings", "lm_head"):
+                tensors[k] = torch.cat([tensors[k], torch.zeros(pad, ec.d_model, dtype=tensors[k].dtype)], 0)
+        return cls(cfg, tp, max_batch=max_batch, max_seq=max_seq, full_params=tensors, use_graph=use_graph)
+
     def _random_shards(self, seed: int) -> None:
         """Random weights drawn shard by shard on the device (benchmarks): replicated tensors from
         a stream every rank shares, shards from one keyed by the rank."""
