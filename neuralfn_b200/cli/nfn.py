@@ -307,6 +307,42 @@ def cmd_compat_train(a) -> int:
     return 0
 
 
+def cmd_infer_tp(a) -> int:
+    """Greedy / sampled generation with the tensor-parallel decoder from a Hugging Face Llama directory."""
+    if a.gpus > 1 and "RANK" not in os.environ:
+        import subprocess
+        argv = [x for i, x in enumerate(sys.argv[1:]) if x != "--gpus" and (i == 0 or sys.argv[i] != "--gpus") and not x.startswith("--gpus=")]
+        return subprocess.call([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.gpus}", "--master-addr", "127.0.0.1",
+                                "--master-port", str(29500 + os.getpid() % 2000), "-m", "neuralfn_b200.cli.nfn", *argv])
+    import torch
+    import torch.distributed as dist
+    from ..parallel.tp import TensorParallelContext
+    from ..serving.tp_decode import TPLlamaDecoder
+    cuda = torch.cuda.is_available() and not a.cpu
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    dev = torch.device("cuda", local) if cuda else torch.device("cpu")
+    if cuda:
+        torch.cuda.set_device(dev)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl" if cuda else "gloo")
+    prompts = [[int(t) for t in p.split(",") if t] for p in a.prompt_tokens.split(";") if p]
+    if not prompts or len({len(p) for p in prompts}) != 1:
+        raise ValueError("--prompt-tokens wants one or more ';'-separated prompts of the same length")
+    need = len(prompts) * len(prompts[0])
+    if need % world:
+        raise ValueError(f"rows x prompt length = {need} must divide by the number of ranks ({world})")
+    dec = TPLlamaDecoder.from_hf_directory(a.hf_dir, TensorParallelContext(dev), max_batch=len(prompts), max_seq=len(prompts[0]) + a.max_new_tokens + 8,
+                                           use_graph=cuda and a.temperature <= 0)
+    dec.set_sampling(a.temperature, a.top_k, a.top_p, a.seed)
+    out = dec.generate(torch.tensor(prompts, device=dev), a.max_new_tokens).cpu().tolist()
+    dec.close()
+    if rank == 0:
+        print(json.dumps({"status": "ok", "world_size": world, "generated": out}))
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    return 0
+
+
 def cmd_migrate_native(a) -> int:
     from ..native_ir import migrate_graph_to_native
     man = migrate_graph_to_native(a.graph, a.out_dir, model_name=a.name or None, stop_token_ids=[int(x) for x in a.stop_tokens.split(",") if x])
@@ -352,6 +388,17 @@ def build_parser() -> argparse.ArgumentParser:
     sub.add_parser("native-info").set_defaults(fn=cmd_native_info)
     sub.add_parser("kernels", help="kernel catalogue and coverage of the built library").set_defaults(fn=cmd_kernels)
     sub.add_parser("families", help="model families, their execution routes and capability proofs").set_defaults(fn=cmd_families)
+    it = sub.add_parser("infer-tp", help="tensor-parallel generation from a Hugging Face Llama directory (one rank per GPU with --gpus N)")
+    it.add_argument("--hf-dir", required=True)
+    it.add_argument("--prompt-tokens", required=True, help="comma-separated ids; ';' separates equally long prompts")
+    it.add_argument("--max-new-tokens", type=int, default=32)
+    it.add_argument("--temperature", type=float, default=0.0)
+    it.add_argument("--top-k", type=int, default=0)
+    it.add_argument("--top-p", type=float, default=1.0)
+    it.add_argument("--seed", type=int, default=0)
+    it.add_argument("--gpus", type=int, default=0)
+    it.add_argument("--cpu", action="store_true", help="run on CPU ranks (PyTorch fallbacks)")
+    it.set_defaults(fn=cmd_infer_tp)
     em = sub.add_parser("embed", help="unit-length text vectors from an embedding model directory")
     em.add_argument("--checkpoint", required=True)
     em.add_argument("--text", default=None)

@@ -142,3 +142,16 @@ def test_tp_decoder_loads_a_hugging_face_directory(tmp_path):
     rounded = {k: v.to(torch.bfloat16).float() for k, v in full.items()}
     want, _ = _reference_generate(cfg, rounded, prompt, 5)
     assert torch.equal(got, want)
+
+
+def test_nfn_infer_tp_cli_on_cpu(tmp_path, capsys):
+    import json
+
+    from neuralfn_b200.checkpoint.safetensors_io import export_hf_llama_directory
+    from neuralfn_b200.cli import nfn
+    from neuralfn_b200.serving.tp_decode import random_full_params
+    cfg = _cfg()
+    export_hf_llama_directory(tmp_path / "hf", cfg, random_full_params(cfg, 9), dtype=torch.float32)
+    rc = nfn.main(["infer-tp", "--hf-dir", str(tmp_path / "hf"), "--prompt-tokens", "1,2,3,4;5,6,7,8", "--max-new-tokens", "4", "--cpu"])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and out["status"] == "ok" and len(out["generated"]) == 2 and all(len(r) == 4 for r in out["generated"])
