@@ -225,6 +225,9 @@ class TPLlama:
         if M % W:
             raise ValueError(f"batch x seq = {M} must divide by the TP size {W}")
         rows = M // W
+        if tp.impl == "fused" and rows % 128:
+            raise ValueError(f"the fused collective GEMMs work on 128-row tiles: batch x seq / TP size = {rows} must be a multiple of 128 "
+                             "(or build the context with impl='nccl')")
         lo = tp.rank * rows
         hd, Hq, Hkv, Fl = cfg.head_dim, cfg.n_head // W, cfg.n_kv_head // W, cfg.d_ff // W
         if getattr(self, "_rope_T", None) != (T, tokens.device):

@@ -269,6 +269,14 @@ class TPLlamaDecoder:
         if B != self.B or T > self.cap or M % W:
             raise ValueError("prefill wants max_batch rows, T <= max_seq and B x T divisible by the TP size")
         rows, lo = M // W, tp.rank * (M // W)
+        if tp.impl == "fused" and rows % 128:
+            # the fused collective GEMMs work on 128-row tiles per rank: short prompts take the NCCL
+            # collectives around the plain GEMM for this one pass (decode steps are unaffected)
+            tp.impl = "nccl"
+            try:
+                return self.prefill(tokens)
+            finally:
+                tp.impl = "fused"
         x = self.embed[tokens.reshape(-1)[lo:lo + rows].long()]
         for l, p in enumerate(self.layers):
             qkv = tp.column_linear(_rms(x, p["attn_norm"], cfg.norm_eps), p["wqkv"])
