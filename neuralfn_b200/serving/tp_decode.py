@@ -86,6 +86,7 @@ class TPLlamaDecoder:
         self._draws = 0
         self.use_graph = bool(use_graph and self.cuda)
         self._graph = None
+        self._graph_ok = True   # cleared once a library collective ran on this group (see prefill)
         self._fused_calls_per_step = 2 * cfg.n_layer + (1 if W > 1 else 0)  # two per layer + the candidate exchange
         if self.cuda:
             from ..ops.infer import DecodeAttentionWorkspace
@@ -273,6 +274,9 @@ class TPLlamaDecoder:
             # the fused collective GEMMs work on 128-row tiles per rank: short prompts take the NCCL
             # collectives around the plain GEMM for this one pass (decode steps are unaffected)
             tp.impl = "nccl"
+            # library collectives have now been issued on this communicator: decode steps stay eager
+            # (capturing after NCCL traffic aborted in a 2-GPU run; with the fused prefill it does not)
+            self._graph_ok = W == 1
             try:
                 return self.prefill(tokens)
             finally:
@@ -345,7 +349,7 @@ class TPLlamaDecoder:
     @torch.no_grad()
     def step(self) -> torch.Tensor:
         """One decode step for all rows; returns the new tokens [B]."""
-        if not self.use_graph or self.sampling is not None:  # sampling gathers logits with NCCL: kept out of graphs
+        if not self.use_graph or self.sampling is not None or not self._graph_ok:  # NCCL traffic is kept out of graphs
             self._step_body()
             return self.tokens.clone()
         if self._graph is None:
