@@ -493,7 +493,7 @@ static int launch_attn_bwd(const void* dout, const void* q, const void* k, const
 
 using namespace nfn;
 
-extern "C" int nfn_attention_backward(const void* dout, const void* q, const void* k, const void* v,
+extern "C" int nfn_attention_backward_v1(const void* dout, const void* q, const void* k, const void* v,
                                       const void* o, const float* lse, float* delta, float* dq_accum,
                                       void* dq, void* dk, void* dv, int B, int T, int Hq, int Hkv,
                                       int D, int ld_do, int ld_q, int ld_k, int ld_v, int ld_o,

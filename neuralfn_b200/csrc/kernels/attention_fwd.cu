@@ -405,7 +405,7 @@ using namespace nfn;
 
 // q: bf16 rows [B*T] x (Hq*D) with row stride ld_q; k, v: rows x (Hkv*D); o: rows x (Hq*D).
 // lse: optional fp32 [B, Hq, T].
-extern "C" int nfn_attention_forward(const void* q, const void* k, const void* v, void* o, float* lse,
+extern "C" int nfn_attention_forward_v1(const void* q, const void* k, const void* v, void* o, float* lse,
                                      int B, int T, int Hq, int Hkv, int D, int ld_q, int ld_k,
                                      int ld_v, int ld_o, int causal, int window, float scale,
                                      nfn_stream_t stream) {

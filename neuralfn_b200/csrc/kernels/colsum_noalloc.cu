@@ -100,6 +100,11 @@ extern "C" int nfn_colsum_noalloc(const void* dy, int ld, void* out, int rows, i
   if (rows <= 0) return 0;
   if (!dy || !out) return fail(-1, "colsum_noalloc: null operand");
   if (C <= 0 || (C % 2) || (ld % 2) || ld < C) return fail(-1, "colsum_noalloc: C and ld must be even, ld >= C");
+  // the partial kernel reads dy two bf16 at a time: a view that starts at an odd element passes the
+  // size checks above but would fault with a misaligned address on the device, so refuse it here
+  if ((reinterpret_cast<uintptr_t>(dy) & 3) != 0)
+    return fail(-1, "colsum_noalloc: dy must be 4-byte aligned (a view starting at an odd bf16 element is not)");
+  if ((reinterpret_cast<uintptr_t>(out) & 1) != 0) return fail(-1, "colsum_noalloc: out must be 2-byte aligned");
   if (C > NFN_COLSUM_NOALLOC_MAX_C)
     return fail(-1, "colsum_noalloc: width exceeds NFN_COLSUM_NOALLOC_MAX_C (8192); use nfn_colsum with caller scratch");
   int rc = 0;

@@ -14,8 +14,13 @@ extern "C" {
 #define NFN_COLSUM_NOALLOC_MAX_C 8192
 
 // out[c] = sum_r dy[r, c]  (+ out[c] when accumulate != 0)
-//   dy : bf16 [rows, C], row stride ld elements (ld >= C, both even)
+//   dy : bf16 [rows, C], row stride ld elements (ld >= C, both even); the address must be
+//        4-byte aligned (the kernel reads two elements at a time), so a view that starts at
+//        an odd element is refused before anything is launched
 //   out: bf16 [C]
+// rows <= 0 returns 0 without touching out, also when accumulate == 0 (nfn_colsum does the same).
+// The device address of the scratch array is looked up once per device and kept; after a
+// cudaDeviceReset() in the same process it is stale, so do not reset a device this library has used.
 // Same result as nfn_colsum, but the partial sums live in a fixed array inside the
 // library instead of caller-provided scratch. Returns 0, or a negative code with a
 // message in nfn_last_error() (null operands, odd sizes, C > NFN_COLSUM_NOALLOC_MAX_C).

@@ -22,6 +22,8 @@
 
 namespace nfn {
 
+int epi_direct_flag();  // gemm_tcgen05.cu
+
 constexpr int P2_BM = 128;          // rows per CTA (256 per pair)
 constexpr int P2_BN = 256;          // columns per pair tile; each CTA stages 128 of the B rows
 constexpr int P2_BK = 64;
@@ -264,7 +266,7 @@ int try_launch_gemm_pair(const nfn_gemm_args& a, cudaStream_t stream) {
   p.aux_out = static_cast<__nv_bfloat16*>(a.aux_out);
   p.m = a.m; p.n = a.n; p.k = a.k;
   p.ldc = a.ldc; p.ld_aux_in = a.ld_aux_in; p.ld_aux_out = a.ld_aux_out;
-  p.flags = a.flags; p.alpha = a.alpha; p.act_param = a.act_param;
+  p.flags = a.flags | epi_direct_flag(); p.alpha = a.alpha; p.act_param = a.act_param;
   p.tiles_m = ceil_div(a.m, 2 * P2_BM);
   p.tiles_n = ceil_div(a.n, P2_BN);
   p.split_k = 1;

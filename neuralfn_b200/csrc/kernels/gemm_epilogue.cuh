@@ -114,6 +114,129 @@ __device__ __forceinline__ void bulk_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// one 32-byte store (a whole DRAM sector) of sixteen bf16 values; `addr` must be 32-byte aligned
+__device__ __forceinline__ void st_global_v8(void* addr, const uint4& a, const uint4& b) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(addr), "r"(a.x), "r"(a.y), "r"(a.z),
+               "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+               : "memory");
+}
+// internal epilogue flag (not part of the public ABI): bf16 outputs bypass the shared-memory
+// staging tiles and TMA stores and go out as 32-byte stores straight from registers
+constexpr int NFN_EPI_DIRECT_ST = 1 << 16;
+// ---- specialised register epilogues ---------------------------------------------------------
+// The generic epilogue tests every flag per 8-column group; with one row per thread and two
+// warps per scheduler that is a long dependent instruction stream (about 16 instructions per
+// element), long enough to outlast the main loop of a K = 768 tile. The combinations the
+// trainers use are therefore compiled as straight-line code and selected once per launch.
+enum : int {
+  EPI_K_GENERIC = 0,
+  EPI_K_PLAIN,           // C = acc
+  EPI_K_BIAS,            // C = acc + bias
+  EPI_K_BIAS_RESID,      // C = acc + bias + aux_in
+  EPI_K_BIAS_GELU_SAVE,  // aux_out = acc + bias; C = gelu_tanh(aux_out)
+  EPI_K_DGELU,           // C = acc * gelu_tanh'(aux_in)
+  EPI_K_TANHCAP,         // C = cap * tanh(acc / cap)
+  EPI_K_F32_PLAIN,       // fp32 C = acc (split-K partial slices)
+};
+
+__device__ __forceinline__ int epi_classify(const GemmParams& p) {
+  if (p.alpha != 1.f) return EPI_K_GENERIC;
+  const int act = (p.flags >> NFN_EPI_ACT_SHIFT) & 0xF;
+  const int base = p.flags & 0x3F;
+  if (act == NFN_ACT_NONE) {
+    if (base == 0) return EPI_K_PLAIN;
+    if (base == NFN_EPI_BIAS) return EPI_K_BIAS;
+    if (base == (NFN_EPI_BIAS | NFN_EPI_RESID)) return EPI_K_BIAS_RESID;
+    if (base == NFN_EPI_OUT_F32) return EPI_K_F32_PLAIN;
+  } else if (act == NFN_ACT_GELU_TANH) {
+    if (base == (NFN_EPI_BIAS | NFN_EPI_SAVE_PRE)) return EPI_K_BIAS_GELU_SAVE;
+    if (base == NFN_EPI_DACT) return EPI_K_DGELU;
+  } else if (act == NFN_ACT_TANH_CAP) {
+    if (base == 0) return EPI_K_TANHCAP;
+  }
+  return EPI_K_GENERIC;
+}
+
+__device__ __forceinline__ void st_row32_bf16(__nv_bfloat16* cp, const uint4 (&o)[4], bool wide_st) {
+  if (wide_st) {
+    st_global_v8(cp, o[0], o[1]);
+    st_global_v8(cp + 16, o[2], o[3]);
+  } else {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(cp + g * 8) = o[g];
+  }
+}
+
+// One thread's 32 consecutive columns [nc, nc + 32) of row `row` (all inside the matrix).
+// `taddr` addresses those columns of the thread's TMEM lane. The TMEM load is warp-collective,
+// so every lane calls this; lanes with row_ok == false load and discard.
+template <int KIND>
+__device__ __forceinline__ void epi_chunk32(const GemmParams& p, uint32_t taddr, int row, bool row_ok, int nc, int sp,
+                                            bool wide_st, bool wide_aux) {
+  constexpr bool kBias = KIND == EPI_K_BIAS || KIND == EPI_K_BIAS_RESID || KIND == EPI_K_BIAS_GELU_SAVE;
+  constexpr bool kAuxIn = KIND == EPI_K_BIAS_RESID || KIND == EPI_K_DGELU;
+  uint4 aux[4], bias[4];
+  if (kAuxIn && row_ok) {
+    const uint4* ap = reinterpret_cast<const uint4*>(p.aux_in + (size_t)row * p.ld_aux_in + nc);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) aux[g] = ap[g];
+  }
+  if (kBias) {
+    const uint4* bp = reinterpret_cast<const uint4*>(p.bias + nc);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) bias[g] = __ldg(bp + g);
+  }
+  uint32_t r[32];
+  tmem_ld_32x32(taddr, r);
+  tmem_ld_wait();
+  if (!row_ok) return;
+  if (KIND == EPI_K_F32_PLAIN) {
+    float4* cp = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.c) + (size_t)sp * p.split_stride + (size_t)row * p.ldc + nc);
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+      cp[g] = make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]), __uint_as_float(r[4 * g + 2]),
+                          __uint_as_float(r[4 * g + 3]));
+    return;
+  }
+  uint4 o[4], pre[4];
+  const float cap = p.act_param, inv_cap = (KIND == EPI_K_TANHCAP) ? 1.f / p.act_param : 0.f;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
+    if (kBias) {
+      float b8[8];
+      unpack8_bf16(bias[g], b8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] += b8[j];
+    }
+    if (KIND == EPI_K_BIAS_GELU_SAVE) {
+      pre[g] = pack8_bf16(v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = gelu_tanh_f(v[j]);
+    }
+    if (KIND == EPI_K_TANHCAP) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = cap * fast_tanh(v[j] * inv_cap);
+    }
+    if (kAuxIn) {
+      float x8[8];
+      unpack8_bf16(aux[g], x8);
+      if (KIND == EPI_K_DGELU) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] *= dgelu_tanh_f(x8[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] += x8[j];
+      }
+    }
+    o[g] = pack8_bf16(v);
+  }
+  if (KIND == EPI_K_BIAS_GELU_SAVE) st_row32_bf16(p.aux_out + (size_t)row * p.ld_aux_out + nc, pre, wide_aux);
+  st_row32_bf16(reinterpret_cast<__nv_bfloat16*>(p.c) + (size_t)row * p.ldc + nc, o, wide_st);
+}
+
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // Row r of a [128 x 64] bf16 staging tile with the 128-byte swizzle TMA expects:

@@ -50,6 +50,17 @@ splitk_reduce_kernel(const float* __restrict__ part, long long slice, int splits
   }
 }
 
+// bf16 epilogue route: 1 (default) = straight from registers with 32-byte stores, no epilogue-wide
+// synchronisation; 0 = shared-memory staging tiles + TMA stores. -1 = read NFN_GEMM_EPI_DIRECT once.
+static int g_epi_direct = -1;
+int epi_direct_flag() {
+  if (g_epi_direct < 0) {
+    const char* e = getenv("NFN_GEMM_EPI_DIRECT");
+    g_epi_direct = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_epi_direct ? NFN_EPI_DIRECT_ST : 0;
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 static int launch_gemm(const nfn_gemm_args& a, int split_k, cudaStream_t stream) {
   constexpr size_t SMEM =
@@ -80,7 +91,7 @@ static int launch_gemm(const nfn_gemm_args& a, int split_k, cudaStream_t stream)
   p.aux_out = static_cast<__nv_bfloat16*>(a.aux_out);
   p.m = a.m; p.n = a.n; p.k = a.k;
   p.ldc = a.ldc; p.ld_aux_in = a.ld_aux_in; p.ld_aux_out = a.ld_aux_out;
-  p.flags = a.flags; p.alpha = a.alpha; p.act_param = a.act_param;
+  p.flags = a.flags | epi_direct_flag(); p.alpha = a.alpha; p.act_param = a.act_param;
   p.tiles_m = ceil_div(a.m, BM);
   p.tiles_n = ceil_div(a.n, BN);
   p.split_k = 1;
@@ -151,6 +162,12 @@ static bool pair_enabled() {
 extern "C" int nfn_gemm_set_gemv_mode(int on) {
   const int old = nfn::g_gemv_mode;
   nfn::g_gemv_mode = on ? 1 : 0;
+  return old;
+}
+
+extern "C" int nfn_gemm_set_epilogue_direct(int on) {
+  const int old = nfn::epi_direct_flag() ? 1 : 0;
+  nfn::g_epi_direct = on ? 1 : 0;
   return old;
 }
 

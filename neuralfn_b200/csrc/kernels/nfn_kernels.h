@@ -114,6 +114,40 @@ int nfn_allreduce_resid_norm(const void* const* peer_bufs, const void* multicast
 // Stream-ordered wait until every peer finished reading this rank's buffer in call `epoch`.
 int nfn_allreduce_wait_readers(const int* ctrl_local, int world, int epoch, const int* epoch_dev, nfn_stream_t stream);
 
+// ---- flash attention for training and prefill (attention_fwd2.cu, attention_bwd2.cu) ----------------
+// q: bf16 rows [B*T] x (Hq*D) with row stride ld_q; k, v: rows x (Hkv*D); o: rows x (Hq*D);
+// lse: fp32 [B, Hq, T] (optional in the forward pass). head_dim D is 64 or 128.
+//   causal = 1: keys <= query.  window = W > 0: causal keys in (q - W, q], or |q - k| < W when
+//   not causal.  seq_ids (optional int32 [B*T]): a key is visible only when its id equals the
+//   query's (packed sequences).  softcap = c > 0: scores become c * tanh(s * scale / c).
+//   gate (optional bf16 [rows, Hq*D], forward only): o *= sigmoid(gate).
+// The backward pass needs delta scratch (fp32 [B, Hq, T]); it runs two kernels, one that owns a
+// key block (dK, dV) and one that owns a query tile (dQ), so no gradient is accumulated with atomics.
+typedef struct {
+  const void* q; const void* k; const void* v; void* o; float* lse;
+  int B, T, Hq, Hkv, D;
+  int ld_q, ld_k, ld_v, ld_o;
+  int causal, window;
+  float scale, softcap;
+  const int* seq_ids;
+  const void* gate; int ld_gate;
+  // backward only
+  const void* d_o; int ld_do;
+  float* delta;
+  void* dq; void* dk; void* dv; int ld_dq, ld_dk, ld_dv;
+} nfn_attention_args;
+int nfn_attention_forward_ex(const nfn_attention_args* args, nfn_stream_t stream);
+int nfn_attention_backward_ex(const nfn_attention_args* args, nfn_stream_t stream);
+int nfn_attention_forward(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int Hq,
+                          int Hkv, int D, int ld_q, int ld_k, int ld_v, int ld_o, int causal, int window, float scale,
+                          nfn_stream_t stream);
+int nfn_attention_backward(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                           float* delta, float* dq_accum, void* dq, void* dk, void* dv, int B, int T, int Hq, int Hkv,
+                           int D, int ld_do, int ld_q, int ld_k, int ld_v, int ld_o, int ld_dq, int ld_dk, int ld_dv,
+                           int causal, int window, float scale, nfn_stream_t stream);
+// 2 (default): pipelined kernels; 1: the first-generation kernels (plain masks only). Returns the old value.
+int nfn_attention_set_impl(int impl);
+
 // ---- rotary embedding (rope.cu) -----------------------------------------------------------------
 // In place on the q and k heads of packed rows (q | k | v). sign = +1: "hf" convention,
 // -1: "legacy"; the backward pass is the same call with the opposite sign. Tables are fp32

@@ -97,6 +97,8 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 255u) {
       if (*cta_abort) return false;
+      // another CTA of this launch already gave up: do not make the launch wait once per CTA
+      if (status && *reinterpret_cast<volatile int*>(status) != 0) break;
       const unsigned long long now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;

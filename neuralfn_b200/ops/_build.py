@@ -30,6 +30,13 @@ NVCC_FLAGS = [
 ]
 
 
+def _extra_flags() -> list[str]:
+    """Extra nvcc flags from ``NFN_EXTRA_NVCC_FLAGS`` (for instance ``-DNFN_KERNEL_TIMERS`` to compile
+    the per-role cycle counters into the GEMM and attention kernels). They are part of the object
+    digests, so changing them rebuilds."""
+    return os.environ.get("NFN_EXTRA_NVCC_FLAGS", "").split()
+
+
 def _nvcc() -> str:
     for cand in (os.environ.get("NFN_NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and Path(cand).exists():
@@ -42,13 +49,13 @@ def _digest(paths) -> str:
     for p in sorted(paths):
         h.update(str(p.name).encode())
         h.update(p.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + _extra_flags()).encode())
     return h.hexdigest()
 
 
 def _compile_one(src: Path, obj: Path, extra: list[str], verbose: bool) -> str:
     lang = ["-x", "cu"] if src.suffix == ".cpp" else []
-    cmd = [_nvcc(), *NVCC_FLAGS, *extra, *lang, "-I", str(KERNEL_SRC), "-I", str(ENGINE_SRC), "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *NVCC_FLAGS, *_extra_flags(), *extra, *lang, "-I", str(KERNEL_SRC), "-I", str(ENGINE_SRC), "-c", str(src), "-o", str(obj)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src.name}:\n{proc.stdout}\n{proc.stderr}")

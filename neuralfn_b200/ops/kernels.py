@@ -128,45 +128,88 @@ def qk_norm_backward(dqkv, qkv_normed, rstd, n_q_heads: int, n_kv_heads: int, he
 
 
 # ----------------------------------------------------------------- attention --
-def attention_forward(q, k, v, *, B: int, T: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
-                      causal: bool = True, window: int = 0, scale: float | None = None,
-                      out=None, lse=None, need_lse: bool = True):
-    """q: bf16 [B*T, >= Hq*D] view (row stride free), k/v: [B*T, >= Hkv*D] views.
-    Returns (o [B*T, Hq*D], lse [B, Hq, T])."""
+class AttentionArgs(ctypes.Structure):
+    """Mirror of ``nfn_attention_args`` (csrc/kernels/nfn_kernels.h)."""
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("o", ctypes.c_void_p), ("lse", ctypes.c_void_p),
+        ("B", c_int), ("T", c_int), ("Hq", c_int), ("Hkv", c_int), ("D", c_int),
+        ("ld_q", c_int), ("ld_k", c_int), ("ld_v", c_int), ("ld_o", c_int),
+        ("causal", c_int), ("window", c_int),
+        ("scale", c_float), ("softcap", c_float),
+        ("seq_ids", ctypes.c_void_p),
+        ("gate", ctypes.c_void_p), ("ld_gate", c_int),
+        ("d_o", ctypes.c_void_p), ("ld_do", c_int),
+        ("delta", ctypes.c_void_p),
+        ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p),
+        ("ld_dq", c_int), ("ld_dk", c_int), ("ld_dv", c_int),
+    ]
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _attention_args(q, k, v, o, lse, B, T, n_q_heads, n_kv_heads, head_dim, causal, window, scale, softcap, seq_ids, gate):
     for name, t in (("q", q), ("k", k), ("v", v)):
         if t.dtype != _bf16 or t.stride(1) != 1 or t.shape[0] != B * T:
             raise ValueError(f"attention: bad {name}")
-    if scale is None:
-        scale = head_dim ** -0.5
+    if seq_ids is not None and (seq_ids.dtype != torch.int32 or seq_ids.numel() != B * T or not seq_ids.is_contiguous()):
+        raise ValueError("attention: seq_ids must be contiguous int32 [B*T]")
+    if gate is not None and (gate.dtype != _bf16 or gate.stride(1) != 1 or gate.shape[0] != B * T):
+        raise ValueError("attention: bad gate")
+    a = AttentionArgs()
+    a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(o), _ptr(lse)
+    a.B, a.T, a.Hq, a.Hkv, a.D = B, T, n_q_heads, n_kv_heads, head_dim
+    a.ld_q, a.ld_k, a.ld_v, a.ld_o = q.stride(0), k.stride(0), v.stride(0), (o.stride(0) if o is not None else 0)
+    a.causal, a.window = int(causal), int(window)
+    a.scale, a.softcap = float(head_dim ** -0.5 if scale is None else scale), float(softcap)
+    a.seq_ids = _ptr(seq_ids)
+    a.gate, a.ld_gate = _ptr(gate), (gate.stride(0) if gate is not None else 0)
+    return a
+
+
+def attention_forward(q, k, v, *, B: int, T: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                      causal: bool = True, window: int = 0, scale: float | None = None,
+                      softcap: float = 0.0, seq_ids=None, gate=None, out=None, lse=None, need_lse: bool = True):
+    """q: bf16 [B*T, >= Hq*D] view (row stride free), k/v: [B*T, >= Hkv*D] views.
+    ``seq_ids`` (int32 [B*T]): packed sequences, a key is visible only inside the query's own
+    sequence. ``softcap`` c > 0: scores become c * tanh(s * scale / c). ``gate`` (bf16 [B*T, Hq*D]):
+    the output is multiplied by sigmoid(gate). Returns (o [B*T, Hq*D], lse [B, Hq, T])."""
     o = torch.empty(B * T, n_q_heads * head_dim, device=q.device, dtype=_bf16) if out is None else out
     if lse is None and need_lse:
         lse = torch.empty(B, n_q_heads, T, device=q.device, dtype=torch.float32)
-    rc = _lib.load().nfn_attention_forward(
-        _p(q), _p(k), _p(v), _p(o), _p(lse), c_int(B), c_int(T), c_int(n_q_heads), c_int(n_kv_heads),
-        c_int(head_dim), c_int(q.stride(0)), c_int(k.stride(0)), c_int(v.stride(0)), c_int(o.stride(0)),
-        c_int(int(causal)), c_int(window), c_float(scale), _st())
-    _lib.check(rc, "nfn_attention_forward")
+    a = _attention_args(q, k, v, o, lse, B, T, n_q_heads, n_kv_heads, head_dim, causal, window, scale, softcap, seq_ids, gate)
+    rc = _lib.load().nfn_attention_forward_ex(ctypes.byref(a), _st())
+    _lib.check(rc, "nfn_attention_forward_ex")
     return o, lse
 
 
 def attention_backward(do, q, k, v, o, lse, *, B: int, T: int, n_q_heads: int, n_kv_heads: int,
                        head_dim: int, causal: bool = True, window: int = 0, scale: float | None = None,
-                       dq, dk, dv, delta=None, dq_accum=None):
-    """Gradients of attention. dq/dk/dv are bf16 [B*T, *] views (row stride free).
-    ``dq_accum``: fp32 [B*T, Hq*D] scratch (zeroed here); ``delta``: fp32 [B, Hq, T] scratch."""
-    if scale is None:
-        scale = head_dim ** -0.5
+                       softcap: float = 0.0, seq_ids=None, dq, dk, dv, delta=None, dq_accum=None):
+    """Gradients of attention (of the ungated output). dq/dk/dv are bf16 [B*T, *] views (row
+    stride free). ``delta``: fp32 [B, Hq, T] scratch. ``dq_accum`` (fp32 [B*T, Hq*D]) is only
+    needed by the first-generation kernels (``nfn_attention_set_impl(1)``)."""
     if delta is None:
         delta = torch.empty(B, n_q_heads, T, device=q.device, dtype=torch.float32)
-    if dq_accum is None:
-        dq_accum = torch.empty(B * T, n_q_heads * head_dim, device=q.device, dtype=torch.float32)
-    rc = _lib.load().nfn_attention_backward(
-        _p(do), _p(q), _p(k), _p(v), _p(o), _p(lse), _p(delta), _p(dq_accum), _p(dq), _p(dk), _p(dv),
-        c_int(B), c_int(T), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim),
-        c_int(do.stride(0)), c_int(q.stride(0)), c_int(k.stride(0)), c_int(v.stride(0)),
-        c_int(o.stride(0)), c_int(dq.stride(0)), c_int(dk.stride(0)), c_int(dv.stride(0)),
-        c_int(int(causal)), c_int(window), c_float(scale), _st())
-    _lib.check(rc, "nfn_attention_backward")
+    lib = _lib.load()
+    if dq_accum is not None and softcap == 0.0 and seq_ids is None:
+        # same call for both kernel generations: the library picks by nfn_attention_set_impl
+        sc = head_dim ** -0.5 if scale is None else scale
+        rc = lib.nfn_attention_backward(
+            _p(do), _p(q), _p(k), _p(v), _p(o), _p(lse), _p(delta), _p(dq_accum), _p(dq), _p(dk), _p(dv),
+            c_int(B), c_int(T), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim),
+            c_int(do.stride(0)), c_int(q.stride(0)), c_int(k.stride(0)), c_int(v.stride(0)),
+            c_int(o.stride(0)), c_int(dq.stride(0)), c_int(dk.stride(0)), c_int(dv.stride(0)),
+            c_int(int(causal)), c_int(window), c_float(sc), _st())
+        _lib.check(rc, "nfn_attention_backward")
+        return dq, dk, dv
+    a = _attention_args(q, k, v, o, lse, B, T, n_q_heads, n_kv_heads, head_dim, causal, window, scale, softcap, seq_ids, None)
+    a.d_o, a.ld_do, a.delta = do.data_ptr(), do.stride(0), delta.data_ptr()
+    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    a.ld_dq, a.ld_dk, a.ld_dv = dq.stride(0), dk.stride(0), dv.stride(0)
+    rc = lib.nfn_attention_backward_ex(ctypes.byref(a), _st())
+    _lib.check(rc, "nfn_attention_backward_ex")
     return dq, dk, dv
 
 

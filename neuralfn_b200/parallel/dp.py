@@ -128,7 +128,8 @@ class ShardedAdamW:
             from ..ops import kernels as K
             self.K = K
             self.hyper = torch.zeros(K.HYPER_SIZE, dtype=torch.float32, device=dev)
-            self.hyper_host = torch.zeros(K.HYPER_SIZE, dtype=torch.float32).pin_memory()
+            from ..utils.pinned import PinnedRing
+            self._hyper_ring = PinnedRing(K.HYPER_SIZE, torch.float32, slots=8)
             self.partial = torch.empty(K.optim_max_partials(), dtype=torch.float32, device=dev)
             self.clip = torch.ones(2, dtype=torch.float32, device=dev)
             self.gshard = torch.empty(self.shard, dtype=torch.float32, device=dev) if self.world > 1 else None
@@ -159,9 +160,18 @@ class ShardedAdamW:
         """Upload the hyper-parameter block of the coming step (outside a captured graph)."""
         step = self.step_count + 1 if step is None else step
         gs = 1.0 / self.world if grad_scale is None else grad_scale
-        vals = self._hyper_values(step, gs)
-        self.hyper_host[:len(vals)] = torch.tensor(vals, dtype=torch.float32)
-        self.hyper.copy_(self.hyper_host, non_blocking=True)
+        # each step's values go through their own pinned slot (guarded by an event): the host may
+        # be several steps ahead of the GPU, and a single reused buffer would hand a queued copy
+        # the values of a later step
+        self._hyper_ring.upload(self.hyper, self._hyper_values(step, gs))
+
+    @property
+    def hyper_host(self) -> torch.Tensor:
+        """Pinned copy of the hyper-parameter block staged most recently (lr first)."""
+        ring = getattr(self, "_hyper_ring", None)
+        if ring is not None:
+            return ring.last
+        return torch.tensor(self._hyper_values(max(1, self.step_count), 1.0 / self.world), dtype=torch.float32)
 
     # -------------------------------------------------------------------- step --
     def step(self, *, stage: bool = True) -> None:

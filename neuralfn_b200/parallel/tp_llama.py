@@ -303,7 +303,8 @@ class TPLlamaTrainer:
             from ..ops import kernels as K
             self.K = K
             self.hyper = torch.zeros(K.HYPER_SIZE, dtype=torch.float32, device=dev)
-            self.hyper_host = torch.zeros(K.HYPER_SIZE, dtype=torch.float32).pin_memory()
+            from ..utils.pinned import PinnedRing
+            self._hyper_ring = PinnedRing(K.HYPER_SIZE, torch.float32, slots=8)
 
     def _clip_scale(self) -> None:
         norm = self.model.grad_norm()
@@ -321,8 +322,7 @@ class TPLlamaTrainer:
         lr = lr_at_step(c, t)
         if self.on_cuda:
             vals = [lr, c.beta1, c.beta2, c.eps, c.weight_decay, 1.0 - c.beta1 ** t, 1.0 - c.beta2 ** t, 1.0, c.max_grad_norm]
-            self.hyper_host[:len(vals)] = torch.tensor(vals, dtype=torch.float32)
-            self.hyper.copy_(self.hyper_host, non_blocking=True)
+            self._hyper_ring.upload(self.hyper, vals)  # one pinned slot per step in flight
             self.K.adamw_flat(self.master, self.m, self.v, mdl.grads, mdl.params.detach(), mdl.layout.n_decay, self.hyper, self.clip)
         else:
             with torch.no_grad():

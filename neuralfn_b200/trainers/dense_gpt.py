@@ -73,8 +73,9 @@ class DenseGPTTrainer:
         self._graphs: dict[str, torch.cuda.CUDAGraph] = {}
         self._warm: set[str] = set()
         self.launches_per_step = 0
-        self._h_tokens = torch.zeros(batch * seq, dtype=torch.int32).pin_memory()
-        self._h_targets = torch.zeros(batch * seq, dtype=torch.int32).pin_memory()
+        from ..utils.pinned import PinnedRing
+        self._h_tokens = PinnedRing(batch * seq, torch.int32, slots=3)
+        self._h_targets = PinnedRing(batch * seq, torch.int32, slots=3)
         self._h_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
         if self.world > 1:
             torch.cuda.synchronize(self.device)
@@ -136,8 +137,7 @@ class DenseGPTTrainer:
                 if src.dtype == torch.int32 and src.is_pinned():
                     dst.copy_(src, non_blocking=True)
                 else:
-                    stage.copy_(src)
-                    dst.copy_(stage, non_blocking=True)
+                    stage.upload(dst, src.to(torch.int32))
                 moved += dst.numel() * dst.element_size()
             else:
                 dst.copy_(src)

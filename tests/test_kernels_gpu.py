@@ -159,6 +159,112 @@ def test_attention_fwd_bwd(kernel_lib, B, T, Hq, Hkv, D, causal, window):
         assert r < 3e-2, (name, r)
 
 
+def _attn_ref_ex(q, k, v, B, T, Hq, Hkv, D, causal, window, scale, softcap=0.0, seq_ids=None, gate=None):
+    """fp32 oracle with the optional score soft-cap, packed-sequence mask and sigmoid output gate."""
+    qf = q.float().view(B, T, Hq, D).transpose(1, 2)
+    kf = k.float().view(B, T, Hkv, D).transpose(1, 2).repeat_interleave(Hq // Hkv, dim=1)
+    vf = v.float().view(B, T, Hkv, D).transpose(1, 2).repeat_interleave(Hq // Hkv, dim=1)
+    s = (qf @ kf.transpose(-1, -2)) * scale
+    if softcap > 0:
+        s = softcap * torch.tanh(s / softcap)
+    qi = torch.arange(T, device=q.device)[:, None]
+    ki = torch.arange(T, device=q.device)[None, :]
+    mask = torch.ones(T, T, dtype=torch.bool, device=q.device)
+    if causal:
+        mask &= ki <= qi
+        if window > 0:
+            mask &= ki > qi - window
+    elif window > 0:
+        mask &= (ki > qi - window) & (ki < qi + window)
+    mask = mask[None, None].expand(B, 1, T, T)
+    if seq_ids is not None:
+        ids = seq_ids.view(B, T)
+        mask = mask & (ids[:, None, :, None] == ids[:, None, None, :])
+    s = s.masked_fill(~mask, float("-inf"))
+    o = (torch.softmax(s, dim=-1) @ vf).transpose(1, 2).reshape(B * T, Hq * D)
+    lse = torch.logsumexp(s, dim=-1)
+    if gate is not None:
+        o = o * torch.sigmoid(gate.float())
+    return o, lse
+
+
+@pytest.mark.parametrize("B,T,Hq,Hkv,D,causal,window,softcap,packed", [
+    (2, 384, 4, 2, 64, True, 0, 0.0, True),      # packed sequences, GQA
+    (1, 512, 2, 2, 128, True, 0, 0.0, True),
+    (2, 256, 2, 2, 64, True, 0, 20.0, False),    # score soft-cap
+    (1, 448, 4, 1, 128, True, 160, 30.0, True),  # window + soft-cap + packed sequences
+    (1, 320, 2, 2, 64, False, 0, 15.0, True),    # bidirectional
+])
+def test_attention_softcap_and_sequence_ids(kernel_lib, B, T, Hq, Hkv, D, causal, window, softcap, packed):
+    from neuralfn_b200.ops import kernels as K, _lib
+    torch.manual_seed(1)
+    width = (Hq + 2 * Hkv) * D
+    qkv = torch.randn(B * T, width, device="cuda", dtype=BF) * 1.5
+    q, k, v = qkv[:, : Hq * D], qkv[:, Hq * D: (Hq + Hkv) * D], qkv[:, (Hq + Hkv) * D:]
+    seq = None
+    if packed:  # three documents of uneven length per row of the batch
+        cuts = torch.tensor([0, T // 5, T // 2 + 7, T])
+        seq = torch.cat([torch.full((int(cuts[i + 1] - cuts[i]),), i) for i in range(3)]).repeat(B).to("cuda", torch.int32)
+    scale = 1.0 / math.sqrt(D)
+    o, lse = K.attention_forward(q, k, v, B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, causal=causal,
+                                 window=window, scale=scale, softcap=softcap, seq_ids=seq)
+    _lib.assert_status_ok("attention fwd (soft-cap / sequence ids)")
+    qkv_f = qkv.float().requires_grad_(True)
+    qf, kf, vf = qkv_f[:, : Hq * D], qkv_f[:, Hq * D: (Hq + Hkv) * D], qkv_f[:, (Hq + Hkv) * D:]
+    o_ref, lse_ref = _attn_ref_ex(qf, kf, vf, B, T, Hq, Hkv, D, causal, window, scale, softcap, seq)
+    assert _rel(o, o_ref) < 2e-2, _rel(o, o_ref)
+    assert (lse - lse_ref).abs().max().item() < 3e-2
+    do = torch.randn(B * T, Hq * D, device="cuda", dtype=BF)
+    o_ref.backward(do.float())
+    dqkv = torch.zeros_like(qkv)
+    K.attention_backward(do, q, k, v, o, lse, B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, causal=causal,
+                         window=window, scale=scale, softcap=softcap, seq_ids=seq,
+                         dq=dqkv[:, : Hq * D], dk=dqkv[:, Hq * D: (Hq + Hkv) * D], dv=dqkv[:, (Hq + Hkv) * D:])
+    _lib.assert_status_ok("attention bwd (soft-cap / sequence ids)")
+    g = qkv_f.grad
+    for name, sl in (("dq", slice(0, Hq * D)), ("dk", slice(Hq * D, (Hq + Hkv) * D)), ("dv", slice((Hq + Hkv) * D, width))):
+        assert _rel(dqkv[:, sl], g[:, sl]) < 3e-2, (name, _rel(dqkv[:, sl], g[:, sl]))
+
+
+def test_attention_output_gate(kernel_lib):
+    from neuralfn_b200.ops import kernels as K, _lib
+    torch.manual_seed(2)
+    B, T, Hq, Hkv, D = 2, 256, 4, 1, 128
+    q = torch.randn(B * T, Hq * D, device="cuda", dtype=BF)
+    k = torch.randn(B * T, Hkv * D, device="cuda", dtype=BF)
+    v = torch.randn(B * T, Hkv * D, device="cuda", dtype=BF)
+    gate = torch.randn(B * T, Hq * D, device="cuda", dtype=BF)
+    o, _ = K.attention_forward(q, k, v, B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, causal=True, window=64, gate=gate)
+    _lib.assert_status_ok("attention fwd (gate)")
+    o_ref, _ = _attn_ref_ex(q, k, v, B, T, Hq, Hkv, D, True, 64, D ** -0.5, gate=gate)
+    assert _rel(o, o_ref) < 2e-2
+
+
+def test_attention_first_generation_kernels_still_match(kernel_lib):
+    """The first-generation kernels stay selectable (nfn_attention_set_impl(1)); both generations
+    must give the same gradients."""
+    from neuralfn_b200.ops import kernels as K, _lib
+    torch.manual_seed(3)
+    B, T, H, D = 1, 512, 2, 64
+    qkv = torch.randn(B * T, 3 * H * D, device="cuda", dtype=BF)
+    q, k, v = qkv[:, : H * D], qkv[:, H * D: 2 * H * D], qkv[:, 2 * H * D:]
+    do = torch.randn(B * T, H * D, device="cuda", dtype=BF)
+    outs = []
+    for impl in (2, 1):
+        old = kernel_lib.nfn_attention_set_impl(impl)
+        try:
+            o, lse = K.attention_forward(q, k, v, B=B, T=T, n_q_heads=H, n_kv_heads=H, head_dim=D)
+            d = torch.zeros_like(qkv)
+            K.attention_backward(do, q, k, v, o, lse, B=B, T=T, n_q_heads=H, n_kv_heads=H, head_dim=D,
+                                 dq=d[:, : H * D], dk=d[:, H * D: 2 * H * D], dv=d[:, 2 * H * D:],
+                                 dq_accum=torch.empty(B * T, H * D, device="cuda"))
+            _lib.assert_status_ok(f"attention impl {impl}")
+            outs.append((o.float(), d.float()))
+        finally:
+            kernel_lib.nfn_attention_set_impl(old)
+    assert _rel(outs[0][0], outs[1][0]) < 1e-2 and _rel(outs[0][1], outs[1][1]) < 2e-2
+
+
 @pytest.mark.parametrize("vocab,ld,cap,z", [(50257, 50304, 30.0, 1e-4), (1000, 1024, 0.0, 0.0),
                                             (128256, 128256, 0.0, 1e-4)])
 def test_cross_entropy(kernel_lib, vocab, ld, cap, z):

@@ -54,3 +54,20 @@ def test_noalloc_rejects_oversize(kernel_lib):
     assert _call(kernel_lib, dy, out) != 0
     kernel_lib.nfn_last_error.restype = ctypes.c_char_p
     assert b"8192" in kernel_lib.nfn_last_error()
+
+
+def test_noalloc_rejects_misaligned_view(kernel_lib):
+    """A bf16 view that starts at an odd element has even sizes but a 2-byte aligned address; the
+    entry point must refuse it on the host (no launch, so nothing can fault on the device)."""
+    from neuralfn_b200.ops import _lib
+    wide = torch.zeros(16, 66, device="cuda", dtype=torch.bfloat16)
+    dy = wide[:, 1:65]
+    assert dy.data_ptr() % 4 == 2 and dy.shape[1] % 2 == 0 and dy.stride(0) % 2 == 0
+    out = torch.zeros(64, device="cuda", dtype=torch.bfloat16)
+    before = _lib.launch_count()
+    assert _call(kernel_lib, dy, out) != 0
+    assert _lib.launch_count() == before
+    kernel_lib.nfn_last_error.restype = ctypes.c_char_p
+    assert b"aligned" in kernel_lib.nfn_last_error()
+    torch.cuda.synchronize()
+    _lib.assert_status_ok("colsum_noalloc misaligned")
