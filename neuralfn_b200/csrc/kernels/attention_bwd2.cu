@@ -41,29 +41,30 @@ struct AttnBwd2Params {
   int* status;
 };
 
-// delta[b, h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head)
+// delta[b, h, t] = sum_d dO[t, h, d] * O[t, h, d]. One thread per 16-byte piece of a token row
+// (8 elements); the D / 8 neighbouring lanes that share a head add up with shuffles.
 template <int D>
 __global__ void __launch_bounds__(256)
 attn_delta2_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
                    float* __restrict__ delta, int B, int T, int Hq, int ld_do, int ld_o) {
-  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (w >= (long long)B * T * Hq) return;
-  const int h = (int)(w % Hq);
-  const long long tok = w / Hq;
-  constexpr int PER = D / 32;
-  const __nv_bfloat16* a = dout + tok * ld_do + h * D + lane * PER;
-  const __nv_bfloat16* c = out + tok * ld_o + h * D + lane * PER;
+  constexpr int LANES = D / 8;  // lanes per (token, head): 8 or 16
+  const int per_row = Hq * LANES;
+  const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+  const long long tok = idx / per_row;
+  const int piece = (int)(idx % per_row);
   float s = 0.f;
-#pragma unroll
-  for (int e = 0; e < PER; e += 2) {
-    float2 x = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(a + e));
-    float2 y = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(c + e));
-    s += x.x * y.x + x.y * y.y;
+  const bool live = tok < (long long)B * T;
+  if (live) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(dout + tok * ld_do) + piece);
+    const uint4 c = __ldg(reinterpret_cast<const uint4*>(out + tok * ld_o) + piece);
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+    const float2 c0 = unpack_bf16x2(c.x), c1 = unpack_bf16x2(c.y), c2 = unpack_bf16x2(c.z), c3 = unpack_bf16x2(c.w);
+    s = (a0.x * c0.x + a0.y * c0.y) + (a1.x * c1.x + a1.y * c1.y) + (a2.x * c2.x + a2.y * c2.y) + (a3.x * c3.x + a3.y * c3.y);
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (lane == 0) {
+  for (int o = LANES / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (live && (piece % LANES) == 0) {
+    const int h = piece / LANES;
     const int bi = (int)(tok / T), t = (int)(tok % T);
     delta[((size_t)bi * Hq + h) * T + t] = s;
   }
@@ -76,17 +77,29 @@ attn_delta2_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* 
 template <int N, bool CAPPED>
 __device__ __forceinline__ void bwd_p_ds_row(uint32_t (&s)[N], uint32_t (&dp)[N], float c_mul, float cap_in,
                                              float row_lse2, float row_delta) {
+  // separate passes (exponent, ex2, product) so that neighbouring instructions are independent
+  uint32_t t[CAPPED ? N : 2];  // tanh values, needed again for the soft-cap derivative
+  if (CAPPED) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      t[i] = __float_as_uint(fast_tanh(__uint_as_float(s[i]) * cap_in));
+      s[i] = t[i];
+    }
+  }
 #pragma unroll
   for (int i = 0; i < N; i += 2) {
-    float u0 = __uint_as_float(s[i]), u1 = __uint_as_float(s[i + 1]);
-    if (CAPPED) { u0 = fast_tanh(u0 * cap_in); u1 = fast_tanh(u1 * cap_in); }
     float x0, x1;
-    fma2_bcast(x0, x1, u0, u1, c_mul, -row_lse2);
-    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-    float d0 = (__uint_as_float(dp[i]) - row_delta) * p0, d1 = (__uint_as_float(dp[i + 1]) - row_delta) * p1;
-    if (CAPPED) { d0 *= 1.f - u0 * u0; d1 *= 1.f - u1 * u1; }
-    s[i] = __float_as_uint(p0); s[i + 1] = __float_as_uint(p1);
-    dp[i] = __float_as_uint(d0); dp[i + 1] = __float_as_uint(d1);
+    fma2_bcast(x0, x1, __uint_as_float(s[i]), __uint_as_float(s[i + 1]), c_mul, -row_lse2);
+    s[i] = __float_as_uint(x0);
+    s[i + 1] = __float_as_uint(x1);
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i) s[i] = __float_as_uint(fast_exp2(__uint_as_float(s[i])));
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    float d = (__uint_as_float(dp[i]) - row_delta) * __uint_as_float(s[i]);
+    if (CAPPED) d *= 1.f - __uint_as_float(t[i]) * __uint_as_float(t[i]);
+    dp[i] = __float_as_uint(d);
   }
 }
 
@@ -598,19 +611,33 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bar_sfree));
       if (s + 1 < nsteps) fetch_stats(s + 1);  // latency hidden behind the exponentials
+      uint32_t th[capped ? BQ : 2];
+      if (capped) {
+#pragma unroll
+        for (int i = 0; i < BQ; ++i) {
+          th[i] = __float_as_uint(fast_tanh(__uint_as_float(sv_[i]) * cap_in));
+          sv_[i] = th[i];
+        }
+      }
+      // separate passes (exponent, ex2, product): neighbouring instructions are independent
 #pragma unroll
       for (int i = 0; i < BQ; i += 4) {
         const float4 l4 = *reinterpret_cast<const float4*>(st_lse + i);
+        sv_[i] = __float_as_uint(fmaf(__uint_as_float(sv_[i]), c_mul, -l4.x));
+        sv_[i + 1] = __float_as_uint(fmaf(__uint_as_float(sv_[i + 1]), c_mul, -l4.y));
+        sv_[i + 2] = __float_as_uint(fmaf(__uint_as_float(sv_[i + 2]), c_mul, -l4.z));
+        sv_[i + 3] = __float_as_uint(fmaf(__uint_as_float(sv_[i + 3]), c_mul, -l4.w));
+      }
+#pragma unroll
+      for (int i = 0; i < BQ; ++i) sv_[i] = __float_as_uint(fast_exp2(__uint_as_float(sv_[i])));
+#pragma unroll
+      for (int i = 0; i < BQ; i += 4) {
         const float4 d4 = *reinterpret_cast<const float4*>(st_dlt + i);
-        const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+        const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          float u = __uint_as_float(sv_[i + e]);
-          if (capped) u = fast_tanh(u * cap_in);
-          const float pe = fast_exp2(fmaf(u, c_mul, -lv[e]));
-          float de = (__uint_as_float(dp[i + e]) - dv[e]) * pe;
-          if (capped) de *= 1.f - u * u;
-          sv_[i + e] = __float_as_uint(pe);
+          float de = (__uint_as_float(dp[i + e]) - dv[e]) * __uint_as_float(sv_[i + e]);
+          if (capped) de *= 1.f - __uint_as_float(th[i + e]) * __uint_as_float(th[i + e]);
           dp[i + e] = __float_as_uint(de);
         }
       }
@@ -725,8 +752,8 @@ static int launch_attn_bwd2(const nfn_attention_args& a, cudaStream_t st) {
   if (set_smem_attr(kern_dq, CQ::SMEM, attr_dq) != 0) return launch_check("attn_bwd_dq attr", 0);
   const long long rows = (long long)a.B * a.T;
   {
-    const long long warps = rows * a.Hq;
-    attn_delta2_kernel<D><<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(
+    const long long threads = rows * a.Hq * (D / 8);
+    attn_delta2_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(
         (const __nv_bfloat16*)a.d_o, (const __nv_bfloat16*)a.o, a.delta, a.B, a.T, a.Hq, a.ld_do, a.ld_o);
   }
   AttnBwd2Params p;

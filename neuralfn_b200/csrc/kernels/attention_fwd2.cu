@@ -303,15 +303,24 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // exponentials in place (fp32), row sum
       float l0 = 0.f, l1 = 0.f;
 #pragma unroll
+      // three passes over the row instead of one fused loop: within a pass every instruction is
+      // independent of its neighbours, so a warp keeps the exponential unit fed back to back
+      // instead of stalling on each ex2 result (there are only two such warps per scheduler)
       for (int i = 0; i < BN; i += 2) {
         float x0, x1;
         fma2_bcast(x0, x1, __uint_as_float(s[i]), __uint_as_float(s[i + 1]), c_mul, -moff);
-        const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
-        add2(l0, l1, e0, e1);
-        s[i] = __float_as_uint(e0);
-        s[i + 1] = __float_as_uint(e1);
+        s[i] = __float_as_uint(x0);
+        s[i + 1] = __float_as_uint(x1);
       }
-      l_run += l0 + l1;
+#pragma unroll
+      for (int i = 0; i < BN; ++i) s[i] = __float_as_uint(fast_exp2(__uint_as_float(s[i])));
+      float l2 = 0.f, l3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < BN; i += 4) {
+        add2(l0, l1, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+        add2(l2, l3, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+      }
+      l_run += (l0 + l1) + (l2 + l3);
       NFN_TIMER_LAP(3)  // exponentials
       if (j > 0) {
         // O += P_{j-1} V_{j-1} must have retired before P's tile is overwritten and before O is

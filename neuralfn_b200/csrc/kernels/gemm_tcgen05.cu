@@ -151,7 +151,7 @@ static int gemv_mode() { return g_gemv_mode; }
 static bool pair_enabled() {
   if (g_pair_mode < 0) {
     const char* e = getenv("NFN_GEMM_PAIR");
-    g_pair_mode = (e && e[0] == '1') ? 1 : 0;
+    g_pair_mode = (e && e[0] == '0') ? 0 : 1;  // on unless NFN_GEMM_PAIR=0
   }
   return g_pair_mode == 1;
 }

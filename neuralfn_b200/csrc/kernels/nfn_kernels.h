@@ -65,7 +65,7 @@ typedef struct {
 int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream);
 // Routes eligible products (K-major A and B, bf16 output, no split-K, at least one 256 x 256
 // tile per SM pair) to the CTA-pair kernel (tcgen05 cta_group::2, 256 x 256 tile per 2-CTA
-// cluster). Returns the previous setting. The default comes from NFN_GEMM_PAIR (unset = off).
+// cluster). Returns the previous setting. On by default; NFN_GEMM_PAIR=0 turns it off.
 int nfn_gemm_set_gemv_mode(int on);  // 1 (default): M <= 2 products use the weight-streaming GEMV kernel; returns the old setting
 int nfn_gemm_set_pair_mode(int on);
 

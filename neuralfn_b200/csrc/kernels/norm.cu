@@ -216,38 +216,72 @@ __global__ void norm_bwd_wb_final_kernel(const float* __restrict__ partial,
   if (db) db[col] = __float2bfloat16(b + (accumulate ? __bfloat162float(db[col]) : 0.f));
 }
 
-// Column sum of a bf16 matrix [rows, C] -> bf16 [C] (bias gradients). Same two stages.
+// Column sum of a bf16 matrix [rows, C] -> bf16 [C] (bias gradients). Two stages: block (cx, ry)
+// sums its share of the rows for 128 columns with 16-byte loads (16 row lanes x 16 column vectors,
+// four rows in flight per thread), then a small kernel folds the RY partial rows.
 __global__ void __launch_bounds__(256)
 colsum_partial_kernel(const __nv_bfloat16* __restrict__ dy, int ld, float* __restrict__ partial,
                       int rows, int C) {
-  // each thread owns 2 adjacent columns; 4 row-lanes x 64 column-pairs = 128 columns per block
-  const int cp = threadIdx.x & 63, rlane = threadIdx.x >> 6;
-  const int col = (blockIdx.x * 64 + cp) * 2;
+  const int cv = threadIdx.x & 15, rlane = threadIdx.x >> 4;
+  const int col = (blockIdx.x * 16 + cv) * 8;
   const int RY = gridDim.y;
-  float a = 0.f, b = 0.f;
-  if (col < C) {
-    for (int r = blockIdx.y * 4 + rlane; r < rows; r += RY * 4) {
-      const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(dy + (size_t)r * ld + col));
-      a += f.x; b += f.y;
+  float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const bool vec_ok = col + 8 <= C && (ld & 7) == 0 && (reinterpret_cast<uintptr_t>(dy) & 15) == 0;
+  if (vec_ok) {
+    const int stride = RY * 16;
+    int r = blockIdx.y * 16 + rlane;
+    for (; r + 3 * stride < rows; r += 4 * stride) {
+      float f0[8], f1[8], f2[8], f3[8];
+      load8(dy + (size_t)r * ld + col, f0);
+      load8(dy + (size_t)(r + stride) * ld + col, f1);
+      load8(dy + (size_t)(r + 2 * stride) * ld + col, f2);
+      load8(dy + (size_t)(r + 3 * stride) * ld + col, f3);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += (f0[j] + f1[j]) + (f2[j] + f3[j]);
+    }
+    for (; r < rows; r += stride) {
+      float f0[8];
+      load8(dy + (size_t)r * ld + col, f0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += f0[j];
+    }
+  } else if (col < C) {  // ragged edge or unaligned view: element loads
+    for (int r = blockIdx.y * 16 + rlane; r < rows; r += RY * 16)
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (col + j < C) a[j] += __bfloat162float(dy[(size_t)r * ld + col + j]);
+  }
+  __shared__ float sa[16][129];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sa[rlane][cv * 8 + j] = a[j];
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    const int c = blockIdx.x * 128 + threadIdx.x;
+    if (c < C) {
+      float t = 0.f;
+#pragma unroll
+      for (int r = 0; r < 16; ++r) t += sa[r][threadIdx.x];
+      partial[(size_t)blockIdx.y * C + c] = t;
     }
   }
-  __shared__ float sa[4][64], sb[4][64];
-  sa[rlane][cp] = a; sb[rlane][cp] = b;
-  __syncthreads();
-  if (rlane == 0 && col < C) {
-    a = sa[0][cp] + sa[1][cp] + sa[2][cp] + sa[3][cp];
-    b = sb[0][cp] + sb[1][cp] + sb[2][cp] + sb[3][cp];
-    partial[(size_t)blockIdx.y * C + col] = a;
-    partial[(size_t)blockIdx.y * C + col + 1] = b;
-  }
 }
-__global__ void colsum_final_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
-                                    int RY, int C, int accumulate) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= C) return;
+// 32 columns per block, 8 row groups: coalesced reads of the partial rows, short dependent chains
+__global__ void __launch_bounds__(256)
+colsum_final_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int RY, int C, int accumulate) {
+  __shared__ float s[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + cx;
   float a = 0.f;
-  for (int r = 0; r < RY; ++r) a += partial[(size_t)r * C + col];
-  out[col] = __float2bfloat16(a + (accumulate ? __bfloat162float(out[col]) : 0.f));
+  if (col < C)
+    for (int r = ry; r < RY; r += 8) a += partial[(size_t)r * C + col];
+  s[ry][cx] = a;
+  __syncthreads();
+  if (ry == 0 && col < C) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t += s[r][cx];
+    out[col] = __float2bfloat16(t + (accumulate ? __bfloat162float(out[col]) : 0.f));
+  }
 }
 
 template <typename F>
@@ -401,31 +435,179 @@ extern "C" int nfn_norm_backward_wb(const void* dy, const void* x, const float* 
   return launch_check("norm_bwd_wb", 2);
 }
 
-// Partial rows the fused backward may write: scratch must hold nfn_norm_fused_rows() * 2 * C floats.
-extern "C" int nfn_norm_fused_rows(void) { return 2 * 160; }
+// ---- one-pass backward, many threads per row -------------------------------------------------
+// dx, dweight, dbias and (optionally) the column sum of dx itself in ONE pass over dy and x.
+// A row is spread over C / 8 threads (one 16-byte vector each), so a thread carries only
+// 3 x 8 column accumulators and the kernel runs at high occupancy; a block handles a few rows at
+// a time and strides over the matrix. The row reductions cross warps through a double-buffered
+// shared-memory slot (one block barrier per row step). Each block folds its column accumulators
+// through shared memory and writes one partial row [3][C]; norm_bwd2_final_kernel sums them.
+// The column sum of dx is the bias gradient of the linear layer that produced the residual
+// stream this norm reads (dx is d(residual stream)), so that layer needs no separate pass.
+constexpr int NB2_MAX_THREADS = 1024;
+
+template <bool LAYER>
+__global__ void __launch_bounds__(NB2_MAX_THREADS)
+norm_bwd2_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                 const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
+                 const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dresid,
+                 __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int C, int tpr, int rpb,
+                 int centered) {
+  extern __shared__ float nb2_smem[];       // [rpb][tpr * 8] column fold buffer, then [2][rpb][wpr][2] row sums
+  const int wpr = tpr >> 5;
+  float* s_fold = nb2_smem;
+  float* s_red = nb2_smem + (size_t)rpb * tpr * 8;
+  const int tir = threadIdx.x % tpr, rslot = threadIdx.x / tpr;
+  const int lane = threadIdx.x & 31, wir = tir >> 5;
+  const int c = tir * 8;
+  const bool col_ok = c < C;
+  float wv[8], aw[8], ab[8], ac[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { wv[j] = 1.f; aw[j] = 0.f; ab[j] = 0.f; ac[j] = 0.f; }
+  if (w && col_ok) {
+    load8(w + c, wv);
+    if (centered) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wv[j] += 1.f;
+    }
+  }
+  const float inv_c = 1.f / (float)C;
+  int it = 0;
+  for (int base = blockIdx.x * rpb; base < rows; base += gridDim.x * rpb, ++it) {
+    const int row = base + rslot;
+    const bool live = row < rows && col_ok;
+    const size_t off = (size_t)row * C + c;
+    float g[8], n[8], r[8];
+    float mean = 0.f, rstd = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { g[j] = 0.f; n[j] = 0.f; r[j] = 0.f; }
+    if (live) {
+      float xv[8];
+      load8(dy + off, g);
+      load8(x + off, xv);
+      if (dresid) load8(dresid + off, r);
+      mean = LAYER ? mean_in[row] : 0.f;
+      rstd = rstd_in[row];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) n[j] = (xv[j] - mean) * rstd;
+    }
+    float sg = 0.f, sgn = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      aw[j] += g[j] * n[j];
+      ab[j] += g[j];
+      g[j] *= wv[j];
+      sg += g[j];
+      sgn += g[j] * n[j];
+    }
+    sg = warp_sum(sg);
+    sgn = warp_sum(sgn);
+    if (wpr > 1) {
+      float* slot = s_red + ((size_t)((it & 1) * rpb + rslot) * wpr) * 2;
+      if (lane == 0) { slot[wir * 2] = sg; slot[wir * 2 + 1] = sgn; }
+      __syncthreads();
+      sg = 0.f; sgn = 0.f;
+      for (int k2 = 0; k2 < wpr; ++k2) { sg += slot[k2 * 2]; sgn += slot[k2 * 2 + 1]; }
+    }
+    sg = LAYER ? sg * inv_c : 0.f;
+    sgn *= inv_c;
+    if (live) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rstd * (g[j] - sg - n[j] * sgn) + r[j];
+      uint4 u;
+      u.x = pack_bf16x2(o[0], o[1]); u.y = pack_bf16x2(o[2], o[3]);
+      u.z = pack_bf16x2(o[4], o[5]); u.w = pack_bf16x2(o[6], o[7]);
+      *reinterpret_cast<uint4*>(dx + off) = u;
+      // sum what was stored (bf16-rounded), so the result equals a column sum of dx itself
+      const float2 q0 = unpack_bf16x2(u.x), q1 = unpack_bf16x2(u.y), q2 = unpack_bf16x2(u.z), q3 = unpack_bf16x2(u.w);
+      ac[0] += q0.x; ac[1] += q0.y; ac[2] += q1.x; ac[3] += q1.y;
+      ac[4] += q2.x; ac[5] += q2.y; ac[6] += q3.x; ac[7] += q3.y;
+    }
+  }
+  // fold the row slots of this block, one accumulator kind at a time
+#pragma unroll
+  for (int kind = 0; kind < 3; ++kind) {
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s_fold[(size_t)rslot * tpr * 8 + c + j] = kind == 0 ? aw[j] : (kind == 1 ? ab[j] : ac[j]);
+    __syncthreads();
+    for (int cc = threadIdx.x; cc < C; cc += blockDim.x) {
+      float t = 0.f;
+      for (int r2 = 0; r2 < rpb; ++r2) t += s_fold[(size_t)r2 * tpr * 8 + cc];
+      partial[((size_t)blockIdx.x * 3 + kind) * C + cc] = t;
+    }
+  }
+}
+
+// Sums the partial rows [nblk][3][C]: 32 columns per block, 8 row groups per block.
+__global__ void __launch_bounds__(256)
+norm_bwd2_final_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dw, __nv_bfloat16* __restrict__ db,
+                       __nv_bfloat16* __restrict__ dcol, int nblk, int C, int accumulate) {
+  __shared__ float s[3][8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + cx;
+  float a[3] = {0.f, 0.f, 0.f};
+  if (col < C) {
+    for (int r = ry; r < nblk; r += 8) {
+#pragma unroll
+      for (int k = 0; k < 3; ++k) a[k] += partial[((size_t)r * 3 + k) * C + col];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 3; ++k) s[k][ry][cx] = a[k];
+  __syncthreads();
+  if (ry < 3 && col < C) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t += s[ry][r][cx];
+    __nv_bfloat16* out = ry == 0 ? dw : (ry == 1 ? db : dcol);
+    if (out) out[col] = __float2bfloat16(t + (accumulate ? __bfloat162float(out[col]) : 0.f));
+  }
+}
+
+// Partial rows the one-pass backward may write: scratch must hold nfn_norm_fused_rows() * 3 * C floats.
+extern "C" int nfn_norm_fused_rows(void) { return 640; }
+
+// dx_colsum (optional, bf16 [C]) receives sum over rows of dx.
+extern "C" int nfn_norm_backward_ex(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                                    const void* dresid, void* dx, void* dw, void* db, void* dx_colsum, float* scratch,
+                                    int rows, int C, int mode, int centered, int accumulate, nfn_stream_t stream) {
+  if (rows <= 0) return 0;
+  if (C % 8) return fail(-1, "norm_backward: C must be a multiple of 8");
+  if (C > 8 * NB2_MAX_THREADS) return fail(-1, "norm_backward: rows wider than 8192 are not supported");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int tpr = ((C / 8) + 31) / 32 * 32;               // threads per row, whole warps
+  const int rpb = std::max(1, 384 / tpr);                  // rows a block works on at a time
+  const int threads = tpr * rpb;
+  const int per_sm = std::max(1, 1536 / threads);
+  const int grid = std::min(ceil_div(rows, rpb), std::min(per_sm * sm_count(), nfn_norm_fused_rows()));
+  const size_t smem = ((size_t)rpb * tpr * 8 + (size_t)2 * rpb * (tpr / 32) * 2) * sizeof(float);
+  static bool attr[2][64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int li = mode == 0 ? 0 : 1;
+  if (smem > 48 * 1024 && !attr[li][dev & 63]) {
+    cudaError_t e = li == 0 ? cudaFuncSetAttribute(norm_bwd2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024)
+                            : cudaFuncSetAttribute(norm_bwd2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    if (e != cudaSuccess) return launch_check("norm_backward attr", 0);
+    attr[li][dev & 63] = true;
+  }
+  if (mode == 0)
+    norm_bwd2_kernel<true><<<grid, threads, smem, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, mean,
+                                                        rstd, (const __nv_bfloat16*)dresid, (__nv_bfloat16*)dx, scratch, rows, C, tpr, rpb, centered);
+  else
+    norm_bwd2_kernel<false><<<grid, threads, smem, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, mean,
+                                                         rstd, (const __nv_bfloat16*)dresid, (__nv_bfloat16*)dx, scratch, rows, C, tpr, rpb, centered);
+  norm_bwd2_final_kernel<<<ceil_div(C, 32), 256, 0, st>>>(scratch, (__nv_bfloat16*)dw, (__nv_bfloat16*)db, (__nv_bfloat16*)dx_colsum, grid, C,
+                                                          accumulate);
+  return launch_check("norm_backward", 2);
+}
 
 extern "C" int nfn_norm_backward(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, const void* dresid,
                                  void* dx, void* dw, void* db, float* scratch, int rows, int C, int mode, int centered, int accumulate,
                                  nfn_stream_t stream) {
-  if (rows <= 0) return 0;
-  if (C % 8) return fail(-1, "norm_backward: C must be a multiple of 8");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (C > 1024) {  // wide rows: the two-kernel path
-    int rc = nfn_norm_backward_dx(dy, x, w, mean, rstd, dresid, dx, rows, C, mode, centered, stream);
-    if (rc) return rc;
-    return nfn_norm_backward_wb(dy, x, mean, rstd, dw, db, scratch, rows, C, mode, accumulate, stream);
-  }
-  const int grid = std::min(ceil_div(rows, NORM_THREADS / 32), std::min(2 * sm_count(), nfn_norm_fused_rows()));
-#define NFN_FUSED(V)                                                                                                   \
-  norm_bwd_fused_kernel<V><<<grid, NORM_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,           \
-      (const __nv_bfloat16*)w, mean, rstd, (const __nv_bfloat16*)dresid, (__nv_bfloat16*)dx, scratch, rows, C, mode, centered)
-  if (C <= 256) NFN_FUSED(1);
-  else if (C <= 512) NFN_FUSED(2);
-  else if (C <= 768) NFN_FUSED(3);
-  else NFN_FUSED(4);
-#undef NFN_FUSED
-  norm_bwd_wb_final_kernel<<<ceil_div(C, 256), 256, 0, st>>>(scratch, (__nv_bfloat16*)dw, (__nv_bfloat16*)db, grid, C, accumulate);
-  return launch_check("norm_backward", 2);
+  return nfn_norm_backward_ex(dy, x, w, mean, rstd, dresid, dx, dw, db, nullptr, scratch, rows, C, mode, centered, accumulate, stream);
 }
 
 // scratch: fp32 [64 * C]
@@ -437,8 +619,7 @@ extern "C" int nfn_colsum(const void* dy, int ld, void* out, float* scratch, int
   const int RY = 64;
   dim3 grid(ceil_div(C, 128), RY);
   colsum_partial_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)dy, ld, scratch, rows, C);
-  colsum_final_kernel<<<ceil_div(C, 256), 256, 0, st>>>(scratch, (__nv_bfloat16*)out, RY, C,
-                                                        accumulate);
+  colsum_final_kernel<<<ceil_div(C, 32), 256, 0, st>>>(scratch, (__nv_bfloat16*)out, RY, C, accumulate);
   return launch_check("colsum", 2);
 }
 

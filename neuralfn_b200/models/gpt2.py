@@ -262,7 +262,7 @@ class GPT2Engine:
         self.d_att = e(N, C)
         self.delta = e(batch, cfg.n_head, seq, dtype=f32)
         self.dq_accum = e(N, C, dtype=f32)
-        self.scratch = e(max(64 * 2 * max(Hd, 3 * C), K.norm_fused_rows() * 2 * C), dtype=f32)
+        self.scratch = e(max(64 * 2 * max(Hd, 3 * C), K.norm_fused_rows() * 3 * C), dtype=f32)
         self.ws = e(32 * 1024 * 1024, dtype=f32)  # split-K partial slices of the weight-gradient GEMMs
         self.tokens = torch.zeros(N, device=dev, dtype=torch.int32)
         self.targets = torch.zeros(N, device=dev, dtype=torch.int32)
@@ -320,8 +320,11 @@ class GPT2Engine:
         gemm(dlogits, self.lnf, a_mn=True, b_mn=True, out=g["wte"])
         x_last = self.acts[-1].x2 if self.acts else self.x0
         dx, spare = self.d_res_a, self.d_res_b
+        L = cfg.n_layer
+        # every norm backward also returns the column sum of the residual-stream gradient it
+        # produces, which is the bias gradient of the projection that wrote that stream
         K.norm_backward(self.d_ln, x_last, p["ln_f.weight"], self.lnf_mean, self.lnf_rstd, g["ln_f.weight"], g["ln_f.bias"], sc,
-                        mode=K.NORM_LAYER, out=dx)
+                        mode=K.NORM_LAYER, out=dx, dx_colsum=g[f"h.{L - 1}.mlp.c_proj.bias"] if L > 0 else None)
         for l in range(cfg.n_layer - 1, -1, -1):
             a = self.acts[l]
             pre = f"h.{l}."
@@ -330,17 +333,15 @@ class GPT2Engine:
             gemm(dx, p[pre + "mlp.c_proj.weight"], b_mn=True, act="gelu_tanh", dact_pre=a.fc_pre,
                  out=self.d_fc)
             gemm(dx, a.fc_act, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "mlp.c_proj.weight"])
-            K.colsum(dx, g[pre + "mlp.c_proj.bias"], sc)
             gemm(self.d_fc, p[pre + "mlp.c_fc.weight"], b_mn=True, out=self.d_ln)
             gemm(self.d_fc, a.ln2, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "mlp.c_fc.weight"])
             K.colsum(self.d_fc, g[pre + "mlp.c_fc.bias"], sc)
             K.norm_backward(self.d_ln, a.x1, p[pre + "ln_2.weight"], a.ln2_mean, a.ln2_rstd, g[pre + "ln_2.weight"], g[pre + "ln_2.bias"], sc,
-                            mode=K.NORM_LAYER, dresid=dx, out=spare)
+                            mode=K.NORM_LAYER, dresid=dx, out=spare, dx_colsum=g[pre + "attn.c_proj.bias"])
             dx, spare = spare, dx  # dx now holds d(x1)
             # ---- attention branch: x1 = c_proj(att) + x ----
             gemm(dx, p[pre + "attn.c_proj.weight"], b_mn=True, out=self.d_att)
             gemm(dx, a.att, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "attn.c_proj.weight"])
-            K.colsum(dx, g[pre + "attn.c_proj.bias"], sc)
             K.attention_backward(self.d_att, a.qkv[:, :C], a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], a.att,
                                  a.lse, B=B, T=T, n_q_heads=nh, n_kv_heads=nh, head_dim=hd, causal=True,
                                  dq=self.d_qkv[:, :C], dk=self.d_qkv[:, C:2 * C], dv=self.d_qkv[:, 2 * C:],
@@ -351,7 +352,8 @@ class GPT2Engine:
             gemm(self.d_qkv, a.ln1, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "attn.c_attn.weight"])
             K.colsum(self.d_qkv, g[pre + "attn.c_attn.bias"], sc)
             K.norm_backward(self.d_ln, x_in, p[pre + "ln_1.weight"], a.ln1_mean, a.ln1_rstd, g[pre + "ln_1.weight"], g[pre + "ln_1.bias"], sc,
-                            mode=K.NORM_LAYER, dresid=dx, out=spare)
+                            mode=K.NORM_LAYER, dresid=dx, out=spare,
+                            dx_colsum=g[f"h.{l - 1}.mlp.c_proj.bias"] if l > 0 else None)
             dx, spare = spare, dx
         K.embedding_backward(dx, self.tokens, g["wte"], g["wpe"][:T], B=B, T=T)
         if T < cfg.max_seq_len:

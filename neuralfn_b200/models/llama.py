@@ -209,7 +209,7 @@ class LlamaEngine:
         self.d_qkv, self.d_att = e(N, Q), e(N, A)
         self.delta = e(batch, cfg.n_head, seq, dtype=f32)
         self.dq_accum = e(N, A, dtype=f32)
-        self.scratch = e(max(64 * 2 * max(2 * Fd, Q, C), K.norm_fused_rows() * 2 * C), dtype=f32)
+        self.scratch = e(max(64 * 2 * max(2 * Fd, Q, C), K.norm_fused_rows() * 3 * C), dtype=f32)
         self.ws = e(32 * 1024 * 1024, dtype=f32)
         self.tokens = torch.zeros(N, device=dev, dtype=torch.int32)
         self.targets = torch.zeros(N, device=dev, dtype=torch.int32)

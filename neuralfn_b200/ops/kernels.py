@@ -79,18 +79,21 @@ def norm_fused_rows() -> int:
 
 
 def norm_backward(dy, x, weight, mean, rstd, dweight, dbias, scratch, *, mode: int, centered: bool = False, dresid=None, out=None,
-                  accumulate: bool = False):
+                  accumulate: bool = False, dx_colsum=None):
     """dx (returned), dweight and dbias (bf16 [C], either may be None) in one pass over dy and x.
-    scratch: fp32 with at least ``norm_fused_rows() * 2 * C`` entries."""
+    ``dx_colsum`` (bf16 [C], optional) receives the column sum of dx: the bias gradient of the
+    linear layer whose output is the residual stream this norm reads.
+    scratch: fp32 with at least ``norm_fused_rows() * 3 * C`` entries."""
     _need(dy, _bf16, "dy")
     _need(x, _bf16, "x")
     rows, C = x.shape
-    if scratch.numel() < norm_fused_rows() * 2 * C:
+    if scratch.numel() < norm_fused_rows() * 3 * C:
         raise ValueError("norm_backward: scratch too small")
     dx = torch.empty_like(x) if out is None else out
-    rc = _lib.load().nfn_norm_backward(_p(dy), _p(x), _p(weight), _p(mean), _p(rstd), _p(dresid), _p(dx), _p(dweight), _p(dbias),
-                                       _p(scratch), c_int(rows), c_int(C), c_int(mode), c_int(int(centered)), c_int(int(accumulate)), _st())
-    _lib.check(rc, "nfn_norm_backward")
+    rc = _lib.load().nfn_norm_backward_ex(_p(dy), _p(x), _p(weight), _p(mean), _p(rstd), _p(dresid), _p(dx), _p(dweight), _p(dbias),
+                                          _p(dx_colsum), _p(scratch), c_int(rows), c_int(C), c_int(mode), c_int(int(centered)),
+                                          c_int(int(accumulate)), _st())
+    _lib.check(rc, "nfn_norm_backward_ex")
     return dx
 
 

