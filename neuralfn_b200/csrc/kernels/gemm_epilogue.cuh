@@ -214,7 +214,7 @@ __device__ __forceinline__ void epi_chunk32(const GemmParams& p, uint32_t taddr,
     if (KIND == EPI_K_BIAS_GELU_SAVE) {
       pre[g] = pack8_bf16(v);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = gelu_tanh_f(v[j]);
+      for (int j = 0; j < 8; j += 2) gelu_tanh_2(v[j], v[j + 1], v[j], v[j + 1]);
     }
     if (KIND == EPI_K_TANHCAP) {
 #pragma unroll
@@ -225,7 +225,11 @@ __device__ __forceinline__ void epi_chunk32(const GemmParams& p, uint32_t taddr,
       unpack8_bf16(aux[g], x8);
       if (KIND == EPI_K_DGELU) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] *= dgelu_tanh_f(x8[j]);
+        for (int j = 0; j < 8; j += 2) {
+          float d0, d1;
+          dgelu_tanh_2(d0, d1, x8[j], x8[j + 1]);
+          mul2f(v[j], v[j + 1], v[j], v[j + 1], d0, d1);
+        }
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] += x8[j];

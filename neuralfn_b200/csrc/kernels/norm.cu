@@ -446,8 +446,8 @@ extern "C" int nfn_norm_backward_wb(const void* dy, const void* x, const float* 
 // stream this norm reads (dx is d(residual stream)), so that layer needs no separate pass.
 constexpr int NB2_MAX_THREADS = 1024;
 
-template <bool LAYER>
-__global__ void __launch_bounds__(NB2_MAX_THREADS)
+template <bool LAYER, int MAXT>
+__global__ void __launch_bounds__(MAXT)
 norm_bwd2_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                  const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
                  const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dresid,
@@ -505,7 +505,9 @@ norm_bwd2_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
     if (wpr > 1) {
       float* slot = s_red + ((size_t)((it & 1) * rpb + rslot) * wpr) * 2;
       if (lane == 0) { slot[wir * 2] = sg; slot[wir * 2 + 1] = sgn; }
-      __syncthreads();
+      // only the threads of this row meet (named barrier 1 + slot; at most 12 rows per block),
+      // so the rows of a block do not run in lock step
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + rslot), "r"(tpr) : "memory");
       sg = 0.f; sgn = 0.f;
       for (int k2 = 0; k2 < wpr; ++k2) { sg += slot[k2 * 2]; sgn += slot[k2 * 2 + 1]; }
     }
@@ -540,16 +542,18 @@ norm_bwd2_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
   }
 }
 
-// Sums the partial rows [nblk][3][C]: 32 columns per block, 8 row groups per block.
-__global__ void __launch_bounds__(256)
+// Sums the partial rows [nblk][3][C]: 32 columns per block, 32 row groups per block (the loads
+// of one thread are independent, so with few hundred partial rows the chain per thread is short).
+__global__ void __launch_bounds__(1024)
 norm_bwd2_final_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dw, __nv_bfloat16* __restrict__ db,
                        __nv_bfloat16* __restrict__ dcol, int nblk, int C, int accumulate) {
-  __shared__ float s[3][8][33];
+  __shared__ float s[3][32][33];
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int col = blockIdx.x * 32 + cx;
   float a[3] = {0.f, 0.f, 0.f};
   if (col < C) {
-    for (int r = ry; r < nblk; r += 8) {
+#pragma unroll 4
+    for (int r = ry; r < nblk; r += 32) {
 #pragma unroll
       for (int k = 0; k < 3; ++k) a[k] += partial[((size_t)r * 3 + k) * C + col];
     }
@@ -560,7 +564,7 @@ norm_bwd2_final_kernel(const float* __restrict__ partial, __nv_bfloat16* __restr
   if (ry < 3 && col < C) {
     float t = 0.f;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) t += s[ry][r][cx];
+    for (int r = 0; r < 32; ++r) t += s[ry][r][cx];
     __nv_bfloat16* out = ry == 0 ? dw : (ry == 1 ? db : dcol);
     if (out) out[col] = __float2bfloat16(t + (accumulate ? __bfloat162float(out[col]) : 0.f));
   }
@@ -578,28 +582,21 @@ extern "C" int nfn_norm_backward_ex(const void* dy, const void* x, const void* w
   if (C > 8 * NB2_MAX_THREADS) return fail(-1, "norm_backward: rows wider than 8192 are not supported");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int tpr = ((C / 8) + 31) / 32 * 32;               // threads per row, whole warps
-  const int rpb = std::max(1, 384 / tpr);                  // rows a block works on at a time
+  const int rpb = std::min(12, std::max(1, 384 / tpr));    // rows a block works on at a time (one named barrier each)
   const int threads = tpr * rpb;
   const int per_sm = std::max(1, 1536 / threads);
   const int grid = std::min(ceil_div(rows, rpb), std::min(per_sm * sm_count(), nfn_norm_fused_rows()));
   const size_t smem = ((size_t)rpb * tpr * 8 + (size_t)2 * rpb * (tpr / 32) * 2) * sizeof(float);
-  static bool attr[2][64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  const int li = mode == 0 ? 0 : 1;
-  if (smem > 48 * 1024 && !attr[li][dev & 63]) {
-    cudaError_t e = li == 0 ? cudaFuncSetAttribute(norm_bwd2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024)
-                            : cudaFuncSetAttribute(norm_bwd2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    if (e != cudaSuccess) return launch_check("norm_backward attr", 0);
-    attr[li][dev & 63] = true;
+#define NFN_NB2(L, M)                                                                                                       \
+  norm_bwd2_kernel<L, M><<<grid, threads, smem, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, mean, \
+                                                      rstd, (const __nv_bfloat16*)dresid, (__nv_bfloat16*)dx, scratch, rows, C, tpr, rpb, centered)
+  if (threads <= 512) {
+    if (mode == 0) NFN_NB2(true, 512); else NFN_NB2(false, 512);
+  } else {
+    if (mode == 0) NFN_NB2(true, 1024); else NFN_NB2(false, 1024);
   }
-  if (mode == 0)
-    norm_bwd2_kernel<true><<<grid, threads, smem, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, mean,
-                                                        rstd, (const __nv_bfloat16*)dresid, (__nv_bfloat16*)dx, scratch, rows, C, tpr, rpb, centered);
-  else
-    norm_bwd2_kernel<false><<<grid, threads, smem, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, mean,
-                                                         rstd, (const __nv_bfloat16*)dresid, (__nv_bfloat16*)dx, scratch, rows, C, tpr, rpb, centered);
-  norm_bwd2_final_kernel<<<ceil_div(C, 32), 256, 0, st>>>(scratch, (__nv_bfloat16*)dw, (__nv_bfloat16*)db, (__nv_bfloat16*)dx_colsum, grid, C,
+#undef NFN_NB2
+  norm_bwd2_final_kernel<<<ceil_div(C, 32), 1024, 0, st>>>(scratch, (__nv_bfloat16*)dw, (__nv_bfloat16*)db, (__nv_bfloat16*)dx_colsum, grid, C,
                                                           accumulate);
   return launch_check("norm_backward", 2);
 }

@@ -291,6 +291,51 @@ __device__ __forceinline__ float dgelu_tanh_f(float x) {
   float du = k0 * (1.f + 3.f * k1 * x2);
   return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
 }
+// ---- two-wide fp32 arithmetic (sm_100 fma/mul/add .f32x2: one issue slot for two lanes of work) ----
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void mul2f(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmul.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ void add2f(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tadd.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// tanh-GELU of two values: 0.5 x (1 + tanh(k0 (x + k1 x^3)))
+__device__ __forceinline__ void gelu_tanh_2(float& y0, float& y1, float x0, float x1) {
+  const float k0 = 0.7978845608028654f, k01 = 0.7978845608028654f * 0.044715f;
+  float q0, q1, i0, i1, u0, u1, h0, h1;
+  mul2f(q0, q1, x0, x1, x0, x1);
+  fma2(i0, i1, q0, q1, k01, k01, k0, k0);
+  mul2f(u0, u1, i0, i1, x0, x1);
+  const float t0 = fast_tanh(u0), t1 = fast_tanh(u1);
+  mul2f(h0, h1, x0, x1, 0.5f, 0.5f);
+  fma2(y0, y1, h0, h1, t0, t1, h0, h1);
+}
+// derivative of the tanh-GELU at two points
+__device__ __forceinline__ void dgelu_tanh_2(float& d0, float& d1, float x0, float x1) {
+  const float k0 = 0.7978845608028654f, k01 = 0.7978845608028654f * 0.044715f;
+  float q0, q1, i0, i1, u0, u1, du0, du1, a0, a1, b0, b1, xd0, xd1, e0, e1;
+  mul2f(q0, q1, x0, x1, x0, x1);
+  fma2(i0, i1, q0, q1, k01, k01, k0, k0);
+  mul2f(u0, u1, i0, i1, x0, x1);
+  const float t0 = fast_tanh(u0), t1 = fast_tanh(u1);
+  fma2(du0, du1, q0, q1, 3.f * k01, 3.f * k01, k0, k0);   // k0 (1 + 3 k1 x^2)
+  fma2(a0, a1, t0, t1, 0.5f, 0.5f, 0.5f, 0.5f);           // 0.5 (1 + t)
+  fma2(b0, b1, -t0, -t1, t0, t1, 1.f, 1.f);               // 1 - t^2
+  mul2f(xd0, xd1, x0, x1, du0, du1);
+  mul2f(e0, e1, xd0, xd1, b0, b1);
+  fma2(d0, d1, e0, e1, 0.5f, 0.5f, a0, a1);
+}
 __device__ __forceinline__ float gelu_erf_f(float x) {
   return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
 }
