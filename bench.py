@@ -114,6 +114,14 @@ def run_ours(args) -> dict:
         trainer.step_on_device_batch()
     trainer.check_status()
 
+    # ---- self-check of the fused compute + collective kernels on these very ranks (AG->GEMM,
+    # GEMM->RS, all-reduce + residual + norm, expert-parallel pull dispatch / combine) ----
+    fused = None
+    if world > 1 or args.check_fused:
+        from neuralfn_b200.parallel.fused_check import run_fused_check
+        fused = run_fused_check(torch.device("cuda", local))
+        barrier()
+
     # ---- device-timed region: K optimizer steps on a device-resident batch ----
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -163,6 +171,9 @@ def run_ours(args) -> dict:
         "final_loss": last_loss,
         "impl": "neuralfn_b200",
     }
+    if fused is not None:
+        out["fused_check"] = fused["status"]
+        out["fused_check_max_err"] = fused["max_err"]
     if world > 1:
         dist.destroy_process_group()
     return out if rank == 0 else {}
@@ -196,6 +207,8 @@ def main() -> None:
     ap.add_argument("--micro-batch", type=int, default=16)
     ap.add_argument("--seq-len", type=int, default=1024)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--check-fused", action="store_true",
+                    help="run the fused-collective kernel self-check also on one GPU (always on for N > 1)")
     args = ap.parse_args()
     out = run_reference(args) if args.impl == "reference" else run_ours(args)
     if out:
