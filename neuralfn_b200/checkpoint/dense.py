@@ -226,11 +226,21 @@ def load_dense_checkpoint(trainer, directory, step: int | None = None) -> dict:
         if m["world_size"] == opt.world:
             e = next(e for e in m["shards"] if e["rank"] == opt.rank)
             parts = [torch.empty(opt.shard, dtype=torch.float32) for _ in range(3)]
-            _, sha = read_container(d / e["file"], STATE_HEADER_BYTES, parts)
-            if sha != e["sha256"]:
-                raise ValueError(f"{e['file']}: checksum does not match the manifest")
+            raw, sha = read_container(d / e["file"], STATE_HEADER_BYTES, parts)
+            h = struct.unpack("<32q", raw)
+            # the shard's own header must describe this step, rank, world and slice: a manifest that points
+            # at a shard of another step (with a matching digest entry) must not load silently
+            if (h[0] != SHARD_MAGIC or h[2] != step or h[9] != opt.rank or h[10] != opt.world or e["lo"] != opt.lo
+                    or e["shard"] != opt.shard or sha != e["sha256"]):
+                raise ValueError(f"{e['file']}: header or checksum does not match the manifest / this rank's shard")
         else:  # re-shard through the consolidated form
-            parts = [t[lo:hi] for t in consolidate_sharded_optimizer(d, step, cfg)]
+            parts = []
+            for t in consolidate_sharded_optimizer(d, step, cfg):
+                # the saving world padded the flat buffer to a multiple of 8 * its size; this world pads
+                # to its own multiple. Only padding differs, so cut or zero-extend to this layout's length.
+                if t.numel() < layout.n_total:
+                    t = torch.cat([t, torch.zeros(layout.n_total - t.numel(), dtype=t.dtype)])
+                parts.append(t[:layout.n_total][lo:hi])
         for dst, src in zip((opt.master, opt.m, opt.v), parts):
             dst.copy_(src)
         restored.update(master=True, moments=True)

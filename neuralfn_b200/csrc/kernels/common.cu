@@ -187,6 +187,14 @@ int nfn_status_peek(void) {
   return v;
 }
 
+// Test hook: overwrite the status word of the current device from the host (what a kernel's
+// timed-out wait would have left there), so error handling can be exercised without a device fault.
+int nfn_status_set(int code) {
+  int* p = nfn::status_ptr();
+  if (!p) return -1;
+  return cudaMemcpy(p, &code, sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess ? 0 : -2;
+}
+
 const char* nfn_last_error(void) { return nfn::g_last_error.c_str(); }
 
 long long nfn_launch_count(void) { return nfn::launches(); }

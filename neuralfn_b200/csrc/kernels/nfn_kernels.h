@@ -23,6 +23,8 @@ int nfn_abi_version(void);
 int nfn_status_read_reset(void);
 // Same, but does not synchronise (reads whatever has landed) and does not clear.
 int nfn_status_peek(void);
+// Host-side test hook: sets the status word of the current device.
+int nfn_status_set(int code);
 const char* nfn_last_error(void);
 
 // ---- GEMM family (tcgen05 + TMEM + TMA) -------------------------------------

@@ -118,6 +118,28 @@ class _SyntheticBatches:
         return self.tok, self.tgt
 
 
+def _guard_device_status(trainer, what: str, *, sync: bool = True) -> None:
+    """Raise (so the process exits non-zero and a kill-siblings launcher stops the other ranks) when
+    any kernel recorded an error since the last check. ``sync=False`` only peeks at what has landed,
+    which costs no pipeline stall and is what the per-interval check uses."""
+    if sync:
+        trainer.check_status()
+        return
+    from .ops import _lib
+    code = int(_lib.load().nfn_status_peek())
+    if code > 0:
+        raise _lib.KernelLibraryError(f"{what}: device status {code} ({_lib.STATUS_NAMES.get(code, '?')}); aborting before anything is published")
+
+
+def save_checkpoint_checked(trainer, out_dir, step: int, *, dense_format: bool, sharded_optimizer: bool = False, grad_accum: int = 1):
+    """Write a checkpoint only after the device status word has been verified clean: a step that ran
+    on stale or partial gradients must never reach a DONE marker."""
+    _guard_device_status(trainer, f"checkpoint at step {step}")
+    if dense_format:
+        return save_dense_checkpoint(trainer, out_dir, step, sharded_optimizer=sharded_optimizer, grad_accum=grad_accum)
+    return save_named_checkpoint(trainer, out_dir, step)
+
+
 def _validate(trainer, loader_factory, n_batches: int) -> tuple[float, float]:
     """Mean loss over the first ``n_batches`` validation batches (a fixed slice); forward only."""
     torch.cuda.synchronize()
@@ -213,19 +235,22 @@ def run_native_training(c: NativeTrainConfig) -> dict:
             first_step_ms = (time.perf_counter() - s0) * 1e3
         if loss is not None:
             train_losses.append({"step": step, "loss": loss})
-        if c.progress_every and rank == 0 and step % c.progress_every == 0:
-            import sys
-            print(f"step {step}/{c.max_steps} lr {float(trainer.opt.hyper_host[0]):.3e}", file=sys.stderr, flush=True)
+        if c.progress_every and step % c.progress_every == 0:
+            # a bounded device wait that ran out (straggler, lost peer) leaves a code in the status word
+            # and lets the step continue on stale data: stop here rather than train on and publish it
+            _guard_device_status(trainer, f"step {step}", sync=False)
+            if rank == 0:
+                import sys
+                print(f"step {step}/{c.max_steps} lr {float(trainer.opt.hyper_host[0]):.3e}", file=sys.stderr, flush=True)
         if c.eval_every and (step % c.eval_every == 0 or step == c.max_steps):
+            _guard_device_status(trainer, f"validation at step {step}")
             vl, vms = _validate(trainer, val_factory, c.eval_batches)
             validation_ms += vms
             val_losses.append({"step": step, "loss": vl})
         if out_dir is not None and c.checkpoint_every and (step % c.checkpoint_every == 0 or step == c.max_steps):
             t0 = time.perf_counter()
-            if dense_format:
-                digests = save_dense_checkpoint(trainer, out_dir, step, sharded_optimizer=c.sharded_optimizer_checkpoint, grad_accum=accum)
-            else:
-                digests = save_named_checkpoint(trainer, out_dir, step)
+            digests = save_checkpoint_checked(trainer, out_dir, step, dense_format=dense_format,
+                                              sharded_optimizer=c.sharded_optimizer_checkpoint, grad_accum=accum)
             checkpoint_ms += (time.perf_counter() - t0) * 1e3
             if rank == 0:
                 ckpts.append({"step": step, "files": {k: {"sha256": v, "bytes": (out_dir / k).stat().st_size} for k, v in digests.items()}})

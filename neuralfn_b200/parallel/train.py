@@ -35,6 +35,14 @@ def _emit(rank: int, **ev) -> None:
         print(json.dumps(ev), flush=True)
 
 
+def _check_device_status(device, what: str) -> None:
+    """Raise when a kernel recorded an error (a bounded wait that ran out) since the last check."""
+    if torch.device(device).type != "cuda":
+        return
+    from ..ops import _lib
+    _lib.assert_status_ok(what)
+
+
 def save_parallel_checkpoint(trainer, out_dir: Path, step: int, extra: dict) -> Path:
     from ..checkpoint.safetensors_io import write_safetensors
     mdl = trainer.model
@@ -179,6 +187,7 @@ def main(argv=None) -> int:
                   grad_norm=float(trainer.clip[1]))
             last = now
         if out_dir is not None and a.checkpoint_every and (step % a.checkpoint_every == 0 or step == a.max_steps):
+            _check_device_status(dev, f"checkpoint at step {step}")  # never publish a step that ran on timed-out waits
             d = save_parallel_checkpoint(trainer, out_dir, step, {"parallel": a.parallel, "config": asdict(cfg)})
             _emit(rank, event="checkpoint", step=step, path=str(d))
     if cuda:

@@ -175,6 +175,8 @@ class DenseGPTTrainer:
             loss = self.train_step(tokens, targets)
             losses.append(loss)
             n += 1
+            if log_every and n % log_every == 0:
+                self.check_status()  # a timed-out device wait must stop the run, not poison later steps
             if log_every and n % log_every == 0 and self.rank == 0:
                 print(f"step {n:6d} loss {loss:.4f} lr {self.opt.hyper_host[0].item():.3e} "
                       f"gnorm {self.opt.grad_norm:.3f}", flush=True)
@@ -182,6 +184,7 @@ class DenseGPTTrainer:
                 break
         torch.cuda.synchronize(self.device)
         wall = (time.perf_counter() - t0) * 1e3
+        self.check_status()
         toks = n * self.tokens_per_step
         return TrainReport(n, toks, wall, toks / (wall / 1e3) if wall > 0 else 0.0, losses)
 

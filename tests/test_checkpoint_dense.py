@@ -109,3 +109,78 @@ def test_container_refuses_overwrite_symlink_and_wrong_size(tmp_path):
         read_container(p, 4, [torch.empty(5, dtype=torch.int32)])
     hdr, _ = read_container(p, 4, [torch.empty(4, dtype=torch.int32)])
     assert hdr == b"head"
+
+
+def _write_sharded_by_hand(tmp_path, cfg, world, step, fulls, params):
+    """What ``save_dense_checkpoint`` writes for ``world`` ranks, produced in one process."""
+    from neuralfn_b200.checkpoint import dense as D
+    layout = FlatLayout(gpt2_param_specs(cfg), world=world)
+    digests = {f"model_{step:08d}.bin": D.write_dense_model(tmp_path / f"model_{step:08d}.bin", cfg, layout, params[:layout.n_total])}
+    entries = []
+    for r in range(world):
+        lo = r * layout.shard
+        name = f"optimizer_{step:08d}.rank{r:05d}.bin"
+        hdr = D._state_header(D.SHARD_MAGIC, step, cfg, r, world, lo, layout.shard, layout.n_total)
+        sha = write_container(tmp_path / name, hdr, [t[lo:lo + layout.shard].contiguous() for t in fulls])
+        entries.append({"rank": r, "file": name, "sha256": sha, "lo": lo, "shard": layout.shard})
+        digests[name] = sha
+    (tmp_path / f"optimizer_{step:08d}.manifest.json").write_text(json.dumps(
+        {"schema": "neuralfn_b200.dense_sharded_optimizer.v1", "step": step, "world_size": world, "n_total": layout.n_total,
+         "geometry": D._geometry(cfg), "shards": entries}))
+    (tmp_path / f"DONE_{step:08d}").write_text(json.dumps(digests, sort_keys=True))
+    return layout
+
+
+def test_resharding_between_world_sizes_whose_padding_differs(tmp_path):
+    """Saved by 2 ranks, loaded by rank 2 of 3: the flat buffer is padded to a multiple of 8 * world, so
+    the two layouts have different lengths and the last rank's slice reaches into the padding."""
+    cfg = GPT2Config.variant("gpt2", n_layer=1, n_head=1, d_model=8, vocab_size=11, max_seq_len=5, vocab_pad_to=1)
+    specs = gpt2_param_specs(cfg)
+    l2, l3 = FlatLayout(specs, world=2), FlatLayout(specs, world=3)
+    assert l2.n_used % 24 != 0 and l2.n_total != l3.n_total
+    g = torch.Generator().manual_seed(0)
+    fulls = [torch.randn(l2.n_total, generator=g) for _ in range(3)]
+    for t in fulls:
+        t[l2.n_used:] = 0  # padding carries nothing
+    params = torch.zeros(max(l2.n_total, l3.n_total), dtype=torch.bfloat16)
+    params[:l2.n_used] = fulls[0][:l2.n_used].bfloat16()
+    _write_sharded_by_hand(tmp_path, cfg, 2, 5, fulls, params)
+    for rank in range(3):
+        lo = rank * l3.shard
+        opt = SimpleNamespace(world=3, rank=rank, lo=lo, shard=l3.shard, step_count=0,
+                              master=torch.empty(l3.shard), m=torch.empty(l3.shard), v=torch.empty(l3.shard))
+        bufs = SimpleNamespace(params=torch.zeros(l3.n_total, dtype=torch.bfloat16))
+        tr = SimpleNamespace(cfg=cfg, layout=l3, bufs=bufs, opt=opt, device=torch.device("cpu"))
+        got = load_dense_checkpoint(tr, tmp_path)
+        assert got["master"] and got["moments"]
+        for dst, full in zip((opt.master, opt.m, opt.v), fulls):
+            want = torch.zeros(l3.n_total)
+            want[:l2.n_used] = full[:l2.n_used]
+            assert torch.equal(dst, want[lo:lo + l3.shard]), rank
+
+
+def test_same_world_load_checks_the_shard_header(tmp_path):
+    """A manifest entry that points at a shard written for another step must be refused even when the
+    digest in the manifest matches that file."""
+    cfg = GPT2Config.variant("gpt2", n_layer=1, n_head=1, d_model=8, vocab_size=11, max_seq_len=5, vocab_pad_to=1)
+    specs = gpt2_param_specs(cfg)
+    layout = FlatLayout(specs, world=1)
+    fulls = [torch.randn(layout.n_total, generator=torch.Generator().manual_seed(i)) for i in range(3)]
+    params = fulls[0].bfloat16()
+    _write_sharded_by_hand(tmp_path, cfg, 1, 5, fulls, params)
+    other = tmp_path / "other"
+    other.mkdir()
+    _write_sharded_by_hand(other, cfg, 1, 9, fulls, params)
+    # swap in the step-9 shard under the step-5 name and make the manifest agree with its digest
+    blob = (other / "optimizer_00000009.rank00000.bin").read_bytes()
+    (tmp_path / "optimizer_00000005.rank00000.bin").write_bytes(blob)
+    import hashlib
+    man = json.loads((tmp_path / "optimizer_00000005.manifest.json").read_text())
+    man["shards"][0]["sha256"] = json.loads((other / "optimizer_00000009.manifest.json").read_text())["shards"][0]["sha256"]
+    (tmp_path / "optimizer_00000005.manifest.json").write_text(json.dumps(man))
+    opt = SimpleNamespace(world=1, rank=0, lo=0, shard=layout.shard, step_count=0,
+                          master=torch.empty(layout.shard), m=torch.empty(layout.shard), v=torch.empty(layout.shard))
+    tr = SimpleNamespace(cfg=cfg, layout=layout, bufs=SimpleNamespace(params=torch.zeros(layout.n_total, dtype=torch.bfloat16)),
+                         opt=opt, device=torch.device("cpu"))
+    with pytest.raises(ValueError, match="header or checksum"):
+        load_dense_checkpoint(tr, tmp_path)

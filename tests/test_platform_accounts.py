@@ -134,3 +134,40 @@ def test_rest_accounts_flow(tmp_path):
     c2 = TestClient(app2)
     c2.post("/api/auth/login", json={"email": "admin@x.io", "password": "admin-password"})
     assert c2.get(f"/api/projects/{pid}/sessions/{sid}/graph").json()["revision"] == 3
+
+
+def test_flat_session_routes_respect_project_membership(tmp_path):
+    """The flat /api/sessions routes address the same live store as project-bound sessions: a signed-in
+    user without a membership must not list, read, overwrite, run or delete another project's session."""
+    from fastapi.testclient import TestClient
+
+    from neuralfn_b200.server.app import create_app
+    from neuralfn_b200.server.platform_db import PlatformDB
+    db = PlatformDB(str(tmp_path / "p.db"))
+    db.create_user("admin@example.org", "root-pass-1", is_admin=True)
+    db.create_user("a@example.org", "alice-pass-1")
+    db.create_user("b@example.org", "bobby-pass-1")
+    app = create_app(db=db)
+    alice, bob = TestClient(app), TestClient(app)
+    assert alice.post("/api/auth/login", json={"email": "a@example.org", "password": "alice-pass-1"}).status_code == 200
+    assert bob.post("/api/auth/login", json={"email": "b@example.org", "password": "bobby-pass-1"}).status_code == 200
+    pid = alice.post("/api/projects", json={"name": "secret"}).json()["id"]
+    sid = alice.post(f"/api/projects/{pid}/sessions", json={"name": "g"}).json()["id"]
+    # the owner sees it through both route families
+    assert alice.get(f"/api/sessions/{sid}/graph").status_code == 200
+    assert any((r.get("id") or r.get("session_id")) == sid for r in alice.get("/api/sessions").json())
+    # a stranger does not
+    assert all((r.get("id") or r.get("session_id")) != sid for r in bob.get("/api/sessions").json())
+    assert bob.get(f"/api/sessions/{sid}/graph").status_code == 404
+    assert bob.put(f"/api/sessions/{sid}/graph", json={"name": "x", "nodes": {}, "edges": {}}).status_code == 404
+    assert bob.post(f"/api/sessions/{sid}/runs", json={"inputs": [[0.0]], "targets": [[0.0]]}).status_code == 404
+    assert bob.delete(f"/api/sessions/{sid}").status_code == 404
+    assert alice.get(f"/api/sessions/{sid}/graph").status_code == 200      # still there
+    # writes to a project-bound session must keep the revision check: the flat PUT refuses
+    assert alice.put(f"/api/sessions/{sid}/graph", json={"name": "x", "nodes": {}, "edges": {}}).status_code == 409
+    # flat sessions belong to their creator
+    own = bob.post("/api/sessions", json={"name": "mine"}).json()["session_id"]
+    assert bob.get(f"/api/sessions/{own}/graph").status_code == 200
+    assert alice.get(f"/api/sessions/{own}/graph").status_code == 404
+    # dataset paths: only granted assets
+    assert bob.post("/api/datasets/info", json={"path": str(tmp_path)}).status_code == 403
