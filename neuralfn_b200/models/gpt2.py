@@ -17,6 +17,7 @@ oracle for the tests and the CPU path.
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from dataclasses import dataclass, field
 from typing import Iterator
@@ -266,6 +267,11 @@ class GPT2Engine:
         self.ws = e(32 * 1024 * 1024, dtype=f32)  # split-K partial slices of the weight-gradient GEMMs
         self.tokens = torch.zeros(N, device=dev, dtype=torch.int32)
         self.targets = torch.zeros(N, device=dev, dtype=torch.int32)
+        self.timer = None  # optional utils.stage_timing.StageTimer (eager runs only)
+
+    def _stage(self, name: str):
+        t = self.timer
+        return t.stage(name) if t is not None and t.enabled else contextlib.nullcontext()
 
     # ------------------------------------------------------------------ forward --
     def forward(self, *, compute_grad_logits: bool = True, grad_scale: float | None = None) -> torch.Tensor:
@@ -274,36 +280,50 @@ class GPT2Engine:
         K, gemm, cfg, p = self.K, self.gemm, self.cfg, self.p
         B, T, N = self.B, self.T, self.B * self.T
         C, nh, hd = cfg.d_model, cfg.n_head, cfg.head_dim
-        K.embedding_forward(self.tokens, p["wte"], p["wpe"], T=T, out=self.x0)
+        st = self._stage
+        with st("embedding_residual.forward"):
+            K.embedding_forward(self.tokens, p["wte"], p["wpe"], T=T, out=self.x0)
         x = self.x0
         for l, a in enumerate(self.acts):
             pre = f"h.{l}."
-            K.norm_forward(x, p[pre + "ln_1.weight"], p[pre + "ln_1.bias"], eps=cfg.ln_eps,
-                           mode=K.NORM_LAYER, out=a.ln1, mean=a.ln1_mean, rstd=a.ln1_rstd)
-            gemm(a.ln1, p[pre + "attn.c_attn.weight"], bias=p[pre + "attn.c_attn.bias"], out=a.qkv)
-            if cfg.qk_norm:
-                K.qk_norm_forward(a.qkv, nh, nh, hd, eps=cfg.qk_norm_eps, rstd=a.qk_rstd)
-            K.attention_forward(a.qkv[:, :C], a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], B=B, T=T,
-                                n_q_heads=nh, n_kv_heads=nh, head_dim=hd, causal=True,
-                                out=a.att, lse=a.lse)
-            gemm(a.att, p[pre + "attn.c_proj.weight"], bias=p[pre + "attn.c_proj.bias"], resid=x, out=a.x1)
-            K.norm_forward(a.x1, p[pre + "ln_2.weight"], p[pre + "ln_2.bias"], eps=cfg.ln_eps,
-                           mode=K.NORM_LAYER, out=a.ln2, mean=a.ln2_mean, rstd=a.ln2_rstd)
-            gemm(a.ln2, p[pre + "mlp.c_fc.weight"], bias=p[pre + "mlp.c_fc.bias"], act="gelu_tanh",
-                 save_pre=a.fc_pre, out=a.fc_act)
-            gemm(a.fc_act, p[pre + "mlp.c_proj.weight"], bias=p[pre + "mlp.c_proj.bias"], resid=a.x1,
-                 out=a.x2)
+            with st("block_forward"):
+                with st("block_forward.attention.ln1"):
+                    K.norm_forward(x, p[pre + "ln_1.weight"], p[pre + "ln_1.bias"], eps=cfg.ln_eps,
+                                   mode=K.NORM_LAYER, out=a.ln1, mean=a.ln1_mean, rstd=a.ln1_rstd)
+                with st("block_forward.attention.qkv"):
+                    gemm(a.ln1, p[pre + "attn.c_attn.weight"], bias=p[pre + "attn.c_attn.bias"], out=a.qkv)
+                if cfg.qk_norm:
+                    with st("block_forward.attention.qk_norm"):
+                        K.qk_norm_forward(a.qkv, nh, nh, hd, eps=cfg.qk_norm_eps, rstd=a.qk_rstd)
+                with st("block_forward.attention.sdpa"):
+                    K.attention_forward(a.qkv[:, :C], a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], B=B, T=T,
+                                        n_q_heads=nh, n_kv_heads=nh, head_dim=hd, causal=True,
+                                        out=a.att, lse=a.lse)
+                with st("block_forward.attention.proj_residual"):
+                    gemm(a.att, p[pre + "attn.c_proj.weight"], bias=p[pre + "attn.c_proj.bias"], resid=x, out=a.x1)
+                with st("block_forward.mlp.ln2"):
+                    K.norm_forward(a.x1, p[pre + "ln_2.weight"], p[pre + "ln_2.bias"], eps=cfg.ln_eps,
+                                   mode=K.NORM_LAYER, out=a.ln2, mean=a.ln2_mean, rstd=a.ln2_rstd)
+                with st("block_forward.mlp.fc_gelu"):
+                    gemm(a.ln2, p[pre + "mlp.c_fc.weight"], bias=p[pre + "mlp.c_fc.bias"], act="gelu_tanh",
+                         save_pre=a.fc_pre, out=a.fc_act)
+                with st("block_forward.mlp.proj_residual"):
+                    gemm(a.fc_act, p[pre + "mlp.c_proj.weight"], bias=p[pre + "mlp.c_proj.bias"], resid=a.x1,
+                         out=a.x2)
             x = a.x2
-        K.norm_forward(x, p["ln_f.weight"], p["ln_f.bias"], eps=cfg.ln_eps, mode=K.NORM_LAYER,
-                       out=self.lnf, mean=self.lnf_mean, rstd=self.lnf_rstd)
-        if cfg.logit_softcap > 0:
-            gemm(self.lnf, p["wte"], act="tanh_cap", act_param=cfg.logit_softcap, out=self.logits)
-        else:
-            gemm(self.lnf, p["wte"], out=self.logits)
-        K.cross_entropy(self.logits, self.targets, vocab=cfg.vocab_size, cap=cfg.logit_softcap,
-                        z_coef=cfg.z_loss, grad_scale=(1.0 / N if grad_scale is None else grad_scale),
-                        loss_scale=1.0 / N, write_grad=compute_grad_logits, row_loss=self.row_loss,
-                        mean_loss=self.loss)
+        with st("lm_head.final_norm"):
+            K.norm_forward(x, p["ln_f.weight"], p["ln_f.bias"], eps=cfg.ln_eps, mode=K.NORM_LAYER,
+                           out=self.lnf, mean=self.lnf_mean, rstd=self.lnf_rstd)
+        with st("lm_head_backward.logits"):
+            if cfg.logit_softcap > 0:
+                gemm(self.lnf, p["wte"], act="tanh_cap", act_param=cfg.logit_softcap, out=self.logits)
+            else:
+                gemm(self.lnf, p["wte"], out=self.logits)
+        with st("lm_head_backward.ce"):
+            K.cross_entropy(self.logits, self.targets, vocab=cfg.vocab_size, cap=cfg.logit_softcap,
+                            z_coef=cfg.z_loss, grad_scale=(1.0 / N if grad_scale is None else grad_scale),
+                            loss_scale=1.0 / N, write_grad=compute_grad_logits, row_loss=self.row_loss,
+                            mean_loss=self.loss)
         return self.loss
 
     # ----------------------------------------------------------------- backward --
@@ -315,47 +335,65 @@ class GPT2Engine:
         C, nh, hd = cfg.d_model, cfg.n_head, cfg.head_dim
         sc = self.scratch
         dlogits = self.logits
+        st = self._stage
         # tied head: d(lnf) and d(wte)
-        gemm(dlogits, p["wte"], b_mn=True, out=self.d_ln)
-        gemm(dlogits, self.lnf, a_mn=True, b_mn=True, out=g["wte"])
+        with st("lm_head_backward.dhidden"):
+            gemm(dlogits, p["wte"], b_mn=True, out=self.d_ln)
+        with st("lm_head_backward.dweight"):
+            gemm(dlogits, self.lnf, a_mn=True, b_mn=True, out=g["wte"])
         x_last = self.acts[-1].x2 if self.acts else self.x0
         dx, spare = self.d_res_a, self.d_res_b
         L = cfg.n_layer
         # every norm backward also returns the column sum of the residual-stream gradient it
         # produces, which is the bias gradient of the projection that wrote that stream
-        K.norm_backward(self.d_ln, x_last, p["ln_f.weight"], self.lnf_mean, self.lnf_rstd, g["ln_f.weight"], g["ln_f.bias"], sc,
-                        mode=K.NORM_LAYER, out=dx, dx_colsum=g[f"h.{L - 1}.mlp.c_proj.bias"] if L > 0 else None)
+        with st("final_norm_backward"):
+            K.norm_backward(self.d_ln, x_last, p["ln_f.weight"], self.lnf_mean, self.lnf_rstd, g["ln_f.weight"], g["ln_f.bias"], sc,
+                            mode=K.NORM_LAYER, out=dx, dx_colsum=g[f"h.{L - 1}.mlp.c_proj.bias"] if L > 0 else None)
         for l in range(cfg.n_layer - 1, -1, -1):
             a = self.acts[l]
             pre = f"h.{l}."
             x_in = self.acts[l - 1].x2 if l > 0 else self.x0
-            # ---- MLP branch: x2 = c_proj(gelu(c_fc(ln2))) + x1 ----
-            gemm(dx, p[pre + "mlp.c_proj.weight"], b_mn=True, act="gelu_tanh", dact_pre=a.fc_pre,
-                 out=self.d_fc)
-            gemm(dx, a.fc_act, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "mlp.c_proj.weight"])
-            gemm(self.d_fc, p[pre + "mlp.c_fc.weight"], b_mn=True, out=self.d_ln)
-            gemm(self.d_fc, a.ln2, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "mlp.c_fc.weight"])
-            K.colsum(self.d_fc, g[pre + "mlp.c_fc.bias"], sc)
-            K.norm_backward(self.d_ln, a.x1, p[pre + "ln_2.weight"], a.ln2_mean, a.ln2_rstd, g[pre + "ln_2.weight"], g[pre + "ln_2.bias"], sc,
-                            mode=K.NORM_LAYER, dresid=dx, out=spare, dx_colsum=g[pre + "attn.c_proj.bias"])
-            dx, spare = spare, dx  # dx now holds d(x1)
-            # ---- attention branch: x1 = c_proj(att) + x ----
-            gemm(dx, p[pre + "attn.c_proj.weight"], b_mn=True, out=self.d_att)
-            gemm(dx, a.att, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "attn.c_proj.weight"])
-            K.attention_backward(self.d_att, a.qkv[:, :C], a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], a.att,
-                                 a.lse, B=B, T=T, n_q_heads=nh, n_kv_heads=nh, head_dim=hd, causal=True,
-                                 dq=self.d_qkv[:, :C], dk=self.d_qkv[:, C:2 * C], dv=self.d_qkv[:, 2 * C:],
-                                 delta=self.delta, dq_accum=self.dq_accum)
-            if cfg.qk_norm:
-                K.qk_norm_backward(self.d_qkv, a.qkv, a.qk_rstd, nh, nh, hd)
-            gemm(self.d_qkv, p[pre + "attn.c_attn.weight"], b_mn=True, out=self.d_ln)
-            gemm(self.d_qkv, a.ln1, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "attn.c_attn.weight"])
-            K.colsum(self.d_qkv, g[pre + "attn.c_attn.bias"], sc)
-            K.norm_backward(self.d_ln, x_in, p[pre + "ln_1.weight"], a.ln1_mean, a.ln1_rstd, g[pre + "ln_1.weight"], g[pre + "ln_1.bias"], sc,
-                            mode=K.NORM_LAYER, dresid=dx, out=spare,
-                            dx_colsum=g[f"h.{l - 1}.mlp.c_proj.bias"] if l > 0 else None)
-            dx, spare = spare, dx
-        K.embedding_backward(dx, self.tokens, g["wte"], g["wpe"][:T], B=B, T=T)
+            with st("block_backward"):
+                # ---- MLP branch: x2 = c_proj(gelu(c_fc(ln2))) + x1 ----
+                with st("block_backward.mlp_proj.dinput"):
+                    gemm(dx, p[pre + "mlp.c_proj.weight"], b_mn=True, act="gelu_tanh", dact_pre=a.fc_pre,
+                         out=self.d_fc)
+                with st("block_backward.mlp_proj.dweight_bias"):
+                    gemm(dx, a.fc_act, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "mlp.c_proj.weight"])
+                with st("block_backward.mlp_fc.dinput"):
+                    gemm(self.d_fc, p[pre + "mlp.c_fc.weight"], b_mn=True, out=self.d_ln)
+                with st("block_backward.mlp_fc.dweight_bias"):
+                    gemm(self.d_fc, a.ln2, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "mlp.c_fc.weight"])
+                    K.colsum(self.d_fc, g[pre + "mlp.c_fc.bias"], sc)
+                with st("block_backward.ln2_residual.fused_affine_dinput_add"):
+                    K.norm_backward(self.d_ln, a.x1, p[pre + "ln_2.weight"], a.ln2_mean, a.ln2_rstd, g[pre + "ln_2.weight"], g[pre + "ln_2.bias"], sc,
+                                    mode=K.NORM_LAYER, dresid=dx, out=spare, dx_colsum=g[pre + "attn.c_proj.bias"])
+                dx, spare = spare, dx  # dx now holds d(x1)
+                # ---- attention branch: x1 = c_proj(att) + x ----
+                with st("block_backward.attn_proj.dinput"):
+                    gemm(dx, p[pre + "attn.c_proj.weight"], b_mn=True, out=self.d_att)
+                with st("block_backward.attn_proj.dweight_bias"):
+                    gemm(dx, a.att, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "attn.c_proj.weight"])
+                with st("block_backward.attn_sdpa"):
+                    K.attention_backward(self.d_att, a.qkv[:, :C], a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], a.att,
+                                         a.lse, B=B, T=T, n_q_heads=nh, n_kv_heads=nh, head_dim=hd, causal=True,
+                                         dq=self.d_qkv[:, :C], dk=self.d_qkv[:, C:2 * C], dv=self.d_qkv[:, 2 * C:],
+                                         delta=self.delta, dq_accum=self.dq_accum)
+                if cfg.qk_norm:
+                    with st("block_backward.qk_norm"):
+                        K.qk_norm_backward(self.d_qkv, a.qkv, a.qk_rstd, nh, nh, hd)
+                with st("block_backward.qkv.dinput"):
+                    gemm(self.d_qkv, p[pre + "attn.c_attn.weight"], b_mn=True, out=self.d_ln)
+                with st("block_backward.qkv.dweight_bias"):
+                    gemm(self.d_qkv, a.ln1, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "attn.c_attn.weight"])
+                    K.colsum(self.d_qkv, g[pre + "attn.c_attn.bias"], sc)
+                with st("block_backward.ln1_residual.fused_affine_dinput_add"):
+                    K.norm_backward(self.d_ln, x_in, p[pre + "ln_1.weight"], a.ln1_mean, a.ln1_rstd, g[pre + "ln_1.weight"], g[pre + "ln_1.bias"], sc,
+                                    mode=K.NORM_LAYER, dresid=dx, out=spare,
+                                    dx_colsum=g[f"h.{l - 1}.mlp.c_proj.bias"] if l > 0 else None)
+                dx, spare = spare, dx
+        with st("embedding_backward"):
+            K.embedding_backward(dx, self.tokens, g["wte"], g["wpe"][:T], B=B, T=T)
         if T < cfg.max_seq_len:
             g["wpe"][T:].zero_()
 

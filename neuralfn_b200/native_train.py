@@ -275,6 +275,8 @@ def run_native_training(c: NativeTrainConfig) -> dict:
         "total_wall_ms": (time.perf_counter() - t_start) * 1e3, "kernel_launches_per_step": trainer.launches_per_step,
         "train_losses": train_losses, "validation": {"losses": val_losses, "fixed_validation_slice": c.eval_batches},
         "checkpoints": ckpts,
+        # per-stage CUDA-event times (NFN_NATIVE_GPT_STAGE_TIMING=1), field names of the reference's report
+        "timing": trainer.timer.report() if getattr(trainer, "timer", None) is not None else {"stage_timing_enabled": False},
     }
     if out_dir is not None and rank == 0:
         out_dir.mkdir(parents=True, exist_ok=True)

@@ -147,7 +147,9 @@ def resident_inference_capabilities() -> dict:
     return {"abi_version": resident_inference_abi_version(), "families": ["gpt2", "llama"], "kv_cache": "bf16",
             "hybrid_local_global": True, "qk_norm": True, "rope": ["hf", "legacy"], "continuous_batching": True,
             "cuda_graph_decode": True, "on_device_sampling": ["greedy", "temperature", "top_k", "top_p"],
-            "quantized_weights": ["Q4_K", "Q5_K", "Q6_K", "NF4"]}
+            # the engine executes bf16 weights only: K-quant / NF4 checkpoints are dequantised at load time
+            # (``quant.kquant`` / ``checkpoint.gguf``); the packed-weight kernels are not wired into it
+            "quantized_weights": [], "weight_dtypes": ["bf16"], "dequantised_at_load": ["Q4_K", "Q5_K", "Q6_K", "NF4"]}
 
 
 class EngineError(RuntimeError):

@@ -63,7 +63,11 @@ class DenseGPTTrainer:
         del master
         self.bufs.grads.zero_()
         self.engine = cfg.make_engine(self.layout, self.bufs.params, self.bufs.grads, batch, seq)
-        self.use_cuda_graph = use_cuda_graph
+        from ..utils.stage_timing import StageTimer
+        self.timer = StageTimer()  # NFN_NATIVE_GPT_STAGE_TIMING=1: per-stage CUDA events (+ NVTX with NFN_NVTX=1)
+        self.engine.timer = self.timer
+        # a captured graph cannot be timed stage by stage: the diagnostic mode runs eagerly
+        self.use_cuda_graph = use_cuda_graph and not self.timer.enabled
         # gradient accumulation: `grad_accum_steps` micro-batches per optimizer step, summed in
         # an fp32 side buffer; each phase of the cycle is its own captured graph
         self.grad_accum = max(1, int(grad_accum_steps))
@@ -93,7 +97,8 @@ class DenseGPTTrainer:
                                                  ctypes.c_float(1.0 / self.grad_accum), ctypes.c_void_p(_lib.stream_ptr()))
             _lib.check(rc, "nfn_grad_accumulate")
         if phase in ("single", "last"):
-            self.opt.launch_step()
+            with self.timer.stage("adamw_update"):  # gradient reduction, clip factor and the sharded update
+                self.opt.launch_step()
 
     def _run_step(self) -> None:
         """forward + backward (+ accumulate) (+ optimizer) on the batch already in the engine
@@ -124,11 +129,18 @@ class DenseGPTTrainer:
         if final:
             self.opt.step_count += 1
             self._micro = 0
+            self.timer.next_step()
         else:
             self._micro += 1
 
     def upload(self, tokens: torch.Tensor, targets: torch.Tensor) -> int:
         """Copy a batch into the device input buffers; returns the bytes moved host->device."""
+        moved = 0
+        with self.timer.stage("token_upload"):
+            moved = self._upload(tokens, targets)
+        return moved
+
+    def _upload(self, tokens: torch.Tensor, targets: torch.Tensor) -> int:
         moved = 0
         for src, stage, dst in ((tokens, self._h_tokens, self.engine.tokens),
                                 (targets, self._h_targets, self.engine.targets)):

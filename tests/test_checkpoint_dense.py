@@ -184,3 +184,36 @@ def test_same_world_load_checks_the_shard_header(tmp_path):
                          opt=opt, device=torch.device("cpu"))
     with pytest.raises(ValueError, match="header or checksum"):
         load_dense_checkpoint(tr, tmp_path)
+
+
+def test_model_file_is_accepted_by_the_reference_reader(tmp_path):
+    """The dense-v5 model file is a byte-for-byte contract: the reference's own pure-Python inspector
+    (``neuralfn/native_dense_checkpoint.py``, importable from the ``baseline/_ref`` install) must accept
+    our file and report the same geometry, tensor order, offsets, per-tensor digests and file digest."""
+    import hashlib
+    import importlib.util
+    import sys
+    from pathlib import Path
+    ref_file = Path(__file__).resolve().parent.parent / "baseline" / "_ref" / "neuralfn" / "native_dense_checkpoint.py"
+    if not ref_file.exists():
+        pytest.skip("the reference package is not installed under baseline/_ref")
+    spec = importlib.util.spec_from_file_location("_ref_native_dense_checkpoint", ref_file)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod   # dataclasses resolve their module through sys.modules
+    try:
+        spec.loader.exec_module(mod)
+    finally:
+        sys.modules.pop(spec.name, None)
+    tr = _cpu_trainer()
+    digests = save_dense_checkpoint(tr, tmp_path, sharded_optimizer=False)
+    info = mod.inspect_native_dense_checkpoint(tmp_path / "model_00000007.bin")
+    assert (info.max_seq_len, info.vocab_size, info.num_layers, info.num_heads, info.channels, info.padded_vocab_size) == (16, 100, 2, 2, 32, 128)
+    assert info.sha256 == digests["model_00000007.bin"]
+    ours = gpt2_param_specs(tr.cfg)
+    assert info.parameter_count == sum(s.numel for s in ours) and len(info.tensors) == len(ours)
+    raw = (tmp_path / "model_00000007.bin").read_bytes()
+    for t, s in zip(info.tensors, ours):
+        assert tuple(t.shape) == tuple(s.shape), (t.name, s.name)
+        want = tr.layout.view(tr.bufs.params, s.name).contiguous().view(torch.uint8).numpy().tobytes()
+        assert raw[t.offset:t.offset + t.nbytes] == want, s.name          # same tensor at the reference's offset
+        assert t.sha256 == hashlib.sha256(want).hexdigest()

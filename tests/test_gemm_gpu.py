@@ -16,6 +16,11 @@ def _close(out, ref, k):
     err = (out.float() - ref).abs().max().item()
     scale = ref.abs().max().item() + 1e-6
     assert err <= tol * scale / 4 + 1e-2, f"max err {err} (scale {scale})"
+    # the element-wise bound above only catches mis-indexed tiles; a dropped k-slice at large K changes
+    # every element a little, which the relative Frobenius error sees (bf16 output rounding alone
+    # gives about 1.7e-3)
+    fro = ((out.float() - ref).norm() / (ref.norm() + 1e-12)).item()
+    assert fro <= 4e-3, f"relative Frobenius error {fro}"
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
