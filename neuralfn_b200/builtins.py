@@ -53,7 +53,7 @@ def _default_config(module_type: str) -> dict:
         "load_balance_loss": {"experts": 8}, "aux_loss_add": {"coef": 0.01}, "loss_scale": {"coef": 1.0},
         "tensor_scale": {"scale": 1.0}, "mamba": {"model_dim": d}, "ttt_linear": {"input_dim": d, "output_dim": d},
         "universal_transformer": {"model_dim": d, "num_heads": h}, "act_halt_gate": {"model_dim": d},
-        "attentionless_decoder": {"model_dim": d}, "jepa_projector": {"input_dim": d, "latent_dim": d},
+        "running_mean_decoder": {"model_dim": d}, "attentionless_decoder": {"vocab_size": g["vocab_size"]}, "jepa_projector": {"input_dim": d, "latent_dim": d},
         "jepa_predictor": {"latent_dim": d}, "mask_scheduler": {"vocab_size": g["vocab_size"], "mask_token_id": 0},
         "denoise_head": {"model_dim": d, "vocab_size": g["vocab_size"]}, "byte_patch_embed": {"model_dim": d},
         "reward_head": {"model_dim": d}, "masked_reward_head": {"model_dim": d}, "value_head": {"model_dim": d},

@@ -137,11 +137,33 @@ class CompiledTorchGraph(nn.Module):
             cur += n
         return table
 
+    def enable_activation_checkpointing(self, enabled: bool = True) -> int:
+        """Recompute decoder blocks in the backward pass instead of keeping their activations: every
+        subgraph node whose id ends in ``block_<n>`` (here and in nested graphs) runs under
+        ``torch.utils.checkpoint`` while gradients are enabled. Returns the number of such nodes."""
+        import re
+        count = 0
+        self._checkpointed = set()
+        for ins in self._program:
+            mod = self.node_modules[ins.node_id]
+            if ins.kind == "subgraph" and re.search(r"(^|_)block_\d+$", ins.node_id):
+                if enabled:
+                    self._checkpointed.add(ins.node_id)
+                count += 1
+            elif isinstance(mod, CompiledTorchGraph):
+                count += mod.enable_activation_checkpointing(enabled)
+        return count
+
     def forward(self, *flat_inputs: Tensor) -> tuple[Tensor, ...]:
         table = self._seed(flat_inputs)
         mods = self.node_modules
+        ckpt = getattr(self, "_checkpointed", None)
         for ins in self._program:
-            out = mods[ins.node_id](*[table[s][p] for s, p in ins.args])
+            if ckpt and ins.node_id in ckpt and torch.is_grad_enabled():
+                from torch.utils.checkpoint import checkpoint
+                out = checkpoint(mods[ins.node_id], *[table[s][p] for s, p in ins.args], use_reentrant=False)
+            else:
+                out = mods[ins.node_id](*[table[s][p] for s, p in ins.args])
             table[ins.slot] = out if isinstance(out, tuple) else (tuple(out) if isinstance(out, list) else (out,))
         flat: list[Tensor] = []
         for s in self._output_slots:

@@ -140,7 +140,7 @@ class _AttentionFn(torch.autograd.Function):
     """q [B, Hq, T, D], k/v [B, Hkv, T, D] (bf16) -> [B, Hq, T, D]."""
 
     @staticmethod
-    def forward(ctx, q, k, v, causal, window, scale):
+    def forward(ctx, q, k, v, causal, window, scale, softcap=0.0, seq_ids=None):
         K = _K()
         B, Hq, T, D = q.shape
         Hkv = k.shape[1]
@@ -149,22 +149,48 @@ class _AttentionFn(torch.autograd.Function):
         kp = k.transpose(1, 2).reshape(B * T, Hkv * D).contiguous()
         vp = v.transpose(1, 2).reshape(B * T, Hkv * D).contiguous()
         o, lse = K.attention_forward(qp, kp, vp, B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D,
-                                     causal=causal, window=window, scale=scale)
+                                     causal=causal, window=window, scale=scale, softcap=softcap, seq_ids=seq_ids)
         ctx.save_for_backward(qp, kp, vp, o, lse)
-        ctx.meta = (B, T, Hq, Hkv, D, causal, window, scale)
+        ctx.meta = (B, T, Hq, Hkv, D, causal, window, scale, softcap)
+        ctx.seq_ids = seq_ids
         return o.view(B, T, Hq, D).transpose(1, 2)
 
     @staticmethod
     def backward(ctx, do):
         K = _K()
         qp, kp, vp, o, lse = ctx.saved_tensors
-        B, T, Hq, Hkv, D, causal, window, scale = ctx.meta
+        B, T, Hq, Hkv, D, causal, window, scale, softcap = ctx.meta
         dop = do.transpose(1, 2).reshape(B * T, Hq * D).contiguous()
         dq, dk, dv = torch.empty_like(qp), torch.empty_like(kp), torch.empty_like(vp)
         K.attention_backward(dop, qp, kp, vp, o, lse, B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D,
-                             causal=causal, window=window, scale=scale, dq=dq, dk=dk, dv=dv)
+                             causal=causal, window=window, scale=scale, softcap=softcap, seq_ids=ctx.seq_ids,
+                             dq=dq, dk=dk, dv=dv)
         return (dq.view(B, T, Hq, D).transpose(1, 2), dk.view(B, T, Hkv, D).transpose(1, 2),
-                dv.view(B, T, Hkv, D).transpose(1, 2), None, None, None)
+                dv.view(B, T, Hkv, D).transpose(1, 2), None, None, None, None, None)
+
+
+def segment_attention(q: Tensor, k: Tensor, v: Tensor, seq_ids: Tensor, *, causal: bool = False,
+                      scale: float | None = None) -> Tensor:
+    """Attention over packed sequences: q/k/v [B, H, T, D], ``seq_ids`` int [B, T]; a key is visible
+    only to queries of its own segment. On the native path one kernel launch covers all segments
+    (the flash kernels mask by sequence id and skip key blocks outside the visible range of a
+    causal tile); head dims other than 64 / 128 are zero-padded up, which leaves scores and
+    outputs unchanged. Elsewhere: scaled-dot-product attention under a block-diagonal mask."""
+    q, k, v = _autocast_bf16(q, k, v)
+    D = q.shape[-1]
+    sc = float(scale if scale is not None else D ** -0.5)
+    if _native_ok(q, k, v) and D <= 128 and q.shape[1] % k.shape[1] == 0 and q.shape[-2] == k.shape[-2]:
+        Dp = 64 if D <= 64 else 128
+        if Dp != D:
+            q, k, v = (F.pad(t, (0, Dp - D)) for t in (q, k, v))
+        ids = seq_ids.reshape(-1).to(torch.int32).contiguous()
+        out = _AttentionFn.apply(q, k, v, bool(causal), 0, sc, 0.0, ids)
+        return out[..., :D] if Dp != D else out
+    same = seq_ids.unsqueeze(-1) == seq_ids.unsqueeze(-2)                      # [B, T, T]
+    if causal:
+        same = same & torch.ones(same.shape[-2:], dtype=torch.bool, device=same.device).tril()
+    return F.scaled_dot_product_attention(q, k, v, attn_mask=same.unsqueeze(1), scale=sc,
+                                          enable_gqa=q.size(1) != k.size(1))
 
 
 def attention(q: Tensor, k: Tensor, v: Tensor, *, causal: bool = True, window: int = 0, dropout_p: float = 0.0,
@@ -174,7 +200,7 @@ def attention(q: Tensor, k: Tensor, v: Tensor, *, causal: bool = True, window: i
     same_len = q.shape[-2] == k.shape[-2]
     if (_native_ok(q, k, v) and D in (64, 128) and dropout_p == 0.0 and same_len and not math_path
             and q.shape[1] % k.shape[1] == 0):
-        return _AttentionFn.apply(q, k, v, bool(causal), int(window), float(scale or D ** -0.5))
+        return _AttentionFn.apply(q, k, v, bool(causal), int(window), float(scale or D ** -0.5), 0.0, None)
     if window and window > 0:
         from .stages_attention import sparse_attention_mask
         mask = sparse_attention_mask(q.size(-2), k.size(-2), is_causal=causal, window=window, num_sinks=0,

@@ -84,18 +84,42 @@ MODULE_PORTS: dict[str, tuple[tuple[str, ...], tuple[str, ...]]] = {
     # sequence-model variants / JEPA / diffusion / bytes
     "mamba": (("x",), ("y",)), "ttt_linear": (("x",), ("y",)), "universal_transformer": (("x",), ("y",)),
     "act_halt_gate": (("x",), ("p",)), "act_weighted_sum": (("states", "weights"), ("y",)),
-    "attentionless_decoder": (("x",), ("y",)),
+    "running_mean_decoder": (("x",), ("y",)),
     "jepa_mask": (("tokens",), ("context_tokens", "mask")), "latent_pool": (("hidden", "mask"), ("latent",)),
     "jepa_projector": (("x",), ("z",)), "jepa_predictor": (("z",), ("z",)),
     "random_timesteps": (("tokens",), ("timesteps",)),
     "mask_scheduler": (("tokens", "timesteps"), ("noisy_tokens", "mask")),
     "denoise_head": (("hidden",), ("logits",)),
     "byte_patch_embed": (("tokens",), ("patches",)), "byte_patch_merge": (("patches", "like"), ("hidden",)),
+    # semantic routing
+    "semantic_projector": (("hidden",), ("semantic_vec", "residual", "topic_logits")),
+    "semantic_chunk_projector": (("chunk_state",), ("semantic_vec", "residual", "topic_logits")),
+    "semantic_alignment_loss": (("pred_logits", "target"), ("loss",)),
+    "semantic_hasher": (("semantic_vec",), ("bucket_indices",)),
+    "semantic_chunk_hasher": (("semantic_vec",), ("bucket_indices",)),
+    "semantic_moe_router": (("semantic_vec",), ("expert_weights", "expert_indices")),
+    "semantic_hash_router": (("semantic_vec", "bucket_indices", "topic_logits", "sem_targets"),
+                             ("expert_weights", "expert_indices")),
+    "causal_chunk_state": (("hidden",), ("chunk_state",)),
+    "semantic_moe_jepa_evo_router": (("semantic_vec", "bucket_indices", "topic_logits", "sem_targets"),
+                                     ("expert_weights", "expert_indices", "route_logits")),
+    "broadcast_chunk_routes": (("hidden", "expert_weights", "expert_indices"), ("routing_weights", "routing_indices")),
+    "route_balance_loss": (("route_logits",), ("loss",)),
+    "route_selection_loss": (("route_logits", "sem_targets"), ("loss",)),
+    "route_distillation_loss": (("student_route_logits", "target_topic_logits"), ("loss",)),
+    "routed_attention_experts": (("hidden", "expert_weights", "expert_indices"), ("hidden_out",)),
+    "attentionless_decoder": (("bucket_indices", "expert_output"), ("logits",)),
+    "semantic_unforced_targets": (("hidden",), ("sem_targets",)),
+    "semantic_targets_from_tokens": (("tokens",), ("sem_targets",)),
+    # vision
+    "muse_glimmer_vision_tower": (("pixel_values", "grid_thw"), ("merged_patches",)),
+    "muse_glimmer_perception_norm": (("features",), ("normalized",)),
+    "muse_glimmer_media_scatter": (("embeddings", "token_ids", "features"), ("fused_embeddings",)),
 }
 
 _TOKEN_PORTS = {"tokens", "target_ids", "targets", "indices", "context_tokens", "noisy_tokens",
                 "chosen_tokens", "rejected_tokens", "chosen_targets", "rejected_targets",
-                "block_positions", "context_positions"}
+                "block_positions", "context_positions", "token_ids", "sem_targets", "target"}
 
 
 def _port(name: str) -> Port:

@@ -35,7 +35,7 @@ def stage(*names: str):
 def build_module(module_type: str, module_config: dict[str, Any] | None = None, tile_cuda_config: Any = None) -> nn.Module:
     """Instantiate the stage registered for ``module_type`` from its JSON config."""
     from . import (stages_attention, stages_attention_blocks, stages_linear, stages_losses,  # noqa: F401
-                   stages_moe, stages_misc)
+                   stages_moe, stages_misc, stages_semantic, stages_vision)
     cfg = dict(module_config or {})
     cfg["__module_type__"] = module_type
     try:

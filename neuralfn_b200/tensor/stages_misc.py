@@ -370,8 +370,8 @@ class BytePatchMergeStage(nn.Module):
         return up[:, :t]
 
 
-@stage("attentionless_decoder")
-class AttentionlessDecoderStage(nn.Module):
+@stage("running_mean_decoder")
+class RunningMeanDecoderStage(nn.Module):
     """Token-mixing-free decoder block: norm -> gated MLP with a causal running mean as context."""
 
     def __init__(self, model_dim: int, mlp_mult: float = 4.0) -> None:

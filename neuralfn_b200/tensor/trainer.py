@@ -311,13 +311,30 @@ class TorchTrainer:
         compiled = CompiledTorchGraph(self.graph, kernel_backend=c.kernel_backend)
         self.compiled = compiled
         self._apply_finetune_prehook(compiled)
+        template_spec = dict(self.graph.torch_config.get("template_spec") or {})
+        tensors = self._complete_semantic_inputs(tensors, compiled, template_spec)
+        self._prepare_ema_targets(compiled)
+        if c.activation_checkpointing and not c.evolutionary:
+            compiled.enable_activation_checkpointing()
         device = self._device()
         amp_dtype, amp_name, use_amp = resolve_amp_settings(self.graph.torch_config.get("amp_dtype", c.amp_dtype)
                                                             if c.amp_dtype == "float32" else c.amp_dtype)
         use_amp = use_amp and device.type == "cuda"
         compiled.to(device)
-        run: nn.Module = torch.compile(compiled) if c.compile else compiled
-        optimizers = self._build_optimizers(compiled)
+        run: nn.Module = torch.compile(compiled) if (c.compile and not c.evolutionary) else compiled
+        from . import evolution as evo
+        layer_cfg = None if c.evolutionary else evo.layer_evo_config(template_spec)
+        layer_params: list[Tensor] = []
+        if layer_cfg is not None:
+            layer_params = evo.layer_evo_parameters(compiled, layer_cfg["layer_index"])
+            if not layer_params:
+                raise ValueError(f"layer_evo_index={layer_cfg['layer_index']} matched no parameters; expected a transformer "
+                                 f"block index in [0, {int(template_spec.get('num_layers', 0)) - 1}]")
+            for p in layer_params:      # this block is trained by evolution only
+                p.requires_grad_(False)
+        route_cfg = None if c.evolutionary else evo.route_evo_config(template_spec)
+        route_params = evo.route_evo_parameters(compiled) if route_cfg is not None else []
+        optimizers = [] if c.evolutionary else self._build_optimizers(compiled)
         self._optimizers = optimizers
         base_lrs = [[g["lr"] for g in o.param_groups] for o in optimizers]
         if self._resume_state is not None:
@@ -340,7 +357,18 @@ class TorchTrainer:
         total_steps = c.max_steps or steps_per_epoch * c.epochs
         routing = compiled.routing_modules()
         params = [p for p in compiled.parameters() if p.requires_grad]
+        owner_of = self._shard_optimizer_state(optimizers, params, world) if (c.fsdp2_enabled and world > 1) else None
         start = time.perf_counter()
+        autocast = lambda: torch.autocast(device_type=device.type, dtype=amp_dtype, enabled=use_amp)  # noqa: E731
+        extract = lambda out: self._extract_scalar_loss(out, self.graph.name)  # noqa: E731
+        population = None
+        if c.evolutionary:
+            if not params:
+                raise ValueError("Evolutionary torch training requires at least one trainable parameter")
+            population = evo.Population(torch.nn.utils.parameters_to_vector(params), evo.EvolutionSettings.from_train_config(c))
+            self.graph.torch_config["evolutionary"] = population.s.as_dict()
+        else:
+            self.graph.torch_config.pop("evolutionary", None)
         gen = torch.Generator().manual_seed(int(c.seed if c.seed is not None else 0) + self.global_step)
         self._stop = False
         for epoch in range(c.epochs):
@@ -357,15 +385,46 @@ class TorchTrainer:
                 for m in routing:
                     m.reset_routing_accum()
                 step_loss, step_rows = torch.zeros((), device=device), 0
+                macro: list[tuple[Tensor, ...]] = []
                 for _a in range(accum):
                     idx = perm[cursor:cursor + c.batch_size]
                     if idx.numel() == 0 or (drop_last and idx.numel() < c.batch_size):
                         cursor = 0
                         idx = perm[:c.batch_size]
                     cursor += c.batch_size
-                    batch = tuple(t[idx].to(device, non_blocking=True) for t in tensors)
-                    with torch.autocast(device_type=device.type, dtype=amp_dtype, enabled=use_amp):
-                        loss = self._extract_scalar_loss(run(*batch), self.graph.name)
+                    macro.append(tuple(t[idx].to(device, non_blocking=True) for t in tensors))
+                extra_info: dict[str, Any] = {}
+                if population is not None:
+                    # one generation: score every member on this step's batches, keep the best in the model
+                    scored = [evo.evaluate_candidate(run, row, params, macro, extract=extract, autocast=autocast, routing=routing)
+                              for row in population.members]
+                    scores = torch.stack([sc[0] for sc in scored])
+                    best = int(scores.argmin())
+                    with torch.no_grad():
+                        torch.nn.utils.vector_to_parameters(population.members[best].to(params[0].dtype), params)
+                    step_rows = scored[best][1]
+                    step_loss = scores[best] * step_rows
+                    if scored[best][2]:
+                        extra_info["routing_stats"] = scored[best][2]
+                    population.next_generation(scores)
+                    self._ema_update(compiled)
+                    loss_total = float(step_loss.item())
+                    total_loss += loss_total
+                    total_rows += step_rows
+                    self.global_step += 1
+                    if on_step is not None:
+                        on_step({"phase": "train", "optimization_method": "evolutionary", "step": self.global_step,
+                                 "max_steps": int(total_steps), "epoch": epoch + 1, "max_epochs": c.epochs,
+                                 "steps_per_epoch": steps_per_epoch, "loss": loss_total / max(step_rows, 1),
+                                 "elapsed_seconds": time.perf_counter() - start, "grad_accum_steps": accum,
+                                 "learning_rates": [], "population_size": population.s.population_size, **extra_info})
+                    if c.max_wallclock_seconds > 0 and time.perf_counter() - start >= c.max_wallclock_seconds:
+                        self._stop = True
+                        break
+                    continue
+                for batch in macro:
+                    with autocast():
+                        loss = extract(run(*batch))
                     (loss / accum).backward()
                     for m in routing:
                         m.add_to_routing_accum()
@@ -389,7 +448,22 @@ class TorchTrainer:
                     torch.nn.utils.clip_grad_norm_(params, c.grad_clip_norm)
                 for o in optimizers:
                     o.step()
+                if owner_of is not None:
+                    self._broadcast_owned_params(params, owner_of, world)
                 self._ema_update(compiled)
+                stats_before_evo = [m.merged_routing_stats() for m in routing]
+                if evo.evolution_interval_due(route_cfg, self.global_step) and route_params:
+                    info_r = evo.partial_evolution_step(run, route_params, macro, extract=extract, autocast=autocast, routing=routing,
+                                                        population=route_cfg["population"], mutation_scale=route_cfg["mutation_scale"],
+                                                        seed=route_cfg["seed"], step=self.global_step)
+                    if info_r is not None:
+                        extra_info["route_evo"] = info_r
+                if evo.evolution_interval_due(layer_cfg, self.global_step) and layer_params:
+                    info_l = evo.partial_evolution_step(run, layer_params, macro, extract=extract, autocast=autocast, routing=routing,
+                                                        population=layer_cfg["population"], mutation_scale=layer_cfg["mutation_scale"],
+                                                        seed=layer_cfg["seed"], step=self.global_step)
+                    if info_l is not None:
+                        extra_info["layer_evo"] = {**info_l, "layer_index": int(layer_cfg["layer_index"])}
                 loss_total = float(step_loss.item())
                 total_loss += loss_total
                 total_rows += step_rows
@@ -400,9 +474,9 @@ class TorchTrainer:
                             "steps_per_epoch": steps_per_epoch, "loss": loss_total / max(step_rows, 1),
                             "elapsed_seconds": time.perf_counter() - start, "grad_accum_steps": accum,
                             "learning_rates": [g["lr"] for o in optimizers for g in o.param_groups]}
-                    stats = [m.merged_routing_stats() for m in routing]
-                    if any(stats):
-                        info["routing_stats"] = [s for s in stats if s]
+                    if any(stats_before_evo):
+                        info["routing_stats"] = [s for s in stats_before_evo if s]
+                    info.update(extra_info)
                     on_step(info)
                 if c.max_wallclock_seconds > 0 and time.perf_counter() - start >= c.max_wallclock_seconds:
                     self._stop = True
@@ -415,15 +489,120 @@ class TorchTrainer:
         compiled.sync_state_back()
         return self.loss_history
 
-    def _ema_update(self, compiled: nn.Module) -> None:
-        spec = (self.graph.torch_config.get("template_spec") or {})
-        objective = str((spec.get("template") or {}).get("objective", "ar"))
-        if "jepa" not in objective:
-            return
-        decay = float(spec.get("ema_decay", 0.99))
-        targets = getattr(compiled, "_ema_pairs", None)
-        if not targets:
-            return
+    # -------------------------------------------------------- EMA target encoders --
+    @staticmethod
+    def _ema_groups(compiled: nn.Module) -> list[tuple[list[Tensor], list[Tensor], list[tuple[Tensor, Tensor]], nn.Module]]:
+        """For every ``target_encoder`` node: (target params, matching online params, buffer pairs).
+        The online side is the sibling ``online_encoder`` when there is one; otherwise (the trunk is
+        the online network) the sibling nodes that carry the same names as the target encoder's
+        backbone nodes, and ``online_projector`` for its projector."""
+        groups = []
+
+        def visit(g: nn.Module) -> None:
+            mods = getattr(g, "node_modules", None)
+            if mods is None:
+                return
+            for child in mods.values():
+                if isinstance(child, CompiledTorchGraph):
+                    visit(child)
+            if "target_encoder" not in mods:
+                return
+            target = mods["target_encoder"]
+            if "online_encoder" in mods:
+                online_p = dict(mods["online_encoder"].named_parameters())
+                online_b = dict(mods["online_encoder"].named_buffers())
+            else:
+                online_p, online_b = {}, {}
+                for name, mod in mods.items():
+                    if name == "target_encoder":
+                        continue
+                    alias = {"online_projector": "node_modules.projector"}.get(name, f"node_modules.backbone.node_modules.{name}")
+                    for k, v in mod.named_parameters():
+                        online_p[f"{alias}.{k}"] = v
+                    for k, v in mod.named_buffers():
+                        online_b[f"{alias}.{k}"] = v
+            tp, op, bufs = [], [], []
+            for k, v in target.named_parameters():
+                src = online_p.get(k)
+                if src is not None and src.shape == v.shape:
+                    tp.append(v)
+                    op.append(src)
+            for k, v in target.named_buffers():
+                src = online_b.get(k)
+                if src is not None and src.shape == v.shape:
+                    bufs.append((v, src))
+            groups.append((tp, op, bufs, target))
+
+        visit(compiled)
+        return groups
+
+    def _prepare_ema_targets(self, compiled: nn.Module) -> None:
+        """Target encoders start as copies of their online networks and never receive gradients."""
+        self._ema = self._ema_groups(compiled)
         with torch.no_grad():
-            for tgt, src in targets:
-                tgt.mul_(decay).add_(src.detach(), alpha=1 - decay)
+            for tp, op, bufs, target in self._ema:
+                for t, o in zip(tp, op):
+                    t.copy_(o)
+                for t, o in bufs:
+                    t.copy_(o)
+                for p in target.parameters():
+                    p.requires_grad_(False)
+
+    def _ema_update(self, compiled: nn.Module) -> None:
+        """target <- decay * target + (1 - decay) * online, as one multi-tensor lerp per encoder."""
+        groups = getattr(self, "_ema", None)
+        if not groups:
+            return
+        decay = float((self.graph.torch_config.get("template_spec") or {}).get("ema_decay", 0.99))
+        with torch.no_grad():
+            for tp, op, bufs, _target in groups:
+                if tp:
+                    torch._foreach_lerp_(tp, [o.detach() for o in op], 1.0 - decay)
+                for t, o in bufs:
+                    t.copy_(o)
+
+    # ------------------------------------------------- semantic targets / sharding --
+    @staticmethod
+    def _complete_semantic_inputs(tensors: list[Tensor], compiled: CompiledTorchGraph, template_spec: dict) -> list[Tensor]:
+        """Semantic objectives take a third input (one target topic per vocabulary dimension). When the
+        caller passes only tokens and targets, derive it from the tokens through the token -> topic
+        table (``semantic_table_path``; a deterministic synthetic table without one)."""
+        names = [compiled.graph.nodes[n].neuron_def.output_ports[0].name for n in compiled.graph.input_node_ids]
+        if len(tensors) + 1 == len(names) and names[-1] == "sem_targets":
+            from .stages_semantic import SemanticTargetsFromTokensStage
+            stage = SemanticTargetsFromTokensStage(int(template_spec.get("vocab_size", 0) or int(tensors[0].max()) + 1),
+                                                   str(template_spec.get("semantic_vocab_ref", "")),
+                                                   str(template_spec.get("semantic_table_path", "")),
+                                                   2 ** min(int(template_spec.get("semantic_n_lsh_planes", 12)), 12))
+            return list(tensors) + [stage(tensors[0])]
+        return tensors
+
+    @staticmethod
+    def _shard_optimizer_state(optimizers: list[torch.optim.Optimizer], params: list[Tensor], world: int) -> dict[int, int]:
+        """Optimizer-state sharding over the data-parallel group: every parameter tensor gets one
+        owner rank (greedy by size); a rank keeps only its own parameters in its optimizers, so moment
+        buffers exist once per group instead of once per rank. Returns ``id(param) -> owner``."""
+        import torch.distributed as dist
+        rank = dist.get_rank()
+        load = [0] * world
+        owner: dict[int, int] = {}
+        for p in sorted(params, key=lambda t: -t.numel()):
+            r = min(range(world), key=load.__getitem__)
+            owner[id(p)] = r
+            load[r] += p.numel()
+        for o in optimizers:
+            for g in o.param_groups:
+                g["params"] = [p for p in g["params"] if owner.get(id(p), rank) == rank]
+        return owner
+
+    @staticmethod
+    def _broadcast_owned_params(params: list[Tensor], owner: dict[int, int], world: int) -> None:
+        import torch.distributed as dist
+        for r in range(world):
+            mine = [p for p in params if owner[id(p)] == r]
+            if not mine:
+                continue
+            flat = torch.cat([p.detach().reshape(-1) for p in mine])
+            dist.broadcast(flat, src=r)
+            for p, chunk in zip(mine, flat.split([p.numel() for p in mine])):
+                p.detach().copy_(chunk.view_as(p))

@@ -64,6 +64,11 @@ class GraphBuilder:
     def subgraph(self, graph: NeuronGraph, name: str, inputs: list[Ref], node_id: str | None = None,
                  in_aliases: list[str] | None = None, out_aliases: list[str] | None = None,
                  variant_ref: dict[str, str] | None = None) -> str:
+        if graph.variant_library:
+            # variant references resolve against the outermost graph: hoist a nested library
+            for fam, versions in graph.variant_library.items():
+                self.graph.variant_library.setdefault(fam, {}).update(versions)
+            graph.variant_library = {}
         nd = subgraph_neuron(graph, name=name, input_aliases=in_aliases, output_aliases=out_aliases,
                              variant_ref=variant_ref)
         return self._add(nd, node_id, inputs)
@@ -110,13 +115,28 @@ def _geometry(spec: ModelSpec) -> tuple[int, int, int, int]:
     return heads, kv, hd, inner
 
 
-def build_dense_attention_graph(spec: ModelSpec, layer_index: int = 0) -> NeuronGraph:
-    """hidden -> attention output (residual not included)."""
+def build_dense_attention_graph(spec: ModelSpec, layer_index: int = 0, *, cross: bool = False) -> NeuronGraph:
+    """hidden -> attention output (residual not included). ``cross``: a second input ``context``
+    supplies keys and values (encoder-decoder attention: bidirectional, no rotary embedding)."""
     bs = spec.block_spec
     d = spec.model_dim
     heads, kv, hd, inner = _geometry(spec)
-    b = GraphBuilder(f"attention_{layer_index}")
+    b = GraphBuilder(f"cross_attention_{layer_index}" if cross else f"attention_{layer_index}")
     x = b.input("x")
+    if cross:
+        ctx = b.input("context")
+        q = _linear(b, x, d, inner, bs.linear_bias, bs, "q_proj", "q_proj")
+        k = _linear(b, ctx, d, kv * hd, bs.linear_bias, bs, "k_proj", "k_proj")
+        v = _linear(b, ctx, d, kv * hd, bs.linear_bias, bs, "v_proj", "v_proj")
+        qh = (b.node("reshape_heads", {"num_heads": heads}, [q]), 0)
+        kh = (b.node("reshape_heads", {"num_heads": kv}, [k]), 0)
+        vh = (b.node("reshape_heads", {"num_heads": kv}, [v]), 0)
+        if bs.use_qk_norm:
+            n = b.node("qk_norm", {"eps": bs.qk_norm_eps}, [qh, kh])
+            qh, kh = (n, 0), (n, 1)
+        a = b.node("scaled_dot_product_attention", {"is_causal": False, "dropout_p": bs.dropout_p}, [qh, kh, vh])
+        merged_c: Ref = (b.node("merge_heads", {}, [(a, 0)]), 0)
+        return b.outputs(_linear(b, merged_c, inner, d, bs.linear_bias, bs, "o_proj", "o_proj"))
     if spec.template.runtime == "megakernel" and bs.pos_encoding == "rope" and bs.attention_variant == "dense" \
             and bs.attention_gate == "none" and not bs.layer_attention_pattern:
         y = b.node("fused_causal_attention", {"model_dim": d, "num_heads": heads, "num_kv_heads": kv,
@@ -267,11 +287,31 @@ def _residual(b: GraphBuilder, x: Ref, delta: Ref, spec: ModelSpec) -> Ref:
     return (b.node("residual_add", {"dim": spec.model_dim, "init_scale": 1.0}, [x, delta]), 0)
 
 
-def build_decoder_block_graph(spec: ModelSpec, layer_index: int = 0) -> NeuronGraph:
-    """hidden -> hidden (dense) or (hidden, aux loss) for MoE blocks."""
+def build_routed_mlp_graph(spec: ModelSpec, experts: int) -> NeuronGraph:
+    """(hidden, routing weights, routing indices) -> expert output: an MoE MLP whose routes come from
+    outside the block (the semantic routers). Same shape as the reference's
+    ``build_semantic_router_mlp_graph`` (``neuralfn/torch_templates.py:1414``)."""
+    bs = spec.block_spec
+    b = GraphBuilder("semantic_router_mlp")
+    x, rw, ri = b.input("x"), b.input("routing_weights"), b.input("routing_indices")
+    cfg = {"model_dim": spec.model_dim, "experts": experts, "mlp_mult": bs.mlp_multiplier, "multiple_of": bs.multiple_of}
+    if bs.intermediate_size:
+        cfg["hidden_dim"] = bs.intermediate_size
+    y = b.node("expert_dispatch", cfg, [x, rw, ri], "dispatch")
+    return b.outputs((b.node("expert_combine", {}, [(y, 0)], "combine"), 0))
+
+
+def build_decoder_block_graph(spec: ModelSpec, layer_index: int = 0, *, cross: bool = False,
+                              routed_experts: int = 0) -> NeuronGraph:
+    """hidden -> hidden (dense) or (hidden, aux loss) for MoE blocks. ``cross``: second input
+    ``context`` and a cross-attention sub-layer between self-attention and the MLP (decoder of an
+    encoder-decoder stack). ``routed_experts`` > 0: inputs (x, routing_weights, routing_indices) and
+    an externally routed MoE MLP with that many experts, no aux output."""
     bs = spec.block_spec
     b = GraphBuilder(f"block_{layer_index}")
     x = b.input("x")
+    context = b.input("context") if cross else None
+    routes = (b.input("routing_weights"), b.input("routing_indices")) if routed_experts else None
     sandwich = bs.norm_layout == "sandwich"
     attn_graph = build_dense_attention_graph(spec, layer_index)
     if bs.family == "jamba" and layer_index % 2 == 1:
@@ -286,9 +326,17 @@ def build_decoder_block_graph(spec: ModelSpec, layer_index: int = 0) -> NeuronGr
     if sandwich:
         a_out = _norm(b, a_out, spec, bs.post_norm_eps, "post_attn_norm")
     h1 = _residual(b, x, a_out, spec)
+    if context is not None:
+        c_out: Ref = (b.subgraph(build_dense_attention_graph(spec, layer_index, cross=True), "cross_attention",
+                                 [_norm(b, h1, spec, node_id="cross_attn_norm"), context], "cross_attention",
+                                 ["x", "context"], ["y"]), 0)
+        h1 = _residual(b, h1, c_out, spec)
     n2 = _norm(b, h1, spec, node_id="mlp_norm")
     aux: Ref | None = None
-    if bs.mlp_type == "moe":
+    if routes is not None:
+        m_out = (b.subgraph(build_routed_mlp_graph(spec, routed_experts), "semantic_router_mlp", [n2, routes[0], routes[1]],
+                            "mlp", ["x", "routing_weights", "routing_indices"], ["y"]), 0)
+    elif bs.mlp_type == "moe":
         m = b.subgraph(build_moe_mlp_graph(spec), "moe_mlp", [n2], "mlp", ["x"], ["y", "aux_loss"])
         m_out, aux = (m, 0), (m, 1)
     else:

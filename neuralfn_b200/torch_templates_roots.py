@@ -124,7 +124,11 @@ def build_gpt_root_graph(model_spec: ModelSpec | None = None, **kwargs: Any) -> 
         return build_reward_model_root_graph(spec)
     if objective == "ppo":
         return build_ppo_root_graph(spec)
-    g = build_model_stage_graph(spec)
+    if objective == "pretrain" and spec.template.objective in ("sft", "dpo", "reward_model", "ppo"):
+        return {"sft": build_sft_root_graph, "dpo": build_dpo_root_graph, "reward_model": build_reward_model_root_graph,
+                "ppo": build_ppo_root_graph}[spec.template.objective](spec)
+    from .torch_templates_objectives import build_objective_stage
+    g = build_objective_stage(spec) or build_model_stage_graph(spec)
     g.name = f"{spec.template.backbone}_root"
     g.torch_config = _torch_config(spec)
     g.validate()

@@ -25,8 +25,22 @@ def test_preset_builds_compiles_and_runs(name):
     graph = build_gpt_root_graph(spec)
     rt = graph_from_json(graph_to_json(graph))          # JSON round trip incl. variant library
     model = CompiledTorchGraph(rt)
-    tok, tgt = torch.randint(0, 64, (2, 16)), torch.randint(0, 64, (2, 16))
-    loss = model(tok, tgt)[0]
+    names = [rt.nodes[n].neuron_def.output_ports[0].name for n in rt.input_node_ids]
+    expected = {"seq2seq": ["enc_tokens", "dec_tokens", "target_ids"], "diffusion": ["tokens"], "jepa": ["tokens"]}
+    objective = spec.template.objective
+    if "semantic" in objective:
+        assert names == ["tokens", "target_ids", "sem_targets"]
+    else:
+        assert names == expected.get(objective, ["tokens", "target_ids"])
+    inputs = []
+    for n in names:
+        if n == "sem_targets":
+            sem = torch.full((2, 9), -100)
+            sem[:, 0], sem[0, 3] = 1, 2
+            inputs.append(sem)
+        else:
+            inputs.append(torch.randint(0, 64, (2, 16)))
+    loss = model(*inputs)[0]
     assert loss.ndim == 0 and torch.isfinite(loss)
     loss.backward()
     assert any(p.grad is not None and p.grad.abs().sum() > 0 for p in model.parameters())
