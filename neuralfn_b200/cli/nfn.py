@@ -134,6 +134,21 @@ def cmd_embed(a) -> int:
 def cmd_train(a) -> int:
     if a.base_model == "embedding":
         return cmd_train_embedding(a)
+    from . import graph_cli
+    if graph_cli.wants_graph_runtime(a):
+        return graph_cli.cmd_train_graph(a)
+    if getattr(a, "pipeline_parallel_size", 1) > 1:
+        # pipeline stages: one process per GPU through the pipeline driver
+        import subprocess
+        argv = ["--stages", str(a.pipeline_parallel_size), "--dataset", a.dataset, "--batch-size", str(a.batch_size), "--seq-len", str(a.seq_len),
+                "--max-steps", str(a.max_steps), "--learning-rate", str(a.learning_rate), "--n-layer", str(a.n_layer), "--n-head", str(a.n_head),
+                "--d-model", str(a.d_model), "--vocab-size", str(a.vocab_size), "--seed", str(a.seed), "--output-dir", a.output_dir]
+        if "RANK" in os.environ:
+            from ..parallel.pp import main as pp_main
+            return pp_main(argv)
+        return subprocess.call([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.pipeline_parallel_size}",
+                                "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 2000), "-m",
+                                "neuralfn_b200.parallel.pp", *argv])
     if a.parallel in ("tp", "ep"):
         # the model-parallel families have their own driver; one process per GPU
         argv = _parallel_train_argv(a)
@@ -354,9 +369,17 @@ def cmd_migrate_native(a) -> int:
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="nfn", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="command", required=True)
-    t = sub.add_parser("train", help="native training run (JSON report on stdout)")
+    t = sub.add_parser("train", help="training run (JSON report on stdout): native sm_100a engines, or the graph runtime for any preset / objective")
     _add_train_flags(t)
+    from . import graph_cli
+    graph_cli.add_graph_train_arguments(t)
     t.set_defaults(fn=cmd_train)
+    ev = sub.add_parser("eval", help="validation loss and prompt probes of a graph trained with the graph runtime")
+    graph_cli.add_eval_arguments(ev)
+    ev.set_defaults(fn=graph_cli.cmd_eval)
+    mig = sub.add_parser("migrate", help="lower a graph (and weights) to a native execution artifact: nfn migrate graph-to-native --graph G --output-dir D")
+    graph_cli.add_migrate_arguments(mig)
+    mig.set_defaults(fn=graph_cli.cmd_migrate)
     i = sub.add_parser("infer", help="generate from a dense checkpoint file or an artifact directory; --serve starts the HTTP server")
     i.add_argument("--checkpoint", required=True)
     i.add_argument("--prompt-tokens", default="", help="comma-separated ids; ';' separates prompts")

@@ -215,6 +215,61 @@ dp_reduce_kernel(PeerTable grads, int rank, int world, long long lo8, long long 
   if (threadIdx.x == 0) partial[blockIdx.x] = ss;
 }
 
+// Bucketed ("relay") form of the reduce, for overlapping the reduction with the backward pass: the
+// 8-element vectors [b8, b8 + n8) of the flat space - a bucket of layers whose gradients are final on
+// every rank - are split evenly over the ranks regardless of who owns them. This rank sums its slice
+// over all peers' bf16 gradients and stores each fp32 sum into the reduced-gradient shard of the rank
+// that owns the vector (a peer store unless that is this rank), so all ranks' links are busy for
+// every bucket and the optimizer keeps its contiguous shards. Squared-norm partials accumulate over
+// the buckets of a step: the norm a rank publishes then covers the vectors it reduced, and the sum
+// over ranks is the global norm as before.
+//
+// THREADS = 128 is the background form: with at most 80 registers a 128-thread block (10 K registers,
+// no dynamic shared memory) fits on an SM beside a resident GEMM CTA of the backward pass
+// (320 threads x 168 registers), so it neither waits for an SM to drain nor keeps the next GEMM's
+// CTA off an SM - a 256-thread block did both and cost more than the overlap saved.
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS, THREADS == 128 ? 6 : 1)
+dp_reduce_relay_kernel(PeerTable grads, PeerTable gshards, int rank, int world, unsigned b8, unsigned n8,
+                       unsigned shard8, float* __restrict__ partial, int accumulate) {
+  constexpr int INFLIGHT = THREADS == 128 ? 4 : MAX_PEERS;   // loads in flight per thread
+  const unsigned per = (n8 + world - 1) / world;
+  const unsigned lo = b8 + (unsigned)rank * per;
+  unsigned hi = lo + per;
+  if (hi > b8 + n8) hi = b8 + n8;
+  float ss = 0.f;
+  for (unsigned i = lo + blockIdx.x * THREADS + threadIdx.x; i < hi; i += gridDim.x * THREADS) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r0 = 0; r0 < MAX_PEERS; r0 += INFLIGHT) {
+      uint4 u[INFLIGHT];
+#pragma unroll
+      for (int r = 0; r < INFLIGHT; ++r)
+        if (r0 + r < world) u[r] = reinterpret_cast<const uint4*>(grads.p[r0 + r])[i];   // table rotated by the host: entry 0 = this rank
+#pragma unroll
+      for (int r = 0; r < INFLIGHT; ++r) {
+        if (r0 + r < world) {
+          float f[8];
+          unpack8(u[r], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += f[j];
+        }
+      }
+    }
+    const unsigned owner = i / shard8;
+    st8f(static_cast<float*>(gshards.p[owner]) + (size_t)(i - owner * shard8) * 8, acc);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += acc[j] * acc[j];
+  }
+  // one partial slot per warp: the kernel uses no shared memory at all, so that a block fits on an SM
+  // whose shared memory a GEMM CTA has taken whole
+  ss = warp_sum_f(ss);
+  if ((threadIdx.x & 31) == 0) {
+    float* slot = partial + blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5);
+    *slot = accumulate ? *slot + ss : ss;
+  }
+}
+
 // Publish this rank's squared norm (sum of `npartial` partials) into every peer's
 // norm slots: slots[rank] = {sumsq, epoch} written as one 8-byte release store.
 __global__ void __launch_bounds__(256)
@@ -305,6 +360,22 @@ static int grid_for(long long n8) {
   return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 
+// Kernels that run beside the backward pass on a second stream ask for the largest shared-memory
+// carve-out although they use next to none: an SM holds one carve-out at a time and only changes it when
+// it is empty, so a block launched with the default (small) carve-out keeps the 227 KB GEMM CTAs off its
+// SM until it exits - measured as a GEMM delay equal to the whole side kernel's duration.
+static void prefer_max_smem_once() {
+  static bool done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || done[dev]) return;
+  done[dev] = true;
+  cudaFuncSetAttribute(dp_reduce_relay_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  cudaFuncSetAttribute(dp_reduce_relay_kernel<256>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  cudaFuncSetAttribute(peer_arrive_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  cudaFuncSetAttribute(peer_wait_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 static bool fill_table(PeerTable& t, void* const* ptrs, int world) {
   if (world < 1 || world > MAX_PEERS) return false;
   for (int i = 0; i < MAX_PEERS; ++i) t.p[i] = i < world ? ptrs[i] : nullptr;
@@ -352,6 +423,7 @@ extern "C" int nfn_peer_arrive(void* const* peer_flags, int rank, int world, int
                                nfn_stream_t stream) {
   PeerTable t;
   if (!fill_table(t, peer_flags, world)) return fail(-1, "peer_arrive: bad world size");
+  prefer_max_smem_once();
   peer_arrive_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(t, rank, world, slot, epoch, epoch_dev);
   return launch_check("peer_arrive");
 }
@@ -360,6 +432,7 @@ extern "C" int nfn_peer_wait(const int* my_flags, int world, int slot, int epoch
                              double timeout_s,
                              nfn_stream_t stream) {
   if (world < 1 || world > MAX_PEERS) return fail(-1, "peer_wait: bad world size");
+  prefer_max_smem_once();
   peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
       my_flags, world, slot, epoch, epoch_dev, (unsigned long long)(timeout_s * 1e9), status_ptr());
   return launch_check("peer_wait");
@@ -374,6 +447,48 @@ extern "C" int nfn_dp_reduce(void* const* peer_grads, int rank, int world, long 
   dp_reduce_kernel<<<grid_for(n / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       t, rank, world, lo / 8, n / 8, gshard, partial);
   return launch_check("dp_reduce");
+}
+
+// Size of the squared-norm partial array of the bucketed reduce (the largest grid it launches).
+extern "C" int nfn_dp_relay_blocks(void) { return sm_count() * 8 * 8; }   // one slot per warp of the largest grid
+
+// Bucket = elements [lo, lo + n) of the flat space (multiples of 8); peer_gshards[r] = rank r's fp32
+// reduced-gradient shard of `shard` elements (peer-writable); partial: fp32 [nfn_dp_relay_blocks()],
+// zeroed by the caller at the start of a step when `accumulate` is set on every launch.
+// `background` != 0: one 128-thread block per SM, for a launch that runs beside the backward pass's
+// GEMMs (it is bound by NVLink and must fit next to their CTAs); 0: a full grid, for a launch nothing hides.
+extern "C" int nfn_dp_reduce_relay(void* const* peer_grads, void* const* peer_gshards, int rank, int world,
+                                   long long lo, long long n, long long shard, float* partial, int accumulate,
+                                   int background, nfn_stream_t stream) {
+  PeerTable tg, ts;
+  if (!fill_table(tg, peer_grads, world) || !fill_table(ts, peer_gshards, world)) return fail(-1, "dp_reduce_relay: bad world size");
+  if (lo % 8 || n % 8 || shard % 8 || n < 0 || shard <= 0) return fail(-1, "dp_reduce_relay: bounds must be multiples of 8");
+  if (lo < 0 || lo + n > shard * world) return fail(-1, "dp_reduce_relay: bucket outside the flat space");
+  if (shard * world / 8 >= (1ll << 31)) return fail(-1, "dp_reduce_relay: flat space too large for 32-bit vector indices");
+  prefer_max_smem_once();
+  // start at home and stagger the peers across ranks; a fixed order per entry keeps the table in registers
+  PeerTable rot = tg;
+  for (int r = 0; r < world; ++r) rot.p[r] = tg.p[(rank + r) % world];
+  tg = rot;
+  const long long slice8 = (n / 8 + world - 1) / world;
+  if (background) {
+    dp_reduce_relay_kernel<128><<<sm_count(), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        tg, ts, rank, world, (unsigned)(lo / 8), (unsigned)(n / 8), (unsigned)(shard / 8), partial, accumulate);
+  } else {
+    dp_reduce_relay_kernel<256><<<grid_for(slice8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        tg, ts, rank, world, (unsigned)(lo / 8), (unsigned)(n / 8), (unsigned)(shard / 8), partial, accumulate);
+  }
+  return launch_check("dp_reduce_relay");
+}
+
+// Same as nfn_dp_norm_publish with the number of partials given directly.
+extern "C" int nfn_dp_norm_publish_n(const float* partial, int npartial, void* const* peer_slots,
+                                     int rank, int world, int epoch, const int* epoch_dev, nfn_stream_t stream) {
+  PeerTable t;
+  if (!fill_table(t, peer_slots, world)) return fail(-1, "dp_norm_publish: bad world size");
+  if (npartial < 1) return fail(-1, "dp_norm_publish: no partials");
+  dp_norm_publish_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(partial, npartial, t, rank, world, epoch, epoch_dev);
+  return launch_check("dp_norm_publish");
 }
 
 extern "C" int nfn_dp_norm_publish(const float* partial, long long shard_n, void* const* peer_slots,

@@ -268,6 +268,17 @@ class GPT2Engine:
         self.tokens = torch.zeros(N, device=dev, dtype=torch.int32)
         self.targets = torch.zeros(N, device=dev, dtype=torch.int32)
         self.timer = None  # optional utils.stage_timing.StageTimer (eager runs only)
+        # data-parallel overlap: called as hook(lo, hi) from the backward pass as soon as the weight
+        # gradients of a group of layers (one contiguous flat range) are final
+        self.grad_ready_hook = None
+        self.grad_bucket_layers = max(1, -(-cfg.n_layer // 6))
+
+    def _layer_range(self, l_lo: int, l_hi: int) -> tuple[int, int]:
+        """Flat range of the decayed weights of layers l_lo..l_hi (inclusive)."""
+        lay = self.layout
+        last = f"h.{l_hi}.mlp.c_proj.weight"
+        hi = lay.offsets[last] + (lay.specs[last].numel + 7) // 8 * 8
+        return lay.offsets[f"h.{l_lo}.attn.c_attn.weight"], hi
 
     def _stage(self, name: str):
         t = self.timer
@@ -392,6 +403,8 @@ class GPT2Engine:
                                     mode=K.NORM_LAYER, dresid=dx, out=spare,
                                     dx_colsum=g[f"h.{l - 1}.mlp.c_proj.bias"] if l > 0 else None)
                 dx, spare = spare, dx
+            if self.grad_ready_hook is not None and l % self.grad_bucket_layers == 0:
+                self.grad_ready_hook(*self._layer_range(l, min(l + self.grad_bucket_layers, cfg.n_layer) - 1))
         with st("embedding_backward"):
             K.embedding_backward(dx, self.tokens, g["wte"], g["wpe"][:T], B=B, T=T)
         if T < cfg.max_seq_len:

@@ -309,6 +309,26 @@ def dp_reduce(peer_grad_ptrs, rank: int, world: int, lo: int, n: int, gshard, pa
     _lib.check(rc, "nfn_dp_reduce")
 
 
+def dp_relay_blocks() -> int:
+    return int(_lib.load().nfn_dp_relay_blocks())
+
+
+def dp_reduce_relay(peer_grad_ptrs, peer_gshard_ptrs, rank: int, world: int, lo: int, n: int, shard: int, partial,
+                    accumulate: bool, background: bool = False):
+    """Bucketed reduce of flat elements [lo, lo + n): this rank sums its 1/world slice of the bucket
+    over all peers and stores the fp32 sums into the owners' reduced-gradient shards."""
+    rc = _lib.load().nfn_dp_reduce_relay(_ptr_array(peer_grad_ptrs), _ptr_array(peer_gshard_ptrs), c_int(rank), c_int(world),
+                                         c_longlong(lo), c_longlong(n), c_longlong(shard), _p(partial),
+                                         c_int(int(accumulate)), c_int(int(background)), _st())
+    _lib.check(rc, "nfn_dp_reduce_relay")
+
+
+def dp_norm_publish_n(partial, npartial: int, peer_slot_ptrs, rank: int, world: int, epoch: int, epoch_dev=None):
+    rc = _lib.load().nfn_dp_norm_publish_n(_p(partial), c_int(npartial), _ptr_array(peer_slot_ptrs),
+                                           c_int(rank), c_int(world), c_int(epoch), _p(epoch_dev), _st())
+    _lib.check(rc, "nfn_dp_norm_publish_n")
+
+
 def dp_norm_publish(partial, shard_n: int, peer_slot_ptrs, rank: int, world: int, epoch: int, epoch_dev=None):
     rc = _lib.load().nfn_dp_norm_publish(_p(partial), c_longlong(shard_n), _ptr_array(peer_slot_ptrs),
                                          c_int(rank), c_int(world), c_int(epoch), _p(epoch_dev), _st())

@@ -23,7 +23,9 @@ stages); its single-GPU counterpart is the descriptor-table AdamW
 """
 from __future__ import annotations
 
+import contextlib
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -82,7 +84,10 @@ class SymmetricBuffers:
             self.grads = symm.empty(n_total, dtype=torch.bfloat16, device=device)
             self.ctrl = symm.empty(self.CTRL_INT64, dtype=torch.int64, device=device)
             self.ctrl.zero_()
-            self._handles = [symm.rendezvous(t, gname) for t in (self.params, self.grads, self.ctrl)]
+            # fp32 reduced-gradient shard, peer-writable: the bucketed reduce stores into its owner's shard
+            self.gshard = symm.empty(n_total // self.world, dtype=torch.float32, device=device)
+            self._handles = [symm.rendezvous(t, gname) for t in (self.params, self.grads, self.ctrl, self.gshard)]
+            self.gshard_ptrs = list(self._handles[3].buffer_ptrs)
             self.param_ptrs = list(self._handles[0].buffer_ptrs)
             self.grad_ptrs = list(self._handles[1].buffer_ptrs)
             ctrl_ptrs = list(self._handles[2].buffer_ptrs)
@@ -132,8 +137,21 @@ class ShardedAdamW:
             self._hyper_ring = PinnedRing(K.HYPER_SIZE, torch.float32, slots=8)
             self.partial = torch.empty(K.optim_max_partials(), dtype=torch.float32, device=dev)
             self.clip = torch.ones(2, dtype=torch.float32, device=dev)
-            self.gshard = torch.empty(self.shard, dtype=torch.float32, device=dev) if self.world > 1 else None
+            self.gshard = getattr(bufs, "gshard", None) if self.world > 1 else None
+            if self.world > 1 and self.gshard is None:
+                self.gshard = torch.empty(self.shard, dtype=torch.float32, device=dev)
             self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=dev)
+            # Bucketed reduction of the gradients under the backward pass (multi-GPU only). Opt-in: the
+            # persistent GEMM CTAs of the backward pass own their SMs with a static tile schedule, and a
+            # block of any other kernel that lands on an SM first keeps that GEMM CTA - and with it the
+            # whole GEMM - waiting until the block exits. Measured on two B200s the bucketed path costs
+            # 0.3 - 0.45 ms per step more than reducing after the backward pass, so the default stays off.
+            self.overlap = (self.world > 1 and getattr(bufs, "symmetric", False)
+                            and os.environ.get("NFN_DP_OVERLAP", "0") == "1")
+            self._side = torch.cuda.Stream(device=dev) if self.overlap else None
+            self._relay_partial = (torch.zeros(K.dp_relay_blocks(), dtype=torch.float32, device=dev) if self.overlap else None)
+            self._covered: list[tuple[int, int]] = []
+            self._in_overlap = False
         else:
             self.clip = torch.ones(2, dtype=torch.float32)
 
@@ -183,6 +201,57 @@ class ShardedAdamW:
         self.launch_step()
         self.step_count += 1
 
+    # ------------------------------------------------ reduction under the backward --
+    MAX_BUCKETS = 10      # flag slots 2..11 of the control block
+
+    def begin_overlap(self) -> None:
+        """Call on the main stream before the backward pass of a step whose gradients will be reduced
+        bucket by bucket (``reduce_range``) while later layers are still being differentiated."""
+        if not self.overlap:
+            return
+        self.K.counter_add(self.epoch_dev, 1)
+        self._relay_partial.zero_()
+        self._covered = []
+        self._slots_used = 0
+        self._in_overlap = True
+
+    def reduce_range(self, lo: int, hi: int) -> None:
+        """Gradients of flat elements [lo, hi) are final on this rank (everything launched so far on
+        the current stream produces them): reduce that bucket across ranks on the side stream. All
+        ranks must call this with the same ranges in the same order."""
+        if not self._in_overlap or hi <= lo:
+            return
+        if self._slots_used >= self.MAX_BUCKETS - 1:
+            return                                  # the rest is reduced at the step
+        self._relay(lo, hi, stream=self._side)
+
+    def _relay(self, lo: int, hi: int, stream=None, sync: bool = True) -> None:
+        """``sync``: first wait until every rank's gradients of the range are final (one flag slot)."""
+        K, b = self.K, self.bufs
+        W, r, ed = self.world, self.rank, self.epoch_dev
+        main = torch.cuda.current_stream()
+        if stream is not None:
+            stream.wait_stream(main)
+        with torch.cuda.stream(stream) if stream is not None else contextlib.nullcontext():
+            if sync:
+                slot = 2 + self._slots_used
+                self._slots_used += 1
+                K.peer_arrive(b.flag_ptrs, r, W, slot, 0, ed)
+                K.peer_wait(b.flag_ptrs[r], W, slot, 0, self.peer_timeout_s, ed)
+            K.dp_reduce_relay(b.grad_ptrs, b.gshard_ptrs, r, W, lo, hi - lo, self.shard, self._relay_partial,
+                              accumulate=True, background=stream is not None)
+        self._covered.append((lo, hi))
+
+    def _uncovered(self) -> list[tuple[int, int]]:
+        out, cur = [], 0
+        for lo, hi in sorted(self._covered):
+            if lo > cur:
+                out.append((cur, lo))
+            cur = max(cur, hi)
+        if cur < self.layout.n_total:
+            out.append((cur, self.layout.n_total))
+        return out
+
     def launch_step(self) -> None:
         """Kernel launches only (capturable); uses ``self.epoch`` as the signal epoch base."""
         K, b = self.K, self.bufs
@@ -193,6 +262,22 @@ class ShardedAdamW:
         if not b.symmetric:
             raise RuntimeError("multi-GPU ShardedAdamW needs symmetric-memory buffers")
         W, r, ed = self.world, self.rank, self.epoch_dev
+        if self._in_overlap:
+            # what the backward pass did not hand over (embeddings, the small non-decayed tail) is
+            # reduced here, after one wait for all of it
+            for i, (lo, hi) in enumerate(self._uncovered()):
+                self._relay(lo, hi, stream=None, sync=i == 0)
+            torch.cuda.current_stream().wait_stream(self._side)
+            self._in_overlap = False
+            # a rank publishes its squared norm after its last bucket, so collecting every rank's norm
+            # also tells this rank that all stores into its reduced-gradient shard have landed
+            K.dp_norm_publish_n(self._relay_partial, self._relay_partial.numel(), b.slot_ptrs, r, W, 0, ed)
+            K.dp_norm_collect(b.slot_ptrs[r], W, 0, self.hyper, self.clip, self.peer_timeout_s, ed)
+            K.dp_adamw(self.master, self.m, self.v, self.gshard, b.param_ptrs, r, W, self.lo, self.shard,
+                       self.layout.n_decay, self.hyper, self.clip)
+            K.peer_arrive(b.flag_ptrs, r, W, 1, 0, ed)
+            K.peer_wait(b.flag_ptrs[r], W, 1, 0, self.peer_timeout_s, ed)
+            return
         # the signal epoch lives on the device and advances once per launch of this
         # sequence, so replaying a captured graph produces fresh epochs every time
         K.counter_add(ed, 1)

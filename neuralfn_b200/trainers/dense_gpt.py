@@ -66,6 +66,9 @@ class DenseGPTTrainer:
         from ..utils.stage_timing import StageTimer
         self.timer = StageTimer()  # NFN_NATIVE_GPT_STAGE_TIMING=1: per-stage CUDA events (+ NVTX with NFN_NVTX=1)
         self.engine.timer = self.timer
+        if getattr(self.opt, "overlap", False) and max(1, int(grad_accum_steps)) == 1 and hasattr(self.engine, "grad_ready_hook"):
+            # the gradient reduction of each group of layers runs under the rest of the backward pass
+            self.engine.grad_ready_hook = self.opt.reduce_range
         # a captured graph cannot be timed stage by stage: the diagnostic mode runs eagerly
         self.use_cuda_graph = use_cuda_graph and not self.timer.enabled
         # gradient accumulation: `grad_accum_steps` micro-batches per optimizer step, summed in
@@ -89,6 +92,8 @@ class DenseGPTTrainer:
     def _launch_phase(self, phase: str) -> None:
         from ..ops import _lib
         self.engine.forward()
+        if phase == "single" and getattr(self.engine, "grad_ready_hook", None) is not None:
+            self.opt.begin_overlap()
         self.engine.backward()
         if phase != "single":
             mode = {"first": 0, "mid": 1, "last": 2}[phase]
