@@ -13,8 +13,10 @@
 //                       path as the 1-CTA kernel); the peer releases the accumulator with a
 //                       remote mbarrier arrive on the leader's barrier
 //
-// K-major A and B only (forward products X W^T); other operand layouts, split-K and fp32 /
-// accumulating outputs stay on the 1-CTA kernel. No load in this file uses cluster multicast.
+// A is K-major; B is K-major (forward products X W^T) or MN-major (input gradients dY W, template
+// parameter B_MN: each CTA then stages its 128 columns of B as two 64-column panels of BK rows).
+// MN-major A, split-K and fp32 / accumulating outputs stay on the 1-CTA kernel. No load in this
+// file uses cluster multicast.
 #include <algorithm>
 
 #include "gemm_epilogue.cuh"
@@ -81,6 +83,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
                : "memory");
 }
 
+template <bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P2_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_aux, const GemmParams p) {
@@ -153,14 +156,19 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
           if (leader) mbar_expect_tx(smem_u32(&full_bar[stage]), 2 * STAGE_BYTES);
           tma_load_2d_pair(sa, &tma_a, fb_leader, kb * BK, m0);
-          tma_load_2d_pair(sa + A_BYTES, &tma_b, fb_leader, kb * BK, nb0);
+          if (!B_MN) {
+            tma_load_2d_pair(sa + A_BYTES, &tma_b, fb_leader, kb * BK, nb0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < (BN / 2) / 64; ++j) tma_load_2d_pair(sa + A_BYTES + j * 8192, &tma_b, fb_leader, nb0 + 64 * j, kb * BK);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     if (leader && lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, 0, 0);
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, 0, B_MN ? 1 : 0);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
@@ -174,11 +182,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-          const uint64_t da = make_smem_desc_sw128(sa, 16, 1024), db = make_smem_desc_sw128(sa + A_BYTES, 16, 1024);
+          const uint64_t da = make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t db = B_MN ? make_smem_desc_sw128(sa + A_BYTES, 8192, 1024) : make_smem_desc_sw128(sa + A_BYTES, 16, 1024);
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-            const uint64_t adv = (uint64_t)((UMMA_K * 2) >> 4) * kk;
-            umma_bf16_ss_pair(tmem_d, da + adv, db + adv, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            const uint64_t a_adv = (uint64_t)((UMMA_K * 2) >> 4) * kk;
+            const uint64_t b_adv = B_MN ? (uint64_t)((UMMA_K * 128) >> 4) * kk : a_adv;
+            umma_bf16_ss_pair(tmem_d, da + a_adv, db + b_adv, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
           }
           umma_commit_pair(smem_u32(&empty_bar[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -219,19 +229,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 
 namespace nfn {
 
-// Returns 1 when the problem was launched on CTA pairs, 0 when it is not eligible, < 0 on error.
-int try_launch_gemm_pair(const nfn_gemm_args& a, cudaStream_t stream) {
-  const bool out_f32 = a.flags & NFN_EPI_OUT_F32, accum = a.flags & NFN_EPI_ACCUM;
-  if (a.a_mn || a.b_mn || out_f32 || accum || a.split_k > 1) return 0;
-  if (a.m < 512 || a.n < 256 || a.k < 256) return 0;
+template <bool B_MN>
+static int launch_gemm_pair(const nfn_gemm_args& a, cudaStream_t stream) {
   constexpr size_t SMEM = 1024 + (size_t)P2_STAGES * (P2_BM * P2_BK * 2 + (P2_BN / 2) * P2_BK * 2) + 2 * P2_EPI_TILE + 256;
   // per device: opt in to the shared-memory size once and ask how many 2-CTA clusters can be
   // resident at the same time (GPCs with an odd number of free SMs leave one SM without a partner)
   static int max_pairs[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
+  auto kern = gemm_bf16_pair_kernel<B_MN>;
   if (!max_pairs[dev & 63]) {
-    if (cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess)
       return launch_check("gemm_pair attr", 0);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sm_count() & ~1, 1, 1);
@@ -245,7 +253,7 @@ int try_launch_gemm_pair(const nfn_gemm_args& a, cudaStream_t stream) {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
       cudaGetLastError();
       n = sm_count() / 2;
     }
@@ -253,7 +261,11 @@ int try_launch_gemm_pair(const nfn_gemm_args& a, cudaStream_t stream) {
   }
   CUtensorMap ta, tb, tc, tx;
   if (!make_tmap_2d(&ta, a.a, 2, (uint64_t)a.k, (uint64_t)a.m, (uint64_t)a.lda, P2_BK, P2_BM, 128)) return -3;
-  if (!make_tmap_2d(&tb, a.b, 2, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.ldb, P2_BK, P2_BN / 2, 128)) return -3;
+  if (!B_MN) {
+    if (!make_tmap_2d(&tb, a.b, 2, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.ldb, P2_BK, P2_BN / 2, 128)) return -3;
+  } else {
+    if (!make_tmap_2d(&tb, a.b, 2, (uint64_t)a.n, (uint64_t)a.k, (uint64_t)a.ldb, 64, P2_BK, 128)) return -3;
+  }
   if (!make_tmap_2d(&tc, a.c, 2, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldc, 64, P2_BM, 128)) return -3;
   tx = tc;
   if ((a.flags & NFN_EPI_SAVE_PRE) &&
@@ -276,9 +288,17 @@ int try_launch_gemm_pair(const nfn_gemm_args& a, cudaStream_t stream) {
   p.raster_gw = pick_raster_gw(a.m, a.k, p.tiles_n);
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = std::min(max_pairs[dev & 63], tiles);
-  gemm_bf16_pair_kernel<<<2 * pairs, P2_THREADS, SMEM, stream>>>(ta, tb, tc, tx, p);
+  kern<<<2 * pairs, P2_THREADS, SMEM, stream>>>(ta, tb, tc, tx, p);
   const int rc = launch_check("gemm_pair", 1);
   return rc < 0 ? rc : 1;
+}
+
+// Returns 1 when the problem was launched on CTA pairs, 0 when it is not eligible, < 0 on error.
+int try_launch_gemm_pair(const nfn_gemm_args& a, cudaStream_t stream) {
+  const bool out_f32 = a.flags & NFN_EPI_OUT_F32, accum = a.flags & NFN_EPI_ACCUM;
+  if (a.a_mn || out_f32 || accum || a.split_k > 1) return 0;
+  if (a.m < 512 || a.n < 256 || a.k < 256) return 0;
+  return a.b_mn ? launch_gemm_pair<true>(a, stream) : launch_gemm_pair<false>(a, stream);
 }
 
 }  // namespace nfn

@@ -236,7 +236,7 @@ extern "C" int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream_) {
         (long long)want * a.m * a.n * 4 <= a.workspace_bytes)
       split = want;
   }
-  if (wide && split == 1 && !a.a_mn && !a.b_mn && pair_enabled()) {
+  if (wide && split == 1 && !a.a_mn && pair_enabled()) {
     const int rc = try_launch_gemm_pair(a, stream);
     if (rc != 0) return rc < 0 ? rc : 0;
   }

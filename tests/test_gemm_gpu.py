@@ -159,3 +159,32 @@ def test_gemv_small_m_with_epilogues(kernel_lib, m, n, k):
         L.nfn_gemm_set_gemv_mode(old)
     torch.testing.assert_close(out.float(), tc.float(), atol=3e-2, rtol=3e-2)
     _lib.assert_status_ok("gemv")
+
+
+@pytest.mark.parametrize("m,n,k", [(16384, 768, 2304), (16384, 3072, 768), (8192 + 128, 768 + 64, 3072 + 32), (1024, 256, 256)])
+def test_gemm_cta_pair_mn_major_b(kernel_lib, m, n, k):
+    """CTA-pair kernel with an MN-major B operand (input gradients dY W): plain product and the
+    dGELU epilogue against fp32; the one-CTA kernel must agree to rounding."""
+    from neuralfn_b200.ops import _lib
+    from neuralfn_b200.ops.gemm import gemm
+    L = _lib.load()
+    torch.manual_seed(5)
+    dy = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(k, n, device="cuda", dtype=torch.bfloat16) * 0.05      # [K, N]: N contiguous
+    pre = torch.randn(m, n, device="cuda", dtype=torch.bfloat16)
+    base = dy.float() @ w.float()
+    t = pre.float().requires_grad_(True)
+    torch.nn.functional.gelu(t, approximate="tanh").sum().backward()
+    old = L.nfn_gemm_set_pair_mode(1)
+    try:
+        y = gemm(dy, w, b_mn=True)
+        _lib.assert_status_ok("gemm pair b_mn")
+        _close(y, base, k)
+        yg = gemm(dy, w, b_mn=True, act="gelu_tanh", dact_pre=pre)
+        _lib.assert_status_ok("gemm pair b_mn dgelu")
+        _close(yg, base * t.grad, k)
+        L.nfn_gemm_set_pair_mode(0)
+        y1 = gemm(dy, w, b_mn=True)
+        assert (y.float() - y1.float()).abs().max().item() <= 0.02 * base.abs().max().item()
+    finally:
+        L.nfn_gemm_set_pair_mode(old)
