@@ -103,7 +103,17 @@ def read_dense_model(path, variant: dict | None = None) -> tuple[GPT2Config, dic
     specs = gpt2_param_specs(cfg)
     tensors = [torch.empty(s.shape, dtype=torch.bfloat16) for s in specs]
     _, sha = read_container(path, MODEL_HEADER_BYTES, tensors)
-    return cfg, {s.name: t for s, t in zip(specs, tensors)}, sha
+    named = {s.name: t for s, t in zip(specs, tensors)}
+    diff_meta = Path(str(path)[:-4] + ".diff.json")
+    if getattr(cfg, "differential", False) and diff_meta.exists():
+        import numpy as np
+        meta = json.loads(diff_meta.read_text())
+        lam = np.frombuffer((diff_meta.parent / meta["parameters"]).read_bytes(), dtype="<f4")
+        for l in range(cfg.n_layer):
+            slot = torch.zeros(8, dtype=torch.bfloat16)
+            slot[0] = float(lam[l])
+            named[f"h.{l}.attn.diff_lambda"] = slot
+    return cfg, named, sha
 
 
 def latest_step(directory) -> int | None:
@@ -142,7 +152,8 @@ def save_dense_checkpoint(trainer, out_dir, step: int | None = None, *, sharded_
         name = f"model_{step:08d}.bin"
         digests[name] = write_dense_model(out / name, cfg, layout, trainer.bufs.params)
         (out / f"model_{step:08d}.variant.json").write_text(json.dumps(
-            {k: getattr(cfg, k) for k in ("qk_norm", "qk_norm_eps", "logit_softcap", "z_loss", "ln_eps", "mlp_mult", "vocab_pad_to")}))
+            {k: getattr(cfg, k) for k in ("qk_norm", "qk_norm_eps", "logit_softcap", "z_loss", "ln_eps", "mlp_mult", "vocab_pad_to",
+                                          "differential", "diff_lambda_init", "diff_norm_eps")}))
     if sharded:
         name = f"optimizer_{step:08d}.rank{rank:05d}.bin"
         hdr = _state_header(SHARD_MAGIC, step, cfg, rank, world, opt.lo, opt.shard, layout.n_total)
@@ -166,11 +177,78 @@ def save_dense_checkpoint(trainer, out_dir, step: int | None = None, *, sharded_
             name = f"optimizer_{step:08d}.bin"
             mv = [t for a, b in zip(_ordered_views(cfg, layout, m), _ordered_views(cfg, layout, v)) for t in (a, b)]
             digests[name] = write_container(out / name, _state_header(OPTIM_MAGIC, step, cfg, len(specs), 2 * n_el, grad_accum, step * grad_accum), mv)
+    if getattr(cfg, "differential", False):
+        digests.update(_write_diff_sidecars(out, step, cfg, layout, opt, world, rank))
     if world > 1:
         dist.barrier()
     if rank == 0:
         (out / f"DONE_{step:08d}").write_text(json.dumps(digests, sort_keys=True))
     return digests
+
+
+DIFF_SCHEMA = "neuralfn_b200.gpt2_diff.sidecar.v1"
+
+
+def _diff_values(cfg: GPT2Config, layout: FlatLayout, flat: torch.Tensor) -> torch.Tensor:
+    """[n_layer] fp32: element 0 of every layer's lambda slot of a full flat fp32 buffer."""
+    return torch.stack([layout.view(flat, f"h.{l}.attn.diff_lambda")[0] for l in range(cfg.n_layer)]).float().cpu()
+
+
+def _write_diff_sidecars(out: Path, step: int, cfg: GPT2Config, layout: FlatLayout, opt, world: int, rank: int) -> dict[str, str]:
+    """Differential variant: the learned lambdas are no tensors of the dense model file. Their fp32
+    values and AdamW moments go to ``diff_parameters_<step>.bin`` / ``diff_optimizer_<step>.bin`` (raw
+    little-endian fp32, one value per layer; moments as m then v) with ``model_<step>.diff.json``
+    describing them (file names as the reference's, ``nfn_gpt2_native_train.cpp:4402-4430``)."""
+    import hashlib
+    master, m, v = (_all_gather_flat(t, world).cpu() for t in (opt.master, opt.m, opt.v))
+    if rank != 0:
+        return {}
+    lam, lm, lv = (_diff_values(cfg, layout, t) for t in (master, m, v))
+    digests = {}
+    for name, payload in ((f"diff_parameters_{step:08d}.bin", lam), (f"diff_optimizer_{step:08d}.bin", torch.cat([lm, lv]))):
+        raw = payload.numpy().astype("<f4").tobytes()
+        (out / name).write_bytes(raw)
+        digests[name] = hashlib.sha256(raw).hexdigest()
+    meta = {"schema": DIFF_SCHEMA, "step": step, "layers": cfg.n_layer, "lambda_init": cfg.diff_lambda_init,
+            "norm_eps": cfg.diff_norm_eps, "dtype": "float32", "parameters": f"diff_parameters_{step:08d}.bin",
+            "optimizer": f"diff_optimizer_{step:08d}.bin", "sha256": digests}
+    (out / f"model_{step:08d}.diff.json").write_text(json.dumps(meta, indent=2))
+    return digests
+
+
+def _load_diff_sidecars(d: Path, step: int, cfg: GPT2Config, layout: FlatLayout, trainer, restored: dict) -> None:
+    """Restores lambdas (bf16 parameters, fp32 master) and their moments from the sidecars. A checkpoint
+    of the differential variant without them is refused: silently re-initialised lambdas would change the model."""
+    import hashlib
+    import numpy as np
+    meta_path = d / f"model_{step:08d}.diff.json"
+    if not meta_path.exists():
+        raise FileNotFoundError(f"{meta_path.name} is missing: a gpt2_diff checkpoint needs its differential sidecars")
+    meta = json.loads(meta_path.read_text())
+    if meta.get("schema") != DIFF_SCHEMA or int(meta["layers"]) != cfg.n_layer or int(meta["step"]) != step:
+        raise ValueError("differential sidecar metadata does not match this model / step")
+    opt = trainer.opt
+    lo, hi = opt.lo, opt.lo + opt.shard
+
+    def read(name: str, count: int) -> torch.Tensor:
+        raw = (d / name).read_bytes()
+        if hashlib.sha256(raw).hexdigest() != meta["sha256"][name] or len(raw) != 4 * count:
+            raise ValueError(f"{name}: size or checksum does not match {meta_path.name}")
+        return torch.from_numpy(np.frombuffer(raw, dtype="<f4").copy())
+
+    lam = read(meta["parameters"], cfg.n_layer)
+    mv = read(meta["optimizer"], 2 * cfg.n_layer)
+    params = trainer.bufs.params
+    for l in range(cfg.n_layer):
+        name = f"h.{l}.attn.diff_lambda"
+        off = layout.offsets[name]
+        layout.view(params, name)[0] = lam[l].to(params.dtype)
+        if lo <= off < hi:                       # this rank owns the slot's first element
+            opt.master[off - lo] = lam[l]
+            if restored.get("moments"):
+                opt.m[off - lo] = mv[l]
+                opt.v[off - lo] = mv[cfg.n_layer + l]
+    restored["diff_sidecars"] = True
 
 
 def _read_state(path, magic: int, cfg: GPT2Config, tensors: list[torch.Tensor]) -> tuple[int, ...]:
@@ -268,5 +346,7 @@ def load_dense_checkpoint(trainer, directory, step: int | None = None) -> dict:
         else:
             opt.m.zero_()
             opt.v.zero_()
+    if getattr(cfg, "differential", False):
+        _load_diff_sidecars(d, step, cfg, layout, trainer, restored)
     opt.step_count = step if restored["moments"] else 0
     return restored

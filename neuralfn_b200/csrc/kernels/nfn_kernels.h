@@ -256,6 +256,15 @@ int nfn_dequant_nf4(const void* codes, const float* absmax, long long n_weights,
 int nfn_kquant_gemv(int qtype, const void* w1, const void* w2, const void* x, int ldx, void* y, int ldy,
                     const void* bias, const void* resid, int ld_resid, int B, int N, int K, nfn_stream_t stream);
 
+// ---- differential attention glue (diff_attention.cu) ----
+int nfn_diff_partials(void);
+int nfn_diff_q_expand(const void* q, int ldq, void* q2, long long tokens, int H, int D, nfn_stream_t stream);
+int nfn_diff_q_collapse(const void* dq2, void* dq, int lddq, long long tokens, int H, int D, nfn_stream_t stream);
+int nfn_diff_combine(const void* a, const void* lambda, float out_scale, float eps, void* out, float* rstd,
+                     long long tokens, int H, int D, nfn_stream_t stream);
+int nfn_diff_combine_backward(const void* dout, const void* a, const void* lambda, float out_scale, const float* rstd,
+                              void* da, float* partial, void* dlambda, long long tokens, int H, int D, nfn_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

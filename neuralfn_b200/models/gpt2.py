@@ -43,6 +43,9 @@ class GPT2Config:
     z_loss: float = 0.0
     ln_eps: float = 1e-5
     vocab_pad_to: int = 128
+    differential: bool = False          # differential attention (two softmaxes on the halves of each head)
+    diff_lambda_init: float = 0.8
+    diff_norm_eps: float = 1e-5
 
     @property
     def padded_vocab(self) -> int:
@@ -55,7 +58,7 @@ class GPT2Config:
 
     # hooks used by trainers.dense_gpt.DenseGPTTrainer (every model family provides them)
     def param_specs(self) -> "list[ParamSpec]":
-        return gpt2_param_specs(self)
+        return gpt2_param_specs(self) + diff_param_specs(self)
 
     def init_params_(self, layout: "FlatLayout", master: torch.Tensor, seed: int) -> None:
         init_gpt2_params_(self, layout, master, seed)
@@ -74,6 +77,7 @@ class GPT2Config:
             "gpt2_qknorm": {"qk_norm": True},
             "gpt2_stable": {"qk_norm": True, "z_loss": 1e-4},
             "gpt2_qknorm_softcap_zloss": {"qk_norm": True, "logit_softcap": 30.0, "z_loss": 1e-4},
+            "gpt2_diff": {"differential": True, "diff_lambda_init": 0.8},
         }
         if name not in table:
             raise KeyError(f"unknown dense GPT variant {name!r}")
@@ -113,6 +117,16 @@ def gpt2_param_specs(cfg: GPT2Config) -> list[ParamSpec]:
         ]
     specs += [ParamSpec("ln_f.weight", (C,), False, "ones"), ParamSpec("ln_f.bias", (C,), False, "zeros")]
     return specs
+
+
+def diff_param_specs(cfg: GPT2Config) -> list[ParamSpec]:
+    """Side parameters of the differential variant: one learned lambda per layer, kept in an 8-element
+    (16-byte) slot of the flat buffers (element 0 is the value). They are not part of the dense model
+    file; checkpoints carry them as ``diff_parameters_*.bin`` / ``diff_optimizer_*.bin`` sidecars, as the
+    reference does (``neuralfn/csrc/native_gpt2/nfn_gpt2_native_train.cpp:4402-4430``)."""
+    if not cfg.differential:
+        return []
+    return [ParamSpec(f"h.{l}.attn.diff_lambda", (8,), False, "lambda") for l in range(cfg.n_layer)]
 
 
 class FlatLayout:
@@ -162,6 +176,8 @@ def init_gpt2_params_(cfg: GPT2Config, layout: FlatLayout, master: torch.Tensor,
             v.normal_(0.0, 0.02 / math.sqrt(2 * cfg.n_layer), generator=gen)
         elif s.init == "ones":
             v.fill_(1.0)
+        elif s.init == "lambda":
+            v[0] = cfg.diff_lambda_init
     layout.view(master, "wte")[cfg.vocab_size:].zero_()
 
 
@@ -180,7 +196,14 @@ def reference_forward(cfg: GPT2Config, params: dict[str, torch.Tensor], tokens: 
         if cfg.qk_norm:
             q = q * torch.rsqrt(q.float().pow(2).mean(-1, keepdim=True) + cfg.qk_norm_eps).to(q.dtype)
             k = k * torch.rsqrt(k.float().pow(2).mean(-1, keepdim=True) + cfg.qk_norm_eps).to(k.dtype)
-        a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        if cfg.differential:
+            half = hd // 2
+            a1 = F.scaled_dot_product_attention(q[..., :half], k[..., :half], v, is_causal=True)
+            a2 = F.scaled_dot_product_attention(q[..., half:], k[..., half:], v, is_causal=True)
+            d = a1 - params[p + "attn.diff_lambda"][0].to(a1.dtype) * a2
+            a = (d.float() * torch.rsqrt(d.float().pow(2).mean(-1, keepdim=True) + cfg.diff_norm_eps)).to(d.dtype) * (1.0 - cfg.diff_lambda_init)
+        else:
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         a = a.transpose(1, 2).reshape(B, T, C)
         x = x + F.linear(a, params[p + "attn.c_proj.weight"], params[p + "attn.c_proj.bias"])
         h = F.layer_norm(x, (C,), params[p + "ln_2.weight"], params[p + "ln_2.bias"], cfg.ln_eps)
@@ -216,6 +239,8 @@ class _LayerActs:
     fc_pre: torch.Tensor
     fc_act: torch.Tensor
     x2: torch.Tensor
+    diff_a: torch.Tensor | None = None      # differential variant: both attentions' outputs [N, 2C]
+    diff_rstd: torch.Tensor | None = None
 
 
 class GPT2Engine:
@@ -246,10 +271,18 @@ class GPT2Engine:
         self.acts = [
             _LayerActs(ln1=e(N, C), ln1_mean=e(N, dtype=f32), ln1_rstd=e(N, dtype=f32), qkv=e(N, 3 * C),
                        qk_rstd=e(N, 2 * cfg.n_head, dtype=f32) if cfg.qk_norm else None, att=e(N, C),
-                       lse=e(batch, cfg.n_head, seq, dtype=f32), x1=e(N, C), ln2=e(N, C),
+                       lse=e(batch, cfg.n_head * (2 if cfg.differential else 1), seq, dtype=f32), x1=e(N, C), ln2=e(N, C),
                        ln2_mean=e(N, dtype=f32), ln2_rstd=e(N, dtype=f32), fc_pre=e(N, Hd),
-                       fc_act=e(N, Hd), x2=e(N, C))
+                       fc_act=e(N, Hd), x2=e(N, C),
+                       diff_a=e(N, 2 * C) if cfg.differential else None,
+                       diff_rstd=e(N * cfg.n_head, dtype=f32) if cfg.differential else None)
             for _ in range(cfg.n_layer)]
+        if cfg.differential:
+            if cfg.head_dim not in (64, 128):
+                raise ValueError("the differential variant needs head_dim 64 or 128")
+            # every head runs as two zero-padded pseudo-heads through the ordinary flash kernels
+            self.q2, self.d_a2, self.dq2 = e(N, 2 * C), e(N, 2 * C), e(N, 2 * C)
+            self.diff_partial = e(K.diff_partials(), dtype=f32)
         self.lnf = e(N, C)
         self.lnf_mean, self.lnf_rstd = e(N, dtype=f32), e(N, dtype=f32)
         self.logits = e(N, cfg.padded_vocab)
@@ -261,7 +294,7 @@ class GPT2Engine:
         self.d_fc = e(N, Hd)
         self.d_qkv = e(N, 3 * C)
         self.d_att = e(N, C)
-        self.delta = e(batch, cfg.n_head, seq, dtype=f32)
+        self.delta = e(batch, cfg.n_head * (2 if cfg.differential else 1), seq, dtype=f32)
         self.dq_accum = e(N, C, dtype=f32)
         self.scratch = e(max(64 * 2 * max(Hd, 3 * C), K.norm_fused_rows() * 3 * C), dtype=f32)
         self.ws = e(32 * 1024 * 1024, dtype=f32)  # split-K partial slices of the weight-gradient GEMMs
@@ -307,9 +340,17 @@ class GPT2Engine:
                     with st("block_forward.attention.qk_norm"):
                         K.qk_norm_forward(a.qkv, nh, nh, hd, eps=cfg.qk_norm_eps, rstd=a.qk_rstd)
                 with st("block_forward.attention.sdpa"):
-                    K.attention_forward(a.qkv[:, :C], a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], B=B, T=T,
-                                        n_q_heads=nh, n_kv_heads=nh, head_dim=hd, causal=True,
-                                        out=a.att, lse=a.lse)
+                    if cfg.differential:
+                        K.diff_q_expand(a.qkv[:, :C], self.q2, nh, hd)
+                        K.attention_forward(self.q2, a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], B=B, T=T, n_q_heads=2 * nh,
+                                            n_kv_heads=nh, head_dim=hd, causal=True, scale=(hd // 2) ** -0.5,
+                                            out=a.diff_a, lse=a.lse)
+                        K.diff_combine(a.diff_a, p[pre + "attn.diff_lambda"], 1.0 - cfg.diff_lambda_init, cfg.diff_norm_eps,
+                                       a.att, a.diff_rstd, nh, hd)
+                    else:
+                        K.attention_forward(a.qkv[:, :C], a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], B=B, T=T,
+                                            n_q_heads=nh, n_kv_heads=nh, head_dim=hd, causal=True,
+                                            out=a.att, lse=a.lse)
                 with st("block_forward.attention.proj_residual"):
                     gemm(a.att, p[pre + "attn.c_proj.weight"], bias=p[pre + "attn.c_proj.bias"], resid=x, out=a.x1)
                 with st("block_forward.mlp.ln2"):
@@ -386,10 +427,19 @@ class GPT2Engine:
                 with st("block_backward.attn_proj.dweight_bias"):
                     gemm(dx, a.att, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "attn.c_proj.weight"])
                 with st("block_backward.attn_sdpa"):
-                    K.attention_backward(self.d_att, a.qkv[:, :C], a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], a.att,
-                                         a.lse, B=B, T=T, n_q_heads=nh, n_kv_heads=nh, head_dim=hd, causal=True,
-                                         dq=self.d_qkv[:, :C], dk=self.d_qkv[:, C:2 * C], dv=self.d_qkv[:, 2 * C:],
-                                         delta=self.delta, dq_accum=self.dq_accum)
+                    if cfg.differential:
+                        K.diff_combine_backward(self.d_att, a.diff_a, p[pre + "attn.diff_lambda"], 1.0 - cfg.diff_lambda_init,
+                                                a.diff_rstd, self.d_a2, self.diff_partial, g[pre + "attn.diff_lambda"], nh, hd)
+                        K.diff_q_expand(a.qkv[:, :C], self.q2, nh, hd)      # recomputed: cheaper than keeping [N, 2C] per layer
+                        K.attention_backward(self.d_a2, self.q2, a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], a.diff_a, a.lse, B=B, T=T,
+                                             n_q_heads=2 * nh, n_kv_heads=nh, head_dim=hd, causal=True, scale=(hd // 2) ** -0.5,
+                                             dq=self.dq2, dk=self.d_qkv[:, C:2 * C], dv=self.d_qkv[:, 2 * C:], delta=self.delta)
+                        K.diff_q_collapse(self.dq2, self.d_qkv[:, :C], nh, hd)
+                    else:
+                        K.attention_backward(self.d_att, a.qkv[:, :C], a.qkv[:, C:2 * C], a.qkv[:, 2 * C:], a.att,
+                                             a.lse, B=B, T=T, n_q_heads=nh, n_kv_heads=nh, head_dim=hd, causal=True,
+                                             dq=self.d_qkv[:, :C], dk=self.d_qkv[:, C:2 * C], dv=self.d_qkv[:, 2 * C:],
+                                             delta=self.delta, dq_accum=self.dq_accum)
                 if cfg.qk_norm:
                     with st("block_backward.qk_norm"):
                         K.qk_norm_backward(self.d_qkv, a.qkv, a.qk_rstd, nh, nh, hd)

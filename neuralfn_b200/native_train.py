@@ -23,7 +23,7 @@ from pathlib import Path
 import torch
 import torch.distributed as dist
 
-GPT_VARIANTS = ("gpt2", "gpt2_zloss", "gpt2_softcap", "gpt2_qknorm", "gpt2_stable", "gpt2_qknorm_softcap_zloss")
+GPT_VARIANTS = ("gpt2", "gpt2_zloss", "gpt2_softcap", "gpt2_qknorm", "gpt2_stable", "gpt2_qknorm_softcap_zloss", "gpt2_diff")
 LLAMA_TEMPLATES = ("llama", "llama_fast", "llama_modern", "qwen3_longctx")
 
 __all__ = ["NativeTrainConfig", "run_native_training", "build_model_config", "training_plan", "GPT_VARIANTS", "LLAMA_TEMPLATES"]
@@ -134,6 +134,8 @@ def _guard_device_status(trainer, what: str, *, sync: bool = True) -> None:
 def save_checkpoint_checked(trainer, out_dir, step: int, *, dense_format: bool, sharded_optimizer: bool = False, grad_accum: int = 1):
     """Write a checkpoint only after the device status word has been verified clean: a step that ran
     on stale or partial gradients must never reach a DONE marker."""
+    from .checkpoint import save_dense_checkpoint
+    from .checkpoint.named import save_named_checkpoint
     _guard_device_status(trainer, f"checkpoint at step {step}")
     if dense_format:
         return save_dense_checkpoint(trainer, out_dir, step, sharded_optimizer=sharded_optimizer, grad_accum=grad_accum)

@@ -130,6 +130,35 @@ def qk_norm_backward(dqkv, qkv_normed, rstd, n_q_heads: int, n_kv_heads: int, he
     _lib.check(rc, "nfn_qk_norm_backward")
 
 
+# ---------------------------------------------------- differential attention glue --
+def diff_partials() -> int:
+    return int(_lib.load().nfn_diff_partials())
+
+
+def diff_q_expand(q, q2, n_heads: int, head_dim: int):
+    """q: bf16 [tokens, >= H*D] view -> q2 [tokens, 2*H*D]: pseudo-head 2h keeps the first half of head h, 2h+1 the second."""
+    rc = _lib.load().nfn_diff_q_expand(_p(q), c_int(q.stride(0)), _p(q2), c_longlong(q.shape[0]), c_int(n_heads), c_int(head_dim), _st())
+    _lib.check(rc, "nfn_diff_q_expand")
+
+
+def diff_q_collapse(dq2, dq, n_heads: int, head_dim: int):
+    rc = _lib.load().nfn_diff_q_collapse(_p(dq2), _p(dq), c_int(dq.stride(0)), c_longlong(dq.shape[0]), c_int(n_heads), c_int(head_dim), _st())
+    _lib.check(rc, "nfn_diff_q_collapse")
+
+
+def diff_combine(a, lam, out_scale: float, eps: float, out, rstd, n_heads: int, head_dim: int):
+    """out = rms_norm(a1 - lambda * a2) * out_scale over each head; a: [tokens, 2*H*D], lam: bf16 (element 0)."""
+    rc = _lib.load().nfn_diff_combine(_p(a), _p(lam), c_float(out_scale), c_float(eps), _p(out), _p(rstd), c_longlong(a.shape[0]),
+                                      c_int(n_heads), c_int(head_dim), _st())
+    _lib.check(rc, "nfn_diff_combine")
+
+
+def diff_combine_backward(dout, a, lam, out_scale: float, rstd, da, partial, dlam, n_heads: int, head_dim: int):
+    rc = _lib.load().nfn_diff_combine_backward(_p(dout), _p(a), _p(lam), c_float(out_scale), _p(rstd), _p(da), _p(partial), _p(dlam),
+                                               c_longlong(a.shape[0]), c_int(n_heads), c_int(head_dim), _st())
+    _lib.check(rc, "nfn_diff_combine_backward")
+
+
 # ----------------------------------------------------------------- attention --
 class AttentionArgs(ctypes.Structure):
     """Mirror of ``nfn_attention_args`` (csrc/kernels/nfn_kernels.h)."""

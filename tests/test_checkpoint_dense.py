@@ -217,3 +217,49 @@ def test_model_file_is_accepted_by_the_reference_reader(tmp_path):
         want = tr.layout.view(tr.bufs.params, s.name).contiguous().view(torch.uint8).numpy().tobytes()
         assert raw[t.offset:t.offset + t.nbytes] == want, s.name          # same tensor at the reference's offset
         assert t.sha256 == hashlib.sha256(want).hexdigest()
+
+
+def _cpu_diff_trainer(seed=3):
+    cfg = GPT2Config.variant("gpt2_diff", n_layer=3, n_head=2, d_model=128, vocab_size=100, max_seq_len=16)
+    layout = FlatLayout(cfg.param_specs(), world=1)
+    bufs = SymmetricBuffers(layout.n_total, torch.device("cpu"))
+    master = torch.empty(layout.n_total)
+    init_gpt2_params_(cfg, layout, master, seed)
+    for l in range(cfg.n_layer):                       # distinct trained values
+        layout.view(master, f"h.{l}.attn.diff_lambda")[0] = 0.8 - 0.1 * (l + 1) - 0.01 * seed
+    opt = ShardedAdamW(layout, bufs, AdamWConfig(), master_init=master)
+    bufs.params.copy_(master.bfloat16())
+    opt.m.normal_(generator=torch.Generator().manual_seed(seed))
+    opt.v.uniform_(generator=torch.Generator().manual_seed(seed + 1))
+    opt.step_count = 5
+    return SimpleNamespace(cfg=cfg, layout=layout, bufs=bufs, opt=opt, device=torch.device("cpu"))
+
+
+def test_differential_variant_sidecars_roundtrip_and_are_required(tmp_path):
+    a = _cpu_diff_trainer(seed=3)
+    digests = save_dense_checkpoint(a, tmp_path, sharded_optimizer=False)
+    # the dense model file holds exactly the ordinary tensors: lambdas live in the sidecars
+    raw = (tmp_path / "model_00000005.bin").read_bytes()
+    assert len(raw) == 1024 + 2 * sum(s.numel for s in gpt2_param_specs(a.cfg))
+    lam = np.frombuffer((tmp_path / "diff_parameters_00000005.bin").read_bytes(), dtype="<f4")
+    assert lam.shape == (3,) and np.allclose(lam, [0.67, 0.57, 0.47], atol=1e-6)
+    assert len((tmp_path / "diff_optimizer_00000005.bin").read_bytes()) == 4 * 2 * 3
+    meta = json.loads((tmp_path / "model_00000005.diff.json").read_text())
+    assert meta["layers"] == 3 and meta["lambda_init"] == 0.8 and set(meta["sha256"]) <= set(digests)
+    b = _cpu_diff_trainer(seed=9)
+    got = load_dense_checkpoint(b, tmp_path)
+    assert got["diff_sidecars"] and got["moments"]
+    for l in range(3):
+        name = f"h.{l}.attn.diff_lambda"
+        for buf in ("master", "m", "v"):
+            assert a.layout.view(getattr(a.opt, buf), name)[0] == b.layout.view(getattr(b.opt, buf), name)[0], (buf, l)
+        assert a.layout.view(a.bufs.params, name)[0] == b.layout.view(b.bufs.params, name)[0]
+    cfg, tensors, _sha = read_dense_model(tmp_path / "model_00000005.bin")
+    assert cfg.differential and float(tensors["h.2.attn.diff_lambda"][0]) == pytest.approx(0.47, abs=4e-3)
+    # a tampered or missing sidecar is refused
+    (tmp_path / "diff_parameters_00000005.bin").write_bytes(b"\0" * 12)
+    with pytest.raises(ValueError):
+        load_dense_checkpoint(_cpu_diff_trainer(seed=1), tmp_path)
+    (tmp_path / "model_00000005.diff.json").unlink()
+    with pytest.raises(FileNotFoundError):
+        load_dense_checkpoint(_cpu_diff_trainer(seed=1), tmp_path)

@@ -416,3 +416,47 @@ def test_peer_wait_times_out_cleanly(kernel_lib):
     assert _lib.status_read_reset() == 0
     x = torch.ones(4, device="cuda")
     assert x.sum().item() == 4
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_differential_glue_kernels(kernel_lib, D):
+    """q expand / collapse, the differential combine and its backward against fp32 autograd."""
+    from neuralfn_b200.ops import _lib
+    from neuralfn_b200.ops import kernels as K
+    torch.manual_seed(0)
+    N, H = 300, 3                                      # a ragged last warp of (token, head) groups
+    qkv = torch.randn(N, 3 * H * D, device="cuda", dtype=torch.bfloat16)
+    q2 = torch.empty(N, 2 * H * D, device="cuda", dtype=torch.bfloat16)
+    K.diff_q_expand(qkv[:, :H * D], q2, H, D)
+    q = qkv[:, :H * D].view(N, H, D)
+    ref = torch.zeros(N, H, 2, D, device="cuda", dtype=torch.bfloat16)
+    ref[:, :, 0, :D // 2] = q[..., :D // 2]
+    ref[:, :, 1, D // 2:] = q[..., D // 2:]
+    assert torch.equal(q2.view(N, H, 2, D), ref)
+    dq = torch.zeros(N, 3 * H * D, device="cuda", dtype=torch.bfloat16)
+    g2 = torch.randn_like(q2)
+    K.diff_q_collapse(g2, dq[:, :H * D], H, D)
+    want = torch.cat([g2.view(N, H, 2, D)[:, :, 0, :D // 2], g2.view(N, H, 2, D)[:, :, 1, D // 2:]], dim=-1)
+    assert torch.equal(dq[:, :H * D].view(N, H, D), want) and dq[:, H * D:].abs().max() == 0
+
+    a = torch.randn(N, 2 * H * D, device="cuda", dtype=torch.bfloat16)
+    lam = torch.zeros(8, device="cuda", dtype=torch.bfloat16)
+    lam[0] = 0.6875
+    out = torch.empty(N, H * D, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.empty(N * H, device="cuda", dtype=torch.float32)
+    K.diff_combine(a, lam, 0.2, 1e-5, out, rstd, H, D)
+    af = a.float().view(N, H, 2, D).requires_grad_(True)
+    lf = lam[0].float().clone().requires_grad_(True)
+    x = af[:, :, 0] - lf * af[:, :, 1]
+    y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * 0.2
+    torch.testing.assert_close(out.float().view(N, H, D), y, atol=2e-3, rtol=2e-2)
+    dout = torch.randn(N, H * D, device="cuda", dtype=torch.bfloat16)
+    y.backward(dout.float().view(N, H, D))
+    da = torch.empty_like(a)
+    dlam = torch.full((8,), 7.0, device="cuda", dtype=torch.bfloat16)
+    partial = torch.empty(K.diff_partials(), device="cuda", dtype=torch.float32)
+    K.diff_combine_backward(dout, a, lam, 0.2, rstd, da, partial, dlam, H, D)
+    _lib.assert_status_ok("differential glue")
+    torch.testing.assert_close(da.float().view(N, H, 2, D), af.grad, atol=3e-3, rtol=3e-2)
+    assert abs(float(dlam[0]) - float(lf.grad)) <= 2e-2 * abs(float(lf.grad)) + 1e-2
+    assert dlam[1:].abs().max() == 0
