@@ -39,6 +39,10 @@ struct ArParams {
   const __nv_bfloat16* norm_weight;  // null: no norm, `out` receives the reduced (+resid) rows
   float eps;
   int centered;  // norm weight applied as (1 + w)
+  // sandwich blocks: the reduced branch output is normalised with `post_weight` BEFORE it joins the
+  // residual stream (null: not used)
+  const __nv_bfloat16* post_weight;
+  float post_eps;
   __nv_bfloat16* out;
   int ld_out;
   int* status;
@@ -101,6 +105,28 @@ allreduce_resid_norm_kernel(const ArParams p) {
   if (!sh_ok) return;
 
   const int vecs = p.n / 8;
+  auto block_total = [&](float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();   // the previous use of `red` is over
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float tot = 0.f;
+    for (int w = 0; w < AR_THREADS / 32; ++w) tot += red[w];
+    return tot;
+  };
+  auto add_resid_store = [&](int row, int v, float (&s)[8]) {
+    __nv_bfloat16* rp = p.resid + (long long)row * p.ld_resid + v * 8;
+    const uint4 u = *reinterpret_cast<const uint4*>(rp);
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+    s[0] += a.x; s[1] += a.y; s[2] += b.x; s[3] += b.y; s[4] += c.x; s[5] += c.y; s[6] += d.x; s[7] += d.y;
+    uint4 o;
+    o.x = pack_bf16x2(s[0], s[1]); o.y = pack_bf16x2(s[2], s[3]); o.z = pack_bf16x2(s[4], s[5]); o.w = pack_bf16x2(s[6], s[7]);
+    *reinterpret_cast<uint4*>(rp) = o;
+    // the norm sees the residual stream as stored (bf16)
+    const float2 a2 = unpack_bf16x2(o.x), b2 = unpack_bf16x2(o.y), c2 = unpack_bf16x2(o.z), d2 = unpack_bf16x2(o.w);
+    s[0] = a2.x; s[1] = a2.y; s[2] = b2.x; s[3] = b2.y; s[4] = c2.x; s[5] = c2.y; s[6] = d2.x; s[7] = d2.y;
+  };
   for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
     float ss = 0.f;
     for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
@@ -122,35 +148,34 @@ allreduce_resid_norm_kernel(const ArParams p) {
         const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
         s[0] += a.x; s[1] += a.y; s[2] += b.x; s[3] += b.y; s[4] += c.x; s[5] += c.y; s[6] += d.x; s[7] += d.y;
       }
-      if (p.resid) {
-        __nv_bfloat16* rp = p.resid + (long long)row * p.ld_resid + v * 8;
-        const uint4 u = *reinterpret_cast<const uint4*>(rp);
-        const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-        s[0] += a.x; s[1] += a.y; s[2] += b.x; s[3] += b.y; s[4] += c.x; s[5] += c.y; s[6] += d.x; s[7] += d.y;
-        uint4 o;
-        o.x = pack_bf16x2(s[0], s[1]); o.y = pack_bf16x2(s[2], s[3]); o.z = pack_bf16x2(s[4], s[5]); o.w = pack_bf16x2(s[6], s[7]);
-        *reinterpret_cast<uint4*>(rp) = o;
-        // the norm sees the residual stream as stored (bf16)
-        const float2 a2 = unpack_bf16x2(o.x), b2 = unpack_bf16x2(o.y), c2 = unpack_bf16x2(o.z), d2 = unpack_bf16x2(o.w);
-        s[0] = a2.x; s[1] = a2.y; s[2] = b2.x; s[3] = b2.y; s[4] = c2.x; s[5] = c2.y; s[6] = d2.x; s[7] = d2.y;
-      }
+      if (p.resid && !p.post_weight) add_resid_store(row, v, s);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         rowbuf[v * 8 + j] = s[j];
         ss += s[j] * s[j];
       }
     }
-    float scale = 1.f;
-    if (p.norm_weight) {
+    if (p.post_weight) {
+      // sandwich: branch <- rms_norm(branch) * w_post, then residual += branch
+      const float pscale = rsqrtf(block_total(ss) / (float)p.n + p.post_eps);
+      ss = 0.f;
+      for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p.post_weight + v * 8);
+        const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+        const float w8[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+        float s[8];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      __syncthreads();
-      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-      __syncthreads();
-      float tot = 0.f;
-      for (int w = 0; w < AR_THREADS / 32; ++w) tot += red[w];
-      scale = rsqrtf(tot / (float)p.n + p.eps);
+        for (int j = 0; j < 8; ++j) s[j] = rowbuf[v * 8 + j] * pscale * (p.centered ? 1.f + w8[j] : w8[j]);
+        if (p.resid) add_resid_store(row, v, s);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          rowbuf[v * 8 + j] = s[j];
+          ss += s[j] * s[j];
+        }
+      }
     }
+    float scale = 1.f;
+    if (p.norm_weight) scale = rsqrtf(block_total(ss) / (float)p.n + p.eps);
     for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
       float s[8];
 #pragma unroll
@@ -191,10 +216,25 @@ __global__ void allreduce_wait_readers_kernel(const int* ctrl, int world, int ep
 
 using namespace nfn;
 
+extern "C" int nfn_allreduce_sandwich_norm(const void* const* peer_bufs, const void* multicast_buf, int* ctrl_local, int* const* ctrl_peer,
+                                           int rank, int world, int epoch, const int* epoch_dev, int rows, int n, int ld,
+                                           const void* bias, const void* post_weight, float post_eps, void* resid, int ld_resid,
+                                           const void* norm_weight, float eps, int centered, void* out, int ld_out, nfn_stream_t stream);
+
 extern "C" int nfn_allreduce_resid_norm(const void* const* peer_bufs, const void* multicast_buf, int* ctrl_local, int* const* ctrl_peer,
                                         int rank, int world, int epoch, const int* epoch_dev, int rows, int n, int ld,
                                         const void* bias, void* resid, int ld_resid, const void* norm_weight, float eps,
                                         int centered, void* out, int ld_out, nfn_stream_t stream) {
+  return nfn_allreduce_sandwich_norm(peer_bufs, multicast_buf, ctrl_local, ctrl_peer, rank, world, epoch, epoch_dev, rows, n, ld, bias,
+                                     nullptr, 0.f, resid, ld_resid, norm_weight, eps, centered, out, ld_out, stream);
+}
+
+// As nfn_allreduce_resid_norm; with `post_weight` the reduced rows are RMS-normalised (post_eps, same
+// centering) before they are added to the residual stream, as sandwich-norm blocks need.
+extern "C" int nfn_allreduce_sandwich_norm(const void* const* peer_bufs, const void* multicast_buf, int* ctrl_local, int* const* ctrl_peer,
+                                           int rank, int world, int epoch, const int* epoch_dev, int rows, int n, int ld,
+                                           const void* bias, const void* post_weight, float post_eps, void* resid, int ld_resid,
+                                           const void* norm_weight, float eps, int centered, void* out, int ld_out, nfn_stream_t stream) {
   if (rows <= 0) return 0;
   if (!peer_bufs || !ctrl_local || !ctrl_peer || !out) return fail(-1, "allreduce_resid_norm: null operand");
   if (world < 1 || world > AR_MAX_WORLD || rank < 0 || rank >= world) return fail(-1, "allreduce_resid_norm: bad rank / world");
@@ -215,6 +255,8 @@ extern "C" int nfn_allreduce_resid_norm(const void* const* peer_bufs, const void
   p.ld_resid = ld_resid;
   p.norm_weight = static_cast<const __nv_bfloat16*>(norm_weight);
   p.eps = eps; p.centered = centered;
+  p.post_weight = static_cast<const __nv_bfloat16*>(post_weight);
+  p.post_eps = post_eps;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.ld_out = ld_out;
   p.status = status_ptr();

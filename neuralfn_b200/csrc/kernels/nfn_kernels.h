@@ -256,6 +256,11 @@ int nfn_dequant_nf4(const void* codes, const float* absmax, long long n_weights,
 int nfn_kquant_gemv(int qtype, const void* w1, const void* w2, const void* x, int ldx, void* y, int ldy,
                     const void* bias, const void* resid, int ld_resid, int B, int N, int K, nfn_stream_t stream);
 
+int nfn_allreduce_sandwich_norm(const void* const* peer_bufs, const void* multicast_buf, int* ctrl_local, int* const* ctrl_peer,
+                                int rank, int world, int epoch, const int* epoch_dev, int rows, int n, int ld, const void* bias,
+                                const void* post_weight, float post_eps, void* resid, int ld_resid, const void* norm_weight,
+                                float eps, int centered, void* out, int ld_out, nfn_stream_t stream);
+
 // ---- differential attention glue (diff_attention.cu) ----
 int nfn_diff_partials(void);
 int nfn_diff_q_expand(const void* q, int ldq, void* q2, long long tokens, int H, int D, nfn_stream_t stream);

@@ -187,6 +187,32 @@ def kv_commit_layers(stage_k: list, stage_v: list, k_caches: list, v_caches: lis
     torch.cuda.current_stream().synchronize()  # the pointer tables above must outlive the launch
 
 
+def sigmoid_gate_inplace(att: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """att[r, :] *= sigmoid(gate[r, :]) (bf16 row views of equal width; row strides free)."""
+    rc = _lib.load().nfn_sigmoid_gate_inplace(_p(att), c_int(att.stride(0)), _p(gate), c_int(gate.stride(0)), c_longlong(att.shape[0]),
+                                              c_int(att.shape[1]), _st())
+    _lib.check(rc, "nfn_sigmoid_gate_inplace")
+    return att
+
+
+def rmsnorm_residual(x: torch.Tensor, weight: torch.Tensor, resid: torch.Tensor | None, *, eps: float, centered: bool = False, out=None):
+    """out = resid + rms_norm(x) * weight (``(1 + weight)`` when centered); contiguous [rows, C] bf16. ``out`` may alias ``resid``."""
+    out = torch.empty_like(x) if out is None else out
+    rc = _lib.load().nfn_rmsnorm_residual(_p(x), _p(weight), _p(resid), _p(out), c_longlong(x.shape[0]), c_int(x.shape[1]), c_float(eps),
+                                          c_int(int(centered)), _st())
+    _lib.check(rc, "nfn_rmsnorm_residual")
+    return out
+
+
+def kv_cache_write(qkv: torch.Tensor, k_cache_slot: torch.Tensor, v_cache_slot: torch.Tensor, *, n_q_heads: int, n_kv_heads: int,
+                   head_dim: int, pos0: int = 0) -> None:
+    """Writes the k and v heads of ``qkv`` rows (one sequence, positions pos0 ...) into one slot's caches
+    [Hkv, cap, D]; positions wrap modulo cap (ring caches of sliding-window layers)."""
+    rc = _lib.load().nfn_kv_cache_write(_p(qkv), c_int(qkv.stride(0)), _p(k_cache_slot), _p(v_cache_slot), c_int(qkv.shape[0]),
+                                        c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(k_cache_slot.shape[1]), c_int(pos0), _st())
+    _lib.check(rc, "nfn_kv_cache_write")
+
+
 def swiglu_forward(gate_up: torch.Tensor, inter: int, out=None) -> torch.Tensor:
     """gate_up bf16 [rows, 2 * inter] (gate | up) -> silu(gate) * up, bf16 [rows, inter]."""
     rows = gate_up.shape[0]

@@ -238,15 +238,21 @@ class TensorParallelContext:
         return sym.t.view(rows, n), sym
 
     def allreduce_resid_norm(self, partial: torch.Tensor, sym: "_Symmetric | None", *, bias=None, resid=None, norm_weight=None,
-                             eps: float = 1e-6, centered: bool = False, use_multicast: bool = True):
+                             eps: float = 1e-6, centered: bool = False, use_multicast: bool = True, post_weight=None,
+                             post_eps: float = 1e-6):
         """sum over ranks of ``partial`` (+ bias + resid, resid updated in place), then RMS
-        norm with ``norm_weight`` when given. Returns the bf16 [rows, n] result."""
+        norm with ``norm_weight`` when given. With ``post_weight`` (sandwich-norm blocks) the summed
+        rows are RMS-normalised with it before they join the residual stream. Returns the bf16
+        [rows, n] result."""
         rows, n = partial.shape
         if self.impl != "fused":
             y = partial.float().clone()
             if self.world > 1:
                 dist.all_reduce(y, group=self.group)
             y = y + bias.float() if bias is not None else y
+            if post_weight is not None:
+                pw = post_weight.float()
+                y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + post_eps) * (1 + pw if centered else pw)
             if resid is not None:
                 y = y + resid.float()
                 resid.copy_(y.to(resid.dtype))
@@ -262,10 +268,11 @@ class TensorParallelContext:
         mc = 0
         if use_multicast and sym.handle is not None:
             mc = int(getattr(sym.handle, "multicast_ptr", 0) or 0)
-        rc = _lib.load().nfn_allreduce_resid_norm(
+        rc = _lib.load().nfn_allreduce_sandwich_norm(
             ptr_arr, c_void_p(mc), c_void_p(self.ctrl.t.data_ptr() + 4 * 1024), ctrl_arr, c_int(self.rank), c_int(self.world),
             c_int(self._next_epoch()), c_void_p(self.epoch_dev.data_ptr()), c_int(rows), c_int(n), c_int(partial.stride(0)),
-            c_void_p(0 if bias is None else bias.data_ptr()), c_void_p(0 if resid is None else resid.data_ptr()),
+            c_void_p(0 if bias is None else bias.data_ptr()), c_void_p(0 if post_weight is None else post_weight.data_ptr()),
+            c_float(post_eps), c_void_p(0 if resid is None else resid.data_ptr()),
             c_int(0 if resid is None else resid.stride(0)), c_void_p(0 if norm_weight is None else norm_weight.data_ptr()),
             c_float(eps), c_int(int(centered)), c_void_p(out.data_ptr()), c_int(out.stride(0)), c_void_p(_lib.stream_ptr()))
         _lib.check(rc, "nfn_allreduce_resid_norm")
