@@ -42,8 +42,15 @@ __all__ = ["TPLlama", "TPLlamaTrainer", "shard_llama_params", "tp_llama_param_sp
 
 
 # ------------------------------------------------------------------ parameter sharding --
+def tp_vocab_rows(cfg: LlamaConfig, world: int) -> int:
+    """Rows of the embedding / head shard of one rank: the vocabulary padded so that every shard is a
+    whole number of 128-row GEMM tiles."""
+    q = 128 * world
+    return (cfg.vocab_size + q - 1) // q * 128
+
+
 def tp_llama_param_specs(cfg: LlamaConfig, world: int) -> list[ParamSpec]:
-    C, hd, Vp = cfg.d_model, cfg.head_dim, cfg.padded_vocab
+    C, hd, Vl = cfg.d_model, cfg.head_dim, tp_vocab_rows(cfg, world)
     if cfg.n_head % world or cfg.n_kv_head % world or cfg.d_ff % world:
         raise ValueError(f"heads ({cfg.n_head}/{cfg.n_kv_head}) and d_ff ({cfg.d_ff}) must divide by the TP size {world}")
     if cfg.tie_embeddings or cfg.qk_norm or cfg.logit_softcap > 0:
@@ -54,7 +61,8 @@ def tp_llama_param_specs(cfg: LlamaConfig, world: int) -> list[ParamSpec]:
         p = f"layers.{l}."
         specs += [ParamSpec(p + "wqkv", ((Hq + 2 * Hkv) * hd, C), True, "normal"), ParamSpec(p + "wo", (C, Hq * hd), True, "resid"),
                   ParamSpec(p + "w_gate_up", (2 * Fl, C), True, "normal"), ParamSpec(p + "w_down", (C, Fl), True, "resid")]
-    specs += [ParamSpec("tok_embeddings", (Vp, C), True, "normal"), ParamSpec("lm_head", (Vp, C), True, "normal")]
+    # vocabulary-parallel: every rank keeps Vl consecutive rows of the embedding and of the head
+    specs += [ParamSpec("tok_embeddings", (Vl, C), True, "normal"), ParamSpec("lm_head", (Vl, C), True, "normal")]
     for l in range(cfg.n_layer):
         specs += [ParamSpec(f"layers.{l}.attn_norm", (C,), False, "ones"), ParamSpec(f"layers.{l}.ffn_norm", (C,), False, "ones")]
     specs.append(ParamSpec("norm", (C,), False, "ones"))
@@ -62,7 +70,7 @@ def tp_llama_param_specs(cfg: LlamaConfig, world: int) -> list[ParamSpec]:
 
 
 def is_sharded(name: str) -> bool:
-    return name.endswith((".wqkv", ".wo", ".w_gate_up", ".w_down"))
+    return name.endswith((".wqkv", ".wo", ".w_gate_up", ".w_down")) or name in ("tok_embeddings", "lm_head")
 
 
 def shard_llama_params(cfg: LlamaConfig, full: dict[str, torch.Tensor], rank: int, world: int) -> dict[str, torch.Tensor]:
@@ -81,6 +89,10 @@ def shard_llama_params(cfg: LlamaConfig, full: dict[str, torch.Tensor], rank: in
             out[name] = torch.cat([t[rank * Fl:(rank + 1) * Fl], t[F_ + rank * Fl:F_ + (rank + 1) * Fl]], 0)
         elif name.endswith(".w_down"):
             out[name] = t[:, rank * Fl:(rank + 1) * Fl]
+        elif name in ("tok_embeddings", "lm_head"):
+            Vl = tp_vocab_rows(cfg, world)
+            rows = t[rank * Vl:(rank + 1) * Vl]          # rows past the end of the table are zero padding
+            out[name] = torch.cat([rows, torch.zeros(Vl - rows.shape[0], t.shape[1], dtype=t.dtype)], 0) if rows.shape[0] < Vl else rows
         else:
             out[name] = t
     return {k: v.contiguous() for k, v in out.items()}
@@ -133,6 +145,97 @@ class _RowParallel(torch.autograd.Function):
         return dx, None, dy_local, None
 
 
+def _group_reduce_scatter(full: torch.Tensor, tp: TensorParallelContext) -> torch.Tensor:
+    """[M, C] partial sums on every rank -> this rank's [M / W, C] rows of the total."""
+    W = tp.world
+    if W == 1:
+        return full
+    rows = full.shape[0] // W
+    out = torch.empty(rows, full.shape[1], dtype=full.dtype, device=full.device)
+    if full.is_cuda:
+        dist.reduce_scatter_tensor(out, full.contiguous(), group=tp.group)
+    else:
+        dist.reduce_scatter(out, [c.contiguous() for c in full.chunk(W, 0)], group=tp.group)
+    return out
+
+
+def _group_all_gather(local: torch.Tensor, tp: TensorParallelContext) -> torch.Tensor:
+    W = tp.world
+    if W == 1:
+        return local
+    full = torch.empty(W * local.shape[0], *local.shape[1:], dtype=local.dtype, device=local.device)
+    if local.is_cuda:
+        dist.all_gather_into_tensor(full, local.contiguous(), group=tp.group)
+    else:
+        parts = [torch.empty_like(local) for _ in range(W)]
+        dist.all_gather(parts, local.contiguous(), group=tp.group)
+        full.copy_(torch.cat(parts, 0))
+    return full
+
+
+class _VocabParallelEmbedding(torch.autograd.Function):
+    """tokens [M] (all of them, on every rank), weight [Vl, C] (rows v0 ... v0 + Vl of the table) -> this
+    rank's [M / W, C] rows of the embedded sequence. Every rank looks up the tokens that fall into its
+    rows (zero elsewhere); a reduce-scatter adds the shards and hands each rank its sequence slice."""
+
+    @staticmethod
+    def forward(ctx, tokens, weight, tp: TensorParallelContext):
+        Vl = weight.shape[0]
+        v0 = tp.rank * Vl
+        idx = tokens.long() - v0
+        mine = (idx >= 0) & (idx < Vl)
+        part = F.embedding(idx.clamp(0, Vl - 1), weight) * mine.unsqueeze(-1).to(weight.dtype)
+        ctx.save_for_backward(idx.clamp(0, Vl - 1), mine)
+        ctx.tp, ctx.weight = tp, weight
+        return _group_reduce_scatter(part, tp)
+
+    @staticmethod
+    def backward(ctx, dy_local):
+        idx, mine = ctx.saved_tensors
+        dy = _group_all_gather(dy_local.contiguous(), ctx.tp)                 # [M, C]
+        ctx.weight.main_grad.index_add_(0, idx[mine], dy[mine].to(ctx.weight.main_grad.dtype))
+        return None, None, None
+
+
+class _VocabParallelCrossEntropy(torch.autograd.Function):
+    """logits_local [M, Vl] (this rank's vocabulary columns of every row), targets [M] -> mean over rows of
+    lse - logit[target] + z * lse^2. Three small exchanges per step - row maxima, row sums of exponentials
+    and the target logits, [M] floats each - replace the gather of the logits; the full-vocabulary logits
+    never exist on one rank. The backward pass turns the logits into their gradient in place."""
+
+    @staticmethod
+    def forward(ctx, logits, targets, z_coef: float, vocab_size: int, tp: TensorParallelContext):
+        M, Vl = logits.shape
+        v0 = tp.rank * Vl
+        live = min(max(vocab_size - v0, 0), Vl)                                  # columns of real vocabulary entries
+        lf = logits.float()
+        if live < Vl:
+            lf[:, live:] = float("-inf")
+        mx = lf.max(dim=-1).values if live > 0 else torch.full((M,), float("-inf"), device=logits.device)
+        if tp.world > 1:
+            dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=tp.group)
+        ex = torch.exp(lf - mx.unsqueeze(-1))
+        stats = torch.stack([ex.sum(-1), torch.zeros_like(mx)], 0)
+        idx = targets.long() - v0
+        mine = (idx >= 0) & (idx < live)
+        stats[1] = torch.where(mine, lf.gather(1, idx.clamp(0, Vl - 1).unsqueeze(1)).squeeze(1), torch.zeros_like(mx))
+        if tp.world > 1:
+            dist.all_reduce(stats, group=tp.group)
+        lse = mx + torch.log(stats[0])
+        loss = (lse - stats[1] + z_coef * lse * lse).mean()
+        ctx.save_for_backward(ex, stats[0], lse, idx.clamp(0, Vl - 1), mine)
+        ctx.z, ctx.dtype = z_coef, logits.dtype
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        ex, denom, lse, idx, mine = ctx.saved_tensors
+        M = ex.shape[0]
+        d = ex * ((1.0 + 2.0 * ctx.z * lse) / denom).unsqueeze(-1)            # softmax * d(loss_row)/d(lse)
+        d[mine, idx[mine]] -= 1.0
+        return (d * (g / M)).to(ctx.dtype), None, None, None, None
+
+
 def _rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, sign: float) -> torch.Tensor:
     half = x.shape[-1] // 2
     a, b = x[..., :half], x[..., half:]
@@ -147,7 +250,7 @@ class TPLlama:
         dev = tp.device
         self.dtype = dtype or (torch.bfloat16 if dev.type == "cuda" else torch.float32)
         self.layout = FlatLayout(tp_llama_param_specs(cfg, tp.world))
-        self.n_sharded = self.layout.offsets["tok_embeddings"]  # the sharded tensors come first
+        self.n_sharded = self.layout.offsets["layers.0.attn_norm"]  # the sharded tensors (incl. embedding and head rows) come first
         self.params = torch.zeros(self.layout.n_total, dtype=self.dtype, device=dev)
         self.grads = torch.zeros_like(self.params)
         self.p = {}
@@ -176,8 +279,10 @@ class TPLlama:
             else:
                 std = 0.02 / math.sqrt(2 * self.cfg.n_layer) if s.init == "resid" else 0.02
                 v.copy_(torch.empty(v.shape, dtype=torch.float32, device=dev).normal_(0.0, std, generator=gen))
+        Vl = tp_vocab_rows(self.cfg, self.tp.world)
+        live = min(max(self.cfg.vocab_size - self.tp.rank * Vl, 0), Vl)
         for name in ("tok_embeddings", "lm_head"):
-            self.p[name][self.cfg.vocab_size:].zero_()
+            self.p[name][live:].zero_()                       # rows of the vocabulary padding
 
     @torch.no_grad()
     def load_full(self, full: dict[str, torch.Tensor]) -> None:
@@ -205,6 +310,10 @@ class TPLlama:
                 full = torch.cat([q[:Hq * hd] for q in parts] + [q[Hq * hd:(Hq + Hkv) * hd] for q in parts] + [q[(Hq + Hkv) * hd:] for q in parts], 0)
             elif name.endswith(".w_gate_up"):
                 full = torch.cat([q[:Fl] for q in parts] + [q[Fl:] for q in parts], 0)
+            elif name in ("tok_embeddings", "lm_head"):
+                full = torch.cat(parts, 0)[:cfg.padded_vocab]
+                if full.shape[0] < cfg.padded_vocab:
+                    full = torch.cat([full, torch.zeros(cfg.padded_vocab - full.shape[0], full.shape[1])], 0)
             else:  # wo / w_down: column shards
                 full = torch.cat(parts, 1)
             out[name] = full.cpu()
@@ -236,7 +345,7 @@ class TPLlama:
             ang = torch.outer(torch.arange(T, dtype=torch.float64), inv)
             self._rope_f32 = (ang.cos().float().to(tokens.device).contiguous(), ang.sin().float().to(tokens.device).contiguous())
             self._rope_T = (T, tokens.device)
-        x = F.embedding(tokens.reshape(-1)[lo:lo + rows].long(), p["tok_embeddings"])
+        x = _VocabParallelEmbedding.apply(tokens.reshape(-1), p["tok_embeddings"], tp)
         for l in range(cfg.n_layer):
             q_ = f"layers.{l}."
             h = KB.rms_norm(x, p[q_ + "attn_norm"], cfg.norm_eps)
@@ -249,13 +358,13 @@ class TPLlama:
             gu = _ColumnParallel.apply(h, p[q_ + "w_gate_up"], tp)
             x = _RowParallel.apply(KB.swiglu(gu, Fl), p[q_ + "w_down"], x, tp)
         x = KB.rms_norm(x, p["norm"], cfg.norm_eps)
-        logits = KB.linear(x, p["lm_head"])
-        tgt = targets.reshape(-1)[lo:lo + rows]
-        if cfg.padded_vocab != cfg.vocab_size:
-            pad = torch.zeros(cfg.padded_vocab, dtype=logits.dtype, device=logits.device)
-            pad[cfg.vocab_size:] = -30000.0
-            logits = logits + pad
-        return KB.token_cross_entropy(logits, tgt, cfg.z_loss) / W
+        # vocabulary-parallel head: all-gather -> GEMM like every other column-parallel product, then a
+        # cross-entropy that exchanges three [M] vectors instead of the logits
+        logits = _ColumnParallel.apply(x, p["lm_head"], tp)                      # [M, Vl]
+        full = _VocabParallelCrossEntropy.apply(logits, targets.reshape(-1), float(cfg.z_loss), cfg.vocab_size, tp)
+        # every rank holds the whole batch mean; callers sum the returned shares over the group, so hand
+        # back 1 / W of the value while the gradient stays that of the full loss
+        return full - full.detach() * (1.0 - 1.0 / W)
 
     def backward(self, loss: torch.Tensor) -> None:
         """Fills the flat gradient buffer: sharded weights are accumulated by the parallel

@@ -33,6 +33,9 @@ def _batches(steps, micro):
     return tok, [[torch.roll(t, -1, 1) for t in row] for row in tok]
 
 
+MICRO = 3   # more micro-batches than stages: warm-up, steady 1F1B pairs and a cool-down all occur
+
+
 def _worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
@@ -40,9 +43,9 @@ def _worker(rank, world, port, q):
     try:
         from neuralfn_b200.parallel.dp import AdamWConfig
         from neuralfn_b200.parallel.pp import PipelineParallelTrainer
-        tr = PipelineParallelTrainer(_cfg(), 2, 128, AdamWConfig(lr=2e-3, warmup_steps=1, total_steps=20, weight_decay=0.0), micro_batches=2)
+        tr = PipelineParallelTrainer(_cfg(), 2, 128, AdamWConfig(lr=2e-3, warmup_steps=1, total_steps=20, weight_decay=0.0), micro_batches=MICRO)
         _fill_by_name(tr.inner)
-        tok, tgt = _batches(4, 2)
+        tok, tgt = _batches(4, MICRO)
         losses = [tr.train_step(tok[i], tgt[i]) for i in range(4)]
         tr.inner.check_status()
         names = [s.name for s in tr.layout.order]
@@ -71,15 +74,13 @@ def test_two_stage_pipeline_matches_single_gpu(tmp_path):
     # single-GPU reference with the same weights, batches and accumulation
     from neuralfn_b200.parallel.dp import AdamWConfig
     from neuralfn_b200.trainers.dense_gpt import DenseGPTTrainer
-    ref = DenseGPTTrainer(_cfg(), 2, 128, AdamWConfig(lr=2e-3, warmup_steps=1, total_steps=20, weight_decay=0.0), grad_accum_steps=2,
+    ref = DenseGPTTrainer(_cfg(), 2, 128, AdamWConfig(lr=2e-3, warmup_steps=1, total_steps=20, weight_decay=0.0), grad_accum_steps=MICRO,
                           use_cuda_graph=False)
     _fill_by_name(ref)
-    tok, tgt = _batches(4, 2)
+    tok, tgt = _batches(4, MICRO)
     want = []
     for i in range(4):
-        a = ref.train_step(tok[i][0], tgt[i][0])
-        b = ref.train_step(tok[i][1], tgt[i][1])
-        want.append((a + b) / 2)
+        want.append(sum(ref.train_step(tok[i][m], tgt[i][m]) for m in range(MICRO)) / MICRO)
     # per-stage gradient clipping vs global clipping differ slightly once the norm exceeds 1
     assert max(abs(x - y) for x, y in zip(res[0][0], want)) < 0.05, (res[0][0], want)
     assert want[-1] < want[0]

@@ -17,7 +17,7 @@ def _free_port() -> int:
 
 def _cfg():
     from neuralfn_b200.models.llama import LlamaConfig
-    return LlamaConfig(n_layer=2, n_head=4, n_kv_head=2, d_model=256, d_ff=512, vocab_size=512, max_seq_len=256, vocab_pad_to=128)
+    return LlamaConfig(n_layer=2, n_head=4, n_kv_head=2, d_model=256, d_ff=512, vocab_size=500, max_seq_len=256, vocab_pad_to=128)
 
 
 def _full_params(cfg, seed=3):
