@@ -27,6 +27,9 @@ def main(argv=None) -> int:
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--exchange", choices=("peer", "nccl"), default="peer",
+                    help="peer: rows travel by this framework's pull kernels over peer memory; nccl: all_to_all_single (the baseline)")
+    ap.add_argument("--capacity-factor", type=float, default=2.0, help="--exchange peer: receive capacity in units of tokens * top_k")
     a = ap.parse_args(argv)
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     dev = torch.device("cuda", local)
@@ -38,6 +41,10 @@ def main(argv=None) -> int:
     from ..tensor import kernel_bridge as KB
 
     layer = ExpertParallelFFN(a.dim, a.hidden, a.experts, device=dev, dtype=torch.bfloat16)
+    exchange = None
+    if a.exchange == "peer":
+        from ..parallel.ep_fused_train import PeerExchange, fused_expert_parallel_ffn
+        exchange = PeerExchange(a.experts, a.top_k, a.dim, a.tokens, dev, capacity_factor=min(a.capacity_factor, world))
     g = torch.Generator(device=dev).manual_seed(11 + rank)
     w_router = (torch.randn(a.experts, a.dim, device=dev, generator=g) * 0.02).to(torch.bfloat16).requires_grad_(True)
     x = torch.randn(a.tokens, a.dim, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
@@ -49,7 +56,7 @@ def main(argv=None) -> int:
         scores = torch.softmax(logits, -1)
         w, idx = scores.topk(a.top_k, -1)
         w = w / w.sum(-1, keepdim=True)
-        y = layer(x, w, idx)
+        y = fused_expert_parallel_ffn(x, w, idx, layer.w1, layer.w2, layer.w3, exchange) if exchange is not None else layer(x, w, idx)
         balance = a.experts * scores.mean(0).pow(2).sum()
         zloss = torch.logsumexp(logits, -1).pow(2).mean()
         loss = y.float().mean() + 0.01 * balance + 1e-3 * zloss
@@ -76,7 +83,7 @@ def main(argv=None) -> int:
         sec = ms.item() / 1e3
         print(json.dumps({"metric": "moe_layer_train_tokens_per_second", "value": round(a.tokens * world / sec, 1), "unit": "tokens/s",
                           "ms_per_step": round(ms.item(), 3), "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "dtype": "bf16",
-                          "expert_tflops_per_gpu": round(flops / sec / 1e12, 1), "loss": round(float(loss), 5), "device_status": status,
+                          "expert_tflops_per_gpu": round(flops / sec / 1e12, 1), "loss": round(float(loss), 5), "device_status": status, "exchange": a.exchange,
                           "row_bytes_exchanged_per_gpu_per_step": 4 * a.tokens * a.top_k * a.dim * 2 * (world - 1) // max(world, 1),
                           "config": {"tokens_per_gpu": a.tokens, "d_model": a.dim, "experts": a.experts, "expert_hidden": a.hidden,
                                      "top_k": a.top_k, "parallelism": f"ep{world}"}}), flush=True)

@@ -84,7 +84,8 @@ def save_named_checkpoint(trainer, out_dir, step: int | None = None) -> dict:
     return digests
 
 
-def load_named_checkpoint(trainer, directory, step: int | None = None) -> dict:
+def load_named_checkpoint(trainer, directory, step: int | None = None, *, weights_only: bool = False) -> dict:
+    """``weights_only``: start a new run from the saved weights (fresh moments, step 0), as post-training does."""
     from .dense import latest_step
     d = Path(directory)
     step = latest_step(d) if step is None else step
@@ -103,7 +104,7 @@ def load_named_checkpoint(trainer, directory, step: int | None = None) -> dict:
     trainer.bufs.params.copy_(flat)
     restored = {"step": step, "model": True, "moments": False}
     sfile = d / f"state_{step:08d}.rank{opt.rank:05d}.nfns"
-    if sfile.exists():
+    if sfile.exists() and not weights_only:
         st, smeta, _ = read_named_tensors(sfile)
         if smeta["world_size"] != opt.world or smeta["shard"] != opt.shard:
             raise ValueError("optimizer state was saved for a different world size")

@@ -55,7 +55,9 @@ def add_graph_train_arguments(p: argparse.ArgumentParser) -> None:
     ft.add_argument("--qlora-compute-dtype", default=None)
     ft.add_argument("--base-checkpoint", default=None)
     ft.add_argument("--ref-checkpoint", default=None)
+    ft.add_argument("--ref-graph", default=None, help="graph JSON of the frozen reference (default: the .json beside --ref-checkpoint)")
     ft.add_argument("--reward-checkpoint", default=None)
+    ft.add_argument("--reward-graph", default=None, help="graph JSON of the reward model (default: the .json beside --reward-checkpoint)")
     ft.add_argument("--adapter-only-save", action="store_true", default=None)
     ft.add_argument("--dpo-beta", type=float, default=None)
     ft.add_argument("--dpo-loss-type", choices=("sigmoid", "hinge", "ipo"), default=None)
@@ -141,6 +143,14 @@ def build_spec_from_args(a):
             v = getattr(a, flag, None)
             if v is not None and field in FineTuneSpec.__dataclass_fields__:
                 kw[field] = v
+        # a frozen model is a (graph, weights) pair; training runs write the graph beside the weights
+        for ckpt, flag, field in (("ref_checkpoint", "ref_graph", "ref_graph_path"), ("reward_checkpoint", "reward_graph", "reward_graph_path")):
+            if field not in FineTuneSpec.__dataclass_fields__:
+                continue
+            if getattr(a, flag, None):
+                kw[field] = getattr(a, flag)
+            elif kw.get(ckpt) and Path(kw[ckpt]).with_suffix(".json").exists():
+                kw[field] = str(Path(kw[ckpt]).with_suffix(".json"))
         spec.finetune = FineTuneSpec(**kw)
     return spec
 

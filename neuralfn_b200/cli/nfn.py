@@ -20,7 +20,11 @@ import sys
 
 
 def _add_train_flags(p: argparse.ArgumentParser) -> None:
-    p.add_argument("--base-model", default="gpt", help="gpt | gpt2 | gpt3 | nanogpt | llama | embedding")
+    p.add_argument("--base-model", default="gpt", help="gpt | gpt2 | gpt3 | nanogpt | llama | muse-glimmer | embedding")
+    p.add_argument("--objective", choices=["ar", "sft", "dpo"], default="ar",
+                   help="native engines: ar (all families); sft / dpo from record shards (--base-model muse-glimmer)")
+    p.add_argument("--head-dim", type=int, default=0, help="muse-glimmer: attention head width (0: d_model / n_head)")
+    p.add_argument("--init-from", default="", help="--objective sft|dpo: named checkpoint directory whose weights start the run")
     p.add_argument("--template-name", default="gpt2")
     p.add_argument("--dataset", default="", help="dataset alias, directory or shard file (empty: synthetic uniform tokens)")
     p.add_argument("--output-dir", default="")
@@ -78,7 +82,8 @@ def _train_config(a):
         final_lr_fraction=a.final_lr_fraction, warmup_steps=a.warmup_steps, lr_schedule_total_steps=a.lr_schedule_total_steps,
         weight_decay=a.weight_decay, beta1=a.beta1, beta2=a.beta2, eps=a.eps, max_grad_norm=a.max_grad_norm, max_steps=a.max_steps,
         eval_every=a.eval_every, eval_batches=a.eval_batches, train_loss_every=a.train_loss_every, progress_every=a.progress_every,
-        checkpoint_every=a.checkpoint_every, seed=a.seed, resume=a.resume, use_cuda_graph=not a.no_cuda_graph)
+        checkpoint_every=a.checkpoint_every, seed=a.seed, resume=a.resume, use_cuda_graph=not a.no_cuda_graph,
+        objective=a.objective, head_dim=a.head_dim, extra_paths={"init_from": a.init_from} if a.init_from else {})
 
 
 def _parallel_train_argv(a) -> list[str]:

@@ -427,3 +427,105 @@ extern "C" int nfn_moe_ep_combine(const void* const* ys_bufs, int d, int T, int 
       static_cast<__nv_bfloat16*>(out), ld_out);
   return launch_check("moe_ep_combine", 1);
 }
+
+// ------------------------------------------------------------------------------------------------
+// Training side of the expert-parallel exchange. The backward pass sends the upstream gradient of
+// every (token, slot) to the owner of its expert along the route of the forward pass, so the rows
+// have to land where the forward pass put them: the sources scatter by the saved `row_of` instead of
+// claiming rows again. Per-row scalars travel both ways too: the routing weight to the owner (it
+// scales the row gradients that feed the expert weight gradients) and <upstream, expert output>
+// back to the source (the gradient of the routing weight).
+namespace nfn {
+
+// one warp per (token, slot): send[row_of[item]] = src[token]
+__global__ void __launch_bounds__(256)
+moe_scatter_rows_kernel(const __nv_bfloat16* __restrict__ src, int ld, int T, int k, int d, const int* __restrict__ row_of, int capacity_rows,
+                        __nv_bfloat16* __restrict__ send) {
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= (long long)T * k) return;
+  const int row = row_of[item];
+  if (row < 0 || row >= capacity_rows) return;
+  const uint4* s = reinterpret_cast<const uint4*>(src + (item / k) * ld);
+  uint4* o = reinterpret_cast<uint4*>(send + (long long)row * d);
+  for (int i = lane; i < d / 8; i += 32) o[i] = s[i];
+}
+
+// grid (segments): copies each segment's fp32 scalars from the source rank's buffer
+__global__ void __launch_bounds__(256)
+moe_ep_pull_f32_kernel(EpPeers send_bufs, const int* __restrict__ seg_src_row, const int* __restrict__ seg_dst_row, const int* __restrict__ seg_rows,
+                       int world, int capacity_rows, float* __restrict__ out) {
+  const int seg = blockIdx.x, s = seg % world;
+  const int rows = seg_rows[seg];
+  const long long src0 = seg_src_row[seg], dst0 = seg_dst_row[seg];
+  const float* src = static_cast<const float*>(send_bufs.p[s]) + src0;
+  for (int i = threadIdx.x; i < rows && dst0 + i < capacity_rows; i += blockDim.x) {
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(src + i) : "memory");
+    out[dst0 + i] = v;
+  }
+}
+
+// one thread per (token, slot): reads the scalar of its row from the owner's buffer
+__global__ void __launch_bounds__(256)
+moe_ep_gather_f32_kernel(EpPeers bufs, int T, int k, int E, int world, const int* __restrict__ topk_idx, const int* __restrict__ row_of,
+                         const int* __restrict__ src_off, const int* __restrict__ home_row, float* __restrict__ out) {
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= (long long)T * k) return;
+  const int e = topk_idx[item], local_row = row_of[item], El = E / world;
+  float v = 0.f;
+  if (local_row >= 0 && e >= 0 && e < E) {
+    const float* p = static_cast<const float*>(bufs.p[e / El]) + (long long)home_row[e] + (local_row - src_off[e]);
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  }
+  out[item] = v;
+}
+
+}  // namespace nfn
+
+// send[row_of[t * k + j]] = src[t] for every (token, slot); rows of `send` are d wide.
+extern "C" int nfn_moe_scatter_rows(const void* src, int ld, int T, int k, int d, const int* row_of, int capacity_rows, void* send,
+                                    nfn_stream_t stream) {
+  using namespace nfn;
+  if (T <= 0) return 0;
+  if (!src || !row_of || !send || (d & 7) || (ld & 7) || k <= 0 || capacity_rows <= 0) return fail(-1, "moe_scatter_rows: bad arguments");
+  const long long items = (long long)T * k, grid = (items + 7) / 8;
+  if (grid > 0x7fffffffLL) return fail(-1, "moe_scatter_rows: too large for one launch");
+  moe_scatter_rows_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(src), ld, T, k, d, row_of,
+                                                                                         capacity_rows, static_cast<__nv_bfloat16*>(send));
+  return launch_check("moe_scatter_rows", 1);
+}
+
+// The fp32 counterpart of nfn_moe_ep_pull for one scalar per row (same segment tables).
+extern "C" int nfn_moe_ep_pull_f32(const void* const* send_bufs, const int* seg_src_row, const int* seg_dst_row, const int* seg_rows,
+                                   int n_local_experts, int world, int capacity_rows, float* out, nfn_stream_t stream) {
+  using namespace nfn;
+  if (!send_bufs || !seg_src_row || !seg_dst_row || !seg_rows || !out || world < 1 || world > EP_MAX_WORLD || n_local_experts <= 0)
+    return fail(-1, "moe_ep_pull_f32: bad arguments");
+  EpPeers s{};
+  for (int r = 0; r < world; ++r) {
+    if (!send_bufs[r]) return fail(-1, "moe_ep_pull_f32: missing peer pointer");
+    s.p[r] = send_bufs[r];
+  }
+  moe_ep_pull_f32_kernel<<<n_local_experts * world, 256, 0, static_cast<cudaStream_t>(stream)>>>(s, seg_src_row, seg_dst_row, seg_rows, world,
+                                                                                                 capacity_rows, out);
+  return launch_check("moe_ep_pull_f32", 1);
+}
+
+// out[t * k + j] = the owner's scalar of the row that (token t, slot j) was sent to.
+extern "C" int nfn_moe_ep_gather_f32(const void* const* bufs, int T, int k, int E, int world, const int* topk_idx, const int* row_of,
+                                     const int* src_off, const int* home_row, float* out, nfn_stream_t stream) {
+  using namespace nfn;
+  if (T <= 0) return 0;
+  if (!bufs || !topk_idx || !row_of || !src_off || !home_row || !out || world < 1 || world > EP_MAX_WORLD || E <= 0 || E % world)
+    return fail(-1, "moe_ep_gather_f32: bad arguments");
+  EpPeers b{};
+  for (int r = 0; r < world; ++r) {
+    if (!bufs[r]) return fail(-1, "moe_ep_gather_f32: missing peer pointer");
+    b.p[r] = bufs[r];
+  }
+  const long long items = (long long)T * k, grid = (items + 255) / 256;
+  if (grid > 0x7fffffffLL) return fail(-1, "moe_ep_gather_f32: too large for one launch");
+  moe_ep_gather_f32_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(b, T, k, E, world, topk_idx, row_of, src_off, home_row, out);
+  return launch_check("moe_ep_gather_f32", 1);
+}

@@ -261,6 +261,12 @@ int nfn_allreduce_sandwich_norm(const void* const* peer_bufs, const void* multic
                                 const void* post_weight, float post_eps, void* resid, int ld_resid, const void* norm_weight,
                                 float eps, int centered, void* out, int ld_out, nfn_stream_t stream);
 
+// ---- gated attention, training (gate.cu) ----
+int nfn_sigmoid_gate_forward(const void* att, int ld_att, const void* gate, int ld_gate, void* out, int ld_out, long long rows, int width,
+                             nfn_stream_t stream);
+int nfn_sigmoid_gate_backward(const void* dout, int ld_dout, const void* att, int ld_att, const void* gate, int ld_gate, void* datt,
+                              int ld_datt, void* dgate, int ld_dgate, long long rows, int width, nfn_stream_t stream);
+
 // ---- differential attention glue (diff_attention.cu) ----
 int nfn_diff_partials(void);
 int nfn_diff_q_expand(const void* q, int ldq, void* q2, long long tokens, int H, int D, nfn_stream_t stream);

@@ -1,0 +1,397 @@
+"""Native training engine for the Muse-Glimmer decoder block (CUDA, sm_100a kernels, explicit
+forward / backward over preallocated buffers like ``models/llama.py``).
+
+Block: centred RMS norm -> packed q | k | v | gate projection -> weightless per-head QK norm with a
+query scale -> rotary embedding on sliding-window layers only (every ``global_every``-th layer is global
+and position-free) -> flash attention -> sigmoid output gate -> output projection -> centred post-norm
+-> residual add; the same sandwich around a SwiGLU MLP. Weightless RMS norm of the embeddings, plain
+RMS final norm, untied head with an output multiplier and a tanh soft-cap.
+
+``GlimmerConfig`` provides the hooks ``DenseGPTTrainer`` needs (``param_specs`` / ``init_params_`` /
+``make_engine``), so data parallelism with the sharded AdamW, CUDA-graph steps, gradient accumulation
+and the named-tensor checkpoints apply unchanged. Objectives (``GlimmerEngine.objective``):
+
+* ``"ar"``   next-token cross-entropy over all rows;
+* ``"sft"``  response-only cross-entropy: ``set_loss_mask`` gives the rows that count;
+* ``"dpo"``  pairwise preference loss over (chosen, rejected) halves of the batch against frozen
+  reference log-probabilities (``set_reference_logps``): the sequence log-probabilities come from the
+  cross-entropy kernel's row losses, and the backward pass re-runs that kernel with a per-row gradient
+  scale, so no second set of logits is needed.
+
+Reference: the native Glimmer trainer ``neuralfn/csrc/native_train/muse_glimmer_native_train.cpp``
+(objective table :187 and :355-359, DPO options :125 and :192, block forward :3461-3515); the block
+definition is that of ``neuralfn/torch_templates.py:493-790``. Only the sigmoid DPO loss is built here. Adapter (LoRA / QLoRA) fine-tuning, the reward-model and PPO
+objectives and activation checkpointing are not in this engine (they run in the tensor runtime).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .gpt2 import FlatLayout, ParamSpec
+
+__all__ = ["GlimmerConfig", "GlimmerEngine", "glimmer_param_specs", "glimmer_reference_loss"]
+
+
+@dataclass(frozen=True)
+class GlimmerConfig:
+    n_layer: int = 52
+    n_head: int = 32
+    n_kv_head: int = 2
+    head_dim: int = 128
+    d_model: int = 6656
+    d_ff: int = 19968
+    vocab_size: int = 202048
+    max_seq_len: int = 4096
+    window: int = 2048
+    global_every: int = 4
+    rope_theta: float = 500000.0
+    q_scale: float = 3.87
+    norm_eps: float = 1e-5
+    post_norm_eps: float = 1e-8
+    qk_norm_eps: float = 1e-5
+    logit_softcap: float = 20.0
+    output_multiplier: float = 0.19611613513818404
+    z_loss: float = 0.0
+    vocab_pad_to: int = 128
+    dpo_beta: float = 0.1
+
+    @property
+    def padded_vocab(self) -> int:
+        p = self.vocab_pad_to
+        return (self.vocab_size + p - 1) // p * p
+
+    @property
+    def att_dim(self) -> int:
+        return self.n_head * self.head_dim
+
+    @property
+    def qkv_dim(self) -> int:
+        return (self.n_head + 2 * self.n_kv_head) * self.head_dim
+
+    def is_local(self, layer: int) -> bool:
+        return self.global_every <= 0 or (layer + 1) % self.global_every != 0
+
+    # hooks used by trainers.dense_gpt.DenseGPTTrainer
+    def param_specs(self) -> list[ParamSpec]:
+        return glimmer_param_specs(self)
+
+    def init_params_(self, layout: FlatLayout, master: torch.Tensor, seed: int) -> None:
+        gen = torch.Generator(device=master.device).manual_seed(seed)
+        master.zero_()
+        for s in layout.order:
+            v = layout.view(master, s.name)
+            if s.init == "normal":
+                v.normal_(0.0, 0.02, generator=gen)
+            elif s.init == "resid":
+                v.normal_(0.0, 0.02 / math.sqrt(2 * self.n_layer), generator=gen)
+            elif s.init == "ones":
+                v.fill_(1.0)
+            # "zeros": centred norm weights start at 0 (scale 1 + w = 1)
+        for name in ("tok_embeddings", "lm_head"):
+            layout.view(master, name)[self.vocab_size:].zero_()
+
+    def make_engine(self, layout, params, grads, batch: int, seq: int) -> "GlimmerEngine":
+        return GlimmerEngine(self, layout, params, grads, batch, seq)
+
+    @classmethod
+    def from_spec(cls, spec, **over) -> "GlimmerConfig":
+        bs = spec.block_spec
+        kw = dict(n_layer=spec.num_layers, d_model=spec.model_dim, n_head=bs.num_heads, n_kv_head=bs.num_kv_heads or bs.num_heads,
+                  head_dim=bs.head_dim, d_ff=bs.intermediate_size, vocab_size=spec.vocab_size, window=bs.window_size,
+                  global_every=len(bs.layer_attention_pattern) or 0, rope_theta=bs.rope_theta, q_scale=bs.q_scale_factor,
+                  norm_eps=bs.norm_eps, post_norm_eps=bs.post_norm_eps, qk_norm_eps=bs.qk_norm_eps, logit_softcap=spec.logit_softcap,
+                  output_multiplier=spec.output_multiplier, z_loss=spec.z_loss_coef)
+        kw.update(over)
+        return cls(**kw)
+
+
+def glimmer_param_specs(cfg: GlimmerConfig) -> list[ParamSpec]:
+    C, Fd, Vp = cfg.d_model, cfg.d_ff, cfg.padded_vocab
+    specs = [ParamSpec("tok_embeddings", (Vp, C), True, "normal")]
+    for l in range(cfg.n_layer):
+        p = f"layers.{l}."
+        specs += [ParamSpec(p + "attn_norm", (C,), False, "zeros"), ParamSpec(p + "wqkvg", (cfg.qkv_dim + cfg.att_dim, C), True, "normal"),
+                  ParamSpec(p + "wo", (C, cfg.att_dim), True, "resid"), ParamSpec(p + "post_attn_norm", (C,), False, "zeros"),
+                  ParamSpec(p + "mlp_norm", (C,), False, "zeros"), ParamSpec(p + "w_gate_up", (2 * Fd, C), True, "normal"),
+                  ParamSpec(p + "w_down", (C, Fd), True, "resid"), ParamSpec(p + "post_mlp_norm", (C,), False, "zeros")]
+    specs += [ParamSpec("norm", (C,), False, "ones"), ParamSpec("lm_head", (Vp, C), True, "normal")]
+    return specs
+
+
+# ------------------------------------------------------------------------------- oracle --
+def glimmer_reference_loss(cfg: GlimmerConfig, p: dict[str, torch.Tensor], tokens: torch.Tensor, targets: torch.Tensor,
+                           loss_mask: torch.Tensor | None = None):
+    """Plain PyTorch restatement with this engine's parameter names. Returns (loss, logits [B, T, V], row
+    losses [B, T]); with ``loss_mask`` the loss is the masked mean."""
+    import torch.nn.functional as F
+    B, T = tokens.shape
+    hd, H, Hkv, Fd = cfg.head_dim, cfg.n_head, cfg.n_kv_head, cfg.d_ff
+
+    def crms(x, w, eps, centered=True):
+        y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+        return y if w is None else y * (1.0 + w if centered else w)
+
+    x = crms(p["tok_embeddings"][tokens.long()], None, cfg.norm_eps)
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, device=x.device, dtype=torch.float32) / hd))
+    ang = torch.outer(torch.arange(T, device=x.device, dtype=torch.float32), inv)
+    cos, sin = ang.cos().to(x.dtype), ang.sin().to(x.dtype)
+
+    def rot(t):
+        a, b = t[..., :hd // 2], t[..., hd // 2:]
+        return torch.cat((a * cos - b * sin, b * cos + a * sin), -1)
+
+    pos = torch.arange(T, device=x.device)
+    for l in range(cfg.n_layer):
+        g = lambda k: p[f"layers.{l}.{k}"]  # noqa: E731
+        h = crms(x, g("attn_norm"), cfg.norm_eps)
+        qkvg = h @ g("wqkvg").T
+        q = qkvg[..., :H * hd].view(B, T, H, hd).transpose(1, 2)
+        k = qkvg[..., H * hd:(H + Hkv) * hd].view(B, T, Hkv, hd).transpose(1, 2)
+        v = qkvg[..., (H + Hkv) * hd:cfg.qkv_dim].view(B, T, Hkv, hd).transpose(1, 2)
+        gate = torch.sigmoid(qkvg[..., cfg.qkv_dim:])
+        q, k = crms(q, None, cfg.qk_norm_eps) * cfg.q_scale, crms(k, None, cfg.qk_norm_eps)
+        local = cfg.is_local(l)
+        if local:
+            q, k = rot(q), rot(k)
+        mask = pos[None, :] <= pos[:, None]
+        if local and cfg.window > 0:
+            mask = mask & (pos[None, :] > pos[:, None] - cfg.window)
+        a = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, enable_gqa=H != Hkv)
+        a = a.transpose(1, 2).reshape(B, T, H * hd) * gate
+        x = x + crms(a @ g("wo").T, g("post_attn_norm"), cfg.post_norm_eps)
+        h = crms(x, g("mlp_norm"), cfg.norm_eps)
+        gu = h @ g("w_gate_up").T
+        x = x + crms((F.silu(gu[..., :Fd]) * gu[..., Fd:]) @ g("w_down").T, g("post_mlp_norm"), cfg.post_norm_eps)
+    x = crms(x, p["norm"], cfg.norm_eps, centered=False)
+    logits = (x @ p["lm_head"].T)[..., :cfg.vocab_size] * cfg.output_multiplier
+    if cfg.logit_softcap > 0:
+        logits = cfg.logit_softcap * torch.tanh(logits / cfg.logit_softcap)
+    lf = logits.float()
+    lse = torch.logsumexp(lf, -1)
+    rows = lse - lf.gather(-1, targets.long().unsqueeze(-1)).squeeze(-1) + cfg.z_loss * lse * lse
+    if loss_mask is None:
+        return rows.mean(), logits, rows
+    m = loss_mask.to(rows.dtype)
+    return (rows * m).sum() / m.sum().clamp(min=1.0), logits, rows
+
+
+# ------------------------------------------------------------------------------- engine --
+class GlimmerEngine:
+    OBJECTIVES = ("ar", "sft", "dpo")
+
+    def __init__(self, cfg: GlimmerConfig, layout: FlatLayout, params: torch.Tensor, grads: torch.Tensor, batch: int, seq: int) -> None:
+        from ..ops import infer as I
+        from ..ops import kernels as K
+        from ..ops.gemm import gemm
+        self.K, self.I, self.gemm = K, I, gemm
+        self.cfg, self.layout, self.B, self.T = cfg, layout, batch, seq
+        if seq > cfg.max_seq_len:
+            raise ValueError("sequence longer than max_seq_len")
+        if cfg.head_dim not in (64, 128):
+            raise ValueError("head_dim must be 64 or 128")
+        self.params, self.grads = params, grads
+        self.p, self.g = layout.views(params), layout.views(grads)
+        dev = params.device
+        N, C, Fd, Q, A = batch * seq, cfg.d_model, cfg.d_ff, cfg.qkv_dim, cfg.att_dim
+        bf, f32 = torch.bfloat16, torch.float32
+        e = lambda *s, dtype=bf: torch.empty(*s, device=dev, dtype=dtype)  # noqa: E731
+        self.cos, self.sin = I.rope_tables(seq, cfg.head_dim, cfg.rope_theta, device=dev)
+        self.ones = torch.ones(C, device=dev, dtype=bf)
+        self.xe, self.re = e(N, C), e(N, dtype=f32)          # raw embeddings and the rstd of their weightless norm
+        self.x0 = e(N, C)
+        self.acts = [dict(n1=e(N, C), r1=e(N, dtype=f32), qkvg=e(N, Q + A), qk_rstd=e(N, cfg.n_head + cfg.n_kv_head, dtype=f32),
+                          att=e(N, A), attg=e(N, A), lse=e(batch, cfg.n_head, seq, dtype=f32), br=e(N, C), rp1=e(N, dtype=f32), x1=e(N, C),
+                          n2=e(N, C), r2=e(N, dtype=f32), gu=e(N, 2 * Fd), h=e(N, Fd), mb=e(N, C), rp2=e(N, dtype=f32), x2=e(N, C))
+                     for _ in range(cfg.n_layer)]
+        self.nb = e(N, C)                                       # normalised branch (temporary)
+        self.nf, self.rf = e(N, C), e(N, dtype=f32)
+        self.mean_scratch = e(N, dtype=f32)
+        self.logits = e(N, cfg.padded_vocab)
+        self.row_loss = e(N, dtype=f32)
+        self.loss = torch.zeros(1, device=dev, dtype=f32)
+        self.d_a, self.d_b, self.d_n, self.d_br = e(N, C), e(N, C), e(N, C), e(N, C)
+        self.d_h, self.d_gu = e(N, Fd), e(N, 2 * Fd)
+        self.d_qkvg, self.d_attg, self.d_att = e(N, Q + A), e(N, A), e(N, A)
+        self.delta = e(batch, cfg.n_head, seq, dtype=f32)
+        self.scratch = e(max(64 * 2 * max(2 * Fd, Q + A, C), K.norm_fused_rows() * 3 * C), dtype=f32)
+        self.ws = e(32 * 1024 * 1024, dtype=f32)
+        self.tokens = torch.zeros(N, device=dev, dtype=torch.int32)
+        self.targets = torch.zeros(N, device=dev, dtype=torch.int32)
+        # objective state
+        self.objective = "ar"
+        self.loss_mask = torch.ones(N, device=dev, dtype=f32)       # SFT / DPO: rows that count
+        self.row_scale = torch.ones(N, device=dev, dtype=f32)       # per-row gradient scale handed to the loss kernel
+        self.ref_logps = torch.zeros(batch, device=dev, dtype=f32)  # DPO: frozen reference sequence log-probabilities
+        self.seq_logps = torch.zeros(batch, device=dev, dtype=f32)
+        self.dpo_stats = torch.zeros(3, device=dev, dtype=f32)      # loss, reward accuracy, reward margin
+        self.timer = None
+
+    # --------------------------------------------------------------------------- inputs --
+    def set_batch(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
+        self.tokens.copy_(tokens.reshape(-1), non_blocking=True)
+        self.targets.copy_(targets.reshape(-1), non_blocking=True)
+
+    def set_objective(self, objective: str) -> None:
+        if objective not in self.OBJECTIVES:
+            raise ValueError(f"objective must be one of {self.OBJECTIVES}")
+        if objective == "dpo" and self.B % 2:
+            raise ValueError("DPO batches hold (chosen, rejected) pairs: the batch size must be even")
+        self.objective = objective
+
+    def set_loss_mask(self, mask: torch.Tensor) -> None:
+        """mask [B, T] (1 = the row's target counts). Used by the ``sft`` and ``dpo`` objectives."""
+        self.loss_mask.copy_(mask.reshape(-1).to(self.loss_mask.dtype), non_blocking=True)
+
+    def set_reference_logps(self, logps: torch.Tensor) -> None:
+        """[B] sequence log-probabilities of the frozen reference model (first half chosen, second half rejected)."""
+        self.ref_logps.copy_(logps.reshape(-1).to(self.ref_logps.dtype), non_blocking=True)
+
+    def _views(self, t):
+        cfg = self.cfg
+        q_end, k_end = cfg.n_head * cfg.head_dim, (cfg.n_head + cfg.n_kv_head) * cfg.head_dim
+        return t[:, :q_end], t[:, q_end:k_end], t[:, k_end:cfg.qkv_dim], t[:, cfg.qkv_dim:]
+
+    # -------------------------------------------------------------------------- forward --
+    def forward(self, *, compute_grad_logits: bool = True, grad_scale: float | None = None) -> torch.Tensor:
+        K, I, gemm, cfg, p = self.K, self.I, self.gemm, self.cfg, self.p
+        B, T, N = self.B, self.T, self.B * self.T
+        Hq, Hkv, hd, Fd = cfg.n_head, cfg.n_kv_head, cfg.head_dim, cfg.d_ff
+        rms = dict(mode=K.NORM_RMS, mean=self.mean_scratch)
+        K.embedding_forward(self.tokens, p["tok_embeddings"], None, T=T, out=self.xe)
+        K.norm_forward(self.xe, self.ones, None, eps=cfg.norm_eps, out=self.x0, rstd=self.re, **rms)
+        x = self.x0
+        for l, a in enumerate(self.acts):
+            pre, local = f"layers.{l}.", cfg.is_local(l)
+            K.norm_forward(x, p[pre + "attn_norm"], None, eps=cfg.norm_eps, centered=True, out=a["n1"], rstd=a["r1"], **rms)
+            gemm(a["n1"], p[pre + "wqkvg"], out=a["qkvg"])
+            K.qk_norm_forward(a["qkvg"], Hq, Hkv, hd, eps=cfg.qk_norm_eps, q_scale=cfg.q_scale, rstd=a["qk_rstd"])
+            if local:
+                I.rope_inplace(a["qkvg"], T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=self.cos, sin=self.sin, convention="hf")
+            q, k, v, gate = self._views(a["qkvg"])
+            K.attention_forward(q, k, v, B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, causal=True,
+                                window=cfg.window if local else 0, out=a["att"], lse=a["lse"])
+            K.sigmoid_gate_forward(a["att"], gate, a["attg"])
+            gemm(a["attg"], p[pre + "wo"], out=a["br"])
+            K.norm_forward(a["br"], p[pre + "post_attn_norm"], None, eps=cfg.post_norm_eps, centered=True, out=self.nb, rstd=a["rp1"], **rms)
+            torch.add(x, self.nb, out=a["x1"])
+            K.norm_forward(a["x1"], p[pre + "mlp_norm"], None, eps=cfg.norm_eps, centered=True, out=a["n2"], rstd=a["r2"], **rms)
+            gemm(a["n2"], p[pre + "w_gate_up"], out=a["gu"])
+            I.swiglu_forward(a["gu"], Fd, out=a["h"])
+            gemm(a["h"], p[pre + "w_down"], out=a["mb"])
+            K.norm_forward(a["mb"], p[pre + "post_mlp_norm"], None, eps=cfg.post_norm_eps, centered=True, out=self.nb, rstd=a["rp2"], **rms)
+            torch.add(a["x1"], self.nb, out=a["x2"])
+            x = a["x2"]
+        K.norm_forward(x, p["norm"], None, eps=cfg.norm_eps, out=self.nf, rstd=self.rf, **rms)
+        if cfg.logit_softcap > 0:
+            gemm(self.nf, p["lm_head"], act="tanh_cap", act_param=cfg.logit_softcap, alpha=cfg.output_multiplier, out=self.logits)
+        else:
+            gemm(self.nf, p["lm_head"], alpha=cfg.output_multiplier, out=self.logits)
+        return self._loss(compute_grad_logits, grad_scale)
+
+    def _ce(self, write_grad: bool, grad_scale: float, loss_scale: float, row_scale, z: float | None = None) -> None:
+        cfg = self.cfg
+        self.K.cross_entropy(self.logits, self.targets, vocab=cfg.vocab_size, cap=cfg.logit_softcap,
+                             z_coef=cfg.z_loss if z is None else z, grad_scale=grad_scale,
+                             loss_scale=loss_scale, row_scale=row_scale, write_grad=write_grad, row_loss=self.row_loss, mean_loss=self.loss)
+
+    def _loss(self, compute_grad: bool, grad_scale: float | None) -> torch.Tensor:
+        N = self.B * self.T
+        if self.objective == "ar":
+            self._ce(compute_grad, 1.0 / N if grad_scale is None else grad_scale, 1.0 / N, None)
+            return self.loss
+        if self.objective == "sft":
+            # masked mean: every counted row weighs 1 / (number of counted rows)
+            torch.div(self.loss_mask, self.loss_mask.sum().clamp(min=1.0), out=self.row_scale)
+            self._ce(compute_grad, 1.0 if grad_scale is None else grad_scale * N, 1.0, self.row_scale)
+            return self.loss
+        # DPO: pass 1 leaves the logits intact and yields the row losses = -log p(target)
+        self._ce(False, 1.0, 1.0, None, z=0.0)
+        half = self.B // 2
+        torch.sum((self.row_loss * self.loss_mask).view(self.B, self.T), dim=1, out=self.seq_logps)
+        self.seq_logps.neg_()
+        pol, ref = self.seq_logps, self.ref_logps
+        margin = self.cfg.dpo_beta * ((pol[:half] - pol[half:]) - (ref[:half] - ref[half:]))
+        self.dpo_stats[0] = torch.nn.functional.softplus(-margin).mean()
+        self.dpo_stats[1] = (margin > 0).float().mean()
+        self.dpo_stats[2] = margin.mean()
+        self.loss.copy_(self.dpo_stats[:1])
+        if compute_grad:
+            # d loss / d logp_chosen = -beta * sigmoid(-margin) / pairs, the opposite for rejected; logp = -sum(row loss)
+            coef = self.cfg.dpo_beta * torch.sigmoid(-margin) / half
+            per_seq = torch.cat([coef, -coef])                      # d loss / d (sum of row losses) per sequence
+            torch.mul(self.loss_mask.view(self.B, self.T), per_seq.unsqueeze(1), out=self.row_scale.view(self.B, self.T))
+            keep = self.loss.clone()
+            self._ce(True, 1.0 if grad_scale is None else grad_scale * N, 1.0, self.row_scale, z=0.0)
+            self.loss.copy_(keep)                                   # the kernel's own mean is not the DPO loss
+        return self.loss
+
+    # ------------------------------------------------------------------------- backward --
+    def backward(self) -> None:
+        K, I, gemm, cfg, p, g = self.K, self.I, self.gemm, self.cfg, self.p, self.g
+        B, T = self.B, self.T
+        Hq, Hkv, hd, Fd = cfg.n_head, cfg.n_kv_head, cfg.head_dim, cfg.d_ff
+        sc, ws, mult = self.scratch, self.ws, cfg.output_multiplier
+        rms = dict(mode=K.NORM_RMS)
+        dx, spare = self.d_a, self.d_b
+        gemm(self.logits, p["lm_head"], b_mn=True, alpha=mult, out=self.d_n)
+        gemm(self.logits, self.nf, a_mn=True, b_mn=True, alpha=mult, out=g["lm_head"])
+        x_last = self.acts[-1]["x2"] if self.acts else self.x0
+        K.norm_backward(self.d_n, x_last, p["norm"], None, self.rf, g["norm"], None, sc, out=dx, **rms)
+        for l in range(cfg.n_layer - 1, -1, -1):
+            a, pre, local = self.acts[l], f"layers.{l}.", cfg.is_local(l)
+            x_in = self.acts[l - 1]["x2"] if l > 0 else self.x0
+            # MLP sandwich: x2 = x1 + post_norm(w_down(swiglu(w_gate_up(norm(x1)))))
+            K.norm_backward(dx, a["mb"], p[pre + "post_mlp_norm"], None, a["rp2"], g[pre + "post_mlp_norm"], None, sc, centered=True,
+                            out=self.d_br, **rms)
+            gemm(self.d_br, p[pre + "w_down"], b_mn=True, out=self.d_h)
+            gemm(self.d_br, a["h"], a_mn=True, b_mn=True, workspace=ws, out=g[pre + "w_down"])
+            I.swiglu_backward(a["gu"], self.d_h, Fd, out=self.d_gu)
+            gemm(self.d_gu, p[pre + "w_gate_up"], b_mn=True, out=self.d_n)
+            gemm(self.d_gu, a["n2"], a_mn=True, b_mn=True, workspace=ws, out=g[pre + "w_gate_up"])
+            K.norm_backward(self.d_n, a["x1"], p[pre + "mlp_norm"], None, a["r2"], g[pre + "mlp_norm"], None, sc, centered=True, dresid=dx,
+                            out=spare, **rms)
+            dx, spare = spare, dx
+            # attention sandwich: x1 = x + post_norm(wo(att * sigmoid(gate)))
+            K.norm_backward(dx, a["br"], p[pre + "post_attn_norm"], None, a["rp1"], g[pre + "post_attn_norm"], None, sc, centered=True,
+                            out=self.d_br, **rms)
+            gemm(self.d_br, p[pre + "wo"], b_mn=True, out=self.d_attg)
+            gemm(self.d_br, a["attg"], a_mn=True, b_mn=True, workspace=ws, out=g[pre + "wo"])
+            q, k, v, gate = self._views(a["qkvg"])
+            dq, dk, dv, dgate = self._views(self.d_qkvg)
+            K.sigmoid_gate_backward(self.d_attg, a["att"], gate, self.d_att, dgate)
+            K.attention_backward(self.d_att, q, k, v, a["att"], a["lse"], B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, causal=True,
+                                 window=cfg.window if local else 0, dq=dq, dk=dk, dv=dv, delta=self.delta)
+            if local:
+                I.rope_inplace(self.d_qkvg, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=self.cos, sin=self.sin, convention="hf",
+                               backward=True)
+                # the norm backward needs the normalised, un-rotated q / k: undo the rotation of the saved copy
+                I.rope_inplace(a["qkvg"], T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=self.cos, sin=self.sin, convention="hf",
+                               backward=True)
+            K.qk_norm_backward(self.d_qkvg, a["qkvg"], a["qk_rstd"], Hq, Hkv, hd, q_scale=cfg.q_scale)
+            gemm(self.d_qkvg, p[pre + "wqkvg"], b_mn=True, out=self.d_n)
+            gemm(self.d_qkvg, a["n1"], a_mn=True, b_mn=True, workspace=ws, out=g[pre + "wqkvg"])
+            K.norm_backward(self.d_n, x_in, p[pre + "attn_norm"], None, a["r1"], g[pre + "attn_norm"], None, sc, centered=True, dresid=dx,
+                            out=spare, **rms)
+            dx, spare = spare, dx
+        # weightless norm of the embeddings, then the scatter into the table
+        K.norm_backward(dx, self.xe, self.ones, None, self.re, None, None, sc, out=spare, **rms)
+        g["tok_embeddings"].zero_()
+        K.embedding_backward(spare, self.tokens, g["tok_embeddings"], None, B=B, T=T)
+
+    def logits_view(self) -> torch.Tensor:
+        return self.logits.view(self.B, self.T, -1)[..., :self.cfg.vocab_size]
+
+    @torch.no_grad()
+    def sequence_logps(self, tokens: torch.Tensor, targets: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        """[B] masked sequence log-probabilities of a batch under the CURRENT parameters (forward only): what a
+        frozen copy of the model contributes as the DPO reference."""
+        keep = self.objective
+        self.set_batch(tokens, targets)
+        self.set_loss_mask(mask)
+        self.objective = "dpo"
+        self.forward(compute_grad_logits=False)
+        self.objective = keep
+        return self.seq_logps.clone()

@@ -25,13 +25,16 @@ import torch.distributed as dist
 
 GPT_VARIANTS = ("gpt2", "gpt2_zloss", "gpt2_softcap", "gpt2_qknorm", "gpt2_stable", "gpt2_qknorm_softcap_zloss", "gpt2_diff")
 LLAMA_TEMPLATES = ("llama", "llama_fast", "llama_modern", "qwen3_longctx")
+GLIMMER_FAMILIES = ("glimmer", "muse-glimmer", "muse_glimmer")
 
 __all__ = ["NativeTrainConfig", "run_native_training", "build_model_config", "training_plan", "GPT_VARIANTS", "LLAMA_TEMPLATES"]
 
 
 @dataclass
 class NativeTrainConfig:
-    base_model: str = "gpt"                 # gpt | gpt2 | gpt3 | nanogpt | llama
+    base_model: str = "gpt"                 # gpt | gpt2 | gpt3 | nanogpt | llama | muse-glimmer
+    objective: str = "ar"                   # muse-glimmer also trains "sft" and "dpo" from record shards
+    head_dim: int = 0                       # muse-glimmer: 0 = d_model / n_head
     template_name: str = "gpt2"
     dataset: str = ""                       # alias under the datasets dir, directory, or file; "" = synthetic
     output_dir: str = ""
@@ -67,6 +70,7 @@ class NativeTrainConfig:
     use_cuda_graph: bool = True
     sharded_optimizer_checkpoint: bool | None = None
     extra: dict = field(default_factory=dict)
+    extra_paths: dict = field(default_factory=dict)   # "init_from": named checkpoint whose weights start a post-training run
 
 
 def build_model_config(c: NativeTrainConfig):
@@ -83,7 +87,12 @@ def build_model_config(c: NativeTrainConfig):
         return LlamaConfig(n_layer=c.n_layer, n_head=c.n_head, n_kv_head=c.n_kv_head or c.n_head, d_model=c.d_model, d_ff=d_ff,
                            vocab_size=c.vocab_size, max_seq_len=c.seq_len, qk_norm=c.template_name == "qwen3_longctx",
                            **c.extra)
-    raise ValueError(f"no native engine for model family {c.base_model!r} (available: gpt, gpt2, gpt3, nanogpt, llama)")
+    if fam in GLIMMER_FAMILIES:
+        from .models.glimmer import GlimmerConfig
+        d_ff = c.d_ff or 3 * c.d_model
+        return GlimmerConfig(n_layer=c.n_layer, n_head=c.n_head, n_kv_head=c.n_kv_head or c.n_head, head_dim=c.head_dim or c.d_model // c.n_head,
+                             d_model=c.d_model, d_ff=d_ff, vocab_size=c.vocab_size, max_seq_len=c.seq_len, **c.extra)
+    raise ValueError(f"no native engine for model family {c.base_model!r} (available: gpt, gpt2, gpt3, nanogpt, llama, muse-glimmer)")
 
 
 def training_plan(c: NativeTrainConfig, world: int = 1) -> dict:
@@ -162,6 +171,34 @@ def _validate(trainer, loader_factory, n_batches: int) -> tuple[float, float]:
     return total / max(n, 1), (time.perf_counter() - t0) * 1e3
 
 
+def _run_glimmer_post_training(c: NativeTrainConfig) -> dict:
+    """SFT / DPO of the native Glimmer engine from record shards (``c.dataset``); one named checkpoint at the end."""
+    from .checkpoint.named import load_named_checkpoint, save_named_checkpoint
+    from .parallel.dp import AdamWConfig
+    from .trainers.glimmer_post import GlimmerPostTrainer
+    if c.base_model.lower() not in GLIMMER_FAMILIES:
+        raise ValueError(f"--objective {c.objective} has a native engine for muse-glimmer only; other families post-train in the graph runtime")
+    if not c.dataset:
+        raise ValueError(f"--objective {c.objective} needs --dataset: prepared {'preference' if c.objective == 'dpo' else 'sft'} record shards")
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    opt = AdamWConfig(lr=c.learning_rate, beta1=c.beta1, beta2=c.beta2, eps=c.eps, weight_decay=c.weight_decay, max_grad_norm=c.max_grad_norm,
+                      warmup_steps=c.warmup_steps, total_steps=c.lr_schedule_total_steps or c.max_steps,
+                      final_lr_fraction=c.final_lr_fraction, schedule=c.lr_schedule)
+    post = GlimmerPostTrainer(build_model_config(c), c.batch_size, c.seq_len, c.objective, opt, seed=c.seed, use_cuda_graph=c.use_cuda_graph)
+    init_from = c.extra_paths.get("init_from", "")
+    if init_from:
+        load_named_checkpoint(post.trainer, Path(init_from), weights_only=True)
+    report = post.fit(c.dataset, c.max_steps, allow_train_as_val=c.allow_train_as_val, log_every=c.progress_every)
+    report.update({"model_family": c.base_model, "backend": "neuralfn_b200-native", "status": "ok",
+                   "world_size": post.trainer.world, "architecture": asdict(post.trainer.cfg)})
+    if c.output_dir:
+        out_dir = Path(c.output_dir)
+        save_checkpoint_checked(post.trainer, out_dir, post.trainer.opt.step_count, dense_format=False)
+        if rank == 0:
+            (out_dir / "train_report.json").write_text(json.dumps(report, indent=2, default=str))
+    return report
+
+
 def run_native_training(c: NativeTrainConfig) -> dict:
     from .checkpoint import latest_step, load_dense_checkpoint, save_dense_checkpoint
     from .checkpoint.named import load_named_checkpoint, save_named_checkpoint
@@ -173,6 +210,8 @@ def run_native_training(c: NativeTrainConfig) -> dict:
     if "RANK" in os.environ and not dist.is_initialized():
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
         dist.init_process_group("nccl")
+    if c.objective != "ar":
+        return _run_glimmer_post_training(c)
     world = dist.get_world_size() if dist.is_initialized() else 1
     rank = dist.get_rank() if dist.is_initialized() else 0
     plan = training_plan(c, world)

@@ -130,6 +130,23 @@ def qk_norm_backward(dqkv, qkv_normed, rstd, n_q_heads: int, n_kv_heads: int, he
     _lib.check(rc, "nfn_qk_norm_backward")
 
 
+# ------------------------------------------------------------ gated attention --
+def sigmoid_gate_forward(att, gate, out):
+    """out = att * sigmoid(gate); bf16 [rows, width] views with free row strides."""
+    rc = _lib.load().nfn_sigmoid_gate_forward(_p(att), c_int(att.stride(0)), _p(gate), c_int(gate.stride(0)), _p(out), c_int(out.stride(0)),
+                                              c_longlong(att.shape[0]), c_int(att.shape[1]), _st())
+    _lib.check(rc, "nfn_sigmoid_gate_forward")
+    return out
+
+
+def sigmoid_gate_backward(dout, att, gate, datt, dgate):
+    """d(att) = dout * sigmoid(gate); d(gate) = dout * att * sigmoid'(gate)."""
+    rc = _lib.load().nfn_sigmoid_gate_backward(_p(dout), c_int(dout.stride(0)), _p(att), c_int(att.stride(0)), _p(gate), c_int(gate.stride(0)),
+                                               _p(datt), c_int(datt.stride(0)), _p(dgate), c_int(dgate.stride(0)),
+                                               c_longlong(att.shape[0]), c_int(att.shape[1]), _st())
+    _lib.check(rc, "nfn_sigmoid_gate_backward")
+
+
 # ---------------------------------------------------- differential attention glue --
 def diff_partials() -> int:
     return int(_lib.load().nfn_diff_partials())

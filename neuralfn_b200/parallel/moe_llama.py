@@ -166,11 +166,32 @@ class EPMoELlama:
         """This rank's loss over ITS batch [B, T] (cross-entropy + router losses)."""
         p, cfg = self.p, self.cfg
 
+        exchange = self._exchange(tokens.numel())
+
         def ffn(l, h, w, idx):
             q_ = f"layers.{l}."
+            if exchange is not None:
+                from .ep_fused_train import fused_expert_parallel_ffn
+                return fused_expert_parallel_ffn(h, w, idx, p[q_ + "w1"], p[q_ + "w2"], p[q_ + "w3"], exchange)
             return expert_parallel_ffn(h, w, idx, p[q_ + "w1"], p[q_ + "w2"], p[q_ + "w3"], cfg.n_experts, self.group)
 
         return _forward_loss(cfg, p, tokens, targets, ffn, self.dtype)
+
+    def _exchange(self, n_tokens: int):
+        """Peer-memory exchange buffers for the expert rows (CUDA bf16, up to 8 ranks); None selects the library
+        all-to-all (``NFN_EP_EXCHANGE=nccl``, CPU, other dtypes). Built once for the largest batch seen."""
+        import os
+        cfg = self.cfg
+        dev = self.params.device
+        if (dev.type != "cuda" or self.dtype != torch.bfloat16 or self.world > 8 or os.environ.get("NFN_EP_EXCHANGE", "peer") == "nccl"
+                or cfg.d_model % 64 or cfg.expert_hidden % 64):
+            return None
+        ex = getattr(self, "_peer_exchange", None)
+        if ex is None or ex.T < n_tokens:
+            from .ep_fused_train import PeerExchange
+            factor = float(os.environ.get("NFN_EP_CAPACITY_FACTOR", self.world))
+            ex = self._peer_exchange = PeerExchange(cfg.n_experts, cfg.top_k, cfg.d_model, n_tokens, dev, self.group, capacity_factor=factor)
+        return ex
 
     def backward(self, loss: torch.Tensor) -> None:
         self.grads.zero_()

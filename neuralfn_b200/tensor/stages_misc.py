@@ -56,12 +56,21 @@ class _FrozenGraphStage(nn.Module):
         from ..inference import graph_topology_sha256, load_pt_checkpoint
         from .compiler import CompiledTorchGraph
         graph = load_graph(self.graph_path)
-        compiled = CompiledTorchGraph(graph)
         state, meta = load_pt_checkpoint(self.weights_path, map_location=device or "cpu")
         digest = str(meta.get("graph_topology_sha256", ""))
         if digest and digest != graph_topology_sha256(graph):
             raise ValueError("frozen graph weights were saved for a different graph topology")
-        compiled.load_state_dict(state, strict=True)
+        view = self._inference_view(graph)
+        if view is None:
+            compiled = CompiledTorchGraph(graph)
+            compiled.load_state_dict(state, strict=True)
+        else:
+            # a training root (tokens, targets, ... -> loss): run the same trunk and head without the loss nodes
+            compiled = CompiledTorchGraph(view)
+            result = compiled.load_state_dict(state, strict=False)
+            if result.missing_keys:
+                raise ValueError(f"frozen graph weights lack {len(result.missing_keys)} tensors of the inference view, "
+                                 f"first: {result.missing_keys[0]}")
         for p in compiled.parameters():
             p.requires_grad = False
         compiled.train(False)
@@ -69,9 +78,24 @@ class _FrozenGraphStage(nn.Module):
         object.__setattr__(self, "_compiled", compiled)  # keep it out of the parent's state_dict
         return compiled
 
+    def _inference_view(self, graph):
+        """None when ``graph`` already maps this stage's inputs to its output; else the graph to run instead."""
+        return None
+
+    @staticmethod
+    def _training_spec(graph):
+        """The model spec stored in a training root that takes more than the token input, else None."""
+        if len(graph.input_node_ids) <= 1 or not (graph.torch_config or {}).get("template_spec"):
+            return None
+        from ..torch_templates_roots import build_model_spec_from_config
+        return build_model_spec_from_config(graph.torch_config)
+
+    def _call(self, compiled, tokens: Tensor):
+        return compiled(tokens)
+
     @torch.no_grad()
     def forward(self, tokens: Tensor) -> Tensor:
-        out = self._ensure_loaded(tokens.device)(tokens)
+        out = self._call(self._ensure_loaded(tokens.device), tokens)
         return out[0] if isinstance(out, (tuple, list)) else out
 
 
@@ -82,6 +106,13 @@ class ReferenceForwardStage(_FrozenGraphStage):
         return cls(str(cfg.get("ref_graph_path", "")), str(cfg.get("ref_weights_path", "")),
                    vocab_size=int(cfg.get("vocab_size", 256)), model_dim=int(cfg.get("model_dim", 128)))
 
+    def _inference_view(self, graph):
+        spec = self._training_spec(graph)
+        if spec is None:
+            return None
+        from ..torch_templates_roots import build_model_stage_graph
+        return build_model_stage_graph(spec, with_loss=False)
+
 
 @stage("reward_forward")
 class RewardForwardStage(_FrozenGraphStage):
@@ -89,6 +120,18 @@ class RewardForwardStage(_FrozenGraphStage):
     def from_config(cls, cfg):
         return cls(str(cfg.get("reward_graph_path", "")), str(cfg.get("reward_weights_path", "")),
                    model_dim=int(cfg.get("model_dim", 128)))
+
+    def _inference_view(self, graph):
+        spec = self._training_spec(graph)
+        if spec is None:
+            return None
+        from ..torch_templates_roots import build_reward_scoring_graph
+        return build_reward_scoring_graph(spec)
+
+    def _call(self, compiled, tokens: Tensor):
+        if compiled._expected_flat_inputs == 2:      # the scoring view: every position counts, the head reads the last one
+            return compiled(tokens, torch.ones(tokens.shape, device=tokens.device))
+        return compiled(tokens)
 
 
 # ------------------------------------------------------------ sequence-model variants --

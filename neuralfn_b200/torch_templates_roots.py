@@ -211,6 +211,18 @@ def build_reward_model_root_graph(spec: ModelSpec) -> NeuronGraph:
     return g
 
 
+def build_reward_scoring_graph(spec: ModelSpec) -> NeuronGraph:
+    """(tokens, mask) -> one reward per row: the trunk and head of the reward-model root without the pair loss
+    (same node ids, so the trained weights load unchanged)."""
+    b = GraphBuilder("reward_scoring")
+    toks, msks = b.input("tokens", "tokens"), b.input("mask")
+    hidden, _w, _auxes = _trunk(b, spec, toks)
+    reward = (b.node("masked_reward_head", {"model_dim": spec.model_dim}, [hidden, msks], "reward_head"), 0)
+    g = b.outputs(reward)
+    g.validate()
+    return g
+
+
 def build_ppo_root_graph(spec: ModelSpec) -> NeuronGraph:
     """PPO update graph over a stored rollout: (tokens, targets, loss_mask, logp_old, value_old,
     advantages, returns) -> clipped policy/value loss with entropy bonus."""

@@ -1,0 +1,166 @@
+"""Native Glimmer training engine: oracle consistency on CPU; forward, backward and the three objectives
+(next-token, response-only SFT, pairwise DPO) against autograd on the fp32 restatement on a GPU."""
+import pytest
+import torch
+
+
+def _cfg(**kw):
+    from neuralfn_b200.models.glimmer import GlimmerConfig
+    base = dict(n_layer=4, n_head=4, n_kv_head=2, head_dim=64, d_model=256, d_ff=512, vocab_size=1000, max_seq_len=128, window=48,
+                global_every=4, logit_softcap=20.0, output_multiplier=0.5, z_loss=1e-4)
+    base.update(kw)
+    return GlimmerConfig(**base)
+
+
+def test_oracle_agrees_with_the_serving_restatement():
+    from neuralfn_b200.models.glimmer import glimmer_param_specs, glimmer_reference_loss
+    from neuralfn_b200.models.gpt2 import FlatLayout
+    from neuralfn_b200.serving.tp_glimmer import GlimmerTPConfig, glimmer_reference_logits
+    cfg = _cfg(n_layer=4, d_model=64, head_dim=16, d_ff=96, vocab_size=120, window=8, vocab_pad_to=8)
+    layout = FlatLayout(glimmer_param_specs(cfg))
+    flat = torch.empty(layout.n_total)
+    cfg.init_params_(layout, flat, 5)
+    flat.add_(torch.randn(flat.shape, generator=torch.Generator().manual_seed(2)) * 0.05)
+    p = layout.views(flat)
+    tok = torch.randint(0, cfg.vocab_size, (2, 24), generator=torch.Generator().manual_seed(3))
+    loss, logits, rows = glimmer_reference_loss(cfg, p, tok, torch.roll(tok, -1, 1))
+    scfg = GlimmerTPConfig(n_layer=4, d_model=64, n_head=4, n_kv_head=2, head_dim=16, d_ff=96, vocab_size=120, window=8, global_every=4,
+                           rope_theta=cfg.rope_theta, q_scale=cfg.q_scale, norm_eps=cfg.norm_eps, post_norm_eps=cfg.post_norm_eps,
+                           qk_norm_eps=cfg.qk_norm_eps, logit_softcap=cfg.logit_softcap, output_multiplier=cfg.output_multiplier, vocab_pad_to=8)
+    q_end, k_end = cfg.att_dim, cfg.att_dim + cfg.n_kv_head * cfg.head_dim
+    sp = {"embed": p["tok_embeddings"], "final_norm": p["norm"], "head": p["lm_head"]}
+    for l in range(cfg.n_layer):
+        w = p[f"layers.{l}.wqkvg"]
+        sp.update({f"layers.{l}.wq": w[:q_end], f"layers.{l}.wk": w[q_end:k_end], f"layers.{l}.wv": w[k_end:cfg.qkv_dim],
+                   f"layers.{l}.wg": w[cfg.qkv_dim:], f"layers.{l}.w_gate": p[f"layers.{l}.w_gate_up"][:cfg.d_ff],
+                   f"layers.{l}.w_up": p[f"layers.{l}.w_gate_up"][cfg.d_ff:]})
+        for k in ("attn_norm", "wo", "post_attn_norm", "mlp_norm", "w_down", "post_mlp_norm"):
+            sp[f"layers.{l}.{k}"] = p[f"layers.{l}.{k}"]
+    assert (glimmer_reference_logits(scfg, sp, tok) - logits).abs().max() < 1e-4
+    assert torch.isfinite(loss) and rows.shape == tok.shape
+    m = torch.zeros(2, 24)
+    m[:, 10:] = 1
+    masked, _, _ = glimmer_reference_loss(cfg, p, tok, torch.roll(tok, -1, 1), m)
+    assert abs(float(masked) - float(rows[:, 10:].mean())) < 1e-5
+
+
+def test_config_from_the_benchmark_spec_and_layer_kinds():
+    from neuralfn_b200.models.glimmer import GlimmerConfig
+    from neuralfn_b200.presets_glimmer import glimmer_benchmark_shape
+    cfg = GlimmerConfig.from_spec(glimmer_benchmark_shape())
+    assert (cfg.n_layer, cfg.d_model, cfg.n_head, cfg.n_kv_head, cfg.head_dim, cfg.d_ff) == (48, 6656, 32, 2, 128, 24576)
+    assert [cfg.is_local(l) for l in range(4)] == [True, True, True, False]
+    names = [s.name for s in cfg.param_specs()]
+    assert names[0] == "tok_embeddings" and names[-1] == "lm_head" and "layers.47.post_mlp_norm" in names
+    with pytest.raises(ValueError):
+        from neuralfn_b200.models.glimmer import GlimmerEngine
+        GlimmerEngine.set_objective(object.__new__(GlimmerEngine), "ppo")
+
+
+def _setup(**kw):
+    from neuralfn_b200.models.glimmer import GlimmerEngine
+    from neuralfn_b200.models.gpt2 import FlatLayout
+    cfg = _cfg(**kw)
+    layout = FlatLayout(cfg.param_specs())
+    master = torch.empty(layout.n_total, device="cuda")
+    cfg.init_params_(layout, master, 0)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for s in layout.order:
+        if not s.decay:
+            layout.view(master, s.name).add_(torch.randn(s.shape, device="cuda", generator=g) * 0.05)
+    params = master.to(torch.bfloat16)
+    grads = torch.zeros_like(params)
+    B, T = 4, 128
+    eng = GlimmerEngine(cfg, layout, params, grads, B, T)
+    tok = torch.randint(0, cfg.vocab_size, (B, T), device="cuda", generator=g)
+    tgt = torch.roll(tok, -1, 1)
+    eng.set_batch(tok, tgt)
+    return cfg, layout, params, grads, eng, tok, tgt
+
+
+def _compare(layout, grads, ref_p, tol=6e-2):
+    gv, bad = layout.views(grads), {}
+    for name, ref in ref_p.items():
+        denom = ref.grad.norm().item() + 1e-8
+        rel = (gv[name].float() - ref.grad).norm().item() / denom
+        if rel > tol and denom > 1e-4:
+            bad[name] = (rel, denom)
+    return bad
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kw", [dict(), dict(n_head=2, n_kv_head=1, head_dim=128, logit_softcap=0.0, z_loss=0.0, global_every=2)])
+def test_next_token_objective_matches_autograd(kernel_lib, kw):
+    from neuralfn_b200.models.glimmer import glimmer_reference_loss
+    from neuralfn_b200.ops import _lib
+    cfg, layout, params, grads, eng, tok, tgt = _setup(**kw)
+    loss = eng.forward()
+    eng.backward()
+    _lib.assert_status_ok("glimmer engine")
+    ref_p = {k: v.float().clone().requires_grad_(True) for k, v in layout.views(params).items()}
+    ref_loss, ref_logits, _ = glimmer_reference_loss(cfg, ref_p, tok, tgt)
+    ref_loss.backward()
+    assert abs(loss.item() - ref_loss.item()) < 2e-2 * max(1.0, ref_loss.item())
+    assert (eng.logits_view().float() - ref_logits).abs().max() < 0.15
+    assert not _compare(layout, grads, ref_p)
+
+
+@pytest.mark.gpu
+def test_sft_objective_counts_only_masked_rows(kernel_lib):
+    from neuralfn_b200.models.glimmer import glimmer_reference_loss
+    cfg, layout, params, grads, eng, tok, tgt = _setup()
+    mask = torch.zeros(4, 128, device="cuda")
+    mask[:, 40:100] = 1
+    mask[1] = 0
+    eng.set_objective("sft")
+    eng.set_loss_mask(mask)
+    loss = eng.forward()
+    eng.backward()
+    ref_p = {k: v.float().clone().requires_grad_(True) for k, v in layout.views(params).items()}
+    ref_loss, _, _ = glimmer_reference_loss(cfg, ref_p, tok, tgt, mask)
+    ref_loss.backward()
+    assert abs(loss.item() - ref_loss.item()) < 2e-2 * max(1.0, ref_loss.item())
+    assert not _compare(layout, grads, ref_p)
+
+
+@pytest.mark.gpu
+def test_dpo_objective_matches_autograd(kernel_lib):
+    import torch.nn.functional as F
+
+    from neuralfn_b200.models.glimmer import glimmer_reference_loss
+    cfg, layout, params, grads, eng, tok, tgt = _setup(z_loss=0.0)
+    mask = torch.zeros(4, 128, device="cuda")
+    mask[:, 64:120] = 1
+    ref_logps = torch.tensor([-300.0, -310.0, -295.0, -305.0], device="cuda")
+    eng.set_objective("dpo")
+    eng.set_loss_mask(mask)
+    eng.set_reference_logps(ref_logps)
+    loss = eng.forward()
+    eng.backward()
+    ref_p = {k: v.float().clone().requires_grad_(True) for k, v in layout.views(params).items()}
+    _, _, rows = glimmer_reference_loss(cfg, ref_p, tok, tgt)
+    pol = -(rows * mask).sum(1)
+    margin = cfg.dpo_beta * ((pol[:2] - pol[2:]) - (ref_logps[:2] - ref_logps[2:]))
+    ref_loss = F.softplus(-margin).mean()
+    ref_loss.backward()
+    assert (eng.seq_logps - pol.detach()).abs().max() < 0.02 * pol.detach().abs().max()
+    assert abs(loss.item() - ref_loss.item()) < 0.05 * max(1.0, ref_loss.item())
+    assert not _compare(layout, grads, ref_p, tol=0.12)
+    # a frozen copy of the same parameters gives a zero margin: loss = log 2
+    eng.set_reference_logps(eng.sequence_logps(tok, tgt, mask))
+    eng.set_batch(tok, tgt)
+    assert abs(eng.forward(compute_grad_logits=False).item() - 0.6931) < 1e-3
+
+
+@pytest.mark.gpu
+def test_dense_trainer_drives_the_glimmer_engine(kernel_lib):
+    from neuralfn_b200.parallel.dp import AdamWConfig
+    from neuralfn_b200.trainers.dense_gpt import DenseGPTTrainer
+    cfg = _cfg(vocab_size=512)
+    tr = DenseGPTTrainer(cfg, 4, 128, AdamWConfig(lr=3e-3, warmup_steps=2, total_steps=50, weight_decay=0.0), seed=3)
+    torch.manual_seed(0)
+    tok = torch.randint(0, 512, (4, 128))
+    tgt = torch.roll(tok, -1, dims=1)
+    losses = [tr.train_step(tok, tgt) for _ in range(14)]
+    tr.check_status()
+    assert losses[-1] < losses[0] - 0.5, losses
