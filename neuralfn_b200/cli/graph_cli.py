@@ -503,23 +503,42 @@ def add_migrate_arguments(p: argparse.ArgumentParser) -> None:
     p.add_argument("--stop-tokens", default="")
     p.add_argument("--source", default=None)
     p.add_argument("--gguf", action="append", default=[])
+    p.add_argument("--geometry", default=None, help="muse-glimmer kinds: JSON (text or file) overriding the published geometry, e.g. for small test models")
+    p.add_argument("--allow-extra-prefix", action="append", default=[], help="tensor-name prefix to skip (e.g. model.vision_tower.)")
     p.add_argument("--artifact", default=None)
     p.add_argument("--checkpoint", default=None)
 
 
 def cmd_migrate(a) -> int:
+    if a.kind in ("muse-glimmer-to-native", "muse-glimmer-gguf-to-native"):
+        # published text weights -> a named-tensor checkpoint of the native Glimmer engine
+        from ..checkpoint import glimmer_weights as gw
+        geom = gw.GlimmerGeometry.from_json(a.geometry) if a.geometry else gw.GlimmerGeometry()
+        gguf = a.kind.endswith("gguf-to-native")
+        source = a.gguf if gguf else a.source
+        if not source:
+            raise ValueError(f"nfn migrate {a.kind} needs " + ("--gguf FILE (repeatable)" if gguf else "--source DIR"))
+        extra = tuple(x for x in (a.allow_extra_prefix or []) if x)
+        if a.dry_run:
+            if gguf:
+                from ..checkpoint.gguf import GGUFFile
+                names = {}
+                for path in source:
+                    with GGUFFile(path) as f:
+                        names.update({n: tuple(t.shape) for n, t in f.tensors.items()})
+                missing = [c.source for c in gw.gguf_contracts(geom) if names.get(c.source) != c.shape]
+                print(json.dumps({"status": "ok" if not missing else "mismatch", "tensors": len(names), "missing_or_misshapen": missing[:8]}))
+                return 0 if not missing else 2
+            print(json.dumps(gw.inspect_glimmer_safetensors(source, geom, allow_extra_prefixes=extra)))
+            return 0
+        if not a.output_dir:
+            raise ValueError("--output-dir is required (or --dry-run)")
+        man = gw.convert_glimmer_weights(source, a.output_dir, geom, gguf=gguf, allow_extra_prefixes=extra)
+        print(json.dumps({"status": "ok", "output_dir": a.output_dir, **man}))
+        return 0
     if a.kind != "graph-to-native":
-        if a.kind == "muse-glimmer-gguf-to-native" and a.gguf:
-            from ..checkpoint.gguf import read_gguf
-            tables = [read_gguf(path, load_tensors=False) for path in a.gguf]
-            print(json.dumps({"status": "inspected", "files": [{"path": p, "tensors": len(t.tensors), "metadata_keys": len(t.metadata)}
-                                                              for p, t in zip(a.gguf, tables)],
-                              "note": "GGUF tensors are parsed and dequantised by neuralfn_b200.checkpoint.gguf; the Muse-Glimmer "
-                                      "tensor contract that maps them onto a native artifact is not part of this build"}))
-            return 2
         print(json.dumps({"status": "unsupported", "kind": a.kind,
-                          "reason": "official Muse-Glimmer weight conversion is not part of this build; "
-                                    "graph-to-native covers graphs trained here"}), file=sys.stderr)
+                          "reason": "LoRA attachment to a converted Muse-Glimmer artifact is not part of this build"}), file=sys.stderr)
         return 2
     if not a.graph or not (a.output_dir or a.dry_run):
         raise ValueError("nfn migrate graph-to-native needs --graph and --output-dir (or --dry-run)")

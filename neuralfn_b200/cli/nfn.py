@@ -21,8 +21,8 @@ import sys
 
 def _add_train_flags(p: argparse.ArgumentParser) -> None:
     p.add_argument("--base-model", default="gpt", help="gpt | gpt2 | gpt3 | nanogpt | llama | muse-glimmer | embedding")
-    p.add_argument("--objective", choices=["ar", "sft", "dpo"], default="ar",
-                   help="native engines: ar (all families); sft / dpo from record shards (--base-model muse-glimmer)")
+    p.add_argument("--objective", choices=["ar", "sft", "dpo", "reward_model"], default="ar",
+                   help="native engines: ar (all families); sft / dpo / reward_model from record shards (--base-model muse-glimmer)")
     p.add_argument("--head-dim", type=int, default=0, help="muse-glimmer: attention head width (0: d_model / n_head)")
     p.add_argument("--init-from", default="", help="--objective sft|dpo: named checkpoint directory whose weights start the run")
     p.add_argument("--template-name", default="gpt2")

@@ -13,6 +13,9 @@ and the named-tensor checkpoints apply unchanged. Objectives (``GlimmerEngine.ob
 
 * ``"ar"``   next-token cross-entropy over all rows;
 * ``"sft"``  response-only cross-entropy: ``set_loss_mask`` gives the rows that count;
+* ``"reward_model"``  Bradley-Terry preference loss on a scalar head (``GlimmerConfig.reward_head=True`` adds the
+  ``reward_head`` vector): the reward of a sequence is <final-norm hidden state at its last counted position, head>;
+  the vocabulary head is skipped in both passes;
 * ``"dpo"``  pairwise preference loss over (chosen, rejected) halves of the batch against frozen
   reference log-probabilities (``set_reference_logps``): the sequence log-probabilities come from the
   cross-entropy kernel's row losses, and the backward pass re-runs that kernel with a per-row gradient
@@ -20,8 +23,9 @@ and the named-tensor checkpoints apply unchanged. Objectives (``GlimmerEngine.ob
 
 Reference: the native Glimmer trainer ``neuralfn/csrc/native_train/muse_glimmer_native_train.cpp``
 (objective table :187 and :355-359, DPO options :125 and :192, block forward :3461-3515); the block
-definition is that of ``neuralfn/torch_templates.py:493-790``. Only the sigmoid DPO loss is built here. Adapter (LoRA / QLoRA) fine-tuning, the reward-model and PPO
-objectives and activation checkpointing are not in this engine (they run in the tensor runtime).
+definition is that of ``neuralfn/torch_templates.py:493-790``; the reward head is ``MaskedRewardHeadStage`` (``neuralfn/torch_backend.py``, "masked_reward_head").
+Only the sigmoid DPO loss is built here. Adapter (LoRA / QLoRA) fine-tuning, the PPO objective and activation
+checkpointing are not in this engine (they run in the tensor runtime).
 """
 from __future__ import annotations
 
@@ -57,6 +61,7 @@ class GlimmerConfig:
     z_loss: float = 0.0
     vocab_pad_to: int = 128
     dpo_beta: float = 0.1
+    reward_head: bool = False
 
     @property
     def padded_vocab(self) -> int:
@@ -118,14 +123,17 @@ def glimmer_param_specs(cfg: GlimmerConfig) -> list[ParamSpec]:
                   ParamSpec(p + "mlp_norm", (C,), False, "zeros"), ParamSpec(p + "w_gate_up", (2 * Fd, C), True, "normal"),
                   ParamSpec(p + "w_down", (C, Fd), True, "resid"), ParamSpec(p + "post_mlp_norm", (C,), False, "zeros")]
     specs += [ParamSpec("norm", (C,), False, "ones"), ParamSpec("lm_head", (Vp, C), True, "normal")]
+    if cfg.reward_head:
+        specs.append(ParamSpec("reward_head", (C,), False, "normal"))
     return specs
 
 
 # ------------------------------------------------------------------------------- oracle --
 def glimmer_reference_loss(cfg: GlimmerConfig, p: dict[str, torch.Tensor], tokens: torch.Tensor, targets: torch.Tensor,
-                           loss_mask: torch.Tensor | None = None):
+                           loss_mask: torch.Tensor | None = None, hidden_out: list | None = None):
     """Plain PyTorch restatement with this engine's parameter names. Returns (loss, logits [B, T, V], row
-    losses [B, T]); with ``loss_mask`` the loss is the masked mean."""
+    losses [B, T]); with ``loss_mask`` the loss is the masked mean. ``hidden_out`` (a list) receives the
+    final-norm hidden states [B, T, C], which the reward head reads."""
     import torch.nn.functional as F
     B, T = tokens.shape
     hd, H, Hkv, Fd = cfg.head_dim, cfg.n_head, cfg.n_kv_head, cfg.d_ff
@@ -166,6 +174,8 @@ def glimmer_reference_loss(cfg: GlimmerConfig, p: dict[str, torch.Tensor], token
         gu = h @ g("w_gate_up").T
         x = x + crms((F.silu(gu[..., :Fd]) * gu[..., Fd:]) @ g("w_down").T, g("post_mlp_norm"), cfg.post_norm_eps)
     x = crms(x, p["norm"], cfg.norm_eps, centered=False)
+    if hidden_out is not None:
+        hidden_out.append(x)
     logits = (x @ p["lm_head"].T)[..., :cfg.vocab_size] * cfg.output_multiplier
     if cfg.logit_softcap > 0:
         logits = cfg.logit_softcap * torch.tanh(logits / cfg.logit_softcap)
@@ -180,7 +190,7 @@ def glimmer_reference_loss(cfg: GlimmerConfig, p: dict[str, torch.Tensor], token
 
 # ------------------------------------------------------------------------------- engine --
 class GlimmerEngine:
-    OBJECTIVES = ("ar", "sft", "dpo")
+    OBJECTIVES = ("ar", "sft", "dpo", "reward_model")
 
     def __init__(self, cfg: GlimmerConfig, layout: FlatLayout, params: torch.Tensor, grads: torch.Tensor, batch: int, seq: int) -> None:
         from ..ops import infer as I
@@ -237,8 +247,10 @@ class GlimmerEngine:
     def set_objective(self, objective: str) -> None:
         if objective not in self.OBJECTIVES:
             raise ValueError(f"objective must be one of {self.OBJECTIVES}")
-        if objective == "dpo" and self.B % 2:
-            raise ValueError("DPO batches hold (chosen, rejected) pairs: the batch size must be even")
+        if objective in ("dpo", "reward_model") and self.B % 2:
+            raise ValueError("preference batches hold (chosen, rejected) pairs: the batch size must be even")
+        if objective == "reward_model" and not self.cfg.reward_head:
+            raise ValueError("the reward_model objective needs GlimmerConfig(reward_head=True)")
         self.objective = objective
 
     def set_loss_mask(self, mask: torch.Tensor) -> None:
@@ -285,6 +297,8 @@ class GlimmerEngine:
             torch.add(a["x1"], self.nb, out=a["x2"])
             x = a["x2"]
         K.norm_forward(x, p["norm"], None, eps=cfg.norm_eps, out=self.nf, rstd=self.rf, **rms)
+        if self.objective == "reward_model":
+            return self._reward_loss()
         if cfg.logit_softcap > 0:
             gemm(self.nf, p["lm_head"], act="tanh_cap", act_param=cfg.logit_softcap, alpha=cfg.output_multiplier, out=self.logits)
         else:
@@ -328,6 +342,34 @@ class GlimmerEngine:
             self.loss.copy_(keep)                                   # the kernel's own mean is not the DPO loss
         return self.loss
 
+    def _reward_rows(self) -> torch.Tensor:
+        """Flat row index of the last counted position of every sequence (a sequence without one reads position 0)."""
+        pos = torch.arange(self.T, device=self.loss_mask.device)
+        last = torch.where(self.loss_mask.view(self.B, self.T) > 0, pos, -1).amax(1).clamp(min=0)
+        return last + torch.arange(self.B, device=last.device) * self.T
+
+    def _reward_loss(self) -> torch.Tensor:
+        half = self.B // 2
+        rows = self._reward_rows()
+        r = self.nf[rows].float() @ self.p["reward_head"].float()
+        margin = r[:half] - r[half:]
+        self.seq_logps.copy_(r)                                 # the rewards, chosen then rejected
+        self.dpo_stats[0] = torch.nn.functional.softplus(-margin).mean()
+        self.dpo_stats[1] = (margin > 0).float().mean()
+        self.dpo_stats[2] = margin.mean()
+        self.loss.copy_(self.dpo_stats[:1])
+        coef = torch.sigmoid(-margin) / half
+        self._d_reward = torch.cat([-coef, coef])               # d loss / d reward per sequence
+        return self.loss
+
+    def _reward_backward(self) -> None:
+        """d(final-norm output) has one non-zero row per sequence; the vocabulary head gets no gradient."""
+        rows, dr = self._reward_rows(), self._d_reward
+        self.d_n.zero_()
+        self.d_n[rows] = (dr[:, None] * self.p["reward_head"].float()[None, :]).to(self.d_n.dtype)
+        self.g["reward_head"].copy_((dr[:, None] * self.nf[rows].float()).sum(0))
+        self.g["lm_head"].zero_()
+
     # ------------------------------------------------------------------------- backward --
     def backward(self) -> None:
         K, I, gemm, cfg, p, g = self.K, self.I, self.gemm, self.cfg, self.p, self.g
@@ -336,8 +378,13 @@ class GlimmerEngine:
         sc, ws, mult = self.scratch, self.ws, cfg.output_multiplier
         rms = dict(mode=K.NORM_RMS)
         dx, spare = self.d_a, self.d_b
-        gemm(self.logits, p["lm_head"], b_mn=True, alpha=mult, out=self.d_n)
-        gemm(self.logits, self.nf, a_mn=True, b_mn=True, alpha=mult, out=g["lm_head"])
+        if self.objective == "reward_model":
+            self._reward_backward()
+        else:
+            gemm(self.logits, p["lm_head"], b_mn=True, alpha=mult, out=self.d_n)
+            gemm(self.logits, self.nf, a_mn=True, b_mn=True, alpha=mult, out=g["lm_head"])
+            if cfg.reward_head:
+                g["reward_head"].zero_()
         x_last = self.acts[-1]["x2"] if self.acts else self.x0
         K.norm_backward(self.d_n, x_last, p["norm"], None, self.rf, g["norm"], None, sc, out=dx, **rms)
         for l in range(cfg.n_layer - 1, -1, -1):

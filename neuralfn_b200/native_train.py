@@ -33,7 +33,7 @@ __all__ = ["NativeTrainConfig", "run_native_training", "build_model_config", "tr
 @dataclass
 class NativeTrainConfig:
     base_model: str = "gpt"                 # gpt | gpt2 | gpt3 | nanogpt | llama | muse-glimmer
-    objective: str = "ar"                   # muse-glimmer also trains "sft" and "dpo" from record shards
+    objective: str = "ar"                   # muse-glimmer also trains "sft", "dpo" and "reward_model" from record shards
     head_dim: int = 0                       # muse-glimmer: 0 = d_model / n_head
     template_name: str = "gpt2"
     dataset: str = ""                       # alias under the datasets dir, directory, or file; "" = synthetic
@@ -179,7 +179,7 @@ def _run_glimmer_post_training(c: NativeTrainConfig) -> dict:
     if c.base_model.lower() not in GLIMMER_FAMILIES:
         raise ValueError(f"--objective {c.objective} has a native engine for muse-glimmer only; other families post-train in the graph runtime")
     if not c.dataset:
-        raise ValueError(f"--objective {c.objective} needs --dataset: prepared {'preference' if c.objective == 'dpo' else 'sft'} record shards")
+        raise ValueError(f"--objective {c.objective} needs --dataset: prepared {'sft' if c.objective == 'sft' else 'preference'} record shards")
     rank = dist.get_rank() if dist.is_initialized() else 0
     opt = AdamWConfig(lr=c.learning_rate, beta1=c.beta1, beta2=c.beta2, eps=c.eps, weight_decay=c.weight_decay, max_grad_norm=c.max_grad_norm,
                       warmup_steps=c.warmup_steps, total_steps=c.lr_schedule_total_steps or c.max_steps,

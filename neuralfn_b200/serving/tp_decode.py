@@ -67,8 +67,9 @@ class TPLlamaDecoder:
         if full_params is not None:
             sh = shard_llama_params(cfg, full_params, tp.rank, W)
             to = lambda t: t.to(dev, self.dtype).contiguous()
-            self.embed = to(sh["tok_embeddings"])
-            self.head = to(sh["lm_head"][tp.rank * self.Vl:(tp.rank + 1) * self.Vl])
+            # the decoder keeps the embedding table whole (one row gather per token) and shards the head by vocabulary rows
+            self.embed = to(full_params["tok_embeddings"])
+            self.head = to(full_params["lm_head"][tp.rank * self.Vl:(tp.rank + 1) * self.Vl])
             self.norm = to(sh["norm"])
             self.layers = [{k: to(sh[f"layers.{l}.{k}"]) for k in ("attn_norm", "wqkv", "wo", "ffn_norm", "w_gate_up", "w_down")}
                            for l in range(cfg.n_layer)]

@@ -1,5 +1,5 @@
-"""Post-training of the native Glimmer engine: response-only SFT and pairwise DPO from prepared record
-shards, on the dense trainer's step (sharded AdamW over peer memory, CUDA-graph replay).
+"""Post-training of the native Glimmer engine: response-only SFT, pairwise DPO and the Bradley-Terry reward model
+from prepared record shards, on the dense trainer's step (sharded AdamW over peer memory, CUDA-graph replay).
 
 SFT feeds each batch's loss mask to the engine; the step is otherwise the pre-training step. DPO stacks
 every batch as (chosen rows, rejected rows), so one forward / backward covers the pair. The frozen
@@ -26,10 +26,13 @@ __all__ = ["GlimmerPostTrainer"]
 class GlimmerPostTrainer:
     def __init__(self, cfg: GlimmerConfig, batch: int, seq: int, objective: str, optim: AdamWConfig | None = None, *, seed: int = 1337,
                  use_cuda_graph: bool = True, group=None) -> None:
-        if objective not in ("sft", "dpo"):
-            raise ValueError("objective must be 'sft' or 'dpo' (pre-training uses DenseGPTTrainer directly)")
+        if objective not in ("sft", "dpo", "reward_model"):
+            raise ValueError("objective must be 'sft', 'dpo' or 'reward_model' (pre-training uses DenseGPTTrainer directly)")
+        if objective == "reward_model" and not cfg.reward_head:
+            from dataclasses import replace
+            cfg = replace(cfg, reward_head=True)
         self.objective, self.pairs = objective, batch
-        rows = 2 * batch if objective == "dpo" else batch
+        rows = batch if objective == "sft" else 2 * batch
         self.trainer = DenseGPTTrainer(cfg, rows, seq, optim, seed=seed, use_cuda_graph=use_cuda_graph, group=group)
         self.engine = self.trainer.engine
         self.engine.set_objective(objective)
@@ -51,10 +54,12 @@ class GlimmerPostTrainer:
         ids, tg, mask = self.stack_preference(rec)
         return self.engine.sequence_logps(ids.to(self.trainer.device), tg.to(self.trainer.device), mask).cpu()
 
-    def dpo_step(self, rec: dict, ref_logps: torch.Tensor) -> dict:
+    def dpo_step(self, rec: dict, ref_logps: torch.Tensor | None = None) -> dict:
+        """One preference step: DPO against ``ref_logps``, or the reward-model loss when the objective is ``reward_model``."""
         ids, tg, mask = self.stack_preference(rec)
         self.engine.set_loss_mask(mask)
-        self.engine.set_reference_logps(ref_logps)
+        if ref_logps is not None:
+            self.engine.set_reference_logps(ref_logps)
         self.trainer.train_step(ids, tg, return_loss=False)
         self._h_stats.copy_(self.engine.dpo_stats, non_blocking=True)
         torch.cuda.current_stream().synchronize()
@@ -65,7 +70,7 @@ class GlimmerPostTrainer:
         """``steps`` optimizer steps over the record shards at ``records`` (wrapping around at the end)."""
         from ..data.shards import RecordReader
         tr = self.trainer
-        reader = RecordReader(records, "preference" if self.objective == "dpo" else "sft", split, self.pairs,
+        reader = RecordReader(records, "sft" if self.objective == "sft" else "preference", split, self.pairs,
                               allow_train_as_val=allow_train_as_val, rank=tr.rank, world=tr.world)
         if reader.seq_len != tr.seq:
             raise ValueError(f"records hold sequences of {reader.seq_len} tokens, the trainer was built for {tr.seq}")
@@ -91,7 +96,10 @@ class GlimmerPostTrainer:
         ref_ms = (time.perf_counter() - t0) * 1e3
         t0 = time.perf_counter()
         for i, rec in enumerate(batches(steps)):
-            out = self.dpo_step(rec, refs[i % len(refs)]) if self.objective == "dpo" else {"loss": self.sft_step(rec)}
+            if self.objective == "sft":
+                out = {"loss": self.sft_step(rec)}
+            else:
+                out = self.dpo_step(rec, refs[i % len(refs)] if refs else None)
             history.append(out)
             if log_every and (i + 1) % log_every == 0 and tr.rank == 0:
                 import sys

@@ -153,6 +153,33 @@ def test_dpo_objective_matches_autograd(kernel_lib):
 
 
 @pytest.mark.gpu
+def test_reward_model_objective_matches_autograd(kernel_lib):
+    import torch.nn.functional as F
+
+    from neuralfn_b200.models.glimmer import glimmer_reference_loss
+    cfg, layout, params, grads, eng, tok, tgt = _setup(reward_head=True)
+    mask = torch.zeros(4, 128, device="cuda")
+    for b, end in enumerate((100, 128, 77, 90)):
+        mask[b, 20:end] = 1
+    eng.set_objective("reward_model")
+    eng.set_loss_mask(mask)
+    loss = eng.forward()
+    eng.backward()
+    ref_p = {k: v.float().clone().requires_grad_(True) for k, v in layout.views(params).items()}
+    hidden = []
+    glimmer_reference_loss(cfg, ref_p, tok, tgt, hidden_out=hidden)
+    last = torch.tensor([99, 127, 76, 89], device="cuda")
+    r = hidden[0][torch.arange(4, device="cuda"), last] @ ref_p["reward_head"]
+    ref_loss = F.softplus(-(r[:2] - r[2:])).mean()
+    ref_loss.backward()
+    ref_p["lm_head"].grad = torch.zeros_like(ref_p["lm_head"])
+    assert (eng.seq_logps - r.detach()).abs().max() < 0.05 * max(1.0, float(r.detach().abs().max()))
+    assert abs(loss.item() - ref_loss.item()) < 0.03
+    assert not _compare(layout, grads, ref_p, tol=0.1)
+    assert float(layout.views(grads)["lm_head"].abs().max()) == 0.0
+
+
+@pytest.mark.gpu
 def test_dense_trainer_drives_the_glimmer_engine(kernel_lib):
     from neuralfn_b200.parallel.dp import AdamWConfig
     from neuralfn_b200.trainers.dense_gpt import DenseGPTTrainer
