@@ -83,7 +83,23 @@ def _train_config(a):
         weight_decay=a.weight_decay, beta1=a.beta1, beta2=a.beta2, eps=a.eps, max_grad_norm=a.max_grad_norm, max_steps=a.max_steps,
         eval_every=a.eval_every, eval_batches=a.eval_batches, train_loss_every=a.train_loss_every, progress_every=a.progress_every,
         checkpoint_every=a.checkpoint_every, seed=a.seed, resume=a.resume, use_cuda_graph=not a.no_cuda_graph,
-        objective=a.objective, head_dim=a.head_dim, extra_paths={"init_from": a.init_from} if a.init_from else {})
+        objective=a.objective, head_dim=a.head_dim, extra_paths={"init_from": a.init_from} if a.init_from else {},
+        extra=_native_adapter_options(a))
+
+
+def _native_adapter_options(a) -> dict:
+    """--runtime native --adapter-type lora: adapter geometry for the native Glimmer engine (other families adapt in the graph runtime)."""
+    kind = getattr(a, "adapter_type", None)
+    if kind in (None, "none"):
+        return {}
+    if kind != "lora" or a.base_model.lower().replace("_", "-") not in ("muse-glimmer", "glimmer"):
+        raise ValueError("the native engines train LoRA adapters on --base-model muse-glimmer only; drop --runtime native for the others")
+    out = {"lora_rank": int(getattr(a, "lora_rank", None) or 16)}
+    if getattr(a, "lora_alpha", None) is not None:
+        out["lora_alpha"] = float(a.lora_alpha)
+    if getattr(a, "lora_targets", None):
+        out["lora_targets"] = tuple(t.strip() for t in a.lora_targets.split(",") if t.strip())
+    return out
 
 
 def _parallel_train_argv(a) -> list[str]:
@@ -147,7 +163,9 @@ def cmd_train(a) -> int:
         import subprocess
         argv = ["--stages", str(a.pipeline_parallel_size), "--dataset", a.dataset, "--batch-size", str(a.batch_size), "--seq-len", str(a.seq_len),
                 "--max-steps", str(a.max_steps), "--learning-rate", str(a.learning_rate), "--n-layer", str(a.n_layer), "--n-head", str(a.n_head),
-                "--d-model", str(a.d_model), "--vocab-size", str(a.vocab_size), "--seed", str(a.seed), "--output-dir", a.output_dir]
+                "--d-model", str(a.d_model), "--vocab-size", str(a.vocab_size), "--seed", str(a.seed), "--output-dir", a.output_dir,
+                "--base-model", "muse-glimmer" if a.base_model.lower().replace("_", "-") in ("muse-glimmer", "glimmer") else "llama",
+                "--head-dim", str(a.head_dim), "--n-kv-head", str(a.n_kv_head), "--d-ff", str(a.d_ff)]
         if "RANK" in os.environ:
             from ..parallel.pp import main as pp_main
             return pp_main(argv)

@@ -24,8 +24,16 @@ and the named-tensor checkpoints apply unchanged. Objectives (``GlimmerEngine.ob
 Reference: the native Glimmer trainer ``neuralfn/csrc/native_train/muse_glimmer_native_train.cpp``
 (objective table :187 and :355-359, DPO options :125 and :192, block forward :3461-3515); the block
 definition is that of ``neuralfn/torch_templates.py:493-790``; the reward head is ``MaskedRewardHeadStage`` (``neuralfn/torch_backend.py``, "masked_reward_head").
-Only the sigmoid DPO loss is built here. Adapter (LoRA / QLoRA) fine-tuning, the PPO objective and activation
-checkpointing are not in this engine (they run in the tensor runtime).
+Only the sigmoid DPO loss is built here.
+
+LoRA (``GlimmerConfig.lora_rank > 0``): the trainable flat buffer then holds only the adapters (``<projection>.lora_a`` [r, in],
+``<projection>.lora_b`` [out, r], B zero at the start) of the projections named in ``lora_targets``; the base weights sit in a
+frozen bf16 buffer owned by the engine (``load_base`` / ``merged_state``). Every adapted projection is the base GEMM plus two
+skinny GEMMs whose second one adds ``alpha / r * t B^T`` in its epilogue; the backward pass skips every base weight gradient
+(the big TN GEMMs, the norm-weight reductions and the embedding scatter), which is where LoRA's saving comes from. Reference:
+the adapter options of ``muse_glimmer_native_train.cpp:187-203`` and ``inspect_native_muse_glimmer_lora_checkpoint``
+(``neuralfn/native_muse_glimmer_checkpoint.py:580``). NF4 / K-quant base weights under the adapters, the PPO objective and
+activation checkpointing are not in this engine (they run in the tensor runtime).
 """
 from __future__ import annotations
 
@@ -36,7 +44,7 @@ import torch
 
 from .gpt2 import FlatLayout, ParamSpec
 
-__all__ = ["GlimmerConfig", "GlimmerEngine", "glimmer_param_specs", "glimmer_reference_loss"]
+__all__ = ["GlimmerConfig", "GlimmerEngine", "glimmer_param_specs", "glimmer_lora_specs", "glimmer_reference_loss"]
 
 
 @dataclass(frozen=True)
@@ -62,6 +70,20 @@ class GlimmerConfig:
     vocab_pad_to: int = 128
     dpo_beta: float = 0.1
     reward_head: bool = False
+    lora_rank: int = 0                      # > 0: train low-rank adapters over frozen base weights
+    lora_alpha: float = 32.0
+    lora_targets: tuple = ("wqkvg", "wo", "w_gate_up", "w_down")
+    base_seed: int = 1337                   # LoRA: seed of the frozen base weights until load_base() replaces them
+    # pipeline-parallel stage view: this engine owns layers [pp_layer_begin, pp_layer_end); the first stage also owns
+    # the embedding, the last one the final norm and the heads (0 / 0 = whole model)
+    pp_layer_begin: int = 0
+    pp_layer_end: int = 0
+    pp_first: bool = True
+    pp_last: bool = True
+
+    @property
+    def layer_range(self) -> range:
+        return range(self.pp_layer_begin, self.pp_layer_end or self.n_layer)
 
     @property
     def padded_vocab(self) -> int:
@@ -81,6 +103,10 @@ class GlimmerConfig:
 
     # hooks used by trainers.dense_gpt.DenseGPTTrainer
     def param_specs(self) -> list[ParamSpec]:
+        """The TRAINABLE tensors: the whole model, or only the adapters when ``lora_rank > 0``."""
+        return glimmer_lora_specs(self) if self.lora_rank > 0 else glimmer_param_specs(self)
+
+    def base_param_specs(self) -> list[ParamSpec]:
         return glimmer_param_specs(self)
 
     def init_params_(self, layout: FlatLayout, master: torch.Tensor, seed: int) -> None:
@@ -90,13 +116,16 @@ class GlimmerConfig:
             v = layout.view(master, s.name)
             if s.init == "normal":
                 v.normal_(0.0, 0.02, generator=gen)
+            elif s.init == "lora_a":
+                v.normal_(0.0, 1.0 / math.sqrt(s.shape[1]), generator=gen)
             elif s.init == "resid":
                 v.normal_(0.0, 0.02 / math.sqrt(2 * self.n_layer), generator=gen)
             elif s.init == "ones":
                 v.fill_(1.0)
             # "zeros": centred norm weights start at 0 (scale 1 + w = 1)
         for name in ("tok_embeddings", "lm_head"):
-            layout.view(master, name)[self.vocab_size:].zero_()
+            if name in layout.offsets:
+                layout.view(master, name)[self.vocab_size:].zero_()
 
     def make_engine(self, layout, params, grads, batch: int, seq: int) -> "GlimmerEngine":
         return GlimmerEngine(self, layout, params, grads, batch, seq)
@@ -113,18 +142,35 @@ class GlimmerConfig:
         return cls(**kw)
 
 
+def glimmer_lora_specs(cfg: GlimmerConfig) -> list[ParamSpec]:
+    """Adapter tensors of this stage: A [r, in] (random) and B [out, r] (zero) per targeted projection."""
+    if cfg.lora_rank % 16:
+        raise ValueError("lora_rank must be a multiple of 16 (tensor-core tile granularity)")
+    shapes = {s.name: s.shape for s in glimmer_param_specs(cfg)}
+    specs = []
+    for l in cfg.layer_range:
+        for t in cfg.lora_targets:
+            out_dim, in_dim = shapes[f"layers.{l}.{t}"]
+            specs += [ParamSpec(f"layers.{l}.{t}.lora_a", (cfg.lora_rank, in_dim), True, "lora_a"),
+                      ParamSpec(f"layers.{l}.{t}.lora_b", (out_dim, cfg.lora_rank), True, "zeros")]
+    if cfg.reward_head and cfg.pp_last:
+        specs.append(ParamSpec("reward_head", (cfg.d_model,), False, "normal"))
+    return specs
+
+
 def glimmer_param_specs(cfg: GlimmerConfig) -> list[ParamSpec]:
     C, Fd, Vp = cfg.d_model, cfg.d_ff, cfg.padded_vocab
-    specs = [ParamSpec("tok_embeddings", (Vp, C), True, "normal")]
-    for l in range(cfg.n_layer):
+    specs = [ParamSpec("tok_embeddings", (Vp, C), True, "normal")] if cfg.pp_first else []
+    for l in cfg.layer_range:
         p = f"layers.{l}."
         specs += [ParamSpec(p + "attn_norm", (C,), False, "zeros"), ParamSpec(p + "wqkvg", (cfg.qkv_dim + cfg.att_dim, C), True, "normal"),
                   ParamSpec(p + "wo", (C, cfg.att_dim), True, "resid"), ParamSpec(p + "post_attn_norm", (C,), False, "zeros"),
                   ParamSpec(p + "mlp_norm", (C,), False, "zeros"), ParamSpec(p + "w_gate_up", (2 * Fd, C), True, "normal"),
                   ParamSpec(p + "w_down", (C, Fd), True, "resid"), ParamSpec(p + "post_mlp_norm", (C,), False, "zeros")]
-    specs += [ParamSpec("norm", (C,), False, "ones"), ParamSpec("lm_head", (Vp, C), True, "normal")]
-    if cfg.reward_head:
-        specs.append(ParamSpec("reward_head", (C,), False, "normal"))
+    if cfg.pp_last:
+        specs += [ParamSpec("norm", (C,), False, "ones"), ParamSpec("lm_head", (Vp, C), True, "normal")]
+        if cfg.reward_head and cfg.lora_rank == 0:
+            specs.append(ParamSpec("reward_head", (C,), False, "normal"))
     return specs
 
 
@@ -205,6 +251,17 @@ class GlimmerEngine:
         self.params, self.grads = params, grads
         self.p, self.g = layout.views(params), layout.views(grads)
         dev = params.device
+        self.lora = cfg.lora_rank > 0
+        self.lora_scale = cfg.lora_alpha / cfg.lora_rank if self.lora else 0.0
+        if self.lora:
+            # frozen base weights in their own flat buffer; self.p resolves both kinds of names, self.g only adapters
+            self.base_layout = FlatLayout(cfg.base_param_specs())
+            master = torch.empty(self.base_layout.n_total, device=dev, dtype=torch.float32)
+            replace_cfg = GlimmerConfig(**{**cfg.__dict__, "lora_rank": 0})
+            replace_cfg.init_params_(self.base_layout, master, cfg.base_seed)
+            self.base = master.to(torch.bfloat16)
+            del master
+            self.p = {**self.base_layout.views(self.base), **self.p}
         N, C, Fd, Q, A = batch * seq, cfg.d_model, cfg.d_ff, cfg.qkv_dim, cfg.att_dim
         bf, f32 = torch.bfloat16, torch.float32
         e = lambda *s, dtype=bf: torch.empty(*s, device=dev, dtype=dtype)  # noqa: E731
@@ -215,7 +272,12 @@ class GlimmerEngine:
         self.acts = [dict(n1=e(N, C), r1=e(N, dtype=f32), qkvg=e(N, Q + A), qk_rstd=e(N, cfg.n_head + cfg.n_kv_head, dtype=f32),
                           att=e(N, A), attg=e(N, A), lse=e(batch, cfg.n_head, seq, dtype=f32), br=e(N, C), rp1=e(N, dtype=f32), x1=e(N, C),
                           n2=e(N, C), r2=e(N, dtype=f32), gu=e(N, 2 * Fd), h=e(N, Fd), mb=e(N, C), rp2=e(N, dtype=f32), x2=e(N, C))
-                     for _ in range(cfg.n_layer)]
+                     for _ in cfg.layer_range]
+        if self.lora:
+            for a in self.acts:
+                a.update({"t_" + t: e(N, cfg.lora_rank) for t in cfg.lora_targets})
+            self.d_t = e(N, cfg.lora_rank)
+        self.layers = list(cfg.layer_range)
         self.nb = e(N, C)                                       # normalised branch (temporary)
         self.nf, self.rf = e(N, C), e(N, dtype=f32)
         self.mean_scratch = e(N, dtype=f32)
@@ -261,6 +323,54 @@ class GlimmerEngine:
         """[B] sequence log-probabilities of the frozen reference model (first half chosen, second half rejected)."""
         self.ref_logps.copy_(logps.reshape(-1).to(self.ref_logps.dtype), non_blocking=True)
 
+    # ----------------------------------------------------------------------------- LoRA --
+    def load_base(self, tensors: dict[str, torch.Tensor]) -> None:
+        """Replace the frozen base weights (names and shapes of ``base_param_specs``)."""
+        if not self.lora:
+            raise RuntimeError("load_base() is for LoRA engines; full fine-tuning loads weights through the trainer")
+        for s in self.base_layout.order:
+            if tuple(tensors[s.name].shape) != tuple(s.shape):
+                raise ValueError(f"{s.name}: shape {tuple(tensors[s.name].shape)} instead of {tuple(s.shape)}")
+            self.base_layout.view(self.base, s.name).copy_(tensors[s.name])
+
+    @torch.no_grad()
+    def merged_state(self) -> dict[str, torch.Tensor]:
+        """Base weights with the adapters folded in (W + alpha / r * B A), on the host, fp32."""
+        out = {s.name: self.base_layout.view(self.base, s.name).float().cpu() for s in self.base_layout.order} if self.lora else \
+              {k: v.float().cpu() for k, v in self.p.items()}
+        if self.lora:
+            for name in list(out):
+                if name + ".lora_a" in self.p:
+                    out[name] += self.lora_scale * (self.p[name + ".lora_b"].float() @ self.p[name + ".lora_a"].float()).cpu()
+        return out
+
+    def _proj(self, x, name: str, out, acts: dict, key: str):
+        """out = x W^T (+ alpha / r * (x A^T) B^T when the projection carries an adapter)."""
+        self.gemm(x, self.p[name], out=out)
+        if self.lora and name + ".lora_a" in self.p:
+            t = acts["t_" + key]
+            self.gemm(x, self.p[name + ".lora_a"], out=t)
+            self.gemm(t, self.p[name + ".lora_b"], alpha=self.lora_scale, resid=out, out=out)
+        return out
+
+    def _proj_backward(self, dy, x, name: str, dx_out, acts: dict, key: str):
+        """dx_out = dy W (+ adapter path); weight gradients of whatever is trainable."""
+        gemm, p, g = self.gemm, self.p, self.g
+        gemm(dy, p[name], b_mn=True, out=dx_out)
+        if not self.lora:
+            gemm(dy, x, a_mn=True, b_mn=True, workspace=self.ws, out=g[name])
+        elif name + ".lora_a" in p:
+            t, s = acts["t_" + key], self.lora_scale
+            gemm(dy, p[name + ".lora_b"], b_mn=True, alpha=s, out=self.d_t)                          # [N, r] = s * dy B
+            gemm(dy, t, a_mn=True, b_mn=True, alpha=s, workspace=self.ws, out=g[name + ".lora_b"])  # [out, r] = s * dy^T t
+            gemm(self.d_t, x, a_mn=True, b_mn=True, workspace=self.ws, out=g[name + ".lora_a"])     # [r, in] = d_t^T x
+            gemm(self.d_t, p[name + ".lora_a"], b_mn=True, resid=dx_out, out=dx_out)                # + d_t A
+        return dx_out
+
+    def _gw(self, name: str):
+        """Gradient slot of a base tensor: None (= not computed) when only adapters train."""
+        return None if self.lora else self.g[name]
+
     def _views(self, t):
         cfg = self.cfg
         q_end, k_end = cfg.n_head * cfg.head_dim, (cfg.n_head + cfg.n_kv_head) * cfg.head_dim
@@ -272,13 +382,14 @@ class GlimmerEngine:
         B, T, N = self.B, self.T, self.B * self.T
         Hq, Hkv, hd, Fd = cfg.n_head, cfg.n_kv_head, cfg.head_dim, cfg.d_ff
         rms = dict(mode=K.NORM_RMS, mean=self.mean_scratch)
-        K.embedding_forward(self.tokens, p["tok_embeddings"], None, T=T, out=self.xe)
-        K.norm_forward(self.xe, self.ones, None, eps=cfg.norm_eps, out=self.x0, rstd=self.re, **rms)
-        x = self.x0
-        for l, a in enumerate(self.acts):
+        if cfg.pp_first:
+            K.embedding_forward(self.tokens, p["tok_embeddings"], None, T=T, out=self.xe)
+            K.norm_forward(self.xe, self.ones, None, eps=cfg.norm_eps, out=self.x0, rstd=self.re, **rms)
+        x = self.x0  # later stages: filled by the pipeline runtime with the previous stage's output
+        for l, a in zip(self.layers, self.acts):
             pre, local = f"layers.{l}.", cfg.is_local(l)
             K.norm_forward(x, p[pre + "attn_norm"], None, eps=cfg.norm_eps, centered=True, out=a["n1"], rstd=a["r1"], **rms)
-            gemm(a["n1"], p[pre + "wqkvg"], out=a["qkvg"])
+            self._proj(a["n1"], pre + "wqkvg", a["qkvg"], a, "wqkvg")
             K.qk_norm_forward(a["qkvg"], Hq, Hkv, hd, eps=cfg.qk_norm_eps, q_scale=cfg.q_scale, rstd=a["qk_rstd"])
             if local:
                 I.rope_inplace(a["qkvg"], T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=self.cos, sin=self.sin, convention="hf")
@@ -286,16 +397,18 @@ class GlimmerEngine:
             K.attention_forward(q, k, v, B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, causal=True,
                                 window=cfg.window if local else 0, out=a["att"], lse=a["lse"])
             K.sigmoid_gate_forward(a["att"], gate, a["attg"])
-            gemm(a["attg"], p[pre + "wo"], out=a["br"])
+            self._proj(a["attg"], pre + "wo", a["br"], a, "wo")
             K.norm_forward(a["br"], p[pre + "post_attn_norm"], None, eps=cfg.post_norm_eps, centered=True, out=self.nb, rstd=a["rp1"], **rms)
             torch.add(x, self.nb, out=a["x1"])
             K.norm_forward(a["x1"], p[pre + "mlp_norm"], None, eps=cfg.norm_eps, centered=True, out=a["n2"], rstd=a["r2"], **rms)
-            gemm(a["n2"], p[pre + "w_gate_up"], out=a["gu"])
+            self._proj(a["n2"], pre + "w_gate_up", a["gu"], a, "w_gate_up")
             I.swiglu_forward(a["gu"], Fd, out=a["h"])
-            gemm(a["h"], p[pre + "w_down"], out=a["mb"])
+            self._proj(a["h"], pre + "w_down", a["mb"], a, "w_down")
             K.norm_forward(a["mb"], p[pre + "post_mlp_norm"], None, eps=cfg.post_norm_eps, centered=True, out=self.nb, rstd=a["rp2"], **rms)
             torch.add(a["x1"], self.nb, out=a["x2"])
             x = a["x2"]
+        if not cfg.pp_last:
+            return x  # handed to the next stage
         K.norm_forward(x, p["norm"], None, eps=cfg.norm_eps, out=self.nf, rstd=self.rf, **rms)
         if self.objective == "reward_model":
             return self._reward_loss()
@@ -368,7 +481,8 @@ class GlimmerEngine:
         self.d_n.zero_()
         self.d_n[rows] = (dr[:, None] * self.p["reward_head"].float()[None, :]).to(self.d_n.dtype)
         self.g["reward_head"].copy_((dr[:, None] * self.nf[rows].float()).sum(0))
-        self.g["lm_head"].zero_()
+        if not self.lora:
+            self.g["lm_head"].zero_()
 
     # ------------------------------------------------------------------------- backward --
     def backward(self) -> None:
@@ -377,35 +491,35 @@ class GlimmerEngine:
         Hq, Hkv, hd, Fd = cfg.n_head, cfg.n_kv_head, cfg.head_dim, cfg.d_ff
         sc, ws, mult = self.scratch, self.ws, cfg.output_multiplier
         rms = dict(mode=K.NORM_RMS)
-        dx, spare = self.d_a, self.d_b
-        if self.objective == "reward_model":
-            self._reward_backward()
-        else:
-            gemm(self.logits, p["lm_head"], b_mn=True, alpha=mult, out=self.d_n)
-            gemm(self.logits, self.nf, a_mn=True, b_mn=True, alpha=mult, out=g["lm_head"])
-            if cfg.reward_head:
-                g["reward_head"].zero_()
-        x_last = self.acts[-1]["x2"] if self.acts else self.x0
-        K.norm_backward(self.d_n, x_last, p["norm"], None, self.rf, g["norm"], None, sc, out=dx, **rms)
-        for l in range(cfg.n_layer - 1, -1, -1):
-            a, pre, local = self.acts[l], f"layers.{l}.", cfg.is_local(l)
-            x_in = self.acts[l - 1]["x2"] if l > 0 else self.x0
+        dx, spare = self.d_a, self.d_b  # later stages: d_a was filled with the next stage's input gradient
+        if cfg.pp_last:
+            if self.objective == "reward_model":
+                self._reward_backward()
+            else:
+                gemm(self.logits, p["lm_head"], b_mn=True, alpha=mult, out=self.d_n)
+                if not self.lora:
+                    gemm(self.logits, self.nf, a_mn=True, b_mn=True, alpha=mult, out=g["lm_head"])
+                if "reward_head" in g:
+                    g["reward_head"].zero_()
+            x_last = self.acts[-1]["x2"] if self.acts else self.x0
+            K.norm_backward(self.d_n, x_last, p["norm"], None, self.rf, self._gw("norm"), None, sc, out=dx, **rms)
+        for i in range(len(self.layers) - 1, -1, -1):
+            a, l = self.acts[i], self.layers[i]
+            pre, local = f"layers.{l}.", cfg.is_local(l)
+            x_in = self.acts[i - 1]["x2"] if i > 0 else self.x0
             # MLP sandwich: x2 = x1 + post_norm(w_down(swiglu(w_gate_up(norm(x1)))))
-            K.norm_backward(dx, a["mb"], p[pre + "post_mlp_norm"], None, a["rp2"], g[pre + "post_mlp_norm"], None, sc, centered=True,
+            K.norm_backward(dx, a["mb"], p[pre + "post_mlp_norm"], None, a["rp2"], self._gw(pre + "post_mlp_norm"), None, sc, centered=True,
                             out=self.d_br, **rms)
-            gemm(self.d_br, p[pre + "w_down"], b_mn=True, out=self.d_h)
-            gemm(self.d_br, a["h"], a_mn=True, b_mn=True, workspace=ws, out=g[pre + "w_down"])
+            self._proj_backward(self.d_br, a["h"], pre + "w_down", self.d_h, a, "w_down")
             I.swiglu_backward(a["gu"], self.d_h, Fd, out=self.d_gu)
-            gemm(self.d_gu, p[pre + "w_gate_up"], b_mn=True, out=self.d_n)
-            gemm(self.d_gu, a["n2"], a_mn=True, b_mn=True, workspace=ws, out=g[pre + "w_gate_up"])
-            K.norm_backward(self.d_n, a["x1"], p[pre + "mlp_norm"], None, a["r2"], g[pre + "mlp_norm"], None, sc, centered=True, dresid=dx,
+            self._proj_backward(self.d_gu, a["n2"], pre + "w_gate_up", self.d_n, a, "w_gate_up")
+            K.norm_backward(self.d_n, a["x1"], p[pre + "mlp_norm"], None, a["r2"], self._gw(pre + "mlp_norm"), None, sc, centered=True, dresid=dx,
                             out=spare, **rms)
             dx, spare = spare, dx
             # attention sandwich: x1 = x + post_norm(wo(att * sigmoid(gate)))
-            K.norm_backward(dx, a["br"], p[pre + "post_attn_norm"], None, a["rp1"], g[pre + "post_attn_norm"], None, sc, centered=True,
+            K.norm_backward(dx, a["br"], p[pre + "post_attn_norm"], None, a["rp1"], self._gw(pre + "post_attn_norm"), None, sc, centered=True,
                             out=self.d_br, **rms)
-            gemm(self.d_br, p[pre + "wo"], b_mn=True, out=self.d_attg)
-            gemm(self.d_br, a["attg"], a_mn=True, b_mn=True, workspace=ws, out=g[pre + "wo"])
+            self._proj_backward(self.d_br, a["attg"], pre + "wo", self.d_attg, a, "wo")
             q, k, v, gate = self._views(a["qkvg"])
             dq, dk, dv, dgate = self._views(self.d_qkvg)
             K.sigmoid_gate_backward(self.d_attg, a["att"], gate, self.d_att, dgate)
@@ -418,15 +532,16 @@ class GlimmerEngine:
                 I.rope_inplace(a["qkvg"], T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=self.cos, sin=self.sin, convention="hf",
                                backward=True)
             K.qk_norm_backward(self.d_qkvg, a["qkvg"], a["qk_rstd"], Hq, Hkv, hd, q_scale=cfg.q_scale)
-            gemm(self.d_qkvg, p[pre + "wqkvg"], b_mn=True, out=self.d_n)
-            gemm(self.d_qkvg, a["n1"], a_mn=True, b_mn=True, workspace=ws, out=g[pre + "wqkvg"])
-            K.norm_backward(self.d_n, x_in, p[pre + "attn_norm"], None, a["r1"], g[pre + "attn_norm"], None, sc, centered=True, dresid=dx,
+            self._proj_backward(self.d_qkvg, a["n1"], pre + "wqkvg", self.d_n, a, "wqkvg")
+            K.norm_backward(self.d_n, x_in, p[pre + "attn_norm"], None, a["r1"], self._gw(pre + "attn_norm"), None, sc, centered=True, dresid=dx,
                             out=spare, **rms)
             dx, spare = spare, dx
-        # weightless norm of the embeddings, then the scatter into the table
-        K.norm_backward(dx, self.xe, self.ones, None, self.re, None, None, sc, out=spare, **rms)
-        g["tok_embeddings"].zero_()
-        K.embedding_backward(spare, self.tokens, g["tok_embeddings"], None, B=B, T=T)
+        self.d_input = dx  # gradient w.r.t. this stage's input (sent to the previous stage)
+        if cfg.pp_first and not self.lora:
+            # weightless norm of the embeddings, then the scatter into the table
+            K.norm_backward(dx, self.xe, self.ones, None, self.re, None, None, sc, out=spare, **rms)
+            g["tok_embeddings"].zero_()
+            K.embedding_backward(spare, self.tokens, g["tok_embeddings"], None, B=B, T=T)
 
     def logits_view(self) -> torch.Tensor:
         return self.logits.view(self.B, self.T, -1)[..., :self.cfg.vocab_size]

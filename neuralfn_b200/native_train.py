@@ -186,7 +186,16 @@ def _run_glimmer_post_training(c: NativeTrainConfig) -> dict:
                       final_lr_fraction=c.final_lr_fraction, schedule=c.lr_schedule)
     post = GlimmerPostTrainer(build_model_config(c), c.batch_size, c.seq_len, c.objective, opt, seed=c.seed, use_cuda_graph=c.use_cuda_graph)
     init_from = c.extra_paths.get("init_from", "")
-    if init_from:
+    if init_from and post.engine.lora:
+        # adapters start fresh; the checkpoint provides the frozen base weights
+        from .checkpoint import latest_step
+        from .checkpoint.named import read_named_tensors
+        step = latest_step(Path(init_from))
+        if step is None:
+            raise FileNotFoundError(f"no completed checkpoint (DONE_*) under {init_from}")
+        tensors, _meta, _sha = read_named_tensors(Path(init_from) / f"weights_{step:08d}.nfnw")
+        post.engine.load_base(tensors)
+    elif init_from:
         load_named_checkpoint(post.trainer, Path(init_from), weights_only=True)
     report = post.fit(c.dataset, c.max_steps, allow_train_as_val=c.allow_train_as_val, log_every=c.progress_every)
     report.update({"model_family": c.base_model, "backend": "neuralfn_b200-native", "status": "ok",

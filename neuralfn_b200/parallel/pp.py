@@ -257,6 +257,8 @@ def main(argv=None) -> int:
     import time
     ap = argparse.ArgumentParser(prog="neuralfn_b200.parallel.pp")
     ap.add_argument("--stages", type=int, default=0)
+    ap.add_argument("--base-model", default="llama", help="llama | muse-glimmer (engines with pipeline stage views)")
+    ap.add_argument("--head-dim", type=int, default=0, help="muse-glimmer: attention head width (0: d_model / n_head)")
     ap.add_argument("--micro-batches", type=int, default=0, help="micro-batches per step (default: 2 x stages)")
     ap.add_argument("--dataset", default="")
     ap.add_argument("--batch-size", type=int, default=4)
@@ -281,8 +283,14 @@ def main(argv=None) -> int:
         dist.init_process_group("nccl", device_id=dev)
     from ..models.llama import LlamaConfig
     from .dp import AdamWConfig
-    cfg = LlamaConfig(n_layer=a.n_layer, n_head=a.n_head, n_kv_head=a.n_kv_head or a.n_head, d_model=a.d_model,
-                      d_ff=a.d_ff or 4 * a.d_model, vocab_size=a.vocab_size, max_seq_len=a.seq_len)
+    if a.base_model.lower().replace("_", "-") in ("muse-glimmer", "glimmer"):
+        from ..models.glimmer import GlimmerConfig
+        cfg = GlimmerConfig(n_layer=a.n_layer, n_head=a.n_head, n_kv_head=a.n_kv_head or a.n_head, head_dim=a.head_dim or a.d_model // a.n_head,
+                            d_model=a.d_model, d_ff=a.d_ff or 3 * a.d_model, vocab_size=a.vocab_size, max_seq_len=a.seq_len,
+                            window=min(2048, a.seq_len))
+    else:
+        cfg = LlamaConfig(n_layer=a.n_layer, n_head=a.n_head, n_kv_head=a.n_kv_head or a.n_head, d_model=a.d_model,
+                          d_ff=a.d_ff or 4 * a.d_model, vocab_size=a.vocab_size, max_seq_len=a.seq_len)
     M = a.micro_batches or 2 * world
     tr = PipelineParallelTrainer(cfg, a.batch_size, a.seq_len, AdamWConfig(lr=a.learning_rate, warmup_steps=min(10, a.max_steps), total_steps=a.max_steps),
                                  micro_batches=M, seed=a.seed, device=dev)
@@ -309,7 +317,7 @@ def main(argv=None) -> int:
         tr.save(a.output_dir, a.max_steps)
     if rank == 0:
         sim = simulate_schedule(world, M)
-        print(json.dumps({"status": "ok", "parallelism": f"pp{world}", "micro_batches": M, "steps": a.max_steps, "first_loss": losses[0],
+        print(json.dumps({"status": "ok", "model_family": a.base_model, "parallelism": f"pp{world}", "micro_batches": M, "steps": a.max_steps, "first_loss": losses[0],
                           "final_loss": losses[-1], "tokens_per_second": a.max_steps * M * a.batch_size * a.seq_len / wall,
                           "schedule": "1f1b", "bubble_fraction": round(1.0 - sim["ideal_slots"] / sim["slots"], 4),
                           "peak_in_flight": sim["peak_in_flight"]}))

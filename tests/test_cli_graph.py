@@ -40,7 +40,7 @@ def test_pretrain_then_eval_then_migrate(tmp_path, capsys):
     assert rc == 0 and (tmp_path / "native" / "native-execution-manifest.json").exists() and mig["tensor_bytes"] > 0
     with pytest.raises(FileExistsError):
         _run(["migrate", "graph-to-native", "--graph", str(out.with_suffix(".json")), "--output-dir", str(tmp_path / "native")], capsys)
-    a = build_parser().parse_args(["migrate", "muse-glimmer-to-native", "--source", "x", "--output-dir", str(tmp_path / "g")])
+    a = build_parser().parse_args(["migrate", "muse-glimmer-lora-to-native", "--source", "x", "--output-dir", str(tmp_path / "g")])
     assert a.fn(a) == 2                                               # fails closed: not part of this build
 
 

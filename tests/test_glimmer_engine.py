@@ -180,6 +180,38 @@ def test_reward_model_objective_matches_autograd(kernel_lib):
 
 
 @pytest.mark.gpu
+def test_lora_adapters_match_autograd_on_the_merged_weights(kernel_lib):
+    from neuralfn_b200.models.glimmer import GlimmerEngine, glimmer_reference_loss
+    from neuralfn_b200.models.gpt2 import FlatLayout
+    from neuralfn_b200.ops import _lib
+    cfg = _cfg(lora_rank=16, lora_alpha=24.0)
+    layout = FlatLayout(cfg.param_specs())
+    g = torch.Generator(device="cuda").manual_seed(5)
+    params = (torch.randn(layout.n_total, device="cuda", generator=g) * 0.05).to(torch.bfloat16)     # A and B both non-zero
+    grads = torch.full_like(params, 7.0)                                                             # every slot must be overwritten
+    eng = GlimmerEngine(cfg, layout, params, grads, 4, 128)
+    assert set(eng.g) == {s.name for s in cfg.param_specs()} and "layers.0.wo" in eng.p and "layers.0.wo" not in eng.g
+    tok = torch.randint(0, cfg.vocab_size, (4, 128), device="cuda", generator=g)
+    tgt = torch.roll(tok, -1, 1)
+    eng.set_batch(tok, tgt)
+    loss = eng.forward()
+    eng.backward()
+    _lib.assert_status_ok("glimmer lora engine")
+    adapters = {k: v.float().clone().requires_grad_(True) for k, v in layout.views(params).items()}
+    merged = {k: v.float() for k, v in eng.base_layout.views(eng.base).items()}
+    for name in list(merged):
+        if name + ".lora_a" in adapters:
+            merged[name] = merged[name] + eng.lora_scale * adapters[name + ".lora_b"] @ adapters[name + ".lora_a"]
+    ref_loss, _, _ = glimmer_reference_loss(cfg, merged, tok, tgt)
+    ref_loss.backward()
+    assert abs(loss.item() - ref_loss.item()) < 2e-2 * max(1.0, ref_loss.item())
+    assert not _compare(layout, grads, adapters, tol=8e-2)
+    # folding the adapters in gives the same model
+    folded = eng.merged_state()
+    assert (folded["layers.1.w_down"] - merged["layers.1.w_down"].detach().cpu()).abs().max() < 1e-2
+
+
+@pytest.mark.gpu
 def test_dense_trainer_drives_the_glimmer_engine(kernel_lib):
     from neuralfn_b200.parallel.dp import AdamWConfig
     from neuralfn_b200.trainers.dense_gpt import DenseGPTTrainer
@@ -191,3 +223,11 @@ def test_dense_trainer_drives_the_glimmer_engine(kernel_lib):
     losses = [tr.train_step(tok, tgt) for _ in range(14)]
     tr.check_status()
     assert losses[-1] < losses[0] - 0.5, losses
+    # LoRA on the same trainer: only adapters train (B starts at zero), the frozen base comes from the full run
+    lcfg = _cfg(vocab_size=512, lora_rank=16)
+    lt = DenseGPTTrainer(lcfg, 4, 128, AdamWConfig(lr=1e-2, warmup_steps=2, total_steps=50, weight_decay=0.0), seed=3)
+    lt.engine.load_base({k: v for k, v in tr.layout.views(tr.bufs.params).items()})
+    ll = [lt.train_step(tok, tgt) for _ in range(12)]
+    lt.check_status()
+    assert abs(ll[0] - losses[-1]) < 0.35 and ll[-1] < ll[0] - 0.05, (ll, losses[-1])
+    assert lt.layout.n_total < tr.layout.n_total // 4

@@ -1,4 +1,4 @@
-"""Pipeline-parallel Llama training on two GPUs matches the single-GPU trainer step for step."""
+"""Pipeline-parallel training (Llama and Glimmer engines) on two GPUs matches the single-GPU trainer step for step."""
 import os
 import socket
 import zlib
@@ -11,7 +11,11 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 
 
-def _cfg():
+def _cfg(family="llama"):
+    if family == "glimmer":
+        from neuralfn_b200.models.glimmer import GlimmerConfig
+        return GlimmerConfig(n_layer=4, n_head=4, n_kv_head=2, head_dim=64, d_model=256, d_ff=512, vocab_size=512, max_seq_len=128, window=48,
+                             global_every=2, output_multiplier=0.5)
     from neuralfn_b200.models.llama import LlamaConfig
     return LlamaConfig(n_layer=4, n_head=4, n_kv_head=2, d_model=256, d_ff=512, vocab_size=512, max_seq_len=128)
 
@@ -22,7 +26,7 @@ def _fill_by_name(tr):
     for s in tr.layout.order:
         g = torch.Generator().manual_seed(zlib.crc32(s.name.encode()))
         v = tr.layout.view(flat, s.name)
-        v.copy_(torch.ones(s.shape) if s.init == "ones" else torch.randn(s.shape, generator=g) * 0.02)
+        v.copy_(torch.ones(s.shape) if s.init == "ones" else (torch.zeros(s.shape) if s.init == "zeros" else torch.randn(s.shape, generator=g) * 0.02))
     tr.opt.master.copy_(flat)
     tr.bufs.params.copy_(flat.bfloat16())
 
@@ -36,14 +40,14 @@ def _batches(steps, micro):
 MICRO = 3   # more micro-batches than stages: warm-up, steady 1F1B pairs and a cool-down all occur
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, family):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world)
     try:
         from neuralfn_b200.parallel.dp import AdamWConfig
         from neuralfn_b200.parallel.pp import PipelineParallelTrainer
-        tr = PipelineParallelTrainer(_cfg(), 2, 128, AdamWConfig(lr=2e-3, warmup_steps=1, total_steps=20, weight_decay=0.0), micro_batches=MICRO)
+        tr = PipelineParallelTrainer(_cfg(family), 2, 128, AdamWConfig(lr=2e-3, warmup_steps=1, total_steps=20, weight_decay=0.0), micro_batches=MICRO)
         _fill_by_name(tr.inner)
         tok, tgt = _batches(4, MICRO)
         losses = [tr.train_step(tok[i], tgt[i]) for i in range(4)]
@@ -54,7 +58,8 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_two_stage_pipeline_matches_single_gpu(tmp_path):
+@pytest.mark.parametrize("family", ["llama", "glimmer"])
+def test_two_stage_pipeline_matches_single_gpu(tmp_path, family):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     with socket.socket() as s:
@@ -62,7 +67,7 @@ def test_two_stage_pipeline_matches_single_gpu(tmp_path):
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, family)) for r in range(2)]
     for p in procs:
         p.start()
     res = {r: (l, n) for r, l, n in (q.get(timeout=240) for _ in procs)}
@@ -70,11 +75,12 @@ def test_two_stage_pipeline_matches_single_gpu(tmp_path):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert res[0][0] == res[1][0]
-    assert "tok_embeddings" in res[0][1] and "lm_head" in res[1][1] and "layers.2.wqkv" in res[1][1] and "layers.1.wo" in res[0][1]
+    qkv = "layers.2.wqkv" if family == "llama" else "layers.2.wqkvg"
+    assert "tok_embeddings" in res[0][1] and "lm_head" in res[1][1] and qkv in res[1][1] and "layers.1.wo" in res[0][1]
     # single-GPU reference with the same weights, batches and accumulation
     from neuralfn_b200.parallel.dp import AdamWConfig
     from neuralfn_b200.trainers.dense_gpt import DenseGPTTrainer
-    ref = DenseGPTTrainer(_cfg(), 2, 128, AdamWConfig(lr=2e-3, warmup_steps=1, total_steps=20, weight_decay=0.0), grad_accum_steps=MICRO,
+    ref = DenseGPTTrainer(_cfg(family), 2, 128, AdamWConfig(lr=2e-3, warmup_steps=1, total_steps=20, weight_decay=0.0), grad_accum_steps=MICRO,
                           use_cuda_graph=False)
     _fill_by_name(ref)
     tok, tgt = _batches(4, MICRO)
