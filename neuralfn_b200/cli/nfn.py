@@ -24,6 +24,8 @@ def _add_train_flags(p: argparse.ArgumentParser) -> None:
     p.add_argument("--objective", choices=["ar", "sft", "dpo", "reward_model"], default="ar",
                    help="native engines: ar (all families); sft / dpo / reward_model from record shards (--base-model muse-glimmer)")
     p.add_argument("--head-dim", type=int, default=0, help="muse-glimmer: attention head width (0: d_model / n_head)")
+    p.add_argument("--activation-checkpoint-interval", type=int, default=0,
+                   help="muse-glimmer native engine: resident layers per recomputed segment (0: keep every activation)")
     p.add_argument("--init-from", default="", help="--objective sft|dpo: named checkpoint directory whose weights start the run")
     p.add_argument("--template-name", default="gpt2")
     p.add_argument("--dataset", default="", help="dataset alias, directory or shard file (empty: synthetic uniform tokens)")
@@ -83,7 +85,7 @@ def _train_config(a):
         weight_decay=a.weight_decay, beta1=a.beta1, beta2=a.beta2, eps=a.eps, max_grad_norm=a.max_grad_norm, max_steps=a.max_steps,
         eval_every=a.eval_every, eval_batches=a.eval_batches, train_loss_every=a.train_loss_every, progress_every=a.progress_every,
         checkpoint_every=a.checkpoint_every, seed=a.seed, resume=a.resume, use_cuda_graph=not a.no_cuda_graph,
-        objective=a.objective, head_dim=a.head_dim, extra_paths={"init_from": a.init_from} if a.init_from else {},
+        objective=a.objective, head_dim=a.head_dim, activation_checkpoint_interval=a.activation_checkpoint_interval, extra_paths={"init_from": a.init_from} if a.init_from else {},
         extra=_native_adapter_options(a))
 
 

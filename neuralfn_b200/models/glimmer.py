@@ -32,8 +32,12 @@ frozen bf16 buffer owned by the engine (``load_base`` / ``merged_state``). Every
 skinny GEMMs whose second one adds ``alpha / r * t B^T`` in its epilogue; the backward pass skips every base weight gradient
 (the big TN GEMMs, the norm-weight reductions and the embedding scatter), which is where LoRA's saving comes from. Reference:
 the adapter options of ``muse_glimmer_native_train.cpp:187-203`` and ``inspect_native_muse_glimmer_lora_checkpoint``
-(``neuralfn/native_muse_glimmer_checkpoint.py:580``). NF4 / K-quant base weights under the adapters, the PPO objective and
-activation checkpointing are not in this engine (they run in the tensor runtime).
+(``neuralfn/native_muse_glimmer_checkpoint.py:580``). NF4 / K-quant base weights under the adapters and the PPO objective are
+not in this engine (they run in the tensor runtime).
+
+Activation checkpointing (``ckpt_every = k``): activation buffers exist for k layers only and are reused by every k-layer
+segment; the input of each segment is kept, and the backward pass re-runs a segment's forward before differentiating it
+(the reference's ``--activation-checkpoint-interval``, default 4: ``muse_glimmer_native_train.cpp:115,204,1045-1049``).
 """
 from __future__ import annotations
 
@@ -74,6 +78,7 @@ class GlimmerConfig:
     lora_alpha: float = 32.0
     lora_targets: tuple = ("wqkvg", "wo", "w_gate_up", "w_down")
     base_seed: int = 1337                   # LoRA: seed of the frozen base weights until load_base() replaces them
+    ckpt_every: int = 0                     # > 0: keep activations of this many layers only; recompute segments in backward
     # pipeline-parallel stage view: this engine owns layers [pp_layer_begin, pp_layer_end); the first stage also owns
     # the embedding, the last one the final norm and the heads (0 / 0 = whole model)
     pp_layer_begin: int = 0
@@ -272,7 +277,10 @@ class GlimmerEngine:
         self.acts = [dict(n1=e(N, C), r1=e(N, dtype=f32), qkvg=e(N, Q + A), qk_rstd=e(N, cfg.n_head + cfg.n_kv_head, dtype=f32),
                           att=e(N, A), attg=e(N, A), lse=e(batch, cfg.n_head, seq, dtype=f32), br=e(N, C), rp1=e(N, dtype=f32), x1=e(N, C),
                           n2=e(N, C), r2=e(N, dtype=f32), gu=e(N, 2 * Fd), h=e(N, Fd), mb=e(N, C), rp2=e(N, dtype=f32), x2=e(N, C))
-                     for _ in cfg.layer_range]
+                     for _ in range(self._resident_layers())]
+        n_seg = -(-len(cfg.layer_range) // len(self.acts)) if self.acts else 0
+        # input of every segment of layers (segment 0 reads x0 itself); one segment = everything resident = no recompute
+        self.bound = [self.x0] + [e(N, C) for _ in range(n_seg - 1)]
         if self.lora:
             for a in self.acts:
                 a.update({"t_" + t: e(N, cfg.lora_rank) for t in cfg.lora_targets})
@@ -322,6 +330,10 @@ class GlimmerEngine:
     def set_reference_logps(self, logps: torch.Tensor) -> None:
         """[B] sequence log-probabilities of the frozen reference model (first half chosen, second half rejected)."""
         self.ref_logps.copy_(logps.reshape(-1).to(self.ref_logps.dtype), non_blocking=True)
+
+    def _resident_layers(self) -> int:
+        n = len(self.cfg.layer_range)
+        return n if self.cfg.ckpt_every <= 0 else min(n, self.cfg.ckpt_every)
 
     # ----------------------------------------------------------------------------- LoRA --
     def load_base(self, tensors: dict[str, torch.Tensor]) -> None:
@@ -377,6 +389,32 @@ class GlimmerEngine:
         return t[:, :q_end], t[:, q_end:k_end], t[:, k_end:cfg.qkv_dim], t[:, cfg.qkv_dim:]
 
     # -------------------------------------------------------------------------- forward --
+    def _layer_forward(self, l: int, a: dict, x: torch.Tensor) -> torch.Tensor:
+        K, I, cfg, p = self.K, self.I, self.cfg, self.p
+        B, T = self.B, self.T
+        Hq, Hkv, hd, Fd = cfg.n_head, cfg.n_kv_head, cfg.head_dim, cfg.d_ff
+        rms = dict(mode=K.NORM_RMS, mean=self.mean_scratch)
+        pre, local = f"layers.{l}.", cfg.is_local(l)
+        K.norm_forward(x, p[pre + "attn_norm"], None, eps=cfg.norm_eps, centered=True, out=a["n1"], rstd=a["r1"], **rms)
+        self._proj(a["n1"], pre + "wqkvg", a["qkvg"], a, "wqkvg")
+        K.qk_norm_forward(a["qkvg"], Hq, Hkv, hd, eps=cfg.qk_norm_eps, q_scale=cfg.q_scale, rstd=a["qk_rstd"])
+        if local:
+            I.rope_inplace(a["qkvg"], T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=self.cos, sin=self.sin, convention="hf")
+        q, k, v, gate = self._views(a["qkvg"])
+        K.attention_forward(q, k, v, B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, causal=True,
+                            window=cfg.window if local else 0, out=a["att"], lse=a["lse"])
+        K.sigmoid_gate_forward(a["att"], gate, a["attg"])
+        self._proj(a["attg"], pre + "wo", a["br"], a, "wo")
+        K.norm_forward(a["br"], p[pre + "post_attn_norm"], None, eps=cfg.post_norm_eps, centered=True, out=self.nb, rstd=a["rp1"], **rms)
+        torch.add(x, self.nb, out=a["x1"])
+        K.norm_forward(a["x1"], p[pre + "mlp_norm"], None, eps=cfg.norm_eps, centered=True, out=a["n2"], rstd=a["r2"], **rms)
+        self._proj(a["n2"], pre + "w_gate_up", a["gu"], a, "w_gate_up")
+        I.swiglu_forward(a["gu"], Fd, out=a["h"])
+        self._proj(a["h"], pre + "w_down", a["mb"], a, "w_down")
+        K.norm_forward(a["mb"], p[pre + "post_mlp_norm"], None, eps=cfg.post_norm_eps, centered=True, out=self.nb, rstd=a["rp2"], **rms)
+        torch.add(a["x1"], self.nb, out=a["x2"])
+        return a["x2"]
+
     def forward(self, *, compute_grad_logits: bool = True, grad_scale: float | None = None) -> torch.Tensor:
         K, I, gemm, cfg, p = self.K, self.I, self.gemm, self.cfg, self.p
         B, T, N = self.B, self.T, self.B * self.T
@@ -386,27 +424,12 @@ class GlimmerEngine:
             K.embedding_forward(self.tokens, p["tok_embeddings"], None, T=T, out=self.xe)
             K.norm_forward(self.xe, self.ones, None, eps=cfg.norm_eps, out=self.x0, rstd=self.re, **rms)
         x = self.x0  # later stages: filled by the pipeline runtime with the previous stage's output
-        for l, a in zip(self.layers, self.acts):
-            pre, local = f"layers.{l}.", cfg.is_local(l)
-            K.norm_forward(x, p[pre + "attn_norm"], None, eps=cfg.norm_eps, centered=True, out=a["n1"], rstd=a["r1"], **rms)
-            self._proj(a["n1"], pre + "wqkvg", a["qkvg"], a, "wqkvg")
-            K.qk_norm_forward(a["qkvg"], Hq, Hkv, hd, eps=cfg.qk_norm_eps, q_scale=cfg.q_scale, rstd=a["qk_rstd"])
-            if local:
-                I.rope_inplace(a["qkvg"], T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=self.cos, sin=self.sin, convention="hf")
-            q, k, v, gate = self._views(a["qkvg"])
-            K.attention_forward(q, k, v, B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, causal=True,
-                                window=cfg.window if local else 0, out=a["att"], lse=a["lse"])
-            K.sigmoid_gate_forward(a["att"], gate, a["attg"])
-            self._proj(a["attg"], pre + "wo", a["br"], a, "wo")
-            K.norm_forward(a["br"], p[pre + "post_attn_norm"], None, eps=cfg.post_norm_eps, centered=True, out=self.nb, rstd=a["rp1"], **rms)
-            torch.add(x, self.nb, out=a["x1"])
-            K.norm_forward(a["x1"], p[pre + "mlp_norm"], None, eps=cfg.norm_eps, centered=True, out=a["n2"], rstd=a["r2"], **rms)
-            self._proj(a["n2"], pre + "w_gate_up", a["gu"], a, "w_gate_up")
-            I.swiglu_forward(a["gu"], Fd, out=a["h"])
-            self._proj(a["h"], pre + "w_down", a["mb"], a, "w_down")
-            K.norm_forward(a["mb"], p[pre + "post_mlp_norm"], None, eps=cfg.post_norm_eps, centered=True, out=self.nb, rstd=a["rp2"], **rms)
-            torch.add(a["x1"], self.nb, out=a["x2"])
-            x = a["x2"]
+        k = len(self.acts)
+        for i, l in enumerate(self.layers):
+            if i and i % k == 0:
+                self.bound[i // k].copy_(x)      # the slot that holds x is reused by the layers of this segment
+                x = self.bound[i // k]
+            x = self._layer_forward(l, self.acts[i % k], x)
         if not cfg.pp_last:
             return x  # handed to the next stage
         K.norm_forward(x, p["norm"], None, eps=cfg.norm_eps, out=self.nf, rstd=self.rf, **rms)
@@ -485,6 +508,44 @@ class GlimmerEngine:
             self.g["lm_head"].zero_()
 
     # ------------------------------------------------------------------------- backward --
+    def _layer_backward(self, l: int, a: dict, x_in: torch.Tensor, dx: torch.Tensor, spare: torch.Tensor):
+        """Gradients of one layer. ``dx`` is d(layer output); returns (d(layer input), the other scratch buffer)."""
+        K, I, cfg, p = self.K, self.I, self.cfg, self.p
+        B, T = self.B, self.T
+        Hq, Hkv, hd, Fd = cfg.n_head, cfg.n_kv_head, cfg.head_dim, cfg.d_ff
+        sc, rms = self.scratch, dict(mode=K.NORM_RMS)
+        pre, local = f"layers.{l}.", cfg.is_local(l)
+        # MLP sandwich: x2 = x1 + post_norm(w_down(swiglu(w_gate_up(norm(x1)))))
+        K.norm_backward(dx, a["mb"], p[pre + "post_mlp_norm"], None, a["rp2"], self._gw(pre + "post_mlp_norm"), None, sc, centered=True,
+                        out=self.d_br, **rms)
+        self._proj_backward(self.d_br, a["h"], pre + "w_down", self.d_h, a, "w_down")
+        I.swiglu_backward(a["gu"], self.d_h, Fd, out=self.d_gu)
+        self._proj_backward(self.d_gu, a["n2"], pre + "w_gate_up", self.d_n, a, "w_gate_up")
+        K.norm_backward(self.d_n, a["x1"], p[pre + "mlp_norm"], None, a["r2"], self._gw(pre + "mlp_norm"), None, sc, centered=True, dresid=dx,
+                        out=spare, **rms)
+        dx, spare = spare, dx
+        # attention sandwich: x1 = x + post_norm(wo(att * sigmoid(gate)))
+        K.norm_backward(dx, a["br"], p[pre + "post_attn_norm"], None, a["rp1"], self._gw(pre + "post_attn_norm"), None, sc, centered=True,
+                        out=self.d_br, **rms)
+        self._proj_backward(self.d_br, a["attg"], pre + "wo", self.d_attg, a, "wo")
+        q, k, v, gate = self._views(a["qkvg"])
+        dq, dk, dv, dgate = self._views(self.d_qkvg)
+        K.sigmoid_gate_backward(self.d_attg, a["att"], gate, self.d_att, dgate)
+        K.attention_backward(self.d_att, q, k, v, a["att"], a["lse"], B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, causal=True,
+                             window=cfg.window if local else 0, dq=dq, dk=dk, dv=dv, delta=self.delta)
+        if local:
+            I.rope_inplace(self.d_qkvg, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=self.cos, sin=self.sin, convention="hf",
+                           backward=True)
+            # the norm backward needs the normalised, un-rotated q / k: undo the rotation of the saved copy
+            I.rope_inplace(a["qkvg"], T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=self.cos, sin=self.sin, convention="hf",
+                           backward=True)
+        K.qk_norm_backward(self.d_qkvg, a["qkvg"], a["qk_rstd"], Hq, Hkv, hd, q_scale=cfg.q_scale)
+        self._proj_backward(self.d_qkvg, a["n1"], pre + "wqkvg", self.d_n, a, "wqkvg")
+        K.norm_backward(self.d_n, x_in, p[pre + "attn_norm"], None, a["r1"], self._gw(pre + "attn_norm"), None, sc, centered=True, dresid=dx,
+                        out=spare, **rms)
+        dx, spare = spare, dx
+        return dx, spare
+
     def backward(self) -> None:
         K, I, gemm, cfg, p, g = self.K, self.I, self.gemm, self.cfg, self.p, self.g
         B, T = self.B, self.T
@@ -501,41 +562,19 @@ class GlimmerEngine:
                     gemm(self.logits, self.nf, a_mn=True, b_mn=True, alpha=mult, out=g["lm_head"])
                 if "reward_head" in g:
                     g["reward_head"].zero_()
-            x_last = self.acts[-1]["x2"] if self.acts else self.x0
+            x_last = self.acts[(len(self.layers) - 1) % len(self.acts)]["x2"] if self.acts else self.x0
             K.norm_backward(self.d_n, x_last, p["norm"], None, self.rf, self._gw("norm"), None, sc, out=dx, **rms)
-        for i in range(len(self.layers) - 1, -1, -1):
-            a, l = self.acts[i], self.layers[i]
-            pre, local = f"layers.{l}.", cfg.is_local(l)
-            x_in = self.acts[i - 1]["x2"] if i > 0 else self.x0
-            # MLP sandwich: x2 = x1 + post_norm(w_down(swiglu(w_gate_up(norm(x1)))))
-            K.norm_backward(dx, a["mb"], p[pre + "post_mlp_norm"], None, a["rp2"], self._gw(pre + "post_mlp_norm"), None, sc, centered=True,
-                            out=self.d_br, **rms)
-            self._proj_backward(self.d_br, a["h"], pre + "w_down", self.d_h, a, "w_down")
-            I.swiglu_backward(a["gu"], self.d_h, Fd, out=self.d_gu)
-            self._proj_backward(self.d_gu, a["n2"], pre + "w_gate_up", self.d_n, a, "w_gate_up")
-            K.norm_backward(self.d_n, a["x1"], p[pre + "mlp_norm"], None, a["r2"], self._gw(pre + "mlp_norm"), None, sc, centered=True, dresid=dx,
-                            out=spare, **rms)
-            dx, spare = spare, dx
-            # attention sandwich: x1 = x + post_norm(wo(att * sigmoid(gate)))
-            K.norm_backward(dx, a["br"], p[pre + "post_attn_norm"], None, a["rp1"], self._gw(pre + "post_attn_norm"), None, sc, centered=True,
-                            out=self.d_br, **rms)
-            self._proj_backward(self.d_br, a["attg"], pre + "wo", self.d_attg, a, "wo")
-            q, k, v, gate = self._views(a["qkvg"])
-            dq, dk, dv, dgate = self._views(self.d_qkvg)
-            K.sigmoid_gate_backward(self.d_attg, a["att"], gate, self.d_att, dgate)
-            K.attention_backward(self.d_att, q, k, v, a["att"], a["lse"], B=B, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, causal=True,
-                                 window=cfg.window if local else 0, dq=dq, dk=dk, dv=dv, delta=self.delta)
-            if local:
-                I.rope_inplace(self.d_qkvg, T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=self.cos, sin=self.sin, convention="hf",
-                               backward=True)
-                # the norm backward needs the normalised, un-rotated q / k: undo the rotation of the saved copy
-                I.rope_inplace(a["qkvg"], T=T, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, cos=self.cos, sin=self.sin, convention="hf",
-                               backward=True)
-            K.qk_norm_backward(self.d_qkvg, a["qkvg"], a["qk_rstd"], Hq, Hkv, hd, q_scale=cfg.q_scale)
-            self._proj_backward(self.d_qkvg, a["n1"], pre + "wqkvg", self.d_n, a, "wqkvg")
-            K.norm_backward(self.d_n, x_in, p[pre + "attn_norm"], None, a["r1"], self._gw(pre + "attn_norm"), None, sc, centered=True, dresid=dx,
-                            out=spare, **rms)
-            dx, spare = spare, dx
+        k, L = len(self.acts), len(self.layers)
+        for seg in range((L - 1) // k if L else -1, -1, -1):
+            lo, hi = seg * k, min(L, seg * k + k)
+            if hi != L:
+                # the slots hold a later segment by now: run this segment's forward again from its saved input
+                x = self.bound[seg]
+                for i in range(lo, hi):
+                    x = self._layer_forward(self.layers[i], self.acts[i % k], x)
+            for i in range(hi - 1, lo - 1, -1):
+                x_in = self.acts[(i - 1) % k]["x2"] if i > lo else self.bound[seg]
+                dx, spare = self._layer_backward(self.layers[i], self.acts[i % k], x_in, dx, spare)
         self.d_input = dx  # gradient w.r.t. this stage's input (sent to the previous stage)
         if cfg.pp_first and not self.lora:
             # weightless norm of the embeddings, then the scatter into the table

@@ -35,6 +35,7 @@ class NativeTrainConfig:
     base_model: str = "gpt"                 # gpt | gpt2 | gpt3 | nanogpt | llama | muse-glimmer
     objective: str = "ar"                   # muse-glimmer also trains "sft", "dpo" and "reward_model" from record shards
     head_dim: int = 0                       # muse-glimmer: 0 = d_model / n_head
+    activation_checkpoint_interval: int = 0 # muse-glimmer: keep this many layers' activations, recompute the rest (0 = keep all)
     template_name: str = "gpt2"
     dataset: str = ""                       # alias under the datasets dir, directory, or file; "" = synthetic
     output_dir: str = ""
@@ -91,7 +92,8 @@ def build_model_config(c: NativeTrainConfig):
         from .models.glimmer import GlimmerConfig
         d_ff = c.d_ff or 3 * c.d_model
         return GlimmerConfig(n_layer=c.n_layer, n_head=c.n_head, n_kv_head=c.n_kv_head or c.n_head, head_dim=c.head_dim or c.d_model // c.n_head,
-                             d_model=c.d_model, d_ff=d_ff, vocab_size=c.vocab_size, max_seq_len=c.seq_len, **c.extra)
+                             d_model=c.d_model, d_ff=d_ff, vocab_size=c.vocab_size, max_seq_len=c.seq_len,
+                             ckpt_every=c.activation_checkpoint_interval, **c.extra)
     raise ValueError(f"no native engine for model family {c.base_model!r} (available: gpt, gpt2, gpt3, nanogpt, llama, muse-glimmer)")
 
 

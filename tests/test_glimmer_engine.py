@@ -106,6 +106,28 @@ def test_next_token_objective_matches_autograd(kernel_lib, kw):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("every", [1, 2, 3])
+def test_activation_checkpointing_reproduces_the_plain_engine(kernel_lib, every):
+    """Five layers in segments of 1, 2 or 3 resident layers: recomputed segments give the gradients of the engine that keeps everything."""
+    from neuralfn_b200.models.glimmer import GlimmerEngine
+    from neuralfn_b200.ops import _lib
+    cfg, layout, params, grads, eng, tok, tgt = _setup(n_layer=5, global_every=2)
+    loss = eng.forward().clone()
+    eng.backward()
+    from dataclasses import replace
+    grads2 = torch.full_like(grads, 3.0)
+    eng2 = GlimmerEngine(replace(cfg, ckpt_every=every), layout, params, grads2, 4, 128)
+    assert len(eng2.acts) == every and len(eng2.bound) == -(-5 // every)
+    eng2.set_batch(tok, tgt)
+    loss2 = eng2.forward().clone()
+    eng2.backward()
+    _lib.assert_status_ok("glimmer engine with activation checkpointing")
+    assert abs(loss.item() - loss2.item()) < 1e-6
+    diff = (grads.float() - grads2.float()).abs().max().item()
+    assert diff <= 1e-3 * grads.float().abs().max().item(), diff
+
+
+@pytest.mark.gpu
 def test_sft_objective_counts_only_masked_rows(kernel_lib):
     from neuralfn_b200.models.glimmer import glimmer_reference_loss
     cfg, layout, params, grads, eng, tok, tgt = _setup()
