@@ -94,6 +94,8 @@ def test_next_token_objective_matches_autograd(kernel_lib, kw):
     from neuralfn_b200.models.glimmer import glimmer_reference_loss
     from neuralfn_b200.ops import _lib
     cfg, layout, params, grads, eng, tok, tgt = _setup(**kw)
+    eng.forward(compute_grad_logits=False)                 # keeps the logits (the training call overwrites them with their gradient)
+    logits = eng.logits_view().float().clone()
     loss = eng.forward()
     eng.backward()
     _lib.assert_status_ok("glimmer engine")
@@ -101,7 +103,7 @@ def test_next_token_objective_matches_autograd(kernel_lib, kw):
     ref_loss, ref_logits, _ = glimmer_reference_loss(cfg, ref_p, tok, tgt)
     ref_loss.backward()
     assert abs(loss.item() - ref_loss.item()) < 2e-2 * max(1.0, ref_loss.item())
-    assert (eng.logits_view().float() - ref_logits).abs().max() < 0.15
+    assert (logits - ref_logits).abs().max() < 0.15
     assert not _compare(layout, grads, ref_p)
 
 
