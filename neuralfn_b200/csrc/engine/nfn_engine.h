@@ -98,6 +98,16 @@ int nfn_engine_truncate(nfn_engine* e, int slot, int n);
 // Copies the first n cached tokens of src_slot into dst_slot (device-to-device; the two slots
 // are independent afterwards).
 int nfn_engine_fork(nfn_engine* e, int src_slot, int dst_slot, int n);
+
+// ---- hidden-state taps (context of a block-diffusion draft model) ------------------------------
+// Keeps the residual stream after each listed layer (0-based) for every cached position of every slot:
+// [max_batch][max_seq][d_model] bf16 per tap. Prefill, decode steps and verification blocks all write
+// their rows; rows of a block that is not committed are overwritten before they can be read. Must be
+// called after finalize and before the first decode step.
+int nfn_engine_enable_taps(nfn_engine* e, const int32_t* layers, int n);
+// Copies positions [pos0, pos0 + n) of `slot` to dst as bf16 [n][taps * d_model] (taps side by side in
+// the order they were enabled). dst is device memory when dst_on_device != 0, else host memory.
+int nfn_engine_read_taps(nfn_engine* e, int slot, int pos0, int n, void* dst, int dst_on_device);
 // Kernel launches issued so far by this engine (graph replays count their captured launches).
 long long nfn_engine_launches(const nfn_engine* e);
 

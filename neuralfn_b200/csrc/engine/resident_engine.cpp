@@ -116,6 +116,9 @@ struct nfn_engine {
   void* argmax_ws = nullptr;
   std::vector<int> h_vrows;               // live rows per slot of the last verification
   std::vector<int> logit_src;             // 0: e.logits, 1: logits_v
+  // hidden-state taps (inputs of a block-diffusion draft): residual stream after the listed layers, by slot and position
+  std::vector<int> tap_layers;
+  std::vector<void*> taps;                // per tap [max_batch][max_seq][d_model] bf16
 
   int alloc(void** p, long long nbytes) {
     CU(cudaMalloc(p, (size_t)nbytes));
@@ -284,6 +287,20 @@ int forward_layers(nfn_engine& e, int rows, bool decode, int slot, const int* d_
         K(nfn_rmsnorm_residual(e.branch, e.W(yname(l, "post_ffn_norm")), e.x, e.x, rows, C, post_eps, c.centered_norms, e.stream));
       } else if (gemm(e, e.ffa, F, e.W(yname(l, "w_down")), e.x, C, rows, C, F, 0, nullptr, e.x, C)) {
         return -1;
+      }
+    }
+    for (size_t t = 0; t < e.tap_layers.size(); ++t) {
+      if (e.tap_layers[t] != l) continue;
+      const long long stride = (long long)c.max_seq * C;
+      if (!decode && block_rows == 0) {
+        // a prompt: rows are positions 0 .. rows - 1 of `slot`
+        CU(cudaMemcpyAsync(static_cast<char*>(e.taps[t]) + (size_t)slot * stride * 2, e.x, (size_t)rows * C * 2, cudaMemcpyDeviceToDevice, e.stream));
+      } else if (decode) {
+        // lengths count the new token: it sits at lengths[slot] - 1. Rows of idle slots have length 0 and are skipped.
+        K(nfn_rows_to_slots(e.x, C, rows, C, e.taps[t], stride, c.max_seq, d_lengths, 1, -1, nullptr, e.stream));
+      } else {
+        // a verification block starts at lengths[slot]; rows past the committed length are overwritten before they are read
+        K(nfn_rows_to_slots(e.x, C, rows, C, e.taps[t], stride, c.max_seq, d_lengths, block_rows, 0, d_block_live, e.stream));
       }
     }
   }
@@ -802,8 +819,49 @@ int nfn_engine_fork(nfn_engine* e, int src_slot, int dst_slot, int n) {
     CU(cudaMemcpy2DAsync(kc + dst_slot * slot_bytes, head_bytes, kc + src_slot * slot_bytes, head_bytes, live, c.n_kv_head, cudaMemcpyDeviceToDevice, e->stream));
     CU(cudaMemcpy2DAsync(vc + dst_slot * slot_bytes, head_bytes, vc + src_slot * slot_bytes, head_bytes, live, c.n_kv_head, cudaMemcpyDeviceToDevice, e->stream));
   }
+  for (size_t t = 0; t < e->taps.size() && n > 0; ++t) {
+    const size_t stride = (size_t)c.max_seq * c.d_model * 2;
+    CU(cudaMemcpyAsync(static_cast<char*>(e->taps[t]) + dst_slot * stride, static_cast<char*>(e->taps[t]) + src_slot * stride,
+                       (size_t)n * c.d_model * 2, cudaMemcpyDeviceToDevice, e->stream));
+  }
   CU(cudaStreamSynchronize(e->stream));
   e->len[dst_slot] = n;
+  return 0;
+}
+
+int nfn_engine_enable_taps(nfn_engine* e, const int32_t* layers, int n) {
+  if (!e || !e->finalized || !layers) return efail("engine_enable_taps: finalize the engine first");
+  if (!e->taps.empty()) return efail("engine_enable_taps: taps are already enabled");
+  if (e->graph || e->decode_calls > 0) return efail("engine_enable_taps: enable taps before the first decode step (the step is captured once)");
+  const nfn_engine_config& c = e->c;
+  if (n < 1 || n > 8) return efail("engine_enable_taps: between 1 and 8 tap layers");
+  for (int i = 0; i < n; ++i)
+    if (layers[i] < 0 || layers[i] >= c.n_layer) return efail("engine_enable_taps: tap layer outside the model");
+  CU(cudaSetDevice(e->device));
+  for (int i = 0; i < n; ++i) {
+    void* p = nullptr;
+    const long long bytes = (long long)c.max_batch * c.max_seq * c.d_model * 2;
+    if (e->alloc(&p, bytes)) return -1;
+    CU(cudaMemset(p, 0, (size_t)bytes));
+    e->taps.push_back(p);
+    e->tap_layers.push_back(layers[i]);
+  }
+  return 0;
+}
+
+int nfn_engine_read_taps(nfn_engine* e, int slot, int pos0, int n, void* dst, int dst_on_device) {
+  if (!e || !dst || e->taps.empty()) return efail("engine_read_taps: taps are not enabled");
+  const nfn_engine_config& c = e->c;
+  if (slot < 0 || slot >= c.max_batch || pos0 < 0 || n < 0 || pos0 + n > e->len[slot]) return efail("engine_read_taps: positions outside the slot's cached tokens");
+  if (n == 0) return 0;
+  CU(cudaSetDevice(e->device));
+  const size_t row = (size_t)c.d_model * 2, T = e->taps.size();
+  for (size_t t = 0; t < T; ++t) {
+    const char* src = static_cast<const char*>(e->taps[t]) + ((size_t)slot * c.max_seq + pos0) * row;
+    CU(cudaMemcpy2DAsync(static_cast<char*>(dst) + t * row, T * row, src, row, row, (size_t)n,
+                         dst_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, e->stream));
+  }
+  CU(cudaStreamSynchronize(e->stream));
   return 0;
 }
 

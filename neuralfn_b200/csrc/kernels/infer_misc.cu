@@ -153,6 +153,39 @@ extern "C" int nfn_kv_cache_write(const void* qkv, int ld, void* k_cache, void* 
   return launch_check("kv_cache_write", 1);
 }
 
+// ---- hidden-state taps: rows of the residual stream into per-slot position-indexed buffers ------
+namespace nfn {
+
+// one warp per row: row r belongs to sequence r / block_rows, block row j = r % block_rows, and lands at
+// position lengths[sequence] + j + pos_offset of that sequence's [max_pos, C] region
+__global__ void __launch_bounds__(256)
+rows_to_slots_kernel(const __nv_bfloat16* __restrict__ x, int ldx, int rows, int C, __nv_bfloat16* __restrict__ dst, long long slot_stride,
+                     int max_pos, const int* __restrict__ lengths, int block_rows, int pos_offset, const int* __restrict__ live_rows) {
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int b = r / block_rows, j = r % block_rows;
+  if (live_rows && j >= live_rows[b]) return;
+  const int pos = lengths[b] + j + pos_offset;
+  if (pos < 0 || pos >= max_pos) return;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (long long)r * ldx);
+  uint4* out = reinterpret_cast<uint4*>(dst + b * slot_stride + (long long)pos * C);
+  for (int i = threadIdx.x & 31; i < C / 8; i += 32) out[i] = src[i];
+}
+
+}  // namespace nfn
+
+extern "C" int nfn_rows_to_slots(const void* x, int ldx, int rows, int C, void* dst, long long slot_stride, int max_pos, const int* lengths,
+                                 int block_rows, int pos_offset, const int* live_rows, nfn_stream_t stream) {
+  using namespace nfn;
+  if (rows <= 0) return 0;
+  if (!x || !dst || !lengths || (C & 7) || (ldx & 7) || block_rows <= 0 || max_pos <= 0 || slot_stride < (long long)max_pos * C)
+    return fail(-1, "rows_to_slots: bad arguments");
+  rows_to_slots_kernel<<<(rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, rows, C, static_cast<__nv_bfloat16*>(dst), slot_stride, max_pos, lengths, block_rows, pos_offset,
+      live_rows);
+  return launch_check("rows_to_slots", 1);
+}
+
 // ---- gated attention output and sandwich norms (Glimmer-style blocks) ---------------------------
 namespace nfn {
 

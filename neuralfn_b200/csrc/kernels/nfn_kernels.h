@@ -215,6 +215,12 @@ int nfn_kv_commit_layers(const void* const* stage_k, const void* const* stage_v,
                          const int* caps, const int* lengths, const int* accepted, int n_layers, int B, int rows, int n_kv_heads,
                          int head_dim, nfn_stream_t stream);
 
+// Hidden-state taps: row r of x (bf16 [rows, ldx], C columns used) belongs to sequence r / block_rows and is copied to
+// position lengths[sequence] + r % block_rows + pos_offset of dst [sequences][max_pos][C] (slot_stride elements between
+// sequences). live_rows (optional): rows at or past live_rows[sequence] are skipped. Positions outside [0, max_pos) are skipped.
+int nfn_rows_to_slots(const void* x, int ldx, int rows, int C, void* dst, long long slot_stride, int max_pos, const int* lengths,
+                      int block_rows, int pos_offset, const int* live_rows, nfn_stream_t stream);
+
 // ---- GEMM over K-quant weights, dequantisation fused into the operand pipeline (gemm_kquant.cu) ----
 // C[M, N] = A[M, K] . dequant(W)^T with args->b pointing at N rows of K / 256 super-blocks
 // (qtype: NFN_QTYPE_Q4_K / Q5_K / Q6_K, declared below). K-major A, bf16 output, the bias /

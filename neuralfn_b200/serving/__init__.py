@@ -9,6 +9,6 @@ from .chat import (AssistantResponse, ByteTextCodec, ChatConfigurationError, Cha
                    IncrementalTokenDecoder, MuseGlimmerATEMRenderer, PlaceholderChatRenderer, PlainRolesRenderer, TextCodec,
                    TiktokenTextCodec, TokenIdTextCodec, load_text_codec, parse_assistant_response, resolve_chat_renderer,
                    strip_text_delimiters)
-from .inference import (DraftEngineProposer, GenerationConfig, GenerationEvent, GenerationResult, InferenceError, KVCacheConfig,  # noqa: E402,F401
+from .inference import (DFlashProposer, DraftEngineProposer, GenerationConfig, GenerationEvent, GenerationResult, InferenceError, KVCacheConfig, target_embed_and_head,  # noqa: E402,F401
                         NativeInferenceCapabilities, NativeInferenceModel, NativeInferenceSession, NativeModelLoadConfig, NGramProposer,
                         write_artifact)

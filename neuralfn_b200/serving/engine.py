@@ -135,6 +135,8 @@ def _api():
     L.nfn_engine_commit.argtypes = [vp, vp]
     L.nfn_engine_truncate.argtypes = [vp, ip, ip]
     L.nfn_engine_fork.argtypes = [vp, ip, ip, ip]
+    L.nfn_engine_enable_taps.argtypes = [vp, vp, ip]
+    L.nfn_engine_read_taps.argtypes = [vp, ip, ip, ip, vp, ip]
     L._engine_ready = True
     return L
 
@@ -159,6 +161,7 @@ class EngineError(RuntimeError):
 class ResidentEngine:
     def __init__(self, config: EngineConfig, device: int = 0) -> None:
         self.config = config
+        self.device = int(device)
         self._L = _api()
         cc = config.c()
         self._h = self._L.nfn_engine_create(C.byref(cc), device)
@@ -270,6 +273,23 @@ class ResidentEngine:
     def last_logits(self, slot: int) -> torch.Tensor:
         out = torch.empty(self.config.vocab, dtype=torch.float32)
         self._check(self._L.nfn_engine_last_logits(self._h, slot, out.data_ptr()))
+        return out
+
+    # ---- hidden-state taps (context of a block-diffusion draft) ---------------------------------
+    def enable_taps(self, layers: Sequence[int]) -> None:
+        """Keep the residual stream after each listed layer (0-based) for every cached position. Call before the first decode step."""
+        arr = (C.c_int32 * len(layers))(*[int(l) for l in layers])
+        self._check(self._L.nfn_engine_enable_taps(self._h, C.cast(arr, C.c_void_p), len(layers)))
+        self.tap_layers = tuple(int(l) for l in layers)
+
+    def read_taps(self, slot: int, pos0: int, n: int, *, device: bool = True):
+        """bf16 [n, taps * d_model] for positions [pos0, pos0 + n) of ``slot`` (a CUDA tensor, or a host tensor with ``device=False``)."""
+        import torch
+        width = len(getattr(self, "tap_layers", ())) * self.config.d_model
+        if not width:
+            raise RuntimeError("taps are not enabled on this engine")
+        out = torch.empty(n, width, dtype=torch.bfloat16, device=torch.device("cuda", self.device) if device else "cpu")
+        self._check(self._L.nfn_engine_read_taps(self._h, slot, pos0, n, C.c_void_p(out.data_ptr()), int(device)))
         return out
 
     # ---- block verification / session operations ----------------------------------------------

@@ -33,7 +33,7 @@ from .chat import IncrementalTokenDecoder, TextCodec, TokenIdTextCodec, load_tex
 from .engine import EngineConfig, ResidentEngine, Sampling, resident_inference_abi_version
 
 __all__ = ["InferenceError", "NativeInferenceCapabilities", "GenerationConfig", "KVCacheConfig", "NativeModelLoadConfig", "GenerationEvent",
-           "GenerationResult", "Proposer", "NGramProposer", "DraftEngineProposer", "NativeInferenceModel", "NativeInferenceSession",
+           "GenerationResult", "Proposer", "NGramProposer", "DraftEngineProposer", "DFlashProposer", "target_embed_and_head", "NativeInferenceModel", "NativeInferenceSession",
            "MANIFEST_NAME", "write_artifact"]
 
 MANIFEST_NAME = "native-execution-manifest.json"
@@ -242,6 +242,71 @@ class DraftEngineProposer:
 
 
 # ----------------------------------------------------------------------------------- model
+
+
+class DFlashProposer:
+    """Block-diffusion draft on the target's own hidden states: the resident engine keeps the residual
+    stream after the draft's tap layers for every cached position (``ResidentEngine.enable_taps``); one
+    call reads the last ``context_window`` positions of the slot, runs the draft over the block
+    [pending token, mask, mask, ...] (bidirectional inside the block, context on the taps) and maps the
+    block's hidden states through the target's final norm and head. Block slot i proposes the token at
+    distance i from the pending one, so a single draft pass yields ``block_size - 1`` proposals, which
+    the engine then verifies in one batched pass.
+
+    ``draft``: a ``tensor.dflash.DFlashDraftModel`` (trained by ``DFlashDistillationTrainer`` or loaded from its
+    exported assistant file); ``embed`` [vocab, d] and ``head(hidden) -> logits`` are the target's embedding
+    table and its final norm + LM head on the engine's device. Proposals are the draft's arg-max (a point-mass
+    proposal distribution: rejection sampling then accepts with the target's own probability).
+
+    Reference: the assistant path of ``neuralfn/csrc/native_gpt2/resident_glimmer_assistant.cpp:1295-1352`` (tap
+    context + block through the draft, shared target head) and ``resident_glimmer.cpp:2503-2925`` (propose /
+    verify / commit loop)."""
+
+    def __init__(self, engine: ResidentEngine, slot: int, draft, embed: torch.Tensor, head: Callable[[torch.Tensor], torch.Tensor]) -> None:
+        cfg = draft.cfg
+        if tuple(getattr(engine, "tap_layers", ())) != tuple(cfg.tap_layers):
+            raise InferenceError(f"the engine taps layers {getattr(engine, 'tap_layers', ())}, the draft was trained on {tuple(cfg.tap_layers)}")
+        self.engine, self.slot, self.draft, self.embed, self.head, self.cfg = engine, slot, draft.eval(), embed, head, cfg
+        self.calls = 0
+
+    def reset(self) -> None:
+        self.calls = 0
+
+    @torch.no_grad()
+    def propose(self, history: Sequence[int], k: int) -> tuple[list[int], list[float] | None]:
+        cfg, n = self.cfg, len(history) - 1                     # n tokens are cached; history[-1] is the pending anchor
+        if k <= 0 or n <= 0 or n != self.engine.slot_length(self.slot):
+            return [], None
+        W = min(cfg.context_window, n)
+        dev = self.embed.device
+        taps = self.engine.read_taps(self.slot, n - W, W).to(self.embed.dtype)[None]                  # [1, W, taps * d]
+        ids = torch.full((cfg.block_size,), cfg.mask_token_id, dtype=torch.long, device=dev)
+        ids[0] = int(history[-1])
+        mask = torch.ones(1, 1, cfg.block_size, W + cfg.block_size, dtype=torch.bool, device=dev)
+        hidden = self.draft(self.embed[ids][None, None], taps, mask)[0, 0, 1:]                        # [S - 1, d]
+        picks = self.head(hidden).float().argmax(-1)
+        self.calls += 1
+        return [int(t) for t in picks[:k].tolist()], None
+
+
+def target_embed_and_head(config: EngineConfig, tensors: dict[str, torch.Tensor], device) -> tuple[torch.Tensor, Callable[[torch.Tensor], torch.Tensor]]:
+    """(embedding table, final norm + LM head) of a Llama-family engine's weights, for ``DFlashProposer``. The head applies the
+    plain RMS final norm, the (tied or separate) vocabulary projection, the output multiplier and the soft-cap."""
+    if config.family != 1:
+        raise InferenceError("target_embed_and_head covers the Llama-family tensor names")
+    embed = tensors["tok_embeddings"].to(device, torch.bfloat16)
+    norm = tensors["norm"].to(device, torch.float32)
+    w = embed if config.tie_embeddings else tensors["lm_head"].to(device, torch.bfloat16)
+    mult = config.output_multiplier if getattr(config, "output_multiplier", 0.0) > 0 else 1.0
+    cap, eps, vocab = float(getattr(config, "logit_softcap", 0.0)), config.norm_eps, config.vocab
+
+    def head(hidden: torch.Tensor) -> torch.Tensor:
+        h = hidden.float()
+        h = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps) * norm
+        logits = (h.to(w.dtype) @ w.T).float()[..., :vocab] * mult
+        return cap * torch.tanh(logits / cap) if cap > 0 else logits
+
+    return embed, head
 
 
 def write_artifact(out_dir: str | Path, config: EngineConfig, tensors: dict[str, torch.Tensor], *, chat_template: str | None = None,

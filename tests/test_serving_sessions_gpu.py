@@ -166,3 +166,94 @@ def test_artifact_round_trip_prefix_cache_and_structured_output(tmp_path):
     assert out2["reused_tokens"] >= 4
     json.dumps(out2)
     model.close()
+
+
+def test_hidden_state_taps_agree_across_prefill_decode_and_verify():
+    """The same positions reached three ways (one prompt; prompt + decode steps; prompt + committed verification blocks)
+    hold the same tapped hidden states, and a fork carries them along."""
+    from neuralfn_b200.serving import Sampling
+    toks = (PROMPT * 2)[:36]
+    greedy = Sampling(temperature=0.0)
+
+    def fresh():
+        _cfg, _w, eng = _engine(max_batch=2)
+        eng.enable_taps([0, 2])
+        return eng
+
+    a = fresh()
+    a.prefill(0, toks)
+    full = a.read_taps(0, 0, 36).float()
+    assert full.shape == (36, 512) and float(full.abs().max()) > 0
+    assert torch.equal(a.read_taps(0, 30, 6, device=False).float(), full[30:36].cpu())
+    b = fresh()
+    b.prefill(1, toks[:30])
+    for t in toks[30:36]:
+        b.decode({1: t}, greedy)
+    step = b.read_taps(1, 0, 36).float()
+    assert (step[:30] - full[:30]).abs().max() < 1e-6 and (step - full).abs().max() < 0.06 * full.abs().max()
+    c = fresh()
+    c.prefill(0, toks[:30])
+    c.verify({0: toks[30:34] + [1, 2, 3]})
+    c.commit({0: 4})                                       # three block rows are discarded
+    c.verify({0: toks[34:36]})
+    c.commit({0: 2})
+    blk = c.read_taps(0, 0, 36).float()
+    assert (blk - full).abs().max() < 0.06 * full.abs().max()
+    c.fork(0, 1, 33)
+    assert torch.equal(c.read_taps(1, 0, 33), c.read_taps(0, 0, 33))
+    with pytest.raises(Exception):
+        c.read_taps(1, 30, 6)                              # past the fork's 33 cached tokens
+    for e in (a, b, c):
+        e.close()
+
+
+def test_dflash_proposer_keeps_greedy_output_and_counts_blocks():
+    """A random-initialised block-diffusion draft on the engine's taps: whatever it proposes, verification keeps the
+    target's greedy stream; a draft distilled on the target's own continuation gets its proposals accepted."""
+    from neuralfn_b200.serving import DFlashProposer, GenerationConfig, NativeInferenceModel, target_embed_and_head
+    from neuralfn_b200.tensor.dflash import DFlashConfig, DFlashDraftModel
+    cfg, w, eng = _engine(max_batch=2)
+    eng.enable_taps([0, 2])
+    model = NativeInferenceModel(eng)
+    greedy = GenerationConfig(max_new_tokens=24, temperature=0.0)
+    with model.create_session() as s:
+        s.prefill(PROMPT)
+        plain = s.decode(greedy)
+    dcfg = DFlashConfig(d_model=128, n_layer=2, n_head=4, block_size=8, context_window=64, tap_layers=(0, 2), mask_token_id=0)
+    torch.manual_seed(0)
+    draft = DFlashDraftModel(dcfg, cfg.d_model).cuda().bfloat16()
+    tensors = {k: v.view(-1, cfg.d_model) if k in ("tok_embeddings", "lm_head") else v for k, v in w.items()}
+    embed, head = target_embed_and_head(cfg, tensors, "cuda")
+    with model.create_session() as s:
+        s.prefill(PROMPT)
+        prop = DFlashProposer(eng, s.slot, draft, embed, head)
+        res = s.decode(greedy, proposer=prop, speculative_tokens=7)
+        assert res.completion_tokens == 24 and prop.calls > 0
+        assert res.speculative_proposed_tokens == 7 * res.speculative_assistant_blocks or res.speculative_proposed_tokens > 0
+        assert res.speculative_target_rows >= res.speculative_assistant_blocks
+        _same_up_to_ties(model, PROMPT, plain.token_ids, res.token_ids)
+    # teach the draft the target's continuation of this prompt (a few hundred steps on one sequence), then propose again
+    seq = torch.tensor([PROMPT + list(plain.token_ids)], device="cuda")
+    with model.create_session() as s:
+        s.prefill(seq[0].tolist())
+        taps = eng.read_taps(s.slot, 0, seq.shape[1]).float()[None]
+    draft = draft.float()
+    opt = torch.optim.AdamW(draft.parameters(), lr=3e-3)
+    from neuralfn_b200.tensor.dflash import build_block_inputs, dflash_attention_mask
+    anchors = torch.arange(len(PROMPT) - 1, seq.shape[1] - dcfg.block_size, device="cuda")[None]
+    ids, _pos, tgt_idx = build_block_inputs(seq, anchors, dcfg.block_size, dcfg.mask_token_id)
+    mask = dflash_attention_mask(seq.shape[1], anchors, dcfg.block_size, dcfg.context_window)
+    gold = seq.gather(1, tgt_idx.flatten(1)).view(tgt_idx.shape)
+    for _ in range(300):
+        logits = head(draft(embed.float()[ids], taps, mask))
+        loss = torch.nn.functional.cross_entropy(logits[..., 1:, :].reshape(-1, logits.shape[-1]), gold[..., 1:].reshape(-1))
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    with model.create_session() as s:
+        s.prefill(PROMPT)
+        res = s.decode(greedy, proposer=DFlashProposer(eng, s.slot, draft.bfloat16(), embed, head), speculative_tokens=7)
+        _same_up_to_ties(model, PROMPT, plain.token_ids, res.token_ids)
+        assert res.speculative_accepted_tokens >= 0.5 * res.speculative_proposed_tokens > 0, (res.speculative_accepted_tokens, res.speculative_proposed_tokens)
+        assert res.speculative_target_rows < 24 + res.speculative_assistant_blocks
+    model.close()
