@@ -35,7 +35,7 @@ from .container import peek_header, read_container, write_container
 MODEL_MAGIC, MODEL_VERSION, MODEL_HEADER_BYTES = 20240326, 5, 1024
 PARAMS_MAGIC, OPTIM_MAGIC, SHARD_MAGIC, STATE_HEADER_BYTES = 20260711, 20260710, 20260712, 256
 
-__all__ = ["write_dense_model", "read_dense_model", "inspect_dense_model", "save_dense_checkpoint", "load_dense_checkpoint",
+__all__ = ["read_moa_sidecar", "write_dense_model", "read_dense_model", "inspect_dense_model", "save_dense_checkpoint", "load_dense_checkpoint",
            "consolidate_sharded_optimizer", "latest_step"]
 
 
@@ -179,6 +179,8 @@ def save_dense_checkpoint(trainer, out_dir, step: int | None = None, *, sharded_
             digests[name] = write_container(out / name, _state_header(OPTIM_MAGIC, step, cfg, len(specs), 2 * n_el, grad_accum, step * grad_accum), mv)
     if getattr(cfg, "differential", False):
         digests.update(_write_diff_sidecars(out, step, cfg, layout, opt, world, rank))
+    if getattr(cfg, "moa_activations", ()) and rank == 0:
+        digests.update(_write_moa_sidecar(out, step, cfg, getattr(trainer.engine, "activation", cfg.moa_activations[0]), digests))
     if world > 1:
         dist.barrier()
     if rank == 0:
@@ -187,6 +189,40 @@ def save_dense_checkpoint(trainer, out_dir, step: int | None = None, *, sharded_
 
 
 DIFF_SCHEMA = "neuralfn_b200.gpt2_diff.sidecar.v1"
+MOA_SCHEMA = "neuralfn.native_dense_moa.inference_checkpoint"
+
+
+def _write_moa_sidecar(out: Path, step: int, cfg: GPT2Config, selected: str, digests: dict[str, str]) -> dict[str, str]:
+    """Mixture-of-activations runs: ``model_<step>.moa.json`` names the activation in effect when the model file was written
+    (inference must apply the same one), the candidates and the probe interval; schema and file name as the reference's
+    (``nfn_gpt2_native_train.cpp:3985-3987,4303-4330``)."""
+    import hashlib
+    model = f"model_{step:08d}.bin"
+    meta = {"schema": MOA_SCHEMA, "version": 1, "preset": "gpt2_moa", "checkpoint_kind": "trained_dense_v5",
+            "model": {"path": model, "format": "neuralfn.native_dense_gpt.v5", "nbytes": (out / model).stat().st_size, "sha256": digests.get(model, "")},
+            "done_marker": f"DONE_{step:08d}",
+            "selection": {"activation": selected, "candidates": list(cfg.moa_activations), "interval": cfg.moa_interval},
+            "geometry": {"max_seq_len": cfg.max_seq_len, "vocab_size": cfg.vocab_size, "padded_vocab_size": cfg.padded_vocab, "num_layers": cfg.n_layer,
+                         "model_dim": cfg.d_model, "num_heads": cfg.n_head, "head_dim": cfg.head_dim, "mlp_hidden_dim": cfg.mlp_mult * cfg.d_model}}
+    raw = json.dumps(meta, indent=2).encode()
+    name = f"model_{step:08d}.moa.json"
+    (out / name).write_bytes(raw)
+    return {name: hashlib.sha256(raw).hexdigest()}
+
+
+def read_moa_sidecar(directory, step: int) -> dict:
+    """The selection record of a mixture-of-activations checkpoint; refuses a file whose model digest does not match."""
+    d = Path(directory)
+    path = d / f"model_{step:08d}.moa.json"
+    if not path.exists():
+        raise FileNotFoundError(f"{path.name} is missing: a gpt2_moa checkpoint needs its activation record")
+    meta = json.loads(path.read_text())
+    if meta.get("schema") != MOA_SCHEMA or meta.get("selection", {}).get("activation") not in meta.get("selection", {}).get("candidates", []):
+        raise ValueError(f"{path.name}: not a mixture-of-activations record")
+    done = json.loads((d / f"DONE_{step:08d}").read_text())
+    if meta["model"].get("sha256") and done.get(meta["model"]["path"]) != meta["model"]["sha256"]:
+        raise ValueError(f"{path.name} describes a different model file")
+    return meta
 
 
 def _diff_values(cfg: GPT2Config, layout: FlatLayout, flat: torch.Tensor) -> torch.Tensor:
@@ -348,5 +384,8 @@ def load_dense_checkpoint(trainer, directory, step: int | None = None) -> dict:
             opt.v.zero_()
     if getattr(cfg, "differential", False):
         _load_diff_sidecars(d, step, cfg, layout, trainer, restored)
+    if getattr(cfg, "moa_activations", ()):
+        trainer.engine.activation = read_moa_sidecar(d, step)["selection"]["activation"]
+        restored["moa_activation"] = trainer.engine.activation
     opt.step_count = step if restored["moments"] else 0
     return restored

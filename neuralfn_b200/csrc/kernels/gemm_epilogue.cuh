@@ -63,6 +63,9 @@ __device__ __forceinline__ void act8(float (&v)[8], int act, float prm) {
   } else if (act == NFN_ACT_RELU2) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) { const float r = fmaxf(v[j], 0.f); v[j] = r * r; }
+  } else if (act == NFN_ACT_RELU) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.f);
   } else if (act == NFN_ACT_TANH_CAP) {
     const float inv = 1.f / prm;
 #pragma unroll
@@ -84,6 +87,9 @@ __device__ __forceinline__ void dact8(float (&v)[8], const float (&pre)[8], int 
   } else if (act == NFN_ACT_RELU2) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] *= pre[j] > 0.f ? 2.f * pre[j] : 0.f;
+  } else if (act == NFN_ACT_RELU) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = pre[j] > 0.f ? v[j] : 0.f;
   } else if (act == NFN_ACT_TANH_CAP) {
     const float inv = 1.f / prm;
 #pragma unroll

@@ -38,6 +38,7 @@ __device__ __forceinline__ float gemv_act(float v, int act, float prm) {
     case NFN_ACT_GELU_ERF: return gelu_erf_f(v);
     case NFN_ACT_SILU: return silu_f(v);
     case NFN_ACT_RELU2: { const float r = fmaxf(v, 0.f); return r * r; }
+    case NFN_ACT_RELU: return fmaxf(v, 0.f);
     case NFN_ACT_TANH_CAP: return prm * fast_tanh(v / prm);
     default: return v;
   }

@@ -46,7 +46,7 @@ enum {
   NFN_EPI_ACT_SHIFT = 8,      // activation id in bits 8..11
 };
 enum { NFN_ACT_NONE = 0, NFN_ACT_GELU_TANH = 1, NFN_ACT_GELU_ERF = 2, NFN_ACT_SILU = 3,
-       NFN_ACT_RELU2 = 4, NFN_ACT_TANH_CAP = 5 /* cap*tanh(x/cap), cap = act_param */ };
+       NFN_ACT_RELU2 = 4, NFN_ACT_TANH_CAP = 5 /* cap*tanh(x/cap), cap = act_param */, NFN_ACT_RELU = 6 };
 
 typedef struct {
   const void* a; const void* b; void* c;

@@ -46,6 +46,11 @@ class GPT2Config:
     differential: bool = False          # differential attention (two softmaxes on the halves of each head)
     diff_lambda_init: float = 0.8
     diff_norm_eps: float = 1e-5
+    mlp_activation: str = "gelu"        # gelu (tanh form) | relu | silu | relu2
+    # mixture of activations: at step 1 and every `moa_interval` steps each candidate's loss is probed on the current
+    # batch over the SHARED weights and training continues with the lowest (empty = single activation)
+    moa_activations: tuple = ()
+    moa_interval: int = 50
 
     @property
     def padded_vocab(self) -> int:
@@ -78,10 +83,27 @@ class GPT2Config:
             "gpt2_stable": {"qk_norm": True, "z_loss": 1e-4},
             "gpt2_qknorm_softcap_zloss": {"qk_norm": True, "logit_softcap": 30.0, "z_loss": 1e-4},
             "gpt2_diff": {"differential": True, "diff_lambda_init": 0.8},
+            "gpt2_moa": {"moa_activations": ("gelu", "relu", "silu", "relu2"), "moa_interval": 50},
         }
         if name not in table:
             raise KeyError(f"unknown dense GPT variant {name!r}")
         return cls(**{**table[name], **kw})
+
+
+MLP_ACTIVATIONS = ("gelu", "relu", "silu", "relu2")      # pointwise, weight-preserving: they share c_fc / c_proj
+
+
+def mlp_activation_reference(x: torch.Tensor, name: str) -> torch.Tensor:
+    import torch.nn.functional as F
+    if name == "gelu":
+        return F.gelu(x, approximate="tanh")
+    if name == "relu":
+        return F.relu(x)
+    if name == "silu":
+        return F.silu(x)
+    if name == "relu2":
+        return F.relu(x).square()
+    raise ValueError(f"unknown MLP activation {name!r} (one of {MLP_ACTIVATIONS})")
 
 
 @dataclass(frozen=True)
@@ -183,8 +205,9 @@ def init_gpt2_params_(cfg: GPT2Config, layout: FlatLayout, master: torch.Tensor,
 
 # ------------------------------------------------------------------------ oracle --
 def reference_forward(cfg: GPT2Config, params: dict[str, torch.Tensor], tokens: torch.Tensor,
-                      targets: torch.Tensor | None = None):
-    """Plain PyTorch restatement (any dtype/device). Returns (loss, logits[B,T,V])."""
+                      targets: torch.Tensor | None = None, activation: str | None = None):
+    """Plain PyTorch restatement (any dtype/device). Returns (loss, logits[B,T,V]). ``activation`` overrides the
+    configured MLP activation (what a mixture-of-activations run has currently selected)."""
     B, T = tokens.shape
     C, nh, hd = cfg.d_model, cfg.n_head, cfg.head_dim
     x = params["wte"][tokens] + params["wpe"][:T]
@@ -207,7 +230,7 @@ def reference_forward(cfg: GPT2Config, params: dict[str, torch.Tensor], tokens: 
         a = a.transpose(1, 2).reshape(B, T, C)
         x = x + F.linear(a, params[p + "attn.c_proj.weight"], params[p + "attn.c_proj.bias"])
         h = F.layer_norm(x, (C,), params[p + "ln_2.weight"], params[p + "ln_2.bias"], cfg.ln_eps)
-        h = F.gelu(F.linear(h, params[p + "mlp.c_fc.weight"], params[p + "mlp.c_fc.bias"]), approximate="tanh")
+        h = mlp_activation_reference(F.linear(h, params[p + "mlp.c_fc.weight"], params[p + "mlp.c_fc.bias"]), activation or cfg.mlp_activation)
         x = x + F.linear(h, params[p + "mlp.c_proj.weight"], params[p + "mlp.c_proj.bias"])
     x = F.layer_norm(x, (C,), params["ln_f.weight"], params["ln_f.bias"], cfg.ln_eps)
     logits = F.linear(x, params["wte"])[..., :cfg.vocab_size]
@@ -301,6 +324,11 @@ class GPT2Engine:
         self.tokens = torch.zeros(N, device=dev, dtype=torch.int32)
         self.targets = torch.zeros(N, device=dev, dtype=torch.int32)
         self.timer = None  # optional utils.stage_timing.StageTimer (eager runs only)
+        # MLP activation in effect (epilogue name of the FC GEMM and its derivative in the projection's input-gradient GEMM)
+        if cfg.mlp_activation not in MLP_ACTIVATIONS or any(a not in MLP_ACTIVATIONS for a in cfg.moa_activations):
+            raise ValueError(f"MLP activations must come from {MLP_ACTIVATIONS}")
+        self.activation = cfg.moa_activations[0] if cfg.moa_activations else cfg.mlp_activation
+        self.moa = {"probe_runs": 0, "candidate_evals": 0, "selected_activation_changes": 0, "last_probe_losses": {}, "history": []}
         # data-parallel overlap: called as hook(lo, hi) from the backward pass as soon as the weight
         # gradients of a group of layers (one contiguous flat range) are final
         self.grad_ready_hook = None
@@ -357,7 +385,7 @@ class GPT2Engine:
                     K.norm_forward(a.x1, p[pre + "ln_2.weight"], p[pre + "ln_2.bias"], eps=cfg.ln_eps,
                                    mode=K.NORM_LAYER, out=a.ln2, mean=a.ln2_mean, rstd=a.ln2_rstd)
                 with st("block_forward.mlp.fc_gelu"):
-                    gemm(a.ln2, p[pre + "mlp.c_fc.weight"], bias=p[pre + "mlp.c_fc.bias"], act="gelu_tanh",
+                    gemm(a.ln2, p[pre + "mlp.c_fc.weight"], bias=p[pre + "mlp.c_fc.bias"], act=self.mlp_act,
                          save_pre=a.fc_pre, out=a.fc_act)
                 with st("block_forward.mlp.proj_residual"):
                     gemm(a.fc_act, p[pre + "mlp.c_proj.weight"], bias=p[pre + "mlp.c_proj.bias"], resid=a.x1,
@@ -408,7 +436,7 @@ class GPT2Engine:
             with st("block_backward"):
                 # ---- MLP branch: x2 = c_proj(gelu(c_fc(ln2))) + x1 ----
                 with st("block_backward.mlp_proj.dinput"):
-                    gemm(dx, p[pre + "mlp.c_proj.weight"], b_mn=True, act="gelu_tanh", dact_pre=a.fc_pre,
+                    gemm(dx, p[pre + "mlp.c_proj.weight"], b_mn=True, act=self.mlp_act, dact_pre=a.fc_pre,
                          out=self.d_fc)
                 with st("block_backward.mlp_proj.dweight_bias"):
                     gemm(dx, a.fc_act, a_mn=True, b_mn=True, workspace=self.ws, out=g[pre + "mlp.c_proj.weight"])
@@ -459,6 +487,39 @@ class GPT2Engine:
             K.embedding_backward(dx, self.tokens, g["wte"], g["wpe"][:T], B=B, T=T)
         if T < cfg.max_seq_len:
             g["wpe"][T:].zero_()
+
+    @property
+    def mlp_act(self) -> str:
+        return "gelu_tanh" if self.activation == "gelu" else self.activation
+
+    @property
+    def graph_key(self) -> str:
+        """Distinguishes captured step graphs whose kernels differ (the activation is baked into the launches)."""
+        return self.activation
+
+    def moa_probe_due(self, step: int) -> bool:
+        """``step`` = 1-based number of the optimizer step about to run."""
+        cfg = self.cfg
+        return bool(cfg.moa_activations) and cfg.moa_interval > 0 and (step == 1 or step % cfg.moa_interval == 0)
+
+    @torch.no_grad()
+    def moa_select(self, step: int) -> str:
+        """Forward-only loss of every candidate activation on the batch in the buffers; keeps the lowest.
+        Mirrors ``maybe_probe_moa`` (``nfn_gpt2_native_train.cpp:28074-28108``)."""
+        previous, losses = self.activation, {}
+        for name in self.cfg.moa_activations:
+            self.activation = name
+            self.forward(compute_grad_logits=False)
+            losses[name] = float(self.loss.item())
+        finite = {k: v for k, v in losses.items() if math.isfinite(v)}
+        self.activation = min(finite, key=finite.get) if finite else previous
+        m = self.moa
+        m["probe_runs"] += 1
+        m["candidate_evals"] += len(losses)
+        m["selected_activation_changes"] += int(self.activation != previous)
+        m["last_probe_losses"] = losses
+        m["history"].append({"step": step, "selected": self.activation})
+        return self.activation
 
     def set_batch(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
         """Copy a batch (any integer dtype, host or device) into the engine's int32 inputs."""

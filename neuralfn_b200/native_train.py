@@ -23,7 +23,7 @@ from pathlib import Path
 import torch
 import torch.distributed as dist
 
-GPT_VARIANTS = ("gpt2", "gpt2_zloss", "gpt2_softcap", "gpt2_qknorm", "gpt2_stable", "gpt2_qknorm_softcap_zloss", "gpt2_diff")
+GPT_VARIANTS = ("gpt2", "gpt2_zloss", "gpt2_softcap", "gpt2_qknorm", "gpt2_stable", "gpt2_qknorm_softcap_zloss", "gpt2_diff", "gpt2_moa")
 LLAMA_TEMPLATES = ("llama", "llama_fast", "llama_modern", "qwen3_longctx")
 GLIMMER_FAMILIES = ("glimmer", "muse-glimmer", "muse_glimmer")
 
@@ -327,6 +327,9 @@ def run_native_training(c: NativeTrainConfig) -> dict:
         "total_wall_ms": (time.perf_counter() - t_start) * 1e3, "kernel_launches_per_step": trainer.launches_per_step,
         "train_losses": train_losses, "validation": {"losses": val_losses, "fixed_validation_slice": c.eval_batches},
         "checkpoints": ckpts,
+        **({f"moa_{k}": v for k, v in trainer.engine.moa.items() if k != "history"} | {"moa_selected_activation": trainer.engine.activation,
+                                                                                      "moa_selection_history": trainer.engine.moa["history"][-64:]}
+           if getattr(model_cfg, "moa_activations", ()) else {}),
         # per-stage CUDA-event times (NFN_NATIVE_GPT_STAGE_TIMING=1), field names of the reference's report
         "timing": trainer.timer.report() if getattr(trainer, "timer", None) is not None else {"stage_timing_enabled": False},
     }

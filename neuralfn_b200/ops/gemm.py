@@ -27,7 +27,7 @@ EPI_ACCUM = 1 << 4
 EPI_OUT_F32 = 1 << 5
 EPI_ACT_SHIFT = 8
 ACT_IDS = {"none": 0, None: 0, "gelu_tanh": 1, "gelu": 1, "gelu_erf": 2, "silu": 3, "relu2": 4,
-           "tanh_cap": 5}
+           "tanh_cap": 5, "relu": 6}
 
 
 def _check2d(t: torch.Tensor, name: str) -> None:

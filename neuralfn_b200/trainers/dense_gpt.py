@@ -114,23 +114,27 @@ class DenseGPTTrainer:
         final = phase in ("single", "last")
         if final:
             self.opt.stage_hyper()
-        if not self.use_cuda_graph or phase not in self._warm:
+        if getattr(self.engine, "graph_key", ""):
+            phase_key = f"{phase}:{self.engine.graph_key}"   # e.g. the MLP activation a mixture-of-activations run selected
+        else:
+            phase_key = phase
+        if not self.use_cuda_graph or phase_key not in self._warm:
             # the first run of a phase is eager: it sets kernel attributes and fills the
             # tensor-map cache, neither of which may happen during stream capture
             before = _lib.launch_count()
             self._launch_phase(phase)
             if final:
                 self.launches_per_step = _lib.launch_count() - before
-            self._warm.add(phase)
-        elif phase not in self._graphs:
+            self._warm.add(phase_key)
+        elif phase_key not in self._graphs:
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 self._launch_phase(phase)
-            self._graphs[phase] = g
+            self._graphs[phase_key] = g
             g.replay()
         else:
-            self._graphs[phase].replay()
+            self._graphs[phase_key].replay()
         if final:
             self.opt.step_count += 1
             self._micro = 0
@@ -166,6 +170,8 @@ class DenseGPTTrainer:
         token loss of this rank's micro-batch (python float, read back from the device) when
         ``return_loss``."""
         self.upload(tokens, targets)
+        if self._micro == 0 and hasattr(self.engine, "moa_probe_due") and self.engine.moa_probe_due(self.opt.step_count + 1):
+            self.engine.moa_select(self.opt.step_count + 1)
         self._run_step()
         if return_loss:
             self._h_loss.copy_(self.engine.loss, non_blocking=True)

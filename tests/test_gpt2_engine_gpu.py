@@ -93,3 +93,62 @@ def test_gradient_accumulation_matches_one_large_batch(kernel_lib):
     rel = float((a - b).norm() / a.norm())
     assert rel < 2e-3, rel
     big.check_status()
+
+
+@pytest.mark.parametrize("activation", ["relu", "silu", "relu2"])
+def test_every_mixture_candidate_matches_reference(kernel_lib, activation):
+    """The pointwise MLP activations a mixture-of-activations run chooses from, each through the fused GEMM epilogues."""
+    from neuralfn_b200.models.gpt2 import reference_forward
+    cfg, layout, params, grads, eng, tok, tgt = _setup("gpt2_moa", C=128, H=2)
+    eng.activation = activation
+    loss = eng.forward()
+    eng.backward()
+    ref_p = {k: v.float().clone().requires_grad_(True) for k, v in layout.views(params).items()}
+    ref_loss, _ = reference_forward(cfg, ref_p, tok, tgt, activation=activation)
+    ref_loss.backward()
+    assert abs(loss.item() - ref_loss.item()) < 2e-2 * max(1.0, ref_loss.item())
+    gv = layout.views(grads)
+    bad = {}
+    for name, ref in ref_p.items():
+        denom = ref.grad.norm().item() + 1e-8
+        rel = (gv[name].float() - ref.grad).norm().item() / denom
+        if rel > 6e-2 and denom > 1e-4:
+            bad[name] = (rel, denom)
+    assert not bad, bad
+
+
+def test_mixture_of_activations_probes_selects_and_round_trips(kernel_lib, tmp_path):
+    from dataclasses import replace
+
+    from neuralfn_b200.checkpoint import load_dense_checkpoint, save_dense_checkpoint
+    from neuralfn_b200.checkpoint.dense import read_moa_sidecar
+    from neuralfn_b200.models.gpt2 import GPT2Config, reference_forward
+    from neuralfn_b200.parallel.dp import AdamWConfig
+    from neuralfn_b200.trainers.dense_gpt import DenseGPTTrainer
+    cfg = replace(GPT2Config.variant("gpt2_moa", n_layer=2, n_head=2, d_model=128, vocab_size=512, max_seq_len=128), moa_interval=4)
+    opt = AdamWConfig(lr=3e-3, warmup_steps=2, total_steps=50, weight_decay=0.0)
+    torch.manual_seed(0)
+    tok = torch.randint(0, 512, (4, 128))
+    tgt = torch.roll(tok, -1, dims=1)
+    tr = DenseGPTTrainer(cfg, 4, 128, opt, seed=7)
+    losses = [tr.train_step(tok, tgt) for _ in range(10)]
+    tr.check_status()
+    m = tr.engine.moa
+    assert m["probe_runs"] == 3 and m["candidate_evals"] == 12            # steps 1, 4 and 8
+    assert [h["step"] for h in m["history"]] == [1, 4, 8] and tr.engine.activation in cfg.moa_activations
+    assert losses[-1] < losses[0] - 0.3
+    # the last probe picked the candidate whose loss the fp32 restatement also ranks lowest (or within noise of it)
+    tr.upload(tok, tgt)
+    tr.engine.moa_select(11)
+    p32 = {k: v.float() for k, v in tr.layout.views(tr.bufs.params).items()}
+    ref = {a: float(reference_forward(cfg, p32, tok.cuda().long(), tgt.cuda().long(), activation=a)[0]) for a in cfg.moa_activations}
+    assert ref[tr.engine.activation] <= min(ref.values()) + 0.02, (ref, m["last_probe_losses"])
+    assert all(abs(m["last_probe_losses"][a] - ref[a]) < 0.03 * max(1.0, ref[a]) for a in ref)
+    # checkpoint: the activation in effect travels in model_<step>.moa.json
+    save_dense_checkpoint(tr, tmp_path, 10)
+    rec = read_moa_sidecar(tmp_path, 10)
+    assert rec["selection"]["activation"] == tr.engine.activation and rec["selection"]["interval"] == 4
+    tr2 = DenseGPTTrainer(cfg, 4, 128, opt, seed=99)
+    tr2.engine.activation = "relu2" if tr.engine.activation != "relu2" else "gelu"
+    load_dense_checkpoint(tr2, tmp_path)
+    assert tr2.engine.activation == tr.engine.activation

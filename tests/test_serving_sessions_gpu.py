@@ -232,28 +232,25 @@ def test_dflash_proposer_keeps_greedy_output_and_counts_blocks():
         assert res.speculative_proposed_tokens == 7 * res.speculative_assistant_blocks or res.speculative_proposed_tokens > 0
         assert res.speculative_target_rows >= res.speculative_assistant_blocks
         _same_up_to_ties(model, PROMPT, plain.token_ids, res.token_ids)
-    # teach the draft the target's continuation of this prompt (a few hundred steps on one sequence), then propose again
-    seq = torch.tensor([PROMPT + list(plain.token_ids)], device="cuda")
-    with model.create_session() as s:
-        s.prefill(seq[0].tolist())
-        taps = eng.read_taps(s.slot, 0, seq.shape[1]).float()[None]
-    draft = draft.float()
-    opt = torch.optim.AdamW(draft.parameters(), lr=3e-3)
-    from neuralfn_b200.tensor.dflash import build_block_inputs, dflash_attention_mask
-    anchors = torch.arange(len(PROMPT) - 1, seq.shape[1] - dcfg.block_size, device="cuda")[None]
-    ids, _pos, tgt_idx = build_block_inputs(seq, anchors, dcfg.block_size, dcfg.mask_token_id)
-    mask = dflash_attention_mask(seq.shape[1], anchors, dcfg.block_size, dcfg.context_window)
-    gold = seq.gather(1, tgt_idx.flatten(1)).view(tgt_idx.shape)
-    for _ in range(300):
-        logits = head(draft(embed.float()[ids], taps, mask))
-        loss = torch.nn.functional.cross_entropy(logits[..., 1:, :].reshape(-1, logits.shape[-1]), gold[..., 1:].reshape(-1))
-        opt.zero_grad()
-        loss.backward()
-        opt.step()
+    # a draft that knows the continuation: its proposals are accepted, which proves that the tap window the proposer
+    # reads, the block layout ([pending, mask, ...]; slot i = distance i) and the shared final norm + head line up
+    future = list(PROMPT) + list(plain.token_ids)
+    rows = tensors["lm_head"].float().cuda() / tensors["norm"].float().cuda()     # the head then scores each row's own token highest
+
+    class KnowingDraft(torch.nn.Module):
+        cfg = dcfg
+
+        def forward(self, block_embeds, taps, mask):
+            n = taps.shape[1]                                   # cached tokens, all inside the context window here
+            assert block_embeds.shape[:3] == (1, 1, dcfg.block_size) and mask.shape[-1] == n + dcfg.block_size
+            assert taps.shape[-1] == 2 * cfg.d_model and float(taps.abs().max()) > 0
+            toks = [future[n + i] if n + i < len(future) else 0 for i in range(dcfg.block_size)]
+            return rows[toks][None, None]
+
     with model.create_session() as s:
         s.prefill(PROMPT)
-        res = s.decode(greedy, proposer=DFlashProposer(eng, s.slot, draft.bfloat16(), embed, head), speculative_tokens=7)
-        _same_up_to_ties(model, PROMPT, plain.token_ids, res.token_ids)
-        assert res.speculative_accepted_tokens >= 0.5 * res.speculative_proposed_tokens > 0, (res.speculative_accepted_tokens, res.speculative_proposed_tokens)
-        assert res.speculative_target_rows < 24 + res.speculative_assistant_blocks
+        res = s.decode(greedy, proposer=DFlashProposer(eng, s.slot, KnowingDraft(), embed, head), speculative_tokens=7)
+        assert tuple(res.token_ids) == tuple(plain.token_ids)
+        assert res.speculative_accepted_tokens >= 0.8 * res.speculative_proposed_tokens > 0, (res.speculative_accepted_tokens, res.speculative_proposed_tokens)
+        assert res.speculative_target_rows < 24 + res.speculative_assistant_blocks and res.speculative_assistant_blocks <= 5
     model.close()
