@@ -249,13 +249,21 @@ def cmd_infer(a) -> int:
     from ..checkpoint import read_dense_model
     from ..serving import EngineConfig, ResidentEngine, Sampling
     cfg, tensors, sha = read_dense_model(a.checkpoint)
-    eng = ResidentEngine(EngineConfig.gpt2(cfg, max_batch=a.max_batch))
+    activation = None
+    moa = a.checkpoint[:-4] + ".moa.json" if a.checkpoint.endswith(".bin") else ""
+    if moa and os.path.exists(moa):
+        # a mixture-of-activations run: generate with the activation that was in effect when the file was written
+        import re
+        from ..checkpoint.dense import read_moa_sidecar
+        step = int(re.search(r"model_(\d+)\.bin$", a.checkpoint).group(1))
+        activation = read_moa_sidecar(os.path.dirname(a.checkpoint) or ".", step)["selection"]["activation"]
+    eng = ResidentEngine(EngineConfig.gpt2(cfg, max_batch=a.max_batch, activation=activation))
     eng.load_named_tensors(tensors)
     prompts = [[int(t) for t in p.split(",") if t] for p in a.prompt_tokens.split(";")]
     out = eng.generate(prompts, max_new_tokens=a.max_new_tokens,
                        sampling=Sampling(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p, seed=a.seed),
                        eos_token=a.eos_token if a.eos_token >= 0 else None)
-    print(json.dumps({"status": "ok", "checkpoint_sha256": sha, "prompts": prompts, "generated": out,
+    print(json.dumps({"status": "ok", "checkpoint_sha256": sha, "prompts": prompts, "generated": out, "mlp_activation": activation or "gelu",
                       "device_bytes": eng.device_bytes, "kernel_launches": eng.launches}))
     return 0
 

@@ -44,6 +44,7 @@ typedef struct {
   float q_scale;        // multiplies the normalised, rotated query (0 = 1)
   float output_multiplier;  // multiplies the logits before the soft cap (0 = 1)
   float post_norm_eps;  // epsilon of the sandwich norms (0 = norm_eps)
+  int mlp_activation;   // family 0: NFN_ACT_* id of the MLP activation (0 = GELU, tanh form); mixture-of-activations checkpoints name theirs
 } nfn_engine_config;
 
 typedef struct {

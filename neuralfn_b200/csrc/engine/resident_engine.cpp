@@ -265,7 +265,7 @@ int forward_layers(nfn_engine& e, int rows, bool decode, int slot, const int* d_
     if (c.family == 0) {
       if (gemm(e, e.att, ATT, e.W(gname(l, "attn.c_proj.weight")), e.x, C, rows, C, ATT, 0, e.W(gname(l, "attn.c_proj.bias")), e.x, C)) return -1;
       K(nfn_norm_forward(e.x, e.W(gname(l, "ln_2.weight")), e.W(gname(l, "ln_2.bias")), e.xn, nullptr, nullptr, rows, C, c.norm_eps, 0, 0, e.stream));
-      if (gemm(e, e.xn, C, e.W(gname(l, "mlp.c_fc.weight")), e.ff, F, rows, F, C, NFN_ACT_GELU_TANH << NFN_EPI_ACT_SHIFT, e.W(gname(l, "mlp.c_fc.bias")), nullptr, 0)) return -1;
+      if (gemm(e, e.xn, C, e.W(gname(l, "mlp.c_fc.weight")), e.ff, F, rows, F, C, (c.mlp_activation > 0 ? c.mlp_activation : NFN_ACT_GELU_TANH) << NFN_EPI_ACT_SHIFT, e.W(gname(l, "mlp.c_fc.bias")), nullptr, 0)) return -1;
       if (gemm(e, e.ff, F, e.W(gname(l, "mlp.c_proj.weight")), e.x, C, rows, C, F, 0, e.W(gname(l, "mlp.c_proj.bias")), e.x, C)) return -1;
     } else {
       const float post_eps = c.post_norm_eps > 0.f ? c.post_norm_eps : c.norm_eps;

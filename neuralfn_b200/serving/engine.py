@@ -30,7 +30,8 @@ class _CConfig(C.Structure):
                 ("norm_eps", C.c_float), ("qk_norm_eps", C.c_float), ("logit_softcap", C.c_float), ("tie_embeddings", C.c_int),
                 ("window", C.c_int), ("global_every", C.c_int), ("embed_scale", C.c_float), ("use_cuda_graph", C.c_int),
                 ("gated_attention", C.c_int), ("sandwich_norms", C.c_int), ("centered_norms", C.c_int), ("embed_norm", C.c_int),
-                ("rope_local_only", C.c_int), ("q_scale", C.c_float), ("output_multiplier", C.c_float), ("post_norm_eps", C.c_float)]
+                ("rope_local_only", C.c_int), ("q_scale", C.c_float), ("output_multiplier", C.c_float), ("post_norm_eps", C.c_float),
+                ("mlp_activation", C.c_int)]
 
 
 class _CSampling(C.Structure):
@@ -83,10 +84,15 @@ class EngineConfig:
     q_scale: float = 0.0
     output_multiplier: float = 0.0
     post_norm_eps: float = 0.0
+    mlp_activation: int = 0       # GPT-2 family: epilogue id of the MLP activation (0 = tanh GELU); see MLP_ACTIVATION_IDS
+
+    MLP_ACTIVATION_IDS = {"gelu": 1, "silu": 3, "relu2": 4, "relu": 6}
 
     @classmethod
-    def gpt2(cls, cfg, max_batch: int = 8, **kw) -> "EngineConfig":
-        """From a ``models.gpt2.GPT2Config``."""
+    def gpt2(cls, cfg, max_batch: int = 8, *, activation: str | None = None, **kw) -> "EngineConfig":
+        """From a ``models.gpt2.GPT2Config``. ``activation``: the one a mixture-of-activations checkpoint selected
+        (``checkpoint.dense.read_moa_sidecar``); default: the configuration's own."""
+        kw.setdefault("mlp_activation", cls.MLP_ACTIVATION_IDS[activation or getattr(cfg, "mlp_activation", "gelu")])
         return cls(family=0, n_layer=cfg.n_layer, d_model=cfg.d_model, n_head=cfg.n_head, n_kv_head=cfg.n_head,
                    head_dim=cfg.head_dim, d_ff=cfg.mlp_mult * cfg.d_model, vocab=cfg.vocab_size, padded_vocab=cfg.padded_vocab,
                    max_seq=cfg.max_seq_len, max_batch=max_batch, qk_norm=1 if cfg.qk_norm else 0, norm_eps=cfg.ln_eps,
