@@ -38,7 +38,7 @@ from ..tensor import kernel_bridge as KB
 from .dp import AdamWConfig, lr_at_step
 from .tp import TensorParallelContext
 
-__all__ = ["TPLlama", "TPLlamaTrainer", "shard_llama_params", "tp_llama_param_specs"]
+__all__ = ["tp_dp_mesh", "TPLlama", "TPLlamaTrainer", "shard_llama_params", "tp_llama_param_specs"]
 
 
 # ------------------------------------------------------------------ parameter sharding --
@@ -243,10 +243,34 @@ def _rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, sign: float) ->
 
 
 # ------------------------------------------------------------------------------- model --
+def tp_dp_mesh(tp_size: int):
+    """Splits the default process group into a TP x DP mesh: consecutive ranks form a tensor-parallel group (they
+    share NVLink peer memory for the fused collective GEMMs), ranks with the same position in their groups form a
+    data-parallel group. Collective: every rank creates every group. Returns (tp_group, dp_group, tp_index, dp_index)."""
+    world, rank = dist.get_world_size(), dist.get_rank()
+    if tp_size < 1 or world % tp_size:
+        raise ValueError(f"world size {world} is not a multiple of the tensor-parallel size {tp_size}")
+    n_dp = world // tp_size
+    tp_group = dp_group = None
+    for d in range(n_dp):
+        g = dist.new_group(list(range(d * tp_size, (d + 1) * tp_size)))
+        if rank // tp_size == d:
+            tp_group = g
+    for t in range(tp_size):
+        g = dist.new_group([d * tp_size + t for d in range(n_dp)])
+        if rank % tp_size == t:
+            dp_group = g
+    return tp_group, dp_group, rank % tp_size, rank // tp_size
+
+
 class TPLlama:
     def __init__(self, cfg: LlamaConfig, tp: TensorParallelContext, *, dtype=None, seed: int = 1337,
-                 full_params: dict[str, torch.Tensor] | None = None) -> None:
+                 full_params: dict[str, torch.Tensor] | None = None, dp_group=None) -> None:
+        """``dp_group``: the ranks that hold the SAME shard in other tensor-parallel groups (a TP x DP mesh, see
+        ``tp_dp_mesh``); every replica trains on its own batch and gradients are averaged over that group."""
         self.cfg, self.tp = cfg, tp
+        self.dp_group = dp_group
+        self.dp_world = dist.get_world_size(dp_group) if dp_group is not None else 1
         dev = tp.device
         self.dtype = dtype or (torch.bfloat16 if dev.type == "cuda" else torch.float32)
         self.layout = FlatLayout(tp_llama_param_specs(cfg, tp.world))
@@ -381,11 +405,18 @@ class TPLlama:
                     v.grad = None
             if self.tp.world > 1:
                 dist.all_reduce(self.grads[self.n_sharded:], group=self.tp.group)
+            if self.dp_world > 1:
+                # replicas of this shard saw different batches: one flat all-reduce averages the whole buffer
+                dist.all_reduce(self.grads, group=self.dp_group)
+                self.grads.mul_(1.0 / self.dp_world)
 
     def reduce_loss(self, share: torch.Tensor) -> torch.Tensor:
-        """Batch-mean loss from this rank's share (``loss`` returns mean-over-local-rows / W)."""
+        """Batch-mean loss from this rank's share (``loss`` returns mean-over-local-rows / W), averaged over the replicas."""
         if self.tp.world > 1:
             dist.all_reduce(share, group=self.tp.group)
+        if self.dp_world > 1:
+            dist.all_reduce(share, group=self.dp_group)
+            share /= self.dp_world
         return share
 
     def grad_norm(self) -> torch.Tensor:

@@ -117,6 +117,7 @@ def main(argv=None) -> int:
     ap.add_argument("--output-dir", default="")
     ap.add_argument("--resume", action="store_true")
     ap.add_argument("--seed", type=int, default=1337)
+    ap.add_argument("--tp-size", type=int, default=0, help="--parallel tp: ranks per tensor-parallel group (0 = all); the rest is data parallel (TP x DP mesh)")
     ap.add_argument("--device", default="auto", choices=["auto", "cuda", "cpu"])
     a = ap.parse_args(argv)
 
@@ -134,9 +135,16 @@ def main(argv=None) -> int:
         from .tp import TensorParallelContext
         from .tp_llama import TPLlama, TPLlamaTrainer
         cfg = LlamaConfig(max_seq_len=a.seq_len, vocab_pad_to=128, **MODELS[a.model])
-        model = TPLlama(cfg, TensorParallelContext(dev), seed=a.seed)
+        tp_size = a.tp_size or world
+        if world > 1 and tp_size != world:
+            from .tp_llama import tp_dp_mesh
+            tp_group, dp_group, _t, dp_index = tp_dp_mesh(tp_size)
+            model = TPLlama(cfg, TensorParallelContext(dev, tp_group), seed=a.seed, dp_group=dp_group)
+            data_rank, data_world = dp_index, world // tp_size          # every tensor-parallel group reads its own batches
+        else:
+            model = TPLlama(cfg, TensorParallelContext(dev), seed=a.seed)
+            data_rank, data_world = 0, 1
         trainer = TPLlamaTrainer(model, opt)
-        data_rank, data_world = 0, 1
     else:
         from .moe_llama import EPMoELlama, FlatAdamWTrainer, MoELlamaConfig
         cfg = MoELlamaConfig(n_layer=a.n_layer, n_head=a.n_head, n_kv_head=a.n_kv_head, d_model=a.d_model, n_experts=a.experts, top_k=a.top_k,
@@ -173,7 +181,7 @@ def main(argv=None) -> int:
                 sampler.seek(start)
                 batches = iter(sampler)
             _emit(rank, event="resumed", step=start)
-    tokens_per_step = a.batch_size * a.seq_len * (1 if a.parallel == "tp" else world)
+    tokens_per_step = a.batch_size * a.seq_len * data_world
     t0 = last = time.perf_counter()
     loss = None
     for step in range(start + 1, a.max_steps + 1):

@@ -157,6 +157,7 @@ def resident_inference_capabilities() -> dict:
             "cuda_graph_decode": True, "on_device_sampling": ["greedy", "temperature", "top_k", "top_p"],
             # the engine executes bf16 weights only: K-quant / NF4 checkpoints are dequantised at load time
             # (``quant.kquant`` / ``checkpoint.gguf``); the packed-weight kernels are not wired into it
+            "block_verification": True, "hidden_state_taps": True, "gpt2_mlp_activations": sorted(EngineConfig.MLP_ACTIVATION_IDS),
             "quantized_weights": [], "weight_dtypes": ["bf16"], "dequantised_at_load": ["Q4_K", "Q5_K", "Q6_K", "NF4"]}
 
 
