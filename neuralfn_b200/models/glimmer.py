@@ -16,6 +16,13 @@ and the named-tensor checkpoints apply unchanged. Objectives (``GlimmerEngine.ob
 * ``"reward_model"``  Bradley-Terry preference loss on a scalar head (``GlimmerConfig.reward_head=True`` adds the
   ``reward_head`` vector): the reward of a sequence is <final-norm hidden state at its last counted position, head>;
   the vocabulary head is skipped in both passes;
+* ``"ppo"``  the clipped-surrogate UPDATE on a stored rollout (``GlimmerConfig.value_head=True`` adds the ``value_head``
+  vector; ``set_ppo_batch`` gives old log-probabilities, advantages, returns and old values per row): the new
+  log-probabilities are the negated row losses of the cross-entropy kernel, values are <final-norm hidden state, head>,
+  the policy term's gradient goes back through the same kernel as a per-row scale, the value term's through the
+  final norm. Same formulas as ``tensor.stages_losses._ppo_terms`` / ``masked_ppo_clipped_loss`` (masked means, advantage
+  normalisation); no entropy bonus (the kernel does not form the full-distribution entropy gradient). Rollouts and
+  advantages come from the caller (``tensor.ppo`` has the samplers and GAE);
 * ``"dpo"``  pairwise preference loss over (chosen, rejected) halves of the batch against frozen
   reference log-probabilities (``set_reference_logps``): the sequence log-probabilities come from the
   cross-entropy kernel's row losses, and the backward pass re-runs that kernel with a per-row gradient
@@ -74,6 +81,10 @@ class GlimmerConfig:
     vocab_pad_to: int = 128
     dpo_beta: float = 0.1
     reward_head: bool = False
+    value_head: bool = False
+    ppo_clip: float = 0.2
+    ppo_vf_coef: float = 0.5
+    ppo_normalize_advantages: bool = True
     lora_rank: int = 0                      # > 0: train low-rank adapters over frozen base weights
     lora_alpha: float = 32.0
     lora_targets: tuple = ("wqkvg", "wo", "w_gate_up", "w_down")
@@ -158,8 +169,8 @@ def glimmer_lora_specs(cfg: GlimmerConfig) -> list[ParamSpec]:
             out_dim, in_dim = shapes[f"layers.{l}.{t}"]
             specs += [ParamSpec(f"layers.{l}.{t}.lora_a", (cfg.lora_rank, in_dim), True, "lora_a"),
                       ParamSpec(f"layers.{l}.{t}.lora_b", (out_dim, cfg.lora_rank), True, "zeros")]
-    if cfg.reward_head and cfg.pp_last:
-        specs.append(ParamSpec("reward_head", (cfg.d_model,), False, "normal"))
+    if cfg.pp_last:
+        specs += [ParamSpec(n, (cfg.d_model,), False, "normal") for n, on in (("reward_head", cfg.reward_head), ("value_head", cfg.value_head)) if on]
     return specs
 
 
@@ -174,8 +185,8 @@ def glimmer_param_specs(cfg: GlimmerConfig) -> list[ParamSpec]:
                   ParamSpec(p + "w_down", (C, Fd), True, "resid"), ParamSpec(p + "post_mlp_norm", (C,), False, "zeros")]
     if cfg.pp_last:
         specs += [ParamSpec("norm", (C,), False, "ones"), ParamSpec("lm_head", (Vp, C), True, "normal")]
-        if cfg.reward_head and cfg.lora_rank == 0:
-            specs.append(ParamSpec("reward_head", (C,), False, "normal"))
+        if cfg.lora_rank == 0:
+            specs += [ParamSpec(n, (C,), False, "normal") for n, on in (("reward_head", cfg.reward_head), ("value_head", cfg.value_head)) if on]
     return specs
 
 
@@ -241,7 +252,7 @@ def glimmer_reference_loss(cfg: GlimmerConfig, p: dict[str, torch.Tensor], token
 
 # ------------------------------------------------------------------------------- engine --
 class GlimmerEngine:
-    OBJECTIVES = ("ar", "sft", "dpo", "reward_model")
+    OBJECTIVES = ("ar", "sft", "dpo", "reward_model", "ppo")
 
     def __init__(self, cfg: GlimmerConfig, layout: FlatLayout, params: torch.Tensor, grads: torch.Tensor, batch: int, seq: int) -> None:
         from ..ops import infer as I
@@ -307,6 +318,9 @@ class GlimmerEngine:
         self.ref_logps = torch.zeros(batch, device=dev, dtype=f32)  # DPO: frozen reference sequence log-probabilities
         self.seq_logps = torch.zeros(batch, device=dev, dtype=f32)
         self.dpo_stats = torch.zeros(3, device=dev, dtype=f32)      # loss, reward accuracy, reward margin
+        self.ppo_in = torch.zeros(4, N, device=dev, dtype=f32)      # rollout: old log-probabilities, advantages, returns, old values
+        self.ppo_stats = torch.zeros(4, device=dev, dtype=f32)      # policy loss, value loss, clipped fraction, approximate KL
+        self.values = torch.zeros(N, device=dev, dtype=f32)
         self.timer = None
 
     # --------------------------------------------------------------------------- inputs --
@@ -321,6 +335,8 @@ class GlimmerEngine:
             raise ValueError("preference batches hold (chosen, rejected) pairs: the batch size must be even")
         if objective == "reward_model" and not self.cfg.reward_head:
             raise ValueError("the reward_model objective needs GlimmerConfig(reward_head=True)")
+        if objective == "ppo" and not self.cfg.value_head:
+            raise ValueError("the ppo objective needs GlimmerConfig(value_head=True)")
         self.objective = objective
 
     def set_loss_mask(self, mask: torch.Tensor) -> None:
@@ -383,6 +399,11 @@ class GlimmerEngine:
         """Gradient slot of a base tensor: None (= not computed) when only adapters train."""
         return None if self.lora else self.g[name]
 
+    def set_ppo_batch(self, logp_old: torch.Tensor, advantages: torch.Tensor, returns: torch.Tensor, value_old: torch.Tensor) -> None:
+        """Per-row rollout records [B, T] (rows that do not count are masked by ``set_loss_mask``)."""
+        for i, t in enumerate((logp_old, advantages, returns, value_old)):
+            self.ppo_in[i].copy_(t.reshape(-1).to(self.ppo_in.dtype), non_blocking=True)
+
     def _views(self, t):
         cfg = self.cfg
         q_end, k_end = cfg.n_head * cfg.head_dim, (cfg.n_head + cfg.n_kv_head) * cfg.head_dim
@@ -435,6 +456,8 @@ class GlimmerEngine:
         K.norm_forward(x, p["norm"], None, eps=cfg.norm_eps, out=self.nf, rstd=self.rf, **rms)
         if self.objective == "reward_model":
             return self._reward_loss()
+        if self.objective == "ppo":
+            torch.mv(self.nf.float(), p["value_head"].float(), out=self.values)
         if cfg.logit_softcap > 0:
             gemm(self.nf, p["lm_head"], act="tanh_cap", act_param=cfg.logit_softcap, alpha=cfg.output_multiplier, out=self.logits)
         else:
@@ -457,6 +480,8 @@ class GlimmerEngine:
             torch.div(self.loss_mask, self.loss_mask.sum().clamp(min=1.0), out=self.row_scale)
             self._ce(compute_grad, 1.0 if grad_scale is None else grad_scale * N, 1.0, self.row_scale)
             return self.loss
+        if self.objective == "ppo":
+            return self._ppo_loss(compute_grad, grad_scale)
         # DPO: pass 1 leaves the logits intact and yields the row losses = -log p(target)
         self._ce(False, 1.0, 1.0, None, z=0.0)
         half = self.B // 2
@@ -476,6 +501,40 @@ class GlimmerEngine:
             keep = self.loss.clone()
             self._ce(True, 1.0 if grad_scale is None else grad_scale * N, 1.0, self.row_scale, z=0.0)
             self.loss.copy_(keep)                                   # the kernel's own mean is not the DPO loss
+        return self.loss
+
+    def _ppo_loss(self, compute_grad: bool, grad_scale: float | None) -> torch.Tensor:
+        """Clipped surrogate + clipped value loss over the counted rows; leaves d loss / d logits in the logits buffer and
+        d loss / d value per row in ``self._d_value`` when ``compute_grad``."""
+        cfg, N = self.cfg, self.B * self.T
+        self._ce(False, 1.0, 1.0, None, z=0.0)                      # row losses = -log p(action)
+        logp, (logp_old, adv, ret, v_old) = -self.row_loss, self.ppo_in
+        m, v, c = self.loss_mask, self.values, cfg.ppo_clip
+        denom = m.sum().clamp(min=1.0)
+        if cfg.ppo_normalize_advantages:
+            mean = (adv * m).sum() / denom
+            adv = (adv - mean) * torch.rsqrt((((adv - mean) ** 2) * m).sum() / denom + 1e-8)
+        ratio = torch.exp(logp - logp_old)
+        clipped = ratio.clamp(1.0 - c, 1.0 + c)
+        unclipped_active = (ratio * adv <= clipped * adv)
+        policy = -torch.minimum(ratio * adv, clipped * adv)
+        v_clip = v_old + (v - v_old).clamp(-c, c)
+        first = (v - ret) ** 2 >= (v_clip - ret) ** 2
+        value = 0.5 * torch.where(first, (v - ret) ** 2, (v_clip - ret) ** 2)
+        st = self.ppo_stats
+        st[0], st[1] = (policy * m).sum() / denom, (value * m).sum() / denom
+        st[2] = ((~unclipped_active).float() * m).sum() / denom
+        st[3] = ((logp_old - logp) * m).sum() / denom
+        self.loss.copy_((st[0] + cfg.ppo_vf_coef * st[1]).reshape(1))
+        if compute_grad:
+            gs = 1.0 if grad_scale is None else grad_scale * N
+            # d policy / d logp = -A r where the unclipped branch is the minimum, else 0; log p = -(row loss)
+            torch.mul(torch.where(unclipped_active, adv * ratio, torch.zeros_like(adv)), m / denom, out=self.row_scale)
+            inside = ((v - v_old).abs() < c).to(v.dtype)
+            self._d_value = torch.where(first, v - ret, (v_clip - ret) * inside) * (cfg.ppo_vf_coef * gs) * m / denom
+            keep = self.loss.clone()
+            self._ce(True, gs, 1.0, self.row_scale, z=0.0)
+            self.loss.copy_(keep)
         return self.loss
 
     def _reward_rows(self) -> torch.Tensor:
@@ -504,6 +563,8 @@ class GlimmerEngine:
         self.d_n.zero_()
         self.d_n[rows] = (dr[:, None] * self.p["reward_head"].float()[None, :]).to(self.d_n.dtype)
         self.g["reward_head"].copy_((dr[:, None] * self.nf[rows].float()).sum(0))
+        if "value_head" in self.g:
+            self.g["value_head"].zero_()
         if not self.lora:
             self.g["lm_head"].zero_()
 
@@ -562,6 +623,12 @@ class GlimmerEngine:
                     gemm(self.logits, self.nf, a_mn=True, b_mn=True, alpha=mult, out=g["lm_head"])
                 if "reward_head" in g:
                     g["reward_head"].zero_()
+                if self.objective == "ppo":
+                    # the value head reads the same final-norm rows: its gradient joins theirs
+                    self.d_n.add_((self._d_value[:, None] * p["value_head"].float()[None, :]).to(self.d_n.dtype))
+                    g["value_head"].copy_(torch.mv(self.nf.float().t(), self._d_value))
+                elif "value_head" in g:
+                    g["value_head"].zero_()
             x_last = self.acts[(len(self.layers) - 1) % len(self.acts)]["x2"] if self.acts else self.x0
             K.norm_backward(self.d_n, x_last, p["norm"], None, self.rf, self._gw("norm"), None, sc, out=dx, **rms)
         k, L = len(self.acts), len(self.layers)

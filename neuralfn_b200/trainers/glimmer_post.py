@@ -1,5 +1,5 @@
-"""Post-training of the native Glimmer engine: response-only SFT, pairwise DPO and the Bradley-Terry reward model
-from prepared record shards, on the dense trainer's step (sharded AdamW over peer memory, CUDA-graph replay).
+"""Post-training of the native Glimmer engine: response-only SFT, pairwise DPO, the Bradley-Terry reward model and PPO
+(rollouts sampled with the engine's own forward pass, clipped-surrogate updates on the native step), from prepared record shards, on the dense trainer's step (sharded AdamW over peer memory, CUDA-graph replay).
 
 SFT feeds each batch's loss mask to the engine; the step is otherwise the pre-training step. DPO stacks
 every batch as (chosen rows, rejected rows), so one forward / backward covers the pair. The frozen
@@ -26,13 +26,15 @@ __all__ = ["GlimmerPostTrainer"]
 class GlimmerPostTrainer:
     def __init__(self, cfg: GlimmerConfig, batch: int, seq: int, objective: str, optim: AdamWConfig | None = None, *, seed: int = 1337,
                  use_cuda_graph: bool = True, group=None) -> None:
-        if objective not in ("sft", "dpo", "reward_model"):
-            raise ValueError("objective must be 'sft', 'dpo' or 'reward_model' (pre-training uses DenseGPTTrainer directly)")
+        if objective not in ("sft", "dpo", "reward_model", "ppo"):
+            raise ValueError("objective must be 'sft', 'dpo', 'reward_model' or 'ppo' (pre-training uses DenseGPTTrainer directly)")
+        from dataclasses import replace
         if objective == "reward_model" and not cfg.reward_head:
-            from dataclasses import replace
             cfg = replace(cfg, reward_head=True)
+        if objective == "ppo" and not cfg.value_head:
+            cfg = replace(cfg, value_head=True)
         self.objective, self.pairs = objective, batch
-        rows = batch if objective == "sft" else 2 * batch
+        rows = batch if objective in ("sft", "ppo") else 2 * batch
         self.trainer = DenseGPTTrainer(cfg, rows, seq, optim, seed=seed, use_cuda_graph=use_cuda_graph, group=group)
         self.engine = self.trainer.engine
         self.engine.set_objective(objective)
@@ -64,6 +66,70 @@ class GlimmerPostTrainer:
         self._h_stats.copy_(self.engine.dpo_stats, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return {"loss": float(self._h_stats[0]), "reward_accuracy": float(self._h_stats[1]), "reward_margin": float(self._h_stats[2])}
+
+    # ---------------------------------------------------------------------------------- PPO --
+    @torch.no_grad()
+    def _policy_logits(self, ids: torch.Tensor) -> torch.Tensor:
+        """Logits [B, L, V] of a batch of equal-length prefixes (right-padded to the engine's sequence length; causal
+        attention makes the padding invisible to the positions that are read)."""
+        eng, L = self.engine, ids.shape[1]
+        tok = torch.zeros(eng.B, eng.T, dtype=torch.int32, device=ids.device)
+        tok[:, :L] = ids
+        eng.tokens.copy_(tok.reshape(-1))
+        keep, eng.objective = eng.objective, "ar"
+        eng.forward(compute_grad_logits=False)
+        eng.objective = keep
+        return eng.logits_view()[:, :L].float()
+
+    @torch.no_grad()
+    def ppo_rollout(self, prompts: torch.Tensor, reward, *, max_new_tokens: int = 16, temperature: float = 1.0, top_k: int = 0,
+                    gamma: float = 1.0, gae_lambda: float = 0.95, eos_token_id: int | None = None, pad_token_id: int = 0,
+                    generator: torch.Generator | None = None) -> dict:
+        """Samples continuations of ``prompts`` [B, P] with the current policy, scores them with ``reward(ids, P) -> [B]``
+        (added at the last response token) and returns the per-row rollout the ``ppo`` objective consumes."""
+        from ..tensor.ppo import gae_advantages, sample_continuations
+        eng = self.engine
+        dev = self.trainer.device
+        prompts = prompts.to(dev)
+        B, P = prompts.shape
+        if B != eng.B or P + max_new_tokens > eng.T + 1:
+            raise ValueError("prompts must fill the trainer's batch and leave room for the rollout inside its sequence length")
+        ids, mask = sample_continuations(self._policy_logits, prompts, max_new_tokens, temperature, top_k, generator, eos_token_id, pad_token_id)
+        L = ids.shape[1] - 1                                            # rows: position j predicts token j + 1
+        tok = torch.zeros(B, eng.T, dtype=torch.int32, device=dev)
+        tgt = torch.zeros_like(tok)
+        tok[:, :L], tgt[:, :L] = ids[:, :-1], ids[:, 1:]
+        row_mask = torch.zeros(B, eng.T, device=dev)
+        row_mask[:, P - 1:L] = mask
+        eng.set_batch(tok, tgt)
+        eng.set_loss_mask(row_mask)
+        eng.set_ppo_batch(*(torch.zeros(B, eng.T, device=dev) for _ in range(4)))
+        eng.forward(compute_grad_logits=False)                           # the ppo objective fills row losses and values
+        logp_old, values = (-eng.row_loss).view(B, eng.T).clone(), eng.values.view(B, eng.T).clone()
+        rewards = torch.zeros(B, max_new_tokens, device=dev)
+        last = (mask.sum(1).long() - 1).clamp(min=0)
+        score = reward(ids, P).float().to(dev)
+        rewards[torch.arange(B, device=dev), last] += score
+        adv, ret = gae_advantages(rewards, values[:, P - 1:L] * mask, mask, gamma, gae_lambda)
+        full = lambda t: torch.nn.functional.pad(t, (P - 1, eng.T - L))  # noqa: E731
+        return {"tokens": tok, "targets": tgt, "mask": row_mask, "logp_old": logp_old, "value_old": values, "advantages": full(adv),
+                "returns": full(ret), "score": score, "ids": ids}
+
+    def ppo_update(self, rollout: dict) -> dict:
+        """One optimizer step of the clipped surrogate on a stored rollout."""
+        eng = self.engine
+        eng.set_loss_mask(rollout["mask"])
+        eng.set_ppo_batch(rollout["logp_old"], rollout["advantages"], rollout["returns"], rollout["value_old"])
+        self.trainer.train_step(rollout["tokens"], rollout["targets"], return_loss=False)
+        stats = eng.ppo_stats.tolist()
+        return {"policy_loss": stats[0], "value_loss": stats[1], "clip_fraction": stats[2], "approx_kl": stats[3]}
+
+    def ppo_step(self, prompts: torch.Tensor, reward, *, epochs: int = 2, **rollout_kw) -> dict:
+        roll = self.ppo_rollout(prompts, reward, **rollout_kw)
+        out = {}
+        for _ in range(max(1, epochs)):
+            out = self.ppo_update(roll)
+        return {**out, "mean_score": float(roll["score"].mean())}
 
     # ---------------------------------------------------------------------------------- run --
     def fit(self, records: str, steps: int, *, split: str = "train", allow_train_as_val: bool = True, log_every: int = 0) -> dict:

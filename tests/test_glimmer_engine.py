@@ -54,7 +54,7 @@ def test_config_from_the_benchmark_spec_and_layer_kinds():
     assert names[0] == "tok_embeddings" and names[-1] == "lm_head" and "layers.47.post_mlp_norm" in names
     with pytest.raises(ValueError):
         from neuralfn_b200.models.glimmer import GlimmerEngine
-        GlimmerEngine.set_objective(object.__new__(GlimmerEngine), "ppo")
+        GlimmerEngine.set_objective(object.__new__(GlimmerEngine), "grpo")
 
 
 def _setup(**kw):
@@ -226,6 +226,51 @@ def test_reward_model_objective_matches_autograd(kernel_lib):
 
 
 @pytest.mark.gpu
+def test_ppo_update_objective_matches_autograd(kernel_lib):
+    from neuralfn_b200.models.glimmer import glimmer_reference_loss
+    from neuralfn_b200.tensor.stages_losses import _ppo_terms
+    cfg, layout, params, grads, eng, tok, tgt = _setup(value_head=True, z_loss=0.0)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    mask = torch.zeros(4, 128, device="cuda")
+    mask[:, 30:110] = 1
+    # a stored rollout near the current policy: old log-probabilities a little off, so some ratios leave the clip range
+    eng.set_objective("ppo")
+    eng.set_loss_mask(mask)
+    eng.forward(compute_grad_logits=False)
+    logp_now = (-eng.row_loss).view(4, 128).clone()
+    logp_old = logp_now + 0.3 * torch.randn(4, 128, device="cuda", generator=g)
+    adv = torch.randn(4, 128, device="cuda", generator=g)
+    ret = torch.randn(4, 128, device="cuda", generator=g)
+    v_old = eng.values.view(4, 128).clone() + 0.3 * torch.randn(4, 128, device="cuda", generator=g)
+    eng.set_ppo_batch(logp_old, adv, ret, v_old)
+    loss = eng.forward()
+    eng.backward()
+    stats = eng.ppo_stats.clone()
+    assert 0.05 < float(stats[2]) < 0.95                      # both branches of the clipped surrogate occur
+    ref_p = {k: v.float().clone().requires_grad_(True) for k, v in layout.views(params).items()}
+    hidden = []
+    _, logits, _ = glimmer_reference_loss(cfg, ref_p, tok, tgt, hidden_out=hidden)
+    lp = torch.log_softmax(logits.float(), -1).gather(-1, tgt.long()[..., None]).squeeze(-1)
+    v = hidden[0] @ ref_p["value_head"]
+    denom = mask.sum()
+    mean = (adv * mask).sum() / denom
+    adv_n = (adv - mean) / torch.sqrt((((adv - mean) ** 2) * mask).sum() / denom + 1e-8)
+    pol, val = _ppo_terms(lp, logp_old, adv_n, v, v_old, ret, cfg.ppo_clip)
+    ref_loss = (pol * mask).sum() / denom + cfg.ppo_vf_coef * (val * mask).sum() / denom
+    ref_loss.backward()
+    assert abs(loss.item() - ref_loss.item()) < 0.03 * max(1.0, abs(ref_loss.item()))
+    assert abs(float(stats[0]) - float((pol * mask).sum() / denom)) < 0.03 and abs(float(stats[1]) - float((val * mask).sum() / denom)) < 0.03
+    # rows whose ratio sits near a clip boundary may take the other branch under bf16: compare direction and size
+    gv = layout.views(grads)
+    for name, ref in ref_p.items():
+        gg, r = gv[name].float(), ref.grad
+        if r.norm() < 1e-6:
+            continue
+        cos = float((gg * r).sum() / (gg.norm() * r.norm() + 1e-20))
+        assert cos > 0.97 and abs(float(gg.norm() / r.norm()) - 1.0) < 0.08, (name, cos, float(gg.norm() / r.norm()))
+
+
+@pytest.mark.gpu
 def test_lora_adapters_match_autograd_on_the_merged_weights(kernel_lib):
     from neuralfn_b200.models.glimmer import GlimmerEngine, glimmer_reference_loss
     from neuralfn_b200.models.gpt2 import FlatLayout
@@ -277,3 +322,28 @@ def test_dense_trainer_drives_the_glimmer_engine(kernel_lib):
     lt.check_status()
     assert abs(ll[0] - losses[-1]) < 0.35 and ll[-1] < ll[0] - 0.02, (ll, losses[-1])
     assert lt.layout.n_total < tr.layout.n_total // 4
+
+
+@pytest.mark.gpu
+def test_native_ppo_loop_raises_the_rewarded_token_frequency(kernel_lib):
+    """Rollouts with the engine's own forward pass, GAE, clipped-surrogate steps on the native trainer: the policy learns to
+    emit the token the reward counts."""
+    from neuralfn_b200.parallel.dp import AdamWConfig
+    from neuralfn_b200.trainers.glimmer_post import GlimmerPostTrainer
+    cfg = _cfg(vocab_size=64, n_layer=2, max_seq_len=128)
+    post = GlimmerPostTrainer(cfg, 8, 128, "ppo", AdamWConfig(lr=3e-3, warmup_steps=1, total_steps=100, weight_decay=0.0, schedule="constant"),
+                              seed=1, use_cuda_graph=False)
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    prompts = torch.randint(0, 64, (8, 6), device="cuda", generator=gen)
+    lucky = 7
+
+    def reward(ids, P):
+        return (ids[:, P:] == lucky).float().mean(1)
+
+    scores = []
+    for _ in range(12):
+        out = post.ppo_step(prompts, reward, epochs=2, max_new_tokens=12, temperature=1.0, generator=gen)
+        scores.append(out["mean_score"])
+        assert all(v == v for v in out.values())                      # no NaN
+    post.trainer.check_status()
+    assert sum(scores[-3:]) / 3 > sum(scores[:3]) / 3 + 0.05, scores
