@@ -336,6 +336,7 @@ class NativeInferenceModel:
         self.proposer_factory = proposer_factory
         self._free = list(range(engine.config.max_batch))[::-1]
         self._sessions: dict[int, "NativeInferenceSession"] = {}
+        self._lazy: list["NativeInferenceSession"] = []       # forks that have not needed a slot of their own yet
         self._lock = threading.RLock()
         self._closed = False
         self._counters = {"prefill_tokens": 0, "decode_tokens": 0, "sessions_created": 0, "forks": 0}
@@ -407,38 +408,109 @@ class NativeInferenceModel:
             self._counters["sessions_created"] += 1
             return s
 
-    def fork_session(self, session: "NativeInferenceSession", prefix_tokens: int | None = None, seed: int | None = None) -> "NativeInferenceSession":
-        """A new session that starts with the first ``prefix_tokens`` cached tokens of
-        ``session`` (device-to-device KV copy; the two are independent afterwards). The child
-        caches all but the last prefix token and keeps that one pending: running it again is
-        what gives the child valid logits for its own next token."""
+    def fork_session(self, session: "NativeInferenceSession", prefix_tokens: int | None = None, seed: int | None = None, *,
+                     lazy: bool = True) -> "NativeInferenceSession":
+        """A new session that starts with the first ``prefix_tokens`` cached tokens of ``session``. The child caches all but
+        the last prefix token and keeps that one pending: running it again is what gives the child valid logits for its own
+        next token.
+
+        Copy-on-write at whole-prefix granularity: the child is created WITHOUT a cache slot and reads the parent's rows; the
+        device-to-device copy happens when the child first needs to write (any prefill / decode / logits call), or when the
+        parent is about to invalidate the shared rows (truncate below them, reset, close, or any append while the engine has
+        sliding-window caches that could wrap). A parent that closes hands its slot to its first unused child instead of copying.
+        So a fork costs nothing until it is used, and more forks than cache slots may exist. ``lazy=False`` copies at once."""
         with self._lock:
             self._require_owned(session)
             n = session.cached_tokens if prefix_tokens is None else int(prefix_tokens)
             if n < 0 or n > session.cached_tokens:
                 raise InferenceError("fork prefix longer than the cached tokens of the source session")
-            child = self.create_session(seed)
-            try:
-                if n > 1:
-                    self.engine.fork(session.slot, child.slot, n - 1)
-            except Exception:
-                child.close()
-                raise
+            self._open()
+            child = NativeInferenceSession(self, None, seed)
             child._tokens = list(session._tokens[:max(n - 1, 0)])
             child._pending = session._tokens[n - 1] if n >= 1 else None
             self._counters["forks"] += 1
+            self._counters["sessions_created"] += 1
+            if len(child._tokens) > 0:
+                root = session._origin[0] if session._slot is None else session      # an unused fork forwards to ITS source
+                child._origin = (root, len(child._tokens))
+                root._dependants.append(child)
+            self._lazy.append(child)
+            if not lazy:
+                child.slot  # noqa: B018 - materialises
             return child
 
+    def _materialise(self, child: "NativeInferenceSession") -> int:
+        """Gives an unused fork its own slot and copies the shared rows into it."""
+        with self._lock:
+            if child._slot is not None:
+                return child._slot
+            if child.closed:
+                raise InferenceError("the session is closed")
+            if not self._free:
+                raise InferenceError("every session slot is in use")
+            slot = self._free.pop()
+            origin = child._origin
+            try:
+                if origin is not None:
+                    self.engine.fork(origin[0].slot, slot, origin[1])
+                    self._counters["fork_copies"] = self._counters.get("fork_copies", 0) + 1
+            except Exception:
+                self._free.append(slot)
+                raise
+            if origin is not None and child in origin[0]._dependants:
+                origin[0]._dependants.remove(child)
+            child._origin, child._slot = None, slot
+            if child in self._lazy:
+                self._lazy.remove(child)
+            self._sessions[slot] = child
+            return slot
+
+    def _detach_dependants(self, session: "NativeInferenceSession", keep_rows: int | None = None, *, closing: bool = False) -> None:
+        """Before ``session`` invalidates cached rows: unused forks that read rows past ``keep_rows`` (all of them when None)
+        get their own copy. When the session is closing, the fork that reads the most rows adopts its slot instead (the slot
+        is shortened to that prefix, nothing is copied) and the other forks read from the adopter from then on."""
+        with self._lock:
+            if closing and session._dependants and session._slot is not None and self._sessions.get(session._slot) is session:
+                heir = max(session._dependants, key=lambda c: c._origin[1])
+                slot, rows = session._slot, heir._origin[1]
+                if rows < self.engine.slot_length(slot):
+                    self.engine.truncate(slot, rows)
+                for other in session._dependants:
+                    if other is not heir:
+                        other._origin = (heir, other._origin[1])
+                        heir._dependants.append(other)
+                session._dependants = []
+                heir._origin, heir._slot = None, slot
+                self._lazy.remove(heir)
+                self._sessions[slot] = heir
+                session._slot_given_away = True
+                self._counters["fork_adoptions"] = self._counters.get("fork_adoptions", 0) + 1
+                return
+            for child in list(session._dependants):
+                if keep_rows is not None and child._origin[1] <= keep_rows:
+                    continue
+                self._materialise(child)
+
     def _require_owned(self, session: "NativeInferenceSession") -> None:
-        if self._sessions.get(session.slot) is not session or session.closed:
+        if session.closed or session.model is not self or (session._slot is None and session not in self._lazy) or \
+                (session._slot is not None and self._sessions.get(session._slot) is not session):
             raise InferenceError("the session does not belong to this model (or is closed)")
 
     def _discard(self, session: "NativeInferenceSession") -> None:
         with self._lock:
-            if self._sessions.get(session.slot) is session:
-                del self._sessions[session.slot]
-                self.engine.release(session.slot)
-                self._free.append(session.slot)
+            self._detach_dependants(session, closing=True)
+            if session._slot is None:
+                if session._origin is not None and session in session._origin[0]._dependants:
+                    session._origin[0]._dependants.remove(session)
+                if session in self._lazy:
+                    self._lazy.remove(session)
+                return
+            if getattr(session, "_slot_given_away", False):
+                return
+            if self._sessions.get(session._slot) is session:
+                del self._sessions[session._slot]
+                self.engine.release(session._slot)
+                self._free.append(session._slot)
 
     # convenience forwards (the reference exposes both spellings)
     def prefill(self, session, token_ids):
@@ -461,7 +533,8 @@ class NativeInferenceModel:
 
     def stats(self) -> dict[str, Any]:
         with self._lock:
-            return {**self._counters, "sessions_open": len(self._sessions), "session_slots": self.engine.config.max_batch,
+            return {**self._counters, "sessions_open": len(self._sessions) + len(self._lazy), "unused_forks": len(self._lazy),
+                    "session_slots": self.engine.config.max_batch,
                     "device_bytes": self.engine.device_bytes, "kernel_launches": self.engine.launches,
                     "sessions": {slot: s.stats() for slot, s in self._sessions.items()}}
 
@@ -469,7 +542,7 @@ class NativeInferenceModel:
         with self._lock:
             if self._closed:
                 return
-            for s in list(self._sessions.values()):
+            for s in list(self._lazy) + list(self._sessions.values()):
                 s.close()
             self.engine.close()
             self._closed = True
@@ -485,8 +558,10 @@ class NativeInferenceSession:
     """One sequence. ``token_ids`` is everything the caller has seen (prompt + emitted tokens);
     the KV cache may lag it by the single pending token."""
 
-    def __init__(self, model: NativeInferenceModel, slot: int, seed: int | None) -> None:
-        self.model, self.slot, self.seed = model, slot, seed
+    def __init__(self, model: NativeInferenceModel, slot: int | None, seed: int | None) -> None:
+        self.model, self._slot, self.seed = model, slot, seed
+        self._origin: tuple["NativeInferenceSession", int] | None = None   # an unused fork: (session whose rows it reads, how many)
+        self._dependants: list["NativeInferenceSession"] = []              # unused forks that read this session's rows
         self._tokens: list[int] = []      # tokens in the KV cache
         self._pending: int | None = None  # seen by the caller but not cached
         self._cancel = threading.Event()
@@ -498,6 +573,21 @@ class NativeInferenceSession:
         self._next_greedy: int | None = None  # the engine's own pick after the last cached token
 
     # -- state -----------------------------------------------------------------------------
+    @property
+    def slot(self) -> int:
+        """The engine slot; an unused fork gets one (and its copy of the shared rows) on first access."""
+        return self._slot if self._slot is not None else self.model._materialise(self)
+
+    @property
+    def shares_cache(self) -> bool:
+        """True while this fork still reads its source's rows (nothing has been copied)."""
+        return self._slot is None and self._origin is not None
+
+    def _before_append(self) -> None:
+        """Appends keep every earlier row, except where a sliding-window cache can wrap over them."""
+        if self._dependants and self.model.engine.config.window > 0:
+            self.model._detach_dependants(self)
+
     @property
     def token_ids(self) -> tuple[int, ...]:
         return tuple(self._tokens) + (() if self._pending is None else (self._pending,))
@@ -522,6 +612,7 @@ class NativeInferenceSession:
     def _advance(self, token: int, sampling: Sampling | None) -> int:
         """Runs one token through the engine (appending it to the cache); returns the engine's pick."""
         eng = self.model.engine
+        self._before_append()
         if not self._tokens:
             return eng.prefill(self.slot, [token], sampling)
         return eng.decode({self.slot: token}, sampling)[self.slot]
@@ -549,6 +640,7 @@ class NativeInferenceSession:
         t0 = time.perf_counter()
         with self.model._lock:
             self._flush_pending()
+            self._before_append()
             if not self._tokens:
                 self._next_greedy = eng.prefill(self.slot, ids)
             else:
@@ -577,6 +669,7 @@ class NativeInferenceSession:
             every = list(self.token_ids)
             if n == len(every):
                 return
+            self.model._detach_dependants(self, keep_rows=max(n - 1, 0))
             if n == 0:
                 self.model.engine.release(self.slot)
                 self._tokens, self._pending, self._next_greedy = [], None, None
@@ -590,6 +683,7 @@ class NativeInferenceSession:
     def reset(self) -> None:
         self._usable()
         with self.model._lock:
+            self.model._detach_dependants(self)
             self.model.engine.release(self.slot)
             self._tokens, self._pending, self._next_greedy = [], None, None
             self._cancel.clear()
@@ -742,6 +836,7 @@ class NativeInferenceSession:
         budget = min(k, room - 1, eng.config.max_seq - 2 - len(self.token_ids), rows_cap - 1)
         props, q = proposer.propose(self.token_ids, budget) if budget > 0 else ([], None)
         props = [int(t) for t in props[:max(budget, 0)]]
+        self._before_append()
         block = [self._pending] + props
         picks = eng.verify({self.slot: block})[self.slot]
         st = self._stats

@@ -254,3 +254,62 @@ def test_dflash_proposer_keeps_greedy_output_and_counts_blocks():
         assert res.speculative_accepted_tokens >= 0.8 * res.speculative_proposed_tokens > 0, (res.speculative_accepted_tokens, res.speculative_proposed_tokens)
         assert res.speculative_target_rows < 24 + res.speculative_assistant_blocks and res.speculative_assistant_blocks <= 5
     model.close()
+
+
+def test_forks_copy_on_write():
+    """A fork takes no cache slot and copies nothing until it is used; the source's slot is handed over when it closes first."""
+    from neuralfn_b200.serving import GenerationConfig, NativeInferenceModel
+    _cfg, _w, eng = _engine(max_batch=2)
+    model = NativeInferenceModel(eng)
+    greedy = GenerationConfig(max_new_tokens=10, temperature=0.0)
+    src = model.create_session()
+    src.prefill(PROMPT)
+    want = src.decode(greedy).token_ids
+    n = len(PROMPT)
+    forks = [model.fork_session(src, n) for _ in range(5)]           # more forks than slots
+    st = model.stats()
+    assert st["unused_forks"] == 5 and st["forks"] == 5 and st.get("fork_copies", 0) == 0 and all(f.shares_cache for f in forks)
+    assert forks[0].token_ids == tuple(PROMPT) and forks[0].cached_tokens == n - 1
+    # first use: the rows are copied into the fork's own slot, and it continues exactly like the source did
+    got = forks[0].decode(greedy).token_ids
+    _same_up_to_ties(model, PROMPT, want, got)
+    assert not forks[0].shares_cache and model.stats()["fork_copies"] == 1 and model.stats()["unused_forks"] == 4
+    # both slots are taken now: a further fork cannot materialise, and says so
+    with pytest.raises(Exception, match="slot"):
+        forks[1].current_logits()
+    forks[0].close()
+    # the source appends without disturbing its forks (no sliding-window caches here), truncating below them detaches one first
+    src.decode(GenerationConfig(max_new_tokens=2, temperature=0.0))
+    assert all(f.shares_cache for f in forks[1:])
+    short = model.fork_session(src, 8)
+    with pytest.raises(Exception, match="slot"):
+        src.truncate(10)                                               # four forks read rows 10 .. 18 and only one slot is free: refused
+    assert len(src.token_ids) == n + 12                                # the source is untouched by the refusal
+    for f in forks[2:]:
+        f.close()
+    src.truncate(10)                                                   # the remaining long fork was given its own copy first
+    assert model.stats()["fork_copies"] == 2 and not forks[1].shares_cache and short.shares_cache
+    _same_up_to_ties(model, PROMPT, want, forks[1].decode(greedy).token_ids)
+    forks[1].close()
+    assert short.token_ids == tuple(PROMPT[:8]) and bool(torch.isfinite(short.current_logits()).all())
+    model.close()
+
+
+def test_closing_the_source_hands_its_slot_to_a_fork():
+    from neuralfn_b200.serving import GenerationConfig, NativeInferenceModel
+    _cfg, _w, eng = _engine(max_batch=1)
+    model = NativeInferenceModel(eng)
+    greedy = GenerationConfig(max_new_tokens=8, temperature=0.0)
+    src = model.create_session()
+    src.prefill(PROMPT)
+    want = src.decode(greedy).token_ids
+    a = model.fork_session(src, len(PROMPT))
+    b = model.fork_session(src, 12)
+    src.close()                                                        # the only slot goes to the fork with the longer prefix
+    st = model.stats()
+    assert st["fork_adoptions"] == 1 and st.get("fork_copies", 0) == 0 and not a.shares_cache and b.shares_cache
+    _same_up_to_ties(model, PROMPT, want, a.decode(greedy).token_ids)
+    a.close()                                                          # and on to the next one, shortened to its 11 cached rows
+    assert model.stats()["fork_adoptions"] == 2 and b.cached_tokens == 11
+    assert torch.isfinite(b.current_logits()).all()
+    model.close()
