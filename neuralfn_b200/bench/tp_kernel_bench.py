@@ -14,8 +14,9 @@ Each case runs ``iters`` times per implementation (``fused``: one kernel over pe
 collective and this framework's GEMM as two launches), timed with CUDA events on the launching stream
 after warm-up, maximum over ranks. The roofline time of a case is the larger of FLOPs / the measured GEMM
 peak and the bytes every GPU must receive over NVLink / the measured peer-copy rate (770 GB/s per
-direction); ``roofline_fraction`` is that time over the measured one. Inputs of successive iterations
-rotate through enough buffers to exceed the 126 MB L2 where the shapes allow it.
+direction); ``roofline_fraction`` is that time over the measured one. The GEMM operands of a case (64 - 470 MB with
+the output) are re-used between iterations. The all-reduce is timed twice: as eager calls (host-paced) and as 16 calls on
+two alternating buffers inside a replayed CUDA graph, which is how a decode step issues it.
 
 The reference has no tensor parallelism; the shapes are those of its Llama-3-8B template
 (``neuralfn/config.py`` ``llama3_8b`` geometry: d 4096, 32 / 8 heads, ffn 14336).
@@ -114,6 +115,33 @@ def main(argv=None) -> int:
                 part, sym = rnd(B, d), None
             ms = _time(lambda: ctx.allreduce_resid_norm(part, sym, resid=resid, norm_weight=nw, use_multicast=mc), a.iters * 10, a.warmup, dev)
             record("allreduce_resid_norm", f"{B}x{d}", vname, ms, 0.0, (W - 1) * B * d * 2)
+            if impl == "fused":
+                # the same call as a decode step issues it: K calls on two alternating buffers inside one CUDA graph, replayed
+                # (no host work between launches); the device-side epoch moves on by K before every replay
+                Kc = 16
+                part2, sym2 = ctx.partial_buffer(B, d)
+                part2.copy_(part)
+                bufs = ((part, sym), (part2, sym2))
+
+                def body():
+                    for i in range(Kc):
+                        ctx.allreduce_resid_norm(*bufs[i % 2], resid=resid, norm_weight=nw, use_multicast=mc)
+                body()
+                torch.cuda.synchronize(dev)
+                side = torch.cuda.Stream(dev)
+                side.wait_stream(torch.cuda.current_stream(dev))
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.stream(side):
+                    with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+                        body()
+                torch.cuda.current_stream(dev).wait_stream(side)
+                ctx.advance_epoch_on_device(-Kc)              # capture advanced the host epoch without running anything
+
+                def replay():
+                    ctx.advance_epoch_on_device(Kc)
+                    graph.replay()
+                ms = _time(replay, a.iters, a.warmup, dev) / Kc
+                record("allreduce_resid_norm", f"{B}x{d} (in a CUDA graph, per call)", vname, ms, 0.0, (W - 1) * B * d * 2)
     torch.cuda.synchronize(dev)
     status = _lib.status_read_reset()
     if rank == 0:

@@ -218,6 +218,8 @@ def _infer_artifact(a) -> int:
         return 0
     from ..serving import GenerationConfig, NativeInferenceModel, NativeModelLoadConfig, NGramProposer
     model = NativeInferenceModel.load(a.checkpoint, NativeModelLoadConfig(session_count=1, speculative_decoding=a.speculative_decoding))
+    if getattr(a, "companion_checkpoint", ""):
+        model.attach_dflash(a.companion_checkpoint)                    # a DFlash assistant exported by the distillation trainer
     if a.chat:
         from ..serving.chat import resolve_chat_renderer
         from .tui import InferTUI
@@ -230,7 +232,8 @@ def _infer_artifact(a) -> int:
         s.prefill(ids)
         cfg = GenerationConfig(max_new_tokens=a.max_new_tokens, temperature=a.temperature, top_k=a.top_k or None, top_p=a.top_p, seed=a.seed,
                                stop_token_ids=tuple(model.manifest.get("stop_token_ids", ())))
-        res = s.decode(cfg, proposer=NGramProposer() if a.speculative_decoding != "off" else None)
+        fallback = NGramProposer() if a.speculative_decoding != "off" and not getattr(a, "companion_checkpoint", "") else None
+        res = s.decode(cfg, proposer=fallback)
     print(json.dumps({"status": "ok", "text": res.text, "token_ids": list(res.token_ids), "finish_reason": res.finish_reason,
                       "prompt_tokens": res.prompt_tokens, "speculative": {"proposed": res.speculative_proposed_tokens,
                                                                           "accepted": res.speculative_accepted_tokens}, "stats": model.stats()}))
@@ -425,6 +428,7 @@ def build_parser() -> argparse.ArgumentParser:
     i.add_argument("--allow-unauthenticated-remote", action="store_true")
     i.add_argument("--state-db", default=None, help="SQLite file behind /v1/responses and /v1/conversations")
     i.add_argument("--speculative-decoding", choices=["off", "auto", "required"], default="auto")
+    i.add_argument("--companion-checkpoint", default="", help="artifact directories: DFlash assistant file (block-diffusion draft on the engine's hidden-state taps)")
     i.add_argument("--max-new-tokens", type=int, default=144)
     i.add_argument("--temperature", type=float, default=0.0)
     i.add_argument("--top-k", type=int, default=0)

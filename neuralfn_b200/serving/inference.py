@@ -368,6 +368,43 @@ class NativeInferenceModel:
         codec = load_text_codec(manifest.get("text_codec"), root)
         return cls(engine, codec=codec, manifest=manifest, artifact_root=root, load_config=lc, **kw)
 
+    def attach_dflash(self, assistant, *, target_tensors: dict[str, torch.Tensor] | None = None) -> None:
+        """Makes a DFlash (block-diffusion) draft the model's speculative proposer. ``assistant``: the file written by
+        ``DFlashDistillationTrainer.export_native_assistant`` (or a ``DFlashDraftModel``). Must be called before the first
+        decode step: the engine starts keeping the tapped hidden states from then on. ``target_tensors`` default to the
+        artifact's own weights (embedding table, final norm, head)."""
+        from ..tensor.dflash import DFlashConfig, DFlashDraftModel
+        dev = torch.device("cuda", self.engine.device)
+        if isinstance(assistant, (str, Path)):
+            from ..checkpoint.named import read_named_tensors
+            tensors, meta, _sha = read_named_tensors(assistant)
+            if meta.get("kind") != "dflash_assistant":
+                raise InferenceError(f"{assistant} is not a DFlash assistant file")
+            raw = dict(meta["config"])
+            raw["tap_layers"] = tuple(raw.get("tap_layers", ()))
+            cfg = DFlashConfig(**{k: v for k, v in raw.items() if k in DFlashConfig.__dataclass_fields__})
+            draft = DFlashDraftModel(cfg, self.engine.config.d_model)
+            draft.load_state_dict({k: v.float() for k, v in tensors.items()})
+        else:
+            draft = assistant
+        if target_tensors is None:
+            if self.artifact_root is None or not self.manifest:
+                raise InferenceError("attach_dflash needs target_tensors for a model that was not loaded from an artifact directory")
+            from ..checkpoint.named import read_named_tensors
+            target_tensors = read_named_tensors(self.artifact_root / self.manifest["weights"])[0]
+        c = self.engine.config
+        shaped = {k: (v.view(-1, c.d_model) if k in ("tok_embeddings", "lm_head") and v.dim() == 1 else v) for k, v in target_tensors.items()
+                  if k in ("tok_embeddings", "lm_head", "norm")}
+        embed, head = target_embed_and_head(c, shaped, dev)
+        self.engine.enable_taps(draft.cfg.tap_layers)
+        self._dflash = (draft.to(dev).to(torch.bfloat16), embed, head)
+
+    def dflash_proposer(self, session: "NativeInferenceSession") -> "DFlashProposer":
+        if getattr(self, "_dflash", None) is None:
+            raise InferenceError("no DFlash assistant is attached (attach_dflash)")
+        draft, embed, head = self._dflash
+        return DFlashProposer(self.engine, session.slot, draft, embed, head)
+
     @staticmethod
     def estimate_device_bytes(cfg: EngineConfig) -> int:
         """Weights + KV caches + activations of an engine with this configuration."""
@@ -723,6 +760,8 @@ class NativeInferenceSession:
         if not self._tokens and self._pending is None:
             raise InferenceError("prefill the session before decoding")
         spec_mode = self.model.load_config.speculative_decoding
+        if proposer is None and getattr(self.model, "_dflash", None) is not None and spec_mode != "off":
+            proposer = self.model.dflash_proposer(self)
         if proposer is None and self.model.proposer_factory is not None and spec_mode != "off":
             proposer = self.model.proposer_factory()
         if spec_mode == "required" and proposer is None:

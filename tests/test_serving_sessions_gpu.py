@@ -313,3 +313,30 @@ def test_closing_the_source_hands_its_slot_to_a_fork():
     assert model.stats()["fork_adoptions"] == 2 and b.cached_tokens == 11
     assert torch.isfinite(b.current_logits()).all()
     model.close()
+
+
+def test_artifact_with_a_dflash_assistant_file(tmp_path):
+    """An artifact directory plus an exported assistant file: `attach_dflash` wires taps, draft and the shared head, and
+    decoding uses the draft without being told to."""
+    from neuralfn_b200.serving import GenerationConfig, NativeInferenceModel, NativeModelLoadConfig, write_artifact
+    from neuralfn_b200.tensor.dflash import DFlashConfig, DFlashDistillationTrainer
+    cfg, w, eng = _engine(max_batch=1)
+    eng.close()
+    shaped = {k: (v.view(-1, cfg.d_model) if k in ("tok_embeddings", "lm_head") else v) for k, v in w.items()}
+    write_artifact(tmp_path / "art", cfg, shaped)
+    dcfg = DFlashConfig(d_model=64, n_layer=1, n_head=2, block_size=6, context_window=32, tap_layers=(1,), mask_token_id=0)
+    trainer = DFlashDistillationTrainer(dcfg, target=None, embed=None, lm_head=None, target_dim=cfg.d_model)
+    trainer.export_native_assistant(tmp_path / "assistant.nfnw")
+    greedy = GenerationConfig(max_new_tokens=12, temperature=0.0)
+    with NativeInferenceModel.load(tmp_path / "art", NativeModelLoadConfig(session_count=1, speculative_decoding="off")) as plain_model:
+        with plain_model.create_session() as s:
+            s.prefill(PROMPT)
+            plain = s.decode(greedy)
+    with NativeInferenceModel.load(tmp_path / "art", NativeModelLoadConfig(session_count=1)) as model:
+        model.attach_dflash(tmp_path / "assistant.nfnw")
+        assert model.engine.tap_layers == (1,)
+        with model.create_session() as s:
+            s.prefill(PROMPT)
+            res = s.decode(greedy)
+            assert res.speculative_assistant_blocks > 0 and res.speculative_proposed_tokens > 0
+            _same_up_to_ties(model, PROMPT, plain.token_ids, res.token_ids)
