@@ -231,9 +231,20 @@ class PipelineParallelTrainer:
                 if self.micro_batches > 1:
                     self._accumulate(accumulated)
                     accumulated += 1
-        self.inner.opt.stage_hyper()
-        self.inner.opt.launch_step()
-        self.inner.opt.step_count += 1
+        opt = self.inner.opt
+        opt.stage_hyper()
+        # clip by the norm of the WHOLE model's gradient: every stage contributes its squared norm (one scalar all-reduce),
+        # as the reference's pipeline step does (``muse_glimmer_native_train.cpp:2739-2808``: local norm^2 -> all-reduce -> clip)
+        K = opt.K
+        K.grad_clip_scale(opt.bufs.grads, opt.partial, opt.hyper, opt.clip)
+        sq = opt.clip[1:2].double() ** 2
+        dist.all_reduce(sq)
+        norm = sq.sqrt().float()
+        mx = opt.cfg.max_grad_norm
+        opt.clip[1:2] = norm
+        opt.clip[0:1] = torch.where(norm > mx, mx / (norm + 1e-6), torch.ones_like(norm)) if mx > 0 else torch.ones_like(norm)
+        K.adamw_flat(opt.master, opt.m, opt.v, opt.bufs.grads, opt.bufs.params, opt.layout.n_decay, opt.hyper, opt.clip)
+        opt.step_count += 1
         total /= self.micro_batches
         dist.broadcast(total, src=self.world - 1)
         return float(total.item())

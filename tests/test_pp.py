@@ -87,6 +87,6 @@ def test_two_stage_pipeline_matches_single_gpu(tmp_path, family):
     want = []
     for i in range(4):
         want.append(sum(ref.train_step(tok[i][m], tgt[i][m]) for m in range(MICRO)) / MICRO)
-    # per-stage gradient clipping vs global clipping differ slightly once the norm exceeds 1
+    # the stages clip by the whole model's gradient norm, like the single-GPU trainer
     assert max(abs(x - y) for x, y in zip(res[0][0], want)) < 0.05, (res[0][0], want)
     assert want[-1] < want[0] + 0.05          # four steps on random tokens: no divergence (progress is not the point here)
