@@ -70,6 +70,11 @@ long long nfn_engine_device_bytes(const nfn_engine* e);
 
 // Runs the prompt of `slot` (resets the slot first). Writes the sampled next token.
 int nfn_engine_prefill(nfn_engine* e, int slot, const int32_t* tokens, int n, const nfn_sampling* s, int32_t* next_token);
+// The same for a prompt given as its layer-0 input rows (bf16 [n][d_model], host or device memory): token embeddings after
+// the embedding norm, with rows replaced by projected media features where the prompt holds media placeholders.
+// Llama-family layouts only (the GPT-2 layout adds learned position embeddings inside the engine).
+int nfn_engine_prefill_rows(nfn_engine* e, int slot, const void* rows_bf16, int n, int rows_on_device, const nfn_sampling* s,
+                            int32_t* next_token);
 // One step for all slots: tokens_in[slot] is consumed for every slot with active[slot] != 0,
 // next_tokens[slot] receives its successor. per_slot (optional, max_batch entries) overrides `s`.
 int nfn_engine_decode(nfn_engine* e, const int32_t* tokens_in, const uint8_t* active, const nfn_sampling* s,

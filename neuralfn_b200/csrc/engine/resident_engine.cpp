@@ -539,6 +539,35 @@ int nfn_engine_release(nfn_engine* e, int slot) {
   return 0;
 }
 
+}  // extern "C"
+
+// layers, head on the last row, sampling and bookkeeping of a prompt whose layer-0 inputs sit in e->x
+static int run_prompt_rows(nfn_engine* e, int slot, int n, const nfn_sampling* s, int32_t* next_token, long long before) {
+  const nfn_engine_config& c = e->c;
+  if (forward_layers(*e, n, false, slot, nullptr)) return -1;
+  if (head(*e, n - 1, 1)) return -1;
+  float* rp = reinterpret_cast<float*>(e->h_io + e->io.row_params);
+  fill_params(*e, rp, 0, *s);
+  unsigned long long* off = reinterpret_cast<unsigned long long*>(e->h_io + e->io.offset);
+  *off = (s->seed << 20) ^ (++e->steps);
+  CU(cudaMemcpyAsync(e->d_io + e->io.row_params, rp, 12, cudaMemcpyHostToDevice, e->stream));
+  CU(cudaMemcpyAsync(e->d_io + e->io.offset, off, 8, cudaMemcpyHostToDevice, e->stream));
+  if (sample(*e, 1, reinterpret_cast<const float*>(e->d_io + e->io.row_params),
+             reinterpret_cast<const unsigned long long*>(e->d_io + e->io.offset), reinterpret_cast<int*>(e->d_io + e->io.out_tokens)))
+    return -1;
+  CU(cudaMemcpyAsync(e->h_io + e->io.out_tokens, e->d_io + e->io.out_tokens, 4, cudaMemcpyDeviceToHost, e->stream));
+  CU(cudaStreamSynchronize(e->stream));
+  *next_token = *reinterpret_cast<int*>(e->h_io + e->io.out_tokens);
+  e->len[slot] = n;
+  e->logit_row[slot] = 0;
+  e->logit_src[slot] = 0;
+  e->launches += nfn_launch_count() - before;
+  if (nfn_status_peek() != 0) return efail("engine_prefill: a kernel reported error code " + std::to_string(nfn_status_read_reset()));
+  return 0;
+}
+
+
+extern "C" {
 int nfn_engine_prefill(nfn_engine* e, int slot, const int32_t* tokens, int n, const nfn_sampling* s, int32_t* next_token) {
   if (!e || !tokens || !s || !next_token) return efail("engine_prefill: null argument");
   if (!e->finalized) return efail("engine_prefill: call nfn_engine_finalize first");
@@ -561,26 +590,20 @@ int nfn_engine_prefill(nfn_engine* e, int slot, const int32_t* tokens, int n, co
     K(nfn_embedding_positions(d_tok, nullptr, e->W("tok_embeddings"), nullptr, e->x, n, c.d_model, c.vocab, c.max_seq, c.embed_scale, e->stream));
   }
   if (c.family == 1 && c.embed_norm) K(nfn_norm_forward(e->x, e->ones, nullptr, e->x, nullptr, nullptr, n, c.d_model, c.norm_eps, 1, 0, e->stream));
-  if (forward_layers(*e, n, false, slot, nullptr)) return -1;
-  if (head(*e, n - 1, 1)) return -1;
-  float* rp = reinterpret_cast<float*>(e->h_io + e->io.row_params);
-  fill_params(*e, rp, 0, *s);
-  unsigned long long* off = reinterpret_cast<unsigned long long*>(e->h_io + e->io.offset);
-  *off = (s->seed << 20) ^ (++e->steps);
-  CU(cudaMemcpyAsync(e->d_io + e->io.row_params, rp, 12, cudaMemcpyHostToDevice, e->stream));
-  CU(cudaMemcpyAsync(e->d_io + e->io.offset, off, 8, cudaMemcpyHostToDevice, e->stream));
-  if (sample(*e, 1, reinterpret_cast<const float*>(e->d_io + e->io.row_params),
-             reinterpret_cast<const unsigned long long*>(e->d_io + e->io.offset), reinterpret_cast<int*>(e->d_io + e->io.out_tokens)))
-    return -1;
-  CU(cudaMemcpyAsync(e->h_io + e->io.out_tokens, e->d_io + e->io.out_tokens, 4, cudaMemcpyDeviceToHost, e->stream));
-  CU(cudaStreamSynchronize(e->stream));
-  *next_token = *reinterpret_cast<int*>(e->h_io + e->io.out_tokens);
-  e->len[slot] = n;
-  e->logit_row[slot] = 0;
-  e->logit_src[slot] = 0;
-  e->launches += nfn_launch_count() - before;
-  if (nfn_status_peek() != 0) return efail("engine_prefill: a kernel reported error code " + std::to_string(nfn_status_read_reset()));
-  return 0;
+  return run_prompt_rows(e, slot, n, s, next_token, before);
+}
+
+int nfn_engine_prefill_rows(nfn_engine* e, int slot, const void* rows_bf16, int n, int rows_on_device, const nfn_sampling* s, int32_t* next_token) {
+  if (!e || !rows_bf16 || !s || !next_token) return efail("engine_prefill_rows: null argument");
+  if (!e->finalized) return efail("engine_prefill_rows: call nfn_engine_finalize first");
+  const nfn_engine_config& c = e->c;
+  if (slot < 0 || slot >= c.max_batch) return efail("engine_prefill_rows: bad slot");
+  if (n <= 0 || n >= c.max_seq) return efail("engine_prefill_rows: the prompt must hold between 1 and max_seq - 1 rows");
+  if (c.family == 0) return efail("engine_prefill_rows: the GPT-2 layout adds learned positions to its embeddings; pass token ids");
+  CU(cudaSetDevice(e->device));
+  const long long before = nfn_launch_count();
+  CU(cudaMemcpyAsync(e->x, rows_bf16, (size_t)n * c.d_model * 2, rows_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, e->stream));
+  return run_prompt_rows(e, slot, n, s, next_token, before);
 }
 
 int nfn_engine_decode(nfn_engine* e, const int32_t* tokens_in, const uint8_t* active, const nfn_sampling* s, const nfn_sampling* per_slot,

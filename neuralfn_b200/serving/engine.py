@@ -141,6 +141,7 @@ def _api():
     L.nfn_engine_commit.argtypes = [vp, vp]
     L.nfn_engine_truncate.argtypes = [vp, ip, ip]
     L.nfn_engine_fork.argtypes = [vp, ip, ip, ip]
+    L.nfn_engine_prefill_rows.argtypes = [vp, ip, vp, ip, ip, C.POINTER(_CSampling), vp]
     L.nfn_engine_enable_taps.argtypes = [vp, vp, ip]
     L.nfn_engine_read_taps.argtypes = [vp, ip, ip, ip, vp, ip]
     L._engine_ready = True
@@ -254,6 +255,18 @@ class ResidentEngine:
         out = C.c_int32(0)
         s = (sampling or Sampling()).c()
         self._check(self._L.nfn_engine_prefill(self._h, slot, C.cast(arr, C.c_void_p), len(tokens), C.byref(s), C.cast(C.byref(out), C.c_void_p)))
+        return int(out.value)
+
+    def prefill_rows(self, slot: int, rows: torch.Tensor, sampling: Sampling | None = None) -> int:
+        """Runs a prompt given as its layer-0 input rows (bf16 [n, d_model], host or this engine's device): token embeddings
+        after the embedding norm, media placeholders replaced by projected media features (``serving.multimodal``)."""
+        if rows.dim() != 2 or rows.shape[1] != self.config.d_model or rows.dtype != torch.bfloat16:
+            raise EngineError("prefill_rows wants a bf16 [n, d_model] tensor")
+        rows = rows.contiguous()
+        out = C.c_int32(0)
+        s = (sampling or Sampling()).c()
+        self._check(self._L.nfn_engine_prefill_rows(self._h, slot, C.c_void_p(rows.data_ptr()), rows.shape[0], int(rows.is_cuda), C.byref(s),
+                                                    C.cast(C.byref(out), C.c_void_p)))
         return int(out.value)
 
     def decode(self, tokens_in: dict[int, int], sampling: Sampling | None = None, per_slot: dict[int, Sampling] | None = None) -> dict[int, int]:

@@ -340,3 +340,34 @@ def test_artifact_with_a_dflash_assistant_file(tmp_path):
             res = s.decode(greedy)
             assert res.speculative_assistant_blocks > 0 and res.speculative_proposed_tokens > 0
             _same_up_to_ties(model, PROMPT, plain.token_ids, res.token_ids)
+
+
+def test_media_rows_enter_the_prompt_through_prefill_rows():
+    from neuralfn_b200.serving import GenerationConfig, NativeInferenceModel
+    from neuralfn_b200.serving.multimodal import fuse_media_rows, prefill_with_media
+    cfg, w, eng = _engine(max_batch=2)
+    embed = w["tok_embeddings"].view(-1, cfg.d_model).cuda()
+    # no media: the rows of the plain embeddings reproduce the token prompt exactly
+    nxt = eng.prefill(0, PROMPT)
+    want = eng.last_logits(0).clone()
+    rows = fuse_media_rows(cfg, embed, PROMPT, {})
+    assert eng.prefill_rows(1, rows) == nxt and torch.equal(eng.last_logits(1), want)
+    assert eng.prefill_rows(1, rows.cpu()) == nxt                                   # host rows work too
+    # three placeholder positions take media features; the session carries on as usual
+    model = NativeInferenceModel(eng)
+    eng.release(0), eng.release(1)
+    prompt = list(PROMPT)
+    prompt[3] = prompt[4] = prompt[9] = 700
+    feats = torch.randn(3, cfg.d_model, generator=torch.Generator().manual_seed(0))
+    with model.create_session() as s:
+        info = prefill_with_media(s, embed, prompt, {700: feats})
+        assert info == {"prompt_tokens": 20, "total_tokens": 20, "media_rows": 3}
+        with_media = s.current_logits().clone()
+        out = s.decode(GenerationConfig(max_new_tokens=6, temperature=0.0))
+        assert out.completion_tokens == 6 and len(s.token_ids) == 26
+    with model.create_session() as s:
+        s.prefill(prompt)
+        assert (s.current_logits() - with_media).abs().max() > 1e-3                  # the media rows changed the prompt
+    with pytest.raises(ValueError):
+        fuse_media_rows(cfg, embed, prompt, {700: feats[:2]})
+    model.close()
