@@ -45,6 +45,7 @@ typedef struct {
   float output_multiplier;  // multiplies the logits before the soft cap (0 = 1)
   float post_norm_eps;  // epsilon of the sandwich norms (0 = norm_eps)
   int mlp_activation;   // family 0: NFN_ACT_* id of the MLP activation (0 = GELU, tanh form); mixture-of-activations checkpoints name theirs
+  int kv_cache_mode;    // 0: bf16 K / V rows; 1: TurboQuant records (nfn_engine_set_turboquant before finalize; decode only, no verification blocks)
 } nfn_engine_config;
 
 typedef struct {
@@ -64,6 +65,10 @@ int nfn_engine_set_tensor(nfn_engine* e, const char* name, const void* host_bf16
 int nfn_engine_expected_tensors(const nfn_engine* e, char* buf, int cap);
 // Loads a dense GPT checkpoint (model_%08d.bin, version 5) into a family-0 engine.
 int nfn_engine_load_dense_v5(nfn_engine* e, const char* path);
+// kv_cache_mode 1: the codec tables (device pointers that stay valid for the engine's life, see nfn_tq_tables in
+// nfn_kernels.h; D must equal head_dim). K and V of every layer are then kept as compressed records - keys after QK norm
+// and rotary embedding - and decode attention runs on the records. Call before nfn_engine_finalize.
+int nfn_engine_set_turboquant(nfn_engine* e, const void* tq_tables);
 // Verifies that every expected tensor is present with the right size.
 int nfn_engine_finalize(nfn_engine* e);
 long long nfn_engine_device_bytes(const nfn_engine* e);

@@ -67,7 +67,7 @@ struct DevTensor {
 };
 
 struct StepIO {  // layout of the pinned per-step block; device mirror has the same layout
-  long long tokens, lengths, positions, row_params, offset, out_tokens, total;
+  long long tokens, lengths, positions, row_params, offset, tq_seq, tq_slot_local, tq_slot_global, out_tokens, total;
 };
 
 }  // namespace
@@ -117,6 +117,10 @@ struct nfn_engine {
   std::vector<int> h_vrows;               // live rows per slot of the last verification
   std::vector<int> logit_src;             // 0: e.logits, 1: logits_v
   // hidden-state taps (inputs of a block-diffusion draft): residual stream after the listed layers, by slot and position
+  // TurboQuant cache mode: K / V records instead of bf16 rows (kc / vc then hold records)
+  bool tq = false;
+  nfn_tq_tables tq_tables{};
+  int* tq_idx = nullptr;                  // prompt scratch: sequence, local-ring slot and global slot of every prompt row
   std::vector<int> tap_layers;
   std::vector<void*> taps;                // per tap [max_batch][max_seq][d_model] bf16
 
@@ -216,6 +220,19 @@ int forward_layers(nfn_engine& e, int rows, bool decode, int slot, const int* d_
   const int C = c.d_model, F = c.d_ff, HD = c.head_dim, Hq = c.n_head, Hkv = c.n_kv_head, ATT = Hq * HD;
   const float scale = 1.f / std::sqrt((float)HD);
   const float sign = c.rope_hf ? 1.f : -1.f;
+  if (e.tq && block_rows > 0) return efail("engine: verification blocks are not available with the TurboQuant cache (decode only)");
+  if (e.tq && !decode) {
+    // a prompt: row r of `slot` is position r; its records go to ring row r % window on local layers, row r on global ones
+    const int wcap = c.window > 0 ? std::min(c.window, c.max_seq) : c.max_seq;
+    std::vector<int> idx(3 * (size_t)rows);
+    for (int r = 0; r < rows; ++r) {
+      idx[r] = slot;
+      idx[rows + r] = r >= rows - wcap ? r % wcap : -1;       // earlier rows would be overwritten by later ones of this prompt
+      idx[2 * rows + r] = r;
+    }
+    CU(cudaMemcpyAsync(e.tq_idx, idx.data(), idx.size() * 4, cudaMemcpyHostToDevice, e.stream));
+    CU(cudaStreamSynchronize(e.stream));  // `idx` leaves scope
+  }
   for (int l = 0; l < c.n_layer; ++l) {
     const bool local = layer_is_local(c, l);
     const int cap = e.cap[l];
@@ -233,7 +250,28 @@ int forward_layers(nfn_engine& e, int rows, bool decode, int slot, const int* d_
     }
     const bool rope = c.family == 1 && (!c.rope_local_only || local);
     const float q_scale = (c.family == 1 && c.q_scale > 0.f) ? c.q_scale : 1.f;
-    if (decode) {
+    if (decode && e.tq) {
+      // compressed cache: prepare q / k at their positions, encode the new token's K and V, attend over the records
+      const int* d_pos = reinterpret_cast<const int*>(e.d_io + e.io.positions);
+      if (rope && c.qk_norm) {
+        K(nfn_qk_norm_rope_forward(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, qw, kw, e.cosT, e.sinT, d_pos, c.max_seq, sign, c.qk_norm_eps, q_scale, nullptr, e.stream));
+      } else if (rope) {
+        K(nfn_rope_inplace(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, HD, e.cosT, e.sinT, d_pos, c.max_seq, sign, q_scale, e.stream));
+      } else if (c.qk_norm == 1) {
+        K(nfn_qk_norm_forward(e.qkv, static_cast<float*>(e.rstd), rows, Hq, Hkv, HD, e.qkv_ld, c.qk_norm_eps, q_scale, e.stream));
+      } else if (c.qk_norm == 2) {
+        K(nfn_qk_norm_rope_forward(e.qkv, e.qkv_ld, rows, rows, Hq, Hkv, HD, qw, kw, e.cosT, e.sinT, static_cast<const int*>(e.zero_pos), c.max_seq, sign,
+                                   c.qk_norm_eps, q_scale, nullptr, e.stream));
+      } else if (q_scale != 1.f) {
+        return efail("engine: a query scale without QK norm or rotary embedding is not supported with the TurboQuant cache");
+      }
+      const int* d_seq = reinterpret_cast<const int*>(e.d_io + e.io.tq_seq);
+      const int* d_slot = reinterpret_cast<const int*>(e.d_io + (local ? e.io.tq_slot_local : e.io.tq_slot_global));
+      const char* q = static_cast<const char*>(e.qkv);
+      K(nfn_turboquant_encode(&e.tq_tables, q + (size_t)Hq * HD * 2, e.qkv_ld, d_seq, d_slot, rows, Hkv, cap, 1, kc, e.stream));
+      K(nfn_turboquant_encode(&e.tq_tables, q + (size_t)(Hq + Hkv) * HD * 2, e.qkv_ld, d_seq, d_slot, rows, Hkv, cap, 0, vc, e.stream));
+      K(nfn_turboquant_attention(&e.tq_tables, e.qkv, e.qkv_ld, kc, vc, d_lengths, e.att, ATT, rows, Hq, Hkv, cap, scale, e.stream));
+    } else if (decode) {
       K(nfn_decode_attention(e.qkv, e.qkv_ld, kc, vc, cache_stride, d_lengths, e.att, rows, Hq, Hkv, HD, cap, qw, kw, c.qk_norm != 0,
                              c.qk_norm_eps, rope ? e.cosT : nullptr, rope ? e.sinT : nullptr, rope ? c.max_seq : 0, sign, scale * q_scale,
                              e.dec_ws, e.dec_ws_bytes, 0, e.stream));
@@ -259,7 +297,13 @@ int forward_layers(nfn_engine& e, int rows, bool decode, int slot, const int* d_
         const char* q = static_cast<const char*>(e.qkv);
         K(nfn_attention_forward(q, q + (size_t)Hq * HD * 2, q + (size_t)(Hq + Hkv) * HD * 2, e.att, nullptr, 1, rows, Hq, Hkv, HD, e.qkv_ld,
                                 e.qkv_ld, e.qkv_ld, ATT, 1, local ? c.window : 0, scale, e.stream));
-        K(nfn_kv_cache_write(e.qkv, e.qkv_ld, kc + (size_t)slot * cache_stride * 2, vc + (size_t)slot * cache_stride * 2, rows, Hq, Hkv, HD, cap, 0, e.stream));
+        if (e.tq) {
+          const int* d_slot = e.tq_idx + (local ? rows : 2 * rows);
+          K(nfn_turboquant_encode(&e.tq_tables, q + (size_t)Hq * HD * 2, e.qkv_ld, e.tq_idx, d_slot, rows, Hkv, cap, 1, kc, e.stream));
+          K(nfn_turboquant_encode(&e.tq_tables, q + (size_t)(Hq + Hkv) * HD * 2, e.qkv_ld, e.tq_idx, d_slot, rows, Hkv, cap, 0, vc, e.stream));
+        } else {
+          K(nfn_kv_cache_write(e.qkv, e.qkv_ld, kc + (size_t)slot * cache_stride * 2, vc + (size_t)slot * cache_stride * 2, rows, Hq, Hkv, HD, cap, 0, e.stream));
+        }
       }
     }
     if (c.family == 0) {
@@ -460,9 +504,25 @@ int nfn_engine_load_dense_v5(nfn_engine* e, const char* path) {
   return 0;
 }
 
+int nfn_engine_set_turboquant(nfn_engine* e, const void* tq_tables) {
+  if (!e || !tq_tables) return efail("engine_set_turboquant: null argument");
+  if (e->finalized) return efail("engine_set_turboquant: call it before nfn_engine_finalize (the caches are allocated there)");
+  const nfn_tq_tables* t = static_cast<const nfn_tq_tables*>(tq_tables);
+  const nfn_engine_config& c = e->c;
+  if (c.kv_cache_mode != 1) return efail("engine_set_turboquant: the engine was created with kv_cache_mode 0");
+  if (t->D != c.head_dim || (t->D != 64 && t->D != 128)) return efail("engine_set_turboquant: the codec dimension must equal head_dim (64 or 128)");
+  if (!t->rotation || !t->centroids || !t->key_fields || !t->value_fields || t->key_rec_bytes <= 0 || t->value_rec_bytes <= 0 || (t->qjl && !t->projection))
+    return efail("engine_set_turboquant: incomplete tables");
+  if (c.n_head / c.n_kv_head > 8) return efail("engine_set_turboquant: the record attention kernel takes at most 8 query heads per kv head");
+  e->tq_tables = *t;
+  e->tq = true;
+  return 0;
+}
+
 int nfn_engine_finalize(nfn_engine* e) {
   if (!e) return efail("engine_finalize: null engine");
   if (e->finalized) return 0;
+  if (e->c.kv_cache_mode == 1 && !e->tq) return efail("engine_finalize: kv_cache_mode 1 needs nfn_engine_set_turboquant first");
   CU(cudaSetDevice(e->device));
   for (const auto& kv : e->expected)
     if (!e->has(kv.first)) return efail("engine_finalize: missing tensor " + kv.first);
@@ -500,11 +560,13 @@ int nfn_engine_finalize(nfn_engine* e) {
   e->cap.resize(c.n_layer);
   for (int l = 0; l < c.n_layer; ++l) {
     e->cap[l] = layer_is_local(c, l) ? std::min(c.window, c.max_seq) : c.max_seq;
-    const long long nbytes = (long long)c.max_batch * c.n_kv_head * e->cap[l] * HD * 2;
-    if (e->alloc(&e->kc[l], nbytes) || e->alloc(&e->vc[l], nbytes)) return -1;
-    CU(cudaMemset(e->kc[l], 0, (size_t)nbytes));
-    CU(cudaMemset(e->vc[l], 0, (size_t)nbytes));
+    const long long rows_l = (long long)c.max_batch * c.n_kv_head * e->cap[l];
+    const long long kbytes = rows_l * (e->tq ? e->tq_tables.key_rec_bytes : HD * 2), vbytes = rows_l * (e->tq ? e->tq_tables.value_rec_bytes : HD * 2);
+    if (e->alloc(&e->kc[l], kbytes) || e->alloc(&e->vc[l], vbytes)) return -1;
+    CU(cudaMemset(e->kc[l], 0, (size_t)kbytes));
+    CU(cudaMemset(e->vc[l], 0, (size_t)vbytes));
   }
+  if (e->tq && e->alloc((void**)&e->tq_idx, 3LL * c.max_seq * 4)) return -1;
   e->dec_ws_bytes = nfn_decode_attention_workspace_bytes(c.max_batch, c.n_head, c.n_kv_head, HD, 64);
   if (e->dec_ws_bytes <= 0) return efail("engine_finalize: bad decode attention geometry");
   if (e->alloc(&e->dec_ws, e->dec_ws_bytes)) return -1;
@@ -518,7 +580,10 @@ int nfn_engine_finalize(nfn_engine* e) {
   e->io.positions = e->io.lengths + up(B * 4);
   e->io.row_params = e->io.positions + up(B * 4);
   e->io.offset = e->io.row_params + up(B * 12);
-  e->io.out_tokens = e->io.offset + 256;
+  e->io.tq_seq = e->io.offset + 256;
+  e->io.tq_slot_local = e->io.tq_seq + up(B * 4);
+  e->io.tq_slot_global = e->io.tq_slot_local + up(B * 4);
+  e->io.out_tokens = e->io.tq_slot_global + up(B * 4);
   e->io.total = e->io.out_tokens + up(B * 4);
   CU(cudaMallocHost((void**)&e->h_io, (size_t)e->io.total));
   std::memset(e->h_io, 0, (size_t)e->io.total);
@@ -625,6 +690,13 @@ int nfn_engine_decode(nfn_engine* e, const int32_t* tokens_in, const uint8_t* ac
     tok[b] = on ? tokens_in[b] : 0;
     len[b] = on ? e->len[b] + 1 : 0;
     pos[b] = on ? e->len[b] : 0;
+    if (e->tq) {
+      // where the new token's records go: ring row of the sliding-window layers, plain row of the global ones; -1 = idle
+      const int wcap = c.window > 0 ? std::min(c.window, c.max_seq) : c.max_seq;
+      reinterpret_cast<int*>(e->h_io + e->io.tq_seq)[b] = on ? b : -1;
+      reinterpret_cast<int*>(e->h_io + e->io.tq_slot_local)[b] = on ? e->len[b] % wcap : -1;
+      reinterpret_cast<int*>(e->h_io + e->io.tq_slot_global)[b] = on ? e->len[b] : -1;
+    }
     fill_params(*e, rp, b, per_slot ? per_slot[b] : *s);
     n_active += on;
   }
@@ -686,6 +758,7 @@ int nfn_engine_last_logits(nfn_engine* e, int slot, float* out_vocab) {
 
 int nfn_engine_enable_verify(nfn_engine* e, int max_rows) {
   if (!e || !e->finalized) return efail("engine_enable_verify: finalize the engine first");
+  if (e->tq) return efail("engine_enable_verify: verification blocks are not available with the TurboQuant cache (decode only)");
   if (e->v_rows_max > 0) return max_rows <= e->v_rows_max ? 0 : efail("engine_enable_verify: already enabled with fewer rows");
   const nfn_engine_config& c = e->c;
   if (max_rows < 1 || max_rows > 128) return efail("engine_enable_verify: 1 <= max_rows <= 128");
@@ -835,12 +908,15 @@ int nfn_engine_fork(nfn_engine* e, int src_slot, int dst_slot, int n) {
   CU(cudaSetDevice(e->device));
   for (int l = 0; l < c.n_layer && n > 0; ++l) {
     // rows [0, min(n, cap)) of every kv head; whole-slot copy when most of it is live
-    const size_t head_bytes = (size_t)e->cap[l] * c.head_dim * 2, slot_bytes = head_bytes * c.n_kv_head;
-    const size_t live = (size_t)std::min(n, e->cap[l]) * c.head_dim * 2;
-    char* kc = static_cast<char*>(e->kc[l]);
-    char* vc = static_cast<char*>(e->vc[l]);
-    CU(cudaMemcpy2DAsync(kc + dst_slot * slot_bytes, head_bytes, kc + src_slot * slot_bytes, head_bytes, live, c.n_kv_head, cudaMemcpyDeviceToDevice, e->stream));
-    CU(cudaMemcpy2DAsync(vc + dst_slot * slot_bytes, head_bytes, vc + src_slot * slot_bytes, head_bytes, live, c.n_kv_head, cudaMemcpyDeviceToDevice, e->stream));
+    char* caches[2] = {static_cast<char*>(e->kc[l]), static_cast<char*>(e->vc[l])};
+    const size_t row_bytes[2] = {e->tq ? (size_t)e->tq_tables.key_rec_bytes : (size_t)c.head_dim * 2,
+                                 e->tq ? (size_t)e->tq_tables.value_rec_bytes : (size_t)c.head_dim * 2};
+    for (int which = 0; which < 2; ++which) {
+      const size_t head_bytes = (size_t)e->cap[l] * row_bytes[which], slot_bytes = head_bytes * c.n_kv_head;
+      const size_t live = (size_t)std::min(n, e->cap[l]) * row_bytes[which];
+      CU(cudaMemcpy2DAsync(caches[which] + dst_slot * slot_bytes, head_bytes, caches[which] + src_slot * slot_bytes, head_bytes, live, c.n_kv_head,
+                           cudaMemcpyDeviceToDevice, e->stream));
+    }
   }
   for (size_t t = 0; t < e->taps.size() && n > 0; ++t) {
     const size_t stride = (size_t)c.max_seq * c.d_model * 2;

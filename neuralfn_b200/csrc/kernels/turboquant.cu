@@ -75,6 +75,7 @@ __global__ void __launch_bounds__(128) tq_encode_kernel(const TqEncodeParams p) 
   const long long vec = (long long)blockIdx.x * 4 + warp;
   if (vec >= (long long)p.rows * p.H) return;
   const int row = (int)(vec / p.H), h = (int)(vec % p.H);
+  if (p.slot[row] < 0 || p.slot[row] >= p.cap || p.seq[row] < 0) return;  // rows without a destination (idle sequences) are skipped
   const bool qjl = p.is_key && p.t.qjl;
   const int rec_bytes = p.is_key ? p.t.key_rec_bytes : p.t.value_rec_bytes;
   const int* fields = p.is_key ? p.t.key_fields : p.t.value_fields;

@@ -31,7 +31,7 @@ class _CConfig(C.Structure):
                 ("window", C.c_int), ("global_every", C.c_int), ("embed_scale", C.c_float), ("use_cuda_graph", C.c_int),
                 ("gated_attention", C.c_int), ("sandwich_norms", C.c_int), ("centered_norms", C.c_int), ("embed_norm", C.c_int),
                 ("rope_local_only", C.c_int), ("q_scale", C.c_float), ("output_multiplier", C.c_float), ("post_norm_eps", C.c_float),
-                ("mlp_activation", C.c_int)]
+                ("mlp_activation", C.c_int), ("kv_cache_mode", C.c_int)]
 
 
 class _CSampling(C.Structure):
@@ -85,6 +85,7 @@ class EngineConfig:
     output_multiplier: float = 0.0
     post_norm_eps: float = 0.0
     mlp_activation: int = 0       # GPT-2 family: epilogue id of the MLP activation (0 = tanh GELU); see MLP_ACTIVATION_IDS
+    kv_cache_mode: int = 0        # 0: bf16 K / V rows; 1: TurboQuant 3.5-bit records (decode only: no verification blocks)
 
     MLP_ACTIVATION_IDS = {"gelu": 1, "silu": 3, "relu2": 4, "relu": 6}
 
@@ -128,6 +129,7 @@ def _api():
     L.nfn_engine_expected_tensors.argtypes = [vp, C.c_char_p, ip]
     L.nfn_engine_load_dense_v5.argtypes = [vp, C.c_char_p]
     L.nfn_engine_finalize.argtypes = [vp]
+    L.nfn_engine_set_turboquant.argtypes = [vp, vp]
     L.nfn_engine_device_bytes.restype, L.nfn_engine_device_bytes.argtypes = C.c_longlong, [vp]
     L.nfn_engine_prefill.argtypes = [vp, ip, vp, ip, C.POINTER(_CSampling), vp]
     L.nfn_engine_decode.argtypes = [vp, vp, vp, C.POINTER(_CSampling), vp, vp]
@@ -159,7 +161,7 @@ def resident_inference_capabilities() -> dict:
             # the engine executes bf16 weights only: K-quant / NF4 checkpoints are dequantised at load time
             # (``quant.kquant`` / ``checkpoint.gguf``); the packed-weight kernels are not wired into it
             "block_verification": True, "hidden_state_taps": True, "gpt2_mlp_activations": sorted(EngineConfig.MLP_ACTIVATION_IDS),
-            "quantized_weights": [], "weight_dtypes": ["bf16"], "dequantised_at_load": ["Q4_K", "Q5_K", "Q6_K", "NF4"]}
+            "kv_cache_modes": ["bf16", "turboquant-3.5 (decode only)"], "quantized_weights": [], "weight_dtypes": ["bf16"], "dequantised_at_load": ["Q4_K", "Q5_K", "Q6_K", "NF4"]}
 
 
 class EngineError(RuntimeError):
@@ -167,7 +169,7 @@ class EngineError(RuntimeError):
 
 
 class ResidentEngine:
-    def __init__(self, config: EngineConfig, device: int = 0) -> None:
+    def __init__(self, config: EngineConfig, device: int = 0, *, turboquant_profile: str = "mse-3.5", turboquant_seed: int = 0) -> None:
         self.config = config
         self.device = int(device)
         self._L = _api()
@@ -176,6 +178,32 @@ class ResidentEngine:
         if not self._h:
             raise EngineError(self._err())
         self._finalized = False
+        if config.kv_cache_mode == 1:
+            self._set_turboquant(turboquant_profile, turboquant_seed)
+
+    def _set_turboquant(self, profile: str, seed: int) -> None:
+        """``kv_cache_mode`` 1: the codec of ``quant.turboquant`` (deterministic rotation / projection, Lloyd-Max centroids, the
+        default outlier channel set) lives on the device for the engine's life; K / V are kept as its records."""
+        from ..quant.turboquant import TurboQuantCodec, default_outlier_indices
+        hd = self.config.head_dim
+        self.turboquant = TurboQuantCodec(hd, profile=profile, seed=seed, outlier_indices=default_outlier_indices(hd))
+        self._tq_tensors = t = self.turboquant.device_tables(torch.device("cuda", self.device))
+
+        class _Tables(C.Structure):
+            _fields_ = [("rotation", C.c_void_p), ("projection", C.c_void_p), ("centroids", C.c_void_p), ("key_fields", C.c_void_p),
+                        ("value_fields", C.c_void_p), ("D", C.c_int), ("qjl", C.c_int), ("key_rec_bytes", C.c_int), ("value_rec_bytes", C.c_int)]
+        self._tq_c = _Tables(t["rotation"].data_ptr(), t["projection"].data_ptr(), t["centroids"].data_ptr(), t["key_fields"].data_ptr(),
+                             t["value_fields"].data_ptr(), hd, int(profile == "qjl-3.5"), self.turboquant.key_layout.record_bytes,
+                             self.turboquant.value_layout.record_bytes)
+        self._check(self._L.nfn_engine_set_turboquant(self._h, C.cast(C.byref(self._tq_c), C.c_void_p)))
+
+    @property
+    def kv_bytes_per_token(self) -> int:
+        """Cache bytes one token occupies in a global (full-context) layer."""
+        c = self.config
+        if c.kv_cache_mode == 1:
+            return c.n_kv_head * (self.turboquant.key_layout.record_bytes + self.turboquant.value_layout.record_bytes)
+        return 2 * c.n_kv_head * c.head_dim * 2
 
     def _err(self) -> str:
         return (self._L.nfn_engine_last_error() or b"").decode("utf-8", "replace")

