@@ -55,7 +55,7 @@ import torch
 
 from .gpt2 import FlatLayout, ParamSpec
 
-__all__ = ["GlimmerConfig", "GlimmerEngine", "glimmer_param_specs", "glimmer_lora_specs", "glimmer_reference_loss"]
+__all__ = ["GlimmerConfig", "GlimmerEngine", "ppo_terms_and_gradients", "glimmer_param_specs", "glimmer_lora_specs", "glimmer_reference_loss"]
 
 
 @dataclass(frozen=True)
@@ -248,6 +248,33 @@ def glimmer_reference_loss(cfg: GlimmerConfig, p: dict[str, torch.Tensor], token
         return rows.mean(), logits, rows
     m = loss_mask.to(rows.dtype)
     return (rows * m).sum() / m.sum().clamp(min=1.0), logits, rows
+
+
+def ppo_terms_and_gradients(logp, logp_old, advantages, returns, value, value_old, mask, *, clip: float, vf_coef: float,
+                            normalize_advantages: bool = True) -> dict[str, torch.Tensor]:
+    """The clipped-surrogate policy term and the clipped value term over the rows with ``mask`` > 0 (masked means), and
+    their gradients with respect to the per-row log-probabilities and values, written out by hand (no autograd, no host
+    synchronisation: usable inside a captured step). Same terms as ``tensor.stages_losses._ppo_terms`` /
+    ``masked_ppo_clipped_loss``; loss = policy + vf_coef * value."""
+    m = mask.to(logp.dtype)
+    denom = m.sum().clamp(min=1.0)
+    adv = advantages
+    if normalize_advantages:
+        mean = (adv * m).sum() / denom
+        adv = (adv - mean) * torch.rsqrt((((adv - mean) ** 2) * m).sum() / denom + 1e-8)
+    ratio = torch.exp(logp - logp_old)
+    clipped = ratio.clamp(1.0 - clip, 1.0 + clip)
+    unclipped_active = ratio * adv <= clipped * adv                 # the minimum is the unclipped product (ties included)
+    policy = -torch.minimum(ratio * adv, clipped * adv)
+    v_clip = value_old + (value - value_old).clamp(-clip, clip)
+    first = (value - returns) ** 2 >= (v_clip - returns) ** 2
+    val = 0.5 * torch.where(first, (value - returns) ** 2, (v_clip - returns) ** 2)
+    policy_loss, value_loss = (policy * m).sum() / denom, (val * m).sum() / denom
+    inside = ((value - value_old).abs() < clip).to(value.dtype)      # derivative of the clamp
+    return {"loss": policy_loss + vf_coef * value_loss, "policy_loss": policy_loss, "value_loss": value_loss,
+            "clip_fraction": ((~unclipped_active).to(m.dtype) * m).sum() / denom, "approx_kl": ((logp_old - logp) * m).sum() / denom,
+            "d_logp": torch.where(unclipped_active, -adv * ratio, torch.zeros_like(adv)) * m / denom,
+            "d_value": torch.where(first, value - returns, (v_clip - returns) * inside) * vf_coef * m / denom}
 
 
 # ------------------------------------------------------------------------------- engine --
@@ -508,30 +535,16 @@ class GlimmerEngine:
         d loss / d value per row in ``self._d_value`` when ``compute_grad``."""
         cfg, N = self.cfg, self.B * self.T
         self._ce(False, 1.0, 1.0, None, z=0.0)                      # row losses = -log p(action)
-        logp, (logp_old, adv, ret, v_old) = -self.row_loss, self.ppo_in
-        m, v, c = self.loss_mask, self.values, cfg.ppo_clip
-        denom = m.sum().clamp(min=1.0)
-        if cfg.ppo_normalize_advantages:
-            mean = (adv * m).sum() / denom
-            adv = (adv - mean) * torch.rsqrt((((adv - mean) ** 2) * m).sum() / denom + 1e-8)
-        ratio = torch.exp(logp - logp_old)
-        clipped = ratio.clamp(1.0 - c, 1.0 + c)
-        unclipped_active = (ratio * adv <= clipped * adv)
-        policy = -torch.minimum(ratio * adv, clipped * adv)
-        v_clip = v_old + (v - v_old).clamp(-c, c)
-        first = (v - ret) ** 2 >= (v_clip - ret) ** 2
-        value = 0.5 * torch.where(first, (v - ret) ** 2, (v_clip - ret) ** 2)
-        st = self.ppo_stats
-        st[0], st[1] = (policy * m).sum() / denom, (value * m).sum() / denom
-        st[2] = ((~unclipped_active).float() * m).sum() / denom
-        st[3] = ((logp_old - logp) * m).sum() / denom
-        self.loss.copy_((st[0] + cfg.ppo_vf_coef * st[1]).reshape(1))
+        logp_old, adv, ret, v_old = self.ppo_in
+        out = ppo_terms_and_gradients(-self.row_loss, logp_old, adv, ret, self.values, v_old, self.loss_mask, clip=cfg.ppo_clip,
+                                      vf_coef=cfg.ppo_vf_coef, normalize_advantages=cfg.ppo_normalize_advantages)
+        self.ppo_stats.copy_(torch.stack([out["policy_loss"], out["value_loss"], out["clip_fraction"], out["approx_kl"]]))
+        self.loss.copy_(out["loss"].reshape(1))
         if compute_grad:
             gs = 1.0 if grad_scale is None else grad_scale * N
-            # d policy / d logp = -A r where the unclipped branch is the minimum, else 0; log p = -(row loss)
-            torch.mul(torch.where(unclipped_active, adv * ratio, torch.zeros_like(adv)), m / denom, out=self.row_scale)
-            inside = ((v - v_old).abs() < c).to(v.dtype)
-            self._d_value = torch.where(first, v - ret, (v_clip - ret) * inside) * (cfg.ppo_vf_coef * gs) * m / denom
+            # log p = -(row loss): the loss kernel's per-row scale is -d loss / d log p
+            torch.neg(out["d_logp"], out=self.row_scale)
+            self._d_value = out["d_value"] * gs
             keep = self.loss.clone()
             self._ce(True, gs, 1.0, self.row_scale, z=0.0)
             self.loss.copy_(keep)

@@ -347,3 +347,30 @@ def test_native_ppo_loop_raises_the_rewarded_token_frequency(kernel_lib):
         assert all(v == v for v in out.values())                      # no NaN
     post.trainer.check_status()
     assert sum(scores[-3:]) / 3 > sum(scores[:3]) / 3 + 0.05, scores
+
+
+def test_ppo_gradient_formulas_equal_autograd_on_the_reference_terms():
+    """The hand-written derivatives of the clipped surrogate and the clipped value loss (CPU, float64)."""
+    from neuralfn_b200.models.glimmer import ppo_terms_and_gradients
+    from neuralfn_b200.tensor.stages_losses import _ppo_terms
+    g = torch.Generator().manual_seed(0)
+    n = 400
+    logp = (-2 + torch.randn(n, generator=g, dtype=torch.float64)).requires_grad_(True)
+    logp_old = logp.detach() + 0.3 * torch.randn(n, generator=g, dtype=torch.float64)
+    adv, ret = torch.randn(n, generator=g, dtype=torch.float64), torch.randn(n, generator=g, dtype=torch.float64)
+    v = torch.randn(n, generator=g, dtype=torch.float64).requires_grad_(True)
+    v_old = v.detach() + 0.3 * torch.randn(n, generator=g, dtype=torch.float64)
+    mask = (torch.rand(n, generator=g) > 0.3).double()
+    for normalize in (True, False):
+        out = ppo_terms_and_gradients(logp, logp_old, adv, ret, v, v_old, mask, clip=0.2, vf_coef=0.5, normalize_advantages=normalize)
+        denom = mask.sum()
+        a = adv
+        if normalize:
+            mean = (adv * mask).sum() / denom
+            a = (adv - mean) / torch.sqrt((((adv - mean) ** 2) * mask).sum() / denom + 1e-8)
+        pol, val = _ppo_terms(logp, logp_old, a, v, v_old, ret, 0.2)
+        ref = (pol * mask).sum() / denom + 0.5 * (val * mask).sum() / denom
+        d_logp, d_v = torch.autograd.grad(ref, (logp, v))
+        assert abs(float(out["loss"]) - float(ref)) < 1e-12
+        assert (out["d_logp"] - d_logp).abs().max() < 1e-12 and (out["d_value"] - d_v).abs().max() < 1e-12
+        assert 0.1 < float(out["clip_fraction"]) < 0.9
