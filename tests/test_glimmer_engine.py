@@ -327,26 +327,25 @@ def test_dense_trainer_drives_the_glimmer_engine(kernel_lib):
 @pytest.mark.gpu
 def test_native_ppo_loop_raises_the_rewarded_token_frequency(kernel_lib):
     """Rollouts with the engine's own forward pass, GAE, clipped-surrogate steps on the native trainer: the policy learns to
-    emit the token the reward counts."""
+    prefer the tokens the reward counts (a quarter of a 32-token vocabulary)."""
     from neuralfn_b200.parallel.dp import AdamWConfig
     from neuralfn_b200.trainers.glimmer_post import GlimmerPostTrainer
-    cfg = _cfg(vocab_size=64, n_layer=2, max_seq_len=128)
-    post = GlimmerPostTrainer(cfg, 8, 128, "ppo", AdamWConfig(lr=3e-3, warmup_steps=1, total_steps=100, weight_decay=0.0, schedule="constant"),
+    cfg = _cfg(vocab_size=32, n_layer=2, max_seq_len=128, logit_softcap=0.0, output_multiplier=1.0, z_loss=0.0)
+    post = GlimmerPostTrainer(cfg, 32, 128, "ppo", AdamWConfig(lr=1e-2, warmup_steps=1, total_steps=200, weight_decay=0.0, schedule="constant"),
                               seed=1, use_cuda_graph=False)
     gen = torch.Generator(device="cuda").manual_seed(0)
-    prompts = torch.randint(0, 64, (8, 6), device="cuda", generator=gen)
-    lucky = 7
+    prompts = torch.randint(0, 32, (32, 4), device="cuda", generator=gen)
 
     def reward(ids, P):
-        return (ids[:, P:] == lucky).float().mean(1)
+        return (ids[:, P:] < 8).float().mean(1)
 
     scores = []
-    for _ in range(12):
-        out = post.ppo_step(prompts, reward, epochs=2, max_new_tokens=12, temperature=1.0, generator=gen)
+    for _ in range(16):
+        out = post.ppo_step(prompts, reward, epochs=3, max_new_tokens=8, temperature=1.0, generator=gen)
         scores.append(out["mean_score"])
         assert all(v == v for v in out.values())                      # no NaN
     post.trainer.check_status()
-    assert sum(scores[-3:]) / 3 > sum(scores[:3]) / 3 + 0.05, scores
+    assert sum(scores[-4:]) / 4 > sum(scores[:4]) / 4 + 0.05, scores
 
 
 def test_ppo_gradient_formulas_equal_autograd_on_the_reference_terms():
