@@ -142,6 +142,22 @@ def main(argv=None) -> int:
                     graph.replay()
                 ms = _time(replay, a.iters, a.warmup, dev) / Kc
                 record("allreduce_resid_norm", f"{B}x{d} (in a CUDA graph, per call)", vname, ms, 0.0, (W - 1) * B * d * 2)
+                # where the time goes inside one launch: device-side timestamps of CTA 0 (signal, peers arrived, rows done, end)
+                import ctypes
+                stamps = torch.zeros(5, dtype=torch.int64, device=dev)
+                lib = _lib.load()
+                lib.nfn_allreduce_set_trace(ctypes.c_void_p(stamps.data_ptr()))
+                phases = torch.zeros(4, dtype=torch.float64)
+                n_tr = 20
+                for i in range(n_tr):
+                    if world > 1:
+                        dist.barrier()
+                    ctx.allreduce_resid_norm(*bufs[i % 2], resid=resid, norm_weight=nw, use_multicast=mc)
+                    torch.cuda.synchronize(dev)
+                    t = stamps.cpu().double()
+                    phases += (t[1:] - t[:-1]) / n_tr
+                lib.nfn_allreduce_set_trace(ctypes.c_void_p(0))
+                results[-1]["phases_us"] = {k: round(float(v) / 1e3, 2) for k, v in zip(("signal", "wait_for_peers", "rows", "tail"), phases)}
     torch.cuda.synchronize(dev)
     status = _lib.status_read_reset()
     if rank == 0:

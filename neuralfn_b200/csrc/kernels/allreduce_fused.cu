@@ -23,7 +23,7 @@
 
 namespace nfn {
 
-constexpr int AR_MAX_WORLD = 8, AR_THREADS = 256;
+constexpr int AR_MAX_WORLD = 8, AR_MAX_THREADS = 1024;
 
 struct ArParams {
   const __nv_bfloat16* peer[AR_MAX_WORLD];
@@ -46,10 +46,17 @@ struct ArParams {
   __nv_bfloat16* out;
   int ld_out;
   int* status;
+  unsigned long long* trace;  // optional [5]: globaltimer at start / signalled / peers arrived / rows done / end (CTA 0)
 };
 
 __device__ __forceinline__ void ar_st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// one fence, then a relaxed store per peer: a release store per peer would pay the system-scope fence `world` times
+// (measured: 1.5 us each)
+__device__ __forceinline__ void ar_fence_release_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+__device__ __forceinline__ void ar_st_relaxed_sys(int* p, int v) {
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ int ar_ld_acquire_sys(const int* p) {
   int v;
@@ -88,18 +95,24 @@ __device__ bool ar_wait_all(const int* flags, int world, int want, int* status) 
   return true;
 }
 
-__global__ void __launch_bounds__(AR_THREADS)
+__global__ void __launch_bounds__(AR_MAX_THREADS)
 allreduce_resid_norm_kernel(const ArParams p) {
-  __shared__ float red[AR_THREADS / 32];
+  __shared__ float red[AR_MAX_THREADS / 32];
   __shared__ int sh_ok;
   extern __shared__ float rowbuf[];  // n floats
   const int epoch = p.epoch + (p.epoch_dev ? *p.epoch_dev : 0);
+  const bool tracer = p.trace && blockIdx.x == 0 && threadIdx.x == 0;
+  if (tracer) p.trace[0] = global_timer_ns();
   if (threadIdx.x == 0) {
+    // the partial rows were written by an earlier kernel of this stream: they are complete in this GPU's memory, and the
+    // release at system scope orders them before the flag for the peers that acquire it
     if (blockIdx.x == 0) {
-      __threadfence_system();
-      for (int r = 0; r < p.world; ++r) ar_st_release_sys(p.peer_ctrl[r] + p.rank, epoch);
+      ar_fence_release_sys();
+      for (int r = 0; r < p.world; ++r) ar_st_relaxed_sys(p.peer_ctrl[r] + p.rank, epoch);
     }
+    if (tracer) p.trace[1] = global_timer_ns();
     sh_ok = ar_wait_all(p.ctrl, p.world, epoch, p.status) ? 1 : 0;
+    if (tracer) p.trace[2] = global_timer_ns();
   }
   __syncthreads();
   if (!sh_ok) return;
@@ -112,7 +125,7 @@ allreduce_resid_norm_kernel(const ArParams p) {
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
     __syncthreads();
     float tot = 0.f;
-    for (int w = 0; w < AR_THREADS / 32; ++w) tot += red[w];
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
     return tot;
   };
   auto add_resid_store = [&](int row, int v, float (&s)[8]) {
@@ -137,11 +150,17 @@ allreduce_resid_norm_kernel(const ArParams p) {
         const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
         s[0] = a.x; s[1] = a.y; s[2] = b.x; s[3] = b.y; s[4] = c.x; s[5] = c.y; s[6] = d.x; s[7] = d.y;
       } else {
-        for (int r = 0; r < p.world; ++r) {
-          const uint4 u = ld_peer_16(p.peer[(p.rank + r) % p.world] + off);  // start at self, rotate
-          const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-          s[0] += a.x; s[1] += a.y; s[2] += b.x; s[3] += b.y; s[4] += c.x; s[5] += c.y; s[6] += d.x; s[7] += d.y;
-        }
+        // issue every peer's load before using any of them: one NVLink round trip instead of `world`
+        uint4 u[AR_MAX_WORLD];
+#pragma unroll
+        for (int r = 0; r < AR_MAX_WORLD; ++r)
+          if (r < p.world) u[r] = ld_peer_16(p.peer[(p.rank + r) % p.world] + off);  // start at self, rotate
+#pragma unroll
+        for (int r = 0; r < AR_MAX_WORLD; ++r)
+          if (r < p.world) {
+            const float2 a = unpack_bf16x2(u[r].x), b = unpack_bf16x2(u[r].y), c = unpack_bf16x2(u[r].z), d = unpack_bf16x2(u[r].w);
+            s[0] += a.x; s[1] += a.y; s[2] += b.x; s[3] += b.y; s[4] += c.x; s[5] += c.y; s[6] += d.x; s[7] += d.y;
+          }
       }
       if (p.bias) {
         const uint4 u = *reinterpret_cast<const uint4*>(p.bias + v * 8);
@@ -194,16 +213,19 @@ allreduce_resid_norm_kernel(const ArParams p) {
     __syncthreads();
   }
 
-  // "done reading": the last CTA of this rank tells every peer; ticket lives at ctrl[16]
+  // "done reading": the last CTA of this rank tells every peer; ticket lives at ctrl[16]. The barrier orders every
+  // thread's loads before thread 0's ticket; the release stores order them before the peers' view of the flag.
+  if (tracer) p.trace[3] = global_timer_ns();
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
+    __threadfence();
     const int t = atomicAdd(p.ctrl + 16, 1);
     if (t == (int)gridDim.x - 1) {
       p.ctrl[16] = 0;
-      __threadfence_system();
-      for (int r = 0; r < p.world; ++r) ar_st_release_sys(p.peer_ctrl[r] + 8 + p.rank, epoch);
+      ar_fence_release_sys();
+      for (int r = 0; r < p.world; ++r) ar_st_relaxed_sys(p.peer_ctrl[r] + 8 + p.rank, epoch);
     }
+    if (tracer) p.trace[4] = global_timer_ns();
   }
 }
 
@@ -220,6 +242,13 @@ extern "C" int nfn_allreduce_sandwich_norm(const void* const* peer_bufs, const v
                                            int rank, int world, int epoch, const int* epoch_dev, int rows, int n, int ld,
                                            const void* bias, const void* post_weight, float post_eps, void* resid, int ld_resid,
                                            const void* norm_weight, float eps, int centered, void* out, int ld_out, nfn_stream_t stream);
+
+static unsigned long long* g_ar_trace = nullptr;
+// Debug aid: five device-side timestamps (ns) of CTA 0 of every following launch go to `dev_u64_5` (null switches it off).
+extern "C" int nfn_allreduce_set_trace(void* dev_u64_5) {
+  g_ar_trace = static_cast<unsigned long long*>(dev_u64_5);
+  return 0;
+}
 
 extern "C" int nfn_allreduce_resid_norm(const void* const* peer_bufs, const void* multicast_buf, int* ctrl_local, int* const* ctrl_peer,
                                         int rank, int world, int epoch, const int* epoch_dev, int rows, int n, int ld,
@@ -260,12 +289,15 @@ extern "C" int nfn_allreduce_sandwich_norm(const void* const* peer_bufs, const v
   p.out = static_cast<__nv_bfloat16*>(out);
   p.ld_out = ld_out;
   p.status = status_ptr();
+  p.trace = g_ar_trace;
   const size_t smem = (size_t)n * 4;
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(allreduce_resid_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
     return fail(-2, "allreduce_resid_norm: cannot raise the dynamic shared memory limit");
   const int grid = rows < sm_count() ? rows : sm_count();
-  allreduce_resid_norm_kernel<<<grid, AR_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  // one 16-byte vector per thread where the row allows it: every remote load of a row is in flight at once
+  const int threads = std::min(AR_MAX_THREADS, std::max(256, (n / 8 + 31) / 32 * 32));
+  allreduce_resid_norm_kernel<<<grid, threads, smem, static_cast<cudaStream_t>(stream)>>>(p);
   return launch_check("allreduce_resid_norm", 1);
 }
 
