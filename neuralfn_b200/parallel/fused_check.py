@@ -42,10 +42,9 @@ def run_fused_check(device: torch.device | None = None, *, moe: bool = True) -> 
     errs: dict[str, float] = {}
     ctx = TensorParallelContext(dev, impl="fused")
 
-    rows, K, N = 256, 512, 768
-    while N % world or K % world:
-        N += 64
-        K += 64
+    # shapes every world size from 1 to 8 accepts: the gathered-weight product needs N / world to be a multiple of the
+    # 128-column tile, the reduce-scatter needs K / world to be a multiple of 8
+    rows, K, N = 256, 64 * max(world, 8), 128 * world * (3 if world <= 2 else 1)
     x = _rand((world * rows, K), 0, 0.5)
     w = _rand((N, K), 1, 0.05)
     b = _rand((N,), 2, 0.1)
