@@ -67,6 +67,28 @@ def case_gemm(args, m=None, n=None, k=None, a_mn=False, b_mn=False, tag="gemm"):
                    extra={"m": m, "n": n, "k": k, "a_mn": a_mn, "b_mn": b_mn})
 
 
+def case_skinny(args):
+    """Decode-sized products of a Glimmer 29B layer at TP 4 (32 rows): the mma.sync weight-streaming kernel against the tcgen05
+    split-K path, as fractions of the copy bandwidth."""
+    from neuralfn_b200.ops import _lib
+    from neuralfn_b200.ops.gemm import gemm
+    dev = torch.device("cuda")
+    L = _lib.load()
+    ws = torch.empty(32 * 1024 * 1024, device=dev, dtype=torch.float32)
+    out = []
+    for m, n, k in ((32, 2304, 6656), (32, 6656, 1024), (32, 12288, 6656), (32, 6656, 6144), (8, 12288, 6656), (64, 12288, 6656), (32, 4096, 4096)):
+        a = torch.randn(m, k, device=dev).bfloat16()
+        w = torch.randn(n, k, device=dev).bfloat16()
+        c = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        for impl in (2, 0):
+            old = L.nfn_gemm_skinny_set_impl(impl)
+            ms = time_kernel(lambda: gemm(a, w, out=c, workspace=ws), args.iters, args.warmup, args.flush)  # L2 flushed between calls
+            L.nfn_gemm_skinny_set_impl(old)
+            out.append(_report("skinny_mma" if impl else "skinny_tcgen05_splitk", ms, flops=2.0 * m * n * k, bytes_=2.0 * (n * k + m * k + m * n), args=args,
+                               extra={"m": m, "n": n, "k": k}))
+    return out
+
+
 def case_attention(args, backward=False):
     from neuralfn_b200.ops import kernels as K
     dev = torch.device("cuda")
@@ -253,7 +275,7 @@ def case_engine_decode(args):
 
 CASES = {"gemm": case_gemm, "attention_fwd": case_attention, "attention_bwd": lambda a: case_attention(a, True),
          "cross_entropy": case_cross_entropy, "norm": case_norm, "adamw": case_adamw, "decode_attention": case_decode_attention,
-         "kquant_gemv": case_kquant_gemv, "gemm_kquant": case_gemm_kquant, "block_attention": case_block_attention,
+         "skinny": case_skinny, "kquant_gemv": case_kquant_gemv, "gemm_kquant": case_gemm_kquant, "block_attention": case_block_attention,
          "turboquant_attention": case_turboquant_attention, "engine_decode": case_engine_decode}
 
 

@@ -1,0 +1,202 @@
+// Products with 3 to 64 rows (batched decode, verification blocks): C[M, N] = A[M, K] . B[N, K]^T with the GEMM family's
+// epilogue. Like the one- and two-row case this only streams the weight matrix once, so it is an HBM-bandwidth problem;
+// unlike it there are enough rows for the tensor cores to do the arithmetic, but far too few for a tcgen05 tile (128 rows
+// of A, of which at most half would be real). So: mma.sync.m16n8k16 with the token rows as the 16-row operand and eight
+// weight rows as the 8-column operand, every operand fragment fetched from global memory as ONE 16-byte load per lane.
+//
+// That works because a contraction does not care about the order of k. Inside a chunk of 32 k-values lane (g, j) - g = lane / 4,
+// j = lane % 4 - loads k = 8 j .. 8 j + 7 of weight row g (and of token rows g, g + 8): the four 32-bit words of that
+// load are exactly the fragment registers of two k16 steps (words 0 / 1 = the two k-pairs of step 0, words 2 / 3 = step 1),
+// with A and B using the same assignment. A warp's 32 lanes thus read 8 weight rows x 64 contiguous bytes per load.
+//
+// A CTA owns SK_NT * 8 weight rows; its eight warps split K between them (so a row's whole K range is in flight at
+// once and even narrow products fill the GPU), keep SK_UNROLL chunks of loads in flight each, and add their partial
+// tiles through shared memory; the last step applies alpha, bias, activation, residual and accumulate and stores bf16. The
+// token rows (M x K, a few hundred KB at most) are read by every CTA and stay in L1 / L2.
+//
+// Counterpart in the reference: the small-M tiles of its quantised decode path (`glimmer_k_mmq.cu:48-60`, mmvq / mmq
+// selection by row count); this kernel is the bf16-weight equivalent.
+#include <algorithm>
+
+#include "common.h"
+#include "nfn_kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace nfn {
+
+constexpr int SK_WARPS = 8, SK_THREADS = SK_WARPS * 32, SK_NT = 4, SK_ROWS = SK_NT * 8;
+
+struct SkinnyParams {
+  const __nv_bfloat16* a;
+  const __nv_bfloat16* b;
+  __nv_bfloat16* c;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* resid;
+  int m, n, k, lda, ldb, ldc, ld_resid;
+  int act, accum;
+  float alpha, act_param;
+};
+
+__device__ __forceinline__ uint4 sk_ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void sk_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float sk_act(float v, int act, float prm) {
+  switch (act) {
+    case NFN_ACT_GELU_TANH: return gelu_tanh_f(v);
+    case NFN_ACT_GELU_ERF: return gelu_erf_f(v);
+    case NFN_ACT_SILU: return silu_f(v);
+    case NFN_ACT_RELU2: { const float r = fmaxf(v, 0.f); return r * r; }
+    case NFN_ACT_RELU: return fmaxf(v, 0.f);
+    case NFN_ACT_TANH_CAP: return prm * fast_tanh(v / prm);
+    default: return v;
+  }
+}
+
+// MT = 16-row tiles of A (M <= 16 MT).
+template <int MT>
+__global__ void __launch_bounds__(SK_THREADS, MT <= 2 ? 2 : 1)
+gemm_skinny_kernel(const SkinnyParams p) {
+  constexpr int SK_UNROLL = MT <= 2 ? 4 : 2;  // chunks of weight loads in flight per warp (registers: 16 per chunk)
+  extern __shared__ float sk_part[];  // [SK_WARPS][MT * 16][SK_ROWS + 1]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, j = lane & 3;
+  const int n0 = blockIdx.x * SK_ROWS;
+  // this warp's share of the 32-wide k chunks
+  const int chunks = p.k / 32;
+  const int c_lo = (int)((long long)chunks * warp / SK_WARPS), c_hi = (int)((long long)chunks * (warp + 1) / SK_WARPS);
+
+  float acc[MT][SK_NT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < SK_NT; ++nt)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[mt][nt][q] = 0.f;
+
+  // weight rows of this lane (one per n-tile), clamped at the edge: a clamped row is computed twice and stored once
+  const __nv_bfloat16* wrow[SK_NT];
+#pragma unroll
+  for (int nt = 0; nt < SK_NT; ++nt) wrow[nt] = p.b + (size_t)min(n0 + nt * 8 + g, p.n - 1) * p.ldb + 8 * j;
+  // token rows g and g + 8 of every m-tile, clamped likewise (rows past M are never stored)
+  const __nv_bfloat16* arow[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    arow[mt][0] = p.a + (size_t)min(mt * 16 + g, p.m - 1) * p.lda + 8 * j;
+    arow[mt][1] = p.a + (size_t)min(mt * 16 + g + 8, p.m - 1) * p.lda + 8 * j;
+  }
+
+  for (int c0 = c_lo; c0 < c_hi; c0 += SK_UNROLL) {
+    uint4 w[SK_UNROLL][SK_NT];
+#pragma unroll
+    for (int u = 0; u < SK_UNROLL; ++u) {
+      const bool ok = c0 + u < c_hi;
+#pragma unroll
+      for (int nt = 0; nt < SK_NT; ++nt) w[u][nt] = ok ? sk_ld_stream(wrow[nt] + (size_t)(c0 + u) * 32) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < SK_UNROLL; ++u) {
+      if (c0 + u >= c_hi) break;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const uint4 x0 = __ldg(reinterpret_cast<const uint4*>(arow[mt][0] + (size_t)(c0 + u) * 32));
+        const uint4 x1 = __ldg(reinterpret_cast<const uint4*>(arow[mt][1] + (size_t)(c0 + u) * 32));
+#pragma unroll
+        for (int nt = 0; nt < SK_NT; ++nt) {
+          sk_mma(acc[mt][nt], x0.x, x1.x, x0.y, x1.y, w[u][nt].x, w[u][nt].y);
+          sk_mma(acc[mt][nt], x0.z, x1.z, x0.w, x1.w, w[u][nt].z, w[u][nt].w);
+        }
+      }
+    }
+  }
+
+  // partial tiles -> shared memory: accumulator (row g / g + 8, columns 2 j, 2 j + 1 of the n-tile)
+  constexpr int LD = SK_ROWS + 1;
+  float* mine = sk_part + (size_t)warp * (MT * 16) * LD;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < SK_NT; ++nt) {
+      const int col = nt * 8 + 2 * j;
+      mine[(mt * 16 + g) * LD + col] = acc[mt][nt][0];
+      mine[(mt * 16 + g) * LD + col + 1] = acc[mt][nt][1];
+      mine[(mt * 16 + g + 8) * LD + col] = acc[mt][nt][2];
+      mine[(mt * 16 + g + 8) * LD + col + 1] = acc[mt][nt][3];
+    }
+  __syncthreads();
+  // sum over the K slices and finish: alpha, bias, activation, residual, accumulate (the order of the tcgen05 kernels)
+  for (int i = threadIdx.x; i < p.m * SK_ROWS; i += SK_THREADS) {
+    const int r = i / SK_ROWS, col = i % SK_ROWS, n = n0 + col;
+    if (n >= p.n) continue;
+    float v = 0.f;
+#pragma unroll
+    for (int w8 = 0; w8 < SK_WARPS; ++w8) v += sk_part[((size_t)w8 * (MT * 16) + r) * LD + col];
+    v *= p.alpha;
+    if (p.bias) v += __bfloat162float(p.bias[n]);
+    v = sk_act(v, p.act, p.act_param);
+    if (p.resid) v += __bfloat162float(p.resid[(size_t)r * p.ld_resid + n]);
+    __nv_bfloat16* cp = p.c + (size_t)r * p.ldc + n;
+    if (p.accum) v += __bfloat162float(*cp);
+    *cp = __float2bfloat16(v);
+  }
+}
+
+static int g_skinny_mode = 1;
+
+// Returns 1 when it launched, 0 when the product is not one of its cases (the caller continues with the tcgen05 path),
+// negative on a launch error.
+int try_launch_skinny(const nfn_gemm_args& a, cudaStream_t stream) {
+  const int unsupported = NFN_EPI_SAVE_PRE | NFN_EPI_DACT | NFN_EPI_OUT_F32;
+  if (!g_skinny_mode || a.m < 3 || a.m > 64 || a.a_mn || a.b_mn || (a.flags & unsupported) || (a.k & 31) || a.k < 256 || (a.lda & 7) || (a.ldb & 7))
+    return 0;
+  // measured (12288 x 6656 weights, L2 flushed): 8 rows 49 us against 52 us on the tcgen05 split-K path, 32 rows 65 against
+  // 50 us, 64 rows 81 against 50 us - with more than one 16-row tile the token fragments, which every warp fetches from L2
+  // right before use, become the bottleneck. So by default only up to 16 rows come here; mode 2 forces every eligible product.
+  if (a.m > 16 && g_skinny_mode != 2) return 0;
+  // the weights must dominate the traffic for this to be the right kernel: N x K well above the token rows
+  if ((long long)a.n * a.k < (1LL << 20)) return 0;
+  SkinnyParams p;
+  p.a = static_cast<const __nv_bfloat16*>(a.a);
+  p.b = static_cast<const __nv_bfloat16*>(a.b);
+  p.c = static_cast<__nv_bfloat16*>(a.c);
+  p.bias = (a.flags & NFN_EPI_BIAS) ? static_cast<const __nv_bfloat16*>(a.bias) : nullptr;
+  p.resid = (a.flags & NFN_EPI_RESID) ? static_cast<const __nv_bfloat16*>(a.aux_in) : nullptr;
+  p.m = a.m; p.n = a.n; p.k = a.k; p.lda = a.lda; p.ldb = a.ldb; p.ldc = a.ldc; p.ld_resid = a.ld_aux_in;
+  p.act = (a.flags >> NFN_EPI_ACT_SHIFT) & 0xF;
+  p.accum = (a.flags & NFN_EPI_ACCUM) ? 1 : 0;
+  p.alpha = a.alpha; p.act_param = a.act_param;
+  const int grid = (a.n + SK_ROWS - 1) / SK_ROWS;
+  const int mt = (a.m + 15) / 16;
+  const size_t smem = (size_t)SK_WARPS * (mt <= 1 ? 16 : (mt <= 2 ? 32 : 64)) * (SK_ROWS + 1) * sizeof(float);
+  cudaError_t e = cudaSuccess;
+  if (mt <= 1) {
+    gemm_skinny_kernel<1><<<grid, SK_THREADS, smem, stream>>>(p);
+  } else if (mt <= 2) {
+    gemm_skinny_kernel<2><<<grid, SK_THREADS, smem, stream>>>(p);
+  } else {
+    static bool raised = false;
+    if (!raised) {
+      e = cudaFuncSetAttribute(gemm_skinny_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      raised = e == cudaSuccess;
+    }
+    if (e != cudaSuccess) return fail(-2, "gemm_skinny: cannot raise the dynamic shared memory limit");
+    gemm_skinny_kernel<4><<<grid, SK_THREADS, smem, stream>>>(p);
+  }
+  const int rc = launch_check("gemm_skinny", 1);
+  return rc == 0 ? 1 : rc;
+}
+
+}  // namespace nfn
+
+// 1 (default): products with 3 - 16 rows over K-major operands take the mma.sync weight-streaming kernel; 2: up to 64 rows do;
+// 0: none (the tcgen05 split-K path). Returns the previous setting.
+extern "C" int nfn_gemm_skinny_set_impl(int mode) {
+  const int prev = nfn::g_skinny_mode;
+  nfn::g_skinny_mode = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
+  return prev;
+}

@@ -145,6 +145,7 @@ int try_launch_gemm_pair(const nfn_gemm_args& a, cudaStream_t stream);  // gemm_
 // CTA-pair (cta_group::2) kernel for eligible K-major products: -1 = read NFN_GEMM_PAIR once.
 static int g_pair_mode = -1;
 int try_launch_gemv(const nfn_gemm_args& a, cudaStream_t stream);  // gemv_bf16.cu
+int try_launch_skinny(const nfn_gemm_args& a, cudaStream_t stream);  // gemm_skinny.cu
 static int g_gemv_mode = 1;
 static int gemv_mode() { return g_gemv_mode; }
 
@@ -199,6 +200,10 @@ extern "C" int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream_) {
 
   if (a.m <= 2 && gemv_mode() != 0) {  // one or two rows: pure weight streaming (gemv_bf16.cu)
     const int rc = try_launch_gemv(a, stream);
+    if (rc != 0) return rc < 0 ? rc : 0;
+  }
+  if (a.m >= 3 && a.m <= 64) {  // a handful of rows over a large weight matrix: mma.sync weight streaming (gemm_skinny.cu)
+    const int rc = try_launch_skinny(a, stream);
     if (rc != 0) return rc < 0 ? rc : 0;
   }
   const int sms = sm_count();

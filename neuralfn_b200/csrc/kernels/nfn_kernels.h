@@ -215,6 +215,10 @@ int nfn_kv_commit_layers(const void* const* stage_k, const void* const* stage_v,
                          const int* caps, const int* lengths, const int* accepted, int n_layers, int B, int rows, int n_kv_heads,
                          int head_dim, nfn_stream_t stream);
 
+// Products with a few rows over large K-major weights (decode batches, verification blocks): 1 (default) = 3 - 16 rows take the
+// mma.sync weight-streaming kernel of gemm_skinny.cu, 2 = up to 64 rows do, 0 = none (tcgen05 split-K path). Returns the previous setting.
+int nfn_gemm_skinny_set_impl(int mode);
+
 // Hidden-state taps: row r of x (bf16 [rows, ldx], C columns used) belongs to sequence r / block_rows and is copied to
 // position lengths[sequence] + r % block_rows + pos_offset of dst [sequences][max_pos][C] (slot_stride elements between
 // sequences). live_rows (optional): rows at or past live_rows[sequence] are skipped. Positions outside [0, max_pos) are skipped.

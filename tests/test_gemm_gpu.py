@@ -188,3 +188,44 @@ def test_gemm_cta_pair_mn_major_b(kernel_lib, m, n, k):
         assert (y.float() - y1.float()).abs().max().item() <= 0.02 * base.abs().max().item()
     finally:
         L.nfn_gemm_set_pair_mode(old)
+
+
+@pytest.mark.parametrize("m", [3, 8, 17, 32, 33, 64])
+@pytest.mark.parametrize("n,k", [(6656, 1024), (2304, 6656), (1000, 1056)])
+def test_skinny_products_take_the_weight_streaming_mma_kernel(kernel_lib, m, n, k):
+    """3 - 64 rows over a large K-major weight matrix: mma.sync with permuted-k fragments, in-CTA split-K, fused epilogue.
+    Checked against fp32 and against the tcgen05 split-K path it replaces."""
+    from neuralfn_b200.ops import _lib
+    from neuralfn_b200.ops.gemm import gemm
+    torch.manual_seed(m * 13 + n)
+    a = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+    bias = (torch.randn(n, device="cuda") * 0.1).bfloat16()
+    resid = torch.randn(m, n, device="cuda").bfloat16()
+    ws = torch.empty(32 * 1024 * 1024, device="cuda", dtype=torch.float32)
+    L = _lib.load()
+    forced = L.nfn_gemm_skinny_set_impl(2)                         # every eligible row count (the default stops at 16 rows)
+    before = _lib.launch_count()
+    ref = a.float() @ w.float().t()
+    y = gemm(a, w, workspace=ws)
+    assert _lib.launch_count() - before == 1                       # one launch: no separate split-K reduction
+    _close(y, ref, k)
+    out = gemm(a, w, bias=bias, act="silu", resid=resid, workspace=ws)
+    _close(out, torch.nn.functional.silu(ref + bias.float()) + resid.float(), k)
+    acc = resid.clone()
+    gemm(a, w, out=acc, accum=True, alpha=0.5, workspace=ws)
+    _close(acc, resid.float() + 0.5 * ref, k)
+    # strided views: rows of a wider buffer in, columns of a wider buffer out
+    wide_in = torch.zeros(m, k + 64, device="cuda", dtype=torch.bfloat16)
+    wide_in[:, :k] = a
+    wide_out = torch.zeros(m, n + 128, device="cuda", dtype=torch.bfloat16)
+    gemm(wide_in[:, :k], w, out=wide_out[:, 64:64 + n], workspace=ws)
+    _close(wide_out[:, 64:64 + n], ref, k)
+    assert float(wide_out[:, :64].abs().max()) == 0.0 and float(wide_out[:, 64 + n:].abs().max()) == 0.0
+    L.nfn_gemm_skinny_set_impl(0)
+    try:
+        tc = gemm(a, w, bias=bias, act="silu", resid=resid, workspace=ws)
+    finally:
+        L.nfn_gemm_skinny_set_impl(forced)
+    torch.testing.assert_close(out.float(), tc.float(), atol=4e-2, rtol=4e-2)
+    _lib.assert_status_ok("skinny gemm")
