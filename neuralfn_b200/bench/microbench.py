@@ -80,11 +80,11 @@ def case_skinny(args):
         a = torch.randn(m, k, device=dev).bfloat16()
         w = torch.randn(n, k, device=dev).bfloat16()
         c = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
-        for impl in (2, 0):
+        for impl in ((3, 2, 0) if m <= 32 else (2, 0)):
             old = L.nfn_gemm_skinny_set_impl(impl)
             ms = time_kernel(lambda: gemm(a, w, out=c, workspace=ws), args.iters, args.warmup, args.flush)  # L2 flushed between calls
             L.nfn_gemm_skinny_set_impl(old)
-            out.append(_report("skinny_mma" if impl else "skinny_tcgen05_splitk", ms, flops=2.0 * m * n * k, bytes_=2.0 * (n * k + m * k + m * n), args=args,
+            out.append(_report({3: "skinny_mma_resident_cluster", 2: "skinny_mma", 0: "skinny_tcgen05_splitk"}[impl], ms, flops=2.0 * m * n * k, bytes_=2.0 * (n * k + m * k + m * n), args=args,
                                extra={"m": m, "n": n, "k": k}))
     return out
 

@@ -26,6 +26,7 @@ def _add_train_flags(p: argparse.ArgumentParser) -> None:
     p.add_argument("--head-dim", type=int, default=0, help="muse-glimmer: attention head width (0: d_model / n_head)")
     p.add_argument("--activation-checkpoint-interval", type=int, default=0,
                    help="muse-glimmer native engine: resident layers per recomputed segment (0: keep every activation)")
+    p.add_argument("--dpo-label-smoothing", type=float, default=0.0, help="--objective dpo, sigmoid loss: weight of the flipped preference")
     p.add_argument("--init-from", default="", help="--objective sft|dpo: named checkpoint directory whose weights start the run")
     p.add_argument("--template-name", default="gpt2")
     p.add_argument("--dataset", default="", help="dataset alias, directory or shard file (empty: synthetic uniform tokens)")
@@ -86,7 +87,19 @@ def _train_config(a):
         eval_every=a.eval_every, eval_batches=a.eval_batches, train_loss_every=a.train_loss_every, progress_every=a.progress_every,
         checkpoint_every=a.checkpoint_every, seed=a.seed, resume=a.resume, use_cuda_graph=not a.no_cuda_graph,
         objective=a.objective, head_dim=a.head_dim, activation_checkpoint_interval=a.activation_checkpoint_interval, extra_paths={"init_from": a.init_from} if a.init_from else {},
-        extra=_native_adapter_options(a))
+        extra={**_native_adapter_options(a), **_native_objective_options(a)})
+
+
+def _native_objective_options(a) -> dict:
+    """--objective dpo: the preference loss of the native Glimmer engine (sigmoid with optional label smoothing, hinge, IPO)."""
+    if getattr(a, "objective", "ar") != "dpo":
+        return {}
+    out = {"dpo_label_smoothing": float(getattr(a, "dpo_label_smoothing", 0.0) or 0.0)}
+    if getattr(a, "dpo_beta", None) is not None:
+        out["dpo_beta"] = float(a.dpo_beta)
+    if getattr(a, "dpo_loss_type", None):
+        out["dpo_loss_type"] = a.dpo_loss_type
+    return out
 
 
 def _native_adapter_options(a) -> dict:

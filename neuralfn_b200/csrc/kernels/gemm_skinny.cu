@@ -17,6 +17,7 @@
 // Counterpart in the reference: the small-M tiles of its quantised decode path (`glimmer_k_mmq.cu:48-60`, mmvq / mmq
 // selection by row count); this kernel is the bf16-weight equivalent.
 #include <algorithm>
+#include <cstdint>
 
 #include "common.h"
 #include "nfn_kernels.h"
@@ -146,6 +147,179 @@ gemm_skinny_kernel(const SkinnyParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Up to 32 rows, opt-in (mode 3): the token fragments live in REGISTERS for the whole kernel.
+//
+// With more than one 16-row tile the kernel above re-reads the token rows from L2 for every eight weight rows (32 rows x K
+// against 8 rows x K of weights: four times the DRAM traffic), and that is what it waits for. Here a warp owns a fixed k
+// range of at most RS_UMAX chunks for the whole kernel and loads its token fragments once (8 * MT * RS_UMAX registers); all
+// it does afterwards is stream weight rows: per group of eight rows one 16-byte load per lane and chunk (the next group's
+// loads are issued before the current group's mma), 4 * MT * chunks mma, and a sum over the CTA's eight warps through
+// shared memory into the CTA's fp32 strip [rows, columns of this CTA].
+//
+// K is longer than 8 warps x RS_UMAX chunks, so S CTAs split it: they form a thread-block cluster, each fills its strip for
+// the same weight rows, and after a cluster barrier CTA r sums column share r of all S strips over distributed shared
+// memory in rank order (deterministic), applies the epilogue and stores bf16. No workspace, no second launch.
+constexpr int RS_MAX_COLS = 512;       // most columns (weight rows) per pass of a cluster: strip = MT * 16 x 512 fp32
+
+__device__ __forceinline__ uint32_t rs_cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void rs_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float rs_ld_peer(const float* local, uint32_t rank) {
+  uint32_t a = (uint32_t)__cvta_generic_to_shared(local), ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+  return v;
+}
+
+template <int MT, int UMAX>
+__global__ void __launch_bounds__(SK_THREADS, 1)
+gemm_skinny_resident_kernel(const SkinnyParams p, const int S, const int pass_cols, const int passes_total) {
+  constexpr int ROWS = MT * 16;
+  __shared__ float part[2][SK_WARPS][ROWS][8];              // one group's partial tile of every warp, double-buffered
+  extern __shared__ float strip[];                          // [ROWS][pass_cols]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, j = lane & 3;
+  const uint32_t ks = rs_cluster_ctarank();
+  const int cluster = blockIdx.x / S, n_clusters = gridDim.x / S;
+  // this warp's chunks of 32 k-values: slice ks * 8 + warp of S * 8
+  const int chunks = p.k / 32, slices = S * SK_WARPS, sl = (int)ks * SK_WARPS + warp;
+  const int c_lo = (int)((long long)chunks * sl / slices), cnt = (int)((long long)chunks * (sl + 1) / slices) - c_lo;
+
+  uint4 xa[UMAX][MT][2];
+#pragma unroll
+  for (int u = 0; u < UMAX; ++u)
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int r = mt * 16 + g + 8 * h;
+        xa[u][mt][h] = (u < cnt && r < p.m) ? __ldg(reinterpret_cast<const uint4*>(p.a + (size_t)r * p.lda + (size_t)(c_lo + u) * 32 + 8 * j))
+                                             : make_uint4(0u, 0u, 0u, 0u);
+      }
+  const __nv_bfloat16* wbase = p.b + (size_t)c_lo * 32 + 8 * j;
+
+  auto load_group = [&](uint4 (&w)[UMAX], int n0) {
+    const __nv_bfloat16* row = wbase + (size_t)min(n0 + g, p.n - 1) * p.ldb;      // clamped: computed twice, stored once
+#pragma unroll
+    for (int u = 0; u < UMAX; ++u)
+      if (u < cnt) w[u] = sk_ld_stream(row + (size_t)u * 32);
+  };
+  auto do_group = [&](const uint4 (&w)[UMAX], int col0, int buf) {
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[mt][q] = 0.f;
+#pragma unroll
+    for (int u = 0; u < UMAX; ++u)
+      if (u < cnt) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          sk_mma(acc[mt], xa[u][mt][0].x, xa[u][mt][1].x, xa[u][mt][0].y, xa[u][mt][1].y, w[u].x, w[u].y);
+          sk_mma(acc[mt], xa[u][mt][0].z, xa[u][mt][1].z, xa[u][mt][0].w, xa[u][mt][1].w, w[u].z, w[u].w);
+        }
+      }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      *reinterpret_cast<float2*>(&part[buf][warp][mt * 16 + g][2 * j]) = make_float2(acc[mt][0], acc[mt][1]);
+      *reinterpret_cast<float2*>(&part[buf][warp][mt * 16 + g + 8][2 * j]) = make_float2(acc[mt][2], acc[mt][3]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < ROWS * 8; i += SK_THREADS) {
+      const int r = i >> 3, c = i & 7;
+      float v = 0.f;
+#pragma unroll
+      for (int w8 = 0; w8 < SK_WARPS; ++w8) v += part[buf][w8][r][c];
+      strip[r * pass_cols + col0 + c] = v;
+    }
+  };
+
+  for (int pass = cluster; pass < passes_total; pass += n_clusters) {     // the same trip count in every CTA of a cluster
+    const int n_pass = pass * pass_cols;
+    const int cols = min(pass_cols, p.n - n_pass), groups = (cols + 7) / 8;
+    uint4 w0[UMAX], w1[UMAX];
+    load_group(w0, n_pass);
+    for (int gi = 0; gi < groups; gi += 2) {
+      if (gi + 1 < groups) load_group(w1, n_pass + (gi + 1) * 8);
+      do_group(w0, gi * 8, 0);
+      if (gi + 2 < groups) load_group(w0, n_pass + (gi + 2) * 8);
+      if (gi + 1 < groups) do_group(w1, (gi + 1) * 8, 1);
+    }
+    rs_cluster_sync();                                                    // every strip of the cluster is complete
+    // CTA ks finishes columns [share_lo, share_hi) of the pass
+    const int share_lo = (int)((long long)cols * ks / S), share_hi = (int)((long long)cols * (ks + 1) / S), width = share_hi - share_lo;
+    for (int i = threadIdx.x; i < p.m * width; i += SK_THREADS) {
+      const int r = i / width, c = share_lo + i % width, n = n_pass + c;
+      float v = 0.f;
+      for (int s2 = 0; s2 < S; ++s2) v += rs_ld_peer(&strip[r * pass_cols + c], (uint32_t)s2);
+      v *= p.alpha;
+      if (p.bias) v += __bfloat162float(p.bias[n]);
+      v = sk_act(v, p.act, p.act_param);
+      if (p.resid) v += __bfloat162float(p.resid[(size_t)r * p.ld_resid + n]);
+      __nv_bfloat16* cp = p.c + (size_t)r * p.ldc + n;
+      if (p.accum) v += __bfloat162float(*cp);
+      *cp = __float2bfloat16(v);
+    }
+    rs_cluster_sync();                                                    // nobody overwrites a strip a peer still reads
+  }
+}
+
+template <int MT, int UMAX>
+static int launch_skinny_resident(const SkinnyParams& p, cudaStream_t stream) {
+  auto kern = gemm_skinny_resident_kernel<MT, UMAX>;
+  const int chunks = p.k / 32;
+  const int S = (chunks + SK_WARPS * UMAX - 1) / (SK_WARPS * UMAX);
+  if (S > 8) return 0;                                                   // portable cluster size
+  const size_t smem = (size_t)MT * 16 * RS_MAX_COLS * sizeof(float);
+  static int max_clusters[64][9] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = S;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.blockDim = dim3(SK_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int& mc = max_clusters[dev & 63][S];
+  if (!mc) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      cudaGetLastError();
+      return 0;
+    }
+    cfg.gridDim = dim3(sm_count() / S * S, 1, 1);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      mc = -1;
+    } else {
+      mc = std::min(n, sm_count() / S);
+    }
+  }
+  if (mc <= 0) return 0;
+  // passes of equal width, a whole number of them per cluster: groups of eight weight rows, at most RS_MAX_COLS columns per pass
+  const int groups = (p.n + 7) / 8, max_groups = RS_MAX_COLS / 8;
+  const int clusters = std::min(mc, groups);
+  const int per_cluster = (groups + clusters - 1) / clusters;                       // groups one cluster works through
+  const int passes_per_cluster = (per_cluster + max_groups - 1) / max_groups;
+  const int pass_cols = (per_cluster + passes_per_cluster - 1) / passes_per_cluster * 8;
+  const int passes = (p.n + pass_cols - 1) / pass_cols;
+  cfg.gridDim = dim3(std::min(clusters, passes) * S, 1, 1);
+  if (cudaLaunchKernelEx(&cfg, kern, p, S, pass_cols, passes) != cudaSuccess) return launch_check("gemm_skinny_resident", 0);
+  const int rc = launch_check("gemm_skinny_resident", 1);
+  return rc == 0 ? 1 : rc;
+}
+
 static int g_skinny_mode = 1;
 
 // Returns 1 when it launched, 0 when the product is not one of its cases (the caller continues with the tcgen05 path),
@@ -157,9 +331,12 @@ int try_launch_skinny(const nfn_gemm_args& a, cudaStream_t stream) {
   // measured (12288 x 6656 weights, L2 flushed): 8 rows 49 us against 52 us on the tcgen05 split-K path, 32 rows 65 against
   // 50 us, 64 rows 81 against 50 us - with more than one 16-row tile the token fragments, which every warp fetches from L2
   // right before use, become the bottleneck. So by default only up to 16 rows come here; mode 2 forces every eligible product.
-  if (a.m > 16 && g_skinny_mode != 2) return 0;
+  // The register-resident cluster form (mode 3) removes those re-reads and is still slower: 65.5 us at 32 rows, 53.3 us at
+  // 8 rows - one group of loads ahead (28 KB per SM, all the registers allow) does not cover the DRAM latency.
   // the weights must dominate the traffic for this to be the right kernel: N x K well above the token rows
   if ((long long)a.n * a.k < (1LL << 20)) return 0;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b)) & 15) == 0;
+  if (!aligned) return 0;
   SkinnyParams p;
   p.a = static_cast<const __nv_bfloat16*>(a.a);
   p.b = static_cast<const __nv_bfloat16*>(a.b);
@@ -170,8 +347,14 @@ int try_launch_skinny(const nfn_gemm_args& a, cudaStream_t stream) {
   p.act = (a.flags >> NFN_EPI_ACT_SHIFT) & 0xF;
   p.accum = (a.flags & NFN_EPI_ACCUM) ? 1 : 0;
   p.alpha = a.alpha; p.act_param = a.act_param;
-  const int grid = (a.n + SK_ROWS - 1) / SK_ROWS;
   const int mt = (a.m + 15) / 16;
+  // mode 3: the register-resident cluster form for every product up to 32 rows (measured slower than both other paths, see above)
+  if (g_skinny_mode == 3 && mt <= 2) {
+    const int rc = mt == 2 ? launch_skinny_resident<2, 7>(p, stream) : launch_skinny_resident<1, 8>(p, stream);
+    if (rc != 0) return rc;
+  }
+  if (a.m > 16 && g_skinny_mode != 2) return 0;
+  const int grid = (a.n + SK_ROWS - 1) / SK_ROWS;
   const size_t smem = (size_t)SK_WARPS * (mt <= 1 ? 16 : (mt <= 2 ? 32 : 64)) * (SK_ROWS + 1) * sizeof(float);
   cudaError_t e = cudaSuccess;
   if (mt <= 1) {
@@ -193,10 +376,11 @@ int try_launch_skinny(const nfn_gemm_args& a, cudaStream_t stream) {
 
 }  // namespace nfn
 
-// 1 (default): products with 3 - 16 rows over K-major operands take the mma.sync weight-streaming kernel; 2: up to 64 rows do;
-// 0: none (the tcgen05 split-K path). Returns the previous setting.
+// 1 (default): products with 3 - 16 rows over K-major operands take the mma.sync weight-streaming kernel; 2: up to 64 rows
+// do; 3: products up to 32 rows take its register-resident cluster form; 0: none (the tcgen05 split-K path). Returns the
+// previous setting.
 extern "C" int nfn_gemm_skinny_set_impl(int mode) {
   const int prev = nfn::g_skinny_mode;
-  nfn::g_skinny_mode = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
+  nfn::g_skinny_mode = mode < 0 ? 0 : (mode > 3 ? 3 : mode);
   return prev;
 }

@@ -80,6 +80,8 @@ class GlimmerConfig:
     z_loss: float = 0.0
     vocab_pad_to: int = 128
     dpo_beta: float = 0.1
+    dpo_loss_type: str = "sigmoid"                 # sigmoid | hinge | ipo
+    dpo_label_smoothing: float = 0.0                # sigmoid only: weight of the flipped preference
     reward_head: bool = False
     value_head: bool = False
     ppo_clip: float = 0.2
@@ -250,6 +252,26 @@ def glimmer_reference_loss(cfg: GlimmerConfig, p: dict[str, torch.Tensor], token
     return (rows * m).sum() / m.sum().clamp(min=1.0), logits, rows
 
 
+DPO_LOSS_TYPES = ("sigmoid", "hinge", "ipo")
+
+
+def dpo_pair_terms(z: torch.Tensor, *, beta: float, loss_type: str = "sigmoid", label_smoothing: float = 0.0):
+    """Per-pair preference loss and its derivative for ``z = beta * ((pol_c - pol_r) - (ref_c - ref_r))``: ``(loss [P], d loss / d z [P])``.
+    The three forms of the reference's ``dpo_pairwise_loss`` node (neuralfn/torch_backend.py, ``DPOPairwiseLossStage``): sigmoid
+    ``-log sigmoid(z)`` (with label smoothing e: ``-(1 - e) log sigmoid(z) - e log sigmoid(-z)``), hinge ``relu(1 - z)`` and IPO
+    ``(z - 1 / (2 beta))^2``. Written out by hand because the native engine has no autograd."""
+    if loss_type == "hinge":
+        return torch.relu(1.0 - z), -(z < 1.0).to(z.dtype)
+    if loss_type == "ipo":
+        d = z - 1.0 / (2.0 * max(float(beta), 1e-8))
+        return d * d, 2.0 * d
+    if loss_type != "sigmoid":
+        raise ValueError(f"dpo loss type {loss_type!r}: one of {DPO_LOSS_TYPES}")
+    e = float(label_smoothing)
+    sp = torch.nn.functional.softplus
+    return (1.0 - e) * sp(-z) + e * sp(z), -(1.0 - e) * torch.sigmoid(-z) + e * torch.sigmoid(z)
+
+
 def ppo_terms_and_gradients(logp, logp_old, advantages, returns, value, value_old, mask, *, clip: float, vf_coef: float,
                             normalize_advantages: bool = True) -> dict[str, torch.Tensor]:
     """The clipped-surrogate policy term and the clipped value term over the rows with ``mask`` > 0 (masked means), and
@@ -337,6 +359,8 @@ class GlimmerEngine:
         self.scratch = e(max(64 * 2 * max(2 * Fd, Q + A, C), K.norm_fused_rows() * 3 * C), dtype=f32)
         self.ws = e(32 * 1024 * 1024, dtype=f32)
         self.tokens = torch.zeros(N, device=dev, dtype=torch.int32)
+        self.tok_sorted = torch.zeros(N, device=dev, dtype=torch.int32)      # stable sort of the batch's tokens: the token-embedding gradient
+        self.tok_order = torch.zeros(N, device=dev, dtype=torch.int64)       # sums equal tokens in row order (bitwise reproducible)
         self.targets = torch.zeros(N, device=dev, dtype=torch.int32)
         # objective state
         self.objective = "ar"
@@ -516,13 +540,14 @@ class GlimmerEngine:
         self.seq_logps.neg_()
         pol, ref = self.seq_logps, self.ref_logps
         margin = self.cfg.dpo_beta * ((pol[:half] - pol[half:]) - (ref[:half] - ref[half:]))
-        self.dpo_stats[0] = torch.nn.functional.softplus(-margin).mean()
+        per, d_per = dpo_pair_terms(margin, beta=self.cfg.dpo_beta, loss_type=self.cfg.dpo_loss_type, label_smoothing=self.cfg.dpo_label_smoothing)
+        self.dpo_stats[0] = per.mean()
         self.dpo_stats[1] = (margin > 0).float().mean()
         self.dpo_stats[2] = margin.mean()
         self.loss.copy_(self.dpo_stats[:1])
         if compute_grad:
-            # d loss / d logp_chosen = -beta * sigmoid(-margin) / pairs, the opposite for rejected; logp = -sum(row loss)
-            coef = self.cfg.dpo_beta * torch.sigmoid(-margin) / half
+            # d loss / d logp_chosen = beta * (d loss / d z) / pairs, the opposite for rejected; logp = -sum(row loss)
+            coef = -self.cfg.dpo_beta * d_per / half
             per_seq = torch.cat([coef, -coef])                      # d loss / d (sum of row losses) per sequence
             torch.mul(self.loss_mask.view(self.B, self.T), per_seq.unsqueeze(1), out=self.row_scale.view(self.B, self.T))
             keep = self.loss.clone()
@@ -660,7 +685,8 @@ class GlimmerEngine:
             # weightless norm of the embeddings, then the scatter into the table
             K.norm_backward(dx, self.xe, self.ones, None, self.re, None, None, sc, out=spare, **rms)
             g["tok_embeddings"].zero_()
-            K.embedding_backward(spare, self.tokens, g["tok_embeddings"], None, B=B, T=T)
+            st_, od_ = K.sort_tokens(self.tokens, self.tok_sorted, self.tok_order)
+            K.embedding_backward(spare, self.tokens, g["tok_embeddings"], None, B=B, T=T, sorted_tokens=st_, order=od_)
 
     def logits_view(self) -> torch.Tensor:
         return self.logits.view(self.B, self.T, -1)[..., :self.cfg.vocab_size]

@@ -322,6 +322,8 @@ class GPT2Engine:
         self.scratch = e(max(64 * 2 * max(Hd, 3 * C), K.norm_fused_rows() * 3 * C), dtype=f32)
         self.ws = e(32 * 1024 * 1024, dtype=f32)  # split-K partial slices of the weight-gradient GEMMs
         self.tokens = torch.zeros(N, device=dev, dtype=torch.int32)
+        self.tok_sorted = torch.zeros(N, device=dev, dtype=torch.int32)      # stable sort of the batch's tokens: the token-embedding gradient
+        self.tok_order = torch.zeros(N, device=dev, dtype=torch.int64)       # sums equal tokens in row order (bitwise reproducible)
         self.targets = torch.zeros(N, device=dev, dtype=torch.int32)
         self.timer = None  # optional utils.stage_timing.StageTimer (eager runs only)
         # MLP activation in effect (epilogue name of the FC GEMM and its derivative in the projection's input-gradient GEMM)
@@ -484,7 +486,8 @@ class GPT2Engine:
             if self.grad_ready_hook is not None and l % self.grad_bucket_layers == 0:
                 self.grad_ready_hook(*self._layer_range(l, min(l + self.grad_bucket_layers, cfg.n_layer) - 1))
         with st("embedding_backward"):
-            K.embedding_backward(dx, self.tokens, g["wte"], g["wpe"][:T], B=B, T=T)
+            st_, od_ = K.sort_tokens(self.tokens, self.tok_sorted, self.tok_order)
+            K.embedding_backward(dx, self.tokens, g["wte"], g["wpe"][:T], B=B, T=T, sorted_tokens=st_, order=od_)
         if T < cfg.max_seq_len:
             g["wpe"][T:].zero_()
 

@@ -212,6 +212,8 @@ class LlamaEngine:
         self.scratch = e(max(64 * 2 * max(2 * Fd, Q, C), K.norm_fused_rows() * 3 * C), dtype=f32)
         self.ws = e(32 * 1024 * 1024, dtype=f32)
         self.tokens = torch.zeros(N, device=dev, dtype=torch.int32)
+        self.tok_sorted = torch.zeros(N, device=dev, dtype=torch.int32)      # stable sort of the batch's tokens: the token-embedding gradient
+        self.tok_order = torch.zeros(N, device=dev, dtype=torch.int64)       # sums equal tokens in row order (bitwise reproducible)
         self.targets = torch.zeros(N, device=dev, dtype=torch.int32)
 
     def _views(self, t):
@@ -302,7 +304,8 @@ class LlamaEngine:
             dx, spare = spare, dx
         self.d_input = dx  # gradient w.r.t. this stage's input (sent to the previous stage)
         if cfg.pp_first:
-            K.embedding_backward(dx, self.tokens, g["tok_embeddings"], None, B=B, T=T)
+            st_, od_ = K.sort_tokens(self.tokens, self.tok_sorted, self.tok_order)
+            K.embedding_backward(dx, self.tokens, g["tok_embeddings"], None, B=B, T=T, sorted_tokens=st_, order=od_)
 
     def set_batch(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
         self.tokens.copy_(tokens.reshape(-1), non_blocking=True)

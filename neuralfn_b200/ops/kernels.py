@@ -296,12 +296,33 @@ def embedding_forward(tokens, wte, wpe, *, T: int, out=None):
     return out
 
 
-def embedding_backward(dout, tokens, dwte, dwpe, *, B: int, T: int, accumulate_wpe: bool = False):
+def sort_tokens(tokens, sorted_out=None, order_out=None):
+    """Stable sort of a batch's token ids: (ids ascending [int32], row each came from [int64]). Equal tokens keep their row order,
+    which is what makes ``embedding_backward`` sum them in the same order on every run. With the two output buffers nothing the
+    caller keeps is allocated (safe inside a captured graph)."""
+    flat = tokens.reshape(-1)
+    if sorted_out is None:
+        return torch.sort(flat, stable=True)
+    torch.sort(flat, stable=True, out=(sorted_out, order_out))
+    return sorted_out, order_out
+
+
+def embedding_backward(dout, tokens, dwte, dwpe, *, B: int, T: int, accumulate_wpe: bool = False, sorted_tokens=None, order=None):
+    """Adds the token-embedding gradient onto ``dwte`` (and writes ``dwpe``). With ``sorted_tokens`` / ``order`` (``sort_tokens`` of the
+    batch, e.g. prepared when the batch was uploaded) rows of equal tokens are summed in row order by one block each: bitwise
+    reproducible. Without them the sort happens here."""
     C = dout.shape[1]
     vocab = dwte.shape[0] if dwte is not None else 0
-    rc = _lib.load().nfn_embedding_backward(_p(dout), _p(tokens), _p(dwte), _p(dwpe), c_int(B), c_int(T),
-                                            c_int(C), c_int(vocab), c_int(int(accumulate_wpe)), _st())
-    _lib.check(rc, "nfn_embedding_backward")
+    L = _lib.load()
+    if dwpe is not None:
+        rc = L.nfn_embedding_backward(_p(dout), _p(tokens), _p(None), _p(dwpe), c_int(B), c_int(T), c_int(C), c_int(vocab),
+                                      c_int(int(accumulate_wpe)), _st())
+        _lib.check(rc, "nfn_embedding_backward")
+    if dwte is not None:
+        if sorted_tokens is None or order is None:
+            sorted_tokens, order = sort_tokens(tokens)
+        rc = L.nfn_embedding_backward_sorted(_p(dout), _p(sorted_tokens), _p(order), _p(dwte), c_int(B * T), c_int(C), c_int(vocab), _st())
+        _lib.check(rc, "nfn_embedding_backward_sorted")
 
 
 # ----------------------------------------------------------------- optimizer --

@@ -48,7 +48,7 @@ KERNELS: tuple[KernelEntry, ...] = (
     _k("rmsnorm + residual", "nfn_rmsnorm_residual"), _k("qk_norm", "nfn_qk_norm_forward"), _k("qk_norm backward", "nfn_qk_norm_backward"),
     _k("rope", "nfn_rope_inplace"), _k("qk_norm + rope", "nfn_qk_norm_rope_forward"),
     _k("cross_entropy", "nfn_cross_entropy", ("bf16",), False, "soft-cap derivative, z-loss, in-place gradient"),
-    _k("embedding forward", "nfn_embedding_forward"), _k("embedding backward", "nfn_embedding_backward"),
+    _k("embedding forward", "nfn_embedding_forward"), _k("embedding backward", "nfn_embedding_backward"), _k("embedding backward, sorted tokens (deterministic)", "nfn_embedding_backward_sorted"),
     _k("embedding + positions", "nfn_embedding_positions"), _k("swiglu", "nfn_swiglu_forward"), _k("swiglu backward", "nfn_swiglu_backward"),
     _k("sigmoid gate", "nfn_sigmoid_gate_inplace"), _k("bias gradient (column sum)", "nfn_colsum"),
     _k("adamw (flat, clip on device)", "nfn_adamw_flat", ("fp32 master", "bf16 params")), _k("grad clip scale", "nfn_grad_clip_scale"),

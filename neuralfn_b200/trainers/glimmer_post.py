@@ -84,9 +84,11 @@ class GlimmerPostTrainer:
     @torch.no_grad()
     def ppo_rollout(self, prompts: torch.Tensor, reward, *, max_new_tokens: int = 16, temperature: float = 1.0, top_k: int = 0,
                     gamma: float = 1.0, gae_lambda: float = 0.95, eos_token_id: int | None = None, pad_token_id: int = 0,
-                    generator: torch.Generator | None = None) -> dict:
+                    generator: torch.Generator | None = None, kl_coef: float = 0.0) -> dict:
         """Samples continuations of ``prompts`` [B, P] with the current policy, scores them with ``reward(ids, P) -> [B]``
-        (added at the last response token) and returns the per-row rollout the ``ppo`` objective consumes."""
+        (added at the last response token) and returns the per-row rollout the ``ppo`` objective consumes. ``kl_coef > 0``
+        shapes the per-token rewards with ``-kl_coef * (log p_policy - log p_reference)`` against the parameters kept by
+        ``freeze_reference`` (called here on first use: the reference is then the policy before its first update)."""
         from ..tensor.ppo import gae_advantages, sample_continuations
         eng = self.engine
         dev = self.trainer.device
@@ -107,13 +109,37 @@ class GlimmerPostTrainer:
         eng.forward(compute_grad_logits=False)                           # the ppo objective fills row losses and values
         logp_old, values = (-eng.row_loss).view(B, eng.T).clone(), eng.values.view(B, eng.T).clone()
         rewards = torch.zeros(B, max_new_tokens, device=dev)
+        kl = torch.zeros(B, device=dev)
+        if kl_coef > 0.0:
+            per_token = (logp_old - self._reference_logp())[:, P - 1:L] * mask
+            rewards -= kl_coef * per_token
+            kl = per_token.sum(1)
         last = (mask.sum(1).long() - 1).clamp(min=0)
         score = reward(ids, P).float().to(dev)
         rewards[torch.arange(B, device=dev), last] += score
         adv, ret = gae_advantages(rewards, values[:, P - 1:L] * mask, mask, gamma, gae_lambda)
         full = lambda t: torch.nn.functional.pad(t, (P - 1, eng.T - L))  # noqa: E731
         return {"tokens": tok, "targets": tgt, "mask": row_mask, "logp_old": logp_old, "value_old": values, "advantages": full(adv),
-                "returns": full(ret), "score": score, "ids": ids}
+                "returns": full(ret), "score": score, "ids": ids, "kl": kl}
+
+    def freeze_reference(self) -> None:
+        """Keeps a copy of the current trainable parameters (the whole model, or just the adapters under LoRA) as the frozen
+        reference policy of the KL penalty."""
+        self._ref_params = self.engine.params.clone()
+
+    @torch.no_grad()
+    def _reference_logp(self) -> torch.Tensor:
+        """[B, T] log-probabilities of the resident batch's targets under the frozen reference: its parameters are swapped into
+        the engine's buffer for one forward pass (no second engine, no second set of activations)."""
+        eng = self.engine
+        if getattr(self, "_ref_params", None) is None:
+            self.freeze_reference()
+        live = eng.params.clone()
+        eng.params.copy_(self._ref_params)
+        eng.forward(compute_grad_logits=False)
+        out = (-eng.row_loss).view(eng.B, eng.T).clone()
+        eng.params.copy_(live)
+        return out
 
     def ppo_update(self, rollout: dict) -> dict:
         """One optimizer step of the clipped surrogate on a stored rollout."""
@@ -129,7 +155,7 @@ class GlimmerPostTrainer:
         out = {}
         for _ in range(max(1, epochs)):
             out = self.ppo_update(roll)
-        return {**out, "mean_score": float(roll["score"].mean())}
+        return {**out, "mean_score": float(roll["score"].mean()), "mean_kl": float(roll["kl"].mean())}
 
     # ---------------------------------------------------------------------------------- run --
     def fit(self, records: str, steps: int, *, split: str = "train", allow_train_as_val: bool = True, log_every: int = 0) -> dict:

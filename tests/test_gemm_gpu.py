@@ -229,3 +229,44 @@ def test_skinny_products_take_the_weight_streaming_mma_kernel(kernel_lib, m, n, 
         L.nfn_gemm_skinny_set_impl(forced)
     torch.testing.assert_close(out.float(), tc.float(), atol=4e-2, rtol=4e-2)
     _lib.assert_status_ok("skinny gemm")
+
+
+@pytest.mark.parametrize("m,mode", [(17, 3), (24, 3), (32, 3), (5, 3), (16, 3)])
+@pytest.mark.parametrize("n,k", [(6656, 1024), (2304, 6656), (1000, 1056), (12288, 6656), (520, 4096)])
+def test_skinny_products_with_resident_token_fragments(kernel_lib, m, mode, n, k):
+    """The opt-in form for up to 32 rows: token fragments held in registers, K split over a thread-block cluster whose CTAs
+    add their strips over distributed shared memory. One launch, the same bits on every call, fp32 and tcgen05 agreement."""
+    from neuralfn_b200.ops import _lib
+    from neuralfn_b200.ops.gemm import gemm
+    torch.manual_seed(m * 7 + n)
+    a = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+    bias = (torch.randn(n, device="cuda") * 0.1).bfloat16()
+    resid = torch.randn(m, n, device="cuda").bfloat16()
+    ws = torch.empty(32 * 1024 * 1024, device="cuda", dtype=torch.float32)
+    L = _lib.load()
+    old = L.nfn_gemm_skinny_set_impl(mode)
+    try:
+        ref = a.float() @ w.float().t()
+        before = _lib.launch_count()
+        y = gemm(a, w, workspace=ws)
+        assert _lib.launch_count() - before == 1
+        _close(y, ref, k)
+        assert torch.equal(y, gemm(a, w, workspace=ws))
+        out = gemm(a, w, bias=bias, act="gelu_tanh", resid=resid, workspace=ws)
+        _close(out, torch.nn.functional.gelu(ref + bias.float(), approximate="tanh") + resid.float(), k)
+        acc = resid.clone()
+        gemm(a, w, out=acc, accum=True, alpha=0.5, workspace=ws)
+        _close(acc, resid.float() + 0.5 * ref, k)
+        wide_in = torch.zeros(m, k + 64, device="cuda", dtype=torch.bfloat16)
+        wide_in[:, :k] = a
+        wide_out = torch.zeros(m, n + 128, device="cuda", dtype=torch.bfloat16)
+        gemm(wide_in[:, :k], w, out=wide_out[:, 64:64 + n], workspace=ws)
+        _close(wide_out[:, 64:64 + n], ref, k)
+        assert float(wide_out[:, :64].abs().max()) == 0.0 and float(wide_out[:, 64 + n:].abs().max()) == 0.0
+        L.nfn_gemm_skinny_set_impl(0)
+        tc = gemm(a, w, bias=bias, act="gelu_tanh", resid=resid, workspace=ws)
+    finally:
+        L.nfn_gemm_skinny_set_impl(old)
+    torch.testing.assert_close(out.float(), tc.float(), atol=4e-2, rtol=4e-2)
+    _lib.assert_status_ok("resident skinny gemm")

@@ -170,14 +170,17 @@ def test_sft_objective_counts_only_masked_rows(kernel_lib):
 
 
 @pytest.mark.gpu
-def test_dpo_objective_matches_autograd(kernel_lib):
+@pytest.mark.parametrize("variant", [dict(), dict(dpo_loss_type="hinge"), dict(dpo_loss_type="ipo", dpo_beta=0.05), dict(dpo_label_smoothing=0.2)])
+def test_dpo_objective_matches_autograd(kernel_lib, variant):
     import torch.nn.functional as F
 
     from neuralfn_b200.models.glimmer import glimmer_reference_loss
-    cfg, layout, params, grads, eng, tok, tgt = _setup(z_loss=0.0)
+    cfg, layout, params, grads, eng, tok, tgt = _setup(z_loss=0.0, **variant)
     mask = torch.zeros(4, 128, device="cuda")
     mask[:, 64:120] = 1
-    ref_logps = torch.tensor([-300.0, -310.0, -295.0, -305.0], device="cuda")
+    # reference log-probabilities near the policy's own, one pair inside the hinge and one outside it
+    ref_logps = eng.sequence_logps(tok, tgt, mask).clone() + torch.tensor([-4.0, 30.0, 3.0, -30.0], device="cuda")
+    eng.set_batch(tok, tgt)
     eng.set_objective("dpo")
     eng.set_loss_mask(mask)
     eng.set_reference_logps(ref_logps)
@@ -187,15 +190,22 @@ def test_dpo_objective_matches_autograd(kernel_lib):
     _, _, rows = glimmer_reference_loss(cfg, ref_p, tok, tgt)
     pol = -(rows * mask).sum(1)
     margin = cfg.dpo_beta * ((pol[:2] - pol[2:]) - (ref_logps[:2] - ref_logps[2:]))
-    ref_loss = F.softplus(-margin).mean()
+    kind, eps = cfg.dpo_loss_type, cfg.dpo_label_smoothing
+    if kind == "hinge":
+        ref_loss = F.relu(1.0 - margin).mean()
+    elif kind == "ipo":
+        ref_loss = ((margin - 1.0 / (2.0 * cfg.dpo_beta)) ** 2).mean()
+    else:
+        ref_loss = ((1.0 - eps) * F.softplus(-margin) + eps * F.softplus(margin)).mean()
     ref_loss.backward()
     assert (eng.seq_logps - pol.detach()).abs().max() < 0.02 * pol.detach().abs().max()
     assert abs(loss.item() - ref_loss.item()) < 0.05 * max(1.0, ref_loss.item())
     assert not _compare(layout, grads, ref_p, tol=0.12)
-    # a frozen copy of the same parameters gives a zero margin: loss = log 2
-    eng.set_reference_logps(eng.sequence_logps(tok, tgt, mask))
-    eng.set_batch(tok, tgt)
-    assert abs(eng.forward(compute_grad_logits=False).item() - 0.6931) < 1e-3
+    if not variant:
+        # a frozen copy of the same parameters gives a zero margin: loss = log 2
+        eng.set_reference_logps(eng.sequence_logps(tok, tgt, mask))
+        eng.set_batch(tok, tgt)
+        assert abs(eng.forward(compute_grad_logits=False).item() - 0.6931) < 1e-3
 
 
 @pytest.mark.gpu
@@ -346,6 +356,36 @@ def test_native_ppo_loop_raises_the_rewarded_token_frequency(kernel_lib):
         assert all(v == v for v in out.values())                      # no NaN
     post.trainer.check_status()
     assert sum(scores[-4:]) / 4 > sum(scores[:4]) / 4 + 0.05, scores
+    # KL penalty against a frozen copy: zero while the policy equals the reference, positive after it has moved; the swap
+    # of parameters for the reference pass leaves the policy's own untouched
+    post.freeze_reference()
+    before = post.engine.params.clone()
+    roll = post.ppo_rollout(prompts, reward, max_new_tokens=8, generator=gen, kl_coef=0.1)
+    assert torch.equal(before, post.engine.params) and float(roll["kl"].abs().max()) < 1e-4
+    for _ in range(3):
+        post.ppo_update(roll)
+    moved = post.ppo_rollout(prompts, reward, max_new_tokens=8, generator=gen, kl_coef=0.1)
+    assert float(moved["kl"].abs().max()) > 1e-4
+    plain = post.ppo_rollout(prompts, reward, max_new_tokens=8, generator=torch.Generator(device="cuda").manual_seed(5))
+    shaped = post.ppo_rollout(prompts, reward, max_new_tokens=8, generator=torch.Generator(device="cuda").manual_seed(5), kl_coef=0.5)
+    assert torch.equal(plain["ids"], shaped["ids"]) and not torch.allclose(plain["returns"], shaped["returns"])
+
+
+@pytest.mark.parametrize("kind,eps", [("sigmoid", 0.0), ("sigmoid", 0.15), ("hinge", 0.0), ("ipo", 0.0)])
+def test_dpo_pair_terms_equal_autograd_and_the_graph_runtime_stage(kind, eps):
+    from neuralfn_b200.models.glimmer import dpo_pair_terms
+    from neuralfn_b200.tensor.stages_losses import DPOPairwiseLossStage
+    torch.manual_seed(0)
+    beta = 0.2
+    pc, pr, rc, rr = (torch.randn(16, dtype=torch.float64) * 8 for _ in range(4))
+    z = (beta * ((pc - pr) - (rc - rr))).requires_grad_(True)
+    per, d = dpo_pair_terms(z, beta=beta, loss_type=kind, label_smoothing=eps)
+    per.sum().backward()
+    assert torch.allclose(z.grad, d, atol=1e-12)
+    want, _, _ = DPOPairwiseLossStage(beta, eps, kind)(pc, pr, rc, rr)
+    assert abs(float(per.mean()) - float(want)) < 1e-10
+    with pytest.raises(ValueError):
+        dpo_pair_terms(z.detach(), beta=beta, loss_type="kto")
 
 
 def test_ppo_gradient_formulas_equal_autograd_on_the_reference_terms():
