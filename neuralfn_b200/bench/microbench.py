@@ -62,6 +62,9 @@ def case_gemm(args, m=None, n=None, k=None, a_mn=False, b_mn=False, tag="gemm"):
     b = torch.randn((k, n) if b_mn else (n, k), device=dev).bfloat16()
     out = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
     ws = torch.empty(32 * 1024 * 1024, device=dev, dtype=torch.float32) if (a_mn or m <= 256) else None  # split-K: weight gradients, skinny decode products
+    if getattr(args, "skinny_impl", -1) >= 0:
+        from neuralfn_b200.ops import _lib
+        _lib.load().nfn_gemm_skinny_set_impl(int(args.skinny_impl))
     ms = time_kernel(lambda: gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, workspace=ws), args.iters, args.warmup, args.flush)
     return _report(tag, ms, flops=2.0 * m * n * k, bytes_=2.0 * (m * k + n * k + m * n), args=args,
                    extra={"m": m, "n": n, "k": k, "a_mn": a_mn, "b_mn": b_mn})
@@ -310,6 +313,7 @@ def main(argv=None):
     ap.add_argument("--vocab", type=int, default=50257)
     ap.add_argument("--params", type=int, default=124 * 1000 * 1000)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--skinny-impl", type=int, default=-1, help="gemm case: nfn_gemm_skinny_set_impl mode for products with 3 - 64 rows (-1: the default)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--peak-tflops", type=float, default=0.0, help="measured bf16 GEMM peak to report fractions against")
     ap.add_argument("--peak-gbs", type=float, default=0.0, help="measured HBM copy bandwidth to report fractions against")

@@ -148,19 +148,26 @@ gemm_skinny_kernel(const SkinnyParams p) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Up to 32 rows, opt-in (mode 3): the token fragments live in REGISTERS for the whole kernel.
+// Up to 32 rows (opt-in, mode 3): token fragments in REGISTERS for the whole kernel, weights through a ring of bulk async copies.
 //
-// With more than one 16-row tile the kernel above re-reads the token rows from L2 for every eight weight rows (32 rows x K
-// against 8 rows x K of weights: four times the DRAM traffic), and that is what it waits for. Here a warp owns a fixed k
-// range of at most RS_UMAX chunks for the whole kernel and loads its token fragments once (8 * MT * RS_UMAX registers); all
-// it does afterwards is stream weight rows: per group of eight rows one 16-byte load per lane and chunk (the next group's
-// loads are issued before the current group's mma), 4 * MT * chunks mma, and a sum over the CTA's eight warps through
-// shared memory into the CTA's fp32 strip [rows, columns of this CTA].
+// Why the kernel above stalls with two row tiles: it re-reads the token rows from L2 for every eight weight rows, and its
+// loads in flight are bounded by registers (tens of KB per SM; the DRAM latency needs more than a hundred). Here
+//  * a warp (sixteen per CTA) owns a fixed k range of at most UMAX chunks and loads its token fragments once (8 * MT * UMAX
+//    registers);
+//  * warp 0 streams the weights: per group of sixteen weight rows one bulk async copy per row (lane r copies row r: the CTA's
+//    whole k range, a few KB contiguous) into a ring of shared-memory stages, completion counted on an mbarrier;
+//  * the warps read their weight fragments from the stage (conflict-free 16-byte loads: the row pitch is 64 mod 128 bytes),
+//    run 8 * MT mma per chunk in 2 * MT independent chains, and add their partial tiles through shared memory into the CTA's
+//    fp32 strip [rows, columns of this pass]; the block barrier of that sum is also what frees the stage for the next copy.
+// Measured steps on the way (32 x 12288 x 6656, L2 flushed): loads into registers one group ahead 65.5 us; eight warps and a
+// ring of six 8-row stages filled by one thread 82 us (barrier and fixed-latency stalls: two warps per scheduler walking one
+// dependent mma chain each, and the copy-issuing thread on the critical path); this form 55.4 us.
 //
-// K is longer than 8 warps x RS_UMAX chunks, so S CTAs split it: they form a thread-block cluster, each fills its strip for
-// the same weight rows, and after a cluster barrier CTA r sums column share r of all S strips over distributed shared
-// memory in rank order (deterministic), applies the epilogue and stores bf16. No workspace, no second launch.
-constexpr int RS_MAX_COLS = 512;       // most columns (weight rows) per pass of a cluster: strip = MT * 16 x 512 fp32
+// K is longer than 8 warps x UMAX chunks, so S CTAs split it: they form a thread-block cluster, each fills its strip for the
+// same weight rows, and after a cluster barrier CTA r sums column share r of all S strips over distributed shared memory in
+// rank order (deterministic), applies the epilogue and stores bf16. No workspace, no second launch.
+constexpr int RS_MAX_COLS = 256;       // most columns (weight rows) per pass of a cluster: strip = MT * 16 x 256 fp32
+constexpr int RS_STAGES = 6;
 
 __device__ __forceinline__ uint32_t rs_cluster_ctarank() {
   uint32_t r;
@@ -177,19 +184,69 @@ __device__ __forceinline__ float rs_ld_peer(const float* local, uint32_t rank) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
   return v;
 }
+__device__ __forceinline__ void rs_bulk_g2s(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+constexpr int RS_WARPS = 16, RS_THREADS = RS_WARPS * 32, RS_GROUP_ROWS = 16;   // weight rows per ring stage: two mma column tiles
 
 template <int MT, int UMAX>
-__global__ void __launch_bounds__(SK_THREADS, 1)
-gemm_skinny_resident_kernel(const SkinnyParams p, const int S, const int pass_cols, const int passes_total) {
-  constexpr int ROWS = MT * 16;
-  __shared__ float part[2][SK_WARPS][ROWS][8];              // one group's partial tile of every warp, double-buffered
-  extern __shared__ float strip[];                          // [ROWS][pass_cols]
+struct ResidentLayout {
+  static constexpr int ROWS = MT * 16;
+  static constexpr int PITCH = RS_WARPS * UMAX * 64 + 64;          // bytes per weight row in a stage: 64 mod 128
+  static constexpr int STAGE = RS_GROUP_ROWS * PITCH;
+  static constexpr int PART_BYTES = 2 * RS_WARPS * ROWS * RS_GROUP_ROWS * 4;   // two buffers of every warp's partial tile
+  static constexpr int STRIP_BYTES = ROWS * RS_MAX_COLS * 4;
+  static constexpr int STAGES = (227 * 1024 - 256 - PART_BYTES - STRIP_BYTES) / STAGE;
+  static constexpr int TOTAL = PART_BYTES + STRIP_BYTES + STAGES * STAGE;
+  static_assert(STAGES >= 2 && STAGES <= RS_STAGES, "ring depth");
+};
+
+template <int MT, int UMAX>
+__global__ void __launch_bounds__(RS_THREADS, 1)
+gemm_skinny_resident_kernel(const SkinnyParams p, const int S, const int pass_cols, const int passes_total, int* status) {
+  using Lay = ResidentLayout<MT, UMAX>;
+  constexpr int ROWS = Lay::ROWS, PITCH = Lay::PITCH, STAGE = Lay::STAGE, NS = Lay::STAGES, GR = RS_GROUP_ROWS;
+  extern __shared__ __align__(128) unsigned char rs_smem[];
+  __shared__ __align__(8) uint64_t full[RS_STAGES];
+  __shared__ int sh_abort;
+  float* part = reinterpret_cast<float*>(rs_smem);                                   // [2][RS_WARPS][ROWS][GR]
+  float* strip = reinterpret_cast<float*>(rs_smem + Lay::PART_BYTES);                // [ROWS][pass_cols]
+  unsigned char* ring = rs_smem + Lay::PART_BYTES + Lay::STRIP_BYTES;               // [NS][GR][PITCH]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, j = lane & 3;
   const uint32_t ks = rs_cluster_ctarank();
   const int cluster = blockIdx.x / S, n_clusters = gridDim.x / S;
-  // this warp's chunks of 32 k-values: slice ks * 8 + warp of S * 8
-  const int chunks = p.k / 32, slices = S * SK_WARPS, sl = (int)ks * SK_WARPS + warp;
-  const int c_lo = (int)((long long)chunks * sl / slices), cnt = (int)((long long)chunks * (sl + 1) / slices) - c_lo;
+  // chunks of 32 k-values: this CTA's share of K, and this warp's share of that
+  const int chunks = p.k / 32;
+  const int cta_lo = (int)((long long)chunks * ks / S), cta_cnt = (int)((long long)chunks * (ks + 1) / S) - cta_lo;
+  const int w_lo = cta_cnt * warp / RS_WARPS, cnt = cta_cnt * (warp + 1) / RS_WARPS - w_lo;
+
+  if (threadIdx.x == 0) {
+    sh_abort = 0;
+    for (int s2 = 0; s2 < NS; ++s2) mbar_init(smem_u32(&full[s2]), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  // the groups of sixteen weight rows this cluster works through, pass after pass (pass_cols is a multiple of 16)
+  auto groups_of = [&](int pass) { return (min(pass_cols, p.n - pass * pass_cols) + GR - 1) / GR; };
+  int total = 0;
+  for (int pass = cluster; pass < passes_total; pass += n_clusters) total += groups_of(pass);
+  int prod_pass = cluster, prod_grp = 0;                                             // warp 0 (uniform)
+  const uint32_t slice_bytes = (uint32_t)cta_cnt * 64u;
+  auto issue = [&](int seq) {                                                        // warp 0: lane r copies weight row r of the group
+    const int st = seq % NS, n0 = prod_pass * pass_cols + prod_grp * GR;
+    const uint32_t bar = smem_u32(&full[st]);
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)GR * slice_bytes);
+    if (lane < GR)
+      rs_bulk_g2s(smem_u32(ring + (size_t)st * STAGE + (size_t)lane * PITCH), p.b + (size_t)min(n0 + lane, p.n - 1) * p.ldb + (size_t)cta_lo * 32,
+                  slice_bytes, bar);
+    if (++prod_grp == groups_of(prod_pass)) { prod_grp = 0; prod_pass += n_clusters; }
+  };
+  if (warp == 0)
+    for (int seq = 0; seq < min(NS, total); ++seq) issue(seq);
 
   uint4 xa[UMAX][MT][2];
 #pragma unroll
@@ -199,62 +256,63 @@ gemm_skinny_resident_kernel(const SkinnyParams p, const int S, const int pass_co
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int r = mt * 16 + g + 8 * h;
-        xa[u][mt][h] = (u < cnt && r < p.m) ? __ldg(reinterpret_cast<const uint4*>(p.a + (size_t)r * p.lda + (size_t)(c_lo + u) * 32 + 8 * j))
+        xa[u][mt][h] = (u < cnt && r < p.m) ? __ldg(reinterpret_cast<const uint4*>(p.a + (size_t)r * p.lda + (size_t)(cta_lo + w_lo + u) * 32 + 8 * j))
                                              : make_uint4(0u, 0u, 0u, 0u);
       }
-  const __nv_bfloat16* wbase = p.b + (size_t)c_lo * 32 + 8 * j;
 
-  auto load_group = [&](uint4 (&w)[UMAX], int n0) {
-    const __nv_bfloat16* row = wbase + (size_t)min(n0 + g, p.n - 1) * p.ldb;      // clamped: computed twice, stored once
-#pragma unroll
-    for (int u = 0; u < UMAX; ++u)
-      if (u < cnt) w[u] = sk_ld_stream(row + (size_t)u * 32);
-  };
-  auto do_group = [&](const uint4 (&w)[UMAX], int col0, int buf) {
-    float acc[MT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int q = 0; q < 4; ++q) acc[mt][q] = 0.f;
-#pragma unroll
-    for (int u = 0; u < UMAX; ++u)
-      if (u < cnt) {
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          sk_mma(acc[mt], xa[u][mt][0].x, xa[u][mt][1].x, xa[u][mt][0].y, xa[u][mt][1].y, w[u].x, w[u].y);
-          sk_mma(acc[mt], xa[u][mt][0].z, xa[u][mt][1].z, xa[u][mt][0].w, xa[u][mt][1].w, w[u].z, w[u].w);
-        }
-      }
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      *reinterpret_cast<float2*>(&part[buf][warp][mt * 16 + g][2 * j]) = make_float2(acc[mt][0], acc[mt][1]);
-      *reinterpret_cast<float2*>(&part[buf][warp][mt * 16 + g + 8][2 * j]) = make_float2(acc[mt][2], acc[mt][3]);
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < ROWS * 8; i += SK_THREADS) {
-      const int r = i >> 3, c = i & 7;
-      float v = 0.f;
-#pragma unroll
-      for (int w8 = 0; w8 < SK_WARPS; ++w8) v += part[buf][w8][r][c];
-      strip[r * pass_cols + col0 + c] = v;
-    }
-  };
-
+  bool dead = false;      // a wait ran out: keep walking (the cluster's barriers still need this CTA) without touching the ring
+  int seq = 0;
   for (int pass = cluster; pass < passes_total; pass += n_clusters) {     // the same trip count in every CTA of a cluster
     const int n_pass = pass * pass_cols;
-    const int cols = min(pass_cols, p.n - n_pass), groups = (cols + 7) / 8;
-    uint4 w0[UMAX], w1[UMAX];
-    load_group(w0, n_pass);
-    for (int gi = 0; gi < groups; gi += 2) {
-      if (gi + 1 < groups) load_group(w1, n_pass + (gi + 1) * 8);
-      do_group(w0, gi * 8, 0);
-      if (gi + 2 < groups) load_group(w0, n_pass + (gi + 2) * 8);
-      if (gi + 1 < groups) do_group(w1, (gi + 1) * 8, 1);
+    const int cols = min(pass_cols, p.n - n_pass), groups = (cols + GR - 1) / GR;
+    for (int gi = 0; gi < groups; ++gi, ++seq) {
+      const int st = seq % NS, buf = seq & 1;
+      bool ok = dead ? false : mbar_wait_bounded(smem_u32(&full[st]), (uint32_t)(seq / NS) & 1u, &sh_abort, status, NFN_ERR_WAIT_FULL);
+      float acc[MT][2][4];                                                // [row tile][column tile of eight weight rows]
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int q = 0; q < 4; ++q) acc[mt][nt][q] = 0.f;
+      if (ok) {
+        const unsigned char* wrow = ring + (size_t)st * STAGE + (size_t)g * PITCH + (size_t)w_lo * 64 + j * 16;
+#pragma unroll
+        for (int u = 0; u < UMAX; ++u)
+          if (u < cnt) {
+            const uint4 w0 = *reinterpret_cast<const uint4*>(wrow + u * 64);
+            const uint4 w1 = *reinterpret_cast<const uint4*>(wrow + 8 * PITCH + u * 64);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              sk_mma(acc[mt][0], xa[u][mt][0].x, xa[u][mt][1].x, xa[u][mt][0].y, xa[u][mt][1].y, w0.x, w0.y);
+              sk_mma(acc[mt][1], xa[u][mt][0].x, xa[u][mt][1].x, xa[u][mt][0].y, xa[u][mt][1].y, w1.x, w1.y);
+              sk_mma(acc[mt][0], xa[u][mt][0].z, xa[u][mt][1].z, xa[u][mt][0].w, xa[u][mt][1].w, w0.z, w0.w);
+              sk_mma(acc[mt][1], xa[u][mt][0].z, xa[u][mt][1].z, xa[u][mt][0].w, xa[u][mt][1].w, w1.z, w1.w);
+            }
+          }
+      }
+      float* mine = part + ((size_t)(buf * RS_WARPS + warp) * ROWS) * GR;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          *reinterpret_cast<float2*>(mine + (mt * 16 + g) * GR + nt * 8 + 2 * j) = make_float2(acc[mt][nt][0], acc[mt][nt][1]);
+          *reinterpret_cast<float2*>(mine + (mt * 16 + g + 8) * GR + nt * 8 + 2 * j) = make_float2(acc[mt][nt][2], acc[mt][nt][3]);
+        }
+      ok = __syncthreads_and(ok);                                        // every warp is done with stage st and with its partial tile
+      if (!ok) dead = true;
+      if (warp == 0 && !dead && seq + NS < total) issue(seq + NS);
+      for (int i = threadIdx.x; i < ROWS * GR; i += RS_THREADS) {
+        float v = 0.f;
+#pragma unroll
+        for (int w8 = 0; w8 < RS_WARPS; ++w8) v += part[((size_t)(buf * RS_WARPS + w8) * ROWS) * GR + i];
+        strip[(i / GR) * pass_cols + gi * GR + (i % GR)] = v;
+      }
     }
     rs_cluster_sync();                                                    // every strip of the cluster is complete
     // CTA ks finishes columns [share_lo, share_hi) of the pass
     const int share_lo = (int)((long long)cols * ks / S), share_hi = (int)((long long)cols * (ks + 1) / S), width = share_hi - share_lo;
-    for (int i = threadIdx.x; i < p.m * width; i += SK_THREADS) {
+    for (int i = threadIdx.x; i < p.m * width; i += RS_THREADS) {
       const int r = i / width, c = share_lo + i % width, n = n_pass + c;
       float v = 0.f;
       for (int s2 = 0; s2 < S; ++s2) v += rs_ld_peer(&strip[r * pass_cols + c], (uint32_t)s2);
@@ -268,15 +326,18 @@ gemm_skinny_resident_kernel(const SkinnyParams p, const int S, const int pass_co
     }
     rs_cluster_sync();                                                    // nobody overwrites a strip a peer still reads
   }
+  if (dead)
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);                       // let copies in flight land before the CTA goes away
 }
 
 template <int MT, int UMAX>
 static int launch_skinny_resident(const SkinnyParams& p, cudaStream_t stream) {
+  using Lay = ResidentLayout<MT, UMAX>;
   auto kern = gemm_skinny_resident_kernel<MT, UMAX>;
   const int chunks = p.k / 32;
-  const int S = (chunks + SK_WARPS * UMAX - 1) / (SK_WARPS * UMAX);
+  const int S = (chunks + RS_WARPS * UMAX - 1) / (RS_WARPS * UMAX);
   if (S > 8) return 0;                                                   // portable cluster size
-  const size_t smem = (size_t)MT * 16 * RS_MAX_COLS * sizeof(float);
+  const size_t smem = Lay::TOTAL;
   static int max_clusters[64][9] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -286,7 +347,7 @@ static int launch_skinny_resident(const SkinnyParams& p, cudaStream_t stream) {
   attr.val.clusterDim.x = S;
   attr.val.clusterDim.y = 1;
   attr.val.clusterDim.z = 1;
-  cfg.blockDim = dim3(SK_THREADS, 1, 1);
+  cfg.blockDim = dim3(RS_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cfg.attrs = &attr;
@@ -295,6 +356,7 @@ static int launch_skinny_resident(const SkinnyParams& p, cudaStream_t stream) {
   if (!mc) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
       cudaGetLastError();
+      mc = -1;
       return 0;
     }
     cfg.gridDim = dim3(sm_count() / S * S, 1, 1);
@@ -307,15 +369,15 @@ static int launch_skinny_resident(const SkinnyParams& p, cudaStream_t stream) {
     }
   }
   if (mc <= 0) return 0;
-  // passes of equal width, a whole number of them per cluster: groups of eight weight rows, at most RS_MAX_COLS columns per pass
-  const int groups = (p.n + 7) / 8, max_groups = RS_MAX_COLS / 8;
+  // passes of equal width, a whole number of them per cluster: groups of sixteen weight rows, at most RS_MAX_COLS columns per pass
+  const int groups = (p.n + RS_GROUP_ROWS - 1) / RS_GROUP_ROWS, max_groups = RS_MAX_COLS / RS_GROUP_ROWS;
   const int clusters = std::min(mc, groups);
   const int per_cluster = (groups + clusters - 1) / clusters;                       // groups one cluster works through
   const int passes_per_cluster = (per_cluster + max_groups - 1) / max_groups;
-  const int pass_cols = (per_cluster + passes_per_cluster - 1) / passes_per_cluster * 8;
+  const int pass_cols = (per_cluster + passes_per_cluster - 1) / passes_per_cluster * RS_GROUP_ROWS;
   const int passes = (p.n + pass_cols - 1) / pass_cols;
   cfg.gridDim = dim3(std::min(clusters, passes) * S, 1, 1);
-  if (cudaLaunchKernelEx(&cfg, kern, p, S, pass_cols, passes) != cudaSuccess) return launch_check("gemm_skinny_resident", 0);
+  if (cudaLaunchKernelEx(&cfg, kern, p, S, pass_cols, passes, status_ptr()) != cudaSuccess) return launch_check("gemm_skinny_resident", 0);
   const int rc = launch_check("gemm_skinny_resident", 1);
   return rc == 0 ? 1 : rc;
 }
@@ -331,8 +393,9 @@ int try_launch_skinny(const nfn_gemm_args& a, cudaStream_t stream) {
   // measured (12288 x 6656 weights, L2 flushed): 8 rows 49 us against 52 us on the tcgen05 split-K path, 32 rows 65 against
   // 50 us, 64 rows 81 against 50 us - with more than one 16-row tile the token fragments, which every warp fetches from L2
   // right before use, become the bottleneck. So by default only up to 16 rows come here; mode 2 forces every eligible product.
-  // The register-resident cluster form (mode 3) removes those re-reads and is still slower: 65.5 us at 32 rows, 53.3 us at
-  // 8 rows - one group of loads ahead (28 KB per SM, all the registers allow) does not cover the DRAM latency.
+  // The register-resident cluster form (mode 3) removes those re-reads: 55.4 us at 32 rows (tcgen05 split-K: 50.1), 47.1 us at
+  // 8 rows (49.2 here, 52 - 54 on tcgen05). It stays opt-in: clusters of four fill only 132 of the 148 SMs, and its ring holds
+  // two 16-row stages (the partial tiles of sixteen warps take 64 KB), which is less in flight than the DRAM latency asks for.
   // the weights must dominate the traffic for this to be the right kernel: N x K well above the token rows
   if ((long long)a.n * a.k < (1LL << 20)) return 0;
   const bool aligned = ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b)) & 15) == 0;
@@ -350,7 +413,7 @@ int try_launch_skinny(const nfn_gemm_args& a, cudaStream_t stream) {
   const int mt = (a.m + 15) / 16;
   // mode 3: the register-resident cluster form for every product up to 32 rows (measured slower than both other paths, see above)
   if (g_skinny_mode == 3 && mt <= 2) {
-    const int rc = mt == 2 ? launch_skinny_resident<2, 7>(p, stream) : launch_skinny_resident<1, 8>(p, stream);
+    const int rc = mt == 2 ? launch_skinny_resident<2, 4>(p, stream) : launch_skinny_resident<1, 4>(p, stream);
     if (rc != 0) return rc;
   }
   if (a.m > 16 && g_skinny_mode != 2) return 0;
