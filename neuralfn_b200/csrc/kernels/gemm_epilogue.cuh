@@ -23,6 +23,10 @@ struct GemmParams {
   long long split_stride;  // elements between consecutive split slices of the fp32 workspace
   int* status;
   int raster_gw;      // tile order: bands of this many n-tiles, n fastest inside a band (1 = m fastest)
+  // grouped contraction (weight gradients of MoE experts): split index g contracts rows [group_rows[g], group_rows[g + 1]) of
+  // the K axis (multiples of BK; rows of a group's padding must be finite in both operands and zero in one) and writes slice
+  // g of C (split_stride elements apart, bf16 or fp32). nullptr: the plain / split-K meaning of the fields above.
+  const int* group_rows = nullptr;
 };
 
 // Tile index -> (m-tile, n-tile). CTAs that run at the same time hold consecutive indices, so a

@@ -88,8 +88,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         int tm, tn;
         tile_mn(p, t2, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        const int kb_lo = sp * p.kb_per_split;
-        const int kb_hi = min(total_kb, kb_lo + p.kb_per_split);
+        const int kb_lo = p.group_rows ? p.group_rows[sp] / BK : sp * p.kb_per_split;
+        const int kb_hi = p.group_rows ? min(total_kb, p.group_rows[sp + 1] / BK) : min(total_kb, kb_lo + p.kb_per_split);
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), phase ^ 1, cta_abort, p.status,
                                  NFN_ERR_WAIT_EMPTY)) {
@@ -126,8 +126,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int sp = tile / tiles_mn;
-        const int kb_lo = sp * p.kb_per_split;
-        const int kb_hi = min(total_kb, kb_lo + p.kb_per_split);
+        const int kb_lo = p.group_rows ? p.group_rows[sp] / BK : sp * p.kb_per_split;
+        const int kb_hi = p.group_rows ? min(total_kb, p.group_rows[sp + 1] / BK) : min(total_kb, kb_lo + p.kb_per_split);
         if (!mbar_wait_bounded(smem_u32(&tempty_bar[acc]), acc_phase ^ 1, cta_abort, p.status,
                                NFN_ERR_WAIT_TMEM_EMPTY)) {
           ok = false;

@@ -61,8 +61,10 @@ int epi_direct_flag() {
   return g_epi_direct ? NFN_EPI_DIRECT_ST : 0;
 }
 
+// group_rows != nullptr: the grouped contraction (GemmParams::group_rows) with `groups` slices of C, group_stride elements apart.
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-static int launch_gemm(const nfn_gemm_args& a, int split_k, cudaStream_t stream) {
+static int launch_gemm(const nfn_gemm_args& a, int split_k, cudaStream_t stream, const int* group_rows = nullptr, int groups = 0,
+                       long long group_stride = 0) {
   constexpr size_t SMEM =
       (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 2 * EPI_TILE_BYTES + 1024 + 256;
   static bool attr_set[64] = {};
@@ -102,7 +104,15 @@ static int launch_gemm(const nfn_gemm_args& a, int split_k, cudaStream_t stream)
 
   const bool out_f32 = a.flags & NFN_EPI_OUT_F32;
   const bool accum = a.flags & NFN_EPI_ACCUM;
-  if (split_k > 1) {
+  if (group_rows) {
+    p.group_rows = group_rows;
+    p.split_k = groups;
+    p.split_stride = group_stride;
+    p.flags |= NFN_EPI_DIRECT_ST;
+    p.raster_gw = 1;
+    split_k = 1;
+    tc = ta; tx = ta;  // direct stores only
+  } else if (split_k > 1) {
     // partial products go to fp32 slices of the workspace; the reduce kernel finishes
     p.kb_per_split = ceil_div(ceil_div(a.k, BK), split_k);
     split_k = ceil_div(ceil_div(a.k, BK), p.kb_per_split);  // no empty trailing slice
@@ -176,6 +186,29 @@ extern "C" int nfn_gemm_set_pair_mode(int on) {
   const int old = nfn::pair_enabled() ? 1 : 0;
   nfn::g_pair_mode = on ? 1 : 0;
   return old;
+}
+
+// Grouped contraction: C[g] (M x N, group_stride elements apart, bf16 or fp32) = alpha * A[rows of g]^T-style product over the
+// K rows [group_rows[g], group_rows[g + 1]) only. A and B are MN-major ([K, M] and [K, N]: the activations and the upstream
+// gradients of an expert-sorted token buffer), group_rows holds groups + 1 row offsets on the device, multiples of 64; rows
+// between a group's last real row and the next offset must be finite in both operands and zero in at least one (the MoE plan
+// pads segments with zero rows). One launch for all groups, no host read of the counts; a group without rows gives zeros.
+// Flags: alpha, fp32 output and accumulate are honoured; there is no bias / activation / residual here.
+extern "C" int nfn_gemm_grouped_k(const nfn_gemm_args* args, const int* group_rows, int groups, long long group_stride, nfn_stream_t stream_) {
+  using namespace nfn;
+  if (!args || !group_rows || groups <= 0) return fail(-1, "gemm_grouped_k: bad arguments");
+  const nfn_gemm_args& a = *args;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a.m <= 0 || a.n <= 0 || a.k <= 0) return fail(-1, "gemm_grouped_k: empty problem");
+  if (!a.a_mn || !a.b_mn) return fail(-1, "gemm_grouped_k: both operands must be MN-major ([K, M] and [K, N])");
+  if ((a.m & 7) || (a.n & 7) || (a.ldc & 7) || (a.lda & 7) || (a.ldb & 7) || (group_stride & 7))
+    return fail(-1, "gemm_grouped_k: M, N, leading dimensions and the group stride must be multiples of 8");
+  if ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b) | reinterpret_cast<uintptr_t>(a.c)) & 15)
+    return fail(-1, "gemm_grouped_k: operands must be 16-byte aligned");
+  if (a.flags & ~(NFN_EPI_OUT_F32 | NFN_EPI_ACCUM)) return fail(-1, "gemm_grouped_k: only fp32 output and accumulate are supported");
+  const int tiles256 = ceil_div(a.m, BM) * ceil_div(a.n, 256) * groups;
+  if (tiles256 >= sm_count() && (a.n % 256 == 0 || a.n >= 1024)) return launch_gemm<256, 4, true, true>(a, 1, stream, group_rows, groups, group_stride);
+  return launch_gemm<128, 6, true, true>(a, 1, stream, group_rows, groups, group_stride);
 }
 
 extern "C" int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream_) {

@@ -65,6 +65,10 @@ typedef struct {
 } nfn_gemm_args;
 
 int nfn_gemm_bf16(const nfn_gemm_args* args, nfn_stream_t stream);
+// Grouped contraction for expert weight gradients: C[g] = A[K rows of group g, M]^T . B[same rows, N] for every group in one
+// launch. Both operands MN-major; group_rows = groups + 1 device ints (multiples of 64; padding rows zero); C slices
+// group_stride elements apart. Only alpha, fp32 output and accumulate of the epilogue flags apply.
+int nfn_gemm_grouped_k(const nfn_gemm_args* args, const int* group_rows, int groups, long long group_stride, nfn_stream_t stream);
 // Routes eligible products (K-major A and B, bf16 output, no split-K, at least one 256 x 256
 // tile per SM pair) to the CTA-pair kernel (tcgen05 cta_group::2, 256 x 256 tile per 2-CTA
 // cluster). Returns the previous setting. On by default; NFN_GEMM_PAIR=0 turns it off.

@@ -99,3 +99,39 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     rc = _lib.load().nfn_gemm_bf16(ctypes.byref(args), ctypes.c_void_p(_lib.stream_ptr()))
     _lib.check(rc, "nfn_gemm_bf16")
     return out
+
+
+def gemm_grouped_k(a: torch.Tensor, b: torch.Tensor, group_rows: torch.Tensor, out: torch.Tensor, *, alpha: float = 1.0, accum: bool = False) -> torch.Tensor:
+    """out[g] = alpha * a[r0:r1]^T @ b[r0:r1] with (r0, r1) = group_rows[g], group_rows[g + 1], for every group in ONE launch and
+    without reading the offsets on the host: the weight gradients of all experts of an MoE layer over the expert-sorted token
+    buffer. ``a`` [rows, M] and ``b`` [rows, N] bf16 (row pitch free, columns contiguous), ``group_rows`` int32 [G + 1] on the
+    device, multiples of 64, with the padding rows of every group zero in at least one operand and finite in both;
+    ``out`` [G, M, N] bf16 or fp32, contiguous in its last two dimensions. A group without rows gives zeros.
+
+    The reference computes these per token inside ``moe_swiglu_backward`` (``kernels.cu:12700-12862``, atomics into dense
+    weight gradients); here they are tcgen05 tiles over (group, m-tile, n-tile) whose K loop walks the group's rows."""
+    _check2d(a, "a")
+    _check2d(b, "b")
+    rows, m = a.shape
+    n = b.shape[1]
+    G = group_rows.numel() - 1
+    if b.shape[0] != rows or out.shape != (G, m, n) or out.stride(2) != 1 or out.stride(1) < n or group_rows.dtype != torch.int32:
+        raise ValueError("gemm_grouped_k: a [rows, M], b [rows, N], group_rows int32 [G + 1], out [G, M, N]")
+    flags = 0
+    if accum:
+        flags |= EPI_ACCUM
+    if out.dtype == torch.float32:
+        flags |= EPI_OUT_F32
+    elif out.dtype != torch.bfloat16:
+        raise ValueError("out must be bf16 or fp32")
+    args = _lib.GemmArgs()
+    args.a, args.b, args.c = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.m, args.n, args.k = m, n, rows
+    args.lda, args.ldb, args.ldc = a.stride(0), b.stride(0), out.stride(1)
+    args.a_mn, args.b_mn = 1, 1
+    args.alpha, args.flags, args.split_k = alpha, flags, 1
+    L = _lib.load()
+    rc = L.nfn_gemm_grouped_k(ctypes.byref(args), ctypes.c_void_p(group_rows.data_ptr()), ctypes.c_int(G), ctypes.c_longlong(out.stride(0)),
+                              ctypes.c_void_p(_lib.stream_ptr()))
+    _lib.check(rc, "nfn_gemm_grouped_k")
+    return out

@@ -16,7 +16,7 @@ from ctypes import c_float, c_int, c_void_p
 import torch
 
 from . import _lib
-from .gemm import gemm
+from .gemm import gemm, gemm_grouped_k
 from .infer import swiglu_forward
 
 __all__ = ["MoEWorkspace", "moe_forward", "moe_reference", "moe_experts", "moe_experts_native_ok"]
@@ -189,18 +189,12 @@ class _MoEExpertsFn(torch.autograd.Function):
         dxs = torch.empty_like(ws.xs)
         _grouped_gemm(dh, torch.cat([w1, w3], 2).contiguous(), dxs, ws)  # [cap, d] = dh @ [w1 | w3][e]^T
         dx = dxs[rows].view(T, k, d).float().sum(1).to(torch.bfloat16)
-        # weight gradients: one TN product per expert over its row segment
-        offs, cnts = ws.offsets.tolist(), ws.counts.tolist()
-        dw1, dw2, dw3 = torch.zeros_like(w1), torch.zeros_like(w2), torch.zeros_like(w3)
-        for e in range(E):
-            c = cnts[e]
-            if c == 0:
-                continue
-            lo = offs[e]
-            xe, he, ae, ye = ws.xs[lo:lo + c], dh[lo:lo + c], ws.a[lo:lo + c], dys[lo:lo + c]
-            gemm(xe, he[:, :h], a_mn=True, b_mn=True, out=dw1[e])       # [d, h] = xs^T dh_gate
-            gemm(xe, he[:, h:], a_mn=True, b_mn=True, out=dw3[e])
-            gemm(ae, ye, a_mn=True, b_mn=True, out=dw2[e])              # [h, d] = a^T dys
+        # weight gradients of all experts: three grouped contractions over the plan's padded row segments (pad rows of xs and
+        # dys are zero, those of a and dh are finite), no host read of the counts
+        dw1, dw2, dw3 = torch.empty_like(w1), torch.empty_like(w2), torch.empty_like(w3)
+        gemm_grouped_k(ws.xs, dh[:, :h], ws.offsets, dw1)               # [E, d, h] = xs^T dh_gate
+        gemm_grouped_k(ws.xs, dh[:, h:], ws.offsets, dw3)
+        gemm_grouped_k(ws.a, dys, ws.offsets, dw2)                      # [E, h, d] = a^T dys
         ctx.ws = None
         return dx, dw1, dw2, dw3, d_w.to(ctx.w_dtype), None
 

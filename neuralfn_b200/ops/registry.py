@@ -33,6 +33,7 @@ def _k(op, symbol, dtypes=("bf16",), tc=False, fused="", fallback="torch") -> Ke
 
 KERNELS: tuple[KernelEntry, ...] = (
     _k("gemm", "nfn_gemm_bf16", ("bf16", "fp32-out"), True, "bias, GELU/SiLU/ReLU^2/tanh-cap, residual, dGELU, accumulate, split-K"),
+    _k("gemm, grouped contraction (expert weight gradients)", "nfn_gemm_grouped_k", ("bf16", "fp32-out"), True, "per-group K ranges read on the device, accumulate"),
     _k("gemm_kquant", "nfn_gemm_kquant", ("q4_k", "q5_k", "q6_k"), True, "dequantisation inside the operand pipeline + GEMM epilogues"),
     _k("gemm_nf4_lora", "nfn_gemm_quant_lora", ("nf4",), True, "NF4 decode + LoRA branch as an extra k-block"),
     _k("gemm_allgather / reduce_scatter / grouped", "nfn_gemm_tp", ("bf16",), True, "peer-memory all-gather or reduce-scatter inside the GEMM; grouped MoE GEMM"),

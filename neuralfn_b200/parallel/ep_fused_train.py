@@ -35,7 +35,7 @@ import torch.distributed as dist
 
 from ..ops import _lib
 from ..ops import kernels as K
-from ..ops.gemm import gemm
+from ..ops.gemm import gemm, gemm_grouped_k
 from ..ops.infer import swiglu_backward, swiglu_forward
 from ..ops.moe import _grouped_gemm
 from .tp import _Symmetric
@@ -159,7 +159,7 @@ class _FusedEPFn(torch.autograd.Function):
         ys_keep = ys.clone()                     # the symmetric buffer is reused by the next layer
         ex.barrier(3)                            # nobody refills send / recv while a peer still reads them
         ctx.ex, ctx.tiles, ctx.seg, ctx.route = ex, tiles, seg, (idx, wts, row_of, src_off, home_row)
-        ctx.dims, ctx.segments, ctx.w_dtype = (T, d, F, n_rows), (offs, per_expert), weights.dtype
+        ctx.dims, ctx.segments, ctx.w_dtype, ctx.recv_off = (T, d, F, n_rows), (offs, per_expert), weights.dtype, recv_off
         ctx.save_for_backward(w1, w2, w3, xs, h, a, ys_keep, w_rows)
         return out
 
@@ -194,16 +194,12 @@ class _FusedEPFn(torch.autograd.Function):
         d_w = torch.empty(T, k, dtype=torch.float32, device=dev)
         _lib.check(L.nfn_moe_ep_gather_f32(_arr(ex.frecv.ptrs), c_int(T), c_int(k), c_int(E), c_int(W), _p(idx), _p(row_of), _p(src_off), _p(home_row),
                                            _p(d_w), _st()), "nfn_moe_ep_gather_f32")
-        # weight gradients stay with the owner: one TN product per local expert over its row segment
-        dw1, dw2, dw3 = torch.zeros_like(w1), torch.zeros_like(w2), torch.zeros_like(w3)
-        for e in range(El):
-            c, lo = per_expert[e], offs[e]
-            if c == 0:
-                continue
-            xe, he, ae, ye = xs[lo:lo + c], dh[lo:lo + c], a[lo:lo + c], dys[lo:lo + c]
-            gemm(xe, he[:, :F], a_mn=True, b_mn=True, out=dw1[e])
-            gemm(xe, he[:, F:], a_mn=True, b_mn=True, out=dw3[e])
-            gemm(ae, ye, a_mn=True, b_mn=True, out=dw2[e])
+        # weight gradients stay with the owner: three grouped contractions over the received (128-row padded) segments; the
+        # padding rows of xs and dys are zero, those of a and dh finite
+        dw1, dw2, dw3 = torch.empty_like(w1), torch.empty_like(w2), torch.empty_like(w3)
+        gemm_grouped_k(xs, dh[:, :F], ctx.recv_off, dw1)
+        gemm_grouped_k(xs, dh[:, F:], ctx.recv_off, dw3)
+        gemm_grouped_k(a, dys, ctx.recv_off, dw2)
         ex.barrier(3)
         return dx, dw1, dw2, dw3, d_w.to(ctx.w_dtype), None, None
 

@@ -270,3 +270,41 @@ def test_skinny_products_with_resident_token_fragments(kernel_lib, m, mode, n, k
         L.nfn_gemm_skinny_set_impl(old)
     torch.testing.assert_close(out.float(), tc.float(), atol=4e-2, rtol=4e-2)
     _lib.assert_status_ok("resident skinny gemm")
+
+
+@pytest.mark.parametrize("m,n,dtype", [(256, 512, torch.bfloat16), (2048, 1024, torch.bfloat16), (192, 200, torch.float32)])
+def test_grouped_contraction_gives_every_experts_weight_gradient(kernel_lib, m, n, dtype):
+    """out[g] = a[rows of g]^T b[rows of g] for all groups in one launch: segments padded to 128 rows with zero rows in a, an empty
+    group, accumulation on top of an existing gradient."""
+    from neuralfn_b200.ops import _lib
+    from neuralfn_b200.ops.gemm import gemm_grouped_k
+    torch.manual_seed(m + n)
+    counts = [300, 0, 128, 77, 1, 513]
+    offs = [0]
+    for c in counts:
+        offs.append(offs[-1] + (c + 127) // 128 * 128)
+    rows = offs[-1] + 256                                             # rows past the last group are never read
+    a = torch.zeros(rows, m, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(rows, n, device="cuda") * 0.3).bfloat16()        # padding rows of b are finite, not zero
+    for g, c in enumerate(counts):
+        a[offs[g]:offs[g] + c] = (torch.randn(c, m, device="cuda") * 0.3).bfloat16()
+    a[offs[-1]:] = float("nan")                                       # must not be touched
+    group_rows = torch.tensor(offs, device="cuda", dtype=torch.int32)
+    out = torch.full((len(counts), m, n), 7.0, device="cuda", dtype=dtype)
+    before = _lib.launch_count()
+    gemm_grouped_k(a, b, group_rows, out)
+    assert _lib.launch_count() - before == 1
+    ref = torch.stack([a[offs[g]:offs[g] + c].float().t() @ b[offs[g]:offs[g] + c].float() for g, c in enumerate(counts)])
+    assert float(out[1].abs().max()) == 0.0
+    tol = 2e-2 * float(ref.abs().max()) + 1e-3
+    assert float((out.float() - ref).abs().max()) < tol
+    keep = out.clone()
+    gemm_grouped_k(a, b, group_rows, out, alpha=0.5, accum=True)
+    assert float((out.float() - (keep.float() + 0.5 * ref)).abs().max()) < 2 * tol
+    # column views of a wider buffer (the gate / up halves of the hidden gradient)
+    wide = torch.zeros(rows, 2 * n, device="cuda", dtype=torch.bfloat16)
+    wide[:, n:] = b
+    out2 = torch.empty_like(keep)
+    gemm_grouped_k(a, wide[:, n:], group_rows, out2)
+    assert torch.equal(out2, keep)
+    _lib.assert_status_ok("grouped contraction")
