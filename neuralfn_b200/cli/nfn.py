@@ -103,13 +103,20 @@ def _native_objective_options(a) -> dict:
 
 
 def _native_adapter_options(a) -> dict:
-    """--runtime native --adapter-type lora: adapter geometry for the native Glimmer engine (other families adapt in the graph runtime)."""
+    """--runtime native --adapter-type lora | qlora: adapter geometry for the native Glimmer engine (other families adapt in the graph
+    runtime). qlora keeps the frozen projection weights as NF4 (``--qlora-group-size``)."""
     kind = getattr(a, "adapter_type", None)
     if kind in (None, "none"):
         return {}
-    if kind != "lora" or a.base_model.lower().replace("_", "-") not in ("muse-glimmer", "glimmer"):
-        raise ValueError("the native engines train LoRA adapters on --base-model muse-glimmer only; drop --runtime native for the others")
+    if kind not in ("lora", "qlora") or a.base_model.lower().replace("_", "-") not in ("muse-glimmer", "glimmer"):
+        raise ValueError("the native engines train LoRA / QLoRA adapters on --base-model muse-glimmer only; drop --runtime native for the others")
     out = {"lora_rank": int(getattr(a, "lora_rank", None) or 16)}
+    if getattr(a, "lora_dropout", None):
+        out["lora_dropout"] = float(a.lora_dropout)
+    if kind == "qlora":
+        out["base_quant"] = "nf4"
+        if getattr(a, "qlora_group_size", None):
+            out["nf4_group"] = int(a.qlora_group_size)
     if getattr(a, "lora_alpha", None) is not None:
         out["lora_alpha"] = float(a.lora_alpha)
     if getattr(a, "lora_targets", None):

@@ -281,6 +281,12 @@ int nfn_sigmoid_gate_forward(const void* att, int ld_att, const void* gate, int 
 int nfn_sigmoid_gate_backward(const void* dout, int ld_dout, const void* att, int ld_att, const void* gate, int ld_gate, void* datt,
                               int ld_datt, void* dgate, int ld_dgate, long long rows, int width, nfn_stream_t stream);
 
+// ---- counter-based dropout for the LoRA adapter branch (dropout.cu) ----
+// out (+)= keep ? x / (1 - p) : 0 with keep = f(seed, stream_id, *step_dev, row, column): calling it again with the same ids
+// reproduces the mask (backward pass, recomputation). bf16 [rows, width], width a multiple of 8.
+int nfn_dropout_apply(const void* x, int ld_x, void* out, int ld_out, long long rows, int width, float p, unsigned long long seed,
+                      int stream_id, const long long* step_dev, int accumulate, nfn_stream_t stream);
+
 // ---- differential attention glue (diff_attention.cu) ----
 int nfn_diff_partials(void);
 int nfn_diff_q_expand(const void* q, int ldq, void* q2, long long tokens, int H, int D, nfn_stream_t stream);

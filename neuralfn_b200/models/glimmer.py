@@ -90,6 +90,9 @@ class GlimmerConfig:
     lora_rank: int = 0                      # > 0: train low-rank adapters over frozen base weights
     lora_alpha: float = 32.0
     lora_targets: tuple = ("wqkvg", "wo", "w_gate_up", "w_down")
+    lora_dropout: float = 0.0                      # on the input of the adapters' A matrices (training passes only)
+    base_quant: str = ""                         # "" | "nf4": the frozen projection weights under the adapters as NF4 (QLoRA)
+    nf4_group: int = 64
     base_seed: int = 1337                   # LoRA: seed of the frozen base weights until load_base() replaces them
     ckpt_every: int = 0                     # > 0: keep activations of this many layers only; recompute segments in backward
     # pipeline-parallel stage view: this engine owns layers [pp_layer_begin, pp_layer_end); the first stage also owns
@@ -327,6 +330,27 @@ class GlimmerEngine:
             self.base = master.to(torch.bfloat16)
             del master
             self.p = {**self.base_layout.views(self.base), **self.p}
+            self.q: dict[str, tuple[torch.Tensor, torch.Tensor]] = {}      # NF4 base projections: name -> (codes, absmax)
+            if cfg.base_quant:
+                if cfg.base_quant != "nf4":
+                    raise ValueError(f"base_quant {cfg.base_quant!r}: only 'nf4'")
+                self._quantise_base()
+        elif cfg.base_quant:
+            raise ValueError("base_quant needs lora_rank > 0: a quantised base is frozen, only adapters train")
+        if not 0.0 <= cfg.lora_dropout < 1.0:
+            raise ValueError("lora_dropout must be in [0, 1)")
+        self.drop_p = float(cfg.lora_dropout) if self.lora else 0.0
+        self.drop_on = False                                               # set by forward(): training passes only
+        if self.drop_p > 0.0 and not (cfg.pp_first and cfg.pp_last):
+            raise ValueError("lora_dropout is not available on pipeline stages: a stage runs other micro-batches between a forward and its backward pass")
+        if self.drop_p > 0.0:
+            # masks are regenerated, not stored: a device step word advanced once per forward pass (inside the step graph) and one
+            # stream id per adapted projection; the backward pass and a recomputed segment see the same word
+            self.drop_step = torch.zeros(1, device=dev, dtype=torch.int64)
+            self.drop_ids = {s_.name[:-len(".lora_a")]: i for i, s_ in enumerate(x for x in layout.order if x.name.endswith(".lora_a"))}
+            widest = max(s_.shape[1] for s_ in layout.order if s_.name.endswith(".lora_a"))
+            self.drop_x = torch.empty(batch * seq, widest, device=dev, dtype=torch.bfloat16)
+            self.drop_dx = torch.empty(batch * seq, widest, device=dev, dtype=torch.bfloat16)
         N, C, Fd, Q, A = batch * seq, cfg.d_model, cfg.d_ff, cfg.qkv_dim, cfg.att_dim
         bf, f32 = torch.bfloat16, torch.float32
         e = lambda *s, dtype=bf: torch.empty(*s, device=dev, dtype=dtype)  # noqa: E731
@@ -403,20 +427,82 @@ class GlimmerEngine:
         return n if self.cfg.ckpt_every <= 0 else min(n, self.cfg.ckpt_every)
 
     # ----------------------------------------------------------------------------- LoRA --
+    PROJECTIONS = ("wqkvg", "wo", "w_gate_up", "w_down")
+
+    @torch.no_grad()
+    def _quantise_base(self) -> None:
+        """QLoRA: every layer projection of the frozen base becomes NF4 codes + one fp32 absmax per ``nf4_group`` values
+        (the reference's ``nf4_linear`` stage, neuralfn/torch_backend.py: low nibble = even column); the bf16 copies are
+        dropped - what stays in bf16 is the embedding, the head and the norm weights. A projection is decoded into one shared
+        scratch buffer right before each product that reads it (``nfn_dequant_nf4``)."""
+        from ..tensor.stages_linear import nf4_quantize
+        names = [s.name for s in self.base_layout.order if s.name.rsplit(".", 1)[-1] in self.PROJECTIONS]
+        keep = [s for s in self.base_layout.order if s.name not in set(names)]
+        full = self.base_layout.views(self.base)
+        biggest = 0
+        for name in names:
+            w = full[name]
+            codes, absmax = [], []
+            for r0 in range(0, w.shape[0], 1024):                  # row chunks: the nearest-code search holds 16 floats per value
+                c, a = nf4_quantize(w[r0:r0 + 1024], self.cfg.nf4_group)
+                codes.append(c)
+                absmax.append(a)
+            self.q[name] = (torch.cat(codes).contiguous(), torch.cat(absmax).contiguous())
+            biggest = max(biggest, w.numel())
+        small_layout = FlatLayout(keep)
+        small = torch.empty(small_layout.n_total, device=self.base.device, dtype=torch.bfloat16)
+        for s_ in keep:
+            small_layout.view(small, s_.name).copy_(full[s_.name])
+        for name in names:
+            del self.p[name]
+        self.base_layout, self.base = small_layout, small
+        self.p.update(small_layout.views(small))
+        self._wq_scratch = torch.empty(biggest, device=small.device, dtype=torch.bfloat16)
+
+    def _w(self, name: str) -> torch.Tensor:
+        """The bf16 weight of a projection: the parameter itself, or the NF4 base decoded into the scratch buffer (valid until
+        the next call)."""
+        q = getattr(self, "q", None)
+        if not q or name not in q:
+            return self.p[name]
+        codes, absmax = q[name]
+        out = self._wq_scratch[:codes.numel() * 2]
+        self.I.dequant_nf4(codes, absmax, self.cfg.nf4_group, out=out)
+        return out.view(codes.shape[0], codes.shape[1] * 2)
+
+    def base_bytes(self) -> int:
+        """Bytes the frozen base occupies on the device (bf16 tensors + NF4 codes and scales + the decode scratch)."""
+        if not self.lora:
+            return 0
+        n = self.base.numel() * 2
+        for codes, absmax in self.q.values():
+            n += codes.numel() + absmax.numel() * 4
+        return n + (self._wq_scratch.numel() * 2 if self.q else 0)
+
     def load_base(self, tensors: dict[str, torch.Tensor]) -> None:
-        """Replace the frozen base weights (names and shapes of ``base_param_specs``)."""
+        """Replace the frozen base weights (names and shapes of ``base_param_specs``); projections are re-quantised when the
+        base is NF4."""
         if not self.lora:
             raise RuntimeError("load_base() is for LoRA engines; full fine-tuning loads weights through the trainer")
-        for s in self.base_layout.order:
+        from ..tensor.stages_linear import nf4_quantize
+        for s in self.cfg.base_param_specs():
             if tuple(tensors[s.name].shape) != tuple(s.shape):
                 raise ValueError(f"{s.name}: shape {tuple(tensors[s.name].shape)} instead of {tuple(s.shape)}")
-            self.base_layout.view(self.base, s.name).copy_(tensors[s.name])
+            if s.name in self.q:
+                w = tensors[s.name].to(self.base.device)
+                parts = [nf4_quantize(w[r0:r0 + 1024], self.cfg.nf4_group) for r0 in range(0, w.shape[0], 1024)]
+                self.q[s.name][0].copy_(torch.cat([c for c, _ in parts]))
+                self.q[s.name][1].copy_(torch.cat([a for _, a in parts]))
+            else:
+                self.base_layout.view(self.base, s.name).copy_(tensors[s.name])
 
     @torch.no_grad()
     def merged_state(self) -> dict[str, torch.Tensor]:
         """Base weights with the adapters folded in (W + alpha / r * B A), on the host, fp32."""
         out = {s.name: self.base_layout.view(self.base, s.name).float().cpu() for s in self.base_layout.order} if self.lora else \
               {k: v.float().cpu() for k, v in self.p.items()}
+        for name in getattr(self, "q", {}):
+            out[name] = self._w(name).float().cpu()
         if self.lora:
             for name in list(out):
                 if name + ".lora_a" in self.p:
@@ -425,26 +511,40 @@ class GlimmerEngine:
 
     def _proj(self, x, name: str, out, acts: dict, key: str):
         """out = x W^T (+ alpha / r * (x A^T) B^T when the projection carries an adapter)."""
-        self.gemm(x, self.p[name], out=out)
+        self.gemm(x, self._w(name), out=out)
         if self.lora and name + ".lora_a" in self.p:
             t = acts["t_" + key]
-            self.gemm(x, self.p[name + ".lora_a"], out=t)
+            self.gemm(self._dropped(x, name), self.p[name + ".lora_a"], out=t)
             self.gemm(t, self.p[name + ".lora_b"], alpha=self.lora_scale, resid=out, out=out)
         return out
 
     def _proj_backward(self, dy, x, name: str, dx_out, acts: dict, key: str):
         """dx_out = dy W (+ adapter path); weight gradients of whatever is trainable."""
         gemm, p, g = self.gemm, self.p, self.g
-        gemm(dy, p[name], b_mn=True, out=dx_out)
+        gemm(dy, self._w(name), b_mn=True, out=dx_out)
         if not self.lora:
             gemm(dy, x, a_mn=True, b_mn=True, workspace=self.ws, out=g[name])
         elif name + ".lora_a" in p:
             t, s = acts["t_" + key], self.lora_scale
             gemm(dy, p[name + ".lora_b"], b_mn=True, alpha=s, out=self.d_t)                          # [N, r] = s * dy B
             gemm(dy, t, a_mn=True, b_mn=True, alpha=s, workspace=self.ws, out=g[name + ".lora_b"])  # [out, r] = s * dy^T t
-            gemm(self.d_t, x, a_mn=True, b_mn=True, workspace=self.ws, out=g[name + ".lora_a"])     # [r, in] = d_t^T x
-            gemm(self.d_t, p[name + ".lora_a"], b_mn=True, resid=dx_out, out=dx_out)                # + d_t A
+            gemm(self.d_t, self._dropped(x, name), a_mn=True, b_mn=True, workspace=self.ws, out=g[name + ".lora_a"])   # [r, in] = d_t^T drop(x)
+            if self.drop_on:
+                dxd = self.drop_dx[:, :x.shape[1]]
+                gemm(self.d_t, p[name + ".lora_a"], b_mn=True, out=dxd)                              # d drop(x) = d_t A
+                self.K.dropout_apply(dxd, dx_out, self.drop_p, seed=self.cfg.base_seed, stream_id=self.drop_ids[name], step=self.drop_step,
+                                     accumulate=True)                                                 # dx += mask * d drop(x) / (1 - p)
+            else:
+                gemm(self.d_t, p[name + ".lora_a"], b_mn=True, resid=dx_out, out=dx_out)            # + d_t A
         return dx_out
+
+    def _dropped(self, x: torch.Tensor, name: str) -> torch.Tensor:
+        """The adapter branch's input: x itself, or x under this pass's dropout mask of projection ``name`` (in a scratch buffer
+        valid until the next call)."""
+        if not self.drop_on:
+            return x
+        xd = self.drop_x[:, :x.shape[1]]
+        return self.K.dropout_apply(x, xd, self.drop_p, seed=self.cfg.base_seed, stream_id=self.drop_ids[name], step=self.drop_step)
 
     def _gw(self, name: str):
         """Gradient slot of a base tensor: None (= not computed) when only adapters train."""
@@ -492,6 +592,9 @@ class GlimmerEngine:
         B, T, N = self.B, self.T, self.B * self.T
         Hq, Hkv, hd, Fd = cfg.n_head, cfg.n_kv_head, cfg.head_dim, cfg.d_ff
         rms = dict(mode=K.NORM_RMS, mean=self.mean_scratch)
+        self.drop_on = self.drop_p > 0.0 and compute_grad_logits              # adapter dropout: training passes only
+        if self.drop_on:
+            K.counter_add(self.drop_step.view(torch.int32)[:1], 1)           # new masks for this pass, also when a graph replays it
         if cfg.pp_first:
             K.embedding_forward(self.tokens, p["tok_embeddings"], None, T=T, out=self.xe)
             K.norm_forward(self.xe, self.ones, None, eps=cfg.norm_eps, out=self.x0, rstd=self.re, **rms)

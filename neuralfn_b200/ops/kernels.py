@@ -130,6 +130,18 @@ def qk_norm_backward(dqkv, qkv_normed, rstd, n_q_heads: int, n_kv_heads: int, he
     _lib.check(rc, "nfn_qk_norm_backward")
 
 
+# ----------------------------------------------------------------- dropout --
+def dropout_apply(x, out, p: float, *, seed: int, stream_id: int, step=None, accumulate: bool = False):
+    """out (+)= mask * x / (1 - p); the mask is a function of (seed, stream_id, step[0], row, column) and is never stored: the same
+    call reproduces it. x / out bf16 [rows, width] views with free row strides; ``step`` an int64 device tensor or None."""
+    from ctypes import c_ulonglong
+    rc = _lib.load().nfn_dropout_apply(_p(x), c_int(x.stride(0)), _p(out), c_int(out.stride(0)), c_longlong(x.shape[0]), c_int(x.shape[1]),
+                                       c_float(float(p)), c_ulonglong(int(seed) & (2**64 - 1)), c_int(int(stream_id)), _p(step),
+                                       c_int(int(accumulate)), _st())
+    _lib.check(rc, "nfn_dropout_apply")
+    return out
+
+
 # ------------------------------------------------------------ gated attention --
 def sigmoid_gate_forward(att, gate, out):
     """out = att * sigmoid(gate); bf16 [rows, width] views with free row strides."""

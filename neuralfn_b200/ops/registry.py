@@ -51,7 +51,7 @@ KERNELS: tuple[KernelEntry, ...] = (
     _k("cross_entropy", "nfn_cross_entropy", ("bf16",), False, "soft-cap derivative, z-loss, in-place gradient"),
     _k("embedding forward", "nfn_embedding_forward"), _k("embedding backward", "nfn_embedding_backward"), _k("embedding backward, sorted tokens (deterministic)", "nfn_embedding_backward_sorted"),
     _k("embedding + positions", "nfn_embedding_positions"), _k("swiglu", "nfn_swiglu_forward"), _k("swiglu backward", "nfn_swiglu_backward"),
-    _k("sigmoid gate", "nfn_sigmoid_gate_inplace"), _k("bias gradient (column sum)", "nfn_colsum"),
+    _k("dropout (counter-based, adapter branch)", "nfn_dropout_apply"), _k("sigmoid gate", "nfn_sigmoid_gate_inplace"), _k("bias gradient (column sum)", "nfn_colsum"),
     _k("adamw (flat, clip on device)", "nfn_adamw_flat", ("fp32 master", "bf16 params")), _k("grad clip scale", "nfn_grad_clip_scale"),
     _k("grad accumulate", "nfn_grad_accumulate"),
     _k("dp reduce + sharded adamw + all-gather", "nfn_dp_adamw", ("bf16", "fp32"), False, "peer loads, owner update, parameter push"),

@@ -281,17 +281,18 @@ def test_ppo_update_objective_matches_autograd(kernel_lib):
 
 
 @pytest.mark.gpu
-def test_lora_adapters_match_autograd_on_the_merged_weights(kernel_lib):
+@pytest.mark.parametrize("base_quant", ["", "nf4"])
+def test_lora_adapters_match_autograd_on_the_merged_weights(kernel_lib, base_quant):
     from neuralfn_b200.models.glimmer import GlimmerEngine, glimmer_reference_loss
     from neuralfn_b200.models.gpt2 import FlatLayout
     from neuralfn_b200.ops import _lib
-    cfg = _cfg(lora_rank=16, lora_alpha=24.0)
+    cfg = _cfg(lora_rank=16, lora_alpha=24.0, base_quant=base_quant)
     layout = FlatLayout(cfg.param_specs())
     g = torch.Generator(device="cuda").manual_seed(5)
     params = (torch.randn(layout.n_total, device="cuda", generator=g) * 0.05).to(torch.bfloat16)     # A and B both non-zero
     grads = torch.full_like(params, 7.0)                                                             # every slot must be overwritten
     eng = GlimmerEngine(cfg, layout, params, grads, 4, 128)
-    assert set(eng.g) == {s.name for s in cfg.param_specs()} and "layers.0.wo" in eng.p and "layers.0.wo" not in eng.g
+    assert set(eng.g) == {s.name for s in cfg.param_specs()} and ("layers.0.wo" in eng.p) == (not base_quant) and "layers.0.wo" not in eng.g
     tok = torch.randint(0, cfg.vocab_size, (4, 128), device="cuda", generator=g)
     tgt = torch.roll(tok, -1, 1)
     eng.set_batch(tok, tgt)
@@ -300,6 +301,16 @@ def test_lora_adapters_match_autograd_on_the_merged_weights(kernel_lib):
     _lib.assert_status_ok("glimmer lora engine")
     adapters = {k: v.float().clone().requires_grad_(True) for k, v in layout.views(params).items()}
     merged = {k: v.float() for k, v in eng.base_layout.views(eng.base).items()}
+    if base_quant:
+        # the frozen projections are NF4 codes: no bf16 copy is left, the oracle uses what the codes decode to, and the base
+        # takes well under half of its bf16 size (embedding, head and norms stay bf16)
+        from neuralfn_b200.tensor.stages_linear import nf4_dequantize
+        assert "layers.0.wo" not in merged and len(eng.q) == 4 * cfg.n_layer
+        for name, (codes, absmax) in eng.q.items():
+            merged[name] = nf4_dequantize(codes, absmax, cfg.nf4_group).to(torch.bfloat16).float()
+        plain = sum(int(torch.tensor(sp.shape).prod()) for sp in cfg.base_param_specs()) * 2
+        proj = sum(c.numel() * 2 for c, _ in eng.q.values()) * 2
+        assert eng.base_bytes() < plain - 0.3 * proj
     for name in list(merged):
         if name + ".lora_a" in adapters:
             merged[name] = merged[name] + eng.lora_scale * adapters[name + ".lora_b"] @ adapters[name + ".lora_a"]
@@ -310,6 +321,54 @@ def test_lora_adapters_match_autograd_on_the_merged_weights(kernel_lib):
     # folding the adapters in gives the same model
     folded = eng.merged_state()
     assert (folded["layers.1.w_down"] - merged["layers.1.w_down"].detach().cpu()).abs().max() < 1e-2
+
+
+@pytest.mark.gpu
+def test_adapter_dropout_masks_are_reproduced_in_the_backward_pass(kernel_lib):
+    """The mask is a function of (seed, projection, step word): the kernel reproduces it on demand, keeps ~(1 - p) of the values scaled
+    by 1 / (1 - p), differs between projections and passes, and the projection's forward / backward pair equals autograd on
+    y = x W^T + s * (mask * x / (1 - p)) A^T B^T with that mask."""
+    from neuralfn_b200.models.glimmer import GlimmerEngine
+    from neuralfn_b200.models.gpt2 import FlatLayout
+    from neuralfn_b200.ops import kernels as K
+    pdrop = 0.25
+    cfg = _cfg(lora_rank=16, lora_alpha=24.0, lora_dropout=pdrop)
+    layout = FlatLayout(cfg.param_specs())
+    g = torch.Generator(device="cuda").manual_seed(5)
+    params = (torch.randn(layout.n_total, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    grads = torch.zeros_like(params)
+    eng = GlimmerEngine(cfg, layout, params, grads, 4, 128)
+    name, N = "layers.1.w_down", 4 * 128
+    sid, ones = eng.drop_ids[name], torch.ones(N, cfg.d_ff, device="cuda", dtype=torch.bfloat16)
+    mask = lambda s, step: K.dropout_apply(ones, torch.empty_like(ones), pdrop, seed=cfg.base_seed, stream_id=s, step=step).float()  # noqa: E731
+    step = torch.full((1,), 3, device="cuda", dtype=torch.int64)
+    m = mask(sid, step)
+    assert torch.equal(m, mask(sid, step)) and set(m.unique().tolist()) == {0.0, float(torch.tensor(1 / (1 - pdrop)).bfloat16())}
+    assert abs(float((m > 0).float().mean()) - (1 - pdrop)) < 0.01
+    assert not torch.equal(m, mask(sid + 1, step)) and not torch.equal(m, mask(sid, step + 1))
+    # one projection, forward and backward, against autograd with the mask of the engine's current step word
+    eng.drop_on = True
+    eng.drop_step.fill_(11)
+    m = mask(sid, eng.drop_step) * (1 - pdrop)                       # 0 / 1
+    x = (torch.randn(N, cfg.d_ff, device="cuda", generator=g) * 0.5).bfloat16()
+    dy = (torch.randn(N, cfg.d_model, device="cuda", generator=g) * 0.5).bfloat16()
+    acts = {"t_w_down": torch.empty(N, cfg.lora_rank, device="cuda", dtype=torch.bfloat16)}
+    y = eng._proj(x, name, torch.empty(N, cfg.d_model, device="cuda", dtype=torch.bfloat16), acts, "w_down")
+    dx = eng._proj_backward(dy, x, name, torch.empty_like(x), acts, "w_down")
+    xr = x.float().requires_grad_(True)
+    A, B = (eng.p[name + s].float().clone().requires_grad_(True) for s in (".lora_a", ".lora_b"))
+    ref = xr @ eng.p[name].float().t() + eng.lora_scale * ((xr * m / (1 - pdrop)) @ A.t()) @ B.t()
+    ref.backward(dy.float())
+    rel = lambda a, b: float((a.float() - b).norm() / (b.norm() + 1e-9))  # noqa: E731
+    assert rel(y, ref.detach()) < 2e-2 and rel(dx, xr.grad) < 2e-2
+    assert rel(eng.g[name + ".lora_a"], A.grad) < 3e-2 and rel(eng.g[name + ".lora_b"], B.grad) < 3e-2
+    # a training pass advances the step word, an evaluation pass neither advances it nor drops anything
+    tok = torch.randint(0, cfg.vocab_size, (4, 128), device="cuda", generator=g)
+    eng.set_batch(tok, torch.roll(tok, -1, 1))
+    a = float(eng.forward(compute_grad_logits=False)); b = float(eng.forward(compute_grad_logits=False))
+    assert a == b and int(eng.drop_step) == 11
+    c = float(eng.forward()); eng.backward(); d = float(eng.forward())
+    assert int(eng.drop_step) == 13 and c != d
 
 
 @pytest.mark.gpu
