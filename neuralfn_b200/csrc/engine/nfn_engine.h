@@ -62,6 +62,10 @@ void nfn_engine_destroy(nfn_engine* e);
 // Copies one bf16 tensor to the device under `name` (replacing any earlier one).
 int nfn_engine_set_tensor(nfn_engine* e, const char* name, const void* host_bf16, long long numel);
 // Names the engine expects for its configuration, '\n'-separated "name numel" lines.
+// A projection weight kept resident in its K-quant blocks (qtype 12 / 13 / 14 = Q4_K / Q5_K / Q6_K, the GGUF row layout).
+// Products with up to eight rows read the blocks directly (quantised GEMV); larger ones decode the tensor into one shared
+// bf16 scratch buffer first. Before nfn_engine_finalize; embeddings, norms and biases stay bf16.
+int nfn_engine_set_tensor_kquant(nfn_engine* e, const char* name, int qtype, const void* host_blocks, long long nbytes, long long numel);
 int nfn_engine_expected_tensors(const nfn_engine* e, char* buf, int cap);
 // Loads a dense GPT checkpoint (model_%08d.bin, version 5) into a family-0 engine.
 int nfn_engine_load_dense_v5(nfn_engine* e, const char* path);

@@ -64,6 +64,7 @@ int efail(const std::string& m) {
 struct DevTensor {
   void* ptr = nullptr;
   long long numel = 0;
+  int qtype = 0;  // 0: bf16 values; NFN_QTYPE_Q4_K / Q5_K / Q6_K: packed super-blocks of 256 values, rows back to back
 };
 
 struct StepIO {  // layout of the pinned per-step block; device mirror has the same layout
@@ -123,6 +124,11 @@ struct nfn_engine {
   int* tq_idx = nullptr;                  // prompt scratch: sequence, local-ring slot and global slot of every prompt row
   std::vector<int> tap_layers;
   std::vector<void*> taps;                // per tap [max_batch][max_seq][d_model] bf16
+  // K-quant resident projections: packed pointer -> type; products with more rows than the quantised GEMV takes decode the
+  // tensor into wq_scratch (bf16, sized for the largest one) first
+  std::map<const void*, int> qtype_of;
+  long long wq_max_numel = 0;
+  void* wq_scratch = nullptr;
 
   int alloc(void** p, long long nbytes) {
     CU(cudaMalloc(p, (size_t)nbytes));
@@ -188,6 +194,19 @@ void build_expected(nfn_engine& e) {
 // C[M, N] = A[M, K] . B[N, K]^T with the epilogue selected by flags
 int gemm(nfn_engine& e, const void* a, int lda, const void* b, void* cdst, int ldc, int m, int n, int k, int flags, const void* bias,
          const void* resid, int ld_resid, float act_param = 0.f, float alpha = 1.f) {
+  if (!e.qtype_of.empty()) {
+    const auto it = e.qtype_of.find(b);
+    if (it != e.qtype_of.end()) {
+      // a K-quant resident weight: up to eight rows with a bias / residual epilogue go to the quantised GEMV, which reads
+      // the packed blocks once; everything else decodes the tensor into the scratch buffer and runs the bf16 product on it
+      if (m <= 8 && flags == 0 && alpha == 1.f && (k % 256) == 0) {
+        K(nfn_kquant_gemv(it->second, b, nullptr, a, lda, cdst, ldc, bias, resid, ld_resid, m, n, k, e.stream));
+        return 0;
+      }
+      K(nfn_dequant_kquant(it->second, b, (long long)n * (k / 256), e.wq_scratch, e.stream));
+      b = e.wq_scratch;
+    }
+  }
   nfn_gemm_args g{};
   g.a = a; g.b = b; g.c = cdst;
   g.m = m; g.n = n; g.k = k;
@@ -447,6 +466,7 @@ void nfn_engine_destroy(nfn_engine* e) {
     if (p) cudaFree(p);
   for (void* p : e->kc) cudaFree(p);
   for (void* p : e->vc) cudaFree(p);
+  if (e->wq_scratch) cudaFree(e->wq_scratch);
   if (e->h_io) cudaFreeHost(e->h_io);
   if (e->stream) cudaStreamDestroy(e->stream);
   delete e;
@@ -461,12 +481,54 @@ int nfn_engine_set_tensor(nfn_engine* e, const char* name, const void* host_bf16
   if (want < 0) return efail(std::string("engine_set_tensor: this configuration has no tensor named ") + name);
   if (want != numel) return efail(std::string("engine_set_tensor: ") + name + " has " + std::to_string(numel) + " elements, expected " + std::to_string(want));
   DevTensor& t = e->w[name];
+  if (t.qtype) return efail(std::string("engine_set_tensor: ") + name + " holds K-quant blocks");
   if (!t.ptr) {
     if (e->alloc(&t.ptr, numel * 2)) return -1;
     t.numel = numel;
   }
   CU(cudaMemcpyAsync(t.ptr, host_bf16, (size_t)numel * 2, cudaMemcpyHostToDevice, e->stream));
   CU(cudaStreamSynchronize(e->stream));
+  return 0;
+}
+
+// A projection weight kept in its K-quant blocks (Q4_K / Q5_K / Q6_K: `numel` values = rows of K / 256 super-blocks, rows back
+// to back, the GGUF layout). Only 2-D projection weights qualify (the embedding is gathered, norms and biases are vectors);
+// the row length must be a multiple of 256.
+int nfn_engine_set_tensor_kquant(nfn_engine* e, const char* name, int qtype, const void* host_blocks, long long nbytes, long long numel) {
+  if (!e || !name || !host_blocks || numel <= 0) return efail("engine_set_tensor_kquant: bad arguments");
+  if (e->finalized) return efail("engine_set_tensor_kquant: call before nfn_engine_finalize");
+  const int bb = nfn_quant_block_bytes(qtype);
+  if (bb <= 0 || qtype == NFN_QTYPE_NF4) return efail("engine_set_tensor_kquant: qtype must be Q4_K, Q5_K or Q6_K");
+  const std::string n = name;
+  auto ends = [&](const char* suf) { const std::string s2 = suf; return n.size() >= s2.size() && n.compare(n.size() - s2.size(), s2.size(), s2) == 0; };
+  const nfn_engine_config& c = e->c;
+  long long row = 0;  // the contraction length of the product that reads this tensor
+  if (c.family == 1) {
+    if (ends(".wqkv") || ends(".w_gate_up") || n == "lm_head") row = c.d_model;
+    else if (ends(".wo")) row = (long long)c.n_head * c.head_dim;
+    else if (ends(".w_down")) row = c.d_ff;
+  } else {
+    if (ends("attn.c_attn.weight") || ends("mlp.c_fc.weight")) row = c.d_model;
+    else if (ends("attn.c_proj.weight")) row = (long long)c.n_head * c.head_dim;
+    else if (ends("mlp.c_proj.weight")) row = c.d_ff;
+  }
+  if (row <= 0) return efail("engine_set_tensor_kquant: " + n + " is not a projection weight (embeddings, norms and biases stay bf16)");
+  if (row % 256) return efail("engine_set_tensor_kquant: " + n + " has rows of " + std::to_string(row) + " values, K-quant needs a multiple of 256");
+  long long want = -1;
+  for (const auto& kv : e->expected)
+    if (kv.first == n) want = kv.second;
+  if (want < 0) return efail("engine_set_tensor_kquant: this configuration has no tensor named " + n);
+  if (want != numel || nbytes != numel / 256 * bb) return efail("engine_set_tensor_kquant: " + n + " has the wrong size");
+  CU(cudaSetDevice(e->device));
+  DevTensor& t = e->w[n];
+  if (t.ptr) return efail("engine_set_tensor_kquant: " + n + " is already set");
+  if (e->alloc(&t.ptr, nbytes)) return -1;
+  t.numel = numel;
+  t.qtype = qtype;
+  CU(cudaMemcpyAsync(t.ptr, host_blocks, (size_t)nbytes, cudaMemcpyHostToDevice, e->stream));
+  CU(cudaStreamSynchronize(e->stream));
+  e->qtype_of[t.ptr] = qtype;
+  e->wq_max_numel = std::max(e->wq_max_numel, numel);
   return 0;
 }
 
@@ -526,6 +588,7 @@ int nfn_engine_finalize(nfn_engine* e) {
   CU(cudaSetDevice(e->device));
   for (const auto& kv : e->expected)
     if (!e->has(kv.first)) return efail("engine_finalize: missing tensor " + kv.first);
+  if (e->wq_max_numel > 0 && e->alloc(&e->wq_scratch, e->wq_max_numel * 2)) return -1;
   const nfn_engine_config& c = e->c;
   const int HD = c.head_dim;
   e->qkv_ld = (c.n_head + 2 * c.n_kv_head) * HD + ((c.family == 1 && c.gated_attention) ? c.n_head * HD : 0);

@@ -126,6 +126,7 @@ def _api():
     L.nfn_engine_create.restype, L.nfn_engine_create.argtypes = vp, [C.POINTER(_CConfig), ip]
     L.nfn_engine_destroy.restype, L.nfn_engine_destroy.argtypes = None, [vp]
     L.nfn_engine_set_tensor.argtypes = [vp, C.c_char_p, vp, C.c_longlong]
+    L.nfn_engine_set_tensor_kquant.argtypes = [vp, C.c_char_p, ip, vp, C.c_longlong, C.c_longlong]
     L.nfn_engine_expected_tensors.argtypes = [vp, C.c_char_p, ip]
     L.nfn_engine_load_dense_v5.argtypes = [vp, C.c_char_p]
     L.nfn_engine_finalize.argtypes = [vp]
@@ -158,10 +159,11 @@ def resident_inference_capabilities() -> dict:
     return {"abi_version": resident_inference_abi_version(), "families": ["gpt2", "llama"], "kv_cache": "bf16",
             "hybrid_local_global": True, "qk_norm": True, "rope": ["hf", "legacy"], "continuous_batching": True,
             "cuda_graph_decode": True, "on_device_sampling": ["greedy", "temperature", "top_k", "top_p"],
-            # the engine executes bf16 weights only: K-quant / NF4 checkpoints are dequantised at load time
-            # (``quant.kquant`` / ``checkpoint.gguf``); the packed-weight kernels are not wired into it
+            # projection weights may stay resident in K-quant blocks (``set_tensor_kquant``: quantised GEMV for up to eight rows,
+            # decode-then-GEMM beyond); NF4 checkpoints are dequantised at load time; there is no int8-activation MMQ path
             "block_verification": True, "hidden_state_taps": True, "gpt2_mlp_activations": sorted(EngineConfig.MLP_ACTIVATION_IDS),
-            "kv_cache_modes": ["bf16", "turboquant-3.5 (decode only)"], "quantized_weights": [], "weight_dtypes": ["bf16"], "dequantised_at_load": ["Q4_K", "Q5_K", "Q6_K", "NF4"]}
+            "kv_cache_modes": ["bf16", "turboquant-3.5 (decode only)"], "quantized_weights": ["Q4_K", "Q5_K", "Q6_K"], "weight_dtypes": ["bf16", "k-quant projections (set_tensor_kquant)"],
+            "dequantised_at_load": ["NF4"]}
 
 
 class EngineError(RuntimeError):
@@ -230,8 +232,29 @@ class ResidentEngine:
         t = t.detach().to("cpu", torch.bfloat16).contiguous()
         self._check(self._L.nfn_engine_set_tensor(self._h, name.encode(), t.data_ptr(), t.numel()))
 
-    def load_named_tensors(self, tensors: dict[str, torch.Tensor]) -> None:
+    QTYPES = {"Q4_K": 12, "Q5_K": 13, "Q6_K": 14}
+
+    def set_tensor_kquant(self, name: str, qtype: int | str, blocks: torch.Tensor) -> None:
+        """Keeps projection weight ``name`` resident in its K-quant blocks (uint8, rows of K / 256 super-blocks back to back - the
+        GGUF layout). Decode-sized products (up to eight rows) read the blocks directly; larger ones decode the tensor into one
+        shared bf16 scratch buffer first. Embeddings, norms and biases stay bf16.
+
+        Reference counterpart: the K-quant resident weights of ``resident_glimmer_cuda.cpp`` (``weight_precision k-quant-*``)."""
+        from ..ops.infer import quant_block_bytes
+        q = self.QTYPES[qtype] if isinstance(qtype, str) else int(qtype)
+        b = blocks.detach().to("cpu", torch.uint8).contiguous().reshape(-1)
+        numel = b.numel() // quant_block_bytes(q) * 256
+        self._check(self._L.nfn_engine_set_tensor_kquant(self._h, name.encode(), q, b.data_ptr(), b.numel(), numel))
+
+    def load_named_tensors(self, tensors: dict[str, torch.Tensor], quantized: dict[str, tuple] | None = None) -> None:
+        """``quantized``: name -> (qtype, uint8 blocks) for projection weights that stay in K-quant form; those names need no
+        entry in ``tensors``."""
+        quantized = quantized or {}
+        for name, (qtype, blocks) in quantized.items():
+            self.set_tensor_kquant(name, qtype, blocks)
         for name, numel in self.expected_tensors().items():
+            if name in quantized:
+                continue
             if name not in tensors:
                 raise EngineError(f"missing tensor {name!r}")
             t = tensors[name]

@@ -405,3 +405,53 @@ def test_turboquant_cache_mode_decodes_close_to_the_bf16_cache():
     ref.close()
     tq.close()
     assert torch.isfinite(l0).all() and torch.isfinite(l1).all()
+
+
+def test_projection_weights_stay_resident_in_k_quant_blocks():
+    """Q4_K / Q6_K blocks loaded as they are: prompts (decode the tensor into the scratch buffer, then the bf16 product) and decode
+    steps (quantised GEMV straight from the blocks) agree with an engine that holds the decoded values in bf16; the packed
+    engine is smaller; only projection weights qualify."""
+    import numpy as np
+
+    from neuralfn_b200.quant import kquant
+    from neuralfn_b200.serving import EngineConfig, ResidentEngine
+    from neuralfn_b200.serving.engine import EngineError
+    cfg = EngineConfig(family=1, n_layer=3, d_model=256, n_head=4, n_kv_head=2, head_dim=64, d_ff=512, vocab=777, padded_vocab=784,
+                       max_seq=160, max_batch=4, qk_norm=2, rope_hf=1, rope_theta=10000.0, norm_eps=1e-5, tie_embeddings=0)
+    plain, packed = ResidentEngine(cfg), ResidentEngine(cfg)
+    g = torch.Generator().manual_seed(5)
+    dense, quant = {}, {}
+    for i, (name, numel) in enumerate(plain.expected_tensors().items()):
+        leaf = name.rsplit(".", 1)[-1]
+        if leaf in ("wqkv", "wo", "w_gate_up", "w_down", "lm_head"):
+            qt = 14 if leaf in ("w_down", "lm_head") else 12
+            raw = kquant.random_blocks(qt, numel // 256, seed=i)
+            small = np.random.default_rng(i).uniform(2e-5, 1.5e-4, numel // 256).astype(np.float16).view(np.uint8).reshape(-1, 2)
+            if qt == 12:
+                raw[:, 0:2], raw[:, 2:4] = small, small
+            else:
+                raw[:, 208:210] = np.random.default_rng(i).uniform(5e-6, 2e-5, numel // 256).astype(np.float16).view(np.uint8).reshape(-1, 2)
+            quant[name] = (qt, torch.from_numpy(raw.copy()))
+            dense[name] = torch.from_numpy(kquant.dequantize(qt, raw).astype(np.float32)).bfloat16()
+        else:
+            dense[name] = ((1 + 0.1 * torch.randn(numel, generator=g)) if name.endswith("norm") else torch.randn(numel, generator=g) * 0.05).bfloat16()
+    plain.load_named_tensors(dense)
+    with pytest.raises(EngineError):
+        packed.set_tensor_kquant("tok_embeddings", "Q4_K", torch.zeros(784 * 144, dtype=torch.uint8))
+    packed.load_named_tensors({k: v for k, v in dense.items() if k not in quant}, quantized=quant)
+    assert packed.device_bytes < plain.device_bytes
+    a = plain.prefill(0, PROMPT)
+    b = packed.prefill(0, PROMPT)
+    la, lb = plain.last_logits(0), packed.last_logits(0)
+    scale = float(la.abs().max())
+    assert float((la - lb).abs().max()) < 0.02 * scale and scale > 0.05
+    for _ in range(8):
+        # both engines continue with the plain engine's token, so their caches stay comparable
+        b = packed.decode({0: a})[0]
+        a2 = plain.decode({0: a})[0]
+        la, lb = plain.last_logits(0), packed.last_logits(0)
+        assert float((la - lb).abs().max()) < 0.04 * float(la.abs().max())
+        if a2 != b:
+            assert abs(float(la[a2] - la[b])) < 0.05 * float(la.abs().max())
+        a = a2
+    plain.close(); packed.close()
