@@ -92,6 +92,36 @@ def case_skinny(args):
     return out
 
 
+def case_grouped_k(args):
+    """Weight gradients of all experts of an MoE layer (d = --k columns of the token buffer, hidden --n, --experts experts, --m rows
+    in the expert-sorted buffer, split unevenly): one grouped launch against one TN GEMM per expert."""
+    from neuralfn_b200.ops.gemm import gemm, gemm_grouped_k
+    dev = torch.device("cuda")
+    E, rows_total, d, h = args.experts, args.m, args.k, args.n
+    g = torch.Generator(device=dev).manual_seed(0)
+    w = torch.rand(E, device=dev, generator=g) + 0.2
+    counts = (w / w.sum() * rows_total * 0.97).int().tolist()
+    offs = [0]
+    for c in counts:
+        offs.append(offs[-1] + (c + 127) // 128 * 128)
+    xs = torch.zeros(offs[-1], d, device=dev, dtype=torch.bfloat16)
+    dh = (torch.randn(offs[-1], h, device=dev, generator=g) * 0.1).bfloat16()
+    for e, c in enumerate(counts):
+        xs[offs[e]:offs[e] + c] = (torch.randn(c, d, device=dev, generator=g) * 0.1).bfloat16()
+    group_rows = torch.tensor(offs, device=dev, dtype=torch.int32)
+    dw = torch.empty(E, d, h, device=dev, dtype=torch.bfloat16)
+    flops = 2.0 * sum(counts) * d * h
+
+    def loop():
+        for e, c in enumerate(counts):
+            gemm(xs[offs[e]:offs[e] + c], dh[offs[e]:offs[e] + c], a_mn=True, b_mn=True, out=dw[e])
+    extra = {"experts": E, "rows": offs[-1], "d": d, "h": h}
+    out = [_report("grouped_k", time_kernel(lambda: gemm_grouped_k(xs, dh, group_rows, dw), args.iters, args.warmup, args.flush), flops=flops, args=args, extra=extra)]
+    if not args.no_baseline:
+        out.append(_report("per_expert_loop", time_kernel(loop, args.iters, args.warmup, args.flush), flops=flops, args=args, extra=extra))
+    return out
+
+
 def case_attention(args, backward=False):
     from neuralfn_b200.ops import kernels as K
     dev = torch.device("cuda")
@@ -278,7 +308,7 @@ def case_engine_decode(args):
 
 CASES = {"gemm": case_gemm, "attention_fwd": case_attention, "attention_bwd": lambda a: case_attention(a, True),
          "cross_entropy": case_cross_entropy, "norm": case_norm, "adamw": case_adamw, "decode_attention": case_decode_attention,
-         "skinny": case_skinny, "kquant_gemv": case_kquant_gemv, "gemm_kquant": case_gemm_kquant, "block_attention": case_block_attention,
+         "skinny": case_skinny, "grouped_k": case_grouped_k, "kquant_gemv": case_kquant_gemv, "gemm_kquant": case_gemm_kquant, "block_attention": case_block_attention,
          "turboquant_attention": case_turboquant_attention, "engine_decode": case_engine_decode}
 
 
@@ -313,6 +343,8 @@ def main(argv=None):
     ap.add_argument("--vocab", type=int, default=50257)
     ap.add_argument("--params", type=int, default=124 * 1000 * 1000)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--experts", type=int, default=16, help="grouped_k case")
+    ap.add_argument("--no-baseline", action="store_true", help="grouped_k case: skip the per-expert loop (profiler captures)")
     ap.add_argument("--skinny-impl", type=int, default=-1, help="gemm case: nfn_gemm_skinny_set_impl mode for products with 3 - 64 rows (-1: the default)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--peak-tflops", type=float, default=0.0, help="measured bf16 GEMM peak to report fractions against")
