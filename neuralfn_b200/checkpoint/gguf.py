@@ -128,7 +128,7 @@ class GGUFFile:
         """(ggml type, the tensor's bytes as stored): what ``ResidentEngine.set_tensor_kquant`` takes for a Q4_K / Q5_K / Q6_K
         projection weight (rows of K / 256 super-blocks back to back). Row-wise pieces of one type (q | k | v) can be
         concatenated along the rows without decoding."""
-        return self.tensors[name].ggml_type, self.raw(name)
+        return self.tensors[name].ggml_type, self.raw(name).copy()      # a copy: it outlives the mapping
 
     def dequantize(self, name: str) -> np.ndarray:
         """fp32 values in the tensor's logical shape."""

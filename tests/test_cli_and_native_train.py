@@ -112,3 +112,27 @@ def test_migrate_native_cli(tmp_path, capsys):
     assert nfn.main(["migrate-native", str(tmp_path / "g.json"), str(tmp_path / "out"), "--name", "gpt2", "--stop-tokens", "1,2"]) == 0
     out = json.loads(capsys.readouterr().out)
     assert out["status"] == "ok" and out["model"]["family"] in ("gpt", "gpt2") and (tmp_path / "out" / "tensors.bin").is_file()
+
+
+def test_native_adapter_and_objective_flags_reach_the_glimmer_config():
+    """--runtime native --adapter-type qlora / --lora-dropout / --dpo-* become fields of the native Glimmer engine's configuration;
+    other families and unknown adapter kinds are refused before anything is built."""
+    from neuralfn_b200.cli import nfn as cli
+    from neuralfn_b200.native_train import build_model_config
+
+    def parse(*argv):
+        return cli.build_parser().parse_args(["train", *argv])
+
+    geom = ["--base-model", "muse-glimmer", "--n-layer", "2", "--d-model", "256", "--n-head", "4", "--n-kv-head", "2", "--head-dim", "64", "--d-ff", "512",
+            "--vocab-size", "512", "--seq-len", "128"]
+    a = parse(*geom, "--objective", "dpo", "--dpo-beta", "0.25", "--dpo-loss-type", "ipo", "--dpo-label-smoothing", "0.1",
+              "--adapter-type", "qlora", "--lora-rank", "8", "--lora-alpha", "12", "--lora-dropout", "0.05", "--qlora-group-size", "32")
+    cfg = build_model_config(cli._train_config(a))
+    assert (cfg.lora_rank, cfg.lora_alpha, cfg.lora_dropout, cfg.base_quant, cfg.nf4_group) == (8, 12.0, 0.05, "nf4", 32)
+    assert (cfg.dpo_beta, cfg.dpo_loss_type, cfg.dpo_label_smoothing) == (0.25, "ipo", 0.1)
+    plain = build_model_config(cli._train_config(parse(*geom, "--adapter-type", "lora")))
+    assert plain.lora_rank == 16 and plain.base_quant == "" and plain.lora_dropout == 0.0 and plain.dpo_loss_type == "sigmoid"
+    with pytest.raises(ValueError):
+        cli._train_config(parse("--base-model", "llama", "--adapter-type", "lora"))
+    with pytest.raises(ValueError):
+        cli._train_config(parse(*geom, "--adapter-type", "randmap"))

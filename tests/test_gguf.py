@@ -40,3 +40,19 @@ def test_rejects_bad_files(tmp_path):
     (tmp_path / "t.gguf").write_bytes(raw[:-40])
     with pytest.raises(ValueError, match="past the end"):
         GGUFFile(tmp_path / "t.gguf")
+
+
+def test_packed_rows_of_one_type_concatenate_without_decoding(tmp_path):
+    """``packed`` hands out the blocks as stored (what the resident engine keeps for a K-quant projection); the q | k | v pieces of
+    a fused projection are rows of super-blocks, so joining the bytes equals quantising the joined rows."""
+    rng = np.random.default_rng(1)
+    q, k = rng.normal(size=(4, 512)).astype(np.float32), rng.normal(size=(2, 512)).astype(np.float32)
+    write_gguf(tmp_path / "m.gguf", {"general.architecture": "llama"},
+               {"blk.0.attn_q.weight": (12, (4, 512), kquant.quantize_q4_k(q).tobytes()),
+                "blk.0.attn_k.weight": (12, (2, 512), kquant.quantize_q4_k(k).tobytes())})
+    with GGUFFile(tmp_path / "m.gguf") as g:
+        (tq, bq), (tk, bk) = g.packed("blk.0.attn_q.weight"), g.packed("blk.0.attn_k.weight")
+        assert tq == tk == 12 and bq.dtype == np.uint8 and bq.size == 4 * 2 * kquant.BLOCK_BYTES[12]
+        fused = np.concatenate([bq, bk])
+        want = np.concatenate([g.dequantize("blk.0.attn_q.weight"), g.dequantize("blk.0.attn_k.weight")])
+        assert np.array_equal(kquant.dequantize(12, fused).reshape(6, 512), want)
